@@ -1,0 +1,682 @@
+// Binning stages: per-Gaussian tile counting + prefix sum, (tile|depth) key emission, the stable LSD
+// radix sort of the key/value pairs, tile ranges, and the distribution masks / packers that drive the
+// Gaussian all-to-all.  All integer / byte work, HBM-bound.
+//
+// Prefix sum: three launches without any inter-CTA waiting (count + CTA partial sums, one-CTA scan of
+// the partial sums, emit with a CTA-local rescan).  The radix sort keeps digit histograms on chip
+// (per-warp shared-memory counters filled with match.any ballots), again without inter-CTA spin waits:
+// per pass a histogram kernel, a 256-CTA digit-row scan and a scatter kernel that stages each CTA's
+// keys in shared memory so that every digit run leaves as a contiguous burst.
+#include "cgx_common.cuh"
+
+namespace cgx {
+
+// ------------------------------------------------------------------------------------------------ scan
+constexpr int SCAN_ITEMS = 4;                              // Gaussians per thread in count / emit
+constexpr int SCAN_TILE = CGX_BLOCK_SIZE * SCAN_ITEMS;     // Gaussians per CTA
+
+__device__ __forceinline__ uint32_t count_local_tiles(const float2 xy, int radius, const uint8_t* __restrict__ local,
+                                                      int gx, int gy)
+{
+    uint32_t cnt = 0;
+    if (radius > 0) {
+        uint2 rect_min, rect_max;
+        get_rect(xy, radius, rect_min, rect_max, gx, gy);
+        for (int y = rect_min.y; y < rect_max.y; y++)
+            for (int x = rect_min.x; x < rect_max.x; x++)
+                if (local[y * gx + x]) cnt++;
+    }
+    return cnt;
+}
+
+__device__ __forceinline__ uint32_t warp_incl_scan(uint32_t v)
+{
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        uint32_t n = __shfl_up_sync(0xffffffffu, v, d);
+        if ((threadIdx.x & 31) >= d) v += n;
+    }
+    return v;
+}
+
+// Exclusive prefix of `v` over the CTA (256 threads); returns the CTA total through `total`.
+__device__ __forceinline__ uint32_t block_excl_scan(uint32_t v, uint32_t* s_warp /*[8]*/, uint32_t& total)
+{
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    uint32_t incl = warp_incl_scan(v);
+    if (lane == 31) s_warp[warp] = incl;
+    __syncthreads();
+    uint32_t wbase = 0, tot = 0;
+#pragma unroll
+    for (int w = 0; w < CGX_BLOCK_SIZE / 32; w++) {
+        uint32_t s = s_warp[w];
+        if (w < warp) wbase += s;
+        tot += s;
+    }
+    total = tot;
+    __syncthreads();
+    return wbase + incl - v;
+}
+
+__global__ void __launch_bounds__(CGX_BLOCK_SIZE)
+tile_count_kernel(int P, int gx, int gy, const int* __restrict__ radii, const float2* __restrict__ means2D,
+                  const uint8_t* __restrict__ local, uint32_t* __restrict__ tiles_touched,
+                  uint32_t* __restrict__ block_sums)
+{
+    __shared__ uint32_t s_warp[8];
+    const int base = blockIdx.x * SCAN_TILE;
+    uint32_t sum = 0;
+#pragma unroll
+    for (int k = 0; k < SCAN_ITEMS; k++) {
+        const int idx = base + k * CGX_BLOCK_SIZE + threadIdx.x;
+        if (idx < P) {
+            const uint32_t c = count_local_tiles(means2D[idx], radii[idx], local, gx, gy);
+            tiles_touched[idx] = c;
+            sum += c;
+        }
+    }
+    uint32_t total;
+    block_excl_scan(sum, s_warp, total);
+    if (threadIdx.x == 0) block_sums[blockIdx.x] = total;
+}
+
+
+// In-place exclusive scan of row[0..n) by one 1024-thread CTA; returns the row total (valid on every thread).
+__device__ __forceinline__ uint32_t scan_row_inplace(uint32_t* __restrict__ row, int n)
+{
+    __shared__ uint32_t s_warp[32];
+    __shared__ uint32_t s_carry;
+    if (threadIdx.x == 0) s_carry = 0;
+    __syncthreads();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (int start = 0; start < n; start += 1024) {
+        const int i = start + threadIdx.x;
+        const uint32_t v = i < n ? row[i] : 0;
+        uint32_t incl = warp_incl_scan(v);
+        if (lane == 31) s_warp[warp] = incl;
+        __syncthreads();
+        if (warp == 0) {
+            uint32_t w = s_warp[lane];
+            uint32_t wi = warp_incl_scan(w);
+            s_warp[lane] = wi - w;
+        }
+        __syncthreads();
+        const uint32_t excl = s_carry + s_warp[warp] + incl - v;
+        if (i < n) row[i] = excl;
+        __syncthreads();
+        if (threadIdx.x == 1023) s_carry = excl + v;
+        __syncthreads();
+    }
+    return s_carry;
+}
+
+// One CTA: in-place exclusive scan of the CTA partial sums; writes the grand total.
+__global__ void __launch_bounds__(1024)
+scan_partials_kernel(int n, uint32_t* __restrict__ sums, uint32_t* __restrict__ total_out)
+{
+    const uint32_t total = scan_row_inplace(sums, n);
+    if (threadIdx.x == 0) *total_out = total;
+}
+
+__global__ void __launch_bounds__(CGX_BLOCK_SIZE)
+emit_keys_kernel(int P, int gx, int gy, const int* __restrict__ radii, const float2* __restrict__ means2D,
+                 const float* __restrict__ depths, const uint32_t* __restrict__ tiles_touched,
+                 const uint8_t* __restrict__ local, const uint32_t* __restrict__ block_prefix,
+                 uint32_t* __restrict__ point_offsets, uint64_t* __restrict__ keys, uint32_t* __restrict__ values,
+                 uint32_t capacity)
+{
+    __shared__ uint32_t s_warp[8];
+    const int base = blockIdx.x * SCAN_TILE;
+    uint32_t running = block_prefix[blockIdx.x];
+#pragma unroll 1
+    for (int k = 0; k < SCAN_ITEMS; k++) {
+        const int idx = base + k * CGX_BLOCK_SIZE + threadIdx.x;
+        const uint32_t c = idx < P ? tiles_touched[idx] : 0;
+        uint32_t total;
+        uint32_t off = running + block_excl_scan(c, s_warp, total);
+        running += total;
+        if (idx < P) {
+            point_offsets[idx] = off + c;
+            if (c > 0) {
+                const float2 xy = means2D[idx];
+                uint2 rect_min, rect_max;
+                get_rect(xy, radii[idx], rect_min, rect_max, gx, gy);
+                const uint64_t dbits = (uint64_t)__float_as_uint(depths[idx]);
+                for (int y = rect_min.y; y < rect_max.y; y++)
+                    for (int x = rect_min.x; x < rect_max.x; x++)
+                        if (local[y * gx + x]) {
+                            if (off < capacity) {
+                                uint64_t key = y * gx + x;
+                                key <<= 32;
+                                key |= dbits;
+                                keys[off] = key;
+                                values[off] = idx;
+                            }
+                            off++;
+                        }
+            }
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ sort
+constexpr int SORT_THREADS = 256;
+constexpr int SORT_ITEMS = 16;
+constexpr int SORT_TILE = SORT_THREADS * SORT_ITEMS;  // 4096 pairs per CTA
+constexpr int RADIX_BITS = 8;
+constexpr int RADIX = 1 << RADIX_BITS;
+constexpr int SORT_WARPS = SORT_THREADS / 32;
+constexpr int SORT_SMEM = SORT_TILE * (sizeof(uint64_t) + sizeof(uint32_t));
+
+// table layout: counts[digit * nblocks + block]
+__global__ void __launch_bounds__(SORT_THREADS)
+sort_hist_kernel(int64_t n, int nblocks, int shift, uint32_t mask, const uint64_t* __restrict__ keys,
+                 uint32_t* __restrict__ table)
+{
+    __shared__ uint32_t s_hist[RADIX];
+    for (int i = threadIdx.x; i < RADIX; i += SORT_THREADS) s_hist[i] = 0;
+    __syncthreads();
+    const int64_t base = (int64_t)blockIdx.x * SORT_TILE;
+#pragma unroll 4
+    for (int k = 0; k < SORT_ITEMS; k++) {
+        const int64_t i = base + k * SORT_THREADS + threadIdx.x;
+        if (i < n) {
+            const uint32_t d = (uint32_t)(keys[i] >> shift) & mask;
+            atomicAdd(&s_hist[d], 1u);
+        }
+    }
+    __syncthreads();
+    for (int d = threadIdx.x; d < RADIX; d += SORT_THREADS) table[(size_t)d * nblocks + blockIdx.x] = s_hist[d];
+}
+
+// CTA d scans row d of the table (exclusive, in place) and leaves the digit total in totals[d].
+__global__ void __launch_bounds__(1024)
+sort_scan_rows_kernel(int nblocks, uint32_t* __restrict__ table, uint32_t* __restrict__ totals)
+{
+    const uint32_t total = scan_row_inplace(table + (size_t)blockIdx.x * nblocks, nblocks);
+    if (threadIdx.x == 0) totals[blockIdx.x] = total;
+}
+
+// Stable scatter of one 4096-pair tile.  Thread t of warp w owns the 16 consecutive "rounds" of the warp's
+// contiguous 512-pair chunk: in round r the warp looks at pairs [chunk + 32 r, chunk + 32 r + 32), so
+// (warp, round, lane) order is input order and ranks computed from match.any ballots are stable.
+__global__ void __launch_bounds__(SORT_THREADS)
+sort_scatter_kernel(int64_t n, int nblocks, int shift, uint32_t mask, const uint64_t* __restrict__ keys_in,
+                    const uint32_t* __restrict__ vals_in, uint64_t* __restrict__ keys_out,
+                    uint32_t* __restrict__ vals_out, const uint32_t* __restrict__ table,
+                    const uint32_t* __restrict__ totals)
+{
+    __shared__ uint32_t s_warp_hist[SORT_WARPS][RADIX];  // per-warp digit counters, then exclusive warp offsets
+    __shared__ uint32_t s_digit_start[RADIX];            // start of each digit run inside the CTA's staged tile
+    __shared__ uint32_t s_global_base[RADIX];            // global position of the CTA's first pair of each digit
+    extern __shared__ __align__(16) unsigned char s_dyn[];
+    uint64_t* s_keys = reinterpret_cast<uint64_t*>(s_dyn);
+    uint32_t* s_vals = reinterpret_cast<uint32_t*>(s_dyn + SORT_TILE * sizeof(uint64_t));
+
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (int i = threadIdx.x; i < SORT_WARPS * RADIX; i += SORT_THREADS) (&s_warp_hist[0][0])[i] = 0;
+
+    // global base of every digit: sum of the totals of smaller digits + this CTA's offset inside its digit row
+    {
+        const int d = threadIdx.x;  // SORT_THREADS == RADIX
+        uint32_t t = totals[d];
+        uint32_t incl = warp_incl_scan(t);
+        __shared__ uint32_t s_w[SORT_WARPS];
+        if (lane == 31) s_w[warp] = incl;
+        __syncthreads();
+        uint32_t wb = 0;
+#pragma unroll
+        for (int w = 0; w < SORT_WARPS; w++)
+            if (w < warp) wb += s_w[w];
+        s_global_base[d] = wb + incl - t + table[(size_t)d * nblocks + blockIdx.x];
+    }
+    __syncthreads();
+
+    const int64_t tile_base = (int64_t)blockIdx.x * SORT_TILE;
+    const int64_t chunk = tile_base + (int64_t)warp * (32 * SORT_ITEMS);
+    uint64_t key[SORT_ITEMS];
+    uint32_t val[SORT_ITEMS];
+    uint32_t rank[SORT_ITEMS];  // rank of the pair among same-digit pairs of this warp
+
+#pragma unroll
+    for (int r = 0; r < SORT_ITEMS; r++) {
+        const int64_t i = chunk + r * 32 + lane;
+        const bool valid = i < n;
+        key[r] = valid ? keys_in[i] : ~0ull;
+        val[r] = valid ? vals_in[i] : 0u;
+    }
+#pragma unroll
+    for (int r = 0; r < SORT_ITEMS; r++) {
+        const int64_t i = chunk + r * 32 + lane;
+        const bool valid = i < n;
+        // invalid tail lanes take a digit of their own (RADIX) so they never match a real digit
+        const uint32_t d = valid ? ((uint32_t)(key[r] >> shift) & mask) : (uint32_t)RADIX;
+        const uint32_t peers = __match_any_sync(0xffffffffu, d);
+        const uint32_t before = __popc(peers & ((1u << lane) - 1u));
+        uint32_t prev = 0;
+        if (valid && before == 0) {  // first lane of its digit group updates the warp counter
+            prev = s_warp_hist[warp][d];
+            s_warp_hist[warp][d] = prev + __popc(peers);
+        }
+        prev = __shfl_sync(0xffffffffu, prev, __ffs(peers) - 1);
+        rank[r] = prev + before;
+        __syncwarp();
+    }
+    __syncthreads();
+
+    // per digit: exclusive prefix over the warps, CTA total; then exclusive scan over digits
+    {
+        const int d = threadIdx.x;
+        uint32_t run = 0;
+#pragma unroll
+        for (int w = 0; w < SORT_WARPS; w++) {
+            uint32_t c = s_warp_hist[w][d];
+            s_warp_hist[w][d] = run;
+            run += c;
+        }
+        uint32_t incl = warp_incl_scan(run);
+        __shared__ uint32_t s_w2[SORT_WARPS];
+        if (lane == 31) s_w2[warp] = incl;
+        __syncthreads();
+        uint32_t wb = 0;
+#pragma unroll
+        for (int w = 0; w < SORT_WARPS; w++)
+            if (w < warp) wb += s_w2[w];
+        s_digit_start[d] = wb + incl - run;
+    }
+    __syncthreads();
+
+    // stage the tile in digit order
+#pragma unroll
+    for (int r = 0; r < SORT_ITEMS; r++) {
+        const int64_t i = chunk + r * 32 + lane;
+        if (i < n) {
+            const uint32_t d = (uint32_t)(key[r] >> shift) & mask;
+            const uint32_t pos = s_digit_start[d] + s_warp_hist[warp][d] + rank[r];
+            s_keys[pos] = key[r];
+            s_vals[pos] = val[r];
+        }
+    }
+    __syncthreads();
+
+    const int valid_n = (int)min((int64_t)SORT_TILE, n - tile_base);
+    for (int p = threadIdx.x; p < valid_n; p += SORT_THREADS) {
+        const uint64_t k = s_keys[p];
+        const uint32_t d = (uint32_t)(k >> shift) & mask;
+        const size_t dst = (size_t)s_global_base[d] + (p - s_digit_start[d]);
+        keys_out[dst] = k;
+        vals_out[dst] = s_vals[p];
+    }
+}
+
+__global__ void __launch_bounds__(256)
+tile_ranges_kernel(int64_t L, const uint64_t* __restrict__ keys, uint2* __restrict__ ranges)
+{
+    const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= L) return;
+    const uint32_t currtile = (uint32_t)(keys[idx] >> 32);
+    if (idx == 0)
+        ranges[currtile].x = 0;
+    else {
+        const uint32_t prevtile = (uint32_t)(keys[idx - 1] >> 32);
+        if (currtile != prevtile) {
+            ranges[prevtile].y = (uint32_t)idx;
+            ranges[currtile].x = (uint32_t)idx;
+        }
+    }
+    if (idx == L - 1) ranges[currtile].y = (uint32_t)L;
+}
+
+// ------------------------------------------------------------------------------------------------ distribution
+__device__ __forceinline__ bool touches_band(int tmin, int tmax, int tile_l, int tile_r, int gx, bool avoid)
+{
+    if (avoid) {
+        tile_l -= gx + 1;
+        tile_r += gx + 1;
+    }
+    return !(tmax < tile_l || tmin >= tile_r);
+}
+
+__global__ void __launch_bounds__(256)
+local2j_mask_kernel(int P, int gx, int gy, int ws, const float2* __restrict__ means2D, const int* __restrict__ radii,
+                    const int* __restrict__ bounds, bool avoid, uint8_t* __restrict__ mask)
+{
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= P) return;
+    uint2 rect_min, rect_max;
+    get_rect(means2D[i], radii[i], rect_min, rect_max, gx, gy);
+    const int tmin = rect_min.y * gx + rect_min.x;
+    const int tmax = ((int)rect_max.y - 1) * gx + (int)rect_max.x - 1;
+    const bool any = !(tmax < tmin);
+    for (int rk = 0; rk < ws; rk++)
+        mask[(size_t)i * ws + rk] = any && touches_band(tmin, tmax, bounds[rk], bounds[rk + 1], gx, avoid);
+}
+
+constexpr int MAX_WS = 32;
+constexpr int PACK_TILE = 256;  // rows per CTA
+
+// counts[j] (global) and per-CTA counts block_counts[j * nblocks + b]
+__global__ void __launch_bounds__(PACK_TILE)
+local2j_count_kernel(int P, int gx, int gy, int ws, int nblocks, const float2* __restrict__ means2D,
+                     const int* __restrict__ radii, const int* __restrict__ bounds, bool avoid,
+                     uint32_t* __restrict__ block_counts)
+{
+    __shared__ uint32_t s_cnt[MAX_WS];
+    if (threadIdx.x < MAX_WS) s_cnt[threadIdx.x] = 0;
+    __syncthreads();
+    const int i = blockIdx.x * PACK_TILE + threadIdx.x;
+    uint32_t bits = 0;
+    if (i < P) {
+        uint2 rect_min, rect_max;
+        get_rect(means2D[i], radii[i], rect_min, rect_max, gx, gy);
+        const int tmin = rect_min.y * gx + rect_min.x;
+        const int tmax = ((int)rect_max.y - 1) * gx + (int)rect_max.x - 1;
+        if (!(tmax < tmin))
+            for (int rk = 0; rk < ws; rk++)
+                if (touches_band(tmin, tmax, bounds[rk], bounds[rk + 1], gx, avoid)) bits |= 1u << rk;
+    }
+    for (int rk = 0; rk < ws; rk++) {
+        const uint32_t b = __ballot_sync(0xffffffffu, (bits >> rk) & 1u);
+        if ((threadIdx.x & 31) == 0 && b) atomicAdd(&s_cnt[rk], __popc(b));
+    }
+    __syncthreads();
+    if (threadIdx.x < ws) block_counts[(size_t)threadIdx.x * nblocks + blockIdx.x] = s_cnt[threadIdx.x];
+}
+
+// CTA j scans row j of block_counts in place (exclusive) and writes counts[j].
+__global__ void __launch_bounds__(1024)
+local2j_scan_kernel(int nblocks, uint32_t* __restrict__ block_counts, int32_t* __restrict__ counts)
+{
+    const uint32_t total = scan_row_inplace(block_counts + (size_t)blockIdx.x * nblocks, nblocks);
+    if (threadIdx.x == 0) counts[blockIdx.x] = (int32_t)total;
+}
+
+struct PackOffsets {
+    long long row[MAX_WS];
+};
+
+// Packs the rows selected for each destination, in ascending source index, as 21-float records.
+__global__ void __launch_bounds__(PACK_TILE)
+local2j_pack_kernel(int P, int gx, int gy, int ws, int nblocks, const float2* __restrict__ means2D,
+                    const float* __restrict__ rgb, const float4* __restrict__ conic_opacity,
+                    const float* __restrict__ means3D, const float* __restrict__ scales,
+                    const float4* __restrict__ rotations, const int* __restrict__ radii,
+                    const float* __restrict__ depths, const int* __restrict__ bounds, bool avoid,
+                    const uint32_t* __restrict__ block_prefix, PackOffsets offs, float* __restrict__ send,
+                    int32_t* __restrict__ send_index)
+{
+    __shared__ uint32_t s_warp_cnt[PACK_TILE / 32];
+    const int i = blockIdx.x * PACK_TILE + threadIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    uint32_t bits = 0;
+    float rec[21];
+    if (i < P) {
+        const float2 m2 = means2D[i];
+        const int rad = radii[i];
+        uint2 rect_min, rect_max;
+        get_rect(m2, rad, rect_min, rect_max, gx, gy);
+        const int tmin = rect_min.y * gx + rect_min.x;
+        const int tmax = ((int)rect_max.y - 1) * gx + (int)rect_max.x - 1;
+        if (!(tmax < tmin))
+            for (int rk = 0; rk < ws; rk++)
+                if (touches_band(tmin, tmax, bounds[rk], bounds[rk + 1], gx, avoid)) bits |= 1u << rk;
+        if (bits) {
+            const float4 co = conic_opacity[i];
+            const float4 q = rotations[i];
+            rec[0] = m2.x; rec[1] = m2.y;
+            rec[2] = rgb[3 * i]; rec[3] = rgb[3 * i + 1]; rec[4] = rgb[3 * i + 2];
+            rec[5] = co.x; rec[6] = co.y; rec[7] = co.z; rec[8] = co.w;
+            rec[9] = means3D[3 * i]; rec[10] = means3D[3 * i + 1]; rec[11] = means3D[3 * i + 2];
+            rec[12] = scales[3 * i]; rec[13] = scales[3 * i + 1]; rec[14] = scales[3 * i + 2];
+            rec[15] = q.x; rec[16] = q.y; rec[17] = q.z; rec[18] = q.w;
+            rec[19] = (float)rad;
+            rec[20] = depths[i];
+        }
+    }
+    for (int rk = 0; rk < ws; rk++) {
+        const bool sel = (bits >> rk) & 1u;
+        const uint32_t b = __ballot_sync(0xffffffffu, sel);
+        if (lane == 0) s_warp_cnt[warp] = __popc(b);
+        __syncthreads();
+        uint32_t wbase = 0;
+        for (int w = 0; w < warp; w++) wbase += s_warp_cnt[w];
+        __syncthreads();
+        if (sel) {
+            const long long row = offs.row[rk] + block_prefix[(size_t)rk * nblocks + blockIdx.x] + wbase +
+                                  __popc(b & ((1u << lane) - 1u));
+            float* dst = send + row * 21;
+#pragma unroll
+            for (int k = 0; k < 21; k++) dst[k] = rec[k];
+            if (send_index) send_index[row] = i;
+        }
+    }
+}
+
+__global__ void __launch_bounds__(256)
+unpack_grad_add_kernel(long long n, const float* __restrict__ g, const int32_t* __restrict__ index,
+                       float* __restrict__ d_means2D, float* __restrict__ d_rgb, float* __restrict__ d_co,
+                       float* __restrict__ d_means3D, float* __restrict__ d_scales, float* __restrict__ d_rot)
+{
+    const long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= n * 19) return;
+    const long long row = e / 19;
+    const int c = (int)(e - row * 19);
+    const size_t i = (size_t)index[row];
+    const float v = g[e];
+    if (v == 0.0f) return;
+    if (c < 2) atomicAdd(d_means2D + 2 * i + c, v);
+    else if (c < 5) { if (d_rgb) atomicAdd(d_rgb + 3 * i + (c - 2), v); }
+    else if (c < 9) atomicAdd(d_co + 4 * i + (c - 5), v);
+    else if (c < 12) { if (d_means3D) atomicAdd(d_means3D + 3 * i + (c - 9), v); }
+    else if (c < 15) { if (d_scales) atomicAdd(d_scales + 3 * i + (c - 12), v); }
+    else { if (d_rot) atomicAdd(d_rot + 4 * i + (c - 15), v); }
+}
+
+}  // namespace cgx
+
+using namespace cgx;
+
+static inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+extern "C" uint32_t cgx_higher_msb(uint32_t n)
+{
+    uint32_t msb = sizeof(n) * 4;
+    uint32_t step = msb;
+    while (step > 1) {
+        step /= 2;
+        if (n >> msb)
+            msb += step;
+        else
+            msb -= step;
+    }
+    if (n >> msb) msb++;
+    return msb;
+}
+
+extern "C" size_t cgx_bin_workspace_bytes(int P)
+{
+    const size_t nblocks = ((size_t)(P > 0 ? P : 1) + SCAN_TILE - 1) / SCAN_TILE;
+    return align_up(nblocks * sizeof(uint32_t), 256);
+}
+
+extern "C" int cgx_bin_count_scan(int P, int W, int H, const int32_t* radii, const float* means2D,
+                                  const uint8_t* compute_locally, uint32_t* tiles_touched, uint32_t* num_rendered,
+                                  void* workspace, size_t workspace_bytes, void* stream)
+{
+    if (P < 0 || W <= 0 || H <= 0 || !num_rendered) return CGX_EINVAL;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (P == 0) {
+        cudaError_t e = cudaMemsetAsync(num_rendered, 0, sizeof(uint32_t), st);
+        if (e != cudaSuccess) { set_cuda_error(e); return CGX_ECUDA; }
+        return CGX_OK;
+    }
+    if (!radii || !means2D || !compute_locally || !tiles_touched || !workspace) return CGX_EINVAL;
+    if ((uintptr_t)means2D & 7) return CGX_EINVAL;
+    if (workspace_bytes < cgx_bin_workspace_bytes(P)) return CGX_ENOMEM;
+    const int gx = (W + CGX_BLOCK_X - 1) / CGX_BLOCK_X, gy = (H + CGX_BLOCK_Y - 1) / CGX_BLOCK_Y;
+    const int nblocks = (P + SCAN_TILE - 1) / SCAN_TILE;
+    uint32_t* sums = (uint32_t*)workspace;
+    tile_count_kernel<<<nblocks, CGX_BLOCK_SIZE, 0, st>>>(P, gx, gy, radii, (const float2*)means2D, compute_locally,
+                                                          tiles_touched, sums);
+    scan_partials_kernel<<<1, 1024, 0, st>>>(nblocks, sums, num_rendered);
+    return check_launch();
+}
+
+extern "C" int cgx_emit_keys(int P, int W, int H, const int32_t* radii, const float* means2D, const float* depths,
+                             const uint32_t* tiles_touched, const uint8_t* compute_locally, uint32_t* point_offsets,
+                             uint64_t* keys, uint32_t* values, int64_t capacity, const void* workspace, void* stream)
+{
+    if (P < 0 || W <= 0 || H <= 0 || capacity < 0 || capacity > 0xffffffffLL) return CGX_EINVAL;
+    if (P == 0) return CGX_OK;
+    if (!radii || !means2D || !depths || !tiles_touched || !compute_locally || !point_offsets || !workspace)
+        return CGX_EINVAL;
+    if (capacity > 0 && (!keys || !values)) return CGX_EINVAL;
+    const int gx = (W + CGX_BLOCK_X - 1) / CGX_BLOCK_X, gy = (H + CGX_BLOCK_Y - 1) / CGX_BLOCK_Y;
+    const int nblocks = (P + SCAN_TILE - 1) / SCAN_TILE;
+    emit_keys_kernel<<<nblocks, CGX_BLOCK_SIZE, 0, (cudaStream_t)stream>>>(
+        P, gx, gy, radii, (const float2*)means2D, depths, tiles_touched, compute_locally, (const uint32_t*)workspace,
+        point_offsets, keys, values, (uint32_t)capacity);
+    return check_launch();
+}
+
+extern "C" size_t cgx_sort_workspace_bytes(int64_t n)
+{
+    const size_t nblocks = ((size_t)(n > 0 ? n : 1) + SORT_TILE - 1) / SORT_TILE;
+    return align_up(nblocks * RADIX * sizeof(uint32_t), 256) + align_up(RADIX * sizeof(uint32_t), 256);
+}
+
+extern "C" int cgx_sort_pairs(int64_t n, int end_bit, uint64_t* keys_in, uint32_t* values_in, uint64_t* keys_out,
+                              uint32_t* values_out, void* workspace, size_t workspace_bytes, void* stream)
+{
+    if (n < 0 || end_bit < 0 || end_bit > 64 || n > 0x7fffffffLL) return CGX_EINVAL;
+    if (n == 0) return CGX_OK;
+    if (!keys_in || !values_in || !keys_out || !values_out || !workspace) return CGX_EINVAL;
+    if (workspace_bytes < cgx_sort_workspace_bytes(n)) return CGX_ENOMEM;
+    cudaStream_t st = (cudaStream_t)stream;
+    {
+        // opt in to > 48 KB of dynamic shared memory (per device, cheap and idempotent)
+        cudaError_t e = cudaFuncSetAttribute(sort_scatter_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SORT_SMEM);
+        if (e != cudaSuccess) { set_cuda_error(e); return CGX_ECUDA; }
+    }
+    const int nblocks = (int)((n + SORT_TILE - 1) / SORT_TILE);
+    uint32_t* table = (uint32_t*)workspace;
+    uint32_t* totals = (uint32_t*)((char*)workspace + align_up((size_t)nblocks * RADIX * sizeof(uint32_t), 256));
+    int passes = (end_bit + RADIX_BITS - 1) / RADIX_BITS;
+    // The result must land in keys_out: with an odd number of passes start from keys_in, otherwise copy first.
+    uint64_t* kin = keys_in;
+    uint32_t* vin = values_in;
+    uint64_t* kout = keys_out;
+    uint32_t* vout = values_out;
+    if (passes == 0) {
+        cudaMemcpyAsync(keys_out, keys_in, n * sizeof(uint64_t), cudaMemcpyDeviceToDevice, st);
+        cudaMemcpyAsync(values_out, values_in, n * sizeof(uint32_t), cudaMemcpyDeviceToDevice, st);
+        return check_launch();
+    }
+    if (passes % 2 == 0) {
+        // even: in -> out -> in ... ends in `in`; swap roles by first moving the data to `out`
+        cudaMemcpyAsync(keys_out, keys_in, n * sizeof(uint64_t), cudaMemcpyDeviceToDevice, st);
+        cudaMemcpyAsync(values_out, values_in, n * sizeof(uint32_t), cudaMemcpyDeviceToDevice, st);
+        kin = keys_out; vin = values_out; kout = keys_in; vout = values_in;
+    }
+    for (int p = 0; p < passes; p++) {
+        const int shift = p * RADIX_BITS;
+        const int bits = (end_bit - shift) < RADIX_BITS ? (end_bit - shift) : RADIX_BITS;
+        const uint32_t mask = (1u << bits) - 1u;
+        sort_hist_kernel<<<nblocks, SORT_THREADS, 0, st>>>(n, nblocks, shift, mask, kin, table);
+        sort_scan_rows_kernel<<<RADIX, 1024, 0, st>>>(nblocks, table, totals);
+        sort_scatter_kernel<<<nblocks, SORT_THREADS, SORT_SMEM, st>>>(n, nblocks, shift, mask, kin, vin, kout, vout, table,
+                                                             totals);
+        uint64_t* tk = kin; kin = kout; kout = tk;
+        uint32_t* tv = vin; vin = vout; vout = tv;
+    }
+    return check_launch();
+}
+
+extern "C" int cgx_tile_ranges(int64_t n, int T, const uint64_t* keys_sorted, uint32_t* ranges, void* stream)
+{
+    if (n < 0 || T <= 0 || !ranges) return CGX_EINVAL;
+    cudaStream_t st = (cudaStream_t)stream;
+    cudaError_t e = cudaMemsetAsync(ranges, 0, (size_t)T * sizeof(uint2), st);
+    if (e != cudaSuccess) { set_cuda_error(e); return CGX_ECUDA; }
+    if (n == 0) return CGX_OK;
+    if (!keys_sorted) return CGX_EINVAL;
+    tile_ranges_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(n, keys_sorted, (uint2*)ranges);
+    return check_launch();
+}
+
+extern "C" int cgx_local2j_mask(int P, int H, int W, int ws, const float* means2D, const int32_t* radii,
+                                const int32_t* tile_bounds, int avoid_pixel_all2all, uint8_t* mask, void* stream)
+{
+    if (P < 0 || W <= 0 || H <= 0 || ws <= 0) return CGX_EINVAL;
+    if (P == 0) return CGX_OK;
+    if (!means2D || !radii || !tile_bounds || !mask || ((uintptr_t)means2D & 7)) return CGX_EINVAL;
+    const int gx = (W + CGX_BLOCK_X - 1) / CGX_BLOCK_X, gy = (H + CGX_BLOCK_Y - 1) / CGX_BLOCK_Y;
+    local2j_mask_kernel<<<(P + 255) / 256, 256, 0, (cudaStream_t)stream>>>(P, gx, gy, ws, (const float2*)means2D, radii,
+                                                                          tile_bounds, avoid_pixel_all2all != 0, mask);
+    return check_launch();
+}
+
+extern "C" size_t cgx_local2j_workspace_bytes(int P, int ws)
+{
+    const size_t nblocks = ((size_t)(P > 0 ? P : 1) + PACK_TILE - 1) / PACK_TILE;
+    return align_up(nblocks * (size_t)(ws > 0 ? ws : 1) * sizeof(uint32_t), 256);
+}
+
+extern "C" int cgx_local2j_count(int P, int H, int W, int ws, const float* means2D, const int32_t* radii,
+                                 const int32_t* tile_bounds, int avoid_pixel_all2all, int32_t* counts,
+                                 void* workspace, size_t workspace_bytes, void* stream)
+{
+    if (P < 0 || W <= 0 || H <= 0 || ws <= 0 || ws > MAX_WS || !counts) return CGX_EINVAL;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (P == 0) {
+        cudaError_t e = cudaMemsetAsync(counts, 0, ws * sizeof(int32_t), st);
+        if (e != cudaSuccess) { set_cuda_error(e); return CGX_ECUDA; }
+        return CGX_OK;
+    }
+    if (!means2D || !radii || !tile_bounds || !workspace || ((uintptr_t)means2D & 7)) return CGX_EINVAL;
+    if (workspace_bytes < cgx_local2j_workspace_bytes(P, ws)) return CGX_ENOMEM;
+    const int gx = (W + CGX_BLOCK_X - 1) / CGX_BLOCK_X, gy = (H + CGX_BLOCK_Y - 1) / CGX_BLOCK_Y;
+    const int nblocks = (P + PACK_TILE - 1) / PACK_TILE;
+    local2j_count_kernel<<<nblocks, PACK_TILE, 0, st>>>(P, gx, gy, ws, nblocks, (const float2*)means2D, radii,
+                                                        tile_bounds, avoid_pixel_all2all != 0, (uint32_t*)workspace);
+    local2j_scan_kernel<<<ws, 1024, 0, st>>>(nblocks, (uint32_t*)workspace, counts);
+    return check_launch();
+}
+
+extern "C" int cgx_local2j_pack(int P, int H, int W, int ws, const float* means2D, const float* rgb,
+                                const float* conic_opacity, const float* means3D, const float* scales,
+                                const float* rotations, const int32_t* radii, const float* depths,
+                                const int32_t* tile_bounds, int avoid_pixel_all2all, const int64_t* send_row_offset,
+                                float* send_buffer, int32_t* send_index, void* workspace, size_t workspace_bytes,
+                                void* stream)
+{
+    if (P < 0 || W <= 0 || H <= 0 || ws <= 0 || ws > MAX_WS || !send_row_offset) return CGX_EINVAL;
+    if (P == 0) return CGX_OK;
+    if (!means2D || !rgb || !conic_opacity || !means3D || !scales || !rotations || !radii || !depths ||
+        !tile_bounds || !send_buffer || !workspace)
+        return CGX_EINVAL;
+    if (((uintptr_t)means2D & 7) || !aligned16(conic_opacity) || !aligned16(rotations)) return CGX_EINVAL;
+    if (workspace_bytes < cgx_local2j_workspace_bytes(P, ws)) return CGX_ENOMEM;
+    const int gx = (W + CGX_BLOCK_X - 1) / CGX_BLOCK_X, gy = (H + CGX_BLOCK_Y - 1) / CGX_BLOCK_Y;
+    const int nblocks = (P + PACK_TILE - 1) / PACK_TILE;
+    PackOffsets offs;
+    for (int j = 0; j < MAX_WS; j++) offs.row[j] = j < ws ? (long long)send_row_offset[j] : 0;
+    local2j_pack_kernel<<<nblocks, PACK_TILE, 0, (cudaStream_t)stream>>>(
+        P, gx, gy, ws, nblocks, (const float2*)means2D, rgb, (const float4*)conic_opacity, means3D, scales,
+        (const float4*)rotations, radii, depths, tile_bounds, avoid_pixel_all2all != 0, (const uint32_t*)workspace, offs,
+        send_buffer, send_index);
+    return check_launch();
+}
+
+extern "C" int cgx_unpack_grad_add(int64_t n_rows, const float* grad_rows, const int32_t* send_index,
+                                   float* d_means2D, float* d_rgb, float* d_conic_opacity, float* d_means3D,
+                                   float* d_scales, float* d_rotations, void* stream)
+{
+    if (n_rows < 0) return CGX_EINVAL;
+    if (n_rows == 0) return CGX_OK;
+    if (!grad_rows || !send_index || !d_means2D || !d_conic_opacity) return CGX_EINVAL;
+    const long long total = n_rows * 19;
+    unpack_grad_add_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+        n_rows, grad_rows, send_index, d_means2D, d_rgb, d_conic_opacity, d_means3D, d_scales, d_rotations);
+    return check_launch();
+}

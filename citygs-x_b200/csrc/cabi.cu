@@ -1,0 +1,52 @@
+// Status handling and the small host-only entry points of the C ABI.
+#include <string.h>
+#include "cgx_common.cuh"
+
+namespace cgx {
+
+static thread_local char g_cuda_error[256] = "";
+
+void set_cuda_error(cudaError_t e)
+{
+    strncpy(g_cuda_error, cudaGetErrorString(e), sizeof(g_cuda_error) - 1);
+    g_cuda_error[sizeof(g_cuda_error) - 1] = 0;
+}
+
+// Launch errors only (no synchronisation): configuration problems surface here, execution faults
+// surface at the caller's next synchronising call.
+int check_launch()
+{
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        set_cuda_error(e);
+        return CGX_ECUDA;
+    }
+    return CGX_OK;
+}
+
+}  // namespace cgx
+
+extern "C" const char* cgx_strerror(int status)
+{
+    switch (status) {
+    case CGX_OK: return "ok";
+    case CGX_EINVAL: return "invalid argument (shape, null or misaligned pointer)";
+    case CGX_ENOMEM: return "workspace or capacity too small";
+    case CGX_ETIMEDOUT: return "a bounded device-side wait gave up";
+    case CGX_ECUDA: return "CUDA runtime error";
+    default: return "unknown status";
+    }
+}
+
+extern "C" const char* cgx_last_cuda_error(void) { return cgx::g_cuda_error; }
+
+extern "C" const char* cgx_version(void) { return "cgx_raster 0.1 (sm_100a)"; }
+
+extern "C" int cgx_block_xy(int* block_x, int* block_y, int* one_dim_block)
+{
+    if (!block_x || !block_y || !one_dim_block) return CGX_EINVAL;
+    *block_x = CGX_BLOCK_X;
+    *block_y = CGX_BLOCK_Y;
+    *one_dim_block = CGX_BLOCK_SIZE;
+    return CGX_OK;
+}

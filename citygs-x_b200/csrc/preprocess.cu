@@ -1,0 +1,532 @@
+// Per-Gaussian stages: projection / EWA covariance / radius (forward), the anchor visibility
+// filter, the frustum mark, the optional SH->RGB stage and the fused preprocess backward.
+//
+// Memory plan (HBM-bound kernels): one thread per Gaussian, 256 Gaussians per CTA.  The AoS
+// inputs ((P,3),(P,3),(P,4)) are pulled in as 128-bit loads by the whole CTA into shared
+// memory and read back with conflict-free strides (3 and 4 words); the (P,6) covariance output
+// takes the same route in reverse, so every global transaction is a full 16-byte vector.
+// Outputs are written for every Gaussian (zeros for culled ones), so callers need no memsets.
+#include "cgx_common.cuh"
+
+namespace cgx {
+
+// Scale + (unnormalised) quaternion -> upper triangle of the world-space covariance.
+__device__ __forceinline__ void compute_cov3d(const float3 scale, float mod, const float4 rot, float* cov3D)
+{
+    Mat3 S;
+#pragma unroll
+    for (int c = 0; c < 3; c++)
+#pragma unroll
+        for (int r = 0; r < 3; r++) S.m[c][r] = 0.0f;
+    S.m[0][0] = mod * scale.x;
+    S.m[1][1] = mod * scale.y;
+    S.m[2][2] = mod * scale.z;
+
+    float r = rot.x;
+    float x = rot.y;
+    float y = rot.z;
+    float z = rot.w;
+
+    Mat3 R;
+    R.m[0][0] = 1.f - 2.f * (y * y + z * z); R.m[0][1] = 2.f * (x * y - r * z); R.m[0][2] = 2.f * (x * z + r * y);
+    R.m[1][0] = 2.f * (x * y + r * z); R.m[1][1] = 1.f - 2.f * (x * x + z * z); R.m[1][2] = 2.f * (y * z - r * x);
+    R.m[2][0] = 2.f * (x * z - r * y); R.m[2][1] = 2.f * (y * z + r * x); R.m[2][2] = 1.f - 2.f * (x * x + y * y);
+
+    Mat3 M = mul(S, R);
+    Mat3 Sigma = mul(transpose(M), M);
+
+    cov3D[0] = Sigma.m[0][0];
+    cov3D[1] = Sigma.m[0][1];
+    cov3D[2] = Sigma.m[0][2];
+    cov3D[3] = Sigma.m[1][1];
+    cov3D[4] = Sigma.m[1][2];
+    cov3D[5] = Sigma.m[2][2];
+}
+
+// EWA projection of the 3-D covariance (Zwicker et al. 2002, eq. 29/31) plus the 0.3 px low-pass.
+__device__ __forceinline__ float3 compute_cov2d(const float3& mean, float focal_x, float focal_y, float tan_fovx,
+                                                float tan_fovy, const float* cov3D, const float* viewmatrix)
+{
+    float3 t = transform_point_4x3(mean, viewmatrix);
+
+    const float limx = 1.3f * tan_fovx;
+    const float limy = 1.3f * tan_fovy;
+    const float txtz = t.x / t.z;
+    const float tytz = t.y / t.z;
+    t.x = min(limx, max(-limx, txtz)) * t.z;
+    t.y = min(limy, max(-limy, tytz)) * t.z;
+
+    Mat3 J;
+    J.m[0][0] = focal_x / t.z; J.m[0][1] = 0.0f; J.m[0][2] = -(focal_x * t.x) / (t.z * t.z);
+    J.m[1][0] = 0.0f; J.m[1][1] = focal_y / t.z; J.m[1][2] = -(focal_y * t.y) / (t.z * t.z);
+    J.m[2][0] = 0; J.m[2][1] = 0; J.m[2][2] = 0;
+
+    Mat3 W;
+    W.m[0][0] = viewmatrix[0]; W.m[0][1] = viewmatrix[4]; W.m[0][2] = viewmatrix[8];
+    W.m[1][0] = viewmatrix[1]; W.m[1][1] = viewmatrix[5]; W.m[1][2] = viewmatrix[9];
+    W.m[2][0] = viewmatrix[2]; W.m[2][1] = viewmatrix[6]; W.m[2][2] = viewmatrix[10];
+
+    Mat3 T = mul(W, J);
+
+    Mat3 Vrk;
+    Vrk.m[0][0] = cov3D[0]; Vrk.m[0][1] = cov3D[1]; Vrk.m[0][2] = cov3D[2];
+    Vrk.m[1][0] = cov3D[1]; Vrk.m[1][1] = cov3D[3]; Vrk.m[1][2] = cov3D[4];
+    Vrk.m[2][0] = cov3D[2]; Vrk.m[2][1] = cov3D[4]; Vrk.m[2][2] = cov3D[5];
+
+    Mat3 cov = mul(mul(transpose(T), transpose(Vrk)), T);
+
+    cov.m[0][0] += 0.3f;
+    cov.m[1][1] += 0.3f;
+    return {float(cov.m[0][0]), float(cov.m[0][1]), float(cov.m[1][1])};
+}
+
+template <bool FILTER>
+__global__ void __launch_bounds__(CGX_BLOCK_SIZE)
+preprocess_fwd_kernel(int P, const float* __restrict__ means3D, const float* __restrict__ scales,
+                      const float scale_modifier, const float* __restrict__ rotations,
+                      const float* __restrict__ opacities, const float* __restrict__ viewmatrix_g,
+                      const float* __restrict__ projmatrix_g, const int W, int H, const float tan_fovx,
+                      float tan_fovy, const float focal_x, float focal_y, int* __restrict__ radii,
+                      float2* __restrict__ points_xy_image, float* __restrict__ depths,
+                      float* __restrict__ cov3Ds, float4* __restrict__ conic_opacity, int vec_mask)
+{
+    __shared__ __align__(16) float s_mean[CGX_BLOCK_SIZE * 3];
+    __shared__ __align__(16) float s_scale[CGX_BLOCK_SIZE * 3];
+    __shared__ __align__(16) float s_rot[CGX_BLOCK_SIZE * 4];
+    __shared__ __align__(16) float s_cov[FILTER ? 4 : CGX_BLOCK_SIZE * 6];
+    __shared__ float viewmatrix[16];
+    __shared__ float projmatrix[16];
+
+    const int base = blockIdx.x * CGX_BLOCK_SIZE;
+    const int count = min(CGX_BLOCK_SIZE, P - base);
+    if (threadIdx.x < 16) viewmatrix[threadIdx.x] = viewmatrix_g[threadIdx.x];
+    else if (threadIdx.x < 32) projmatrix[threadIdx.x - 16] = projmatrix_g[threadIdx.x - 16];
+    block_load_rows<3>(means3D + (size_t)base * 3, s_mean, count, vec_mask & 1);
+    block_load_rows<3>(scales + (size_t)base * 3, s_scale, count, vec_mask & 2);
+    block_load_rows<4>(rotations + (size_t)base * 4, s_rot, count, vec_mask & 4);
+    __syncthreads();
+
+    const int t = threadIdx.x;
+    const int idx = base + t;
+    int out_radius = 0;
+    float2 out_xy = {0.f, 0.f};
+    float out_depth = 0.f;
+    float4 out_co = {0.f, 0.f, 0.f, 0.f};
+    float cov3D[6] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+
+    if (t < count) {
+        do {
+            float3 p_orig = {s_mean[3 * t], s_mean[3 * t + 1], s_mean[3 * t + 2]};
+            // Near cull in view space: keep z > 0 only (no x/y frustum test).
+            float4 p_hom = transform_point_4x4(p_orig, projmatrix);
+            float p_w = 1.0f / (p_hom.w + 0.0000001f);
+            float3 p_proj = {p_hom.x * p_w, p_hom.y * p_w, p_hom.z * p_w};
+            float3 p_view = transform_point_4x3(p_orig, viewmatrix);
+            if (p_view.z <= 0.0f) break;
+
+            const float3 sc = {s_scale[3 * t], s_scale[3 * t + 1], s_scale[3 * t + 2]};
+            const float4 q = {s_rot[4 * t], s_rot[4 * t + 1], s_rot[4 * t + 2], s_rot[4 * t + 3]};
+            compute_cov3d(sc, scale_modifier, q, cov3D);
+
+            float3 cov = compute_cov2d(p_orig, focal_x, focal_y, tan_fovx, tan_fovy, cov3D, viewmatrix);
+
+            float det = (cov.x * cov.z - cov.y * cov.y);
+            if (det == 0.0f) break;
+            float det_inv = 1.f / det;
+            float3 conic = {cov.z * det_inv, -cov.y * det_inv, cov.x * det_inv};
+
+            float mid = 0.5f * (cov.x + cov.z);
+            float lambda1 = mid + sqrt(max(0.1f, mid * mid - det));
+            float lambda2 = mid - sqrt(max(0.1f, mid * mid - det));
+            float my_radius = ceil(3.f * sqrt(max(lambda1, lambda2)));
+            float2 point_image = {ndc2pix(p_proj.x, W), ndc2pix(p_proj.y, H)};
+            uint2 rect_min, rect_max;
+            get_rect(point_image, my_radius, rect_min, rect_max, (W + CGX_BLOCK_X - 1) / CGX_BLOCK_X,
+                     (H + CGX_BLOCK_Y - 1) / CGX_BLOCK_Y);
+            if ((rect_max.x - rect_min.x) * (rect_max.y - rect_min.y) == 0) break;
+
+            out_depth = p_view.z;
+            out_radius = my_radius;
+            out_xy = point_image;
+            if (!FILTER) out_co = {conic.x, conic.y, conic.z, __ldg(opacities + idx)};
+        } while (0);
+
+        radii[idx] = out_radius;
+        if (!FILTER) {
+            points_xy_image[idx] = out_xy;
+            depths[idx] = out_depth;
+            conic_opacity[idx] = out_co;
+#pragma unroll
+            for (int k = 0; k < 6; k++) s_cov[6 * t + k] = cov3D[k];
+        }
+    }
+    if (!FILTER) {
+        __syncthreads();
+        block_store_rows<6>(cov3Ds + (size_t)base * 6, s_cov, count, vec_mask & 8);
+    }
+}
+
+__global__ void mark_visible_kernel(int P, const float* __restrict__ means3D, const float* __restrict__ viewmatrix,
+                                    uint8_t* __restrict__ present)
+{
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= P) return;
+    float3 p = {means3D[3 * idx], means3D[3 * idx + 1], means3D[3 * idx + 2]};
+    float3 pv = transform_point_4x3(p, viewmatrix);
+    present[idx] = pv.z > 0.0f;
+}
+
+// Real spherical-harmonic basis constants (degrees 0..3).
+__device__ const float SH_C0 = 0.28209479177387814f;
+__device__ const float SH_C1 = 0.4886025119029199f;
+__device__ const float SH_C2[] = {1.0925484305920792f, -1.0925484305920792f, 0.31539156525252005f,
+                                  -1.0925484305920792f, 0.5462742152960396f};
+__device__ const float SH_C3[] = {-0.5900435899266435f, 2.890611442640554f, -0.4570457994644658f, 0.3731763325901154f,
+                                  -0.4570457994644658f, 1.445305721320277f, -0.5900435899266435f};
+
+// One warp per 32 Gaussians; the (M,3) coefficient block of a Gaussian is contiguous, so the CTA
+// streams its 256*M*3 floats through shared memory in 128-bit pieces.
+__global__ void __launch_bounds__(128)
+sh_to_rgb_kernel(int P, int deg, int M, const float* __restrict__ means3D, const float* __restrict__ campos,
+                 const float* __restrict__ shs, float* __restrict__ rgb, uint8_t* __restrict__ clamped, int vec_ok)
+{
+    extern __shared__ __align__(16) float s_sh[];  // 128 * M * 3 floats
+    const int base = blockIdx.x * 128;
+    const int count = min(128, P - base);
+    {
+        const int nfl = count * M * 3;
+        const float* g = shs + (size_t)base * M * 3;
+        if (vec_ok) {
+            const int nv = nfl >> 2;
+            for (int i = threadIdx.x; i < nv; i += blockDim.x)
+                reinterpret_cast<float4*>(s_sh)[i] = __ldg(reinterpret_cast<const float4*>(g) + i);
+            for (int i = (nv << 2) + threadIdx.x; i < nfl; i += blockDim.x) s_sh[i] = __ldg(g + i);
+        } else {
+            for (int i = threadIdx.x; i < nfl; i += blockDim.x) s_sh[i] = __ldg(g + i);
+        }
+    }
+    __syncthreads();
+    const int t = threadIdx.x;
+    if (t >= count) return;
+    const int idx = base + t;
+    float3 pos = {means3D[3 * idx], means3D[3 * idx + 1], means3D[3 * idx + 2]};
+    float3 dir = {pos.x - campos[0], pos.y - campos[1], pos.z - campos[2]};
+    float len = sqrt(dir.x * dir.x + dir.y * dir.y + dir.z * dir.z);
+    dir = {dir.x / len, dir.y / len, dir.z / len};
+    // stride M*3 between threads: odd multiples of 3 words are bank-conflict free for M=16 (48 words -> 2-way);
+    // accepted, the kernel is bound by the 192 B/Gaussian global read.
+    const float* sh = s_sh + (size_t)t * M * 3;
+    float x = dir.x, y = dir.y, z = dir.z;
+    float res[3];
+#pragma unroll
+    for (int ch = 0; ch < 3; ch++) {
+        float result = SH_C0 * sh[ch];
+        if (deg > 0) {
+            result = result - SH_C1 * y * sh[3 + ch] + SH_C1 * z * sh[6 + ch] - SH_C1 * x * sh[9 + ch];
+            if (deg > 1) {
+                float xx = x * x, yy = y * y, zz = z * z;
+                float xy = x * y, yz = y * z, xz = x * z;
+                result = result + SH_C2[0] * xy * sh[12 + ch] + SH_C2[1] * yz * sh[15 + ch] +
+                         SH_C2[2] * (2.0f * zz - xx - yy) * sh[18 + ch] + SH_C2[3] * xz * sh[21 + ch] +
+                         SH_C2[4] * (xx - yy) * sh[24 + ch];
+                if (deg > 2) {
+                    result = result + SH_C3[0] * y * (3.0f * xx - yy) * sh[27 + ch] + SH_C3[1] * xy * z * sh[30 + ch] +
+                             SH_C3[2] * y * (4.0f * zz - xx - yy) * sh[33 + ch] +
+                             SH_C3[3] * z * (2.0f * zz - 3.0f * xx - 3.0f * yy) * sh[36 + ch] +
+                             SH_C3[4] * x * (4.0f * zz - xx - yy) * sh[39 + ch] + SH_C3[5] * z * (xx - yy) * sh[42 + ch] +
+                             SH_C3[6] * x * (xx - 3.0f * yy) * sh[45 + ch];
+                }
+            }
+        }
+        result += 0.5f;
+        res[ch] = result;
+    }
+#pragma unroll
+    for (int ch = 0; ch < 3; ch++) {
+        clamped[3 * idx + ch] = (res[ch] < 0);
+        rgb[3 * idx + ch] = max(res[ch], 0.0f);
+    }
+}
+
+// Fused backward of the per-Gaussian stage: d(conic) -> d(cov2D) -> d(cov3D), d(mean) through the EWA
+// Jacobian and through the projection of the 2-D mean, then d(cov3D) -> d(scale), d(quaternion).
+// The 3-D covariance is recomputed from scale/rotation (same function as the forward, so same bits)
+// instead of being read back, and the intermediate dL/dcov3D never leaves registers.
+__global__ void __launch_bounds__(CGX_BLOCK_SIZE)
+preprocess_bwd_kernel(int P, const float* __restrict__ means3D, const float* __restrict__ scales,
+                      const float scale_modifier, const float* __restrict__ rotations,
+                      const int* __restrict__ radii, const float* __restrict__ viewmatrix_g,
+                      const float* __restrict__ projmatrix_g, const float h_x, float h_y, const float tan_fovx,
+                      float tan_fovy, const float2* __restrict__ dL_dmean2D,
+                      const float4* __restrict__ dL_dconic_opacity, float* __restrict__ dL_dmeans,
+                      float* __restrict__ dL_dscales, float4* __restrict__ dL_drots,
+                      float* __restrict__ dL_dopacity, int vec_mask)
+{
+    __shared__ __align__(16) float s_mean[CGX_BLOCK_SIZE * 3];   // reused for dL_dmeans
+    __shared__ __align__(16) float s_scale[CGX_BLOCK_SIZE * 3];  // reused for dL_dscales
+    __shared__ __align__(16) float s_rot[CGX_BLOCK_SIZE * 4];
+    __shared__ float view_matrix[16];
+    __shared__ float proj[16];
+
+    const int base = blockIdx.x * CGX_BLOCK_SIZE;
+    const int count = min(CGX_BLOCK_SIZE, P - base);
+    if (threadIdx.x < 16) view_matrix[threadIdx.x] = viewmatrix_g[threadIdx.x];
+    else if (threadIdx.x < 32) proj[threadIdx.x - 16] = projmatrix_g[threadIdx.x - 16];
+    block_load_rows<3>(means3D + (size_t)base * 3, s_mean, count, vec_mask & 1);
+    block_load_rows<3>(scales + (size_t)base * 3, s_scale, count, vec_mask & 2);
+    block_load_rows<4>(rotations + (size_t)base * 4, s_rot, count, vec_mask & 4);
+    __syncthreads();
+
+    const int t = threadIdx.x;
+    const int idx = base + t;
+    float3 g_mean = {0.f, 0.f, 0.f}, g_scale = {0.f, 0.f, 0.f};
+    float4 g_rot = {0.f, 0.f, 0.f, 0.f};
+
+    if (t < count) {
+        const float4 dco = __ldg(dL_dconic_opacity + idx);
+        dL_dopacity[idx] = dco.w;
+        if (radii[idx] > 0) {
+            const float3 mean = {s_mean[3 * t], s_mean[3 * t + 1], s_mean[3 * t + 2]};
+            const float3 sc = {s_scale[3 * t], s_scale[3 * t + 1], s_scale[3 * t + 2]};
+            const float4 rot = {s_rot[4 * t], s_rot[4 * t + 1], s_rot[4 * t + 2], s_rot[4 * t + 3]};
+            float cov3D[6];
+            compute_cov3d(sc, scale_modifier, rot, cov3D);
+
+            // ---- conic -> cov2D -> cov3D and mean (EWA part)
+            float3 dL_dconic = {dco.x, dco.y, dco.z};
+            float3 tt = transform_point_4x3(mean, view_matrix);
+            const float limx = 1.3f * tan_fovx;
+            const float limy = 1.3f * tan_fovy;
+            const float txtz = tt.x / tt.z;
+            const float tytz = tt.y / tt.z;
+            tt.x = min(limx, max(-limx, txtz)) * tt.z;
+            tt.y = min(limy, max(-limy, tytz)) * tt.z;
+            const float x_grad_mul = txtz < -limx || txtz > limx ? 0 : 1;
+            const float y_grad_mul = tytz < -limy || tytz > limy ? 0 : 1;
+
+            Mat3 J;
+            J.m[0][0] = h_x / tt.z; J.m[0][1] = 0.0f; J.m[0][2] = -(h_x * tt.x) / (tt.z * tt.z);
+            J.m[1][0] = 0.0f; J.m[1][1] = h_y / tt.z; J.m[1][2] = -(h_y * tt.y) / (tt.z * tt.z);
+            J.m[2][0] = 0; J.m[2][1] = 0; J.m[2][2] = 0;
+            Mat3 Wm;
+            Wm.m[0][0] = view_matrix[0]; Wm.m[0][1] = view_matrix[4]; Wm.m[0][2] = view_matrix[8];
+            Wm.m[1][0] = view_matrix[1]; Wm.m[1][1] = view_matrix[5]; Wm.m[1][2] = view_matrix[9];
+            Wm.m[2][0] = view_matrix[2]; Wm.m[2][1] = view_matrix[6]; Wm.m[2][2] = view_matrix[10];
+            Mat3 Vrk;
+            Vrk.m[0][0] = cov3D[0]; Vrk.m[0][1] = cov3D[1]; Vrk.m[0][2] = cov3D[2];
+            Vrk.m[1][0] = cov3D[1]; Vrk.m[1][1] = cov3D[3]; Vrk.m[1][2] = cov3D[4];
+            Vrk.m[2][0] = cov3D[2]; Vrk.m[2][1] = cov3D[4]; Vrk.m[2][2] = cov3D[5];
+            Mat3 T = mul(Wm, J);
+            Mat3 cov2D = mul(mul(transpose(T), transpose(Vrk)), T);
+
+            float a = cov2D.m[0][0] += 0.3f;
+            float b = cov2D.m[0][1];
+            float c = cov2D.m[1][1] += 0.3f;
+
+            float denom = a * c - b * b;
+            float dL_da = 0, dL_db = 0, dL_dc = 0;
+            float denom2inv = 1.0f / ((denom * denom) + 0.0000001f);
+            float dL_dcov[6];
+            if (denom2inv != 0) {
+                dL_da = denom2inv * (-c * c * dL_dconic.x + 2 * b * c * dL_dconic.y + (denom - a * c) * dL_dconic.z);
+                dL_dc = denom2inv * (-a * a * dL_dconic.z + 2 * a * b * dL_dconic.y + (denom - a * c) * dL_dconic.x);
+                dL_db = denom2inv * 2 * (b * c * dL_dconic.x - (denom + 2 * b * b) * dL_dconic.y + a * b * dL_dconic.z);
+
+                dL_dcov[0] = (T.m[0][0] * T.m[0][0] * dL_da + T.m[0][0] * T.m[1][0] * dL_db + T.m[1][0] * T.m[1][0] * dL_dc);
+                dL_dcov[3] = (T.m[0][1] * T.m[0][1] * dL_da + T.m[0][1] * T.m[1][1] * dL_db + T.m[1][1] * T.m[1][1] * dL_dc);
+                dL_dcov[5] = (T.m[0][2] * T.m[0][2] * dL_da + T.m[0][2] * T.m[1][2] * dL_db + T.m[1][2] * T.m[1][2] * dL_dc);
+                dL_dcov[1] = 2 * T.m[0][0] * T.m[0][1] * dL_da + (T.m[0][0] * T.m[1][1] + T.m[0][1] * T.m[1][0]) * dL_db + 2 * T.m[1][0] * T.m[1][1] * dL_dc;
+                dL_dcov[2] = 2 * T.m[0][0] * T.m[0][2] * dL_da + (T.m[0][0] * T.m[1][2] + T.m[0][2] * T.m[1][0]) * dL_db + 2 * T.m[1][0] * T.m[1][2] * dL_dc;
+                dL_dcov[4] = 2 * T.m[0][2] * T.m[0][1] * dL_da + (T.m[0][1] * T.m[1][2] + T.m[0][2] * T.m[1][1]) * dL_db + 2 * T.m[1][1] * T.m[1][2] * dL_dc;
+            } else {
+#pragma unroll
+                for (int i = 0; i < 6; i++) dL_dcov[i] = 0;
+            }
+
+            float dL_dT00 = 2 * (T.m[0][0] * Vrk.m[0][0] + T.m[0][1] * Vrk.m[0][1] + T.m[0][2] * Vrk.m[0][2]) * dL_da +
+                            (T.m[1][0] * Vrk.m[0][0] + T.m[1][1] * Vrk.m[0][1] + T.m[1][2] * Vrk.m[0][2]) * dL_db;
+            float dL_dT01 = 2 * (T.m[0][0] * Vrk.m[1][0] + T.m[0][1] * Vrk.m[1][1] + T.m[0][2] * Vrk.m[1][2]) * dL_da +
+                            (T.m[1][0] * Vrk.m[1][0] + T.m[1][1] * Vrk.m[1][1] + T.m[1][2] * Vrk.m[1][2]) * dL_db;
+            float dL_dT02 = 2 * (T.m[0][0] * Vrk.m[2][0] + T.m[0][1] * Vrk.m[2][1] + T.m[0][2] * Vrk.m[2][2]) * dL_da +
+                            (T.m[1][0] * Vrk.m[2][0] + T.m[1][1] * Vrk.m[2][1] + T.m[1][2] * Vrk.m[2][2]) * dL_db;
+            float dL_dT10 = 2 * (T.m[1][0] * Vrk.m[0][0] + T.m[1][1] * Vrk.m[0][1] + T.m[1][2] * Vrk.m[0][2]) * dL_dc +
+                            (T.m[0][0] * Vrk.m[0][0] + T.m[0][1] * Vrk.m[0][1] + T.m[0][2] * Vrk.m[0][2]) * dL_db;
+            float dL_dT11 = 2 * (T.m[1][0] * Vrk.m[1][0] + T.m[1][1] * Vrk.m[1][1] + T.m[1][2] * Vrk.m[1][2]) * dL_dc +
+                            (T.m[0][0] * Vrk.m[1][0] + T.m[0][1] * Vrk.m[1][1] + T.m[0][2] * Vrk.m[1][2]) * dL_db;
+            float dL_dT12 = 2 * (T.m[1][0] * Vrk.m[2][0] + T.m[1][1] * Vrk.m[2][1] + T.m[1][2] * Vrk.m[2][2]) * dL_dc +
+                            (T.m[0][0] * Vrk.m[2][0] + T.m[0][1] * Vrk.m[2][1] + T.m[0][2] * Vrk.m[2][2]) * dL_db;
+
+            float dL_dJ00 = Wm.m[0][0] * dL_dT00 + Wm.m[0][1] * dL_dT01 + Wm.m[0][2] * dL_dT02;
+            float dL_dJ02 = Wm.m[2][0] * dL_dT00 + Wm.m[2][1] * dL_dT01 + Wm.m[2][2] * dL_dT02;
+            float dL_dJ11 = Wm.m[1][0] * dL_dT10 + Wm.m[1][1] * dL_dT11 + Wm.m[1][2] * dL_dT12;
+            float dL_dJ12 = Wm.m[2][0] * dL_dT10 + Wm.m[2][1] * dL_dT11 + Wm.m[2][2] * dL_dT12;
+
+            float tz = 1.f / tt.z;
+            float tz2 = tz * tz;
+            float tz3 = tz2 * tz;
+
+            float dL_dtx = x_grad_mul * -h_x * tz2 * dL_dJ02;
+            float dL_dty = y_grad_mul * -h_y * tz2 * dL_dJ12;
+            float dL_dtz = -h_x * tz2 * dL_dJ00 - h_y * tz2 * dL_dJ11 + (2 * h_x * tt.x) * tz3 * dL_dJ02 + (2 * h_y * tt.y) * tz3 * dL_dJ12;
+
+            float3 dL_dmean = transform_vec_4x3_transpose({dL_dtx, dL_dty, dL_dtz}, view_matrix);
+
+            // ---- projection of the 2-D mean
+            float4 m_hom = transform_point_4x4(mean, proj);
+            float m_w = 1.0f / (m_hom.w + 0.0000001f);
+            const float2 dm2 = __ldg(dL_dmean2D + idx);
+            float mul1 = (proj[0] * mean.x + proj[4] * mean.y + proj[8] * mean.z + proj[12]) * m_w * m_w;
+            float mul2 = (proj[1] * mean.x + proj[5] * mean.y + proj[9] * mean.z + proj[13]) * m_w * m_w;
+            float3 dL_dmean_b;
+            dL_dmean_b.x = (proj[0] * m_w - proj[3] * mul1) * dm2.x + (proj[1] * m_w - proj[3] * mul2) * dm2.y;
+            dL_dmean_b.y = (proj[4] * m_w - proj[7] * mul1) * dm2.x + (proj[5] * m_w - proj[7] * mul2) * dm2.y;
+            dL_dmean_b.z = (proj[8] * m_w - proj[11] * mul1) * dm2.x + (proj[9] * m_w - proj[11] * mul2) * dm2.y;
+            g_mean = {dL_dmean.x + dL_dmean_b.x, dL_dmean.y + dL_dmean_b.y, dL_dmean.z + dL_dmean_b.z};
+
+            // ---- cov3D -> scale, quaternion (quaternion treated as given, not normalised)
+            float r = rot.x, x = rot.y, y = rot.z, z = rot.w;
+            Mat3 R;
+            R.m[0][0] = 1.f - 2.f * (y * y + z * z); R.m[0][1] = 2.f * (x * y - r * z); R.m[0][2] = 2.f * (x * z + r * y);
+            R.m[1][0] = 2.f * (x * y + r * z); R.m[1][1] = 1.f - 2.f * (x * x + z * z); R.m[1][2] = 2.f * (y * z - r * x);
+            R.m[2][0] = 2.f * (x * z - r * y); R.m[2][1] = 2.f * (y * z + r * x); R.m[2][2] = 1.f - 2.f * (x * x + y * y);
+            Mat3 S;
+#pragma unroll
+            for (int cc = 0; cc < 3; cc++)
+#pragma unroll
+                for (int rr = 0; rr < 3; rr++) S.m[cc][rr] = 0.0f;
+            float3 s = {scale_modifier * sc.x, scale_modifier * sc.y, scale_modifier * sc.z};
+            S.m[0][0] = s.x; S.m[1][1] = s.y; S.m[2][2] = s.z;
+            Mat3 M = mul(S, R);
+            Mat3 dL_dSigma;
+            dL_dSigma.m[0][0] = dL_dcov[0]; dL_dSigma.m[0][1] = 0.5f * dL_dcov[1]; dL_dSigma.m[0][2] = 0.5f * dL_dcov[2];
+            dL_dSigma.m[1][0] = 0.5f * dL_dcov[1]; dL_dSigma.m[1][1] = dL_dcov[3]; dL_dSigma.m[1][2] = 0.5f * dL_dcov[4];
+            dL_dSigma.m[2][0] = 0.5f * dL_dcov[2]; dL_dSigma.m[2][1] = 0.5f * dL_dcov[4]; dL_dSigma.m[2][2] = dL_dcov[5];
+            Mat3 M2;
+#pragma unroll
+            for (int cc = 0; cc < 3; cc++)
+#pragma unroll
+                for (int rr = 0; rr < 3; rr++) M2.m[cc][rr] = 2.0f * M.m[cc][rr];
+            Mat3 dL_dM = mul(M2, dL_dSigma);
+            Mat3 Rt = transpose(R);
+            Mat3 dL_dMt = transpose(dL_dM);
+
+            g_scale.x = Rt.m[0][0] * dL_dMt.m[0][0] + Rt.m[0][1] * dL_dMt.m[0][1] + Rt.m[0][2] * dL_dMt.m[0][2];
+            g_scale.y = Rt.m[1][0] * dL_dMt.m[1][0] + Rt.m[1][1] * dL_dMt.m[1][1] + Rt.m[1][2] * dL_dMt.m[1][2];
+            g_scale.z = Rt.m[2][0] * dL_dMt.m[2][0] + Rt.m[2][1] * dL_dMt.m[2][1] + Rt.m[2][2] * dL_dMt.m[2][2];
+
+#pragma unroll
+            for (int rr = 0; rr < 3; rr++) {
+                dL_dMt.m[0][rr] *= s.x;
+                dL_dMt.m[1][rr] *= s.y;
+                dL_dMt.m[2][rr] *= s.z;
+            }
+            g_rot.x = 2 * z * (dL_dMt.m[0][1] - dL_dMt.m[1][0]) + 2 * y * (dL_dMt.m[2][0] - dL_dMt.m[0][2]) + 2 * x * (dL_dMt.m[1][2] - dL_dMt.m[2][1]);
+            g_rot.y = 2 * y * (dL_dMt.m[1][0] + dL_dMt.m[0][1]) + 2 * z * (dL_dMt.m[2][0] + dL_dMt.m[0][2]) + 2 * r * (dL_dMt.m[1][2] - dL_dMt.m[2][1]) - 4 * x * (dL_dMt.m[2][2] + dL_dMt.m[1][1]);
+            g_rot.z = 2 * x * (dL_dMt.m[1][0] + dL_dMt.m[0][1]) + 2 * r * (dL_dMt.m[2][0] - dL_dMt.m[0][2]) + 2 * z * (dL_dMt.m[1][2] + dL_dMt.m[2][1]) - 4 * y * (dL_dMt.m[2][2] + dL_dMt.m[0][0]);
+            g_rot.w = 2 * r * (dL_dMt.m[0][1] - dL_dMt.m[1][0]) + 2 * x * (dL_dMt.m[2][0] + dL_dMt.m[0][2]) + 2 * y * (dL_dMt.m[1][2] + dL_dMt.m[2][1]) - 4 * z * (dL_dMt.m[1][1] + dL_dMt.m[0][0]);
+        }
+        dL_drots[idx] = g_rot;
+    }
+    __syncthreads();  // everyone is done reading s_mean / s_scale
+    if (t < count) {
+        s_mean[3 * t] = g_mean.x; s_mean[3 * t + 1] = g_mean.y; s_mean[3 * t + 2] = g_mean.z;
+        s_scale[3 * t] = g_scale.x; s_scale[3 * t + 1] = g_scale.y; s_scale[3 * t + 2] = g_scale.z;
+    }
+    __syncthreads();
+    block_store_rows<3>(dL_dmeans + (size_t)base * 3, s_mean, count, vec_mask & 8);
+    block_store_rows<3>(dL_dscales + (size_t)base * 3, s_scale, count, vec_mask & 16);
+}
+
+}  // namespace cgx
+
+using namespace cgx;
+
+extern "C" int cgx_mark_visible(int P, const float* means3D, const float* viewmatrix, uint8_t* present, void* stream)
+{
+    if (P < 0) return CGX_EINVAL;
+    if (P == 0) return CGX_OK;
+    if (!means3D || !viewmatrix || !present) return CGX_EINVAL;
+    mark_visible_kernel<<<(P + 255) / 256, 256, 0, (cudaStream_t)stream>>>(P, means3D, viewmatrix, present);
+    return check_launch();
+}
+
+static int preprocess_launch(bool filter, int P, const float* means3D, const float* scales, float scale_modifier,
+                             const float* rotations, const float* opacities, const float* viewmatrix,
+                             const float* projmatrix, int W, int H, float tanfovx, float tanfovy, float* means2D,
+                             float* depths, int32_t* radii, float* cov3D, float* conic_opacity, void* stream)
+{
+    if (P < 0 || W <= 0 || H <= 0) return CGX_EINVAL;
+    if (P == 0) return CGX_OK;
+    if (!means3D || !scales || !rotations || !viewmatrix || !projmatrix || !radii) return CGX_EINVAL;
+    if (!filter && (!opacities || !means2D || !depths || !cov3D || !conic_opacity)) return CGX_EINVAL;
+    if (!filter && (((uintptr_t)means2D & 7) || !aligned16(conic_opacity))) return CGX_EINVAL;
+    // focal lengths are computed on the host in fp32, as the reference does before launching
+    const float focal_y = H / (2.0f * tanfovy);
+    const float focal_x = W / (2.0f * tanfovx);
+    const int vec_mask = (aligned16(means3D) ? 1 : 0) | (aligned16(scales) ? 2 : 0) | (aligned16(rotations) ? 4 : 0) |
+                         ((!filter && aligned16(cov3D)) ? 8 : 0);
+    const int grid = (P + CGX_BLOCK_SIZE - 1) / CGX_BLOCK_SIZE;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (filter)
+        preprocess_fwd_kernel<true><<<grid, CGX_BLOCK_SIZE, 0, st>>>(
+            P, means3D, scales, scale_modifier, rotations, opacities, viewmatrix, projmatrix, W, H, tanfovx, tanfovy,
+            focal_x, focal_y, radii, (float2*)means2D, depths, cov3D, (float4*)conic_opacity, vec_mask);
+    else
+        preprocess_fwd_kernel<false><<<grid, CGX_BLOCK_SIZE, 0, st>>>(
+            P, means3D, scales, scale_modifier, rotations, opacities, viewmatrix, projmatrix, W, H, tanfovx, tanfovy,
+            focal_x, focal_y, radii, (float2*)means2D, depths, cov3D, (float4*)conic_opacity, vec_mask);
+    return check_launch();
+}
+
+extern "C" int cgx_preprocess_fwd(int P, const float* means3D, const float* scales, float scale_modifier,
+                                  const float* rotations, const float* opacities, const float* viewmatrix,
+                                  const float* projmatrix, int W, int H, float tanfovx, float tanfovy,
+                                  float* means2D, float* depths, int32_t* radii, float* cov3D, float* conic_opacity,
+                                  void* stream)
+{
+    return preprocess_launch(false, P, means3D, scales, scale_modifier, rotations, opacities, viewmatrix, projmatrix,
+                             W, H, tanfovx, tanfovy, means2D, depths, radii, cov3D, conic_opacity, stream);
+}
+
+extern "C" int cgx_filter_preprocess(int P, const float* means3D, const float* scales, float scale_modifier,
+                                     const float* rotations, const float* viewmatrix, const float* projmatrix,
+                                     int W, int H, float tanfovx, float tanfovy, int32_t* radii, void* stream)
+{
+    return preprocess_launch(true, P, means3D, scales, scale_modifier, rotations, nullptr, viewmatrix, projmatrix, W,
+                             H, tanfovx, tanfovy, nullptr, nullptr, radii, nullptr, nullptr, stream);
+}
+
+extern "C" int cgx_sh_to_rgb(int P, int degree, int M, const float* means3D, const float* campos, const float* sh,
+                             float* rgb, uint8_t* clamped, void* stream)
+{
+    if (P < 0 || degree < 0 || degree > 3 || M < (degree + 1) * (degree + 1) || M > 16) return CGX_EINVAL;
+    if (P == 0) return CGX_OK;
+    if (!means3D || !campos || !sh || !rgb || !clamped) return CGX_EINVAL;
+    const size_t smem = (size_t)128 * M * 3 * sizeof(float);
+    sh_to_rgb_kernel<<<(P + 127) / 128, 128, smem, (cudaStream_t)stream>>>(P, degree, M, means3D, campos, sh, rgb,
+                                                                          clamped, aligned16(sh) ? 1 : 0);
+    return check_launch();
+}
+
+extern "C" int cgx_preprocess_bwd(int P, const float* means3D, const float* scales, float scale_modifier,
+                                  const float* rotations, const int32_t* radii, const float* viewmatrix,
+                                  const float* projmatrix, int W, int H, float tanfovx, float tanfovy,
+                                  const float* dL_dmeans2D, const float* dL_dconic_opacity, float* dL_dmeans3D,
+                                  float* dL_dscales, float* dL_drotations, float* dL_dopacity, void* stream)
+{
+    if (P < 0 || W <= 0 || H <= 0) return CGX_EINVAL;
+    if (P == 0) return CGX_OK;
+    if (!means3D || !scales || !rotations || !radii || !viewmatrix || !projmatrix || !dL_dmeans2D ||
+        !dL_dconic_opacity || !dL_dmeans3D || !dL_dscales || !dL_drotations || !dL_dopacity)
+        return CGX_EINVAL;
+    if (((uintptr_t)dL_dmeans2D & 7) || !aligned16(dL_dconic_opacity) || !aligned16(dL_drotations)) return CGX_EINVAL;
+    const float focal_y = H / (2.0f * tanfovy);
+    const float focal_x = W / (2.0f * tanfovx);
+    const int vec_mask = (aligned16(means3D) ? 1 : 0) | (aligned16(scales) ? 2 : 0) | (aligned16(rotations) ? 4 : 0) |
+                         (aligned16(dL_dmeans3D) ? 8 : 0) | (aligned16(dL_dscales) ? 16 : 0);
+    preprocess_bwd_kernel<<<(P + CGX_BLOCK_SIZE - 1) / CGX_BLOCK_SIZE, CGX_BLOCK_SIZE, 0, (cudaStream_t)stream>>>(
+        P, means3D, scales, scale_modifier, rotations, radii, viewmatrix, projmatrix, focal_x, focal_y, tanfovx,
+        tanfovy, (const float2*)dL_dmeans2D, (const float4*)dL_dconic_opacity, dL_dmeans3D, dL_dscales,
+        (float4*)dL_drotations, dL_dopacity, vec_mask);
+    return check_launch();
+}

@@ -1,0 +1,770 @@
+// Per-tile alpha compositing, forward and backward (FP32-pipe bound).
+//
+// One CTA (16x16 threads, one pixel each) per 16x16 tile, like the reference, but:
+//  * the five per-Gaussian inputs are first packed into one 64-byte record per Gaussian
+//    [x y | a b c opacity | r g b | m0..m4 | pad pad]; a tile's batch of 256 records is then staged into
+//    shared memory by 256 asynchronous 64-byte bulk copies (cp.async.bulk, completion on an mbarrier),
+//    double-buffered so the gather of batch i+1 overlaps the blending of batch i; colours and the
+//    plane map channels are read from shared memory instead of per-pixel global loads;
+//  * each warp first culls the batch against its own 16x2 pixel strip with an exact-safe bound
+//    (a Gaussian is dropped for the strip only if alpha < 1/255 is guaranteed there), 32 Gaussians per
+//    ballot, and blends only the survivors;
+//  * the per-tile statistics (sum of per-pixel counters) are reduced in the epilogue;
+//  * the backward reduces the 16 gradient terms of a Gaussian over the warp's 32 pixels with a
+//    transposing butterfly (16 shuffles) and issues ONE atomic per term per warp, straight into the
+//    caller's gradient tensors (which also performs the (P,2,2)+(P,1) -> (P,4) repack).
+//
+// Every wait on an mbarrier is bounded: when the limit is hit the CTA records an error in the device
+// status word, stops blending and returns.
+#include "cgx_common.cuh"
+
+namespace cgx {
+
+__device__ int g_status = 0;  // 0 ok; CGX_ETIMEDOUT when a bounded wait gave up
+
+constexpr unsigned long long WAIT_LIMIT_CYCLES = 1ull << 31;  // ~1 s at B200 clocks
+
+struct __align__(16) Record {
+    float4 q0;  // x, y, conic a, conic b
+    float4 q1;  // conic c, opacity, r, g
+    float4 q2;  // b, m0, m1, m2
+    float4 q3;  // m3, m4, 0, 0
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait.  Returns false after WAIT_LIMIT_CYCLES without completion.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity)
+{
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    while (!mbar_try_wait(bar, parity)) {
+        if ((unsigned long long)(clock64() - t0) > WAIT_LIMIT_CYCLES) return false;
+    }
+    return true;
+}
+// 64-byte global -> shared bulk copy, completion counted in bytes on `bar`.
+__device__ __forceinline__ void bulk_load_64(void* dst_smem, const void* src_gmem, uint64_t* bar)
+{
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], 64, [%2];" ::"r"(
+                     smem_u32(dst_smem)),
+                 "l"(src_gmem), "r"(smem_u32(bar))
+                 : "memory");
+}
+
+// ------------------------------------------------------------------------------------------------ pack
+__global__ void __launch_bounds__(256)
+pack_records_kernel(int P, const float2* __restrict__ means2D, const float4* __restrict__ conic_opacity,
+                    const float* __restrict__ rgb, const float* __restrict__ all_map, int render_geo,
+                    Record* __restrict__ records, int* __restrict__ out_observe)
+{
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= P) return;
+    const float2 xy = means2D[i];
+    const float4 co = conic_opacity[i];
+    const float r = rgb[3 * i], g = rgb[3 * i + 1], b = rgb[3 * i + 2];
+    float m[5] = {0.f, 0.f, 0.f, 0.f, 0.f};
+    if (render_geo) {
+#pragma unroll
+        for (int k = 0; k < 5; k++) m[k] = all_map[5 * i + k];
+    }
+    Record rec;
+    rec.q0 = {xy.x, xy.y, co.x, co.y};
+    rec.q1 = {co.z, co.w, r, g};
+    rec.q2 = {b, m[0], m[1], m[2]};
+    rec.q3 = {m[3], m[4], 0.f, 0.f};
+    records[i] = rec;
+    if (out_observe) out_observe[i] = 0;
+}
+
+// Half extents of the axis-aligned box outside of which opacity * exp(power) < 1/255 for certain.
+// power = -0.5 (a dx^2 + c dy^2) - b dx dy >= -tau bounds |dx| <= sqrt(2 tau c / (ac - b^2)), same for dy with a.
+// The box is inflated (1 % + 0.01 px) so float rounding in the per-pixel test can never keep a pixel the box drops.
+__device__ __forceinline__ float2 cull_extent(float a, float b, float c, float o)
+{
+    const float inf = __int_as_float(0x7f800000);
+    if (!(o >= 1.0f / 255.0f)) return {-1.f, -1.f};  // alpha <= o < 1/255 everywhere (NaN opacity: never kept either)
+    const float det = a * c - b * b;
+    if (!(det > 0.f) || !(a > 0.f) || !(c > 0.f)) return {inf, inf};
+    const float tau = __logf(255.0f * o) * 1.01f + 0.01f;
+    const float ex = sqrtf(2.f * tau * c / det) * 1.01f + 0.01f;
+    const float ey = sqrtf(2.f * tau * a / det) * 1.01f + 0.01f;
+    if (!(ex == ex) || !(ey == ey)) return {inf, inf};
+    return {ex, ey};
+}
+
+constexpr int RENDER_THREADS = CGX_BLOCK_SIZE;
+constexpr int RENDER_WARPS = RENDER_THREADS / 32;
+
+struct FwdSmem {
+    Record rec[2][CGX_BLOCK_SIZE];
+    int id[2][CGX_BLOCK_SIZE];
+    uint8_t hits[RENDER_WARPS][CGX_BLOCK_SIZE];
+    uint64_t bar[2];
+    int red[2][RENDER_WARPS];
+};
+
+template <bool CULL>
+__global__ void __launch_bounds__(RENDER_THREADS)
+render_fwd_kernel(const uint2* __restrict__ ranges, const uint32_t* __restrict__ point_list, int W, int H,
+                  const float focal_x, const float focal_y, const float cx, const float cy,
+                  const Record* __restrict__ records, float* __restrict__ final_T, uint32_t* __restrict__ n_contrib,
+                  uint32_t* __restrict__ n_contrib2loss, const uint8_t* __restrict__ compute_locally,
+                  const float* __restrict__ bg_color, float* __restrict__ out_color, int* __restrict__ out_observe,
+                  float* __restrict__ out_all_map, float* __restrict__ out_plane_depth, const bool render_geo,
+                  int* __restrict__ n_render_t, int* __restrict__ n_consider_t, int* __restrict__ n_contrib_t)
+{
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    FwdSmem& sm = *reinterpret_cast<FwdSmem*>(smem_raw);
+
+    const uint32_t horizontal_blocks = (W + CGX_BLOCK_X - 1) / CGX_BLOCK_X;
+    const uint32_t block_id = blockIdx.y * horizontal_blocks + blockIdx.x;
+    const int tid = threadIdx.y * CGX_BLOCK_X + threadIdx.x;
+    const int lane = tid & 31, warp = tid >> 5;
+
+    uint2 pix_min = {blockIdx.x * CGX_BLOCK_X, blockIdx.y * CGX_BLOCK_Y};
+    uint2 pix = {pix_min.x + threadIdx.x, pix_min.y + threadIdx.y};
+    uint32_t pix_id = W * pix.y + pix.x;
+    float2 pixf = {(float)pix.x, (float)pix.y};
+    const float2 ray = {(pixf.x - cx) / focal_x, (pixf.y - cy) / focal_y};
+    bool inside = pix.x < W && pix.y < H;
+    const size_t HW = (size_t)H * W;
+
+    if (!compute_locally[block_id]) {
+        // tiles owned by another rank: defined zeros in every image output
+        if (inside) {
+            final_T[pix_id] = 0.f;
+            n_contrib[pix_id] = 0;
+            n_contrib2loss[pix_id] = 0;
+            for (int ch = 0; ch < CGX_NCH; ch++) out_color[ch * HW + pix_id] = 0.f;
+            for (int ch = 0; ch < CGX_NMAP; ch++) out_all_map[ch * HW + pix_id] = 0.f;
+            out_plane_depth[pix_id] = 0.f;
+        }
+        if (tid == 0) {
+            const uint2 rg = ranges[block_id];
+            n_render_t[block_id] = rg.y - rg.x;
+            n_consider_t[block_id] = 0;
+            n_contrib_t[block_id] = 0;
+        }
+        return;
+    }
+
+    bool done = !inside;
+    uint2 range = ranges[block_id];
+    const int rounds = ((range.y - range.x + CGX_BLOCK_SIZE - 1) / CGX_BLOCK_SIZE);
+    int toDo = range.y - range.x;
+
+    if (tid == 0) {
+        mbar_init(&sm.bar[0], 1);
+        mbar_init(&sm.bar[1], 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
+    // strip of this warp: rows [sy0, sy1], columns [sx0, sx1] in pixel coordinates
+    const float sx0 = (float)pix_min.x, sx1 = (float)(pix_min.x + CGX_BLOCK_X - 1);
+    const float sy0 = (float)(pix_min.y + 2 * warp), sy1 = sy0 + 1.f;
+
+    auto issue = [&](int batch, int buf) {
+        const int progress = batch * CGX_BLOCK_SIZE + tid;
+        const int n_valid = min(CGX_BLOCK_SIZE, (int)(range.y - range.x) - batch * CGX_BLOCK_SIZE);
+        if (tid == 0) mbar_expect_tx(&sm.bar[buf], (uint32_t)n_valid * 64u);
+        if (range.x + progress < range.y) {
+            const int coll_id = point_list[range.x + progress];
+            sm.id[buf][tid] = coll_id;
+            bulk_load_64(&sm.rec[buf][tid], records + coll_id, &sm.bar[buf]);
+        }
+    };
+
+    float T = 1.0f;
+    uint32_t last_contributor = 0;
+    uint32_t thread_n_contrib2loss = 0;
+    float C[CGX_NCH] = {0};
+    float All_map[CGX_NMAP] = {0};
+    bool failed = false;
+
+    if (rounds > 0) issue(0, 0);
+
+    for (int i = 0; i < rounds; i++, toDo -= CGX_BLOCK_SIZE) {
+        const int buf = i & 1;
+        if (!failed && !mbar_wait(&sm.bar[buf], (i >> 1) & 1)) failed = true;
+        // End if the entire block votes that it is done rasterizing (also orders buffer reuse).
+        int num_done = __syncthreads_count(done || failed);
+        if (num_done == CGX_BLOCK_SIZE) break;
+        if (i + 1 < rounds) issue(i + 1, buf ^ 1);
+
+        const int nb = min(CGX_BLOCK_SIZE, toDo);
+        const Record* rec = sm.rec[buf];
+        const int* ids = sm.id[buf];
+        const uint32_t contributor_base = (uint32_t)i * CGX_BLOCK_SIZE;
+
+        if (CULL) {
+            // every warp compacts the Gaussians whose safe box meets its strip (order preserved)
+            uint8_t* my_hits = sm.hits[warp];
+            int n_hits = 0;
+            for (int j0 = 0; j0 < nb; j0 += 32) {
+                const int j = j0 + lane;
+                bool hit = false;
+                if (j < nb) {
+                    const float4 q0 = rec[j].q0;
+                    const float4 q1 = rec[j].q1;
+                    const float2 e = cull_extent(q0.z, q0.w, q1.x, q1.y);
+                    hit = (q0.x + e.x >= sx0) && (q0.x - e.x <= sx1) && (q0.y + e.y >= sy0) && (q0.y - e.y <= sy1);
+                }
+                const uint32_t m = __ballot_sync(0xffffffffu, hit);
+                if (hit) my_hits[n_hits + __popc(m & ((1u << lane) - 1u))] = (uint8_t)j;
+                n_hits += __popc(m);
+            }
+            __syncwarp();
+            for (int k = 0; !done && k < n_hits; k++) {
+                const int j = my_hits[k];
+                const float4 q0 = rec[j].q0;
+                const float4 q1 = rec[j].q1;
+                float2 xy = {q0.x, q0.y};
+                float2 d = {xy.x - pixf.x, xy.y - pixf.y};
+                float4 con_o = {q0.z, q0.w, q1.x, q1.y};
+                float power = -0.5f * (con_o.x * d.x * d.x + con_o.z * d.y * d.y) - con_o.y * d.x * d.y;
+                if (power > 0.0f) continue;
+                float alpha = min(0.99f, con_o.w * exp(power));
+                if (alpha < 1.0f / 255.0f) continue;
+                float test_T = T * (1 - alpha);
+                if (test_T < 0.0001f) {
+                    done = true;
+                    continue;
+                }
+                thread_n_contrib2loss++;
+                const float4 q2 = rec[j].q2;
+                const float feat[CGX_NCH] = {q1.z, q1.w, q2.x};
+                for (int ch = 0; ch < CGX_NCH; ch++) C[ch] += feat[ch] * alpha * T;
+                if (render_geo) {
+                    const float4 q3 = rec[j].q3;
+                    const float am[CGX_NMAP] = {q2.y, q2.z, q2.w, q3.x, q3.y};
+                    for (int ch = 0; ch < CGX_NMAP; ch++) All_map[ch] += am[ch] * alpha * T;
+                }
+                if (T > 0.5) atomicAdd(&(out_observe[ids[j]]), 1);
+                T = test_T;
+                last_contributor = contributor_base + j + 1;
+            }
+        } else {
+            for (int j = 0; !done && j < nb; j++) {
+                const float4 q0 = rec[j].q0;
+                const float4 q1 = rec[j].q1;
+                float2 xy = {q0.x, q0.y};
+                float2 d = {xy.x - pixf.x, xy.y - pixf.y};
+                float4 con_o = {q0.z, q0.w, q1.x, q1.y};
+                float power = -0.5f * (con_o.x * d.x * d.x + con_o.z * d.y * d.y) - con_o.y * d.x * d.y;
+                if (power > 0.0f) continue;
+                float alpha = min(0.99f, con_o.w * exp(power));
+                if (alpha < 1.0f / 255.0f) continue;
+                float test_T = T * (1 - alpha);
+                if (test_T < 0.0001f) {
+                    done = true;
+                    continue;
+                }
+                thread_n_contrib2loss++;
+                const float4 q2 = rec[j].q2;
+                const float feat[CGX_NCH] = {q1.z, q1.w, q2.x};
+                for (int ch = 0; ch < CGX_NCH; ch++) C[ch] += feat[ch] * alpha * T;
+                if (render_geo) {
+                    const float4 q3 = rec[j].q3;
+                    const float am[CGX_NMAP] = {q2.y, q2.z, q2.w, q3.x, q3.y};
+                    for (int ch = 0; ch < CGX_NMAP; ch++) All_map[ch] += am[ch] * alpha * T;
+                }
+                if (T > 0.5) atomicAdd(&(out_observe[ids[j]]), 1);
+                T = test_T;
+                last_contributor = contributor_base + j + 1;
+            }
+        }
+    }
+    if (failed && lane == 0) atomicExch(&g_status, CGX_ETIMEDOUT);
+
+    if (inside) {
+        final_T[pix_id] = T;
+        n_contrib[pix_id] = last_contributor;
+        n_contrib2loss[pix_id] = thread_n_contrib2loss;
+        for (int ch = 0; ch < CGX_NCH; ch++) out_color[ch * HW + pix_id] = C[ch] + T * bg_color[ch];
+        if (render_geo) {
+            for (int ch = 0; ch < CGX_NMAP; ch++) out_all_map[ch * HW + pix_id] = All_map[ch];
+            out_plane_depth[pix_id] = All_map[4] / -(All_map[0] * ray.x + All_map[1] * ray.y + All_map[2] + 1.0e-8);
+        } else {
+            for (int ch = 0; ch < CGX_NMAP; ch++) out_all_map[ch * HW + pix_id] = 0.f;
+            out_plane_depth[pix_id] = 0.f;
+        }
+    }
+
+    // per-tile sums of the two per-pixel counters (pixels outside the image count as 0)
+    int a = inside ? (int)last_contributor : 0;
+    int b = inside ? (int)thread_n_contrib2loss : 0;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        a += __shfl_xor_sync(0xffffffffu, a, o);
+        b += __shfl_xor_sync(0xffffffffu, b, o);
+    }
+    if (lane == 0) {
+        sm.red[0][warp] = a;
+        sm.red[1][warp] = b;
+    }
+    __syncthreads();
+    if (tid == 0) {
+        int sa = 0, sb = 0;
+        for (int w = 0; w < RENDER_WARPS; w++) {
+            sa += sm.red[0][w];
+            sb += sm.red[1][w];
+        }
+        n_render_t[block_id] = range.y - range.x;
+        n_consider_t[block_id] = sa;
+        n_contrib_t[block_id] = sb;
+    }
+}
+
+__global__ void __launch_bounds__(RENDER_THREADS)
+tile_stats_kernel(int W, int H, const uint2* __restrict__ ranges, const uint32_t* __restrict__ n_contrib_px,
+                  const uint32_t* __restrict__ n_c2l_px, const uint8_t* __restrict__ compute_locally,
+                  int* __restrict__ n_render, int* __restrict__ n_consider, int* __restrict__ n_contrib)
+{
+    __shared__ int red[2][RENDER_WARPS];
+    const uint32_t block_id = blockIdx.y * gridDim.x + blockIdx.x;
+    const int tid = threadIdx.y * CGX_BLOCK_X + threadIdx.x;
+    const int lane = tid & 31, warp = tid >> 5;
+    const bool local = compute_locally[block_id];
+    const uint32_t px = blockIdx.x * CGX_BLOCK_X + threadIdx.x, py = blockIdx.y * CGX_BLOCK_Y + threadIdx.y;
+    const bool inside = px < (uint32_t)W && py < (uint32_t)H;
+    int a = (local && inside) ? (int)n_contrib_px[(size_t)W * py + px] : 0;
+    int b = (local && inside) ? (int)n_c2l_px[(size_t)W * py + px] : 0;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        a += __shfl_xor_sync(0xffffffffu, a, o);
+        b += __shfl_xor_sync(0xffffffffu, b, o);
+    }
+    if (lane == 0) {
+        red[0][warp] = a;
+        red[1][warp] = b;
+    }
+    __syncthreads();
+    if (tid == 0) {
+        int sa = 0, sb = 0;
+        for (int w = 0; w < RENDER_WARPS; w++) {
+            sa += red[0][w];
+            sb += red[1][w];
+        }
+        const uint2 rg = ranges[block_id];
+        n_render[block_id] = rg.y - rg.x;
+        n_consider[block_id] = sa;
+        n_contrib[block_id] = sb;
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ backward
+struct BwdOut {
+    float* ptr[16];   // destination array of gradient term k
+    int stride[16];   // floats per Gaussian in that array
+};
+
+struct BwdSmem {
+    Record rec[2][CGX_BLOCK_SIZE];
+    int id[2][CGX_BLOCK_SIZE];
+    uint8_t hits[RENDER_WARPS][CGX_BLOCK_SIZE];
+    uint64_t bar[2];
+};
+
+// Sum v[0..15] over the 32 lanes.  After the call, lane L holds in the return value the total of term
+// term_of_lane(L) = 8*bit4 + 4*bit3 + 2*bit2 + bit1 of L (lanes 2m and 2m+1 hold the same total).
+__device__ __forceinline__ float warp_reduce16(float (&v)[16], int lane)
+{
+    const bool b4 = lane & 16, b3 = lane & 8, b2 = lane & 4, b1 = lane & 2;
+    float w8[8];
+#pragma unroll
+    for (int k = 0; k < 8; k++) {
+        const float keep = b4 ? v[8 + k] : v[k];
+        const float send = b4 ? v[k] : v[8 + k];
+        w8[k] = keep + __shfl_xor_sync(0xffffffffu, send, 16);
+    }
+    float w4[4];
+#pragma unroll
+    for (int k = 0; k < 4; k++) {
+        const float keep = b3 ? w8[4 + k] : w8[k];
+        const float send = b3 ? w8[k] : w8[4 + k];
+        w4[k] = keep + __shfl_xor_sync(0xffffffffu, send, 8);
+    }
+    float w2[2];
+#pragma unroll
+    for (int k = 0; k < 2; k++) {
+        const float keep = b2 ? w4[2 + k] : w4[k];
+        const float send = b2 ? w4[k] : w4[2 + k];
+        w2[k] = keep + __shfl_xor_sync(0xffffffffu, send, 4);
+    }
+    const float keep = b1 ? w2[1] : w2[0];
+    const float send = b1 ? w2[0] : w2[1];
+    float w1 = keep + __shfl_xor_sync(0xffffffffu, send, 2);
+    w1 += __shfl_xor_sync(0xffffffffu, w1, 1);
+    return w1;
+}
+
+template <bool CULL>
+__global__ void __launch_bounds__(RENDER_THREADS)
+render_bwd_kernel(const uint2* __restrict__ ranges, const uint32_t* __restrict__ point_list, int W, int H, float fx,
+                  float fy, const float* __restrict__ bg_color, const Record* __restrict__ records,
+                  const float* __restrict__ all_map_pixels, const float* __restrict__ final_Ts,
+                  const uint32_t* __restrict__ n_contrib, const uint8_t* __restrict__ compute_locally,
+                  const float* __restrict__ dL_dpixels, const float* __restrict__ dL_dout_all_maps,
+                  const float* __restrict__ dL_dout_plane_depths, const bool render_geo, BwdOut out)
+{
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    BwdSmem& sm = *reinterpret_cast<BwdSmem*>(smem_raw);
+
+    const uint32_t horizontal_blocks = (W + CGX_BLOCK_X - 1) / CGX_BLOCK_X;
+    const uint32_t block_id = blockIdx.y * horizontal_blocks + blockIdx.x;
+    if (!compute_locally[block_id]) return;
+    const int tid = threadIdx.y * CGX_BLOCK_X + threadIdx.x;
+    const int lane = tid & 31, warp = tid >> 5;
+
+    const uint2 pix_min = {blockIdx.x * CGX_BLOCK_X, blockIdx.y * CGX_BLOCK_Y};
+    const uint2 pix = {pix_min.x + threadIdx.x, pix_min.y + threadIdx.y};
+    const uint32_t pix_id = W * pix.y + pix.x;
+    const float2 pixf = {(float)pix.x, (float)pix.y};
+    // double arithmetic (W * 0.5 is a double expression), narrowed to float afterwards
+    const float2 ray = {(float)((pixf.x - W * 0.5) / fx), (float)((pixf.y - H * 0.5) / fy)};
+    const bool inside = pix.x < W && pix.y < H;
+    const uint2 range = ranges[block_id];
+    const size_t HW = (size_t)H * W;
+
+    const int rounds = ((range.y - range.x + CGX_BLOCK_SIZE - 1) / CGX_BLOCK_SIZE);
+    bool done = !inside;
+    int toDo = range.y - range.x;
+
+    if (tid == 0) {
+        mbar_init(&sm.bar[0], 1);
+        mbar_init(&sm.bar[1], 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
+    // destination of the term this lane owns after the butterfly
+    const int my_term = ((lane >> 4) & 1) * 8 + ((lane >> 3) & 1) * 4 + ((lane >> 2) & 1) * 2 + ((lane >> 1) & 1);
+    float* my_ptr = out.ptr[my_term];
+    const int my_stride = out.stride[my_term];
+    const bool my_write = (lane & 1) == 0 && my_ptr != nullptr;
+
+    const float sx0 = (float)pix_min.x, sx1 = (float)(pix_min.x + CGX_BLOCK_X - 1);
+    const float sy0 = (float)(pix_min.y + 2 * warp), sy1 = sy0 + 1.f;
+
+    auto issue = [&](int batch, int buf) {
+        const int progress = batch * CGX_BLOCK_SIZE + tid;
+        const int n_valid = min(CGX_BLOCK_SIZE, (int)(range.y - range.x) - batch * CGX_BLOCK_SIZE);
+        if (tid == 0) mbar_expect_tx(&sm.bar[buf], (uint32_t)n_valid * 64u);
+        if (range.x + progress < range.y) {
+            const int coll_id = point_list[range.y - progress - 1];  // back to front
+            sm.id[buf][tid] = coll_id;
+            bulk_load_64(&sm.rec[buf][tid], records + coll_id, &sm.bar[buf]);
+        }
+    };
+
+    const float T_final = inside ? final_Ts[pix_id] : 0;
+    float T = T_final;
+    const uint32_t total = range.y - range.x;
+    const int last_contributor = inside ? n_contrib[pix_id] : 0;
+
+    float accum_rec[CGX_NCH] = {0};
+    float accum_all_map[CGX_NMAP] = {0};
+    float dL_dpixel[CGX_NCH] = {0};
+    float dL_dout_all_map[CGX_NMAP] = {0};
+    if (inside) {
+        for (int i = 0; i < CGX_NCH; i++) dL_dpixel[i] = dL_dpixels[i * HW + pix_id];
+        if (render_geo) {
+            for (int i = 0; i < CGX_NMAP; i++) dL_dout_all_map[i] = dL_dout_all_maps[i * HW + pix_id];
+            const float3 normal = {all_map_pixels[pix_id], all_map_pixels[HW + pix_id], all_map_pixels[2 * HW + pix_id]};
+            const float distance = all_map_pixels[4 * HW + pix_id];
+            const float tmp = (normal.x * ray.x + normal.y * ray.y + normal.z + 1.0e-8);
+            dL_dout_all_map[CGX_NMAP - 1] += (-dL_dout_plane_depths[pix_id] / tmp);
+            dL_dout_all_map[0] += dL_dout_plane_depths[pix_id] * (distance / (tmp * tmp) * ray.x);
+            dL_dout_all_map[1] += dL_dout_plane_depths[pix_id] * (distance / (tmp * tmp) * ray.y);
+            dL_dout_all_map[2] += dL_dout_plane_depths[pix_id] * (distance / (tmp * tmp));
+        }
+    }
+    float bg_dot_dpixel = 0;
+    for (int i = 0; i < CGX_NCH; i++) bg_dot_dpixel += bg_color[i] * dL_dpixel[i];
+
+    float last_alpha = 0;
+    float last_color[CGX_NCH] = {0};
+    float last_all_map[CGX_NMAP] = {0};
+    const float ddelx_dx = 0.5 * W;
+    const float ddely_dy = 0.5 * H;
+    bool failed = false;
+
+    if (rounds > 0) issue(0, 0);
+
+    for (int i = 0; i < rounds; i++, toDo -= CGX_BLOCK_SIZE) {
+        const int buf = i & 1;
+        if (!mbar_wait(&sm.bar[buf], (i >> 1) & 1)) failed = true;
+        const int any_failed = __syncthreads_or(failed);
+        if (any_failed) break;
+        if (i + 1 < rounds) issue(i + 1, buf ^ 1);
+
+        const int nb = min(CGX_BLOCK_SIZE, toDo);
+        const Record* rec = sm.rec[buf];
+        const int* ids = sm.id[buf];
+        // batch slot j holds sorted position range.y - 1 - (i*256 + j); its 0-based index in the tile list is
+        // total - 1 - (i*256 + j), which is the reference's `contributor` after its decrement.
+        const uint32_t idx_base = total - 1 - (uint32_t)i * CGX_BLOCK_SIZE;
+
+        uint8_t* my_hits = sm.hits[warp];
+        int n_hits = nb;
+        if (CULL) {
+            n_hits = 0;
+            for (int j0 = 0; j0 < nb; j0 += 32) {
+                const int j = j0 + lane;
+                bool hit = false;
+                if (j < nb) {
+                    const float4 q0 = rec[j].q0;
+                    const float4 q1 = rec[j].q1;
+                    const float2 e = cull_extent(q0.z, q0.w, q1.x, q1.y);
+                    hit = (q0.x + e.x >= sx0) && (q0.x - e.x <= sx1) && (q0.y + e.y >= sy0) && (q0.y - e.y <= sy1);
+                }
+                const uint32_t m = __ballot_sync(0xffffffffu, hit);
+                if (hit) my_hits[n_hits + __popc(m & ((1u << lane) - 1u))] = (uint8_t)j;
+                n_hits += __popc(m);
+            }
+            __syncwarp();
+        }
+
+        for (int k = 0; k < n_hits; k++) {
+            const int j = CULL ? (int)my_hits[k] : k;
+            const uint32_t contributor = idx_base - (uint32_t)j;
+            float v[16];
+            bool valid = false;
+            if (!done && contributor < (uint32_t)last_contributor) {
+                const float4 q0 = rec[j].q0;
+                const float4 q1 = rec[j].q1;
+                const float2 xy = {q0.x, q0.y};
+                const float2 d = {xy.x - pixf.x, xy.y - pixf.y};
+                const float4 con_o = {q0.z, q0.w, q1.x, q1.y};
+                const float power = -0.5f * (con_o.x * d.x * d.x + con_o.z * d.y * d.y) - con_o.y * d.x * d.y;
+                if (!(power > 0.0f)) {
+                    const float G = exp(power);
+                    const float alpha = min(0.99f, con_o.w * G);
+                    if (!(alpha < 1.0f / 255.0f)) {
+                        valid = true;
+                        T = T / (1.f - alpha);
+                        const float dchannel_dcolor = alpha * T;
+                        float dL_dalpha = 0.0f;
+                        const float4 q2 = rec[j].q2;
+                        const float col[CGX_NCH] = {q1.z, q1.w, q2.x};
+#pragma unroll
+                        for (int ch = 0; ch < CGX_NCH; ch++) {
+                            const float c = col[ch];
+                            accum_rec[ch] = last_alpha * last_color[ch] + (1.f - last_alpha) * accum_rec[ch];
+                            last_color[ch] = c;
+                            const float dL_dchannel = dL_dpixel[ch];
+                            dL_dalpha += (c - accum_rec[ch]) * dL_dchannel;
+                            v[8 + ch] = dchannel_dcolor * dL_dchannel;
+                        }
+                        if (render_geo) {
+                            const float4 q3 = rec[j].q3;
+                            const float am[CGX_NMAP] = {q2.y, q2.z, q2.w, q3.x, q3.y};
+#pragma unroll
+                            for (int ch = 0; ch < CGX_NMAP; ch++) {
+                                const float c = am[ch];
+                                accum_all_map[ch] = last_alpha * last_all_map[ch] + (1.f - last_alpha) * accum_all_map[ch];
+                                last_all_map[ch] = c;
+                                const float dL_dchannel = dL_dout_all_map[ch];
+                                dL_dalpha += (c - accum_all_map[ch]) * dL_dchannel;
+                                v[11 + ch] = dchannel_dcolor * dL_dchannel;
+                            }
+                        } else {
+#pragma unroll
+                            for (int ch = 0; ch < CGX_NMAP; ch++) v[11 + ch] = 0.f;
+                        }
+                        dL_dalpha *= T;
+                        last_alpha = alpha;
+                        dL_dalpha += (-T_final / (1.f - alpha)) * bg_dot_dpixel;
+
+                        const float dL_dG = con_o.w * dL_dalpha;
+                        const float gdx = G * d.x;
+                        const float gdy = G * d.y;
+                        const float dG_ddelx = -gdx * con_o.x - gdy * con_o.y;
+                        const float dG_ddely = -gdy * con_o.z - gdx * con_o.y;
+                        v[0] = dL_dG * dG_ddelx * ddelx_dx;
+                        v[1] = dL_dG * dG_ddely * ddely_dy;
+                        v[2] = fabs(dL_dG * dG_ddelx * ddelx_dx);
+                        v[3] = fabs(dL_dG * dG_ddely * ddely_dy);
+                        v[4] = -0.5f * gdx * d.x * dL_dG;
+                        v[5] = -0.5f * gdx * d.y * dL_dG;
+                        v[6] = -0.5f * gdy * d.y * dL_dG;
+                        v[7] = G * dL_dalpha;
+                    }
+                }
+            }
+            if (!__any_sync(0xffffffffu, valid)) continue;
+            if (!valid) {
+#pragma unroll
+                for (int t = 0; t < 16; t++) v[t] = 0.f;
+            }
+            const float tot = warp_reduce16(v, lane);
+            if (my_write) atomicAdd(my_ptr + (size_t)ids[j] * my_stride, tot);
+        }
+    }
+    if (failed && lane == 0) atomicExch(&g_status, CGX_ETIMEDOUT);
+}
+
+}  // namespace cgx
+
+using namespace cgx;
+
+extern "C" size_t cgx_render_records_bytes(int P) { return (size_t)(P > 0 ? P : 0) * sizeof(Record); }
+
+extern "C" int cgx_device_status(int* status_host, void* stream)
+{
+    if (!status_host) return CGX_EINVAL;
+    cudaError_t e = cudaStreamSynchronize((cudaStream_t)stream);
+    if (e == cudaSuccess) e = cudaMemcpyFromSymbol(status_host, g_status, sizeof(int));
+    if (e != cudaSuccess) { set_cuda_error(e); return CGX_ECUDA; }
+    if (*status_host != 0) {
+        int zero = 0;
+        cudaMemcpyToSymbol(g_status, &zero, sizeof(int));
+    }
+    return CGX_OK;
+}
+
+static int g_render_variant = 1;  // 1: per-warp culling on (default), 0: off
+
+extern "C" int cgx_set_render_variant(int cull)
+{
+    g_render_variant = cull ? 1 : 0;
+    return CGX_OK;
+}
+
+extern "C" int cgx_render_fwd(int P, int W, int H, float tanfovx, float tanfovy, const uint32_t* ranges,
+                              const uint32_t* point_list, const float* means2D, const float* rgb, const float* all_map,
+                              const float* conic_opacity, const uint8_t* compute_locally, const float* bg,
+                              int render_geo, void* records, float* final_T, uint32_t* n_contrib,
+                              uint32_t* n_contrib2loss, float* out_color, int32_t* out_observe, float* out_all_map,
+                              float* out_plane_depth, int32_t* n_render_t, int32_t* n_consider_t, int32_t* n_contrib_t,
+                              void* stream)
+{
+    if (P < 0 || W <= 0 || H <= 0) return CGX_EINVAL;
+    if (!ranges || !compute_locally || !bg || !final_T || !n_contrib || !n_contrib2loss || !out_color ||
+        !out_all_map || !out_plane_depth || !n_render_t || !n_consider_t || !n_contrib_t)
+        return CGX_EINVAL;
+    if (P > 0 && (!means2D || !rgb || !conic_opacity || !records || !out_observe || (render_geo && !all_map)))
+        return CGX_EINVAL;
+    if (P > 0 && (((uintptr_t)means2D & 7) || !aligned16(conic_opacity) || !aligned16(records))) return CGX_EINVAL;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (P > 0)
+        pack_records_kernel<<<(P + 255) / 256, 256, 0, st>>>(P, (const float2*)means2D, (const float4*)conic_opacity,
+                                                             rgb, all_map, render_geo, (Record*)records, out_observe);
+    const float focal_y = H / (2.0f * tanfovy);
+    const float focal_x = W / (2.0f * tanfovx);
+    const dim3 grid((W + CGX_BLOCK_X - 1) / CGX_BLOCK_X, (H + CGX_BLOCK_Y - 1) / CGX_BLOCK_Y, 1);
+    const dim3 block(CGX_BLOCK_X, CGX_BLOCK_Y, 1);
+    const size_t smem = sizeof(FwdSmem);
+    cudaError_t e;
+    if (g_render_variant) {
+        e = cudaFuncSetAttribute(render_fwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) { set_cuda_error(e); return CGX_ECUDA; }
+        render_fwd_kernel<true><<<grid, block, smem, st>>>(
+            (const uint2*)ranges, point_list, W, H, focal_x, focal_y, float(W * 0.5f), float(H * 0.5f),
+            (const Record*)records, final_T, n_contrib, n_contrib2loss, compute_locally, bg, out_color, out_observe,
+            out_all_map, out_plane_depth, render_geo != 0, n_render_t, n_consider_t, n_contrib_t);
+    } else {
+        e = cudaFuncSetAttribute(render_fwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) { set_cuda_error(e); return CGX_ECUDA; }
+        render_fwd_kernel<false><<<grid, block, smem, st>>>(
+            (const uint2*)ranges, point_list, W, H, focal_x, focal_y, float(W * 0.5f), float(H * 0.5f),
+            (const Record*)records, final_T, n_contrib, n_contrib2loss, compute_locally, bg, out_color, out_observe,
+            out_all_map, out_plane_depth, render_geo != 0, n_render_t, n_consider_t, n_contrib_t);
+    }
+    return check_launch();
+}
+
+extern "C" int cgx_tile_stats(int W, int H, const uint32_t* ranges, const uint32_t* n_contrib_px,
+                              const uint32_t* n_contrib2loss_px, const uint8_t* compute_locally, int32_t* n_render,
+                              int32_t* n_consider, int32_t* n_contrib, void* stream)
+{
+    if (W <= 0 || H <= 0 || !ranges || !n_contrib_px || !n_contrib2loss_px || !compute_locally || !n_render ||
+        !n_consider || !n_contrib)
+        return CGX_EINVAL;
+    const dim3 grid((W + CGX_BLOCK_X - 1) / CGX_BLOCK_X, (H + CGX_BLOCK_Y - 1) / CGX_BLOCK_Y, 1);
+    const dim3 block(CGX_BLOCK_X, CGX_BLOCK_Y, 1);
+    tile_stats_kernel<<<grid, block, 0, (cudaStream_t)stream>>>(W, H, (const uint2*)ranges, n_contrib_px,
+                                                               n_contrib2loss_px, compute_locally, n_render,
+                                                               n_consider, n_contrib);
+    return check_launch();
+}
+
+extern "C" int cgx_render_bwd(int P, int W, int H, float tanfovx, float tanfovy, const uint32_t* ranges,
+                              const uint32_t* point_list, const float* bg, const void* records,
+                              const float* all_map_pixels, const float* final_T, const uint32_t* n_contrib,
+                              const uint8_t* compute_locally, const float* dL_dcolor, const float* dL_dout_all_map,
+                              const float* dL_dout_plane_depth, int render_geo, float* dL_dmeans2D,
+                              float* dL_dmeans2D_abs, float* dL_dconic_opacity, float* dL_drgb, float* dL_dall_map,
+                              void* stream)
+{
+    if (P < 0 || W <= 0 || H <= 0) return CGX_EINVAL;
+    if (P == 0) return CGX_OK;
+    if (!ranges) return CGX_EINVAL;
+    if (!bg || !records || !final_T || !n_contrib || !compute_locally || !dL_dcolor || !dL_dmeans2D ||
+        !dL_dmeans2D_abs || !dL_dconic_opacity || !dL_drgb || !dL_dall_map)
+        return CGX_EINVAL;
+    if (render_geo && (!all_map_pixels || !dL_dout_all_map || !dL_dout_plane_depth)) return CGX_EINVAL;
+    if (!aligned16(records)) return CGX_EINVAL;
+    cudaStream_t st = (cudaStream_t)stream;
+    cudaError_t e = cudaMemsetAsync(dL_dmeans2D, 0, (size_t)P * 2 * sizeof(float), st);
+    if (e == cudaSuccess) e = cudaMemsetAsync(dL_dmeans2D_abs, 0, (size_t)P * 3 * sizeof(float), st);
+    if (e == cudaSuccess) e = cudaMemsetAsync(dL_dconic_opacity, 0, (size_t)P * 4 * sizeof(float), st);
+    if (e == cudaSuccess) e = cudaMemsetAsync(dL_drgb, 0, (size_t)P * 3 * sizeof(float), st);
+    if (e == cudaSuccess) e = cudaMemsetAsync(dL_dall_map, 0, (size_t)P * 5 * sizeof(float), st);
+    if (e != cudaSuccess) { set_cuda_error(e); return CGX_ECUDA; }
+
+    BwdOut out;
+    float* ptrs[16] = {dL_dmeans2D, dL_dmeans2D + 1, dL_dmeans2D_abs, dL_dmeans2D_abs + 1,
+                       dL_dconic_opacity, dL_dconic_opacity + 1, dL_dconic_opacity + 2, dL_dconic_opacity + 3,
+                       dL_drgb, dL_drgb + 1, dL_drgb + 2,
+                       dL_dall_map, dL_dall_map + 1, dL_dall_map + 2, dL_dall_map + 3, dL_dall_map + 4};
+    const int strides[16] = {2, 2, 3, 3, 4, 4, 4, 4, 3, 3, 3, 5, 5, 5, 5, 5};
+    for (int k = 0; k < 16; k++) {
+        out.ptr[k] = ptrs[k];
+        out.stride[k] = strides[k];
+    }
+    if (!render_geo)
+        for (int k = 11; k < 16; k++) out.ptr[k] = nullptr;
+
+    const float focal_y = H / (2.0f * tanfovy);
+    const float focal_x = W / (2.0f * tanfovx);
+    const dim3 grid((W + CGX_BLOCK_X - 1) / CGX_BLOCK_X, (H + CGX_BLOCK_Y - 1) / CGX_BLOCK_Y, 1);
+    const dim3 block(CGX_BLOCK_X, CGX_BLOCK_Y, 1);
+    const size_t smem = sizeof(BwdSmem);
+    if (g_render_variant) {
+        e = cudaFuncSetAttribute(render_bwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) { set_cuda_error(e); return CGX_ECUDA; }
+        render_bwd_kernel<true><<<grid, block, smem, st>>>(
+            (const uint2*)ranges, point_list, W, H, focal_x, focal_y, bg, (const Record*)records, all_map_pixels,
+            final_T, n_contrib, compute_locally, dL_dcolor, dL_dout_all_map, dL_dout_plane_depth, render_geo != 0, out);
+    } else {
+        e = cudaFuncSetAttribute(render_bwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) { set_cuda_error(e); return CGX_ECUDA; }
+        render_bwd_kernel<false><<<grid, block, smem, st>>>(
+            (const uint2*)ranges, point_list, W, H, focal_x, focal_y, bg, (const Record*)records, all_map_pixels,
+            final_T, n_contrib, compute_locally, dL_dcolor, dL_dout_all_map, dL_dout_plane_depth, render_geo != 0, out);
+    }
+    return check_launch();
+}

@@ -1,0 +1,208 @@
+/*
+ * cgx_raster — C ABI of the B200 (sm_100a) Gaussian rasterizer hot path.
+ *
+ * Drop-in boundary for the CityGS-X `diff_gaussian_rasterization._C` extension
+ * (reference project paths: RAST = submodule_cityx/diff-gaussian-rasterization).
+ * Every entry point takes plain device pointers and sizes, launches on the
+ * given CUDA stream (passed as void*, i.e. a cudaStream_t), returns an int
+ * status (0 = ok) and never allocates, frees or retains memory: the caller
+ * owns inputs, outputs and workspaces.  Unless stated otherwise all pointers
+ * are DEVICE pointers, floats are fp32, matrices are 16 floats in the
+ * reference's row-vector convention (translation in elements 12..14), and
+ * per-Gaussian arrays are row-major AoS exactly as the reference's tensors.
+ *
+ * Calls are asynchronous with respect to the host unless the comment says
+ * "host-synchronous".
+ */
+#ifndef CGX_RASTER_H
+#define CGX_RASTER_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* status codes */
+#define CGX_OK 0
+#define CGX_EINVAL 22      /* bad shape / null pointer / misaligned pointer            */
+#define CGX_ENOMEM 12      /* caller-provided workspace or capacity too small           */
+#define CGX_ETIMEDOUT 110  /* a bounded device-side wait gave up                        */
+#define CGX_ECUDA 5        /* CUDA runtime reported an error (see cgx_last_cuda_error)  */
+
+const char* cgx_strerror(int status);
+/* Text of the last CUDA runtime error seen by this library on this thread. */
+const char* cgx_last_cuda_error(void);
+/* Library version string. */
+const char* cgx_version(void);
+
+/* GetBlockXY (RAST/rasterize_points.cu:858-861): tile size and 1-D block size. */
+int cgx_block_xy(int* block_x, int* block_y, int* one_dim_block);
+
+/* getHigherMsb (RAST/cuda_rasterizer/rasterizer_impl.cu:39-54). */
+uint32_t cgx_higher_msb(uint32_t n);
+
+/* ------------------------------------------------------------------ per-Gaussian stages */
+
+/* markVisible -> checkFrustum (RAST/rasterize_points.cu:39-58,
+ * RAST/cuda_rasterizer/rasterizer_impl.cu:58-70,147-159): present[i] = view-space z > 0.
+ * present: P bytes (bool). */
+int cgx_mark_visible(int P, const float* means3D, const float* viewmatrix, uint8_t* present, void* stream);
+
+/* PreprocessGaussiansCUDA -> preprocessForward -> preprocessCUDA
+ * (RAST/rasterize_points.cu:63-143, RAST/cuda_rasterizer/rasterizer_impl.cu:336-425,
+ * RAST/cuda_rasterizer/forward.cu:156-259).  Writes EVERY element of every output
+ * (zeros where the reference leaves its zero-filled allocation untouched), so outputs
+ * may be uninitialised memory.
+ *   means3D (P,3) scales (P,3) rotations (P,4) [r,x,y,z, not normalised] opacities (P,1)
+ *   -> means2D (P,2) depths (P) radii int32 (P) cov3D (P,6) conic_opacity (P,4)          */
+int cgx_preprocess_fwd(int P, const float* means3D, const float* scales, float scale_modifier,
+                       const float* rotations, const float* opacities, const float* viewmatrix,
+                       const float* projmatrix, int W, int H, float tanfovx, float tanfovy,
+                       float* means2D, float* depths, int32_t* radii, float* cov3D, float* conic_opacity,
+                       void* stream);
+
+/* RasterizeGaussiansfilterCUDA -> visible_filter -> filter_preprocessCUDA
+ * (RAST/rasterize_points.cu:865-930, RAST/cuda_rasterizer/forward.cu:545-620): radii only. */
+int cgx_filter_preprocess(int P, const float* means3D, const float* scales, float scale_modifier,
+                          const float* rotations, const float* viewmatrix, const float* projmatrix,
+                          int W, int H, float tanfovx, float tanfovy, int32_t* radii, void* stream);
+
+/* Optional SH stage, computeColorFromSH (RAST/cuda_rasterizer/forward.cu:21-72; compiled out of the
+ * reference's kernel, kept here as a switchable stage).  sh (P,M,3), campos 3 floats (device),
+ * -> rgb (P,3), clamped (P,3) bytes. */
+int cgx_sh_to_rgb(int P, int degree, int M, const float* means3D, const float* campos, const float* sh,
+                  float* rgb, uint8_t* clamped, void* stream);
+
+/* PreprocessGaussiansBackwardCUDA -> preprocessBackward -> computeCov2DCUDA + preprocessCUDA(bwd)
+ * (RAST/rasterize_points.cu:146-234, RAST/cuda_rasterizer/backward.cu:69-321,578-641), one fused
+ * kernel, including the (P,4) -> (P,2,2)+(P,1) cotangent repack of rasterize_points.cu:181-194.
+ *   dL_dmeans2D (P,2), dL_dconic_opacity (P,4)
+ *   -> dL_dmeans3D (P,3) dL_dscales (P,3) dL_drotations (P,4) dL_dopacity (P,1); every element written. */
+int cgx_preprocess_bwd(int P, const float* means3D, const float* scales, float scale_modifier,
+                       const float* rotations, const int32_t* radii, const float* viewmatrix,
+                       const float* projmatrix, int W, int H, float tanfovx, float tanfovy,
+                       const float* dL_dmeans2D, const float* dL_dconic_opacity,
+                       float* dL_dmeans3D, float* dL_dscales, float* dL_drotations, float* dL_dopacity,
+                       void* stream);
+
+/* ------------------------------------------------------------------ distribution */
+
+/* GetLocal2jIdsBoolCUDA -> getTouchedIdsBool (RAST/rasterize_points.cu:445-524).
+ * tile_bounds: int32 (ws+1) linear tile ids (= division_pos * TILE_X). mask: (P, ws) bytes, every
+ * element written. */
+int cgx_local2j_mask(int P, int H, int W, int ws, const float* means2D, const int32_t* radii,
+                     const int32_t* tile_bounds, int avoid_pixel_all2all, uint8_t* mask, void* stream);
+
+/* Fused replacement of the caller loop around get_local2j_ids_bool (mask -> nonzero -> index-gather
+ * -> concat; gaussian_renderer/workload_division.py:721-744, gaussian_renderer/__init__.py:612-666,
+ * 709-716): one pass that counts, for each destination column j, the rows whose tile span touches
+ * j's band, then packs those rows (ascending local index, as nonzero() yields them) as
+ * 21-float records [means2D 2 | rgb 3 | conic_opacity 4 | means3D 3 | scales 3 | rotations 4 |
+ * radius-as-float 1 | depth 1] into a send buffer at row offset send_row_offset[j].
+ *   cgx_local2j_count : counts (ws) int32 written (device).
+ *   cgx_local2j_pack  : needs counts' exclusive layout from the caller (row offsets per column). */
+int cgx_local2j_count(int P, int H, int W, int ws, const float* means2D, const int32_t* radii,
+                      const int32_t* tile_bounds, int avoid_pixel_all2all, int32_t* counts,
+                      void* workspace, size_t workspace_bytes, void* stream);
+size_t cgx_local2j_workspace_bytes(int P, int ws);
+int cgx_local2j_pack(int P, int H, int W, int ws, const float* means2D, const float* rgb,
+                     const float* conic_opacity, const float* means3D, const float* scales,
+                     const float* rotations, const int32_t* radii, const float* depths,
+                     const int32_t* tile_bounds, int avoid_pixel_all2all,
+                     const int64_t* send_row_offset /* host, ws entries */, float* send_buffer,
+                     int32_t* send_index /* optional: source row of every packed row */,
+                     void* workspace, size_t workspace_bytes, void* stream);
+/* Reverse of the pack for the backward exchange: grad_rows (n,19) are added into per-source-row
+ * gradient arrays through send_index (rows can repeat across destinations). */
+int cgx_unpack_grad_add(int64_t n_rows, const float* grad_rows, const int32_t* send_index,
+                        float* d_means2D, float* d_rgb, float* d_conic_opacity, float* d_means3D,
+                        float* d_scales, float* d_rotations, void* stream);
+
+/* ------------------------------------------------------------------ binning */
+
+/* updateTileTouched + InclusiveSum (RAST/cuda_rasterizer/rasterizer_impl.cu:264-288,648).
+ * compute_locally: T bytes (bool, row-major Ty x Tx).  Writes tiles_touched u32 (P), the per-block
+ * partial sums into workspace, and the total number of (tile, Gaussian) pairs into *num_rendered
+ * (device, 1 x u32).  The inclusive offsets themselves are produced by cgx_emit_keys. */
+size_t cgx_bin_workspace_bytes(int P);
+int cgx_bin_count_scan(int P, int W, int H, const int32_t* radii, const float* means2D,
+                       const uint8_t* compute_locally, uint32_t* tiles_touched, uint32_t* num_rendered,
+                       void* workspace, size_t workspace_bytes, void* stream);
+
+/* duplicateWithKeys (RAST/cuda_rasterizer/rasterizer_impl.cu:74-117): writes point_offsets u32 (P)
+ * (inclusive sum, as the reference's GeometryState::point_offsets), keys u64 (R) =
+ * (tile << 32) | bits(depth), values u32 (R) = Gaussian index, emission order y-major then x over the
+ * locally computed tiles of the Gaussian's rectangle.  capacity = number of pairs keys/values can hold
+ * (normally the total written by cgx_bin_count_scan); pairs beyond it are dropped, never written.
+ * workspace: the buffer cgx_bin_count_scan filled for the same inputs. */
+int cgx_emit_keys(int P, int W, int H, const int32_t* radii, const float* means2D, const float* depths,
+                  const uint32_t* tiles_touched, const uint8_t* compute_locally,
+                  uint32_t* point_offsets, uint64_t* keys, uint32_t* values, int64_t capacity,
+                  const void* workspace, void* stream);
+
+/* cub::DeviceRadixSort::SortPairs call site (RAST/cuda_rasterizer/rasterizer_impl.cu:679-684):
+ * stable ascending sort of (key, value) pairs on key bits [0, end_bit).  keys_in/values_in are
+ * clobbered (used as ping-pong buffers); the result is in keys_out/values_out. */
+size_t cgx_sort_workspace_bytes(int64_t n);
+int cgx_sort_pairs(int64_t n, int end_bit, uint64_t* keys_in, uint32_t* values_in, uint64_t* keys_out,
+                   uint32_t* values_out, void* workspace, size_t workspace_bytes, void* stream);
+
+/* cudaMemset + identifyTileRanges (RAST/cuda_rasterizer/rasterizer_impl.cu:122-144,687-695):
+ * ranges uint2 (T): [start, end) into the sorted list; empty tiles get (0,0). */
+int cgx_tile_ranges(int64_t n, int T, const uint64_t* keys_sorted, uint32_t* ranges, void* stream);
+
+/* ------------------------------------------------------------------ blending */
+
+/* RenderGaussiansCUDA -> renderForward -> renderCUDA (RAST/rasterize_points.cu:276-364,
+ * RAST/cuda_rasterizer/rasterizer_impl.cu:699-725, RAST/cuda_rasterizer/forward.cu:264-486).
+ * Writes every pixel of every image output (zeros in tiles that are not computed locally) and zero-fills
+ * out_observe before accumulating.  records: scratch for P 64-byte packed records (see
+ * cgx_render_records_bytes), kept by the caller for the backward.
+ *   -> final_T f32 (H*W), n_contrib u32 (H*W), n_contrib2loss u32 (H*W), out_color (3,H,W),
+ *      out_observe int32 (P), out_all_map (5,H,W), out_plane_depth (1,H,W),
+ *      and the per-tile statistics of cgx_tile_stats (n_render, n_consider, n_contrib: int32 (T)),
+ *      reduced in the kernel's epilogue.                                                         */
+size_t cgx_render_records_bytes(int P);
+int cgx_render_fwd(int P, int W, int H, float tanfovx, float tanfovy, const uint32_t* ranges,
+                   const uint32_t* point_list, const float* means2D, const float* rgb, const float* all_map,
+                   const float* conic_opacity, const uint8_t* compute_locally, const float* bg, int render_geo,
+                   void* records, float* final_T, uint32_t* n_contrib, uint32_t* n_contrib2loss,
+                   float* out_color, int32_t* out_observe, float* out_all_map, float* out_plane_depth,
+                   int32_t* n_render, int32_t* n_consider, int32_t* n_contrib_tile, void* stream);
+
+/* get_n_render + reduce_data_per_block x2 (RAST/cuda_rasterizer/rasterizer_impl.cu:219-262,730-752):
+ * per-tile int32 (T) outputs; every element written. */
+int cgx_tile_stats(int W, int H, const uint32_t* ranges, const uint32_t* n_contrib_px,
+                   const uint32_t* n_contrib2loss_px, const uint8_t* compute_locally,
+                   int32_t* n_render, int32_t* n_consider, int32_t* n_contrib, void* stream);
+
+/* RenderGaussiansBackwardCUDA -> renderBackward -> renderCUDA(bwd) (RAST/rasterize_points.cu:366-441,
+ * RAST/cuda_rasterizer/rasterizer_impl.cu:850-932, RAST/cuda_rasterizer/backward.cu:324-567,643-696),
+ * including the (P,2,2)+(P,1) -> (P,4) repack of rasterize_points.cu:428-436.  Zero-fills and then
+ * accumulates:  dL_dmeans2D (P,2), dL_dmeans2D_abs (P,3), dL_dconic_opacity (P,4), dL_drgb (P,3),
+ * dL_dall_map (P,5).  records: the buffer cgx_render_fwd filled for the same inputs. */
+int cgx_render_bwd(int P, int W, int H, float tanfovx, float tanfovy, const uint32_t* ranges,
+                   const uint32_t* point_list, const float* bg, const void* records,
+                   const float* all_map_pixels, const float* final_T, const uint32_t* n_contrib,
+                   const uint8_t* compute_locally, const float* dL_dcolor, const float* dL_dout_all_map,
+                   const float* dL_dout_plane_depth, int render_geo,
+                   float* dL_dmeans2D, float* dL_dmeans2D_abs, float* dL_dconic_opacity, float* dL_drgb,
+                   float* dL_dall_map, void* stream);
+
+/* ------------------------------------------------------------------ diagnostics */
+
+/* Host-synchronous.  Waits for `stream`, reads and clears the device status word that kernels set when a
+ * bounded wait gives up (0 = ok, CGX_ETIMEDOUT otherwise).  Replaces the reference's debug-mode
+ * synchronise-and-throw (RAST/cuda_rasterizer/auxiliary.h:220-227); nothing ever traps. */
+int cgx_device_status(int* status_host, void* stream);
+
+/* 1 (default): blending kernels cull each batch per warp before blending; 0: blend every listed Gaussian.
+ * Results are identical; the switch exists for A/B timing and tests. */
+int cgx_set_render_variant(int cull);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CGX_RASTER_H */

@@ -1,0 +1,362 @@
+"""GPU parity: the CUDA path (through the C ABI / drop-in package) against
+
+  (1) the reference's own CUDA extension on identical inputs, when it is available (built by
+      oracle/build_ref.py): radii, sorted keys, point list, tile ranges, n_contrib bit-exact; forward images
+      within 1e-5 max-abs; gradients within 1e-3 relative L2;
+  (2) the CPU oracle: integer stages exactly (each stage fed with the GPU's own inputs to it), float stages
+      within tolerance.
+"""
+import pytest
+import torch
+
+import util
+from util import cam_dict, cotangents, cuda_args, decode_binning, decode_image, make_case, rel_l2, settings_for
+
+pytestmark = pytest.mark.gpu
+
+FWD_TOL = 1e-5      # max-abs on forward images (north-star tolerance)
+GRAD_TOL = 1e-3     # relative L2 on every gradient tensor
+
+CASES = [
+    dict(cfg=1, n=20000, res=(320, 180)),
+    dict(cfg=1, n=200000, res=(640, 360)),
+    dict(cfg=0, n=50000, res=(256, 144)),
+    dict(cfg=1, n=30000, res=(333, 211), big_scales=True),     # not multiples of 16, many tiles per splat
+    dict(cfg=2, n=300000, res=(800, 600)),
+]
+
+
+def to_dev(g, dev):
+    return {k: v.to(dev) for k, v in g.items()}
+
+
+def run_ours(g, cam, dev, local=None, cot=None, render_geo=True, bg=None, debug=True):
+    """Full path through the drop-in package. Returns dict of CPU tensors."""
+    from diff_gaussian_rasterization import GaussianRasterizer, _C
+
+    rs = settings_for(cam, dev, bg=bg, render_geo=render_geo, debug=debug)
+    rast = GaussianRasterizer(rs)
+    gd = to_dev(g, dev)
+    leaves = {}
+    for k in ("means3D", "scales", "rotations", "opacities", "rgb", "all_map"):
+        leaves[k] = gd[k].clone().requires_grad_(cot is not None)
+    args = cuda_args()
+    means2D, rgb0, conic_opacity, radii, depths = rast.preprocess_gaussians(
+        leaves["means3D"], leaves["scales"], leaves["rotations"], gd["sh"], leaves["opacities"], args)
+    if cot is not None:
+        means2D.retain_grad()
+    TX, TY = (cam.W + 15) // 16, (cam.H + 15) // 16
+    if local is None:
+        local = torch.ones(TY, TX, dtype=torch.bool)
+    local_d = local.to(dev)
+    means2D_abs = torch.zeros(means2D.shape[0], 3, device=dev, requires_grad=cot is not None)
+    # raw call as well, to look at the scratch buffers
+    raw = _C.render_gaussians(rs.bg, cam.H, cam.W, means2D.detach(), depths, radii, conic_opacity.detach(),
+                              leaves["rgb"].detach(), local_d, rs.viewmatrix, rs.campos, cam.tanfovx, cam.tanfovy,
+                              leaves["all_map"].detach(), render_geo, True, args)
+    R = raw[0]
+    bn = decode_binning(raw[9], R) if R else None
+    im = decode_image(raw[10], cam.W * cam.H, TX * TY) if means2D.shape[0] else None
+    color, n_render, n_consider, n_contrib, observe, out_all_map, plane_depth = rast.render_gaussians(
+        means2D, means2D_abs, conic_opacity, leaves["rgb"], leaves["all_map"], depths, radii, local_d, None, args)
+    out = dict(means2D=means2D, depths=depths, radii=radii, conic_opacity=conic_opacity, R=R, color=color,
+               n_render=n_render, n_consider=n_consider, n_contrib=n_contrib, out_observe=observe,
+               out_all_map=out_all_map, out_plane_depth=plane_depth)
+    if bn is not None:
+        out.update(keys=bn["point_list_keys"], point_list=bn["point_list"], keys_unsorted=None)
+    if im is not None:
+        out.update(ranges=im["ranges"].view(-1, 2), final_T=im["accum_alpha"], n_contrib_px=im["n_contrib"],
+                   n_contrib2loss_px=im["n_contrib2loss"])
+    if cot is not None:
+        loss = ((color * cot["color"].to(dev)).sum() + (out_all_map * cot["all_map"].to(dev)).sum()
+                + (plane_depth * cot["plane_depth"].to(dev)).sum())
+        loss.backward()
+        out.update(dL_dmeans3D=leaves["means3D"].grad, dL_dscales=leaves["scales"].grad,
+                   dL_drotations=leaves["rotations"].grad, dL_dopacity=leaves["opacities"].grad,
+                   dL_drgb=leaves["rgb"].grad, dL_dall_map=leaves["all_map"].grad, dL_dmeans2D=means2D.grad,
+                   dL_dmeans2D_abs=means2D_abs.grad)
+    torch.cuda.synchronize()
+    return {k: (v.detach().cpu() if isinstance(v, torch.Tensor) else v) for k, v in out.items()}
+
+
+def run_reference(ref, g, cam, dev, local=None, cot=None, render_geo=True, bg=None):
+    """Same path through the reference extension's raw entry points."""
+    gd = to_dev(g, dev)
+    V, Pm, campos = cam.viewmatrix.to(dev), cam.projmatrix.to(dev), cam.campos.to(dev)
+    bgd = (torch.zeros(3) if bg is None else bg).to(dev)
+    args = cuda_args()
+    _, means2D, depths, radii, cov3D, conic_opacity, rgb0, clamped = ref.preprocess_gaussians(
+        gd["means3D"], gd["scales"], gd["rotations"], gd["sh"], gd["opacities"], 1.0, V, Pm, cam.tanfovx, cam.tanfovy,
+        cam.H, cam.W, 3, campos, False, False, args)
+    TX, TY = (cam.W + 15) // 16, (cam.H + 15) // 16
+    if local is None:
+        local = torch.ones(TY, TX, dtype=torch.bool)
+    local_d = local.to(dev)
+    (R, color, n_render, n_consider, n_contrib, observe, out_all_map, plane_depth, geomB, binB, imgB) = \
+        ref.render_gaussians(bgd, cam.H, cam.W, means2D, depths, radii, conic_opacity, gd["rgb"], local_d, V, campos,
+                             cam.tanfovx, cam.tanfovy, gd["all_map"], render_geo, False, args)
+    out = dict(means2D=means2D, depths=depths, radii=radii, conic_opacity=conic_opacity, cov3D=cov3D, R=R,
+               color=color, n_render=n_render, n_consider=n_consider, n_contrib=n_contrib, out_observe=observe,
+               out_all_map=out_all_map, out_plane_depth=plane_depth)
+    if R:
+        bn = decode_binning(binB, R)
+        out.update(keys=bn["point_list_keys"], point_list=bn["point_list"])
+    im = decode_image(imgB, cam.W * cam.H, cam.W * cam.H)
+    out.update(ranges=im["ranges"].view(-1, 2)[: TX * TY], final_T=im["accum_alpha"], n_contrib_px=im["n_contrib"],
+               n_contrib2loss_px=im["n_contrib2loss"])
+    if cot is not None:
+        d_m2, d_abs, d_co, d_rgb, d_map = ref.render_gaussians_backward(
+            bgd, cam.tanfovx, cam.tanfovy, out_all_map, gd["all_map"], R, geomB, binB, imgB, local_d,
+            cot["color"].to(dev), cot["all_map"].to(dev), cot["plane_depth"].to(dev), means2D, conic_opacity,
+            gd["rgb"], render_geo, False, args)
+        d_means, d_scales, d_rot, d_sh, d_op = ref.preprocess_gaussians_backward(
+            radii, cov3D, clamped, gd["means3D"], gd["scales"], gd["rotations"], gd["sh"], 1.0, V, Pm, cam.tanfovx,
+            cam.tanfovy, cam.H, cam.W, 3, campos, d_m2.contiguous(), d_co, torch.zeros_like(gd["rgb"]), R, False, args)
+        out.update(dL_dmeans3D=d_means, dL_dscales=d_scales, dL_drotations=d_rot, dL_dopacity=d_op, dL_drgb=d_rgb,
+                   dL_dall_map=d_map, dL_dmeans2D=d_m2[:, :2], dL_dmeans2D_abs=d_abs)
+    torch.cuda.synchronize()
+    return {k: (v.detach().cpu() if isinstance(v, torch.Tensor) else v) for k, v in out.items()}
+
+
+GRADS = ["dL_dmeans3D", "dL_dscales", "dL_drotations", "dL_dopacity", "dL_drgb", "dL_dall_map", "dL_dmeans2D",
+         "dL_dmeans2D_abs"]
+
+
+def masked_local(x, cam, local):
+    """Zero pixels of tiles that are not computed locally (the reference leaves no defined value contractually,
+    but both sides zero them; compare only local pixels to be safe)."""
+    if local is None:
+        return x
+    m = local.repeat_interleave(16, 0).repeat_interleave(16, 1)[: cam.H, : cam.W]
+    return x * m
+
+
+@pytest.mark.parametrize("case", CASES, ids=lambda c: f"cfg{c['cfg']}-{c['n']}-{c['res'][0]}x{c['res'][1]}")
+def test_against_reference_extension(case, cuda_device, reference_C):
+    if reference_C is None:
+        pytest.skip("reference CUDA extension not built (oracle/_ref)")
+    g, cam = make_case(**case)
+    cot = cotangents(cam)
+    ours = run_ours(g, cam, cuda_device, cot=cot)
+    ref = run_reference(reference_C, g, cam, cuda_device, cot=cot)
+    # --- bit-exact integers and the floats they derive from
+    assert torch.equal(ours["radii"], ref["radii"])
+    assert torch.equal(ours["means2D"], ref["means2D"])
+    assert torch.equal(ours["depths"], ref["depths"])
+    assert torch.equal(ours["conic_opacity"], ref["conic_opacity"])
+    assert ours["R"] == ref["R"] and ours["R"] > 0
+    assert torch.equal(ours["keys"], ref["keys"])
+    assert torch.equal(ours["point_list"], ref["point_list"])
+    assert torch.equal(ours["ranges"], ref["ranges"])
+    assert torch.equal(ours["n_contrib_px"], ref["n_contrib_px"])
+    assert torch.equal(ours["n_contrib2loss_px"], ref["n_contrib2loss_px"])
+    for k in ("n_render", "n_consider", "n_contrib", "out_observe"):
+        assert torch.equal(ours[k], ref[k]), k
+    # --- forward images
+    for k in ("color", "out_all_map", "final_T"):
+        assert (ours[k] - ref[k]).abs().max().item() <= FWD_TOL, k
+    pd_o, pd_r = ours["out_plane_depth"], ref["out_plane_depth"]
+    big = pd_r.abs() > 1e3          # 1/(n.ray) is unbounded at grazing normals: relative there
+    assert ((pd_o - pd_r).abs()[~big]).max().item() <= FWD_TOL * 10
+    if big.any():
+        assert (((pd_o - pd_r).abs() / pd_r.abs())[big]).max().item() <= 1e-5
+    # --- gradients
+    for k in GRADS:
+        assert rel_l2(ours[k], ref[k]) <= GRAD_TOL, (k, rel_l2(ours[k], ref[k]))
+
+
+@pytest.mark.parametrize("case", CASES[:4], ids=lambda c: f"cfg{c['cfg']}-{c['n']}-{c['res'][0]}x{c['res'][1]}")
+def test_against_cpu_oracle(case, cuda_device):
+    from oracle import cpu_raster as O
+
+    g, cam = make_case(**case)
+    cot = cotangents(cam)
+    ours = run_ours(g, cam, cuda_device, cot=cot)
+    cd = cam_dict(cam)
+    # stage 1: preprocess. The CPU does not contract multiply-adds, so integers are compared where the
+    # oracle says the input is not within rounding distance of a boundary.
+    m2, dep, rad, cov3, co, fragile = O.preprocess_fwd(g["means3D"], g["scales"], g["rotations"], g["opacities"],
+                                                       cam.viewmatrix, cam.projmatrix, cam.W, cam.H, cam.tanfovx,
+                                                       cam.tanfovy, want_fragile=True)
+    ok = ~fragile
+    assert fragile.float().mean().item() < 0.02
+    assert torch.equal(ours["radii"][ok], rad[ok])
+    vis = ok & (rad > 0)
+    assert (ours["means2D"][vis] - m2[vis]).abs().max().item() < 2e-3
+    assert rel_l2(ours["conic_opacity"][vis], co[vis]) < 1e-4
+    assert rel_l2(ours["depths"][vis], dep[vis]) < 1e-6
+    # stage 2: binning on the GPU's own preprocess outputs -> exact
+    TX, TY = (cam.W + 15) // 16, (cam.H + 15) // 16
+    local = torch.ones(TY, TX, dtype=torch.bool)
+    b = O.bin_and_sort(ours["means2D"], ours["depths"], ours["radii"], local, cam.W, cam.H)
+    assert b["R"] == ours["R"]
+    assert torch.equal(b["keys"], ours["keys"])
+    assert torch.equal(b["point_list"], ours["point_list"])
+    assert torch.equal(b["ranges"], ours["ranges"])
+    # stage 3: blending on the GPU's own lists
+    f = O.render_fwd(ours["means2D"], ours["conic_opacity"], g["rgb"], g["all_map"], ours["ranges"],
+                     ours["point_list"], local, cd["bg"], cam.W, cam.H, cam.tanfovx, cam.tanfovy)
+    # libm expf and the device expf differ in the last bits: a pixel whose alpha sits on the 1/255 threshold can
+    # flip, so allow a tiny fraction of outlier pixels
+    for k in ("color", "out_all_map"):
+        bad = ((ours[k] - f[k]).abs() > 2e-5).float().mean().item()
+        assert bad < 1e-4, (k, bad)
+    mism = (ours["n_contrib_px"] != f["n_contrib_px"]).float().mean().item()
+    assert mism < 1e-4
+    # stage 4: backward on the GPU's own forward state
+    rb = O.render_bwd(ours["means2D"], ours["conic_opacity"], g["rgb"], g["all_map"], ours["out_all_map"],
+                      ours["final_T"], ours["n_contrib_px"], ours["ranges"], ours["point_list"], local, cd["bg"],
+                      cam.W, cam.H, cam.tanfovx, cam.tanfovy, cot["color"], cot["all_map"], cot["plane_depth"])
+    for k in ("dL_dmeans2D", "dL_dmeans2D_abs", "dL_drgb", "dL_dall_map"):
+        assert rel_l2(ours[k], rb[k]) <= GRAD_TOL, (k, rel_l2(ours[k], rb[k]))
+    pb = O.preprocess_bwd(g["means3D"], g["scales"], g["rotations"], ours["radii"], cov3, cam.viewmatrix,
+                          cam.projmatrix, cam.W, cam.H, cam.tanfovx, cam.tanfovy, ours["dL_dmeans2D"],
+                          rb["dL_dconic_opacity"])
+    for k in ("dL_dmeans3D", "dL_dscales", "dL_drotations", "dL_dopacity"):
+        assert rel_l2(ours[k], pb[k]) <= GRAD_TOL, (k, rel_l2(ours[k], pb[k]))
+
+
+def test_cull_variant_is_identical(cuda_device):
+    """Per-warp culling must not change a single bit of the forward outputs."""
+    from diff_gaussian_rasterization import _lib
+
+    g, cam = make_case(cfg=1, n=100000, res=(640, 360), big_scales=True)
+    l = _lib.lib()
+    try:
+        l.cgx_set_render_variant(1)
+        a = run_ours(g, cam, cuda_device, cot=cotangents(cam))
+        l.cgx_set_render_variant(0)
+        b = run_ours(g, cam, cuda_device, cot=cotangents(cam))
+    finally:
+        l.cgx_set_render_variant(1)
+    for k in ("color", "out_all_map", "out_plane_depth", "final_T", "n_contrib_px", "n_contrib2loss_px",
+              "out_observe", "n_consider", "n_contrib"):
+        assert torch.equal(a[k], b[k]), k
+    for k in GRADS:
+        assert rel_l2(a[k], b[k]) <= 1e-5, k
+
+
+def test_partial_compute_locally(cuda_device, reference_C):
+    """Only a band of tile rows is local: keys only for local tiles, other pixels zero."""
+    from oracle import cpu_raster as O
+
+    g, cam = make_case(cfg=1, n=50000, res=(640, 360))
+    TX, TY = (cam.W + 15) // 16, (cam.H + 15) // 16
+    local = torch.zeros(TY, TX, dtype=torch.bool)
+    local[5:13] = True
+    cot = cotangents(cam)
+    ours = run_ours(g, cam, cuda_device, local=local, cot=cot)
+    b = O.bin_and_sort(ours["means2D"], ours["depths"], ours["radii"], local, cam.W, cam.H)
+    assert b["R"] == ours["R"]
+    assert torch.equal(b["keys"], ours["keys"]) and torch.equal(b["point_list"], ours["point_list"])
+    assert torch.equal(b["ranges"], ours["ranges"])
+    m = local.repeat_interleave(16, 0).repeat_interleave(16, 1)[: cam.H, : cam.W]
+    assert ours["color"][:, ~m].abs().max().item() == 0.0
+    assert ours["out_all_map"][:, ~m].abs().max().item() == 0.0
+    if reference_C is not None:
+        ref = run_reference(reference_C, g, cam, cuda_device, local=local, cot=cot)
+        assert torch.equal(ours["keys"], ref["keys"]) and torch.equal(ours["ranges"], ref["ranges"])
+        assert (ours["color"] - ref["color"]).abs().max().item() <= FWD_TOL
+        for k in GRADS:
+            assert rel_l2(ours[k], ref[k]) <= GRAD_TOL, k
+
+
+@pytest.mark.parametrize("P", [0, 1, 31, 32, 33, 255, 257])
+def test_small_counts(P, cuda_device):
+    from oracle import cpu_raster as O
+
+    g, cam = make_case(cfg=1, n=max(P, 1), res=(64, 48))
+    g = {k: v[:P].contiguous() for k, v in g.items()}
+    # pull everything in front of the camera so tiny P still renders something
+    g["means3D"] = g["means3D"] * 0.05
+    g["scales"] = g["scales"] * 5
+    g["all_map"] = util.S.build_all_map(g["means3D"], g["scales"], g["rotations"], cam)
+    cot = cotangents(cam)
+    ours = run_ours(g, cam, cuda_device, cot=cot if P else None)
+    assert ours["color"].shape == (3, cam.H, cam.W)
+    assert ours["radii"].shape == (P,)
+    if P == 0:
+        assert ours["color"].abs().max().item() == 0
+        return
+    cd = cam_dict(cam)
+    o = O.full_step(dict(g), cd, cot=cot)
+    assert torch.equal(ours["radii"], o["radii"])
+    assert (ours["color"] - o["color"]).abs().max().item() < 1e-4
+    for k in GRADS:
+        if k in o:
+            assert rel_l2(ours[k], o[k]) <= 5e-3, (k, rel_l2(ours[k], o[k]))
+
+
+def test_all_culled_and_background(cuda_device):
+    g, cam = make_case(cfg=1, n=1000, res=(96, 64))
+    g["means3D"][:, :] = torch.tensor([0.0, -200.0, 200.0])     # behind the camera
+    bg = torch.tensor([0.25, 0.5, 0.75])
+    ours = run_ours(g, cam, cuda_device, bg=bg)
+    assert (ours["radii"] == 0).all() and ours["R"] == 0
+    assert torch.allclose(ours["color"], bg[:, None, None].expand(3, cam.H, cam.W))
+    assert (ours["final_T"] == 1).all()
+
+
+def test_filter_and_mark_visible(cuda_device, reference_C):
+    from diff_gaussian_rasterization import GaussianRasterizer
+    from oracle import cpu_raster as O
+
+    g, cam = make_case(cfg=1, n=100000, res=(640, 360))
+    rast = GaussianRasterizer(settings_for(cam, cuda_device))
+    gd = to_dev(g, cuda_device)
+    radii_f = rast.visible_filter(gd["means3D"], gd["scales"], gd["rotations"]).cpu()
+    vis = rast.markVisible(gd["means3D"]).cpu()
+    m2, dep, rad, cov3, co, fragile = O.preprocess_fwd(g["means3D"], g["scales"], g["rotations"], g["opacities"],
+                                                       cam.viewmatrix, cam.projmatrix, cam.W, cam.H, cam.tanfovx,
+                                                       cam.tanfovy, want_fragile=True)
+    assert torch.equal(radii_f[~fragile], rad[~fragile])
+    assert (vis != O.mark_visible(g["means3D"], cam.viewmatrix)).float().mean().item() < 1e-4
+    ours = run_ours(g, cam, cuda_device)
+    assert torch.equal(radii_f, ours["radii"])        # same geometry as the full preprocess, bit for bit
+    if reference_C is not None:
+        V, Pm = cam.viewmatrix.to(cuda_device), cam.projmatrix.to(cuda_device)
+        r_ref = reference_C.rasterize_aussians_filter(gd["means3D"], gd["scales"], gd["rotations"], 1.0,
+                                                      torch.empty(0, device=cuda_device), V, Pm, cam.tanfovx,
+                                                      cam.tanfovy, cam.H, cam.W, False, False).cpu()
+        assert torch.equal(radii_f, r_ref)
+        assert torch.equal(vis, reference_C.mark_visible(gd["means3D"], V, Pm).cpu())
+
+
+def test_sh_stage(cuda_device):
+    import ctypes as C
+
+    from diff_gaussian_rasterization import _lib
+    from oracle import cpu_raster as O
+
+    g, cam = make_case(cfg=1, n=5000, res=(64, 48))
+    dev = cuda_device
+    P = g["means3D"].shape[0]
+    rgb = torch.empty(P, 3, device=dev)
+    clamped = torch.empty(P, 3, dtype=torch.bool, device=dev)
+    m, sh, cp = g["means3D"].to(dev), g["sh"].to(dev), cam.campos.to(dev)
+    for deg in range(4):
+        st = _lib.lib().cgx_sh_to_rgb(P, deg, 16, m.data_ptr(), cp.data_ptr(), sh.data_ptr(), rgb.data_ptr(),
+                                      clamped.data_ptr(), torch.cuda.current_stream().cuda_stream)
+        assert st == 0
+        ref_rgb, ref_cl = O.sh_to_rgb(g["means3D"], cam.campos, g["sh"], deg)
+        assert (rgb.cpu() - ref_rgb).abs().max().item() < 1e-5
+        assert (clamped.cpu() != ref_cl).float().mean().item() < 1e-3
+
+
+def test_error_codes(cuda_device):
+    from diff_gaussian_rasterization import GaussianRasterizer, _lib
+
+    g, cam = make_case(cfg=1, n=100, res=(64, 48))
+    rast = GaussianRasterizer(settings_for(cam, cuda_device))
+    gd = to_dev(g, cuda_device)
+    with pytest.raises(RuntimeError):
+        rast.preprocess_gaussians(gd["means3D"][:, :2], gd["scales"], gd["rotations"], gd["sh"], gd["opacities"],
+                                  cuda_args())
+    with pytest.raises(RuntimeError):      # CPU tensors are refused, never silently computed on the host
+        rast.preprocess_gaussians(g["means3D"], g["scales"], g["rotations"], g["sh"], g["opacities"], cuda_args())
+    l = _lib.lib()
+    assert l.cgx_preprocess_fwd(-1, *([None] * 2), 1.0, *([None] * 4), 64, 48, 0.5, 0.5, *([None] * 6)) == _lib.CGX_EINVAL
+    assert l.cgx_sort_pairs(10, 40, None, None, None, None, None, 0, None) == _lib.CGX_EINVAL
+    from diff_gaussian_rasterization import _C
+    with pytest.raises(RuntimeError, match="deprecated"):
+        _C.get_distribution_strategy(48, 64, None, None, False, {})
