@@ -1,0 +1,297 @@
+#!/usr/bin/env python
+"""Benchmark of the rasterizer hot path: fwd+bwd Mpix/s on synthetic aerial-city workloads.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload cfg2] [--impl ours|reference]
+
+One "step" = one data-parallel training step of the hot path over a batch of cameras: for every camera
+preprocess_gaussians -> (Gaussian all-to-all when N > 1) -> render_gaussians -> backward of both, through
+the drop-in `diff_gaussian_rasterization` API.  Default workload: 6M Gaussians, 8 cameras 1600x1200
+(the configuration the headline metric is quoted on); total work is fixed as N grows ("strong" scaling).
+
+Prints ONE JSON line (rank 0).  `value` = whole-job Mpix/s with inputs resident in HBM; `e2e` = the same
+step with the step's host inputs copied from pinned memory and its result read back inside the timed region.
+`--impl reference` times the CPU oracle (the reference has no CPU implementation of its own; its rasterizer is
+CUDA-only) on the host cores for a bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+for p in (ROOT, ROOT / "citygs-x_b200"):
+    if str(p) not in sys.path:
+        sys.path.insert(0, str(p))
+
+import torch  # noqa: E402
+
+
+# ----------------------------------------------------------------------------- workloads
+WORKLOADS = {
+    # name: (cfg id, description)
+    "cfg1": (1, "1M Gaussians, 1 camera 1920x1080 (single-GPU rasterizer fwd+bwd)"),
+    "cfg2": (2, "6M Gaussians, 8 cameras 1600x1200 on a ring (data-parallel step)"),
+    "cfg3": (3, "20M clustered Gaussians, 16 cameras 3840x2160 (load-imbalance stress)"),
+}
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS))
+    ap.add_argument("--gaussians", type=int, default=None, help="override the Gaussian count (scaling sweep)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--cpu-sample-gaussians", type=int, default=None)
+    return ap.parse_args()
+
+
+# ----------------------------------------------------------------------------- clocks
+class ClockSampler:
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index=0):
+        self.proc, self.index = None, index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.strip().splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 7:
+                continue
+            try:
+                sm.append(float(f[0]))
+                mx = float(f[1])
+            except ValueError:
+                continue
+            for n, v in zip(names, f[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# ----------------------------------------------------------------------------- reference / CPU arm
+def cpu_step_sample(cfg, n_gauss, cam_idx=0):
+    """One camera of the workload through the CPU oracle (fwd+bwd). Returns (seconds, Mpix, sample text)."""
+    from cgx import synthetic as S
+    from oracle import cpu_raster as O
+
+    g, cams = S.config(cfg, n_gaussians=n_gauss)
+    cam = cams[cam_idx]
+    g["rgb"] = S.colours_for(g, cam)
+    g["all_map"] = S.build_all_map(g["means3D"], g["scales"], g["rotations"], cam)
+    gen = torch.Generator().manual_seed(99)
+    cot = dict(color=torch.randn(3, cam.H, cam.W, generator=gen), all_map=torch.randn(5, cam.H, cam.W, generator=gen),
+               plane_depth=torch.randn(1, cam.H, cam.W, generator=gen))
+    cd = dict(W=cam.W, H=cam.H, tanfovx=cam.tanfovx, tanfovy=cam.tanfovy, viewmatrix=cam.viewmatrix,
+              projmatrix=cam.projmatrix, bg=torch.zeros(3))
+    O.lib()
+    t0 = time.perf_counter()
+    O.full_step(g, cd, cot=cot)
+    dt = time.perf_counter() - t0
+    P = g["means3D"].shape[0]
+    return dt, cam.W * cam.H / 1e6, f"camera {cam_idx} of {P} Gaussians at {cam.W}x{cam.H}, fwd+bwd, oracle (C, OpenMP)"
+
+
+def run_reference_arm(a):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    cfg = WORKLOADS[a.workload][0]
+    cores = os.cpu_count() or 1
+    os.environ.setdefault("OMP_NUM_THREADS", str(cores))
+    torch.set_num_threads(cores)
+    n = a.gaussians
+    times, mpix, sample = [], 0.0, ""
+    for i in range(a.warmup + a.steps):
+        dt, mpix, sample = cpu_step_sample(cfg, n, cam_idx=0)
+        if i >= a.warmup:
+            times.append(dt)
+    t = statistics.mean(times)
+    val = mpix / t
+    line = {
+        "impl": "reference", "metric": "fwd+bwd Mpix/s", "value": val, "unit": "Mpix/s", "n_gpus": a.gpus,
+        "steps": a.steps, "warmup": a.warmup, "ms_per_step": t * 1e3, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": a.workload, "description": WORKLOADS[a.workload][1],
+                   "note": "the reference rasterizer is CUDA-only; this arm times the CPU oracle port"},
+        "cpu_baseline": {"value": val, "unit": "Mpix/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": "Mpix/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ----------------------------------------------------------------------------- our arm
+ALGO_BYTES = {
+    # algorithmic bytes per launch (API-boundary tensors touched once)
+    "cgx_preprocess_fwd": lambda i: 115 * i["P"],
+    "cgx_preprocess_bwd": lambda i: 148 * i["P"],
+    "cgx_bin_count_scan": lambda i: 16 * i["P"],
+    "cgx_emit_keys": lambda i: 20 * i["P"] + 12 * i["R"],
+    "cgx_sort_pairs": lambda i: i["R"] * (8 + 24 * ((i["bits"] + 7) // 8)),
+    "cgx_tile_ranges": lambda i: 8 * i["R"] + 8 * i["T"],
+    "cgx_render_fwd": lambda i: 60 * i["R"] + 48 * i["HW"],
+    "cgx_render_bwd": lambda i: 60 * i["R"] + 60 * i["HW"] + 76 * i["P"],
+}
+
+
+def main():
+    a = parse_args()
+    if a.impl == "reference":
+        run_reference_arm(a)
+        return
+
+    from cgx import synthetic as S
+    from cgx import runtime as RT
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the rasterizer has no CPU path")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+    assert world == a.gpus or world == 1, "launch with torchrun --nproc-per-node N for --gpus N"
+
+    cfg = WORKLOADS[a.workload][0]
+    g, cams = S.config(cfg, n_gaussians=a.gaussians)
+    step = RT.TrainingStep(g, cams, dev, rank=rank, world_size=world)
+    mpix = sum(c.W * c.H for c in cams) / 1e6
+    n_scene = g["means3D"].shape[0]
+
+    from diff_gaussian_rasterization import _C, _lib
+    lib = _lib.lib()
+
+    def barrier():
+        if world > 1:
+            torch.distributed.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        """K steps bracketed by barrier+sync; device time by CUDA events; max over ranks."""
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        barrier()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    # ---- device-resident measurement
+    for _ in range(max(a.warmup, 3)):
+        step.run()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    launches0 = lib.cgx_launch_count()
+    _C.PROFILE = []
+    ms_total = timed(step.run, a.steps)
+    prof, _C.PROFILE = _C.PROFILE, None
+    launches = (lib.cgx_launch_count() - launches0) // a.steps
+    clocks = sampler.stop() if rank == 0 else None
+    ms_step = ms_total / a.steps
+
+    # per-stage device time (events recorded on the launching stream during the timed region)
+    stages = {}
+    for name, e0, e1, info in prof:
+        s = stages.setdefault(name, {"ms": 0.0, "launches": 0, "bytes": 0.0})
+        s["ms"] += e0.elapsed_time(e1)
+        s["launches"] += 1
+        if info is not None and name in ALGO_BYTES:
+            s["bytes"] += ALGO_BYTES[name](info)
+    peaks_path = ROOT / "MEASURED_PEAKS.json"
+    if peaks_path.exists():
+        peak, peak_src = json.loads(peaks_path.read_text())["hbm_gbs"], "measured"
+    else:
+        peak, peak_src = 6650.0, "fallback"
+    stage_out = {}
+    for name, s in stages.items():
+        gbs = s["bytes"] / (s["ms"] * 1e-3) / 1e9 if s["ms"] > 0 and s["bytes"] else None
+        stage_out[name] = {"ms_per_step": s["ms"] / a.steps, "launches_per_step": s["launches"] / a.steps,
+                           "algo_gbs": gbs, "frac_of_hbm_peak": gbs / peak if gbs else None}
+    top = max(stages, key=lambda k: stages[k]["ms"]) if stages else None
+    roofline = None
+    if top:
+        s = stages[top]
+        ach = s["bytes"] / (s["ms"] * 1e-3) / 1e9
+        roofline = {"kernel": top, "bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
+                    "traffic": None, "peak_source": peak_src, "avg_launch_ms": s["ms"] / s["launches"],
+                    "note": "blending is FP32-pipe bound; HBM fraction reported for completeness"}
+
+    # ---- end-to-end: host inputs copied in, result read back, every step
+    e2e = None
+    if not a.no_e2e:
+        for _ in range(2):
+            step.run_e2e()
+        ms_e2e = timed(step.run_e2e, a.steps) / a.steps
+        e2e = {"value": mpix / (ms_e2e * 1e-3), "unit": "Mpix/s", "ms_per_step": ms_e2e,
+               "h2d_bytes_per_step": step.h2d_bytes, "d2h_bytes_per_step": step.d2h_bytes}
+
+    # ---- CPU baseline (rank 0, N=1 only): bounded sample
+    cpu = None
+    if rank == 0 and world == 1 and not a.no_cpu_baseline:
+        cores = os.cpu_count() or 1
+        os.environ.setdefault("OMP_NUM_THREADS", str(cores))
+        dt, mp, sample = cpu_step_sample(cfg, a.cpu_sample_gaussians or a.gaussians, cam_idx=0)
+        cpu = {"value": mp / dt, "unit": "Mpix/s", "cores": cores, "kind": "port", "sample": sample,
+               "seconds": dt}
+
+    if rank == 0:
+        line = {
+            "metric": "fwd+bwd Mpix/s", "value": mpix / (ms_step * 1e-3), "unit": "Mpix/s", "n_gpus": world,
+            "steps": a.steps, "warmup": max(a.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": a.workload, "description": WORKLOADS[a.workload][1], "gaussians": n_scene,
+                       "cameras": len(cams), "resolution": f"{cams[0].W}x{cams[0].H}",
+                       "l2": "inputs larger than L2 (per-step working set of several GB)",
+                       "parallelism": f"gaussian-shard x tile-row split, ws={world}"},
+            "gaussian_views_per_s": n_scene * len(cams) / (ms_step * 1e-3),
+            "roofline": roofline, "stages": stage_out, "cpu_baseline": cpu, "e2e": e2e,
+            "gpu_launches": int(launches), "clocks": clocks, "exchange": step.exchange_stats(),
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        torch.distributed.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

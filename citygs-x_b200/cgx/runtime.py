@@ -1,0 +1,204 @@
+"""One data-parallel step of the hot path, as the reference's training loop drives it
+(train_internal.py:166-265; gaussian_renderer/__init__.py:903-1308 and :1325-1572):
+
+    per camera: preprocess_gaussians on the local Gaussian shard
+    (world_size > 1) all-to-all of the screen-space records to the ranks that own the touched tile rows
+    per (camera, local row band): render_gaussians
+    backward of everything (render bwd -> reverse all-to-all -> preprocess bwd)
+
+This module owns no arithmetic: it allocates tensors, calls the drop-in `diff_gaussian_rasterization` API and
+`cgx.exchange`, and is what bench.py and the smoke check time.  Upstream gradients are fixed N(0,1) images.
+"""
+from __future__ import annotations
+
+import torch
+
+from diff_gaussian_rasterization import GaussianRasterizationSettings, GaussianRasterizer
+
+from . import synthetic as S
+
+
+def make_cuda_args(rank=0, world_size=1, iteration=1):
+    """The dict of strings the reference passes down to its C++ ops (gaussian_renderer/__init__.py:523-537)."""
+    return {"mode": "train", "world_size": str(world_size), "global_rank": str(rank), "local_rank": str(rank),
+            "mp_world_size": str(world_size), "mp_rank": str(rank), "log_folder": "/tmp", "log_interval": "250",
+            "iteration": str(iteration), "zhx_debug": "False", "zhx_time": "False", "dist_global_strategy": "",
+            "avoid_pixel_all2all": False, "stats_collector": {}}
+
+
+class TrainingStep:
+    def __init__(self, g, cams, device, rank=0, world_size=1, seed=4242):
+        self.dev, self.rank, self.ws = device, rank, world_size
+        self.cams = cams
+        # Gaussians are stored round-robin over ranks, like the reference's anchors (scene/gaussian_model.py:476-479)
+        sel = slice(rank, None, world_size)
+        self.host = {k: g[k][sel].contiguous().pin_memory() for k in ("means3D", "scales", "rotations", "opacities")}
+        self.params = {k: v.to(device).requires_grad_(True) for k, v in self.host.items()}
+        sh = g["sh"][sel].contiguous().to(device)
+        self.sh_dummy = torch.empty(0, device=device)
+        self.n_local = self.params["means3D"].shape[0]
+        gen = torch.Generator().manual_seed(seed)
+        self.settings, self.rgb, self.all_map, self.cot_host, self.cot = [], [], [], [], []
+        for cam in cams:
+            self.settings.append(GaussianRasterizationSettings(
+                image_height=cam.H, image_width=cam.W, tanfovx=cam.tanfovx, tanfovy=cam.tanfovy,
+                bg=torch.zeros(3, device=device), scale_modifier=1.0, viewmatrix=cam.viewmatrix.to(device),
+                projmatrix=cam.projmatrix.to(device), sh_degree=3, campos=cam.campos.to(device), prefiltered=False,
+                render_geo=True, debug=False))
+            with torch.no_grad():
+                self.rgb.append(self._colours(sh, cam))
+            ch = [torch.randn(3, cam.H, cam.W, generator=gen), torch.randn(5, cam.H, cam.W, generator=gen),
+                  torch.randn(1, cam.H, cam.W, generator=gen)]
+            self.cot_host.append([c.pin_memory() for c in ch])
+            self.cot.append([c.to(device) for c in ch])
+        del sh
+        self.grad_host = {k: torch.empty_like(v).pin_memory() for k, v in self.host.items()}
+        self.h2d_bytes = sum(v.numel() * 4 for v in self.host.values()) + \
+            sum(c.numel() * 4 for cs in self.cot_host for c in cs)
+        self.d2h_bytes = sum(v.numel() * 4 for v in self.grad_host.values())
+        self.iteration = 0
+        self._exchange = {"bytes_sent_fwd": 0, "bytes_sent_bwd": 0, "ms": 0.0}
+        self.last = None
+        self.history = None
+        if world_size > 1:
+            from . import workload_division as WD
+
+            self.ctx = WD.DivisionContext(image_height=cams[0].H, image_width=cams[0].W, rank=rank,
+                                          world_size=world_size, bsz=len(cams), device=device)
+            self.history = WD.DivisionStrategyHistoryFinal(cams, world_size, rank, ctx=self.ctx)
+
+    def all_map_for(self, k, means3D, scales, rotations, radii):
+        """Plane descriptors of the rows about to be rendered for camera k (one kernel, no autograd)."""
+        from diff_gaussian_rasterization import _lib
+
+        P = means3D.shape[0]
+        out = torch.empty(P, 5, device=self.dev)
+        if P:
+            rs = self.settings[k]
+            _lib.check(_lib.lib().cgx_all_map_fwd(P, means3D.data_ptr(), scales.data_ptr(), rotations.data_ptr(),
+                                                  radii.data_ptr(), rs.viewmatrix.data_ptr(), rs.campos.data_ptr(),
+                                                  out.data_ptr(), torch.cuda.current_stream().cuda_stream),
+                       "cgx_all_map_fwd")
+        return out
+
+    def _colours(self, sh, cam):
+        """View-dependent colours through the library's SH stage (degree 3), as activated RGB."""
+        import ctypes as C
+
+        from diff_gaussian_rasterization import _lib
+
+        P = sh.shape[0]
+        rgb = torch.empty(P, 3, device=self.dev)
+        clamped = torch.empty(P, 3, dtype=torch.bool, device=self.dev)
+        if P:
+            cp = cam.campos.to(self.dev)
+            _lib.check(_lib.lib().cgx_sh_to_rgb(P, 3, 16, self.params["means3D"].data_ptr(), cp.data_ptr(),
+                                                sh.data_ptr(), rgb.data_ptr(), clamped.data_ptr(),
+                                                torch.cuda.current_stream().cuda_stream), "cgx_sh_to_rgb")
+        return rgb
+
+    # ------------------------------------------------------------------ single-GPU step
+    def _step_single(self):
+        p = self.params
+        args = make_cuda_args(self.rank, self.ws, self.iteration)
+        outs = []
+        for k, cam in enumerate(self.cams):
+            rast = GaussianRasterizer(self.settings[k])
+            means2D, _, conic_opacity, radii, depths = rast.preprocess_gaussians(
+                p["means3D"], p["scales"], p["rotations"], self.sh_dummy, p["opacities"], args)
+            means2D.retain_grad()          # the densifier reads means2D.grad
+            TX, TY = (cam.W + 15) // 16, (cam.H + 15) // 16
+            local = self._all_local(TY, TX)
+            means2D_abs = torch.zeros(self.n_local, 3, device=self.dev, requires_grad=True)
+            all_map = self.all_map_for(k, p["means3D"].detach(), p["scales"].detach(), p["rotations"].detach(), radii)
+            color, n_render, n_consider, n_contrib, observe, out_all_map, plane_depth = rast.render_gaussians(
+                means2D, means2D_abs, conic_opacity, self.rgb[k], all_map, depths, radii, local, None, args)
+            torch.autograd.backward([color, out_all_map, plane_depth], self.cot[k])
+            outs.append((radii, means2D))
+        self.last = outs
+
+    _local_cache = {}
+
+    def _all_local(self, TY, TX):
+        key = (TY, TX, self.dev)
+        if key not in self._local_cache:
+            self._local_cache[key] = torch.ones(TY, TX, dtype=torch.bool, device=self.dev)
+        return self._local_cache[key]
+
+    def run(self):
+        self.iteration += 1
+        for v in self.params.values():
+            v.grad = None
+        if self.ws == 1:
+            self._step_single()
+        else:
+            self._step_distributed()
+        return self.params
+
+    # ------------------------------------------------------------------ multi-GPU step
+    def _step_distributed(self):
+        from . import exchange
+        from . import workload_division as WD
+
+        p = self.params
+        self.ctx.iteration = self.iteration
+        strategies, _ = WD.start_strategy_final(self.cams, self.history, ctx=self.ctx)
+        rasts = [GaussianRasterizer(s) for s in self.settings]
+        args = [make_cuda_args(self.rank, self.ws, self.iteration) for _ in self.cams]
+        screen, keep = [], []
+        for k in range(len(self.cams)):
+            means2D, _, conic_opacity, radii, depths = rasts[k].preprocess_gaussians(
+                p["means3D"], p["scales"], p["rotations"], self.sh_dummy, p["opacities"], args[k])
+            means2D.retain_grad()
+            keep.append((radii, means2D))
+            screen.append((means2D, self.rgb[k], conic_opacity, radii, depths, p["means3D"], p["scales"],
+                           p["rotations"]))
+        (m2, rgb, co, rad, dep, m3, sc, rot, sizes, sent, send_index, stats) = \
+            exchange.all_to_all_communication_final(rasts, screen, args, strategies)
+        self._exchange["bytes_sent_fwd"] = stats["bytes_sent_fwd"]
+        self._exchange["bytes_sent_bwd"] = stats["bytes_sent_bwd"]
+        heads, grads = [], []
+        for k, strat in enumerate(strategies):
+            local = strat.get_compute_locally()
+            n_rows = m2[k].shape[0]
+            if local is None or n_rows < 10:
+                # nothing to render here, but the reverse exchange must still run on every rank
+                heads.append(m2[k].sum() + co[k].sum())
+                grads.append(torch.zeros((), device=self.dev))
+                args[k]["stats_collector"].update(forward_render_time=0.0, backward_render_time=0.0)
+                continue
+            all_map = self.all_map_for(k, m3[k].detach(), sc[k].detach(), rot[k].detach(), rad[k])
+            m2abs = torch.zeros(n_rows, 3, device=self.dev, requires_grad=True)
+            color, _, _, _, _, out_all_map, plane_depth = rasts[k].render_gaussians(
+                m2[k], m2abs, co[k], rgb[k], all_map, dep[k], rad[k], local, None, args[k])
+            heads += [color, out_all_map, plane_depth]
+            grads += self.cot[k]
+        torch.autograd.backward(heads, grads)
+        self.last = keep
+        self._strategies = strategies
+        self._stats = [a["stats_collector"] for a in args]
+
+    def finish_balancer(self):
+        """Feed measured render times back into the division heuristics (one tiny all-gather)."""
+        from . import workload_division as WD
+
+        if self.ws > 1:
+            WD.finish_strategy_final(self.cams, self.history, self._strategies, self._stats, ctx=self.ctx)
+
+    def run_e2e(self):
+        """The same step with its host-side inputs copied in from pinned memory (Gaussian parameters and the
+        upstream-gradient images) and the parameter gradients read back, all inside the caller's timed region."""
+        with torch.no_grad():
+            for k, v in self.host.items():
+                self.params[k].copy_(v, non_blocking=True)
+            for k in range(len(self.cams)):
+                for dst, src in zip(self.cot[k], self.cot_host[k]):
+                    dst.copy_(src, non_blocking=True)
+        self.run()
+        for k, v in self.params.items():
+            self.grad_host[k].copy_(v.grad, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        return self.grad_host
+
+    def exchange_stats(self):
+        return None if self.ws == 1 else dict(self._exchange)

@@ -1,0 +1,262 @@
+"""Tile-row workload division across GPUs ("final" mode of the reference).
+
+Mirrors gaussian_renderer/workload_division.py of the reference for the live path:
+``division_pos_heuristic`` (:75-94), ``DivisionStrategyFinal`` (:684-778),
+``DivisionStrategyHistoryFinal`` (:781-824), ``start_strategy_final`` (:827-916) and
+``finish_strategy_final`` (:919-973).  The split unit is a tile row (a 16-pixel-high strip across the full image
+width); the rows of the whole camera batch, concatenated, are cut into ``world_size`` contiguous ranges by a
+running-time heuristic, so a GPU gets (part of) one or several cameras.
+
+Differences from the reference, none of which change a result:
+  * the reference reads rank, world size, tile grid and flags from process-wide globals; here they come from an
+    explicit :class:`DivisionContext` (``configure`` installs a default one, so the reference's call signatures
+    keep working);
+  * the heuristic vectors are a few hundred floats and live on the CPU, so cutting the batch costs no GPU
+    synchronisation (the reference runs cumsum/searchsorted on the GPU and reads the result back);
+  * per-camera times are gathered with a flat ``all_gather_into_tensor`` (works on NCCL and gloo).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import torch
+
+BLOCK_X, BLOCK_Y = 16, 16
+
+
+@dataclass
+class DivisionContext:
+    image_height: int
+    image_width: int
+    rank: int = 0
+    world_size: int = 1
+    bsz: int = 1
+    group: object = None                  # torch.distributed process group (None = default group)
+    device: object = None                 # device of compute_locally / tile-bound tensors
+    local_sampling: bool = False
+    border_divpos_coeff: float = 1.0      # reference default (arguments/__init__.py)
+    heuristic_decay: float = 0.0
+    no_heuristics_update: bool = False
+    adjust_strategy_warmp_iterations: int = -1
+    iteration: int = 0
+    extra: dict = field(default_factory=dict)
+
+    @property
+    def tile_x(self):
+        return (self.image_width + BLOCK_X - 1) // BLOCK_X
+
+    @property
+    def tile_y(self):
+        return (self.image_height + BLOCK_Y - 1) // BLOCK_Y
+
+
+_default_ctx: DivisionContext | None = None
+
+
+def configure(ctx: DivisionContext):
+    global _default_ctx
+    _default_ctx = ctx
+    return ctx
+
+
+def _ctx(ctx):
+    c = ctx or _default_ctx
+    if c is None:
+        raise RuntimeError("workload_division: call configure(DivisionContext(...)) first or pass ctx=")
+    return c
+
+
+def division_pos_heuristic(heuristic, tile_num, world_size, right=False):
+    """Cut ``tile_num`` rows into ``world_size`` contiguous parts of (nearly) equal accumulated heuristic."""
+    assert heuristic.shape[0] == tile_num, "the length of heuristics should be the same as the number of tiles."
+    heuristic = heuristic.detach().to("cpu", torch.float32)
+    heuristic_prefix_sum = torch.cumsum(heuristic, dim=0)
+    heuristic_sum = heuristic_prefix_sum[-1]
+    heuristic_per_worker = heuristic_sum / world_size
+    thresholds = torch.arange(1, world_size) * heuristic_per_worker
+    division_indices = torch.searchsorted(heuristic_prefix_sum, thresholds, right=right)
+    return [0] + division_indices.tolist() + [tile_num]
+
+
+class DivisionStrategyFinal:
+    """Which GPUs render which tile rows of one camera."""
+
+    def __init__(self, camera, world_size, gpu_ids, division_pos, gpu_for_this_camera_tilelr, ctx=None):
+        ctx = _ctx(ctx)
+        assert world_size > 0, "The world_size must be greater than 0."
+        assert len(gpu_ids) == world_size, "The number of gpu_ids must be equal to the world_size."
+        assert len(division_pos) == world_size + 1, "The number of division_pos must be equal to the world_size+1."
+        assert division_pos[0] == 0, "The first element of division_pos must be 0."
+        assert division_pos[-1] == ctx.tile_y, "The last element of division_pos must be equal to the total number of tiles."
+        for i in range(1, len(division_pos)):
+            assert division_pos[i] > division_pos[i - 1], "The division_pos must be in ascending order."
+        for idx in range(len(gpu_for_this_camera_tilelr)):
+            assert (gpu_for_this_camera_tilelr[idx][0] == division_pos[idx]
+                    and gpu_for_this_camera_tilelr[idx][1] == division_pos[idx + 1]), \
+                "The division_pos must be consistent with gpu_for_this_camera_tilelr."
+        self.ctx = ctx
+        self.camera = camera
+        self.world_size = world_size
+        self.gpu_ids = gpu_ids
+        self.rank = gpu_ids.index(ctx.rank) if ctx.rank in gpu_ids else -1
+        self.division_pos = division_pos
+
+    def tile_bounds(self, device=None):
+        """int32 (world_size+1) linear tile ids of the band boundaries (division_pos * TILE_X)."""
+        return (torch.tensor(self.division_pos, dtype=torch.int32) * self.ctx.tile_x).to(device or self.ctx.device or "cpu")
+
+    def get_local2j_ids(self, means2D, radii, raster_settings, cuda_args):
+        """(list of index tensors per destination, (P, world_size) bool mask), as the reference returns them.
+        The fused exchange (cgx.exchange) does not go through this method; it is kept for callers that do."""
+        import diff_gaussian_rasterization
+
+        mask = diff_gaussian_rasterization._C.get_local2j_ids_bool(
+            raster_settings.image_height, raster_settings.image_width, self.rank, self.world_size, means2D, radii,
+            self.tile_bounds(means2D.device), cuda_args)
+        return [mask[:, rk].nonzero() for rk in range(self.world_size)], mask
+
+    def get_compute_locally(self):
+        if self.ctx.rank not in self.gpu_ids:
+            return None
+        rank = self.gpu_ids.index(self.ctx.rank)
+        tx, ty = self.ctx.tile_x, self.ctx.tile_y
+        compute_locally = torch.zeros(ty * tx, dtype=torch.bool, device=self.ctx.device or "cpu")
+        compute_locally[self.division_pos[rank] * tx: self.division_pos[rank + 1] * tx] = True
+        return compute_locally.view(ty, tx)
+
+    def get_compute_locally_all(self):
+        if self.ctx.rank not in self.gpu_ids:
+            return None
+        return torch.ones(self.ctx.tile_y, self.ctx.tile_x, dtype=torch.bool, device=self.ctx.device or "cpu")
+
+    def get_extended_compute_locally(self):
+        return None
+
+
+class DivisionStrategyHistoryFinal:
+    """Per-camera running-time heuristic (one value per tile row) and the log of past divisions."""
+
+    def __init__(self, dataset, world_size, rank, ctx=None):
+        ctx = _ctx(ctx)
+        self.ctx = ctx
+        self.world_size = world_size
+        self.rank = rank
+        self.accum_heuristic = {}
+        cameras = dataset.cameras if hasattr(dataset, "cameras") else dataset
+        for camera in cameras:
+            self.accum_heuristic[camera.uid] = torch.ones((ctx.tile_y,), dtype=torch.float32)
+        self.history = []
+
+    def store_stats(self, batched_cameras, gpu_camera_running_time, batched_strategies):
+        batched_camera_info = []
+        all_camera_running_time = [0 for _ in range(len(batched_cameras))]
+        all_gpu_running_time = [0 for _ in range(self.world_size)]
+        for camera_id, camera in enumerate(batched_cameras):
+            each_gpu_running_time = []
+            for gpu_i in batched_strategies[camera_id].gpu_ids:
+                t = gpu_camera_running_time[gpu_i][camera_id]
+                all_camera_running_time[camera_id] += t
+                all_gpu_running_time[gpu_i] += t
+                each_gpu_running_time.append(t)
+            batched_camera_info.append({"camera_id": camera.uid, "gpu_ids": batched_strategies[camera_id].gpu_ids,
+                                        "division_pos": batched_strategies[camera_id].division_pos,
+                                        "each_gpu_running_time": each_gpu_running_time})
+        self.history.append({"iteration": self.ctx.iteration, "all_gpu_running_time": all_gpu_running_time,
+                             "all_camera_running_time": all_camera_running_time,
+                             "batched_camera_info": batched_camera_info})
+
+    def to_json(self):
+        return self.history
+
+
+def start_strategy_final(batched_cameras, strategy_history, ctx=None):
+    """Division of this batch.  Returns (one DivisionStrategyFinal per camera, gpuid -> [(camera idx, row_l, row_r)])."""
+    ctx = _ctx(ctx)
+    ws = ctx.world_size
+    n_tiles_per_image = ctx.tile_y
+    total_tiles = n_tiles_per_image * len(batched_cameras)
+    batched_strategies = []
+    gpuid2tasks = [[] for _ in range(ws)]
+
+    if ctx.local_sampling:
+        bsz_per_gpu = ctx.bsz // ws
+        for idx, camera in enumerate(batched_cameras):
+            gpu_id = idx // bsz_per_gpu
+            gpuid2tasks[gpu_id].append((idx, 0, n_tiles_per_image))
+            batched_strategies.append(DivisionStrategyFinal(camera, 1, [gpu_id], [0, n_tiles_per_image],
+                                                            [(0, n_tiles_per_image)], ctx=ctx))
+        return batched_strategies, gpuid2tasks
+
+    catted = torch.cat([strategy_history.accum_heuristic[camera.uid] for camera in batched_cameras], dim=0)
+    division_pos = division_pos_heuristic(catted, total_tiles, ws, right=True)
+    # snap cuts that fall within border_divpos_coeff rows of an image border onto the border
+    for i in range(1, len(division_pos) - 1):
+        if division_pos[i] % n_tiles_per_image + ctx.border_divpos_coeff >= n_tiles_per_image:
+            division_pos[i] = division_pos[i] // n_tiles_per_image * n_tiles_per_image + n_tiles_per_image
+        elif division_pos[i] % n_tiles_per_image - ctx.border_divpos_coeff <= 0:
+            division_pos[i] = division_pos[i] // n_tiles_per_image * n_tiles_per_image
+    for i in range(0, len(division_pos) - 1):
+        assert division_pos[i] + ctx.border_divpos_coeff < division_pos[i + 1], \
+            "Each part between division_pos must be large enough."
+
+    for idx, camera in enumerate(batched_cameras):
+        offset = idx * n_tiles_per_image
+        gpu_for_this_camera, tilelr = [], []
+        for gpu_id in range(ws):
+            gpu_tile_l, gpu_tile_r = division_pos[gpu_id], division_pos[gpu_id + 1]
+            if gpu_tile_r <= offset or offset + n_tiles_per_image <= gpu_tile_l:
+                continue
+            gpu_for_this_camera.append(gpu_id)
+            local_l = max(gpu_tile_l, offset) - offset
+            local_r = min(gpu_tile_r, offset + n_tiles_per_image) - offset
+            tilelr.append((local_l, local_r))
+            gpuid2tasks[gpu_id].append((idx, local_l, local_r))
+        batched_strategies.append(DivisionStrategyFinal(camera, len(gpu_for_this_camera), gpu_for_this_camera,
+                                                        [0] + [t[1] for t in tilelr], tilelr, ctx=ctx))
+    return batched_strategies, gpuid2tasks
+
+
+def allgather_float_list(values, ctx):
+    """(world_size, len(values)) nested list of every rank's values."""
+    import torch.distributed as dist
+
+    if ctx.world_size == 1 or not dist.is_available() or not dist.is_initialized():
+        return [list(map(float, values))]
+    backend = dist.get_backend(ctx.group)
+    dev = ctx.device if backend == "nccl" else "cpu"
+    local = torch.tensor(list(map(float, values)), dtype=torch.float32, device=dev)
+    out = torch.empty(ctx.world_size * local.numel(), dtype=torch.float32, device=dev)
+    dist.all_gather_into_tensor(out, local, group=ctx.group)
+    return out.view(ctx.world_size, -1).cpu().tolist()
+
+
+def finish_strategy_final(batched_cameras, strategy_history, batched_strategies, batched_statistic_collector, ctx=None):
+    """Feed the measured per-camera times back into the per-row heuristics."""
+    ctx = _ctx(ctx)
+    batched_running_time = []
+    for idx, strategy in enumerate(batched_strategies):
+        if ctx.rank not in strategy.gpu_ids:
+            batched_running_time.append(-1.0)
+            continue
+        st = batched_statistic_collector[idx]
+        batched_running_time.append(float(st["forward_render_time"]) + float(st["backward_render_time"])
+                                    + float(st.get("forward_loss_time", 0.0)) * 2)
+    gpu_camera_running_time = allgather_float_list(batched_running_time, ctx)
+    strategy_history.store_stats(batched_cameras, gpu_camera_running_time, batched_strategies)
+
+    if ((ctx.iteration <= ctx.adjust_strategy_warmp_iterations) or (ctx.world_size == 1) or ctx.no_heuristics_update
+            or (ctx.bsz >= ctx.world_size and (ctx.image_height <= 1080 or ctx.image_width <= 1920))
+            or (ctx.image_height <= 600 or ctx.image_width <= 1000)):
+        return
+
+    for camera_id, (camera, strategy) in enumerate(zip(batched_cameras, batched_strategies)):
+        new_heuristic = torch.zeros((ctx.tile_y,), dtype=torch.float32)
+        for local_id, gpu_id in enumerate(strategy.gpu_ids):
+            l, r = strategy.division_pos[local_id], strategy.division_pos[local_id + 1]
+            new_heuristic[l:r] = gpu_camera_running_time[gpu_id][camera_id] / (r - l)
+        if ctx.heuristic_decay == 0:
+            strategy_history.accum_heuristic[camera.uid] = new_heuristic
+        else:
+            strategy_history.accum_heuristic[camera.uid] = (
+                strategy_history.accum_heuristic[camera.uid] * ctx.heuristic_decay
+                + new_heuristic * (1 - ctx.heuristic_decay))

@@ -395,7 +395,8 @@ struct PackOffsets {
     long long row[MAX_WS];
 };
 
-// Packs the rows selected for each destination, in ascending source index, as 21-float records.
+// Packs the rows selected for each destination, in ascending source index: 19 differentiable floats into `send`,
+// [radius as float, depth] into `send_aux`, the source row into `send_index`.
 __global__ void __launch_bounds__(PACK_TILE)
 local2j_pack_kernel(int P, int gx, int gy, int ws, int nblocks, const float2* __restrict__ means2D,
                     const float* __restrict__ rgb, const float4* __restrict__ conic_opacity,
@@ -403,7 +404,7 @@ local2j_pack_kernel(int P, int gx, int gy, int ws, int nblocks, const float2* __
                     const float4* __restrict__ rotations, const int* __restrict__ radii,
                     const float* __restrict__ depths, const int* __restrict__ bounds, bool avoid,
                     const uint32_t* __restrict__ block_prefix, PackOffsets offs, float* __restrict__ send,
-                    int32_t* __restrict__ send_index)
+                    float* __restrict__ send_aux, int32_t* __restrict__ send_index)
 {
     __shared__ uint32_t s_warp_cnt[PACK_TILE / 32];
     const int i = blockIdx.x * PACK_TILE + threadIdx.x;
@@ -444,25 +445,38 @@ local2j_pack_kernel(int P, int gx, int gy, int ws, int nblocks, const float2* __
         if (sel) {
             const long long row = offs.row[rk] + block_prefix[(size_t)rk * nblocks + blockIdx.x] + wbase +
                                   __popc(b & ((1u << lane) - 1u));
-            float* dst = send + row * 21;
+            float* dst = send + row * 19;
 #pragma unroll
-            for (int k = 0; k < 21; k++) dst[k] = rec[k];
+            for (int k = 0; k < 19; k++) dst[k] = rec[k];
+            send_aux[row * 2] = rec[19];
+            send_aux[row * 2 + 1] = rec[20];
             if (send_index) send_index[row] = i;
         }
     }
 }
 
+struct RowRanges {
+    int n;
+    long long start[MAX_WS];   // first row of range r in the gradient buffer
+    long long prefix[MAX_WS + 1];  // rows in ranges before r
+};
+
+// grad rows (19 floats) of the listed row ranges are added onto the per-source-row gradient arrays.
 __global__ void __launch_bounds__(256)
-unpack_grad_add_kernel(long long n, const float* __restrict__ g, const int32_t* __restrict__ index,
+unpack_grad_add_kernel(RowRanges rr, const float* __restrict__ g, const int32_t* __restrict__ index,
                        float* __restrict__ d_means2D, float* __restrict__ d_rgb, float* __restrict__ d_co,
                        float* __restrict__ d_means3D, float* __restrict__ d_scales, float* __restrict__ d_rot)
 {
     const long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (e >= n * 19) return;
-    const long long row = e / 19;
-    const int c = (int)(e - row * 19);
+    const long long total_rows = rr.prefix[rr.n];
+    if (e >= total_rows * 19) return;
+    const long long lrow = e / 19;
+    const int c = (int)(e - lrow * 19);
+    int r = 0;
+    while (r + 1 < rr.n && lrow >= rr.prefix[r + 1]) r++;
+    const long long row = rr.start[r] + (lrow - rr.prefix[r]);
     const size_t i = (size_t)index[row];
-    const float v = g[e];
+    const float v = g[row * 19 + c];
     if (v == 0.0f) return;
     if (c < 2) atomicAdd(d_means2D + 2 * i + c, v);
     else if (c < 5) { if (d_rgb) atomicAdd(d_rgb + 3 * i + (c - 2), v); }
@@ -519,7 +533,7 @@ extern "C" int cgx_bin_count_scan(int P, int W, int H, const int32_t* radii, con
     tile_count_kernel<<<nblocks, CGX_BLOCK_SIZE, 0, st>>>(P, gx, gy, radii, (const float2*)means2D, compute_locally,
                                                           tiles_touched, sums);
     scan_partials_kernel<<<1, 1024, 0, st>>>(nblocks, sums, num_rendered);
-    return check_launch();
+    return check_launch(2);
 }
 
 extern "C" int cgx_emit_keys(int P, int W, int H, const int32_t* radii, const float* means2D, const float* depths,
@@ -570,7 +584,7 @@ extern "C" int cgx_sort_pairs(int64_t n, int end_bit, uint64_t* keys_in, uint32_
     if (passes == 0) {
         cudaMemcpyAsync(keys_out, keys_in, n * sizeof(uint64_t), cudaMemcpyDeviceToDevice, st);
         cudaMemcpyAsync(values_out, values_in, n * sizeof(uint32_t), cudaMemcpyDeviceToDevice, st);
-        return check_launch();
+        return check_launch(0);
     }
     if (passes % 2 == 0) {
         // even: in -> out -> in ... ends in `in`; swap roles by first moving the data to `out`
@@ -589,7 +603,7 @@ extern "C" int cgx_sort_pairs(int64_t n, int end_bit, uint64_t* keys_in, uint32_
         uint64_t* tk = kin; kin = kout; kout = tk;
         uint32_t* tv = vin; vin = vout; vout = tv;
     }
-    return check_launch();
+    return check_launch(3 * passes);
 }
 
 extern "C" int cgx_tile_ranges(int64_t n, int T, const uint64_t* keys_sorted, uint32_t* ranges, void* stream)
@@ -640,20 +654,20 @@ extern "C" int cgx_local2j_count(int P, int H, int W, int ws, const float* means
     local2j_count_kernel<<<nblocks, PACK_TILE, 0, st>>>(P, gx, gy, ws, nblocks, (const float2*)means2D, radii,
                                                         tile_bounds, avoid_pixel_all2all != 0, (uint32_t*)workspace);
     local2j_scan_kernel<<<ws, 1024, 0, st>>>(nblocks, (uint32_t*)workspace, counts);
-    return check_launch();
+    return check_launch(2);
 }
 
 extern "C" int cgx_local2j_pack(int P, int H, int W, int ws, const float* means2D, const float* rgb,
                                 const float* conic_opacity, const float* means3D, const float* scales,
                                 const float* rotations, const int32_t* radii, const float* depths,
                                 const int32_t* tile_bounds, int avoid_pixel_all2all, const int64_t* send_row_offset,
-                                float* send_buffer, int32_t* send_index, void* workspace, size_t workspace_bytes,
-                                void* stream)
+                                float* send_buffer, float* send_aux, int32_t* send_index, void* workspace,
+                                size_t workspace_bytes, void* stream)
 {
     if (P < 0 || W <= 0 || H <= 0 || ws <= 0 || ws > MAX_WS || !send_row_offset) return CGX_EINVAL;
     if (P == 0) return CGX_OK;
     if (!means2D || !rgb || !conic_opacity || !means3D || !scales || !rotations || !radii || !depths ||
-        !tile_bounds || !send_buffer || !workspace)
+        !tile_bounds || !send_buffer || !send_aux || !workspace)
         return CGX_EINVAL;
     if (((uintptr_t)means2D & 7) || !aligned16(conic_opacity) || !aligned16(rotations)) return CGX_EINVAL;
     if (workspace_bytes < cgx_local2j_workspace_bytes(P, ws)) return CGX_ENOMEM;
@@ -664,19 +678,30 @@ extern "C" int cgx_local2j_pack(int P, int H, int W, int ws, const float* means2
     local2j_pack_kernel<<<nblocks, PACK_TILE, 0, (cudaStream_t)stream>>>(
         P, gx, gy, ws, nblocks, (const float2*)means2D, rgb, (const float4*)conic_opacity, means3D, scales,
         (const float4*)rotations, radii, depths, tile_bounds, avoid_pixel_all2all != 0, (const uint32_t*)workspace, offs,
-        send_buffer, send_index);
+        send_buffer, send_aux, send_index);
     return check_launch();
 }
 
-extern "C" int cgx_unpack_grad_add(int64_t n_rows, const float* grad_rows, const int32_t* send_index,
-                                   float* d_means2D, float* d_rgb, float* d_conic_opacity, float* d_means3D,
-                                   float* d_scales, float* d_rotations, void* stream)
+extern "C" int cgx_unpack_grad_add(int n_ranges, const int64_t* range_start, const int64_t* range_stop,
+                                   const float* grad_rows, const int32_t* send_index, float* d_means2D, float* d_rgb,
+                                   float* d_conic_opacity, float* d_means3D, float* d_scales, float* d_rotations,
+                                   void* stream)
 {
-    if (n_rows < 0) return CGX_EINVAL;
-    if (n_rows == 0) return CGX_OK;
+    if (n_ranges < 0 || n_ranges > MAX_WS) return CGX_EINVAL;
+    if (n_ranges == 0) return CGX_OK;
+    if (!range_start || !range_stop) return CGX_EINVAL;
+    RowRanges rr;
+    rr.n = n_ranges;
+    rr.prefix[0] = 0;
+    for (int r = 0; r < n_ranges; r++) {
+        if (range_stop[r] < range_start[r] || range_start[r] < 0) return CGX_EINVAL;
+        rr.start[r] = range_start[r];
+        rr.prefix[r + 1] = rr.prefix[r] + (range_stop[r] - range_start[r]);
+    }
+    const long long total = rr.prefix[n_ranges] * 19;
+    if (total == 0) return CGX_OK;
     if (!grad_rows || !send_index || !d_means2D || !d_conic_opacity) return CGX_EINVAL;
-    const long long total = n_rows * 19;
     unpack_grad_add_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
-        n_rows, grad_rows, send_index, d_means2D, d_rgb, d_conic_opacity, d_means3D, d_scales, d_rotations);
+        rr, grad_rows, send_index, d_means2D, d_rgb, d_conic_opacity, d_means3D, d_scales, d_rotations);
     return check_launch();
 }

@@ -5,6 +5,9 @@
 namespace cgx {
 
 static thread_local char g_cuda_error[256] = "";
+static unsigned long long g_launches = 0;  // kernels launched by this library in this process
+
+
 
 void set_cuda_error(cudaError_t e)
 {
@@ -14,8 +17,9 @@ void set_cuda_error(cudaError_t e)
 
 // Launch errors only (no synchronisation): configuration problems surface here, execution faults
 // surface at the caller's next synchronising call.
-int check_launch()
+int check_launch(int launched)
 {
+    __atomic_fetch_add(&g_launches, (unsigned long long)launched, __ATOMIC_RELAXED);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) {
         set_cuda_error(e);
@@ -39,6 +43,8 @@ extern "C" const char* cgx_strerror(int status)
 }
 
 extern "C" const char* cgx_last_cuda_error(void) { return cgx::g_cuda_error; }
+
+extern "C" unsigned long long cgx_launch_count(void) { return __atomic_load_n(&cgx::g_launches, __ATOMIC_RELAXED); }
 
 extern "C" const char* cgx_version(void) { return "cgx_raster 0.1 (sm_100a)"; }
 

@@ -17,7 +17,9 @@
 namespace cgx {
 
 void set_cuda_error(cudaError_t e);
-int check_launch();
+// Checks for a launch error; `launched` = number of kernels the entry point just queued (bookkeeping for
+// cgx_launch_count()).
+int check_launch(int launched = 1);
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 

@@ -248,6 +248,49 @@ sh_to_rgb_kernel(int P, int deg, int M, const float* __restrict__ means3D, const
     }
 }
 
+
+// PGSR plane descriptor of every Gaussian for one camera, as the reference's caller builds it in tensor code
+// (gaussian_renderer/__init__.py:1501-1518): the rotation-matrix column of the smallest scale axis, flipped to
+// face the camera, rotated into camera space; then [normal_cam(3), 1, |normal_cam . p_cam|].
+// The quaternion is normalised here (the caller normalises before converting).  Forward only.
+__global__ void __launch_bounds__(256)
+all_map_kernel(int P, const float* __restrict__ means3D, const float* __restrict__ scales,
+               const float4* __restrict__ rotations, const int* __restrict__ radii,
+               const float* __restrict__ viewmatrix, const float* __restrict__ campos, float* __restrict__ out)
+{
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= P) return;
+    float o5[5] = {0.f, 0.f, 0.f, 0.f, 0.f};
+    if (!radii || radii[i] > 0) {
+        const float3 p = {means3D[3 * i], means3D[3 * i + 1], means3D[3 * i + 2]};
+        const float3 sc = {scales[3 * i], scales[3 * i + 1], scales[3 * i + 2]};
+        float4 q = rotations[i];
+        const float qn = fmaxf(sqrtf(q.x * q.x + q.y * q.y + q.z * q.z + q.w * q.w), 1e-12f);
+        q = {q.x / qn, q.y / qn, q.z / qn, q.w / qn};
+        const float r = q.x, x = q.y, y = q.z, z = q.w;
+        const float two_s = 2.0f / (r * r + x * x + y * y + z * z);
+        int idx = 0;
+        float smin = sc.x;
+        if (sc.y < smin) { smin = sc.y; idx = 1; }
+        if (sc.z < smin) { smin = sc.z; idx = 2; }
+        float3 n;
+        if (idx == 0) n = {1.f - two_s * (y * y + z * z), two_s * (x * y + z * r), two_s * (x * z - y * r)};
+        else if (idx == 1) n = {two_s * (x * y - z * r), 1.f - two_s * (x * x + z * z), two_s * (y * z + x * r)};
+        else n = {two_s * (x * z + y * r), two_s * (y * z - x * r), 1.f - two_s * (x * x + y * y)};
+        const float3 tc = {campos[0] - p.x, campos[1] - p.y, campos[2] - p.z};
+        if (n.x * tc.x + n.y * tc.y + n.z * tc.z < 0.0f) n = {-n.x, -n.y, -n.z};
+        const float* V = viewmatrix;
+        const float3 ln = {n.x * V[0] + n.y * V[4] + n.z * V[8], n.x * V[1] + n.y * V[5] + n.z * V[9],
+                           n.x * V[2] + n.y * V[6] + n.z * V[10]};
+        const float3 pc = {p.x * V[0] + p.y * V[4] + p.z * V[8] + V[12], p.x * V[1] + p.y * V[5] + p.z * V[9] + V[13],
+                           p.x * V[2] + p.y * V[6] + p.z * V[10] + V[14]};
+        o5[0] = ln.x; o5[1] = ln.y; o5[2] = ln.z; o5[3] = 1.0f;
+        o5[4] = fabsf(ln.x * pc.x + ln.y * pc.y + ln.z * pc.z);
+    }
+#pragma unroll
+    for (int k = 0; k < 5; k++) out[5 * (size_t)i + k] = o5[k];
+}
+
 // Fused backward of the per-Gaussian stage: d(conic) -> d(cov2D) -> d(cov3D), d(mean) through the EWA
 // Jacobian and through the projection of the 2-D mean, then d(cov3D) -> d(scale), d(quaternion).
 // The 3-D covariance is recomputed from scale/rotation (same function as the forward, so same bits)
@@ -528,5 +571,18 @@ extern "C" int cgx_preprocess_bwd(int P, const float* means3D, const float* scal
         P, means3D, scales, scale_modifier, rotations, radii, viewmatrix, projmatrix, focal_x, focal_y, tanfovx,
         tanfovy, (const float2*)dL_dmeans2D, (const float4*)dL_dconic_opacity, dL_dmeans3D, dL_dscales,
         (float4*)dL_drotations, dL_dopacity, vec_mask);
+    return check_launch();
+}
+
+extern "C" int cgx_all_map_fwd(int P, const float* means3D, const float* scales, const float* rotations,
+                               const int32_t* radii, const float* viewmatrix, const float* campos, float* all_map,
+                               void* stream)
+{
+    if (P < 0) return CGX_EINVAL;
+    if (P == 0) return CGX_OK;
+    if (!means3D || !scales || !rotations || !viewmatrix || !campos || !all_map || !aligned16(rotations))
+        return CGX_EINVAL;
+    all_map_kernel<<<(P + 255) / 256, 256, 0, (cudaStream_t)stream>>>(P, means3D, scales, (const float4*)rotations,
+                                                                      radii, viewmatrix, campos, all_map);
     return check_launch();
 }

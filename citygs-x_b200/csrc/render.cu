@@ -74,12 +74,16 @@ __device__ __forceinline__ void bulk_load_64(void* dst_smem, const void* src_gme
 
 // ------------------------------------------------------------------------------------------------ pack
 __global__ void __launch_bounds__(256)
-pack_records_kernel(int P, const float2* __restrict__ means2D, const float4* __restrict__ conic_opacity,
-                    const float* __restrict__ rgb, const float* __restrict__ all_map, int render_geo,
-                    Record* __restrict__ records, int* __restrict__ out_observe)
+pack_records_kernel(int P, const int* __restrict__ radii, const float2* __restrict__ means2D,
+                    const float4* __restrict__ conic_opacity, const float* __restrict__ rgb,
+                    const float* __restrict__ all_map, int render_geo, Record* __restrict__ records,
+                    int* __restrict__ out_observe)
 {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= P) return;
+    if (out_observe) out_observe[i] = 0;
+    // Gaussians without a radius never enter a tile list: their record is never read, so it is not written
+    if (radii && radii[i] <= 0) return;
     const float2 xy = means2D[i];
     const float4 co = conic_opacity[i];
     const float r = rgb[3 * i], g = rgb[3 * i + 1], b = rgb[3 * i + 2];
@@ -94,7 +98,6 @@ pack_records_kernel(int P, const float2* __restrict__ means2D, const float4* __r
     rec.q2 = {b, m[0], m[1], m[2]};
     rec.q3 = {m[3], m[4], 0.f, 0.f};
     records[i] = rec;
-    if (out_observe) out_observe[i] = 0;
 }
 
 // Half extents of the axis-aligned box outside of which opacity * exp(power) < 1/255 for certain.
@@ -654,7 +657,7 @@ extern "C" int cgx_set_render_variant(int cull)
 }
 
 extern "C" int cgx_render_fwd(int P, int W, int H, float tanfovx, float tanfovy, const uint32_t* ranges,
-                              const uint32_t* point_list, const float* means2D, const float* rgb, const float* all_map,
+                              const uint32_t* point_list, const int32_t* radii, const float* means2D, const float* rgb, const float* all_map,
                               const float* conic_opacity, const uint8_t* compute_locally, const float* bg,
                               int render_geo, void* records, float* final_T, uint32_t* n_contrib,
                               uint32_t* n_contrib2loss, float* out_color, int32_t* out_observe, float* out_all_map,
@@ -670,8 +673,9 @@ extern "C" int cgx_render_fwd(int P, int W, int H, float tanfovx, float tanfovy,
     if (P > 0 && (((uintptr_t)means2D & 7) || !aligned16(conic_opacity) || !aligned16(records))) return CGX_EINVAL;
     cudaStream_t st = (cudaStream_t)stream;
     if (P > 0)
-        pack_records_kernel<<<(P + 255) / 256, 256, 0, st>>>(P, (const float2*)means2D, (const float4*)conic_opacity,
-                                                             rgb, all_map, render_geo, (Record*)records, out_observe);
+        pack_records_kernel<<<(P + 255) / 256, 256, 0, st>>>(P, radii, (const float2*)means2D,
+                                                             (const float4*)conic_opacity, rgb, all_map, render_geo,
+                                                             (Record*)records, out_observe);
     const float focal_y = H / (2.0f * tanfovy);
     const float focal_x = W / (2.0f * tanfovx);
     const dim3 grid((W + CGX_BLOCK_X - 1) / CGX_BLOCK_X, (H + CGX_BLOCK_Y - 1) / CGX_BLOCK_Y, 1);
@@ -693,7 +697,7 @@ extern "C" int cgx_render_fwd(int P, int W, int H, float tanfovx, float tanfovy,
             (const Record*)records, final_T, n_contrib, n_contrib2loss, compute_locally, bg, out_color, out_observe,
             out_all_map, out_plane_depth, render_geo != 0, n_render_t, n_consider_t, n_contrib_t);
     }
-    return check_launch();
+    return check_launch(P > 0 ? 2 : 1);
 }
 
 extern "C" int cgx_tile_stats(int W, int H, const uint32_t* ranges, const uint32_t* n_contrib_px,

@@ -24,6 +24,24 @@ BLOCK_X, BLOCK_Y, ONE_DIM_BLOCK_SIZE = 16, 16, 256
 NUM_CHANNELS, NUM_ALL_MAP = 3, 5
 
 
+# Optional per-stage profiling: when PROFILE is a list, every C-ABI call is bracketed by two CUDA events on the
+# current stream and (stage, start, end, info) is appended; the owner resolves the events after a synchronise.
+PROFILE = None
+
+
+def _call(stage, fn, *a, info=None):
+    prof = PROFILE
+    if prof is None:
+        check(fn(*a), stage)
+        return
+    e0 = torch.cuda.Event(enable_timing=True)
+    e1 = torch.cuda.Event(enable_timing=True)
+    e0.record()
+    check(fn(*a), stage)
+    e1.record()
+    prof.append((stage, e0, e1, info))
+
+
 def _ptr(t):
     return None if t is None else C.c_void_p(t.data_ptr())
 
@@ -111,8 +129,8 @@ def mark_visible(means3D, viewmatrix, projmatrix):
     present = torch.empty(P, dtype=torch.bool, device=means3D.device)
     if P:
         with torch.cuda.device(means3D.device):
-            check(_lib.lib().cgx_mark_visible(P, _ptr(means3D), _ptr(_cuda_f32(viewmatrix, "viewmatrix")),
-                                              _ptr(present), _stream()), "cgx_mark_visible")
+            _call("cgx_mark_visible", _lib.lib().cgx_mark_visible, P, _ptr(means3D), _ptr(_cuda_f32(viewmatrix, "viewmatrix")),
+                                              _ptr(present), _stream())
     return present
 
 
@@ -132,13 +150,12 @@ def preprocess_gaussians(means3D, scales, rotations, sh, opacity, scale_modifier
     clamped = torch.zeros(P, 3, dtype=torch.bool, device=dev)
     if P:
         with torch.cuda.device(dev):
-            check(_lib.lib().cgx_preprocess_fwd(
+            _call("cgx_preprocess_fwd", _lib.lib().cgx_preprocess_fwd, 
                 P, _ptr(means3D), _ptr(_cuda_f32(scales, "scales")), float(scale_modifier),
                 _ptr(_cuda_f32(rotations, "rotations")), _ptr(_cuda_f32(opacity, "opacity")),
                 _ptr(_cuda_f32(viewmatrix, "viewmatrix")), _ptr(_cuda_f32(projmatrix, "projmatrix")),
                 int(image_width), int(image_height), float(tan_fovx), float(tan_fovy),
-                _ptr(means2D), _ptr(depths), _ptr(radii), _ptr(cov3D), _ptr(conic_opacity), _stream()),
-                "cgx_preprocess_fwd")
+                _ptr(means2D), _ptr(depths), _ptr(radii), _ptr(cov3D), _ptr(conic_opacity), _stream(), info=dict(P=P))
             if debug:
                 _check_device(dev)
     return 0, means2D, depths, radii, cov3D, conic_opacity, rgb, clamped
@@ -159,14 +176,13 @@ def preprocess_gaussians_backward(radii, cov3D, clamped, means3D, scales, rotati
         if dm2.shape[1] == 3:          # the reference pads the cotangent to (P,3); only x,y are used
             dm2 = dm2[:, :2].contiguous()
         with torch.cuda.device(dev):
-            check(_lib.lib().cgx_preprocess_bwd(
+            _call("cgx_preprocess_bwd", _lib.lib().cgx_preprocess_bwd, 
                 P, _ptr(means3D), _ptr(_cuda_f32(scales, "scales")), float(scale_modifier),
                 _ptr(_cuda_f32(rotations, "rotations")), _ptr(_cuda_any(radii, "radii")),
                 _ptr(_cuda_f32(viewmatrix, "viewmatrix")), _ptr(_cuda_f32(projmatrix, "projmatrix")),
                 int(image_width), int(image_height), float(tan_fovx), float(tan_fovy),
                 _ptr(dm2), _ptr(_cuda_f32(dL_dconic_opacity, "dL_dconic_opacity")),
-                _ptr(dL_dmeans3D), _ptr(dL_dscales), _ptr(dL_drotations), _ptr(dL_dopacity), _stream()),
-                "cgx_preprocess_bwd")
+                _ptr(dL_dmeans3D), _ptr(dL_dscales), _ptr(dL_drotations), _ptr(dL_dopacity), _stream(), info=dict(P=P))
             if debug:
                 _check_device(dev)
     return dL_dmeans3D, dL_dscales, dL_drotations, dL_dsh, dL_dopacity
@@ -277,9 +293,9 @@ def render_gaussians(background, image_height, image_width, means2D, depths, rad
         imgBuffer = torch.empty(ilay.total(), dtype=torch.uint8, device=dev)
         im = ilay.views(imgBuffer)
 
-        check(l.cgx_bin_count_scan(P, W, H, _ptr(radii), _ptr(means2D), _ptr(local), _ptr(g["tiles_touched"]),
+        _call("cgx_bin_count_scan", l.cgx_bin_count_scan, P, W, H, _ptr(radii), _ptr(means2D), _ptr(local), _ptr(g["tiles_touched"]),
                                    _ptr(g["num_rendered"]), _ptr(g["scanning_space"]),
-                                   g["scanning_space"].numel(), st), "cgx_bin_count_scan")
+                                   g["scanning_space"].numel(), st, info=dict(P=P))
         # the key/value buffers are sized from the pair count: one host read, as in the reference
         R = int(g["num_rendered"][0].item())
 
@@ -290,20 +306,20 @@ def render_gaussians(background, image_height, image_width, means2D, depths, rad
             ev0 = torch.cuda.Event(enable_timing=True)
             ev1 = torch.cuda.Event(enable_timing=True)
             ev0.record()
-        check(l.cgx_emit_keys(P, W, H, _ptr(radii), _ptr(means2D), _ptr(depths), _ptr(g["tiles_touched"]),
+        _call("cgx_emit_keys", l.cgx_emit_keys, P, W, H, _ptr(radii), _ptr(means2D), _ptr(depths), _ptr(g["tiles_touched"]),
                               _ptr(local), _ptr(g["point_offsets"]), _ptr(b["point_list_keys_unsorted"]),
-                              _ptr(b["point_list_unsorted"]), R, _ptr(g["scanning_space"]), st), "cgx_emit_keys")
+                              _ptr(b["point_list_unsorted"]), R, _ptr(g["scanning_space"]), st, info=dict(P=P, R=R))
         bit = int(l.cgx_higher_msb(T))
-        check(l.cgx_sort_pairs(R, 32 + bit, _ptr(b["point_list_keys_unsorted"]), _ptr(b["point_list_unsorted"]),
+        _call("cgx_sort_pairs", l.cgx_sort_pairs, R, 32 + bit, _ptr(b["point_list_keys_unsorted"]), _ptr(b["point_list_unsorted"]),
                                _ptr(b["point_list_keys"]), _ptr(b["point_list"]), _ptr(b["list_sorting_space"]),
-                               b["list_sorting_space"].numel(), st), "cgx_sort_pairs")
-        check(l.cgx_tile_ranges(R, T, _ptr(b["point_list_keys"]), _ptr(im["ranges"]), st), "cgx_tile_ranges")
-        check(l.cgx_render_fwd(P, W, H, float(tan_fovx), float(tan_fovy), _ptr(im["ranges"]), _ptr(b["point_list"]),
-                               _ptr(means2D), _ptr(rgb), _ptr(all_map), _ptr(conic_opacity), _ptr(local), _ptr(bg),
+                               b["list_sorting_space"].numel(), st, info=dict(R=R, bits=32 + bit))
+        _call("cgx_tile_ranges", l.cgx_tile_ranges, R, T, _ptr(b["point_list_keys"]), _ptr(im["ranges"]), st, info=dict(R=R, T=T))
+        _call("cgx_render_fwd", l.cgx_render_fwd, P, W, H, float(tan_fovx), float(tan_fovy), _ptr(im["ranges"]), _ptr(b["point_list"]),
+                               _ptr(radii), _ptr(means2D), _ptr(rgb), _ptr(all_map), _ptr(conic_opacity), _ptr(local), _ptr(bg),
                                int(bool(render_geo)), _ptr(g["records"]), _ptr(im["accum_alpha"]),
                                _ptr(im["n_contrib"]), _ptr(im["n_contrib2loss"]), _ptr(out_color), _ptr(out_observe),
                                _ptr(out_all_map), _ptr(out_plane_depth), _ptr(n_render), _ptr(n_consider),
-                               _ptr(n_contrib), st), "cgx_render_fwd")
+                               _ptr(n_contrib), st, info=dict(P=P, R=R, HW=H * W))
         if stats is not None:
             ev1.record()
             stats["forward_render_time"] = _EventMs([(ev0, ev1)])
@@ -337,7 +353,7 @@ def render_gaussians_backward(background, tan_fovx, tan_fovy, all_map_pixels, al
                 ev0 = torch.cuda.Event(enable_timing=True)
                 ev1 = torch.cuda.Event(enable_timing=True)
                 ev0.record()
-            check(l.cgx_render_bwd(P, W, H, float(tan_fovx), float(tan_fovy), _ptr(im["ranges"]), _ptr(b["point_list"]),
+            _call("cgx_render_bwd", l.cgx_render_bwd, P, W, H, float(tan_fovx), float(tan_fovy), _ptr(im["ranges"]), _ptr(b["point_list"]),
                                    _ptr(_cuda_f32(background, "background")), _ptr(g["records"]),
                                    _ptr(_cuda_f32(all_map_pixels, "all_map_pixels")), _ptr(im["accum_alpha"]),
                                    _ptr(im["n_contrib"]), _ptr(_cuda_any(compute_locally, "compute_locally")),
@@ -345,7 +361,7 @@ def render_gaussians_backward(background, tan_fovx, tan_fovy, all_map_pixels, al
                                    _ptr(_cuda_f32(dL_dout_all_map, "dL_dout_all_map")),
                                    _ptr(_cuda_f32(dL_dout_plane_depth, "dL_dout_plane_depth")),
                                    int(bool(render_geo)), _ptr(dL_dmeans2D), _ptr(dL_dmeans2D_abs),
-                                   _ptr(dL_dconic_opacity), _ptr(dL_dcolors), _ptr(dL_dall_map), st), "cgx_render_bwd")
+                                   _ptr(dL_dconic_opacity), _ptr(dL_dcolors), _ptr(dL_dall_map), st, info=dict(P=P, R=R, HW=H * W))
             if stats is not None:
                 ev1.record()
                 stats["backward_render_time"] = _EventMs([(ev0, ev1)])
@@ -365,11 +381,11 @@ def get_local2j_ids_bool(image_height, image_width, mp_rank, mp_world_size, mean
     mask = torch.empty(P, mp_world_size, dtype=torch.bool, device=dev)
     if P:
         with torch.cuda.device(dev):
-            check(_lib.lib().cgx_local2j_mask(P, int(image_height), int(image_width), int(mp_world_size),
+            _call("cgx_local2j_mask", _lib.lib().cgx_local2j_mask, P, int(image_height), int(image_width), int(mp_world_size),
                                               _ptr(means2D), _ptr(_cuda_any(radii, "radii")),
                                               _ptr(_cuda_any(dist_global_strategy, "dist_global_strategy")
                                                    .to(torch.int32)), int(avoid),
-                                              _ptr(mask), _stream()), "cgx_local2j_mask")
+                                              _ptr(mask), _stream())
     return mask
 
 
@@ -454,9 +470,9 @@ def rasterize_aussians_filter(means3D, scales, rotations, scale_modifier, cov3D_
         if scales is None or scales.numel() == 0 or rotations is None or rotations.numel() == 0:
             raise RuntimeError("visible_filter needs scales and rotations (precomputed covariances are not supported)")
         with torch.cuda.device(dev):
-            check(_lib.lib().cgx_filter_preprocess(
+            _call("cgx_filter_preprocess", _lib.lib().cgx_filter_preprocess, 
                 P, _ptr(means3D), _ptr(_cuda_f32(scales, "scales")), float(scale_modifier),
                 _ptr(_cuda_f32(rotations, "rotations")), _ptr(_cuda_f32(viewmatrix, "viewmatrix")),
                 _ptr(_cuda_f32(projmatrix, "projmatrix")), int(image_width), int(image_height), float(tan_fovx),
-                float(tan_fovy), _ptr(radii), _stream()), "cgx_filter_preprocess")
+                float(tan_fovy), _ptr(radii), _stream())
     return radii

@@ -56,11 +56,12 @@ SIGNATURES = {
     "cgx_filter_preprocess": (_i, [_i, _vp, _vp, _f, _vp, _vp, _vp, _i, _i, _f, _f, _vp, _vp]),
     "cgx_sh_to_rgb": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp]),
     "cgx_preprocess_bwd": (_i, [_i, _vp, _vp, _f, _vp, _vp, _vp, _vp, _i, _i, _f, _f, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "cgx_all_map_fwd": (_i, [_i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "cgx_local2j_mask": (_i, [_i, _i, _i, _i, _vp, _vp, _vp, _i, _vp, _vp]),
     "cgx_local2j_count": (_i, [_i, _i, _i, _i, _vp, _vp, _vp, _i, _vp, _vp, _sz, _vp]),
     "cgx_local2j_workspace_bytes": (_sz, [_i, _i]),
-    "cgx_local2j_pack": (_i, [_i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _sz, _vp]),
-    "cgx_unpack_grad_add": (_i, [_i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "cgx_local2j_pack": (_i, [_i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
+    "cgx_unpack_grad_add": (_i, [_i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "cgx_bin_workspace_bytes": (_sz, [_i]),
     "cgx_bin_count_scan": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "cgx_emit_keys": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _vp, _vp]),
@@ -68,7 +69,8 @@ SIGNATURES = {
     "cgx_sort_pairs": (_i, [_i64, _i, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "cgx_tile_ranges": (_i, [_i64, _i, _vp, _vp, _vp]),
     "cgx_render_records_bytes": (_sz, [_i]),
-    "cgx_render_fwd": (_i, [_i, _i, _i, _f, _f] + [_vp] * 8 + [_i] + [_vp] * 12),
+    "cgx_render_fwd": (_i, [_i, _i, _i, _f, _f] + [_vp] * 9 + [_i] + [_vp] * 12),
+    "cgx_launch_count": (C.c_uint64, []),
     "cgx_tile_stats": (_i, [_i, _i] + [_vp] * 8),
     "cgx_render_bwd": (_i, [_i, _i, _i, _f, _f] + [_vp] * 11 + [_i] + [_vp] * 6),
     "cgx_device_status": (_i, [_vp, _vp]),

@@ -36,6 +36,8 @@ const char* cgx_strerror(int status);
 const char* cgx_last_cuda_error(void);
 /* Library version string. */
 const char* cgx_version(void);
+/* Number of kernels this library has launched in this process (all entry points, all streams). */
+unsigned long long cgx_launch_count(void);
 
 /* GetBlockXY (RAST/rasterize_points.cu:858-861): tile size and 1-D block size. */
 int cgx_block_xy(int* block_x, int* block_y, int* one_dim_block);
@@ -87,6 +89,13 @@ int cgx_preprocess_bwd(int P, const float* means3D, const float* scales, float s
                        float* dL_dmeans3D, float* dL_dscales, float* dL_drotations, float* dL_dopacity,
                        void* stream);
 
+/* PGSR per-Gaussian plane descriptor [normal_cam(3), 1, plane distance] for one camera, forward only: the
+ * tensor code of the reference's caller (gaussian_renderer/__init__.py:1501-1518) as one kernel.
+ * radii optional: rows with radius <= 0 get zeros.  all_map (P,5). */
+int cgx_all_map_fwd(int P, const float* means3D, const float* scales, const float* rotations,
+                    const int32_t* radii, const float* viewmatrix, const float* campos, float* all_map,
+                    void* stream);
+
 /* ------------------------------------------------------------------ distribution */
 
 /* GetLocal2jIdsBoolCUDA -> getTouchedIdsBool (RAST/rasterize_points.cu:445-524).
@@ -97,26 +106,30 @@ int cgx_local2j_mask(int P, int H, int W, int ws, const float* means2D, const in
 
 /* Fused replacement of the caller loop around get_local2j_ids_bool (mask -> nonzero -> index-gather
  * -> concat; gaussian_renderer/workload_division.py:721-744, gaussian_renderer/__init__.py:612-666,
- * 709-716): one pass that counts, for each destination column j, the rows whose tile span touches
- * j's band, then packs those rows (ascending local index, as nonzero() yields them) as
- * 21-float records [means2D 2 | rgb 3 | conic_opacity 4 | means3D 3 | scales 3 | rotations 4 |
- * radius-as-float 1 | depth 1] into a send buffer at row offset send_row_offset[j].
- *   cgx_local2j_count : counts (ws) int32 written (device).
- *   cgx_local2j_pack  : needs counts' exclusive layout from the caller (row offsets per column). */
+ * 709-716).  Two passes over one camera's local Gaussians:
+ *   cgx_local2j_count : counts (ws) int32 (device) = rows whose tile span touches each destination's band.
+ *   cgx_local2j_pack  : writes those rows, ascending local index per destination (the order nonzero()
+ *                       yields), starting at row send_row_offset[j] (host array, ws entries) of
+ *                       send_buffer (rows of 19 floats: means2D 2 | rgb 3 | conic_opacity 4 | means3D 3 |
+ *                       scales 3 | rotations 4), send_aux (rows of 2 floats: radius as float | depth) and
+ *                       send_index (int32 source row, optional).
+ * workspace: cgx_local2j_workspace_bytes(P, ws) bytes, the SAME buffer for both calls of a camera. */
+size_t cgx_local2j_workspace_bytes(int P, int ws);
 int cgx_local2j_count(int P, int H, int W, int ws, const float* means2D, const int32_t* radii,
                       const int32_t* tile_bounds, int avoid_pixel_all2all, int32_t* counts,
                       void* workspace, size_t workspace_bytes, void* stream);
-size_t cgx_local2j_workspace_bytes(int P, int ws);
 int cgx_local2j_pack(int P, int H, int W, int ws, const float* means2D, const float* rgb,
                      const float* conic_opacity, const float* means3D, const float* scales,
                      const float* rotations, const int32_t* radii, const float* depths,
                      const int32_t* tile_bounds, int avoid_pixel_all2all,
-                     const int64_t* send_row_offset /* host, ws entries */, float* send_buffer,
-                     int32_t* send_index /* optional: source row of every packed row */,
+                     const int64_t* send_row_offset, float* send_buffer, float* send_aux, int32_t* send_index,
                      void* workspace, size_t workspace_bytes, void* stream);
-/* Reverse of the pack for the backward exchange: grad_rows (n,19) are added into per-source-row
- * gradient arrays through send_index (rows can repeat across destinations). */
-int cgx_unpack_grad_add(int64_t n_rows, const float* grad_rows, const int32_t* send_index,
+/* Backward of the pack (the reference gets it from autograd through index/cat): the 19-float gradient rows
+ * of the listed row ranges [range_start[r], range_stop[r]) (host arrays, n_ranges <= 32) are added onto the
+ * per-source-row gradient arrays through send_index (a source row can appear under several destinations).
+ * d_rgb, d_means3D, d_scales, d_rotations may be NULL. */
+int cgx_unpack_grad_add(int n_ranges, const int64_t* range_start, const int64_t* range_stop,
+                        const float* grad_rows, const int32_t* send_index,
                         float* d_means2D, float* d_rgb, float* d_conic_opacity, float* d_means3D,
                         float* d_scales, float* d_rotations, void* stream);
 
@@ -159,14 +172,15 @@ int cgx_tile_ranges(int64_t n, int T, const uint64_t* keys_sorted, uint32_t* ran
  * RAST/cuda_rasterizer/rasterizer_impl.cu:699-725, RAST/cuda_rasterizer/forward.cu:264-486).
  * Writes every pixel of every image output (zeros in tiles that are not computed locally) and zero-fills
  * out_observe before accumulating.  records: scratch for P 64-byte packed records (see
- * cgx_render_records_bytes), kept by the caller for the backward.
+ * cgx_render_records_bytes), kept by the caller for the backward; when `radii` is given, records of
+ * Gaussians with radius <= 0 (never listed in any tile) are left unwritten.
  *   -> final_T f32 (H*W), n_contrib u32 (H*W), n_contrib2loss u32 (H*W), out_color (3,H,W),
  *      out_observe int32 (P), out_all_map (5,H,W), out_plane_depth (1,H,W),
  *      and the per-tile statistics of cgx_tile_stats (n_render, n_consider, n_contrib: int32 (T)),
  *      reduced in the kernel's epilogue.                                                         */
 size_t cgx_render_records_bytes(int P);
 int cgx_render_fwd(int P, int W, int H, float tanfovx, float tanfovy, const uint32_t* ranges,
-                   const uint32_t* point_list, const float* means2D, const float* rgb, const float* all_map,
+                   const uint32_t* point_list, const int32_t* radii /* optional */, const float* means2D, const float* rgb, const float* all_map,
                    const float* conic_opacity, const uint8_t* compute_locally, const float* bg, int render_geo,
                    void* records, float* final_T, uint32_t* n_contrib, uint32_t* n_contrib2loss,
                    float* out_color, int32_t* out_observe, float* out_all_map, float* out_plane_depth,

@@ -437,16 +437,19 @@ void orc_tile_stats(int W, int H, const uint32_t *ranges, const uint32_t *n_cont
     }
 }
 
-static inline void atomic_addf(float *p, float v)
+/* Per-Gaussian gradient sums are accumulated in double and narrowed once at the end: the sums cancel heavily
+ * and their fp32 value depends on the (unordered) summation order, on the GPU as much as here; the double
+ * accumulator makes the oracle the order-independent value both are compared with. */
+static inline void atomic_addd(double *p, float v)
 {
 #pragma omp atomic
-    *p += v;
+    *p += (double)v;
 }
 
 /* backward.cu:324-567.  Gradient outputs must be zero-filled:
  * dL_dmean2D (P,3), dL_dmean2D_abs (P,3), dL_dconic (P,4) [= (P,2,2)],
  * dL_dopacity (P), dL_dcolors (P,3), dL_dall_map (P,5). */
-void orc_render_bwd(int W, int H, float tanx, float tany, const uint32_t *ranges, const uint32_t *point_list,
+void orc_render_bwd(int P, int W, int H, float tanx, float tany, const uint32_t *ranges, const uint32_t *point_list,
                     const float *bg, const float *means2D, const float *conic_opacity, const float *rgb,
                     const float *all_map, const float *all_map_pixels, const float *final_T,
                     const uint32_t *n_contrib, const uint8_t *local, const float *dL_dpix,
@@ -458,6 +461,8 @@ void orc_render_bwd(int W, int H, float tanx, float tany, const uint32_t *ranges
     const float fy = H / (2.0f * tany), fx = W / (2.0f * tanx);
     const size_t HW = (size_t)H * W;
     const float ddelx_dx = (float)(0.5 * W), ddely_dy = (float)(0.5 * H);
+    /* 16 double accumulators per Gaussian: mean2D x,y | abs x,y | conic [0,0],[0,1],[1,1] | opacity | rgb 3 | map 5 */
+    double *acc = (double *)calloc((size_t)(P > 0 ? P : 1) * 16, sizeof(double));
 #pragma omp parallel for schedule(dynamic, 4)
     for (int tile = 0; tile < gx * gy; tile++) {
         if (!local[tile]) continue;
@@ -494,6 +499,7 @@ void orc_render_bwd(int W, int H, float tanx, float tany, const uint32_t *ranges
                     contributor--;
                     if (contributor >= last_contributor) continue;
                     const uint32_t g = point_list[k];
+                    double *a16 = acc + (size_t)g * 16;
                     const float dx = means2D[2 * g] - pfx, dy = means2D[2 * g + 1] - pfy;
                     const float *co = conic_opacity + 4 * (size_t)g;
                     const float power = -0.5f * (co[0] * dx * dx + co[2] * dy * dy) - co[1] * dx * dy;
@@ -509,7 +515,7 @@ void orc_render_bwd(int W, int H, float tanx, float tany, const uint32_t *ranges
                         accum_rec[ch] = last_alpha * last_color[ch] + (1.f - last_alpha) * accum_rec[ch];
                         last_color[ch] = c;
                         dL_dalpha += (c - accum_rec[ch]) * dpix[ch];
-                        atomic_addf(&dL_dcolors[(size_t)g * NCH + ch], dchannel_dcolor * dpix[ch]);
+                        atomic_addd(&a16[8 + ch], dchannel_dcolor * dpix[ch]);
                     }
                     if (render_geo)
                         for (int ch = 0; ch < NMAP; ch++) {
@@ -517,7 +523,7 @@ void orc_render_bwd(int W, int H, float tanx, float tany, const uint32_t *ranges
                             accum_map[ch] = last_alpha * last_map[ch] + (1.f - last_alpha) * accum_map[ch];
                             last_map[ch] = c;
                             dL_dalpha += (c - accum_map[ch]) * dmap[ch];
-                            atomic_addf(&dL_dall_map[(size_t)g * NMAP + ch], dchannel_dcolor * dmap[ch]);
+                            atomic_addd(&a16[11 + ch], dchannel_dcolor * dmap[ch]);
                         }
                     dL_dalpha *= T;
                     last_alpha = alpha;
@@ -528,17 +534,29 @@ void orc_render_bwd(int W, int H, float tanx, float tany, const uint32_t *ranges
                     const float gdx = G * dx, gdy = G * dy;
                     const float dG_ddelx = -gdx * co[0] - gdy * co[1];
                     const float dG_ddely = -gdy * co[2] - gdx * co[1];
-                    atomic_addf(&dL_dmean2D[3 * (size_t)g], dL_dG * dG_ddelx * ddelx_dx);
-                    atomic_addf(&dL_dmean2D[3 * (size_t)g + 1], dL_dG * dG_ddely * ddely_dy);
-                    atomic_addf(&dL_dmean2D_abs[3 * (size_t)g], fabsf(dL_dG * dG_ddelx * ddelx_dx));
-                    atomic_addf(&dL_dmean2D_abs[3 * (size_t)g + 1], fabsf(dL_dG * dG_ddely * ddely_dy));
-                    atomic_addf(&dL_dconic[4 * (size_t)g], -0.5f * gdx * dx * dL_dG);
-                    atomic_addf(&dL_dconic[4 * (size_t)g + 1], -0.5f * gdx * dy * dL_dG);
-                    atomic_addf(&dL_dconic[4 * (size_t)g + 3], -0.5f * gdy * dy * dL_dG);
-                    atomic_addf(&dL_dopacity[g], G * dL_dalpha);
+                    atomic_addd(&a16[0], dL_dG * dG_ddelx * ddelx_dx);
+                    atomic_addd(&a16[1], dL_dG * dG_ddely * ddely_dy);
+                    atomic_addd(&a16[2], fabsf(dL_dG * dG_ddelx * ddelx_dx));
+                    atomic_addd(&a16[3], fabsf(dL_dG * dG_ddely * ddely_dy));
+                    atomic_addd(&a16[4], -0.5f * gdx * dx * dL_dG);
+                    atomic_addd(&a16[5], -0.5f * gdx * dy * dL_dG);
+                    atomic_addd(&a16[6], -0.5f * gdy * dy * dL_dG);
+                    atomic_addd(&a16[7], G * dL_dalpha);
                 }
             }
     }
+#pragma omp parallel for schedule(static)
+    for (int g = 0; g < P; g++) {
+        const double *a16 = acc + (size_t)g * 16;
+        dL_dmean2D[3 * (size_t)g] = (float)a16[0]; dL_dmean2D[3 * (size_t)g + 1] = (float)a16[1];
+        dL_dmean2D_abs[3 * (size_t)g] = (float)a16[2]; dL_dmean2D_abs[3 * (size_t)g + 1] = (float)a16[3];
+        dL_dconic[4 * (size_t)g] = (float)a16[4]; dL_dconic[4 * (size_t)g + 1] = (float)a16[5];
+        dL_dconic[4 * (size_t)g + 3] = (float)a16[6];
+        dL_dopacity[g] = (float)a16[7];
+        for (int ch = 0; ch < NCH; ch++) dL_dcolors[(size_t)g * NCH + ch] = (float)a16[8 + ch];
+        for (int ch = 0; ch < NMAP; ch++) dL_dall_map[(size_t)g * NMAP + ch] = (float)a16[11 + ch];
+    }
+    free(acc);
 }
 
 /* backward.cu:69-199 + 271-321 + 203-266, with the (P,4) conic_opacity

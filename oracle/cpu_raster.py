@@ -183,7 +183,7 @@ def render_bwd(means2D, conic_opacity, rgb, all_map, all_map_pixels, final_T, n_
     d_op = torch.zeros(P)
     d_col = torch.zeros(P, 3)
     d_map = torch.zeros(P, 5)
-    lib().orc_render_bwd(W, H, C.c_float(tanfovx), C.c_float(tanfovy), _p(ranges.contiguous()),
+    lib().orc_render_bwd(P, W, H, C.c_float(tanfovx), C.c_float(tanfovy), _p(ranges.contiguous()),
                          _p(point_list.contiguous()), _p(_f(bg)), _p(_f(means2D)), _p(_f(conic_opacity)),
                          _p(_f(rgb)), _p(_f(all_map)), _p(_f(all_map_pixels)), _p(_f(final_T)),
                          _p(n_contrib_px.contiguous()), _p(local), _p(_f(dL_dcolor)), _p(_f(dL_dall_map_px)),

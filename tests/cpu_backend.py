@@ -1,0 +1,42 @@
+"""Test-only CPU packing backend for cgx.exchange: selection by the oracle's mask, packing by tensor indexing.
+It lets the gloo tests exercise the exchange's host logic (sizes, layout, collectives, autograd, ordering) without
+a GPU.  The shipped package never imports this file."""
+import torch
+
+from oracle import cpu_raster as O
+
+
+class OracleBackend:
+    def workspace(self, P, ws, device):
+        return torch.empty(0, dtype=torch.uint8)
+
+    def _mask(self, means2D, radii, tile_bounds, H, W, avoid):
+        return O.local2j_mask(means2D, radii, tile_bounds, W, H, avoid)
+
+    def count(self, means2D, radii, tile_bounds, H, W, avoid, counts_out, workspace):
+        counts_out.copy_(self._mask(means2D, radii, tile_bounds, H, W, avoid).sum(0).to(torch.int32))
+
+    def pack(self, params, tile_bounds, H, W, avoid, row_offsets, send, send_aux, send_index, workspace):
+        means2D, rgb, conic_opacity, radii, depths, means3D, scales, rotation = params
+        mask = self._mask(means2D, radii, tile_bounds, H, W, avoid)
+        rows = torch.cat([means2D, rgb, conic_opacity, means3D, scales, rotation], dim=1)
+        aux = torch.stack([radii.float(), depths], dim=1)
+        for j, off in enumerate(row_offsets):
+            idx = mask[:, j].nonzero().flatten()
+            send[off:off + idx.numel()] = rows[idx]
+            send_aux[off:off + idx.numel()] = aux[idx]
+            send_index[off:off + idx.numel()] = idx.to(torch.int32)
+
+    def unpack_grad_add(self, grad_rows, send_index, ranges, grads):
+        d_m2, d_rgb, d_co, d_m3, d_sc, d_rot = grads
+        for a, b in ranges:
+            if b <= a:
+                continue
+            idx = send_index[a:b].long()
+            g = grad_rows[a:b]
+            d_m2.index_add_(0, idx, g[:, 0:2])
+            d_rgb.index_add_(0, idx, g[:, 2:5])
+            d_co.index_add_(0, idx, g[:, 5:9])
+            d_m3.index_add_(0, idx, g[:, 9:12])
+            d_sc.index_add_(0, idx, g[:, 12:15])
+            d_rot.index_add_(0, idx, g[:, 15:19])
