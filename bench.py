@@ -49,6 +49,7 @@ def parse_args():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS))
     ap.add_argument("--gaussians", type=int, default=None, help="override the Gaussian count (scaling sweep)")
+    ap.add_argument("--cameras", type=int, default=None, help="use only the first N cameras (profiling captures)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--cpu-sample-gaussians", type=int, default=None)
@@ -188,6 +189,8 @@ def main():
 
     cfg = WORKLOADS[a.workload][0]
     g, cams = S.config(cfg, n_gaussians=a.gaussians)
+    if a.cameras:
+        cams = cams[: a.cameras]
     step = RT.TrainingStep(g, cams, dev, rank=rank, world_size=world)
     mpix = sum(c.W * c.H for c in cams) / 1e6
     n_scene = g["means3D"].shape[0]
