@@ -133,6 +133,7 @@ class TrainingStep:
             self._step_single()
         else:
             self._step_distributed()
+            self.finish_balancer()
         return self.params
 
     # ------------------------------------------------------------------ multi-GPU step

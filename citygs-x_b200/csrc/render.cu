@@ -1,13 +1,14 @@
 // Per-tile alpha compositing, forward and backward (FP32-pipe bound).
 //
-// One CTA (16x16 threads, one pixel each) per 16x16 tile, like the reference, but:
+// One CTA (256 threads, one pixel each) per 16x16 tile, like the reference, but:
 //  * the five per-Gaussian inputs are first packed into one 64-byte record per Gaussian
 //    [x y | a b c opacity | r g b | m0..m4 | pad pad]; a tile's batch of 256 records is then staged into
 //    shared memory by 256 asynchronous 64-byte bulk copies (cp.async.bulk, completion on an mbarrier),
 //    double-buffered so the gather of batch i+1 overlaps the blending of batch i; colours and the
 //    plane map channels are read from shared memory instead of per-pixel global loads;
-//  * each warp first culls the batch against its own 16x2 pixel strip with an exact-safe bound
-//    (a Gaussian is dropped for the strip only if alpha < 1/255 is guaranteed there), 32 Gaussians per
+//  * each warp owns an 8x4 pixel block of the tile and first culls the batch against it with an exact-safe bound
+//    (a Gaussian is dropped for the block only if alpha < 1/255 is guaranteed there; the half extents are
+//    computed once per Gaussian when its record is packed), 32 Gaussians per
 //    ballot, and blends only the survivors;
 //  * the per-tile statistics (sum of per-pixel counters) are reduced in the epilogue;
 //  * the backward reduces the 16 gradient terms of a Gaussian over the warp's 32 pixels with a
@@ -28,7 +29,7 @@ struct __align__(16) Record {
     float4 q0;  // x, y, conic a, conic b
     float4 q1;  // conic c, opacity, r, g
     float4 q2;  // b, m0, m1, m2
-    float4 q3;  // m3, m4, 0, 0
+    float4 q3;  // m3, m4, cull half-extent x, cull half-extent y (see cull_extent)
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -72,6 +73,22 @@ __device__ __forceinline__ void bulk_load_64(void* dst_smem, const void* src_gme
                  : "memory");
 }
 
+// Half extents of the axis-aligned box outside of which opacity * exp(power) < 1/255 for certain.
+// power = -0.5 (a dx^2 + c dy^2) - b dx dy >= -tau bounds |dx| <= sqrt(2 tau c / (ac - b^2)), same for dy with a.
+// The box is inflated (1 % + 0.01 px) so float rounding in the per-pixel test can never keep a pixel the box drops.
+__device__ __forceinline__ float2 cull_extent(float a, float b, float c, float o)
+{
+    const float inf = __int_as_float(0x7f800000);
+    if (!(o >= 1.0f / 255.0f)) return {-1.f, -1.f};  // alpha <= o < 1/255 everywhere (NaN opacity: never kept either)
+    const float det = a * c - b * b;
+    if (!(det > 0.f) || !(a > 0.f) || !(c > 0.f)) return {inf, inf};
+    const float tau = __logf(255.0f * o) * 1.01f + 0.01f;
+    const float ex = sqrtf(2.f * tau * c / det) * 1.01f + 0.01f;
+    const float ey = sqrtf(2.f * tau * a / det) * 1.01f + 0.01f;
+    if (!(ex == ex) || !(ey == ey)) return {inf, inf};
+    return {ex, ey};
+}
+
 // ------------------------------------------------------------------------------------------------ pack
 __global__ void __launch_bounds__(256)
 pack_records_kernel(int P, const int* __restrict__ radii, const float2* __restrict__ means2D,
@@ -96,24 +113,9 @@ pack_records_kernel(int P, const int* __restrict__ radii, const float2* __restri
     rec.q0 = {xy.x, xy.y, co.x, co.y};
     rec.q1 = {co.z, co.w, r, g};
     rec.q2 = {b, m[0], m[1], m[2]};
-    rec.q3 = {m[3], m[4], 0.f, 0.f};
+    const float2 ext = cull_extent(co.x, co.y, co.z, co.w);
+    rec.q3 = {m[3], m[4], ext.x, ext.y};
     records[i] = rec;
-}
-
-// Half extents of the axis-aligned box outside of which opacity * exp(power) < 1/255 for certain.
-// power = -0.5 (a dx^2 + c dy^2) - b dx dy >= -tau bounds |dx| <= sqrt(2 tau c / (ac - b^2)), same for dy with a.
-// The box is inflated (1 % + 0.01 px) so float rounding in the per-pixel test can never keep a pixel the box drops.
-__device__ __forceinline__ float2 cull_extent(float a, float b, float c, float o)
-{
-    const float inf = __int_as_float(0x7f800000);
-    if (!(o >= 1.0f / 255.0f)) return {-1.f, -1.f};  // alpha <= o < 1/255 everywhere (NaN opacity: never kept either)
-    const float det = a * c - b * b;
-    if (!(det > 0.f) || !(a > 0.f) || !(c > 0.f)) return {inf, inf};
-    const float tau = __logf(255.0f * o) * 1.01f + 0.01f;
-    const float ex = sqrtf(2.f * tau * c / det) * 1.01f + 0.01f;
-    const float ey = sqrtf(2.f * tau * a / det) * 1.01f + 0.01f;
-    if (!(ex == ex) || !(ey == ey)) return {inf, inf};
-    return {ex, ey};
 }
 
 constexpr int RENDER_THREADS = CGX_BLOCK_SIZE;
@@ -142,11 +144,14 @@ render_fwd_kernel(const uint2* __restrict__ ranges, const uint32_t* __restrict__
 
     const uint32_t horizontal_blocks = (W + CGX_BLOCK_X - 1) / CGX_BLOCK_X;
     const uint32_t block_id = blockIdx.y * horizontal_blocks + blockIdx.x;
-    const int tid = threadIdx.y * CGX_BLOCK_X + threadIdx.x;
+    const int tid = threadIdx.x;
     const int lane = tid & 31, warp = tid >> 5;
+    // warp w owns the 8x4 pixel block (w & 1, w >> 1) of the tile: compact footprints keep a small splat
+    // inside few warps, which is what the per-warp culling (and the backward's per-warp reduction) pays for
+    const uint32_t lx = (warp & 1) * 8 + (lane & 7), ly = (warp >> 1) * 4 + (lane >> 3);
 
     uint2 pix_min = {blockIdx.x * CGX_BLOCK_X, blockIdx.y * CGX_BLOCK_Y};
-    uint2 pix = {pix_min.x + threadIdx.x, pix_min.y + threadIdx.y};
+    uint2 pix = {pix_min.x + lx, pix_min.y + ly};
     uint32_t pix_id = W * pix.y + pix.x;
     float2 pixf = {(float)pix.x, (float)pix.y};
     const float2 ray = {(pixf.x - cx) / focal_x, (pixf.y - cy) / focal_y};
@@ -184,9 +189,9 @@ render_fwd_kernel(const uint2* __restrict__ ranges, const uint32_t* __restrict__
     }
     __syncthreads();
 
-    // strip of this warp: rows [sy0, sy1], columns [sx0, sx1] in pixel coordinates
-    const float sx0 = (float)pix_min.x, sx1 = (float)(pix_min.x + CGX_BLOCK_X - 1);
-    const float sy0 = (float)(pix_min.y + 2 * warp), sy1 = sy0 + 1.f;
+    // pixel block of this warp: columns [sx0, sx1], rows [sy0, sy1]
+    const float sx0 = (float)(pix_min.x + (warp & 1) * 8), sx1 = sx0 + 7.f;
+    const float sy0 = (float)(pix_min.y + (warp >> 1) * 4), sy1 = sy0 + 3.f;
 
     auto issue = [&](int batch, int buf) {
         const int progress = batch * CGX_BLOCK_SIZE + tid;
@@ -230,9 +235,8 @@ render_fwd_kernel(const uint2* __restrict__ ranges, const uint32_t* __restrict__
                 bool hit = false;
                 if (j < nb) {
                     const float4 q0 = rec[j].q0;
-                    const float4 q1 = rec[j].q1;
-                    const float2 e = cull_extent(q0.z, q0.w, q1.x, q1.y);
-                    hit = (q0.x + e.x >= sx0) && (q0.x - e.x <= sx1) && (q0.y + e.y >= sy0) && (q0.y - e.y <= sy1);
+                    const float4 q3 = rec[j].q3;
+                    hit = (q0.x + q3.z >= sx0) && (q0.x - q3.z <= sx1) && (q0.y + q3.w >= sy0) && (q0.y - q3.w <= sy1);
                 }
                 const uint32_t m = __ballot_sync(0xffffffffu, hit);
                 if (hit) my_hits[n_hits + __popc(m & ((1u << lane) - 1u))] = (uint8_t)j;
@@ -424,7 +428,7 @@ __device__ __forceinline__ float warp_reduce16(float (&v)[16], int lane)
 }
 
 template <bool CULL>
-__global__ void __launch_bounds__(RENDER_THREADS)
+__global__ void __launch_bounds__(RENDER_THREADS, 3)
 render_bwd_kernel(const uint2* __restrict__ ranges, const uint32_t* __restrict__ point_list, int W, int H, float fx,
                   float fy, const float* __restrict__ bg_color, const Record* __restrict__ records,
                   const float* __restrict__ all_map_pixels, const float* __restrict__ final_Ts,
@@ -438,11 +442,12 @@ render_bwd_kernel(const uint2* __restrict__ ranges, const uint32_t* __restrict__
     const uint32_t horizontal_blocks = (W + CGX_BLOCK_X - 1) / CGX_BLOCK_X;
     const uint32_t block_id = blockIdx.y * horizontal_blocks + blockIdx.x;
     if (!compute_locally[block_id]) return;
-    const int tid = threadIdx.y * CGX_BLOCK_X + threadIdx.x;
+    const int tid = threadIdx.x;
     const int lane = tid & 31, warp = tid >> 5;
+    const uint32_t lx = (warp & 1) * 8 + (lane & 7), ly = (warp >> 1) * 4 + (lane >> 3);   // 8x4 block per warp
 
     const uint2 pix_min = {blockIdx.x * CGX_BLOCK_X, blockIdx.y * CGX_BLOCK_Y};
-    const uint2 pix = {pix_min.x + threadIdx.x, pix_min.y + threadIdx.y};
+    const uint2 pix = {pix_min.x + lx, pix_min.y + ly};
     const uint32_t pix_id = W * pix.y + pix.x;
     const float2 pixf = {(float)pix.x, (float)pix.y};
     // double arithmetic (W * 0.5 is a double expression), narrowed to float afterwards
@@ -468,8 +473,8 @@ render_bwd_kernel(const uint2* __restrict__ ranges, const uint32_t* __restrict__
     const int my_stride = out.stride[my_term];
     const bool my_write = (lane & 1) == 0 && my_ptr != nullptr;
 
-    const float sx0 = (float)pix_min.x, sx1 = (float)(pix_min.x + CGX_BLOCK_X - 1);
-    const float sy0 = (float)(pix_min.y + 2 * warp), sy1 = sy0 + 1.f;
+    const float sx0 = (float)(pix_min.x + (warp & 1) * 8), sx1 = sx0 + 7.f;
+    const float sy0 = (float)(pix_min.y + (warp >> 1) * 4), sy1 = sy0 + 3.f;
 
     auto issue = [&](int batch, int buf) {
         const int progress = batch * CGX_BLOCK_SIZE + tid;
@@ -539,9 +544,8 @@ render_bwd_kernel(const uint2* __restrict__ ranges, const uint32_t* __restrict__
                 bool hit = false;
                 if (j < nb) {
                     const float4 q0 = rec[j].q0;
-                    const float4 q1 = rec[j].q1;
-                    const float2 e = cull_extent(q0.z, q0.w, q1.x, q1.y);
-                    hit = (q0.x + e.x >= sx0) && (q0.x - e.x <= sx1) && (q0.y + e.y >= sy0) && (q0.y - e.y <= sy1);
+                    const float4 q3 = rec[j].q3;
+                    hit = (q0.x + q3.z >= sx0) && (q0.x - q3.z <= sx1) && (q0.y + q3.w >= sy0) && (q0.y - q3.w <= sy1);
                 }
                 const uint32_t m = __ballot_sync(0xffffffffu, hit);
                 if (hit) my_hits[n_hits + __popc(m & ((1u << lane) - 1u))] = (uint8_t)j;
@@ -567,7 +571,9 @@ render_bwd_kernel(const uint2* __restrict__ ranges, const uint32_t* __restrict__
                     const float alpha = min(0.99f, con_o.w * G);
                     if (!(alpha < 1.0f / 255.0f)) {
                         valid = true;
-                        T = T / (1.f - alpha);
+                        // gradients carry a 1e-3 tolerance: one correctly rounded reciprocal serves both quotients
+                        const float inv_1ma = __frcp_rn(1.f - alpha);
+                        T = T * inv_1ma;
                         const float dchannel_dcolor = alpha * T;
                         float dL_dalpha = 0.0f;
                         const float4 q2 = rec[j].q2;
@@ -599,7 +605,7 @@ render_bwd_kernel(const uint2* __restrict__ ranges, const uint32_t* __restrict__
                         }
                         dL_dalpha *= T;
                         last_alpha = alpha;
-                        dL_dalpha += (-T_final / (1.f - alpha)) * bg_dot_dpixel;
+                        dL_dalpha += (-T_final * inv_1ma) * bg_dot_dpixel;
 
                         const float dL_dG = con_o.w * dL_dalpha;
                         const float gdx = G * d.x;
@@ -679,7 +685,7 @@ extern "C" int cgx_render_fwd(int P, int W, int H, float tanfovx, float tanfovy,
     const float focal_y = H / (2.0f * tanfovy);
     const float focal_x = W / (2.0f * tanfovx);
     const dim3 grid((W + CGX_BLOCK_X - 1) / CGX_BLOCK_X, (H + CGX_BLOCK_Y - 1) / CGX_BLOCK_Y, 1);
-    const dim3 block(CGX_BLOCK_X, CGX_BLOCK_Y, 1);
+    const dim3 block(RENDER_THREADS, 1, 1);
     const size_t smem = sizeof(FwdSmem);
     cudaError_t e;
     if (g_render_variant) {
@@ -755,7 +761,7 @@ extern "C" int cgx_render_bwd(int P, int W, int H, float tanfovx, float tanfovy,
     const float focal_y = H / (2.0f * tanfovy);
     const float focal_x = W / (2.0f * tanfovx);
     const dim3 grid((W + CGX_BLOCK_X - 1) / CGX_BLOCK_X, (H + CGX_BLOCK_Y - 1) / CGX_BLOCK_Y, 1);
-    const dim3 block(CGX_BLOCK_X, CGX_BLOCK_Y, 1);
+    const dim3 block(RENDER_THREADS, 1, 1);
     const size_t smem = sizeof(BwdSmem);
     if (g_render_variant) {
         e = cudaFuncSetAttribute(render_bwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

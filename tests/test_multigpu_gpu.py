@@ -1,0 +1,83 @@
+"""Multi-GPU equivalence (NCCL): the data-parallel step on 2 ranks must reproduce the single-GPU step.
+
+Runs as child processes, one per GPU, only where at least two GPUs are visible.  NVLS is switched off for NCCL
+in these children (plain peer transport is all the exchange needs)."""
+import os
+import socket
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parent.parent
+N_GAUSS, RES, N_CAMS = 200_000, (640, 480), 4
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, ws, port, out_dir):
+    for p in (ROOT, ROOT / "citygs-x_b200", ROOT / "tests"):
+        sys.path.insert(0, str(p))
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    import torch.distributed as dist
+
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=ws, device_id=dev)
+    try:
+        from cgx import runtime as RT
+        from cgx import synthetic as S
+
+        g, cams = S.config(2, n_gaussians=N_GAUSS, n_cameras=N_CAMS, res=RES)
+        step = RT.TrainingStep(g, cams, dev, rank=rank, world_size=ws)
+        step.run()
+        torch.cuda.synchronize()
+        grads = {k: v.grad.detach().cpu() for k, v in step.params.items()}
+        m2 = [(r.cpu(), (m.grad.cpu() if m.grad is not None else None)) for r, m in step.last]
+        torch.save({"grads": grads, "m2": m2, "ex": step.exchange_stats(),
+                    "strategies": [(s.gpu_ids, s.division_pos) for s in step._strategies]},
+                   os.path.join(out_dir, f"rank{rank}.pt"))
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_gpu_step_equals_single_gpu_step(tmp_path):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    import util
+    from cgx import runtime as RT
+    from cgx import synthetic as S
+
+    port = _free_port()
+    mp.spawn(_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    parts = [torch.load(tmp_path / f"rank{r}.pt", weights_only=False) for r in range(2)]
+
+    dev = torch.device("cuda:0")
+    g, cams = S.config(2, n_gaussians=N_GAUSS, n_cameras=N_CAMS, res=RES)
+    single = RT.TrainingStep(g, cams, dev, rank=0, world_size=1)
+    single.run()
+    torch.cuda.synchronize()
+    # 4 cameras over 2 ranks: two whole cameras each
+    assert parts[0]["strategies"] == [([0], [0, 30]), ([0], [0, 30]), ([1], [0, 30]), ([1], [0, 30])]
+    assert parts[0]["ex"]["bytes_sent_fwd"] > 0
+    for name, full in single.params.items():
+        full = full.grad.cpu()
+        merged = torch.zeros_like(full)
+        for r in range(2):
+            merged[r::2] = parts[r]["grads"][name]
+        assert util.rel_l2(merged, full) <= 1e-3, (name, util.rel_l2(merged, full))
+    # densification statistics: radii and means2D.grad of every camera land on the owning rank
+    for k in range(N_CAMS):
+        radii_full, m2_full = single.last[k][0].cpu(), single.last[k][1].grad.cpu()
+        for r in range(2):
+            radii_r, m2g_r = parts[r]["m2"][k]
+            assert torch.equal(radii_r, radii_full[r::2])
+            assert util.rel_l2(m2g_r, m2_full[r::2]) <= 1e-3
