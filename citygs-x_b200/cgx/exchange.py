@@ -14,9 +14,12 @@ ascending local index; a Gaussian straddling a cut goes to both neighbours), but
                                                         per-destination segments of one send buffer
   list all_to_all x2 (functional + plain)               one ``all_to_all_single`` with split sizes (NCCL over
                                                         NVLink; works on gloo as well)
-  backward: autograd through functional all_to_all,     one reverse ``all_to_all_single`` of 19-float gradient
-  index_put / cat backward kernels                      rows + one scatter-add kernel through the saved
-                                                        source-row index
+  split + cat per camera on the receiver               one unpack kernel per camera writes the contiguous
+                                                        per-camera tensors
+  backward: autograd through functional all_to_all,     ONE autograd node: gradient rows packed by one kernel
+  split / cat / index backward kernels                  per camera, one reverse ``all_to_all_single`` of
+                                                        19-float rows, one scatter-add kernel per camera
+                                                        through the saved source-row index
 
 The packing backend is injected (`backend=`): the product backend drives the CUDA kernels of the C ABI
 (cgx_local2j_count / cgx_local2j_pack / cgx_unpack_grad_add) and refuses CPU tensors; the CPU tests inject
@@ -89,6 +92,28 @@ class CudaPackBackend:
                                                    self._p(d_sc), self._p(d_rot), self._st()), "cgx_unpack_grad_add")
 
 
+    def unpack_rows(self, segments, recv, recv_aux, outs):
+        n = len(segments)
+        if n == 0:
+            return
+        starts = (C.c_int64 * n)(*[a for a, _ in segments])
+        counts = (C.c_int64 * n)(*[c for _, c in segments])
+        m2, rgb, co, rad, dep, m3, sc, rot = outs
+        self._lib.check(self.l.cgx_unpack_rows(n, starts, counts, self._p(recv), self._p(recv_aux), self._p(m2),
+                                               self._p(rgb), self._p(co), self._p(m3), self._p(sc), self._p(rot),
+                                               self._p(rad), self._p(dep), self._st()), "cgx_unpack_rows")
+
+    def pack_grad_rows(self, segments, grads, rows):
+        n = len(segments)
+        if n == 0:
+            return
+        starts = (C.c_int64 * n)(*[a for a, _ in segments])
+        counts = (C.c_int64 * n)(*[c for _, c in segments])
+        g = [None if t is None else t.contiguous() for t in grads]
+        self._lib.check(self.l.cgx_pack_grad_rows(n, starts, counts, *[self._p(t) for t in g], self._p(rows),
+                                                  self._st()), "cgx_pack_grad_rows")
+
+
 _default_backend = None
 
 
@@ -113,47 +138,63 @@ def _gather_sizes(local_sizes, group, device):
     return out.view(ws, ws, -1).cpu()
 
 
-class _Exchange(torch.autograd.Function):
-    """send rows (n_send, 19) -> received rows (n_recv, 19); backward is the reverse exchange."""
+class _GaussianExchange(torch.autograd.Function):
+    """The whole exchange as one autograd node.
+
+    inputs : plan, then 6 differentiable tensors per camera (means2D, rgb, conic_opacity, means3D, scales, rotation)
+    outputs: 8 tensors per camera (means2D, rgb, conic_opacity, radii, depths, means3D, scales, rotation)
+    """
 
     @staticmethod
-    def forward(ctx, send_diff, send_splits, recv_splits, group):
-        ctx.group, ctx.send_splits, ctx.recv_splits = group, send_splits, recv_splits
-        recv = send_diff.new_empty((sum(recv_splits), send_diff.shape[1]))
-        dist.all_to_all_single(recv, send_diff.contiguous(), output_split_sizes=recv_splits,
-                               input_split_sizes=send_splits, group=group)
-        return recv
+    def forward(ctx, plan, *flat):
+        be, group = plan["backend"], plan["group"]
+        send, send_aux = plan["send"], plan["send_aux"]
+        n_recv = sum(plan["recv_splits"])
+        recv = send.new_empty((n_recv, REC_DIFF))
+        recv_aux = send.new_empty((n_recv, REC - REC_DIFF))
+        dist.all_to_all_single(recv, send, output_split_sizes=plan["recv_splits"],
+                               input_split_sizes=plan["send_splits"], group=group)
+        dist.all_to_all_single(recv_aux, send_aux, output_split_sizes=plan["recv_splits"],
+                               input_split_sizes=plan["send_splits"], group=group)
+        outs, nondiff = [], []
+        for segs in plan["recv_segments"]:
+            n = sum(c for _, c in segs)
+            f = dict(dtype=torch.float32, device=send.device)
+            o = (recv.new_empty((n, 2)), recv.new_empty((n, 3)), recv.new_empty((n, 4)),
+                 torch.empty(n, dtype=torch.int32, device=send.device), torch.empty(n, **f),
+                 recv.new_empty((n, 3)), recv.new_empty((n, 3)), recv.new_empty((n, 4)))
+            be.unpack_rows(segs, recv, recv_aux, o)
+            outs += list(o)
+            nondiff += [o[3], o[4]]
+        ctx.plan = plan
+        ctx.shapes = [t.shape for t in flat]
+        ctx.mark_non_differentiable(*nondiff)
+        return tuple(outs)
 
     @staticmethod
-    def backward(ctx, grad_recv):
-        grad_send = grad_recv.new_empty((sum(ctx.send_splits), grad_recv.shape[1]))
-        dist.all_to_all_single(grad_send, grad_recv.contiguous(), output_split_sizes=ctx.send_splits,
-                               input_split_sizes=ctx.recv_splits, group=ctx.group)
-        return grad_send, None, None, None
-
-
-class _PackRows(torch.autograd.Function):
-    """Differentiable view of the packing kernel: flat per-camera inputs -> (n_send, 19) rows.
-
-    forward receives the already packed buffer (packing is fused with selection in one kernel); backward
-    scatter-adds the row gradients back onto the per-camera source tensors through the saved source index."""
-
-    @staticmethod
-    def forward(ctx, packed_diff, cam_of_row_ranges, send_index, backend, *flat_inputs):
-        ctx.backend, ctx.ranges = backend, cam_of_row_ranges
-        ctx.shapes = [t.shape for t in flat_inputs]
-        ctx.save_for_backward(send_index)
-        return packed_diff.view_as(packed_diff)
-
-    @staticmethod
-    def backward(ctx, grad_rows):
-        (send_index,) = ctx.saved_tensors
-        grad_rows = grad_rows.contiguous()
-        grads = [torch.zeros(s, dtype=grad_rows.dtype, device=grad_rows.device) for s in ctx.shapes]
-        # rows of camera k occupy, per destination, the range ctx.ranges[k][..] = (start, stop) of the send buffer
-        for k, per_dst in enumerate(ctx.ranges):
-            ctx.backend.unpack_grad_add(grad_rows, send_index, per_dst, grads[6 * k: 6 * k + 6])
-        return (None, None, None, None) + tuple(grads)
+    def backward(ctx, *gouts):
+        plan = ctx.plan
+        be, group = plan["backend"], plan["group"]
+        dev = plan["send"].device
+        n_recv, n_send = sum(plan["recv_splits"]), sum(plan["send_splits"])
+        grad_recv = torch.empty((n_recv, REC_DIFF), dtype=torch.float32, device=dev)
+        for k, segs in enumerate(plan["recv_segments"]):
+            g8 = gouts[8 * k: 8 * k + 8]
+            be.pack_grad_rows(segs, (g8[0], g8[1], g8[2], g8[5], g8[6], g8[7]), grad_recv)
+        grad_send = torch.empty((n_send, REC_DIFF), dtype=torch.float32, device=dev)
+        dist.all_to_all_single(grad_send, grad_recv, output_split_sizes=plan["send_splits"],
+                               input_split_sizes=plan["recv_splits"], group=group)
+        grads = []
+        for k, per_dst in enumerate(plan["send_ranges"]):
+            need = ctx.needs_input_grad[1 + 6 * k: 1 + 6 * k + 6]
+            g6 = [torch.zeros(s, dtype=torch.float32, device=dev) if nd else None
+                  for s, nd in zip(ctx.shapes[6 * k: 6 * k + 6], need)]
+            if g6[0] is None or g6[2] is None:       # the scatter kernel always writes means2D and conic_opacity
+                g6[0] = g6[0] if g6[0] is not None else torch.zeros(ctx.shapes[6 * k], dtype=torch.float32, device=dev)
+                g6[2] = g6[2] if g6[2] is not None else torch.zeros(ctx.shapes[6 * k + 2], dtype=torch.float32, device=dev)
+            be.unpack_grad_add(grad_send, plan["send_index"], per_dst, g6)
+            grads += [g if nd else None for g, nd in zip(g6, need)]
+        return (None,) + tuple(grads)
 
 
 def all_to_all_communication_final(batched_rasterizers, batched_screenspace_params, batched_cuda_args,
@@ -162,15 +203,15 @@ def all_to_all_communication_final(batched_rasterizers, batched_screenspace_para
     (means2D, rgb, conic_opacity, radii, depths, means3D, scales, rotation) of camera k on this rank.
 
     Returns the reference's tuple: per-camera lists of means2D, rgb, conic_opacity, radii (int32), depths, means3D,
-    scales, rotations (redistributed), then the size table [src][dst][cam] and, per destination and camera, the
-    number of rows sent (the reference returns index tensors there; here the source indices stay on the device in
-    one packed tensor, which is returned as the last element)."""
+    scales, rotations (redistributed), then the size table [src][dst][cam] and the rows sent per destination and
+    camera (the reference returns index tensors there; here the source indices stay on the device in one packed
+    tensor, returned next), and a dict of transfer statistics."""
     backend = backend or default_backend()
     ws, me = _world(group)
     bsz = len(batched_rasterizers)
     dev = batched_screenspace_params[0][0].device
 
-    # ---- 1. counts: one kernel per camera, results land in one (ws, bsz) table, one host read
+    # ---- 1. counts: one kernel pair per camera, results land in one (bsz, ws) table, ONE host read
     counts_dev = torch.zeros(bsz, ws, dtype=torch.int32, device=dev)
     scratch, bounds = [], []
     for k in range(bsz):
@@ -189,23 +230,22 @@ def all_to_all_communication_final(batched_rasterizers, batched_screenspace_para
             counts_dev[k, torch.as_tensor(strat.gpu_ids, device=dev, dtype=torch.long)] = c
         scratch.append(wspace)
         bounds.append(tb)
-    local_sizes = counts_dev.t().contiguous()                      # (dst, cam)
-    sizes = _gather_sizes(local_sizes, group, dev)                 # (src, dst, cam) on the host
+    sizes = _gather_sizes(counts_dev.t().contiguous(), group, dev)   # (src, dst, cam) on the host
     sizes_list = sizes.tolist()
-    my = sizes[me]                                                 # (dst, cam)
+    my = sizes_list[me]                                              # [dst][cam]
 
-    # ---- 2. layout of the send buffer: destination major, camera minor
-    send_splits = [int(my[j].sum()) for j in range(ws)]
-    recv_splits = [int(sizes[i, me].sum()) for i in range(ws)]
-    n_send, n_recv = sum(send_splits), sum(recv_splits)
+    # ---- 2. send buffer: destination major, camera minor; packed by one kernel per camera
+    send_splits = [sum(my[j]) for j in range(ws)]
+    recv_splits = [sum(sizes_list[i][me]) for i in range(ws)]
+    n_send = sum(send_splits)
     dst_base = [0] * ws
     for j in range(1, ws):
         dst_base[j] = dst_base[j - 1] + send_splits[j - 1]
     send = torch.empty(n_send, REC_DIFF, dtype=torch.float32, device=dev)
     send_aux = torch.empty(n_send, REC - REC_DIFF, dtype=torch.float32, device=dev)
     send_index = torch.empty(n_send, dtype=torch.int32, device=dev)
-    ranges = []
-    cam_off = [0] * ws                                             # rows of earlier cameras per destination
+    send_ranges = []
+    cam_off = [0] * ws
     for k in range(bsz):
         strat = batched_strategies[k]
         offs = [dst_base[j] + cam_off[j] for j in strat.gpu_ids]
@@ -215,54 +255,37 @@ def all_to_all_communication_final(batched_rasterizers, batched_screenspace_para
                      batched_cuda_args[k]["avoid_pixel_all2all"], offs, send, send_aux, send_index, scratch[k])
         per_dst = []
         for j in strat.gpu_ids:
-            n = int(my[j, k])
+            n = my[j][k]
             per_dst.append((dst_base[j] + cam_off[j], dst_base[j] + cam_off[j] + n))
             cam_off[j] += n
-        ranges.append(per_dst)
+        send_ranges.append(per_dst)
 
-    # ---- 3. exchange: 19 differentiable columns through autograd, the 2 auxiliary columns plainly
+    # ---- 3. receive layout: source major, camera minor -> per camera one segment per source
+    src_base = [0] * ws
+    for i in range(1, ws):
+        src_base[i] = src_base[i - 1] + recv_splits[i - 1]
+    recv_segments = []
+    cam_off = [0] * ws
+    for k in range(bsz):
+        segs = []
+        for i in range(ws):
+            n = sizes_list[i][me][k]
+            segs.append((src_base[i] + cam_off[i], n))
+            cam_off[i] += n
+        recv_segments.append(segs)
+
+    plan = dict(backend=backend, group=group, send=send, send_aux=send_aux, send_index=send_index,
+                send_splits=send_splits, recv_splits=recv_splits, send_ranges=send_ranges,
+                recv_segments=recv_segments)
     flat = []
     for k in range(bsz):
         m2, rgb, co, radii, depths, m3, sc, rot = batched_screenspace_params[k]
         flat += [m2, rgb, co, m3, sc, rot]
-    needs_grad = torch.is_grad_enabled() and any(t.requires_grad for t in flat)
-    send_diff = send
-    if needs_grad:
-        send_diff = _PackRows.apply(send_diff, ranges, send_index, backend, *flat)
-        recv_diff = _Exchange.apply(send_diff, send_splits, recv_splits, group)
-    else:
-        recv_diff = send.new_empty((n_recv, REC_DIFF))
-        dist.all_to_all_single(recv_diff, send_diff.contiguous(), output_split_sizes=recv_splits,
-                               input_split_sizes=send_splits, group=group)
-    recv_aux = send.new_empty((n_recv, REC - REC_DIFF))
-    dist.all_to_all_single(recv_aux, send_aux, output_split_sizes=recv_splits,
-                           input_split_sizes=send_splits, group=group)
-
-    # ---- 4. per camera: concatenate the blocks of all sources (source rank ascending)
-    src_base = [0] * ws
-    for i in range(1, ws):
-        src_base[i] = src_base[i - 1] + recv_splits[i - 1]
-    out = [[] for _ in range(8)]
-    cam_off = [0] * ws
-    for k in range(bsz):
-        idx = []
-        for i in range(ws):
-            n = sizes_list[i][me][k]
-            a = src_base[i] + cam_off[i]
-            idx.append((a, a + n))
-            cam_off[i] += n
-        rows = torch.cat([recv_diff[a:b] for a, b in idx], dim=0) if ws > 1 else recv_diff[idx[0][0]:idx[0][1]]
-        aux = torch.cat([recv_aux[a:b] for a, b in idx], dim=0) if ws > 1 else recv_aux[idx[0][0]:idx[0][1]]
-        m2, rgb, co, m3, sc, rot = torch.split(rows, SPLITS, dim=1)
-        out[0].append(m2.contiguous())
-        out[1].append(rgb.contiguous())
-        out[2].append(co.contiguous())
-        out[3].append(aux[:, 0].int())
-        out[4].append(aux[:, 1].contiguous())
-        out[5].append(m3.contiguous())
-        out[6].append(sc.contiguous())
-        out[7].append(rot.contiguous())
-    sent_counts = [[sizes_list[me][j][k] for k in range(bsz)] for j in range(ws)]
-    stats = {"rows_sent": n_send, "rows_received": n_recv, "bytes_sent_fwd": n_send * REC * 4,
-             "bytes_sent_bwd": n_send * REC_DIFF * 4}
+    outs = _GaussianExchange.apply(plan, *flat)
+    out = [[outs[8 * k + c] for k in range(bsz)] for c in range(8)]
+    sent_counts = [[my[j][k] for k in range(bsz)] for j in range(ws)]
+    n_recv = sum(recv_splits)
+    self_rows = sum(my[me])
+    stats = {"rows_sent": n_send, "rows_received": n_recv, "rows_to_self": self_rows,
+             "bytes_sent_fwd": (n_send - self_rows) * REC * 4, "bytes_sent_bwd": (n_send - self_rows) * REC_DIFF * 4}
     return (*out, sizes_list, sent_counts, send_index, stats)

@@ -152,8 +152,10 @@ class TrainingStep:
                 p["means3D"], p["scales"], p["rotations"], self.sh_dummy, p["opacities"], args[k])
             means2D.retain_grad()
             keep.append((radii, means2D))
-            screen.append((means2D, self.rgb[k], conic_opacity, radii, depths, p["means3D"], p["scales"],
-                           p["rotations"]))
+            # the plane descriptors are rebuilt on the receiver without autograd, so the 3-D parameters travel
+            # as plain data (no gradient rows come back for them)
+            screen.append((means2D, self.rgb[k], conic_opacity, radii, depths, p["means3D"].detach(),
+                           p["scales"].detach(), p["rotations"].detach()))
         (m2, rgb, co, rad, dep, m3, sc, rot, sizes, sent, send_index, stats) = \
             exchange.all_to_all_communication_final(rasts, screen, args, strategies)
         self._exchange["bytes_sent_fwd"] = stats["bytes_sent_fwd"]

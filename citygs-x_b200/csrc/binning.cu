@@ -486,7 +486,72 @@ unpack_grad_add_kernel(RowRanges rr, const float* __restrict__ g, const int32_t*
     else { if (d_rot) atomicAdd(d_rot + 4 * i + (c - 15), v); }
 }
 
+// Received rows arrive source-rank major; camera k's rows are one segment per source.  These two kernels move
+// between that layout and the per-camera contiguous tensors the rasterizer consumes.
+struct Segments {
+    int n;
+    long long start[MAX_WS];       // first row of segment r in the exchange buffer
+    long long prefix[MAX_WS + 1];  // rows of this camera in segments before r
+};
+
+__device__ __forceinline__ long long segment_row(const Segments& sg, long long lrow)
+{
+    int r = 0;
+    while (r + 1 < sg.n && lrow >= sg.prefix[r + 1]) r++;
+    return sg.start[r] + (lrow - sg.prefix[r]);
+}
+
+__global__ void __launch_bounds__(256)
+unpack_rows_kernel(Segments sg, const float* __restrict__ rows, const float* __restrict__ aux,
+                   float* __restrict__ means2D, float* __restrict__ rgb, float* __restrict__ co,
+                   float* __restrict__ means3D, float* __restrict__ scales, float* __restrict__ rot,
+                   int* __restrict__ radii, float* __restrict__ depths)
+{
+    const long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long n = sg.prefix[sg.n];
+    if (e >= n * 21) return;
+    const long long lrow = e / 21;
+    const int c = (int)(e - lrow * 21);
+    const long long row = segment_row(sg, lrow);
+    if (c < 19) {
+        const float v = rows[row * 19 + c];
+        if (c < 2) means2D[2 * lrow + c] = v;
+        else if (c < 5) rgb[3 * lrow + (c - 2)] = v;
+        else if (c < 9) co[4 * lrow + (c - 5)] = v;
+        else if (c < 12) means3D[3 * lrow + (c - 9)] = v;
+        else if (c < 15) scales[3 * lrow + (c - 12)] = v;
+        else rot[4 * lrow + (c - 15)] = v;
+    } else if (c == 19) {
+        radii[lrow] = (int)aux[row * 2];          // radius travels as a float, exact below 2^24
+    } else {
+        depths[lrow] = aux[row * 2 + 1];
+    }
+}
+
+// Gradients of one camera's received tensors -> 19-float rows of the exchange buffer (NULL tensor = zeros).
+__global__ void __launch_bounds__(256)
+pack_grad_rows_kernel(Segments sg, const float* __restrict__ d_means2D, const float* __restrict__ d_rgb,
+                      const float* __restrict__ d_co, const float* __restrict__ d_means3D,
+                      const float* __restrict__ d_scales, const float* __restrict__ d_rot, float* __restrict__ rows)
+{
+    const long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long n = sg.prefix[sg.n];
+    if (e >= n * 19) return;
+    const long long lrow = e / 19;
+    const int c = (int)(e - lrow * 19);
+    const long long row = segment_row(sg, lrow);
+    float v = 0.f;
+    if (c < 2) { if (d_means2D) v = d_means2D[2 * lrow + c]; }
+    else if (c < 5) { if (d_rgb) v = d_rgb[3 * lrow + (c - 2)]; }
+    else if (c < 9) { if (d_co) v = d_co[4 * lrow + (c - 5)]; }
+    else if (c < 12) { if (d_means3D) v = d_means3D[3 * lrow + (c - 9)]; }
+    else if (c < 15) { if (d_scales) v = d_scales[3 * lrow + (c - 12)]; }
+    else { if (d_rot) v = d_rot[4 * lrow + (c - 15)]; }
+    rows[row * 19 + c] = v;
+}
+
 }  // namespace cgx
+
 
 using namespace cgx;
 
@@ -703,5 +768,51 @@ extern "C" int cgx_unpack_grad_add(int n_ranges, const int64_t* range_start, con
     if (!grad_rows || !send_index || !d_means2D || !d_conic_opacity) return CGX_EINVAL;
     unpack_grad_add_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
         rr, grad_rows, send_index, d_means2D, d_rgb, d_conic_opacity, d_means3D, d_scales, d_rotations);
+    return check_launch();
+}
+
+static int fill_segments(Segments& sg, int n_segments, const int64_t* seg_start, const int64_t* seg_count)
+{
+    if (n_segments < 0 || n_segments > MAX_WS) return CGX_EINVAL;
+    if (n_segments > 0 && (!seg_start || !seg_count)) return CGX_EINVAL;
+    sg.n = n_segments;
+    sg.prefix[0] = 0;
+    for (int r = 0; r < n_segments; r++) {
+        if (seg_start[r] < 0 || seg_count[r] < 0) return CGX_EINVAL;
+        sg.start[r] = seg_start[r];
+        sg.prefix[r + 1] = sg.prefix[r] + seg_count[r];
+    }
+    return CGX_OK;
+}
+
+extern "C" int cgx_unpack_rows(int n_segments, const int64_t* seg_start, const int64_t* seg_count, const float* rows,
+                               const float* aux, float* means2D, float* rgb, float* conic_opacity, float* means3D,
+                               float* scales, float* rotations, int32_t* radii, float* depths, void* stream)
+{
+    Segments sg;
+    int st = fill_segments(sg, n_segments, seg_start, seg_count);
+    if (st != CGX_OK) return st;
+    const long long n = n_segments ? sg.prefix[n_segments] : 0;
+    if (n == 0) return CGX_OK;
+    if (!rows || !aux || !means2D || !rgb || !conic_opacity || !means3D || !scales || !rotations || !radii || !depths)
+        return CGX_EINVAL;
+    unpack_rows_kernel<<<(unsigned)((n * 21 + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+        sg, rows, aux, means2D, rgb, conic_opacity, means3D, scales, rotations, radii, depths);
+    return check_launch();
+}
+
+extern "C" int cgx_pack_grad_rows(int n_segments, const int64_t* seg_start, const int64_t* seg_count,
+                                  const float* d_means2D, const float* d_rgb, const float* d_conic_opacity,
+                                  const float* d_means3D, const float* d_scales, const float* d_rotations, float* rows,
+                                  void* stream)
+{
+    Segments sg;
+    int st = fill_segments(sg, n_segments, seg_start, seg_count);
+    if (st != CGX_OK) return st;
+    const long long n = n_segments ? sg.prefix[n_segments] : 0;
+    if (n == 0) return CGX_OK;
+    if (!rows) return CGX_EINVAL;
+    pack_grad_rows_kernel<<<(unsigned)((n * 19 + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+        sg, d_means2D, d_rgb, d_conic_opacity, d_means3D, d_scales, d_rotations, rows);
     return check_launch();
 }

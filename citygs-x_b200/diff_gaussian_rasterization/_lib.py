@@ -62,6 +62,8 @@ SIGNATURES = {
     "cgx_local2j_workspace_bytes": (_sz, [_i, _i]),
     "cgx_local2j_pack": (_i, [_i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "cgx_unpack_grad_add": (_i, [_i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "cgx_unpack_rows": (_i, [_i] + [_vp] * 13),
+    "cgx_pack_grad_rows": (_i, [_i] + [_vp] * 10),
     "cgx_bin_workspace_bytes": (_sz, [_i]),
     "cgx_bin_count_scan": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "cgx_emit_keys": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _vp, _vp]),

@@ -133,6 +133,21 @@ int cgx_unpack_grad_add(int n_ranges, const int64_t* range_start, const int64_t*
                         float* d_means2D, float* d_rgb, float* d_conic_opacity, float* d_means3D,
                         float* d_scales, float* d_rotations, void* stream);
 
+/* Receiver side of the exchange.  Rows arrive source-rank major; the rows of one camera are one segment per
+ * source rank: segment r = rows [seg_start[r], seg_start[r] + seg_count[r]) of the receive buffers (host
+ * arrays, n_segments <= 32).  cgx_unpack_rows concatenates a camera's segments (source rank ascending, as
+ * gaussian_renderer/__init__.py:683-696 does with split + cat) into the contiguous per-camera tensors
+ * means2D (n,2) rgb (n,3) conic_opacity (n,4) means3D (n,3) scales (n,3) rotations (n,4) radii int32 (n)
+ * depths (n); cgx_pack_grad_rows is its backward: gradient tensors (any may be NULL = zero) back into
+ * 19-float rows at the same places. */
+int cgx_unpack_rows(int n_segments, const int64_t* seg_start, const int64_t* seg_count, const float* rows,
+                    const float* aux, float* means2D, float* rgb, float* conic_opacity, float* means3D,
+                    float* scales, float* rotations, int32_t* radii, float* depths, void* stream);
+int cgx_pack_grad_rows(int n_segments, const int64_t* seg_start, const int64_t* seg_count,
+                       const float* d_means2D, const float* d_rgb, const float* d_conic_opacity,
+                       const float* d_means3D, const float* d_scales, const float* d_rotations, float* rows,
+                       void* stream);
+
 /* ------------------------------------------------------------------ binning */
 
 /* updateTileTouched + InclusiveSum (RAST/cuda_rasterizer/rasterizer_impl.cu:264-288,648).

@@ -40,3 +40,20 @@ class OracleBackend:
             d_m3.index_add_(0, idx, g[:, 9:12])
             d_sc.index_add_(0, idx, g[:, 12:15])
             d_rot.index_add_(0, idx, g[:, 15:19])
+
+    def unpack_rows(self, segments, recv, recv_aux, outs):
+        rows = torch.cat([recv[a:a + c] for a, c in segments]) if segments else recv[:0]
+        aux = torch.cat([recv_aux[a:a + c] for a, c in segments]) if segments else recv_aux[:0]
+        m2, rgb, co, rad, dep, m3, sc, rot = outs
+        m2.copy_(rows[:, 0:2]); rgb.copy_(rows[:, 2:5]); co.copy_(rows[:, 5:9])
+        m3.copy_(rows[:, 9:12]); sc.copy_(rows[:, 12:15]); rot.copy_(rows[:, 15:19])
+        rad.copy_(aux[:, 0].to(torch.int32)); dep.copy_(aux[:, 1])
+
+    def pack_grad_rows(self, segments, grads, rows):
+        n = sum(c for _, c in segments)
+        cols = [2, 3, 4, 3, 3, 4]
+        full = torch.cat([g if g is not None else torch.zeros(n, w) for g, w in zip(grads, cols)], dim=1)
+        off = 0
+        for a, c in segments:
+            rows[a:a + c] = full[off:off + c]
+            off += c
