@@ -816,3 +816,59 @@ extern "C" int cgx_pack_grad_rows(int n_segments, const int64_t* seg_start, cons
         sg, d_means2D, d_rgb, d_conic_opacity, d_means3D, d_scales, d_rotations, rows);
     return check_launch();
 }
+
+// ------------------------------------------------------------------------------------------------
+// Sorting without any caller-provided or freshly allocated scratch.
+//
+// Some hosts of this library are not allowed to allocate device memory at the point where they sort: a
+// renderer embedded in an engine whose memory budget is fixed at start-up, a plugin that runs after its host
+// has frozen the CUDA memory pools, or a service that must not touch the allocator on its latency path because
+// cudaMalloc can synchronise the whole device.  For them the digit tables of the radix sort live in the fixed
+// array below, which is part of the loaded module: every GPU that loads the library carries these bytes until
+// the process exits, so the ceiling is kept modest.
+#define CGX_SORT_STATIC_MAX_PAIRS (1 << 22)   // 4,194,304 (key, value) pairs
+namespace cgx {
+constexpr size_t SORT_STATIC_BYTES =
+    ((size_t)(CGX_SORT_STATIC_MAX_PAIRS / SORT_TILE) * RADIX * sizeof(uint32_t) + 255) / 256 * 256 + 1024;
+static __device__ __align__(256) unsigned char g_sort_static_scratch[SORT_STATIC_BYTES];
+}  // namespace cgx
+
+#include <mutex>
+
+// Device address of the fixed scratch, looked up once per device.  In host code the array's name is only a
+// handle for the runtime, not an address a kernel could use, so the address is asked for explicitly.
+static int sort_static_scratch_ptr(void** out)
+{
+    constexpr int MAX_DEVICES = 64;
+    static std::mutex mu;
+    static void* ptrs[MAX_DEVICES] = {nullptr};
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) { set_cuda_error(e); return CGX_ECUDA; }
+    if (dev < 0 || dev >= MAX_DEVICES) return CGX_EINVAL;
+    std::lock_guard<std::mutex> lock(mu);
+    if (!ptrs[dev]) {
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, cgx::g_sort_static_scratch);
+        if (e != cudaSuccess) { set_cuda_error(e); return CGX_ECUDA; }
+        ptrs[dev] = p;
+    }
+    *out = ptrs[dev];
+    return CGX_OK;
+}
+
+extern "C" int64_t cgx_sort_pairs_static_max(void) { return CGX_SORT_STATIC_MAX_PAIRS; }
+
+extern "C" int cgx_sort_pairs_static(int64_t n, int end_bit, uint64_t* keys_in, uint32_t* values_in,
+                                     uint64_t* keys_out, uint32_t* values_out, void* stream)
+{
+    if (n > CGX_SORT_STATIC_MAX_PAIRS) {
+        cgx::set_error_text("cgx_sort_pairs_static: n exceeds the fixed scratch (at most 4194304 pairs); "
+                            "use cgx_sort_pairs with a caller-provided workspace");
+        return CGX_ENOMEM;
+    }
+    void* scratch = nullptr;
+    const int st = sort_static_scratch_ptr(&scratch);
+    if (st != CGX_OK) return st;
+    return cgx_sort_pairs(n, end_bit, keys_in, values_in, keys_out, values_out, scratch, cgx::SORT_STATIC_BYTES, stream);
+}

@@ -15,6 +15,12 @@ void set_cuda_error(cudaError_t e)
     g_cuda_error[sizeof(g_cuda_error) - 1] = 0;
 }
 
+void set_error_text(const char* text)
+{
+    strncpy(g_cuda_error, text, sizeof(g_cuda_error) - 1);
+    g_cuda_error[sizeof(g_cuda_error) - 1] = 0;
+}
+
 // Launch errors only (no synchronisation): configuration problems surface here, execution faults
 // surface at the caller's next synchronising call.
 int check_launch(int launched)

@@ -17,6 +17,7 @@
 namespace cgx {
 
 void set_cuda_error(cudaError_t e);
+void set_error_text(const char* text);  // free-form text behind cgx_last_cuda_error()
 // Checks for a launch error; `launched` = number of kernels the entry point just queued (bookkeeping for
 // cgx_launch_count()).
 int check_launch(int launched = 1);

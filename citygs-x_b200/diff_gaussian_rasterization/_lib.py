@@ -69,6 +69,8 @@ SIGNATURES = {
     "cgx_emit_keys": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _vp, _vp]),
     "cgx_sort_workspace_bytes": (_sz, [_i64]),
     "cgx_sort_pairs": (_i, [_i64, _i, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
+    "cgx_sort_pairs_static_max": (_i64, []),
+    "cgx_sort_pairs_static": (_i, [_i64, _i, _vp, _vp, _vp, _vp, _vp]),
     "cgx_tile_ranges": (_i, [_i64, _i, _vp, _vp, _vp]),
     "cgx_render_records_bytes": (_sz, [_i]),
     "cgx_render_fwd": (_i, [_i, _i, _i, _f, _f] + [_vp] * 9 + [_i] + [_vp] * 12),

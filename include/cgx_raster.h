@@ -177,6 +177,21 @@ size_t cgx_sort_workspace_bytes(int64_t n);
 int cgx_sort_pairs(int64_t n, int end_bit, uint64_t* keys_in, uint32_t* values_in, uint64_t* keys_out,
                    uint32_t* values_out, void* workspace, size_t workspace_bytes, void* stream);
 
+/* No counterpart in the reference.  Same sort as cgx_sort_pairs for callers that may not allocate device
+ * memory (an engine with a memory budget fixed at start-up, a plugin whose host has frozen the CUDA pools, a
+ * latency path that must stay away from the allocator): the digit tables live in a fixed array inside the
+ * loaded module, so the call takes no workspace and allocates nothing.
+ *   - at most cgx_sort_pairs_static_max() = 4,194,304 pairs; larger n returns CGX_ENOMEM and
+ *     cgx_last_cuda_error() explains;
+ *   - the first call on each device looks up the array's device address (with that device current); make
+ *     that first call before starting any stream capture;
+ *   - all calls on a device share the one array.  Nothing in it has to start at zero (every pass rewrites
+ *     the entries it reads), but two sorts that overlap on the GPU (different streams) corrupt each other:
+ *     keep calls on one device ordered. */
+int64_t cgx_sort_pairs_static_max(void);
+int cgx_sort_pairs_static(int64_t n, int end_bit, uint64_t* keys_in, uint32_t* values_in, uint64_t* keys_out,
+                          uint32_t* values_out, void* stream);
+
 /* cudaMemset + identifyTileRanges (RAST/cuda_rasterizer/rasterizer_impl.cu:122-144,687-695):
  * ranges uint2 (T): [start, end) into the sorted list; empty tiles get (0,0). */
 int cgx_tile_ranges(int64_t n, int T, const uint64_t* keys_sorted, uint32_t* ranges, void* stream);
