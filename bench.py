@@ -184,6 +184,7 @@ def main():
     dev = torch.device("cuda", local_rank)
     if world > 1:
         import torch.distributed as dist
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")   # plain peer stores only, no multicast objects
         dist.init_process_group("nccl", device_id=dev)
     assert world == a.gpus or world == 1, "launch with torchrun --nproc-per-node N for --gpus N"
 

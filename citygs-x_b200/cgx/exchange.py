@@ -21,6 +21,15 @@ ascending local index; a Gaussian straddling a cut goes to both neighbours), but
                                                         19-float rows, one scatter-add kernel per camera
                                                         through the saved source-row index
 
+Two transports share the planning code.  ``collective`` (any backend): pack kernel -> ``all_to_all_single``
+-> unpack kernel, as tabulated above.  ``p2p`` (NCCL groups inside one NVLink/NVSwitch domain, the default there):
+the ranks' receive arenas are symmetric memory mapped into every peer, and ONE kernel per camera does selection,
+packing and transport by storing each selected row straight into the final per-camera tensors of the rank that
+renders it (`cgx_local2j_pack_p2p`); the backward stores gradient rows straight into the source rank's staging
+buffer (`cgx_pack_grad_rows_to`).  Stream-ordered device barriers (symmetric-memory signal pads) order writers
+and readers; no send buffer, no collective, no unpack.  Tensors returned in this mode are views of the arena and
+stay valid until the next exchange of the same group.
+
 The packing backend is injected (`backend=`): the product backend drives the CUDA kernels of the C ABI
 (cgx_local2j_count / cgx_local2j_pack / cgx_unpack_grad_add) and refuses CPU tensors; the CPU tests inject
 their own checker backend to exercise this module's host logic on gloo.
@@ -114,6 +123,38 @@ class CudaPackBackend:
                                                   self._st()), "cgx_pack_grad_rows")
 
 
+    def pack_p2p(self, params, tile_bounds, H, W, avoid, dsts, row_offsets, send_index, workspace):
+        """dsts: per destination column a tuple (8 device pointers, first_row)."""
+        means2D, rgb, conic_opacity, radii, depths, means3D, scales, rotation = [t.contiguous() for t in params]
+        P, ws = means2D.shape[0], tile_bounds.numel() - 1
+
+        class Dst(C.Structure):
+            _fields_ = [(n, C.c_void_p) for n in ("means2D", "rgb", "conic_opacity", "means3D", "scales",
+                                                  "rotations", "radii", "depths")] + [("first_row", C.c_int64)]
+
+        arr = (Dst * ws)()
+        for j, (ptrs, first) in enumerate(dsts):
+            for name, p in zip(("means2D", "rgb", "conic_opacity", "means3D", "scales", "rotations", "radii",
+                                "depths"), ptrs):
+                setattr(arr[j], name, p)
+            arr[j].first_row = first
+        offs = (C.c_int64 * ws)(*[int(o) for o in row_offsets])
+        self._lib.check(self.l.cgx_local2j_pack_p2p(
+            P, H, W, ws, self._p(means2D), self._p(rgb), self._p(conic_opacity), self._p(means3D), self._p(scales),
+            self._p(rotation), self._p(radii), self._p(depths), self._p(tile_bounds), int(avoid), arr, offs,
+            self._p(send_index), self._p(workspace), workspace.numel(), self._st()), "cgx_local2j_pack_p2p")
+
+    def pack_grad_rows_to(self, seg_ptrs, seg_counts, grads):
+        n = len(seg_ptrs)
+        if n == 0 or sum(seg_counts) == 0:
+            return
+        ptrs = (C.c_void_p * n)(*seg_ptrs)
+        counts = (C.c_int64 * n)(*seg_counts)
+        g = [None if t is None else t.contiguous() for t in grads]
+        self._lib.check(self.l.cgx_pack_grad_rows_to(n, ptrs, counts, *[self._p(t) for t in g], self._st()),
+                        "cgx_pack_grad_rows_to")
+
+
 _default_backend = None
 
 
@@ -197,8 +238,166 @@ class _GaussianExchange(torch.autograd.Function):
         return (None,) + tuple(grads)
 
 
+
+def _align_up(v, a=256):
+    return (v + a - 1) // a * a
+
+
+_CAM_FIELDS = (("means2D", 8), ("rgb", 12), ("conic_opacity", 16), ("means3D", 12), ("scales", 12), ("rotations", 16),
+               ("radii", 4), ("depths", 4))
+
+
+def _camera_layout(n):
+    """Byte offsets of the eight per-camera tensors of n rows inside an arena region, and the region size."""
+    offs, cur = [], 0
+    for _, width in _CAM_FIELDS:
+        offs.append(cur)
+        cur = _align_up(cur + n * width)
+    return offs, cur
+
+
+class PeerArena:
+    """Symmetric-memory receive arena (forward rows) and gradient staging buffer (backward rows) of one group."""
+
+    def __init__(self, group, device):
+        import torch.distributed._symmetric_memory as symm
+
+        self._symm = symm
+        self.group = group if group is not None else dist.group.WORLD
+        self.dev = device
+        self.recv = self.grad = None
+        self.recv_hdl = self.grad_hdl = None
+        self.ws, self.me = dist.get_world_size(self.group), dist.get_rank(self.group)
+        # flag words for the stream-ordered barrier: zeroed before any rank can signal
+        self.flags = symm.empty(64, dtype=torch.int32, device=device)
+        self.flags.zero_()
+        torch.cuda.synchronize(device)
+        self.flags_hdl = symm.rendezvous(self.flags, self.group)
+        dist.barrier(group=self.group)
+        self.epoch = 0
+        self._flag_ptrs = (C.c_void_p * self.ws)(*[int(p) for p in self.flags_hdl.buffer_ptrs])
+
+    def _alloc(self, nbytes):
+        nbytes = _align_up(int(nbytes * 1.25) + (1 << 20), 2 << 20)
+        t = self._symm.empty(nbytes, dtype=torch.uint8, device=self.dev)
+        return t, self._symm.rendezvous(t, self.group)
+
+    def ensure(self, recv_bytes, grad_bytes):
+        """Grow (collectively: every rank passes the same numbers) so that every rank's arenas hold these sizes."""
+        if self.recv is None or self.recv.numel() < recv_bytes:
+            self.recv, self.recv_hdl = self._alloc(recv_bytes)
+        if self.grad is None or self.grad.numel() < grad_bytes:
+            self.grad, self.grad_hdl = self._alloc(grad_bytes)
+
+    def barrier(self):
+        """Stream-ordered barrier over the group: work queued before it on every rank is complete after it."""
+        from diff_gaussian_rasterization import _lib
+
+        self.epoch += 1
+        _lib.check(_lib.lib().cgx_peer_barrier(self.ws, self.me, self._flag_ptrs, self.epoch,
+                                               C.c_void_p(torch.cuda.current_stream().cuda_stream)),
+                   "cgx_peer_barrier")
+
+
+_arenas = {}
+
+
+def _arena_for(group, device):
+    key = (id(group), device)
+    if key not in _arenas:
+        _arenas[key] = PeerArena(group, device)
+    return _arenas[key]
+
+
+class _GaussianExchangeP2P(torch.autograd.Function):
+    """Same contract as _GaussianExchange, transport by direct stores into peer memory."""
+
+    @staticmethod
+    def forward(ctx, plan, *flat):
+        be, arena = plan["backend"], plan["arena"]
+        me, ws, sizes = plan["me"], plan["ws"], plan["sizes"]
+        bsz = len(plan["strategies"])
+        arena.barrier()                       # every rank is done with the previous contents of the arenas
+        for k in range(bsz):
+            strat = plan["strategies"][k]
+            dsts = []
+            for j in strat.gpu_ids:
+                base = arena.recv_hdl.buffer_ptrs[j] + plan["cam_base"][j][k]
+                offs, _ = _camera_layout(plan["n_recv"][j][k])
+                first = sum(sizes[i][j][k] for i in range(me))
+                dsts.append(([base + o for o in offs], first))
+            be.pack_p2p(plan["params"][k], plan["bounds"][k], plan["hw"][k][0], plan["hw"][k][1], plan["avoid"][k],
+                        dsts, plan["send_offsets"][k], plan["send_index"], plan["scratch"][k])
+        arena.barrier()                       # every rank's rows have landed
+        outs, nondiff = [], []
+        for k in range(bsz):
+            n = plan["n_recv"][me][k]
+            offs, _ = _camera_layout(n)
+            base = plan["cam_base"][me][k]
+            ts = []
+            for (name, width), o in zip(_CAM_FIELDS, offs):
+                raw = arena.recv[base + o: base + o + n * width]
+                if name == "radii":
+                    ts.append(raw.view(torch.int32))
+                elif name == "depths":
+                    ts.append(raw.view(torch.float32))
+                else:
+                    ts.append(raw.view(torch.float32).view(n, width // 4))
+            m2, rgb, co, m3, sc, rot, rad, dep = ts
+            outs += [m2, rgb, co, rad, dep, m3, sc, rot]
+            nondiff += [rad, dep]
+        ctx.plan = plan
+        ctx.shapes = [t.shape for t in flat]
+        ctx.mark_non_differentiable(*nondiff)
+        return tuple(outs)
+
+    @staticmethod
+    def backward(ctx, *gouts):
+        plan = ctx.plan
+        be, arena = plan["backend"], plan["arena"]
+        me, ws, sizes = plan["me"], plan["ws"], plan["sizes"]
+        dev = arena.dev
+        bsz = len(plan["strategies"])
+        for k in range(bsz):
+            g8 = gouts[8 * k: 8 * k + 8]
+            ptrs, counts = [], []
+            for i in range(ws):
+                n = sizes[i][me][k]
+                # position of segment (i -> me, camera k) in rank i's send order: destination major, camera minor
+                row = sum(sum(sizes[i][j]) for j in range(me)) + sum(sizes[i][me][:k])
+                ptrs.append(arena.grad_hdl.buffer_ptrs[i] + row * REC_DIFF * 4)
+                counts.append(n)
+            be.pack_grad_rows_to(ptrs, counts, (g8[0], g8[1], g8[2], g8[5], g8[6], g8[7]))
+        arena.barrier()                       # every rank's gradient rows have landed in their owners' buffers
+        n_send = plan["n_send"]
+        grad_send = arena.grad[: n_send * REC_DIFF * 4].view(torch.float32).view(n_send, REC_DIFF)
+        grads = []
+        for k, per_dst in enumerate(plan["send_ranges"]):
+            need = ctx.needs_input_grad[1 + 6 * k: 1 + 6 * k + 6]
+            g6 = [torch.zeros(s, dtype=torch.float32, device=dev) if nd else None
+                  for s, nd in zip(ctx.shapes[6 * k: 6 * k + 6], need)]
+            for c in (0, 2):                  # the scatter kernel always writes means2D and conic_opacity
+                if g6[c] is None:
+                    g6[c] = torch.zeros(ctx.shapes[6 * k + c], dtype=torch.float32, device=dev)
+            be.unpack_grad_add(grad_send, plan["send_index"], per_dst, g6)
+            grads += [g if nd else None for g, nd in zip(g6, need)]
+        return (None,) + tuple(grads)
+
+
+def _pick_transport(transport, group, dev, backend):
+    if transport is not None:
+        return transport
+    import os
+
+    if os.environ.get("CGX_EXCHANGE", "").lower() in ("collective", "nccl"):
+        return "collective"
+    if dev.type == "cuda" and dist.get_backend(group) == "nccl" and hasattr(backend, "pack_p2p"):
+        return "p2p"
+    return "collective"
+
+
 def all_to_all_communication_final(batched_rasterizers, batched_screenspace_params, batched_cuda_args,
-                                   batched_strategies, group=None, backend=None):
+                                   batched_strategies, group=None, backend=None, transport=None):
     """See module docstring.  ``batched_screenspace_params[k]`` =
     (means2D, rgb, conic_opacity, radii, depths, means3D, scales, rotation) of camera k on this rank.
 
@@ -234,13 +433,60 @@ def all_to_all_communication_final(batched_rasterizers, batched_screenspace_para
     sizes_list = sizes.tolist()
     my = sizes_list[me]                                              # [dst][cam]
 
-    # ---- 2. send buffer: destination major, camera minor; packed by one kernel per camera
+    # ---- 2. send order: destination major, camera minor
     send_splits = [sum(my[j]) for j in range(ws)]
     recv_splits = [sum(sizes_list[i][me]) for i in range(ws)]
     n_send = sum(send_splits)
     dst_base = [0] * ws
     for j in range(1, ws):
         dst_base[j] = dst_base[j - 1] + send_splits[j - 1]
+    flat = []
+    for k in range(bsz):
+        m2, rgb, co, radii, depths, m3, sc, rot = batched_screenspace_params[k]
+        flat += [m2, rgb, co, m3, sc, rot]
+    sent_counts = [[my[j][k] for k in range(bsz)] for j in range(ws)]
+    self_rows = sum(my[me])
+    stats = {"rows_sent": n_send, "rows_received": sum(recv_splits), "rows_to_self": self_rows,
+             "bytes_sent_fwd": (n_send - self_rows) * REC * 4, "bytes_sent_bwd": (n_send - self_rows) * REC_DIFF * 4}
+
+    transport = _pick_transport(transport, group, dev, backend)
+    stats["transport"] = transport
+    if transport == "p2p":
+        n_recv = [[sum(sizes_list[i][j][k] for i in range(ws)) for k in range(bsz)] for j in range(ws)]
+        cam_base = []
+        for j in range(ws):
+            cur, bases = 0, []
+            for k in range(bsz):
+                bases.append(cur)
+                cur += _camera_layout(n_recv[j][k])[1]
+            cam_base.append(bases + [cur])
+        recv_need = max(cb[-1] for cb in cam_base)
+        grad_need = max(sum(sum(sizes_list[i][j]) for j in range(ws)) for i in range(ws)) * REC_DIFF * 4
+        arena = _arena_for(group, dev)
+        arena.ensure(recv_need, grad_need)
+        send_index = torch.empty(n_send, dtype=torch.int32, device=dev)
+        send_offsets, send_ranges = [], []
+        cam_off = [0] * ws
+        for k in range(bsz):
+            strat = batched_strategies[k]
+            send_offsets.append([dst_base[j] + cam_off[j] for j in strat.gpu_ids])
+            per_dst = []
+            for j in strat.gpu_ids:
+                n = my[j][k]
+                per_dst.append((dst_base[j] + cam_off[j], dst_base[j] + cam_off[j] + n))
+                cam_off[j] += n
+            send_ranges.append(per_dst)
+        plan = dict(backend=backend, arena=arena, me=me, ws=ws, sizes=sizes_list, strategies=batched_strategies,
+                    n_recv=n_recv, cam_base=cam_base, bounds=bounds, scratch=scratch, send_index=send_index,
+                    send_offsets=send_offsets, send_ranges=send_ranges, n_send=n_send,
+                    params=[tuple(t.detach() for t in p) for p in batched_screenspace_params],
+                    hw=[(r.raster_settings.image_height, r.raster_settings.image_width) for r in batched_rasterizers],
+                    avoid=[a["avoid_pixel_all2all"] for a in batched_cuda_args])
+        outs = _GaussianExchangeP2P.apply(plan, *flat)
+        out = [[outs[8 * k + c] for k in range(bsz)] for c in range(8)]
+        return (*out, sizes_list, sent_counts, send_index, stats)
+
+    # ---- 2b. collective transport: send buffer packed by one kernel per camera
     send = torch.empty(n_send, REC_DIFF, dtype=torch.float32, device=dev)
     send_aux = torch.empty(n_send, REC - REC_DIFF, dtype=torch.float32, device=dev)
     send_index = torch.empty(n_send, dtype=torch.int32, device=dev)
@@ -277,15 +523,6 @@ def all_to_all_communication_final(batched_rasterizers, batched_screenspace_para
     plan = dict(backend=backend, group=group, send=send, send_aux=send_aux, send_index=send_index,
                 send_splits=send_splits, recv_splits=recv_splits, send_ranges=send_ranges,
                 recv_segments=recv_segments)
-    flat = []
-    for k in range(bsz):
-        m2, rgb, co, radii, depths, m3, sc, rot = batched_screenspace_params[k]
-        flat += [m2, rgb, co, m3, sc, rot]
     outs = _GaussianExchange.apply(plan, *flat)
     out = [[outs[8 * k + c] for k in range(bsz)] for c in range(8)]
-    sent_counts = [[my[j][k] for k in range(bsz)] for j in range(ws)]
-    n_recv = sum(recv_splits)
-    self_rows = sum(my[me])
-    stats = {"rows_sent": n_send, "rows_received": n_recv, "rows_to_self": self_rows,
-             "bytes_sent_fwd": (n_send - self_rows) * REC * 4, "bytes_sent_bwd": (n_send - self_rows) * REC_DIFF * 4}
     return (*out, sizes_list, sent_counts, send_index, stats)

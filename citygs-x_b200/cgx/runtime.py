@@ -27,8 +27,9 @@ def make_cuda_args(rank=0, world_size=1, iteration=1):
 
 
 class TrainingStep:
-    def __init__(self, g, cams, device, rank=0, world_size=1, seed=4242):
+    def __init__(self, g, cams, device, rank=0, world_size=1, seed=4242, transport=None):
         self.dev, self.rank, self.ws = device, rank, world_size
+        self.transport = transport      # None: peer-to-peer inside an NCCL group, collective otherwise
         self.cams = cams
         # Gaussians are stored round-robin over ranks, like the reference's anchors (scene/gaussian_model.py:476-479)
         sel = slice(rank, None, world_size)
@@ -157,9 +158,9 @@ class TrainingStep:
             screen.append((means2D, self.rgb[k], conic_opacity, radii, depths, p["means3D"].detach(),
                            p["scales"].detach(), p["rotations"].detach()))
         (m2, rgb, co, rad, dep, m3, sc, rot, sizes, sent, send_index, stats) = \
-            exchange.all_to_all_communication_final(rasts, screen, args, strategies)
-        self._exchange["bytes_sent_fwd"] = stats["bytes_sent_fwd"]
-        self._exchange["bytes_sent_bwd"] = stats["bytes_sent_bwd"]
+            exchange.all_to_all_communication_final(rasts, screen, args, strategies, transport=self.transport)
+        self._exchange.update(bytes_sent_fwd=stats["bytes_sent_fwd"], bytes_sent_bwd=stats["bytes_sent_bwd"],
+                              transport=stats["transport"], rows_sent=stats["rows_sent"])
         heads, grads = [], []
         for k, strat in enumerate(strategies):
             local = strat.get_compute_locally()

@@ -550,8 +550,119 @@ pack_grad_rows_kernel(Segments sg, const float* __restrict__ d_means2D, const fl
     rows[row * 19 + c] = v;
 }
 
-}  // namespace cgx
+// ---------------------------------------------------------------- peer-to-peer exchange (fused pack + transport)
+// Destination tensors of one camera on one destination rank, as device pointers valid in THIS process (the
+// destination's memory is mapped here; plain stores travel over NVLink).  row = first row this rank writes.
+struct PeerCameraDst {
+    float* means2D;
+    float* rgb;
+    float* conic_opacity;
+    float* means3D;
+    float* scales;
+    float* rotations;
+    int* radii;
+    float* depths;
+    long long row;
+};
+struct PeerDsts {
+    PeerCameraDst d[MAX_WS];
+};
 
+// Selection + packing + transport in one pass: every selected row is stored straight into the final per-camera
+// tensors of the rank that renders it (its own memory for the local band), in ascending source index behind the
+// rows of lower source ranks.  No send buffer, no collective, no unpack on the receiver.
+__global__ void __launch_bounds__(PACK_TILE)
+local2j_pack_p2p_kernel(int P, int gx, int gy, int ws, int nblocks, const float2* __restrict__ means2D,
+                        const float* __restrict__ rgb, const float4* __restrict__ conic_opacity,
+                        const float* __restrict__ means3D, const float* __restrict__ scales,
+                        const float4* __restrict__ rotations, const int* __restrict__ radii,
+                        const float* __restrict__ depths, const int* __restrict__ bounds, bool avoid,
+                        const uint32_t* __restrict__ block_prefix, PeerDsts dsts, PackOffsets local_offs,
+                        int32_t* __restrict__ send_index)
+{
+    __shared__ uint32_t s_warp_cnt[PACK_TILE / 32];
+    const int i = blockIdx.x * PACK_TILE + threadIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    uint32_t bits = 0;
+    float2 m2 = {0.f, 0.f};
+    float4 co = {0.f, 0.f, 0.f, 0.f}, q = {0.f, 0.f, 0.f, 0.f};
+    float3 c = {0.f, 0.f, 0.f}, m3 = {0.f, 0.f, 0.f}, sc = {0.f, 0.f, 0.f};
+    int rad = 0;
+    float dep = 0.f;
+    if (i < P) {
+        m2 = means2D[i];
+        rad = radii[i];
+        uint2 rect_min, rect_max;
+        get_rect(m2, rad, rect_min, rect_max, gx, gy);
+        const int tmin = rect_min.y * gx + rect_min.x;
+        const int tmax = ((int)rect_max.y - 1) * gx + (int)rect_max.x - 1;
+        if (!(tmax < tmin))
+            for (int rk = 0; rk < ws; rk++)
+                if (touches_band(tmin, tmax, bounds[rk], bounds[rk + 1], gx, avoid)) bits |= 1u << rk;
+        if (bits) {
+            co = conic_opacity[i];
+            q = rotations[i];
+            c = {rgb[3 * i], rgb[3 * i + 1], rgb[3 * i + 2]};
+            m3 = {means3D[3 * i], means3D[3 * i + 1], means3D[3 * i + 2]};
+            sc = {scales[3 * i], scales[3 * i + 1], scales[3 * i + 2]};
+            dep = depths[i];
+        }
+    }
+    for (int rk = 0; rk < ws; rk++) {
+        const bool sel = (bits >> rk) & 1u;
+        const uint32_t b = __ballot_sync(0xffffffffu, sel);
+        if (lane == 0) s_warp_cnt[warp] = __popc(b);
+        __syncthreads();
+        uint32_t wbase = 0;
+        for (int w = 0; w < warp; w++) wbase += s_warp_cnt[w];
+        __syncthreads();
+        if (sel) {
+            const long long seg = (long long)block_prefix[(size_t)rk * nblocks + blockIdx.x] + wbase +
+                                  __popc(b & ((1u << lane) - 1u));
+            const PeerCameraDst& D = dsts.d[rk];
+            const long long row = D.row + seg;
+            reinterpret_cast<float2*>(D.means2D)[row] = m2;
+            D.rgb[3 * row] = c.x; D.rgb[3 * row + 1] = c.y; D.rgb[3 * row + 2] = c.z;
+            reinterpret_cast<float4*>(D.conic_opacity)[row] = co;
+            D.means3D[3 * row] = m3.x; D.means3D[3 * row + 1] = m3.y; D.means3D[3 * row + 2] = m3.z;
+            D.scales[3 * row] = sc.x; D.scales[3 * row + 1] = sc.y; D.scales[3 * row + 2] = sc.z;
+            reinterpret_cast<float4*>(D.rotations)[row] = q;
+            D.radii[row] = rad;
+            D.depths[row] = dep;
+            if (send_index) send_index[local_offs.row[rk] + seg] = i;
+        }
+    }
+}
+
+struct GradSegments {
+    int n;
+    float* rows[MAX_WS];           // where segment r's 19-float gradient rows go (possibly another GPU's memory)
+    long long prefix[MAX_WS + 1];  // rows of this camera in segments before r
+};
+
+__global__ void __launch_bounds__(256)
+pack_grad_rows_to_kernel(GradSegments sg, const float* __restrict__ d_means2D, const float* __restrict__ d_rgb,
+                         const float* __restrict__ d_co, const float* __restrict__ d_means3D,
+                         const float* __restrict__ d_scales, const float* __restrict__ d_rot)
+{
+    const long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long n = sg.prefix[sg.n];
+    if (e >= n * 19) return;
+    const long long lrow = e / 19;
+    const int c = (int)(e - lrow * 19);
+    int r = 0;
+    while (r + 1 < sg.n && lrow >= sg.prefix[r + 1]) r++;
+    float v = 0.f;
+    if (c < 2) { if (d_means2D) v = d_means2D[2 * lrow + c]; }
+    else if (c < 5) { if (d_rgb) v = d_rgb[3 * lrow + (c - 2)]; }
+    else if (c < 9) { if (d_co) v = d_co[4 * lrow + (c - 5)]; }
+    else if (c < 12) { if (d_means3D) v = d_means3D[3 * lrow + (c - 9)]; }
+    else if (c < 15) { if (d_scales) v = d_scales[3 * lrow + (c - 12)]; }
+    else { if (d_rot) v = d_rot[4 * lrow + (c - 15)]; }
+    sg.rows[r][(lrow - sg.prefix[r]) * 19 + c] = v;
+}
+
+}  // namespace cgx
 
 using namespace cgx;
 
@@ -814,6 +925,69 @@ extern "C" int cgx_pack_grad_rows(int n_segments, const int64_t* seg_start, cons
     if (!rows) return CGX_EINVAL;
     pack_grad_rows_kernel<<<(unsigned)((n * 19 + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
         sg, d_means2D, d_rgb, d_conic_opacity, d_means3D, d_scales, d_rotations, rows);
+    return check_launch();
+}
+
+extern "C" int cgx_local2j_pack_p2p(int P, int H, int W, int ws, const float* means2D, const float* rgb,
+                                    const float* conic_opacity, const float* means3D, const float* scales,
+                                    const float* rotations, const int32_t* radii, const float* depths,
+                                    const int32_t* tile_bounds, int avoid_pixel_all2all,
+                                    const cgx_peer_camera_dst* dst, const int64_t* send_row_offset,
+                                    int32_t* send_index, void* workspace, size_t workspace_bytes, void* stream)
+{
+    if (P < 0 || W <= 0 || H <= 0 || ws <= 0 || ws > MAX_WS || !dst) return CGX_EINVAL;
+    if (P == 0) return CGX_OK;
+    if (!means2D || !rgb || !conic_opacity || !means3D || !scales || !rotations || !radii || !depths ||
+        !tile_bounds || !workspace)
+        return CGX_EINVAL;
+    if (send_index && !send_row_offset) return CGX_EINVAL;
+    if (((uintptr_t)means2D & 7) || !aligned16(conic_opacity) || !aligned16(rotations)) return CGX_EINVAL;
+    if (workspace_bytes < cgx_local2j_workspace_bytes(P, ws)) return CGX_ENOMEM;
+    PeerDsts dsts;
+    PackOffsets offs;
+    for (int j = 0; j < MAX_WS; j++) {
+        offs.row[j] = (j < ws && send_row_offset) ? (long long)send_row_offset[j] : 0;
+        if (j >= ws) {
+            dsts.d[j] = PeerCameraDst{nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, 0};
+            continue;
+        }
+        const cgx_peer_camera_dst& s = dst[j];
+        if (!s.means2D || !s.rgb || !s.conic_opacity || !s.means3D || !s.scales || !s.rotations || !s.radii ||
+            !s.depths || s.first_row < 0)
+            return CGX_EINVAL;
+        if (((uintptr_t)s.means2D & 7) || !aligned16(s.conic_opacity) || !aligned16(s.rotations)) return CGX_EINVAL;
+        dsts.d[j] = PeerCameraDst{s.means2D, s.rgb, s.conic_opacity, s.means3D, s.scales, s.rotations, s.radii,
+                                  s.depths, (long long)s.first_row};
+    }
+    const int gx = (W + CGX_BLOCK_X - 1) / CGX_BLOCK_X, gy = (H + CGX_BLOCK_Y - 1) / CGX_BLOCK_Y;
+    const int nblocks = (P + PACK_TILE - 1) / PACK_TILE;
+    local2j_pack_p2p_kernel<<<nblocks, PACK_TILE, 0, (cudaStream_t)stream>>>(
+        P, gx, gy, ws, nblocks, (const float2*)means2D, rgb, (const float4*)conic_opacity, means3D, scales,
+        (const float4*)rotations, radii, depths, tile_bounds, avoid_pixel_all2all != 0, (const uint32_t*)workspace, dsts,
+        offs, send_index);
+    return check_launch();
+}
+
+extern "C" int cgx_pack_grad_rows_to(int n_segments, float* const* seg_rows, const int64_t* seg_count,
+                                     const float* d_means2D, const float* d_rgb, const float* d_conic_opacity,
+                                     const float* d_means3D, const float* d_scales, const float* d_rotations,
+                                     void* stream)
+{
+    if (n_segments < 0 || n_segments > MAX_WS) return CGX_EINVAL;
+    if (n_segments == 0) return CGX_OK;
+    if (!seg_rows || !seg_count) return CGX_EINVAL;
+    GradSegments sg;
+    sg.n = n_segments;
+    sg.prefix[0] = 0;
+    for (int r = 0; r < n_segments; r++) {
+        if (seg_count[r] < 0 || (seg_count[r] > 0 && !seg_rows[r])) return CGX_EINVAL;
+        sg.rows[r] = seg_rows[r];
+        sg.prefix[r + 1] = sg.prefix[r] + seg_count[r];
+    }
+    const long long n = sg.prefix[n_segments];
+    if (n == 0) return CGX_OK;
+    pack_grad_rows_to_kernel<<<(unsigned)((n * 19 + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+        sg, d_means2D, d_rgb, d_conic_opacity, d_means3D, d_scales, d_rotations);
     return check_launch();
 }
 

@@ -62,3 +62,21 @@ extern "C" int cgx_block_xy(int* block_x, int* block_y, int* one_dim_block)
     *one_dim_block = CGX_BLOCK_SIZE;
     return CGX_OK;
 }
+
+namespace cgx {
+int fetch_render_status(int* out);  // render.cu
+int fetch_peer_status(int* out);    // peer.cu
+}  // namespace cgx
+
+extern "C" int cgx_device_status(int* status_host, void* stream)
+{
+    if (!status_host) return CGX_EINVAL;
+    cudaError_t e = cudaStreamSynchronize((cudaStream_t)stream);
+    if (e != cudaSuccess) { cgx::set_cuda_error(e); return CGX_ECUDA; }
+    int a = 0, b = 0;
+    int st = cgx::fetch_render_status(&a);
+    if (st == CGX_OK) st = cgx::fetch_peer_status(&b);
+    if (st != CGX_OK) return st;
+    *status_host = a ? a : b;
+    return CGX_OK;
+}

@@ -641,18 +641,18 @@ using namespace cgx;
 
 extern "C" size_t cgx_render_records_bytes(int P) { return (size_t)(P > 0 ? P : 0) * sizeof(Record); }
 
-extern "C" int cgx_device_status(int* status_host, void* stream)
+namespace cgx {
+int fetch_render_status(int* out)
 {
-    if (!status_host) return CGX_EINVAL;
-    cudaError_t e = cudaStreamSynchronize((cudaStream_t)stream);
-    if (e == cudaSuccess) e = cudaMemcpyFromSymbol(status_host, g_status, sizeof(int));
+    cudaError_t e = cudaMemcpyFromSymbol(out, g_status, sizeof(int));
     if (e != cudaSuccess) { set_cuda_error(e); return CGX_ECUDA; }
-    if (*status_host != 0) {
+    if (*out != 0) {
         int zero = 0;
         cudaMemcpyToSymbol(g_status, &zero, sizeof(int));
     }
     return CGX_OK;
 }
+}  // namespace cgx
 
 static int g_render_variant = 1;  // 1: per-warp culling on (default), 0: off
 

@@ -15,7 +15,7 @@ ROOT = PKG.parent
 CSRC = ROOT / "csrc"
 LIBDIR = ROOT / "lib"
 SO = LIBDIR / "libcgx_raster.so"
-SOURCES = ["cabi.cu", "preprocess.cu", "binning.cu", "render.cu"]
+SOURCES = ["cabi.cu", "preprocess.cu", "binning.cu", "render.cu", "peer.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-shared", "-Xcompiler", "-fPIC"]
 
@@ -64,6 +64,9 @@ SIGNATURES = {
     "cgx_unpack_grad_add": (_i, [_i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "cgx_unpack_rows": (_i, [_i] + [_vp] * 13),
     "cgx_pack_grad_rows": (_i, [_i] + [_vp] * 10),
+    "cgx_local2j_pack_p2p": (_i, [_i, _i, _i, _i] + [_vp] * 9 + [_i] + [_vp] * 4 + [_sz, _vp]),
+    "cgx_pack_grad_rows_to": (_i, [_i] + [_vp] * 9),
+    "cgx_peer_barrier": (_i, [_i, _i, _vp, C.c_uint32, _vp]),
     "cgx_bin_workspace_bytes": (_sz, [_i]),
     "cgx_bin_count_scan": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "cgx_emit_keys": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _vp, _vp]),

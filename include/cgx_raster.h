@@ -148,6 +148,45 @@ int cgx_pack_grad_rows(int n_segments, const int64_t* seg_start, const int64_t* 
                        const float* d_means3D, const float* d_scales, const float* d_rotations, float* rows,
                        void* stream);
 
+/* Peer-to-peer form of the exchange, for ranks of one NVLink/NVSwitch domain whose receive arenas are mapped
+ * into each other's address space (symmetric memory).  cgx_local2j_pack_p2p fuses selection, packing and
+ * transport: each selected row is stored straight into the FINAL per-camera tensors of the rank that renders it
+ * (plain stores; the local band goes to local memory), behind the rows of lower source ranks
+ * (dst[j].first_row), in ascending source index.  It replaces cgx_local2j_pack + the all-to-all + cgx_unpack_rows
+ * (gaussian_renderer/__init__.py:612-696).  send_index (optional, with send_row_offset) records the source row
+ * of every sent row in local send order for the backward.  cgx_pack_grad_rows_to is the backward's transport:
+ * segment r's 19-float gradient rows are stored at seg_rows[r] (host array of device pointers, typically in the
+ * source rank's memory).  The caller orders these stores against the readers (stream-ordered barriers). */
+typedef struct cgx_peer_camera_dst {
+    float* means2D;        /* (n,2) */
+    float* rgb;            /* (n,3) */
+    float* conic_opacity;  /* (n,4) */
+    float* means3D;        /* (n,3) */
+    float* scales;         /* (n,3) */
+    float* rotations;      /* (n,4) */
+    int32_t* radii;        /* (n)   */
+    float* depths;         /* (n)   */
+    int64_t first_row;     /* first row this rank writes in those arrays */
+} cgx_peer_camera_dst;
+int cgx_local2j_pack_p2p(int P, int H, int W, int ws, const float* means2D, const float* rgb,
+                         const float* conic_opacity, const float* means3D, const float* scales,
+                         const float* rotations, const int32_t* radii, const float* depths,
+                         const int32_t* tile_bounds, int avoid_pixel_all2all,
+                         const cgx_peer_camera_dst* dst /* host, ws entries */,
+                         const int64_t* send_row_offset /* host, ws entries, optional */, int32_t* send_index,
+                         void* workspace, size_t workspace_bytes, void* stream);
+int cgx_pack_grad_rows_to(int n_segments, float* const* seg_rows, const int64_t* seg_count,
+                          const float* d_means2D, const float* d_rgb, const float* d_conic_opacity,
+                          const float* d_means3D, const float* d_scales, const float* d_rotations, void* stream);
+
+/* Stream-ordered barrier over the ranks of one NVLink/NVSwitch domain (no counterpart in the reference, which
+ * synchronises through its collectives).  flag_ptrs: host array of `ws` device pointers, flag_ptrs[r] = an array
+ * of at least 32 zero-initialised uint32 words living in rank r's memory and mapped in this process.  Call with
+ * the same, strictly increasing epoch on every rank (1, 2, 3, ...).  After the kernel, everything every rank
+ * queued before its own call is complete and visible.  The wait is bounded (about 2 s): on expiry the device
+ * status word is set (cgx_device_status) and the kernel returns. */
+int cgx_peer_barrier(int ws, int rank, uint32_t* const* flag_ptrs, uint32_t epoch, void* stream);
+
 /* ------------------------------------------------------------------ binning */
 
 /* updateTileTouched + InclusiveSum (RAST/cuda_rasterizer/rasterizer_impl.cu:264-288,648).
@@ -238,7 +277,7 @@ int cgx_render_bwd(int P, int W, int H, float tanfovx, float tanfovy, const uint
 /* ------------------------------------------------------------------ diagnostics */
 
 /* Host-synchronous.  Waits for `stream`, reads and clears the device status word that kernels set when a
- * bounded wait gives up (0 = ok, CGX_ETIMEDOUT otherwise).  Replaces the reference's debug-mode
+ * bounded wait (blending mbarriers, peer barrier) gives up (0 = ok, CGX_ETIMEDOUT otherwise).  Replaces the reference's debug-mode
  * synchronise-and-throw (RAST/cuda_rasterizer/auxiliary.h:220-227); nothing ever traps. */
 int cgx_device_status(int* status_host, void* stream);
 

@@ -1,7 +1,8 @@
 """Multi-GPU equivalence (NCCL): the data-parallel step on 2 ranks must reproduce the single-GPU step.
 
 Runs as child processes, one per GPU, only where at least two GPUs are visible.  NVLS is switched off for NCCL
-in these children (plain peer transport is all the exchange needs)."""
+in these children (plain peer transport is all the exchange needs) and symmetric memory is set up without
+multicast objects."""
 import os
 import socket
 import sys
@@ -21,10 +22,11 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, ws, port, out_dir):
+def _worker(rank, ws, port, out_dir, transport):
     for p in (ROOT, ROOT / "citygs-x_b200", ROOT / "tests"):
         sys.path.insert(0, str(p))
-    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0",
+                      TORCH_SYMM_MEM_DISABLE_MULTICAST="1")
     import torch.distributed as dist
 
     torch.cuda.set_device(rank)
@@ -35,11 +37,17 @@ def _worker(rank, ws, port, out_dir):
         from cgx import synthetic as S
 
         g, cams = S.config(2, n_gaussians=N_GAUSS, n_cameras=N_CAMS, res=RES)
-        step = RT.TrainingStep(g, cams, dev, rank=rank, world_size=ws)
+        step = RT.TrainingStep(g, cams, dev, rank=rank, world_size=ws, transport=transport)
         step.run()
+        step.run()          # twice: the second step reuses the exchange arenas
         torch.cuda.synchronize()
         grads = {k: v.grad.detach().cpu() for k, v in step.params.items()}
         m2 = [(r.cpu(), (m.grad.cpu() if m.grad is not None else None)) for r, m in step.last]
+        import ctypes
+        from diff_gaussian_rasterization import _lib
+        st = ctypes.c_int(0)
+        _lib.check(_lib.lib().cgx_device_status(ctypes.byref(st), None), "cgx_device_status")
+        assert st.value == 0, "a bounded device-side wait gave up"
         torch.save({"grads": grads, "m2": m2, "ex": step.exchange_stats(),
                     "strategies": [(s.gpu_ids, s.division_pos) for s in step._strategies]},
                    os.path.join(out_dir, f"rank{rank}.pt"))
@@ -48,7 +56,8 @@ def _worker(rank, ws, port, out_dir):
         dist.destroy_process_group()
 
 
-def test_two_gpu_step_equals_single_gpu_step(tmp_path):
+@pytest.mark.parametrize("transport", ["p2p", "collective"])
+def test_two_gpu_step_equals_single_gpu_step(tmp_path, transport):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     import torch.multiprocessing as mp
@@ -57,7 +66,7 @@ def test_two_gpu_step_equals_single_gpu_step(tmp_path):
     from cgx import synthetic as S
 
     port = _free_port()
-    mp.spawn(_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    mp.spawn(_worker, args=(2, port, str(tmp_path), transport), nprocs=2, join=True)
     parts = [torch.load(tmp_path / f"rank{r}.pt", weights_only=False) for r in range(2)]
 
     dev = torch.device("cuda:0")
@@ -67,7 +76,7 @@ def test_two_gpu_step_equals_single_gpu_step(tmp_path):
     torch.cuda.synchronize()
     # 4 cameras over 2 ranks: two whole cameras each
     assert parts[0]["strategies"] == [([0], [0, 30]), ([0], [0, 30]), ([1], [0, 30]), ([1], [0, 30])]
-    assert parts[0]["ex"]["bytes_sent_fwd"] > 0
+    assert parts[0]["ex"]["bytes_sent_fwd"] > 0 and parts[0]["ex"]["transport"] == transport
     for name, full in single.params.items():
         full = full.grad.cpu()
         merged = torch.zeros_like(full)
