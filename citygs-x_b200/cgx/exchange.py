@@ -144,15 +144,28 @@ class CudaPackBackend:
             self._p(rotation), self._p(radii), self._p(depths), self._p(tile_bounds), int(avoid), arr, offs,
             self._p(send_index), self._p(workspace), workspace.numel(), self._st()), "cgx_local2j_pack_p2p")
 
-    def pack_grad_rows_to(self, seg_ptrs, seg_counts, grads):
+    def pack_grad_rows_to(self, seg_ptrs, seg_counts, ncols, grads):
         n = len(seg_ptrs)
         if n == 0 or sum(seg_counts) == 0:
             return
         ptrs = (C.c_void_p * n)(*seg_ptrs)
         counts = (C.c_int64 * n)(*seg_counts)
         g = [None if t is None else t.contiguous() for t in grads]
-        self._lib.check(self.l.cgx_pack_grad_rows_to(n, ptrs, counts, *[self._p(t) for t in g], self._st()),
+        self._lib.check(self.l.cgx_pack_grad_rows_to(n, ptrs, counts, ncols, *[self._p(t) for t in g], self._st()),
                         "cgx_pack_grad_rows_to")
+
+    def unpack_grad_add_cols(self, grad_rows, send_index, ranges, ncols, grads):
+        ranges = [(a, b) for a, b in ranges if b > a]
+        if not ranges:
+            return
+        n = len(ranges)
+        starts = (C.c_int64 * n)(*[a for a, _ in ranges])
+        stops = (C.c_int64 * n)(*[b for _, b in ranges])
+        d_m2, d_rgb, d_co, d_m3, d_sc, d_rot = grads
+        self._lib.check(self.l.cgx_unpack_grad_add_cols(n, starts, stops, ncols, self._p(grad_rows),
+                                                        self._p(send_index), self._p(d_m2), self._p(d_rgb),
+                                                        self._p(d_co), self._p(d_m3), self._p(d_sc), self._p(d_rot),
+                                                        self._st()), "cgx_unpack_grad_add_cols")
 
 
 _default_backend = None
@@ -358,6 +371,7 @@ class _GaussianExchangeP2P(torch.autograd.Function):
         me, ws, sizes = plan["me"], plan["ws"], plan["sizes"]
         dev = arena.dev
         bsz = len(plan["strategies"])
+        ncols = plan["grad_cols"]
         for k in range(bsz):
             g8 = gouts[8 * k: 8 * k + 8]
             ptrs, counts = [], []
@@ -365,12 +379,12 @@ class _GaussianExchangeP2P(torch.autograd.Function):
                 n = sizes[i][me][k]
                 # position of segment (i -> me, camera k) in rank i's send order: destination major, camera minor
                 row = sum(sum(sizes[i][j]) for j in range(me)) + sum(sizes[i][me][:k])
-                ptrs.append(arena.grad_hdl.buffer_ptrs[i] + row * REC_DIFF * 4)
+                ptrs.append(arena.grad_hdl.buffer_ptrs[i] + row * ncols * 4)
                 counts.append(n)
-            be.pack_grad_rows_to(ptrs, counts, (g8[0], g8[1], g8[2], g8[5], g8[6], g8[7]))
+            be.pack_grad_rows_to(ptrs, counts, ncols, (g8[0], g8[1], g8[2], g8[5], g8[6], g8[7]))
         arena.barrier()                       # every rank's gradient rows have landed in their owners' buffers
         n_send = plan["n_send"]
-        grad_send = arena.grad[: n_send * REC_DIFF * 4].view(torch.float32).view(n_send, REC_DIFF)
+        grad_send = arena.grad[: n_send * ncols * 4].view(torch.float32).view(n_send, ncols)
         grads = []
         for k, per_dst in enumerate(plan["send_ranges"]):
             need = ctx.needs_input_grad[1 + 6 * k: 1 + 6 * k + 6]
@@ -379,7 +393,7 @@ class _GaussianExchangeP2P(torch.autograd.Function):
             for c in (0, 2):                  # the scatter kernel always writes means2D and conic_opacity
                 if g6[c] is None:
                     g6[c] = torch.zeros(ctx.shapes[6 * k + c], dtype=torch.float32, device=dev)
-            be.unpack_grad_add(grad_send, plan["send_index"], per_dst, g6)
+            be.unpack_grad_add_cols(grad_send, plan["send_index"], per_dst, ncols, g6)
             grads += [g if nd else None for g, nd in zip(g6, need)]
         return (None,) + tuple(grads)
 
@@ -476,7 +490,11 @@ def all_to_all_communication_final(batched_rasterizers, batched_screenspace_para
                 per_dst.append((dst_base[j] + cam_off[j], dst_base[j] + cam_off[j] + n))
                 cam_off[j] += n
             send_ranges.append(per_dst)
+        # gradient rows carry 19 columns only when some rank needs gradients for the 3-D parameters through the
+        # exchange; every rank runs the same model code, so this is the same decision everywhere
+        grad_cols = REC_DIFF if any(flat[6 * k + c].requires_grad for k in range(bsz) for c in (3, 4, 5)) else 9
         plan = dict(backend=backend, arena=arena, me=me, ws=ws, sizes=sizes_list, strategies=batched_strategies,
+                    grad_cols=grad_cols,
                     n_recv=n_recv, cam_base=cam_base, bounds=bounds, scratch=scratch, send_index=send_index,
                     send_offsets=send_offsets, send_ranges=send_ranges, n_send=n_send,
                     params=[tuple(t.detach() for t in p) for p in batched_screenspace_params],

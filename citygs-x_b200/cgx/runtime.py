@@ -30,6 +30,7 @@ class TrainingStep:
     def __init__(self, g, cams, device, rank=0, world_size=1, seed=4242, transport=None):
         self.dev, self.rank, self.ws = device, rank, world_size
         self.transport = transport      # None: peer-to-peer inside an NCCL group, collective otherwise
+        self.batched = True             # camera-batched preprocess (False: the reference's per-camera loop)
         self.cams = cams
         # Gaussians are stored round-robin over ranks, like the reference's anchors (scene/gaussian_model.py:476-479)
         sel = slice(rank, None, world_size)
@@ -99,14 +100,25 @@ class TrainingStep:
         return rgb
 
     # ------------------------------------------------------------------ single-GPU step
+    def _preprocess_all(self, args):
+        """Screen-space state of the local Gaussians for every camera of the batch (one launch)."""
+        from .batched import preprocess_gaussians_batched
+
+        p = self.params
+        if self.batched:
+            return preprocess_gaussians_batched(p["means3D"], p["scales"], p["rotations"], self.sh_dummy,
+                                                p["opacities"], self.settings, args)
+        return [GaussianRasterizer(s).preprocess_gaussians(p["means3D"], p["scales"], p["rotations"], self.sh_dummy,
+                                                           p["opacities"], args) for s in self.settings]
+
     def _step_single(self):
         p = self.params
         args = make_cuda_args(self.rank, self.ws, self.iteration)
-        outs = []
+        outs, heads, grads = [], [], []
+        screen = self._preprocess_all(args)
         for k, cam in enumerate(self.cams):
             rast = GaussianRasterizer(self.settings[k])
-            means2D, _, conic_opacity, radii, depths = rast.preprocess_gaussians(
-                p["means3D"], p["scales"], p["rotations"], self.sh_dummy, p["opacities"], args)
+            means2D, _, conic_opacity, radii, depths = screen[k]
             means2D.retain_grad()          # the densifier reads means2D.grad
             TX, TY = (cam.W + 15) // 16, (cam.H + 15) // 16
             local = self._all_local(TY, TX)
@@ -114,8 +126,10 @@ class TrainingStep:
             all_map = self.all_map_for(k, p["means3D"].detach(), p["scales"].detach(), p["rotations"].detach(), radii)
             color, n_render, n_consider, n_contrib, observe, out_all_map, plane_depth = rast.render_gaussians(
                 means2D, means2D_abs, conic_opacity, self.rgb[k], all_map, depths, radii, local, None, args)
-            torch.autograd.backward([color, out_all_map, plane_depth], self.cot[k])
+            heads += [color, out_all_map, plane_depth]
+            grads += self.cot[k]
             outs.append((radii, means2D))
+        torch.autograd.backward(heads, grads)      # one backward over the batch, as one loss.backward() upstream
         self.last = outs
 
     _local_cache = {}
@@ -148,9 +162,9 @@ class TrainingStep:
         rasts = [GaussianRasterizer(s) for s in self.settings]
         args = [make_cuda_args(self.rank, self.ws, self.iteration) for _ in self.cams]
         screen, keep = [], []
+        pre = self._preprocess_all(args[0])
         for k in range(len(self.cams)):
-            means2D, _, conic_opacity, radii, depths = rasts[k].preprocess_gaussians(
-                p["means3D"], p["scales"], p["rotations"], self.sh_dummy, p["opacities"], args[k])
+            means2D, _, conic_opacity, radii, depths = pre[k]
             means2D.retain_grad()
             keep.append((radii, means2D))
             # the plane descriptors are rebuilt on the receiver without autograd, so the 3-D parameters travel

@@ -200,7 +200,7 @@ sort_scan_rows_kernel(int nblocks, uint32_t* __restrict__ table, uint32_t* __res
 // Stable scatter of one 4096-pair tile.  Thread t of warp w owns the 16 consecutive "rounds" of the warp's
 // contiguous 512-pair chunk: in round r the warp looks at pairs [chunk + 32 r, chunk + 32 r + 32), so
 // (warp, round, lane) order is input order and ranks computed from match.any ballots are stable.
-__global__ void __launch_bounds__(SORT_THREADS)
+__global__ void __launch_bounds__(SORT_THREADS, 3)
 sort_scatter_kernel(int64_t n, int nblocks, int shift, uint32_t mask, const uint64_t* __restrict__ keys_in,
                     const uint32_t* __restrict__ vals_in, uint64_t* __restrict__ keys_out,
                     uint32_t* __restrict__ vals_out, const uint32_t* __restrict__ table,
@@ -580,18 +580,17 @@ local2j_pack_p2p_kernel(int P, int gx, int gy, int ws, int nblocks, const float2
                         const uint32_t* __restrict__ block_prefix, PeerDsts dsts, PackOffsets local_offs,
                         int32_t* __restrict__ send_index)
 {
+    // The CTA's selected rows are compacted field by field in shared memory and leave as eight contiguous bursts
+    // (consecutive threads store consecutive words): full-width transactions, local or across NVLink.
     __shared__ uint32_t s_warp_cnt[PACK_TILE / 32];
+    __shared__ float s_f[21][PACK_TILE + 1];   // field-major staging: [m2 2 | rgb 3 | co 4 | m3 3 | sc 3 | rot 4 | radius | depth]
     const int i = blockIdx.x * PACK_TILE + threadIdx.x;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     uint32_t bits = 0;
-    float2 m2 = {0.f, 0.f};
-    float4 co = {0.f, 0.f, 0.f, 0.f}, q = {0.f, 0.f, 0.f, 0.f};
-    float3 c = {0.f, 0.f, 0.f}, m3 = {0.f, 0.f, 0.f}, sc = {0.f, 0.f, 0.f};
-    int rad = 0;
-    float dep = 0.f;
+    float rec[21];
     if (i < P) {
-        m2 = means2D[i];
-        rad = radii[i];
+        const float2 m2 = means2D[i];
+        const int rad = radii[i];
         uint2 rect_min, rect_max;
         get_rect(m2, rad, rect_min, rect_max, gx, gy);
         const int tmin = rect_min.y * gx + rect_min.x;
@@ -600,12 +599,16 @@ local2j_pack_p2p_kernel(int P, int gx, int gy, int ws, int nblocks, const float2
             for (int rk = 0; rk < ws; rk++)
                 if (touches_band(tmin, tmax, bounds[rk], bounds[rk + 1], gx, avoid)) bits |= 1u << rk;
         if (bits) {
-            co = conic_opacity[i];
-            q = rotations[i];
-            c = {rgb[3 * i], rgb[3 * i + 1], rgb[3 * i + 2]};
-            m3 = {means3D[3 * i], means3D[3 * i + 1], means3D[3 * i + 2]};
-            sc = {scales[3 * i], scales[3 * i + 1], scales[3 * i + 2]};
-            dep = depths[i];
+            const float4 co = conic_opacity[i];
+            const float4 q = rotations[i];
+            rec[0] = m2.x; rec[1] = m2.y;
+            rec[2] = rgb[3 * i]; rec[3] = rgb[3 * i + 1]; rec[4] = rgb[3 * i + 2];
+            rec[5] = co.x; rec[6] = co.y; rec[7] = co.z; rec[8] = co.w;
+            rec[9] = means3D[3 * i]; rec[10] = means3D[3 * i + 1]; rec[11] = means3D[3 * i + 2];
+            rec[12] = scales[3 * i]; rec[13] = scales[3 * i + 1]; rec[14] = scales[3 * i + 2];
+            rec[15] = q.x; rec[16] = q.y; rec[17] = q.z; rec[18] = q.w;
+            rec[19] = __int_as_float(rad);
+            rec[20] = depths[i];
         }
     }
     for (int rk = 0; rk < ws; rk++) {
@@ -613,24 +616,42 @@ local2j_pack_p2p_kernel(int P, int gx, int gy, int ws, int nblocks, const float2
         const uint32_t b = __ballot_sync(0xffffffffu, sel);
         if (lane == 0) s_warp_cnt[warp] = __popc(b);
         __syncthreads();
-        uint32_t wbase = 0;
-        for (int w = 0; w < warp; w++) wbase += s_warp_cnt[w];
-        __syncthreads();
-        if (sel) {
-            const long long seg = (long long)block_prefix[(size_t)rk * nblocks + blockIdx.x] + wbase +
-                                  __popc(b & ((1u << lane) - 1u));
-            const PeerCameraDst& D = dsts.d[rk];
-            const long long row = D.row + seg;
-            reinterpret_cast<float2*>(D.means2D)[row] = m2;
-            D.rgb[3 * row] = c.x; D.rgb[3 * row + 1] = c.y; D.rgb[3 * row + 2] = c.z;
-            reinterpret_cast<float4*>(D.conic_opacity)[row] = co;
-            D.means3D[3 * row] = m3.x; D.means3D[3 * row + 1] = m3.y; D.means3D[3 * row + 2] = m3.z;
-            D.scales[3 * row] = sc.x; D.scales[3 * row + 1] = sc.y; D.scales[3 * row + 2] = sc.z;
-            reinterpret_cast<float4*>(D.rotations)[row] = q;
-            D.radii[row] = rad;
-            D.depths[row] = dep;
-            if (send_index) send_index[local_offs.row[rk] + seg] = i;
+        uint32_t wbase = 0, cnt = 0;
+        for (int w = 0; w < PACK_TILE / 32; w++) {
+            if (w < warp) wbase += s_warp_cnt[w];
+            cnt += s_warp_cnt[w];
         }
+        if (cnt == 0) {          // uniform over the CTA
+            __syncthreads();
+            continue;
+        }
+        const uint32_t slot = wbase + __popc(b & ((1u << lane) - 1u));
+        const long long seg0 = (long long)block_prefix[(size_t)rk * nblocks + blockIdx.x];
+        if (sel) {
+#pragma unroll
+            for (int k = 0; k < 21; k++) s_f[k][slot] = rec[k];
+            if (send_index) send_index[local_offs.row[rk] + seg0 + slot] = i;
+        }
+        __syncthreads();
+        const PeerCameraDst& D = dsts.d[rk];
+        const long long row0 = D.row + seg0;
+        // field f of width w occupies words [row0*w, (row0+cnt)*w) of its destination array
+        auto burst = [&](float* dst, int f0, int w) {
+            const int n = (int)cnt * w;
+            float* out = dst + row0 * w;
+            for (int e = threadIdx.x; e < n; e += PACK_TILE) out[e] = s_f[f0 + e % w][e / w];
+        };
+        burst(D.means2D, 0, 2);
+        burst(D.rgb, 2, 3);
+        burst(D.conic_opacity, 5, 4);
+        burst(D.means3D, 9, 3);
+        burst(D.scales, 12, 3);
+        burst(D.rotations, 15, 4);
+        for (int e = threadIdx.x; e < (int)cnt; e += PACK_TILE) {
+            D.radii[row0 + e] = __float_as_int(s_f[19][e]);
+            D.depths[row0 + e] = s_f[20][e];
+        }
+        __syncthreads();
     }
 }
 
@@ -640,6 +661,9 @@ struct GradSegments {
     long long prefix[MAX_WS + 1];  // rows of this camera in segments before r
 };
 
+// NCOLS = 19: all differentiable columns; NCOLS = 9: only means2D | rgb | conic_opacity (the 3-D parameters carry
+// no gradient back when the receiver builds its plane descriptors without autograd).
+template <int NCOLS>
 __global__ void __launch_bounds__(256)
 pack_grad_rows_to_kernel(GradSegments sg, const float* __restrict__ d_means2D, const float* __restrict__ d_rgb,
                          const float* __restrict__ d_co, const float* __restrict__ d_means3D,
@@ -647,9 +671,9 @@ pack_grad_rows_to_kernel(GradSegments sg, const float* __restrict__ d_means2D, c
 {
     const long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     const long long n = sg.prefix[sg.n];
-    if (e >= n * 19) return;
-    const long long lrow = e / 19;
-    const int c = (int)(e - lrow * 19);
+    if (e >= n * NCOLS) return;
+    const long long lrow = e / NCOLS;
+    const int c = (int)(e - lrow * NCOLS);
     int r = 0;
     while (r + 1 < sg.n && lrow >= sg.prefix[r + 1]) r++;
     float v = 0.f;
@@ -659,7 +683,32 @@ pack_grad_rows_to_kernel(GradSegments sg, const float* __restrict__ d_means2D, c
     else if (c < 12) { if (d_means3D) v = d_means3D[3 * lrow + (c - 9)]; }
     else if (c < 15) { if (d_scales) v = d_scales[3 * lrow + (c - 12)]; }
     else { if (d_rot) v = d_rot[4 * lrow + (c - 15)]; }
-    sg.rows[r][(lrow - sg.prefix[r]) * 19 + c] = v;
+    sg.rows[r][(lrow - sg.prefix[r]) * NCOLS + c] = v;
+}
+
+template <int NCOLS>
+__global__ void __launch_bounds__(256)
+unpack_grad_add_cols_kernel(RowRanges rr, const float* __restrict__ g, const int32_t* __restrict__ index,
+                            float* __restrict__ d_means2D, float* __restrict__ d_rgb, float* __restrict__ d_co,
+                            float* __restrict__ d_means3D, float* __restrict__ d_scales, float* __restrict__ d_rot)
+{
+    const long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long total_rows = rr.prefix[rr.n];
+    if (e >= total_rows * NCOLS) return;
+    const long long lrow = e / NCOLS;
+    const int c = (int)(e - lrow * NCOLS);
+    int r = 0;
+    while (r + 1 < rr.n && lrow >= rr.prefix[r + 1]) r++;
+    const long long row = rr.start[r] + (lrow - rr.prefix[r]);
+    const size_t i = (size_t)index[row];
+    const float v = g[row * NCOLS + c];
+    if (v == 0.0f) return;
+    if (c < 2) atomicAdd(d_means2D + 2 * i + c, v);
+    else if (c < 5) { if (d_rgb) atomicAdd(d_rgb + 3 * i + (c - 2), v); }
+    else if (c < 9) atomicAdd(d_co + 4 * i + (c - 5), v);
+    else if (c < 12) { if (d_means3D) atomicAdd(d_means3D + 3 * i + (c - 9), v); }
+    else if (c < 15) { if (d_scales) atomicAdd(d_scales + 3 * i + (c - 12), v); }
+    else { if (d_rot) atomicAdd(d_rot + 4 * i + (c - 15), v); }
 }
 
 }  // namespace cgx
@@ -968,12 +1017,12 @@ extern "C" int cgx_local2j_pack_p2p(int P, int H, int W, int ws, const float* me
     return check_launch();
 }
 
-extern "C" int cgx_pack_grad_rows_to(int n_segments, float* const* seg_rows, const int64_t* seg_count,
+extern "C" int cgx_pack_grad_rows_to(int n_segments, float* const* seg_rows, const int64_t* seg_count, int ncols,
                                      const float* d_means2D, const float* d_rgb, const float* d_conic_opacity,
                                      const float* d_means3D, const float* d_scales, const float* d_rotations,
                                      void* stream)
 {
-    if (n_segments < 0 || n_segments > MAX_WS) return CGX_EINVAL;
+    if (n_segments < 0 || n_segments > MAX_WS || (ncols != 9 && ncols != 19)) return CGX_EINVAL;
     if (n_segments == 0) return CGX_OK;
     if (!seg_rows || !seg_count) return CGX_EINVAL;
     GradSegments sg;
@@ -986,8 +1035,12 @@ extern "C" int cgx_pack_grad_rows_to(int n_segments, float* const* seg_rows, con
     }
     const long long n = sg.prefix[n_segments];
     if (n == 0) return CGX_OK;
-    pack_grad_rows_to_kernel<<<(unsigned)((n * 19 + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
-        sg, d_means2D, d_rgb, d_conic_opacity, d_means3D, d_scales, d_rotations);
+    if (ncols == 9)
+        pack_grad_rows_to_kernel<9><<<(unsigned)((n * 9 + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+            sg, d_means2D, d_rgb, d_conic_opacity, d_means3D, d_scales, d_rotations);
+    else
+        pack_grad_rows_to_kernel<19><<<(unsigned)((n * 19 + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+            sg, d_means2D, d_rgb, d_conic_opacity, d_means3D, d_scales, d_rotations);
     return check_launch();
 }
 
@@ -1045,4 +1098,32 @@ extern "C" int cgx_sort_pairs_static(int64_t n, int end_bit, uint64_t* keys_in, 
     const int st = sort_static_scratch_ptr(&scratch);
     if (st != CGX_OK) return st;
     return cgx_sort_pairs(n, end_bit, keys_in, values_in, keys_out, values_out, scratch, cgx::SORT_STATIC_BYTES, stream);
+}
+
+extern "C" int cgx_unpack_grad_add_cols(int n_ranges, const int64_t* range_start, const int64_t* range_stop, int ncols,
+                                        const float* grad_rows, const int32_t* send_index, float* d_means2D,
+                                        float* d_rgb, float* d_conic_opacity, float* d_means3D, float* d_scales,
+                                        float* d_rotations, void* stream)
+{
+    if (n_ranges < 0 || n_ranges > MAX_WS || (ncols != 9 && ncols != 19)) return CGX_EINVAL;
+    if (n_ranges == 0) return CGX_OK;
+    if (!range_start || !range_stop) return CGX_EINVAL;
+    RowRanges rr;
+    rr.n = n_ranges;
+    rr.prefix[0] = 0;
+    for (int r = 0; r < n_ranges; r++) {
+        if (range_stop[r] < range_start[r] || range_start[r] < 0) return CGX_EINVAL;
+        rr.start[r] = range_start[r];
+        rr.prefix[r + 1] = rr.prefix[r] + (range_stop[r] - range_start[r]);
+    }
+    const long long total = rr.prefix[n_ranges] * ncols;
+    if (total == 0) return CGX_OK;
+    if (!grad_rows || !send_index || !d_means2D || !d_conic_opacity) return CGX_EINVAL;
+    if (ncols == 9)
+        unpack_grad_add_cols_kernel<9><<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+            rr, grad_rows, send_index, d_means2D, d_rgb, d_conic_opacity, d_means3D, d_scales, d_rotations);
+    else
+        unpack_grad_add_cols_kernel<19><<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+            rr, grad_rows, send_index, d_means2D, d_rgb, d_conic_opacity, d_means3D, d_scales, d_rotations);
+    return check_launch();
 }

@@ -291,6 +291,155 @@ all_map_kernel(int P, const float* __restrict__ means3D, const float* __restrict
     for (int k = 0; k < 5; k++) out[5 * (size_t)i + k] = o5[k];
 }
 
+// Backward of one camera's projection for one Gaussian: conic cotangent -> 2-D covariance -> (accumulated into)
+// dL/dcov3D[6] and dL/dmean, plus the 2-D mean's cotangent through the perspective projection.
+__device__ __forceinline__ void bwd_project_one(const float3 mean, const float* cov3D, const float* view_matrix,
+                                                const float* proj, const float h_x, const float h_y,
+                                                const float tan_fovx, const float tan_fovy, const float4 dco,
+                                                const float2 dm2, float3& g_mean, float* dL_dcov)
+{
+    // ---- conic -> cov2D -> cov3D and mean (EWA part)
+    float3 dL_dconic = {dco.x, dco.y, dco.z};
+    float3 tt = transform_point_4x3(mean, view_matrix);
+    const float limx = 1.3f * tan_fovx;
+    const float limy = 1.3f * tan_fovy;
+    const float txtz = tt.x / tt.z;
+    const float tytz = tt.y / tt.z;
+    tt.x = min(limx, max(-limx, txtz)) * tt.z;
+    tt.y = min(limy, max(-limy, tytz)) * tt.z;
+    const float x_grad_mul = txtz < -limx || txtz > limx ? 0 : 1;
+    const float y_grad_mul = tytz < -limy || tytz > limy ? 0 : 1;
+
+    Mat3 J;
+    J.m[0][0] = h_x / tt.z; J.m[0][1] = 0.0f; J.m[0][2] = -(h_x * tt.x) / (tt.z * tt.z);
+    J.m[1][0] = 0.0f; J.m[1][1] = h_y / tt.z; J.m[1][2] = -(h_y * tt.y) / (tt.z * tt.z);
+    J.m[2][0] = 0; J.m[2][1] = 0; J.m[2][2] = 0;
+    Mat3 Wm;
+    Wm.m[0][0] = view_matrix[0]; Wm.m[0][1] = view_matrix[4]; Wm.m[0][2] = view_matrix[8];
+    Wm.m[1][0] = view_matrix[1]; Wm.m[1][1] = view_matrix[5]; Wm.m[1][2] = view_matrix[9];
+    Wm.m[2][0] = view_matrix[2]; Wm.m[2][1] = view_matrix[6]; Wm.m[2][2] = view_matrix[10];
+    Mat3 Vrk;
+    Vrk.m[0][0] = cov3D[0]; Vrk.m[0][1] = cov3D[1]; Vrk.m[0][2] = cov3D[2];
+    Vrk.m[1][0] = cov3D[1]; Vrk.m[1][1] = cov3D[3]; Vrk.m[1][2] = cov3D[4];
+    Vrk.m[2][0] = cov3D[2]; Vrk.m[2][1] = cov3D[4]; Vrk.m[2][2] = cov3D[5];
+    Mat3 T = mul(Wm, J);
+    Mat3 cov2D = mul(mul(transpose(T), transpose(Vrk)), T);
+
+    float a = cov2D.m[0][0] += 0.3f;
+    float b = cov2D.m[0][1];
+    float c = cov2D.m[1][1] += 0.3f;
+
+    float denom = a * c - b * b;
+    float dL_da = 0, dL_db = 0, dL_dc = 0;
+    float denom2inv = 1.0f / ((denom * denom) + 0.0000001f);
+    float dcv[6];
+    if (denom2inv != 0) {
+        dL_da = denom2inv * (-c * c * dL_dconic.x + 2 * b * c * dL_dconic.y + (denom - a * c) * dL_dconic.z);
+        dL_dc = denom2inv * (-a * a * dL_dconic.z + 2 * a * b * dL_dconic.y + (denom - a * c) * dL_dconic.x);
+        dL_db = denom2inv * 2 * (b * c * dL_dconic.x - (denom + 2 * b * b) * dL_dconic.y + a * b * dL_dconic.z);
+
+        dcv[0] = (T.m[0][0] * T.m[0][0] * dL_da + T.m[0][0] * T.m[1][0] * dL_db + T.m[1][0] * T.m[1][0] * dL_dc);
+        dcv[3] = (T.m[0][1] * T.m[0][1] * dL_da + T.m[0][1] * T.m[1][1] * dL_db + T.m[1][1] * T.m[1][1] * dL_dc);
+        dcv[5] = (T.m[0][2] * T.m[0][2] * dL_da + T.m[0][2] * T.m[1][2] * dL_db + T.m[1][2] * T.m[1][2] * dL_dc);
+        dcv[1] = 2 * T.m[0][0] * T.m[0][1] * dL_da + (T.m[0][0] * T.m[1][1] + T.m[0][1] * T.m[1][0]) * dL_db + 2 * T.m[1][0] * T.m[1][1] * dL_dc;
+        dcv[2] = 2 * T.m[0][0] * T.m[0][2] * dL_da + (T.m[0][0] * T.m[1][2] + T.m[0][2] * T.m[1][0]) * dL_db + 2 * T.m[1][0] * T.m[1][2] * dL_dc;
+        dcv[4] = 2 * T.m[0][2] * T.m[0][1] * dL_da + (T.m[0][1] * T.m[1][2] + T.m[0][2] * T.m[1][1]) * dL_db + 2 * T.m[1][1] * T.m[1][2] * dL_dc;
+    } else {
+#pragma unroll
+        for (int i = 0; i < 6; i++) dcv[i] = 0;
+    }
+
+    float dL_dT00 = 2 * (T.m[0][0] * Vrk.m[0][0] + T.m[0][1] * Vrk.m[0][1] + T.m[0][2] * Vrk.m[0][2]) * dL_da +
+                    (T.m[1][0] * Vrk.m[0][0] + T.m[1][1] * Vrk.m[0][1] + T.m[1][2] * Vrk.m[0][2]) * dL_db;
+    float dL_dT01 = 2 * (T.m[0][0] * Vrk.m[1][0] + T.m[0][1] * Vrk.m[1][1] + T.m[0][2] * Vrk.m[1][2]) * dL_da +
+                    (T.m[1][0] * Vrk.m[1][0] + T.m[1][1] * Vrk.m[1][1] + T.m[1][2] * Vrk.m[1][2]) * dL_db;
+    float dL_dT02 = 2 * (T.m[0][0] * Vrk.m[2][0] + T.m[0][1] * Vrk.m[2][1] + T.m[0][2] * Vrk.m[2][2]) * dL_da +
+                    (T.m[1][0] * Vrk.m[2][0] + T.m[1][1] * Vrk.m[2][1] + T.m[1][2] * Vrk.m[2][2]) * dL_db;
+    float dL_dT10 = 2 * (T.m[1][0] * Vrk.m[0][0] + T.m[1][1] * Vrk.m[0][1] + T.m[1][2] * Vrk.m[0][2]) * dL_dc +
+                    (T.m[0][0] * Vrk.m[0][0] + T.m[0][1] * Vrk.m[0][1] + T.m[0][2] * Vrk.m[0][2]) * dL_db;
+    float dL_dT11 = 2 * (T.m[1][0] * Vrk.m[1][0] + T.m[1][1] * Vrk.m[1][1] + T.m[1][2] * Vrk.m[1][2]) * dL_dc +
+                    (T.m[0][0] * Vrk.m[1][0] + T.m[0][1] * Vrk.m[1][1] + T.m[0][2] * Vrk.m[1][2]) * dL_db;
+    float dL_dT12 = 2 * (T.m[1][0] * Vrk.m[2][0] + T.m[1][1] * Vrk.m[2][1] + T.m[1][2] * Vrk.m[2][2]) * dL_dc +
+                    (T.m[0][0] * Vrk.m[2][0] + T.m[0][1] * Vrk.m[2][1] + T.m[0][2] * Vrk.m[2][2]) * dL_db;
+
+    float dL_dJ00 = Wm.m[0][0] * dL_dT00 + Wm.m[0][1] * dL_dT01 + Wm.m[0][2] * dL_dT02;
+    float dL_dJ02 = Wm.m[2][0] * dL_dT00 + Wm.m[2][1] * dL_dT01 + Wm.m[2][2] * dL_dT02;
+    float dL_dJ11 = Wm.m[1][0] * dL_dT10 + Wm.m[1][1] * dL_dT11 + Wm.m[1][2] * dL_dT12;
+    float dL_dJ12 = Wm.m[2][0] * dL_dT10 + Wm.m[2][1] * dL_dT11 + Wm.m[2][2] * dL_dT12;
+
+    float tz = 1.f / tt.z;
+    float tz2 = tz * tz;
+    float tz3 = tz2 * tz;
+
+    float dL_dtx = x_grad_mul * -h_x * tz2 * dL_dJ02;
+    float dL_dty = y_grad_mul * -h_y * tz2 * dL_dJ12;
+    float dL_dtz = -h_x * tz2 * dL_dJ00 - h_y * tz2 * dL_dJ11 + (2 * h_x * tt.x) * tz3 * dL_dJ02 + (2 * h_y * tt.y) * tz3 * dL_dJ12;
+
+    float3 dL_dmean = transform_vec_4x3_transpose({dL_dtx, dL_dty, dL_dtz}, view_matrix);
+
+    // ---- projection of the 2-D mean
+    float4 m_hom = transform_point_4x4(mean, proj);
+    float m_w = 1.0f / (m_hom.w + 0.0000001f);
+    float mul1 = (proj[0] * mean.x + proj[4] * mean.y + proj[8] * mean.z + proj[12]) * m_w * m_w;
+    float mul2 = (proj[1] * mean.x + proj[5] * mean.y + proj[9] * mean.z + proj[13]) * m_w * m_w;
+    float3 dL_dmean_b;
+    dL_dmean_b.x = (proj[0] * m_w - proj[3] * mul1) * dm2.x + (proj[1] * m_w - proj[3] * mul2) * dm2.y;
+    dL_dmean_b.y = (proj[4] * m_w - proj[7] * mul1) * dm2.x + (proj[5] * m_w - proj[7] * mul2) * dm2.y;
+    dL_dmean_b.z = (proj[8] * m_w - proj[11] * mul1) * dm2.x + (proj[9] * m_w - proj[11] * mul2) * dm2.y;
+    g_mean.x += dL_dmean.x + dL_dmean_b.x;
+        g_mean.y += dL_dmean.y + dL_dmean_b.y;
+        g_mean.z += dL_dmean.z + dL_dmean_b.z;
+#pragma unroll
+        for (int i = 0; i < 6; i++) dL_dcov[i] += dcv[i];
+}
+
+// Backward of scale / (unnormalised) quaternion -> 3-D covariance; dL_dcov is the cotangent of its six entries.
+__device__ __forceinline__ void bwd_cov3d(const float3 sc, const float scale_modifier, const float4 rot,
+                                          const float* dL_dcov, float3& g_scale, float4& g_rot)
+{
+    // ---- cov3D -> scale, quaternion (quaternion treated as given, not normalised)
+    float r = rot.x, x = rot.y, y = rot.z, z = rot.w;
+    Mat3 R;
+    R.m[0][0] = 1.f - 2.f * (y * y + z * z); R.m[0][1] = 2.f * (x * y - r * z); R.m[0][2] = 2.f * (x * z + r * y);
+    R.m[1][0] = 2.f * (x * y + r * z); R.m[1][1] = 1.f - 2.f * (x * x + z * z); R.m[1][2] = 2.f * (y * z - r * x);
+    R.m[2][0] = 2.f * (x * z - r * y); R.m[2][1] = 2.f * (y * z + r * x); R.m[2][2] = 1.f - 2.f * (x * x + y * y);
+    Mat3 S;
+#pragma unroll
+    for (int cc = 0; cc < 3; cc++)
+#pragma unroll
+        for (int rr = 0; rr < 3; rr++) S.m[cc][rr] = 0.0f;
+    float3 s = {scale_modifier * sc.x, scale_modifier * sc.y, scale_modifier * sc.z};
+    S.m[0][0] = s.x; S.m[1][1] = s.y; S.m[2][2] = s.z;
+    Mat3 M = mul(S, R);
+    Mat3 dL_dSigma;
+    dL_dSigma.m[0][0] = dL_dcov[0]; dL_dSigma.m[0][1] = 0.5f * dL_dcov[1]; dL_dSigma.m[0][2] = 0.5f * dL_dcov[2];
+    dL_dSigma.m[1][0] = 0.5f * dL_dcov[1]; dL_dSigma.m[1][1] = dL_dcov[3]; dL_dSigma.m[1][2] = 0.5f * dL_dcov[4];
+    dL_dSigma.m[2][0] = 0.5f * dL_dcov[2]; dL_dSigma.m[2][1] = 0.5f * dL_dcov[4]; dL_dSigma.m[2][2] = dL_dcov[5];
+    Mat3 M2;
+#pragma unroll
+    for (int cc = 0; cc < 3; cc++)
+#pragma unroll
+        for (int rr = 0; rr < 3; rr++) M2.m[cc][rr] = 2.0f * M.m[cc][rr];
+    Mat3 dL_dM = mul(M2, dL_dSigma);
+    Mat3 Rt = transpose(R);
+    Mat3 dL_dMt = transpose(dL_dM);
+
+    g_scale.x = Rt.m[0][0] * dL_dMt.m[0][0] + Rt.m[0][1] * dL_dMt.m[0][1] + Rt.m[0][2] * dL_dMt.m[0][2];
+    g_scale.y = Rt.m[1][0] * dL_dMt.m[1][0] + Rt.m[1][1] * dL_dMt.m[1][1] + Rt.m[1][2] * dL_dMt.m[1][2];
+    g_scale.z = Rt.m[2][0] * dL_dMt.m[2][0] + Rt.m[2][1] * dL_dMt.m[2][1] + Rt.m[2][2] * dL_dMt.m[2][2];
+
+#pragma unroll
+    for (int rr = 0; rr < 3; rr++) {
+        dL_dMt.m[0][rr] *= s.x;
+        dL_dMt.m[1][rr] *= s.y;
+        dL_dMt.m[2][rr] *= s.z;
+    }
+    g_rot.x = 2 * z * (dL_dMt.m[0][1] - dL_dMt.m[1][0]) + 2 * y * (dL_dMt.m[2][0] - dL_dMt.m[0][2]) + 2 * x * (dL_dMt.m[1][2] - dL_dMt.m[2][1]);
+    g_rot.y = 2 * y * (dL_dMt.m[1][0] + dL_dMt.m[0][1]) + 2 * z * (dL_dMt.m[2][0] + dL_dMt.m[0][2]) + 2 * r * (dL_dMt.m[1][2] - dL_dMt.m[2][1]) - 4 * x * (dL_dMt.m[2][2] + dL_dMt.m[1][1]);
+    g_rot.z = 2 * x * (dL_dMt.m[1][0] + dL_dMt.m[0][1]) + 2 * r * (dL_dMt.m[2][0] - dL_dMt.m[0][2]) + 2 * z * (dL_dMt.m[1][2] + dL_dMt.m[2][1]) - 4 * y * (dL_dMt.m[2][2] + dL_dMt.m[0][0]);
+    g_rot.w = 2 * r * (dL_dMt.m[0][1] - dL_dMt.m[1][0]) + 2 * x * (dL_dMt.m[2][0] + dL_dMt.m[0][2]) + 2 * y * (dL_dMt.m[1][2] + dL_dMt.m[2][1]) - 4 * z * (dL_dMt.m[1][1] + dL_dMt.m[0][0]);
+}
+
 // Fused backward of the per-Gaussian stage: d(conic) -> d(cov2D) -> d(cov3D), d(mean) through the EWA
 // Jacobian and through the projection of the 2-D mean, then d(cov3D) -> d(scale), d(quaternion).
 // The 3-D covariance is recomputed from scale/rotation (same function as the forward, so same bits)
@@ -335,138 +484,10 @@ preprocess_bwd_kernel(int P, const float* __restrict__ means3D, const float* __r
             float cov3D[6];
             compute_cov3d(sc, scale_modifier, rot, cov3D);
 
-            // ---- conic -> cov2D -> cov3D and mean (EWA part)
-            float3 dL_dconic = {dco.x, dco.y, dco.z};
-            float3 tt = transform_point_4x3(mean, view_matrix);
-            const float limx = 1.3f * tan_fovx;
-            const float limy = 1.3f * tan_fovy;
-            const float txtz = tt.x / tt.z;
-            const float tytz = tt.y / tt.z;
-            tt.x = min(limx, max(-limx, txtz)) * tt.z;
-            tt.y = min(limy, max(-limy, tytz)) * tt.z;
-            const float x_grad_mul = txtz < -limx || txtz > limx ? 0 : 1;
-            const float y_grad_mul = tytz < -limy || tytz > limy ? 0 : 1;
-
-            Mat3 J;
-            J.m[0][0] = h_x / tt.z; J.m[0][1] = 0.0f; J.m[0][2] = -(h_x * tt.x) / (tt.z * tt.z);
-            J.m[1][0] = 0.0f; J.m[1][1] = h_y / tt.z; J.m[1][2] = -(h_y * tt.y) / (tt.z * tt.z);
-            J.m[2][0] = 0; J.m[2][1] = 0; J.m[2][2] = 0;
-            Mat3 Wm;
-            Wm.m[0][0] = view_matrix[0]; Wm.m[0][1] = view_matrix[4]; Wm.m[0][2] = view_matrix[8];
-            Wm.m[1][0] = view_matrix[1]; Wm.m[1][1] = view_matrix[5]; Wm.m[1][2] = view_matrix[9];
-            Wm.m[2][0] = view_matrix[2]; Wm.m[2][1] = view_matrix[6]; Wm.m[2][2] = view_matrix[10];
-            Mat3 Vrk;
-            Vrk.m[0][0] = cov3D[0]; Vrk.m[0][1] = cov3D[1]; Vrk.m[0][2] = cov3D[2];
-            Vrk.m[1][0] = cov3D[1]; Vrk.m[1][1] = cov3D[3]; Vrk.m[1][2] = cov3D[4];
-            Vrk.m[2][0] = cov3D[2]; Vrk.m[2][1] = cov3D[4]; Vrk.m[2][2] = cov3D[5];
-            Mat3 T = mul(Wm, J);
-            Mat3 cov2D = mul(mul(transpose(T), transpose(Vrk)), T);
-
-            float a = cov2D.m[0][0] += 0.3f;
-            float b = cov2D.m[0][1];
-            float c = cov2D.m[1][1] += 0.3f;
-
-            float denom = a * c - b * b;
-            float dL_da = 0, dL_db = 0, dL_dc = 0;
-            float denom2inv = 1.0f / ((denom * denom) + 0.0000001f);
-            float dL_dcov[6];
-            if (denom2inv != 0) {
-                dL_da = denom2inv * (-c * c * dL_dconic.x + 2 * b * c * dL_dconic.y + (denom - a * c) * dL_dconic.z);
-                dL_dc = denom2inv * (-a * a * dL_dconic.z + 2 * a * b * dL_dconic.y + (denom - a * c) * dL_dconic.x);
-                dL_db = denom2inv * 2 * (b * c * dL_dconic.x - (denom + 2 * b * b) * dL_dconic.y + a * b * dL_dconic.z);
-
-                dL_dcov[0] = (T.m[0][0] * T.m[0][0] * dL_da + T.m[0][0] * T.m[1][0] * dL_db + T.m[1][0] * T.m[1][0] * dL_dc);
-                dL_dcov[3] = (T.m[0][1] * T.m[0][1] * dL_da + T.m[0][1] * T.m[1][1] * dL_db + T.m[1][1] * T.m[1][1] * dL_dc);
-                dL_dcov[5] = (T.m[0][2] * T.m[0][2] * dL_da + T.m[0][2] * T.m[1][2] * dL_db + T.m[1][2] * T.m[1][2] * dL_dc);
-                dL_dcov[1] = 2 * T.m[0][0] * T.m[0][1] * dL_da + (T.m[0][0] * T.m[1][1] + T.m[0][1] * T.m[1][0]) * dL_db + 2 * T.m[1][0] * T.m[1][1] * dL_dc;
-                dL_dcov[2] = 2 * T.m[0][0] * T.m[0][2] * dL_da + (T.m[0][0] * T.m[1][2] + T.m[0][2] * T.m[1][0]) * dL_db + 2 * T.m[1][0] * T.m[1][2] * dL_dc;
-                dL_dcov[4] = 2 * T.m[0][2] * T.m[0][1] * dL_da + (T.m[0][1] * T.m[1][2] + T.m[0][2] * T.m[1][1]) * dL_db + 2 * T.m[1][1] * T.m[1][2] * dL_dc;
-            } else {
-#pragma unroll
-                for (int i = 0; i < 6; i++) dL_dcov[i] = 0;
-            }
-
-            float dL_dT00 = 2 * (T.m[0][0] * Vrk.m[0][0] + T.m[0][1] * Vrk.m[0][1] + T.m[0][2] * Vrk.m[0][2]) * dL_da +
-                            (T.m[1][0] * Vrk.m[0][0] + T.m[1][1] * Vrk.m[0][1] + T.m[1][2] * Vrk.m[0][2]) * dL_db;
-            float dL_dT01 = 2 * (T.m[0][0] * Vrk.m[1][0] + T.m[0][1] * Vrk.m[1][1] + T.m[0][2] * Vrk.m[1][2]) * dL_da +
-                            (T.m[1][0] * Vrk.m[1][0] + T.m[1][1] * Vrk.m[1][1] + T.m[1][2] * Vrk.m[1][2]) * dL_db;
-            float dL_dT02 = 2 * (T.m[0][0] * Vrk.m[2][0] + T.m[0][1] * Vrk.m[2][1] + T.m[0][2] * Vrk.m[2][2]) * dL_da +
-                            (T.m[1][0] * Vrk.m[2][0] + T.m[1][1] * Vrk.m[2][1] + T.m[1][2] * Vrk.m[2][2]) * dL_db;
-            float dL_dT10 = 2 * (T.m[1][0] * Vrk.m[0][0] + T.m[1][1] * Vrk.m[0][1] + T.m[1][2] * Vrk.m[0][2]) * dL_dc +
-                            (T.m[0][0] * Vrk.m[0][0] + T.m[0][1] * Vrk.m[0][1] + T.m[0][2] * Vrk.m[0][2]) * dL_db;
-            float dL_dT11 = 2 * (T.m[1][0] * Vrk.m[1][0] + T.m[1][1] * Vrk.m[1][1] + T.m[1][2] * Vrk.m[1][2]) * dL_dc +
-                            (T.m[0][0] * Vrk.m[1][0] + T.m[0][1] * Vrk.m[1][1] + T.m[0][2] * Vrk.m[1][2]) * dL_db;
-            float dL_dT12 = 2 * (T.m[1][0] * Vrk.m[2][0] + T.m[1][1] * Vrk.m[2][1] + T.m[1][2] * Vrk.m[2][2]) * dL_dc +
-                            (T.m[0][0] * Vrk.m[2][0] + T.m[0][1] * Vrk.m[2][1] + T.m[0][2] * Vrk.m[2][2]) * dL_db;
-
-            float dL_dJ00 = Wm.m[0][0] * dL_dT00 + Wm.m[0][1] * dL_dT01 + Wm.m[0][2] * dL_dT02;
-            float dL_dJ02 = Wm.m[2][0] * dL_dT00 + Wm.m[2][1] * dL_dT01 + Wm.m[2][2] * dL_dT02;
-            float dL_dJ11 = Wm.m[1][0] * dL_dT10 + Wm.m[1][1] * dL_dT11 + Wm.m[1][2] * dL_dT12;
-            float dL_dJ12 = Wm.m[2][0] * dL_dT10 + Wm.m[2][1] * dL_dT11 + Wm.m[2][2] * dL_dT12;
-
-            float tz = 1.f / tt.z;
-            float tz2 = tz * tz;
-            float tz3 = tz2 * tz;
-
-            float dL_dtx = x_grad_mul * -h_x * tz2 * dL_dJ02;
-            float dL_dty = y_grad_mul * -h_y * tz2 * dL_dJ12;
-            float dL_dtz = -h_x * tz2 * dL_dJ00 - h_y * tz2 * dL_dJ11 + (2 * h_x * tt.x) * tz3 * dL_dJ02 + (2 * h_y * tt.y) * tz3 * dL_dJ12;
-
-            float3 dL_dmean = transform_vec_4x3_transpose({dL_dtx, dL_dty, dL_dtz}, view_matrix);
-
-            // ---- projection of the 2-D mean
-            float4 m_hom = transform_point_4x4(mean, proj);
-            float m_w = 1.0f / (m_hom.w + 0.0000001f);
-            const float2 dm2 = __ldg(dL_dmean2D + idx);
-            float mul1 = (proj[0] * mean.x + proj[4] * mean.y + proj[8] * mean.z + proj[12]) * m_w * m_w;
-            float mul2 = (proj[1] * mean.x + proj[5] * mean.y + proj[9] * mean.z + proj[13]) * m_w * m_w;
-            float3 dL_dmean_b;
-            dL_dmean_b.x = (proj[0] * m_w - proj[3] * mul1) * dm2.x + (proj[1] * m_w - proj[3] * mul2) * dm2.y;
-            dL_dmean_b.y = (proj[4] * m_w - proj[7] * mul1) * dm2.x + (proj[5] * m_w - proj[7] * mul2) * dm2.y;
-            dL_dmean_b.z = (proj[8] * m_w - proj[11] * mul1) * dm2.x + (proj[9] * m_w - proj[11] * mul2) * dm2.y;
-            g_mean = {dL_dmean.x + dL_dmean_b.x, dL_dmean.y + dL_dmean_b.y, dL_dmean.z + dL_dmean_b.z};
-
-            // ---- cov3D -> scale, quaternion (quaternion treated as given, not normalised)
-            float r = rot.x, x = rot.y, y = rot.z, z = rot.w;
-            Mat3 R;
-            R.m[0][0] = 1.f - 2.f * (y * y + z * z); R.m[0][1] = 2.f * (x * y - r * z); R.m[0][2] = 2.f * (x * z + r * y);
-            R.m[1][0] = 2.f * (x * y + r * z); R.m[1][1] = 1.f - 2.f * (x * x + z * z); R.m[1][2] = 2.f * (y * z - r * x);
-            R.m[2][0] = 2.f * (x * z - r * y); R.m[2][1] = 2.f * (y * z + r * x); R.m[2][2] = 1.f - 2.f * (x * x + y * y);
-            Mat3 S;
-#pragma unroll
-            for (int cc = 0; cc < 3; cc++)
-#pragma unroll
-                for (int rr = 0; rr < 3; rr++) S.m[cc][rr] = 0.0f;
-            float3 s = {scale_modifier * sc.x, scale_modifier * sc.y, scale_modifier * sc.z};
-            S.m[0][0] = s.x; S.m[1][1] = s.y; S.m[2][2] = s.z;
-            Mat3 M = mul(S, R);
-            Mat3 dL_dSigma;
-            dL_dSigma.m[0][0] = dL_dcov[0]; dL_dSigma.m[0][1] = 0.5f * dL_dcov[1]; dL_dSigma.m[0][2] = 0.5f * dL_dcov[2];
-            dL_dSigma.m[1][0] = 0.5f * dL_dcov[1]; dL_dSigma.m[1][1] = dL_dcov[3]; dL_dSigma.m[1][2] = 0.5f * dL_dcov[4];
-            dL_dSigma.m[2][0] = 0.5f * dL_dcov[2]; dL_dSigma.m[2][1] = 0.5f * dL_dcov[4]; dL_dSigma.m[2][2] = dL_dcov[5];
-            Mat3 M2;
-#pragma unroll
-            for (int cc = 0; cc < 3; cc++)
-#pragma unroll
-                for (int rr = 0; rr < 3; rr++) M2.m[cc][rr] = 2.0f * M.m[cc][rr];
-            Mat3 dL_dM = mul(M2, dL_dSigma);
-            Mat3 Rt = transpose(R);
-            Mat3 dL_dMt = transpose(dL_dM);
-
-            g_scale.x = Rt.m[0][0] * dL_dMt.m[0][0] + Rt.m[0][1] * dL_dMt.m[0][1] + Rt.m[0][2] * dL_dMt.m[0][2];
-            g_scale.y = Rt.m[1][0] * dL_dMt.m[1][0] + Rt.m[1][1] * dL_dMt.m[1][1] + Rt.m[1][2] * dL_dMt.m[1][2];
-            g_scale.z = Rt.m[2][0] * dL_dMt.m[2][0] + Rt.m[2][1] * dL_dMt.m[2][1] + Rt.m[2][2] * dL_dMt.m[2][2];
-
-#pragma unroll
-            for (int rr = 0; rr < 3; rr++) {
-                dL_dMt.m[0][rr] *= s.x;
-                dL_dMt.m[1][rr] *= s.y;
-                dL_dMt.m[2][rr] *= s.z;
-            }
-            g_rot.x = 2 * z * (dL_dMt.m[0][1] - dL_dMt.m[1][0]) + 2 * y * (dL_dMt.m[2][0] - dL_dMt.m[0][2]) + 2 * x * (dL_dMt.m[1][2] - dL_dMt.m[2][1]);
-            g_rot.y = 2 * y * (dL_dMt.m[1][0] + dL_dMt.m[0][1]) + 2 * z * (dL_dMt.m[2][0] + dL_dMt.m[0][2]) + 2 * r * (dL_dMt.m[1][2] - dL_dMt.m[2][1]) - 4 * x * (dL_dMt.m[2][2] + dL_dMt.m[1][1]);
-            g_rot.z = 2 * x * (dL_dMt.m[1][0] + dL_dMt.m[0][1]) + 2 * r * (dL_dMt.m[2][0] - dL_dMt.m[0][2]) + 2 * z * (dL_dMt.m[1][2] + dL_dMt.m[2][1]) - 4 * y * (dL_dMt.m[2][2] + dL_dMt.m[0][0]);
-            g_rot.w = 2 * r * (dL_dMt.m[0][1] - dL_dMt.m[1][0]) + 2 * x * (dL_dMt.m[2][0] + dL_dMt.m[0][2]) + 2 * y * (dL_dMt.m[1][2] + dL_dMt.m[2][1]) - 4 * z * (dL_dMt.m[1][1] + dL_dMt.m[0][0]);
+            float dL_dcov[6] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            bwd_project_one(mean, cov3D, view_matrix, proj, h_x, h_y, tan_fovx, tan_fovy, dco,
+                            __ldg(dL_dmean2D + idx), g_mean, dL_dcov);
+            bwd_cov3d(sc, scale_modifier, rot, dL_dcov, g_scale, g_rot);
         }
         dL_drots[idx] = g_rot;
     }
@@ -480,7 +501,169 @@ preprocess_bwd_kernel(int P, const float* __restrict__ means3D, const float* __r
     block_store_rows<3>(dL_dscales + (size_t)base * 3, s_scale, count, vec_mask & 16);
 }
 
+// ------------------------------------------------------------------------------------------------ batched over cameras
+// The caller's per-camera loop around preprocess (gaussian_renderer/__init__.py:966-1023) as one launch: every
+// Gaussian's parameters are read ONCE and projected into all B cameras of the batch; the backward reads them once
+// and writes the gradients summed over the cameras once (instead of B partial results added up by autograd).
+constexpr int MAX_CAMS = 16;
+
+struct CamBatch {
+    int B;
+    const float* view[MAX_CAMS];   // device pointers to the 4x4 matrices
+    const float* proj[MAX_CAMS];
+    float tan_fovx[MAX_CAMS], tan_fovy[MAX_CAMS], focal_x[MAX_CAMS], focal_y[MAX_CAMS];
+    int W[MAX_CAMS], H[MAX_CAMS];
+};
+struct CamOutputs {
+    float2* means2D[MAX_CAMS];
+    float* depths[MAX_CAMS];
+    int* radii[MAX_CAMS];
+    float4* conic_opacity[MAX_CAMS];
+};
+struct CamCotangents {
+    const int* radii[MAX_CAMS];
+    const float2* dL_dmeans2D[MAX_CAMS];
+    const float4* dL_dconic_opacity[MAX_CAMS];
+};
+
+__global__ void __launch_bounds__(CGX_BLOCK_SIZE)
+preprocess_fwd_batched_kernel(int P, const float* __restrict__ means3D, const float* __restrict__ scales,
+                              const float scale_modifier, const float* __restrict__ rotations,
+                              const float* __restrict__ opacities, CamBatch cams, CamOutputs outs, int vec_mask)
+{
+    __shared__ __align__(16) float s_mean[CGX_BLOCK_SIZE * 3];
+    __shared__ __align__(16) float s_scale[CGX_BLOCK_SIZE * 3];
+    __shared__ __align__(16) float s_rot[CGX_BLOCK_SIZE * 4];
+    __shared__ float s_view[MAX_CAMS][16];
+    __shared__ float s_proj[MAX_CAMS][16];
+
+    const int base = blockIdx.x * CGX_BLOCK_SIZE;
+    const int count = min(CGX_BLOCK_SIZE, P - base);
+    for (int i = threadIdx.x; i < cams.B * 32; i += blockDim.x) {
+        const int b = i >> 5, e = i & 31;
+        if (e < 16) s_view[b][e] = cams.view[b][e];
+        else s_proj[b][e - 16] = cams.proj[b][e - 16];
+    }
+    block_load_rows<3>(means3D + (size_t)base * 3, s_mean, count, vec_mask & 1);
+    block_load_rows<3>(scales + (size_t)base * 3, s_scale, count, vec_mask & 2);
+    block_load_rows<4>(rotations + (size_t)base * 4, s_rot, count, vec_mask & 4);
+    __syncthreads();
+
+    const int t = threadIdx.x;
+    if (t >= count) return;
+    const int idx = base + t;
+    const float3 p_orig = {s_mean[3 * t], s_mean[3 * t + 1], s_mean[3 * t + 2]};
+    const float3 sc = {s_scale[3 * t], s_scale[3 * t + 1], s_scale[3 * t + 2]};
+    const float4 q = {s_rot[4 * t], s_rot[4 * t + 1], s_rot[4 * t + 2], s_rot[4 * t + 3]};
+    const float opacity = __ldg(opacities + idx);
+    float cov3D[6];
+    compute_cov3d(sc, scale_modifier, q, cov3D);   // camera independent
+
+#pragma unroll 1
+    for (int b = 0; b < cams.B; b++) {
+        const float* viewmatrix = s_view[b];
+        const float* projmatrix = s_proj[b];
+        const int W = cams.W[b], H = cams.H[b];
+        int out_radius = 0;
+        float2 out_xy = {0.f, 0.f};
+        float out_depth = 0.f;
+        float4 out_co = {0.f, 0.f, 0.f, 0.f};
+        do {
+            float4 p_hom = transform_point_4x4(p_orig, projmatrix);
+            float p_w = 1.0f / (p_hom.w + 0.0000001f);
+            float3 p_proj = {p_hom.x * p_w, p_hom.y * p_w, p_hom.z * p_w};
+            float3 p_view = transform_point_4x3(p_orig, viewmatrix);
+            if (p_view.z <= 0.0f) break;
+            float3 cov = compute_cov2d(p_orig, cams.focal_x[b], cams.focal_y[b], cams.tan_fovx[b], cams.tan_fovy[b],
+                                       cov3D, viewmatrix);
+            float det = (cov.x * cov.z - cov.y * cov.y);
+            if (det == 0.0f) break;
+            float det_inv = 1.f / det;
+            float3 conic = {cov.z * det_inv, -cov.y * det_inv, cov.x * det_inv};
+            float mid = 0.5f * (cov.x + cov.z);
+            float lambda1 = mid + sqrt(max(0.1f, mid * mid - det));
+            float lambda2 = mid - sqrt(max(0.1f, mid * mid - det));
+            float my_radius = ceil(3.f * sqrt(max(lambda1, lambda2)));
+            float2 point_image = {ndc2pix(p_proj.x, W), ndc2pix(p_proj.y, H)};
+            uint2 rect_min, rect_max;
+            get_rect(point_image, my_radius, rect_min, rect_max, (W + CGX_BLOCK_X - 1) / CGX_BLOCK_X,
+                     (H + CGX_BLOCK_Y - 1) / CGX_BLOCK_Y);
+            if ((rect_max.x - rect_min.x) * (rect_max.y - rect_min.y) == 0) break;
+            out_depth = p_view.z;
+            out_radius = my_radius;
+            out_xy = point_image;
+            out_co = {conic.x, conic.y, conic.z, opacity};
+        } while (0);
+        outs.radii[b][idx] = out_radius;
+        outs.means2D[b][idx] = out_xy;
+        outs.depths[b][idx] = out_depth;
+        outs.conic_opacity[b][idx] = out_co;
+    }
+}
+
+__global__ void __launch_bounds__(CGX_BLOCK_SIZE)
+preprocess_bwd_batched_kernel(int P, const float* __restrict__ means3D, const float* __restrict__ scales,
+                              const float scale_modifier, const float* __restrict__ rotations, CamBatch cams,
+                              CamCotangents cot, float* __restrict__ dL_dmeans, float* __restrict__ dL_dscales,
+                              float4* __restrict__ dL_drots, float* __restrict__ dL_dopacity, int vec_mask)
+{
+    __shared__ __align__(16) float s_mean[CGX_BLOCK_SIZE * 3];   // reused for dL_dmeans
+    __shared__ __align__(16) float s_scale[CGX_BLOCK_SIZE * 3];  // reused for dL_dscales
+    __shared__ __align__(16) float s_rot[CGX_BLOCK_SIZE * 4];
+    __shared__ float s_view[MAX_CAMS][16];
+    __shared__ float s_proj[MAX_CAMS][16];
+
+    const int base = blockIdx.x * CGX_BLOCK_SIZE;
+    const int count = min(CGX_BLOCK_SIZE, P - base);
+    for (int i = threadIdx.x; i < cams.B * 32; i += blockDim.x) {
+        const int b = i >> 5, e = i & 31;
+        if (e < 16) s_view[b][e] = cams.view[b][e];
+        else s_proj[b][e - 16] = cams.proj[b][e - 16];
+    }
+    block_load_rows<3>(means3D + (size_t)base * 3, s_mean, count, vec_mask & 1);
+    block_load_rows<3>(scales + (size_t)base * 3, s_scale, count, vec_mask & 2);
+    block_load_rows<4>(rotations + (size_t)base * 4, s_rot, count, vec_mask & 4);
+    __syncthreads();
+
+    const int t = threadIdx.x;
+    const int idx = base + t;
+    float3 g_mean = {0.f, 0.f, 0.f}, g_scale = {0.f, 0.f, 0.f};
+    float4 g_rot = {0.f, 0.f, 0.f, 0.f};
+    if (t < count) {
+        const float3 mean = {s_mean[3 * t], s_mean[3 * t + 1], s_mean[3 * t + 2]};
+        const float3 sc = {s_scale[3 * t], s_scale[3 * t + 1], s_scale[3 * t + 2]};
+        const float4 rot = {s_rot[4 * t], s_rot[4 * t + 1], s_rot[4 * t + 2], s_rot[4 * t + 3]};
+        float cov3D[6];
+        compute_cov3d(sc, scale_modifier, rot, cov3D);
+        float dL_dcov[6] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        float g_op = 0.f;
+        bool any = false;
+#pragma unroll 1
+        for (int b = 0; b < cams.B; b++) {
+            const float4 dco = __ldg(cot.dL_dconic_opacity[b] + idx);
+            g_op += dco.w;
+            if (cot.radii[b][idx] > 0) {
+                any = true;
+                bwd_project_one(mean, cov3D, s_view[b], s_proj[b], cams.focal_x[b], cams.focal_y[b], cams.tan_fovx[b],
+                                cams.tan_fovy[b], dco, __ldg(cot.dL_dmeans2D[b] + idx), g_mean, dL_dcov);
+            }
+        }
+        if (any) bwd_cov3d(sc, scale_modifier, rot, dL_dcov, g_scale, g_rot);   // linear in dL_dcov: once for all cameras
+        dL_dopacity[idx] = g_op;
+        dL_drots[idx] = g_rot;
+    }
+    __syncthreads();
+    if (t < count) {
+        s_mean[3 * t] = g_mean.x; s_mean[3 * t + 1] = g_mean.y; s_mean[3 * t + 2] = g_mean.z;
+        s_scale[3 * t] = g_scale.x; s_scale[3 * t + 1] = g_scale.y; s_scale[3 * t + 2] = g_scale.z;
+    }
+    __syncthreads();
+    block_store_rows<3>(dL_dmeans + (size_t)base * 3, s_mean, count, vec_mask & 8);
+    block_store_rows<3>(dL_dscales + (size_t)base * 3, s_scale, count, vec_mask & 16);
+}
+
 }  // namespace cgx
+
 
 using namespace cgx;
 
@@ -584,5 +767,82 @@ extern "C" int cgx_all_map_fwd(int P, const float* means3D, const float* scales,
         return CGX_EINVAL;
     all_map_kernel<<<(P + 255) / 256, 256, 0, (cudaStream_t)stream>>>(P, means3D, scales, (const float4*)rotations,
                                                                       radii, viewmatrix, campos, all_map);
+    return check_launch();
+}
+
+static int fill_cams(CamBatch& cb, int B, const cgx_camera* cams)
+{
+    if (B <= 0 || B > MAX_CAMS || !cams) return CGX_EINVAL;
+    cb.B = B;
+    for (int b = 0; b < B; b++) {
+        if (!cams[b].viewmatrix || !cams[b].projmatrix || cams[b].W <= 0 || cams[b].H <= 0) return CGX_EINVAL;
+        cb.view[b] = cams[b].viewmatrix;
+        cb.proj[b] = cams[b].projmatrix;
+        cb.tan_fovx[b] = cams[b].tanfovx;
+        cb.tan_fovy[b] = cams[b].tanfovy;
+        cb.focal_y[b] = cams[b].H / (2.0f * cams[b].tanfovy);
+        cb.focal_x[b] = cams[b].W / (2.0f * cams[b].tanfovx);
+        cb.W[b] = cams[b].W;
+        cb.H[b] = cams[b].H;
+    }
+    return CGX_OK;
+}
+
+extern "C" int cgx_preprocess_fwd_batched(int P, int B, const float* means3D, const float* scales,
+                                          float scale_modifier, const float* rotations, const float* opacities,
+                                          const cgx_camera* cams, float* const* means2D, float* const* depths,
+                                          int32_t* const* radii, float* const* conic_opacity, void* stream)
+{
+    if (P < 0) return CGX_EINVAL;
+    CamBatch cb;
+    int st = fill_cams(cb, B, cams);
+    if (st != CGX_OK) return st;
+    if (P == 0) return CGX_OK;
+    if (!means3D || !scales || !rotations || !opacities || !means2D || !depths || !radii || !conic_opacity)
+        return CGX_EINVAL;
+    CamOutputs o;
+    for (int b = 0; b < B; b++) {
+        if (!means2D[b] || !depths[b] || !radii[b] || !conic_opacity[b]) return CGX_EINVAL;
+        if (((uintptr_t)means2D[b] & 7) || !aligned16(conic_opacity[b])) return CGX_EINVAL;
+        o.means2D[b] = (float2*)means2D[b];
+        o.depths[b] = depths[b];
+        o.radii[b] = radii[b];
+        o.conic_opacity[b] = (float4*)conic_opacity[b];
+    }
+    const int vec_mask = (aligned16(means3D) ? 1 : 0) | (aligned16(scales) ? 2 : 0) | (aligned16(rotations) ? 4 : 0);
+    preprocess_fwd_batched_kernel<<<(P + CGX_BLOCK_SIZE - 1) / CGX_BLOCK_SIZE, CGX_BLOCK_SIZE, 0,
+                                    (cudaStream_t)stream>>>(P, means3D, scales, scale_modifier, rotations, opacities, cb,
+                                                            o, vec_mask);
+    return check_launch();
+}
+
+extern "C" int cgx_preprocess_bwd_batched(int P, int B, const float* means3D, const float* scales,
+                                          float scale_modifier, const float* rotations, const cgx_camera* cams,
+                                          const int32_t* const* radii, const float* const* dL_dmeans2D,
+                                          const float* const* dL_dconic_opacity, float* dL_dmeans3D, float* dL_dscales,
+                                          float* dL_drotations, float* dL_dopacity, void* stream)
+{
+    if (P < 0) return CGX_EINVAL;
+    CamBatch cb;
+    int st = fill_cams(cb, B, cams);
+    if (st != CGX_OK) return st;
+    if (P == 0) return CGX_OK;
+    if (!means3D || !scales || !rotations || !radii || !dL_dmeans2D || !dL_dconic_opacity || !dL_dmeans3D ||
+        !dL_dscales || !dL_drotations || !dL_dopacity || !aligned16(dL_drotations))
+        return CGX_EINVAL;
+    CamCotangents c;
+    for (int b = 0; b < B; b++) {
+        if (!radii[b] || !dL_dmeans2D[b] || !dL_dconic_opacity[b]) return CGX_EINVAL;
+        if (((uintptr_t)dL_dmeans2D[b] & 7) || !aligned16(dL_dconic_opacity[b])) return CGX_EINVAL;
+        c.radii[b] = radii[b];
+        c.dL_dmeans2D[b] = (const float2*)dL_dmeans2D[b];
+        c.dL_dconic_opacity[b] = (const float4*)dL_dconic_opacity[b];
+    }
+    const int vec_mask = (aligned16(means3D) ? 1 : 0) | (aligned16(scales) ? 2 : 0) | (aligned16(rotations) ? 4 : 0) |
+                         (aligned16(dL_dmeans3D) ? 8 : 0) | (aligned16(dL_dscales) ? 16 : 0);
+    preprocess_bwd_batched_kernel<<<(P + CGX_BLOCK_SIZE - 1) / CGX_BLOCK_SIZE, CGX_BLOCK_SIZE, 0,
+                                    (cudaStream_t)stream>>>(P, means3D, scales, scale_modifier, rotations, cb, c,
+                                                            dL_dmeans3D, dL_dscales, (float4*)dL_drotations,
+                                                            dL_dopacity, vec_mask);
     return check_launch();
 }

@@ -12,7 +12,8 @@
 //    ballot, and blends only the survivors;
 //  * the per-tile statistics (sum of per-pixel counters) are reduced in the epilogue;
 //  * the backward reduces the 16 gradient terms of a Gaussian over the warp's 32 pixels with a
-//    transposing butterfly (16 shuffles) and issues ONE atomic per term per warp, straight into the
+//    transposing butterfly (16 shuffles) and issues ONE atomic per term per warp (visits with only one or two
+//    contributing pixels issue their atomics directly, which costs fewer issue slots), straight into the
 //    caller's gradient tensors (which also performs the (P,2,2)+(P,1) -> (P,4) repack).
 //
 // Every wait on an mbarrier is bounded: when the limit is hit the CTA records an error in the device
@@ -130,7 +131,7 @@ struct FwdSmem {
 };
 
 template <bool CULL>
-__global__ void __launch_bounds__(RENDER_THREADS)
+__global__ void __launch_bounds__(RENDER_THREADS, 4)
 render_fwd_kernel(const uint2* __restrict__ ranges, const uint32_t* __restrict__ point_list, int W, int H,
                   const float focal_x, const float focal_y, const float cx, const float cy,
                   const Record* __restrict__ records, float* __restrict__ final_T, uint32_t* __restrict__ n_contrib,
@@ -428,7 +429,7 @@ __device__ __forceinline__ float warp_reduce16(float (&v)[16], int lane)
 }
 
 template <bool CULL>
-__global__ void __launch_bounds__(RENDER_THREADS, 3)
+__global__ void __launch_bounds__(RENDER_THREADS, 4)
 render_bwd_kernel(const uint2* __restrict__ ranges, const uint32_t* __restrict__ point_list, int W, int H, float fx,
                   float fy, const float* __restrict__ bg_color, const Record* __restrict__ records,
                   const float* __restrict__ all_map_pixels, const float* __restrict__ final_Ts,
@@ -492,8 +493,6 @@ render_bwd_kernel(const uint2* __restrict__ ranges, const uint32_t* __restrict__
     const uint32_t total = range.y - range.x;
     const int last_contributor = inside ? n_contrib[pix_id] : 0;
 
-    float accum_rec[CGX_NCH] = {0};
-    float accum_all_map[CGX_NMAP] = {0};
     float dL_dpixel[CGX_NCH] = {0};
     float dL_dout_all_map[CGX_NMAP] = {0};
     if (inside) {
@@ -512,9 +511,10 @@ render_bwd_kernel(const uint2* __restrict__ ranges, const uint32_t* __restrict__
     float bg_dot_dpixel = 0;
     for (int i = 0; i < CGX_NCH; i++) bg_dot_dpixel += bg_color[i] * dL_dpixel[i];
 
-    float last_alpha = 0;
-    float last_color[CGX_NCH] = {0};
-    float last_all_map[CGX_NMAP] = {0};
+    // Suffix sum over the Gaussians behind the current one of alpha_j T_j (c_j . dL/dC): the reference carries the
+    // same information as eight per-channel "accumulated colour behind me" recurrences; contracting them with
+    // the pixel's cotangent first leaves one scalar recurrence (identical in exact arithmetic).
+    float S_behind = 0.f;
     const float ddelx_dx = 0.5 * W;
     const float ddely_dy = 0.5 * H;
     bool failed = false;
@@ -575,37 +575,23 @@ render_bwd_kernel(const uint2* __restrict__ ranges, const uint32_t* __restrict__
                         const float inv_1ma = __frcp_rn(1.f - alpha);
                         T = T * inv_1ma;
                         const float dchannel_dcolor = alpha * T;
-                        float dL_dalpha = 0.0f;
                         const float4 q2 = rec[j].q2;
-                        const float col[CGX_NCH] = {q1.z, q1.w, q2.x};
+                        float dot = q1.z * dL_dpixel[0] + q1.w * dL_dpixel[1] + q2.x * dL_dpixel[2];
 #pragma unroll
-                        for (int ch = 0; ch < CGX_NCH; ch++) {
-                            const float c = col[ch];
-                            accum_rec[ch] = last_alpha * last_color[ch] + (1.f - last_alpha) * accum_rec[ch];
-                            last_color[ch] = c;
-                            const float dL_dchannel = dL_dpixel[ch];
-                            dL_dalpha += (c - accum_rec[ch]) * dL_dchannel;
-                            v[8 + ch] = dchannel_dcolor * dL_dchannel;
-                        }
+                        for (int ch = 0; ch < CGX_NCH; ch++) v[8 + ch] = dchannel_dcolor * dL_dpixel[ch];
                         if (render_geo) {
                             const float4 q3 = rec[j].q3;
-                            const float am[CGX_NMAP] = {q2.y, q2.z, q2.w, q3.x, q3.y};
+                            dot += q2.y * dL_dout_all_map[0] + q2.z * dL_dout_all_map[1] + q2.w * dL_dout_all_map[2] +
+                                   q3.x * dL_dout_all_map[3] + q3.y * dL_dout_all_map[4];
 #pragma unroll
-                            for (int ch = 0; ch < CGX_NMAP; ch++) {
-                                const float c = am[ch];
-                                accum_all_map[ch] = last_alpha * last_all_map[ch] + (1.f - last_alpha) * accum_all_map[ch];
-                                last_all_map[ch] = c;
-                                const float dL_dchannel = dL_dout_all_map[ch];
-                                dL_dalpha += (c - accum_all_map[ch]) * dL_dchannel;
-                                v[11 + ch] = dchannel_dcolor * dL_dchannel;
-                            }
+                            for (int ch = 0; ch < CGX_NMAP; ch++) v[11 + ch] = dchannel_dcolor * dL_dout_all_map[ch];
                         } else {
 #pragma unroll
                             for (int ch = 0; ch < CGX_NMAP; ch++) v[11 + ch] = 0.f;
                         }
-                        dL_dalpha *= T;
-                        last_alpha = alpha;
-                        dL_dalpha += (-T_final * inv_1ma) * bg_dot_dpixel;
+                        // dL/dalpha = T (c . dL) - (sum behind + T_final (bg . dL)) / (1 - alpha)
+                        const float dL_dalpha = T * dot - (S_behind + T_final * bg_dot_dpixel) * inv_1ma;
+                        S_behind += dchannel_dcolor * dot;
 
                         const float dL_dG = con_o.w * dL_dalpha;
                         const float gdx = G * d.x;
@@ -623,7 +609,18 @@ render_bwd_kernel(const uint2* __restrict__ ranges, const uint32_t* __restrict__
                     }
                 }
             }
-            if (!__any_sync(0xffffffffu, valid)) continue;
+            const uint32_t vmask = __ballot_sync(0xffffffffu, valid);
+            if (vmask == 0) continue;
+            if (__popc(vmask) <= 2) {
+                // one or two contributing pixels: their own 16 atomics cost fewer issue slots than the butterfly
+                if (valid) {
+                    const size_t g = (size_t)ids[j];
+#pragma unroll
+                    for (int t = 0; t < 16; t++)
+                        if (out.ptr[t]) atomicAdd(out.ptr[t] + g * out.stride[t], v[t]);
+                }
+                continue;
+            }
             if (!valid) {
 #pragma unroll
                 for (int t = 0; t < 16; t++) v[t] = 0.f;

@@ -56,6 +56,8 @@ SIGNATURES = {
     "cgx_filter_preprocess": (_i, [_i, _vp, _vp, _f, _vp, _vp, _vp, _i, _i, _f, _f, _vp, _vp]),
     "cgx_sh_to_rgb": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp]),
     "cgx_preprocess_bwd": (_i, [_i, _vp, _vp, _f, _vp, _vp, _vp, _vp, _i, _i, _f, _f, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "cgx_preprocess_fwd_batched": (_i, [_i, _i, _vp, _vp, _f, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "cgx_preprocess_bwd_batched": (_i, [_i, _i, _vp, _vp, _f, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "cgx_all_map_fwd": (_i, [_i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "cgx_local2j_mask": (_i, [_i, _i, _i, _i, _vp, _vp, _vp, _i, _vp, _vp]),
     "cgx_local2j_count": (_i, [_i, _i, _i, _i, _vp, _vp, _vp, _i, _vp, _vp, _sz, _vp]),
@@ -65,7 +67,8 @@ SIGNATURES = {
     "cgx_unpack_rows": (_i, [_i] + [_vp] * 13),
     "cgx_pack_grad_rows": (_i, [_i] + [_vp] * 10),
     "cgx_local2j_pack_p2p": (_i, [_i, _i, _i, _i] + [_vp] * 9 + [_i] + [_vp] * 4 + [_sz, _vp]),
-    "cgx_pack_grad_rows_to": (_i, [_i] + [_vp] * 9),
+    "cgx_pack_grad_rows_to": (_i, [_i, _vp, _vp, _i] + [_vp] * 7),
+    "cgx_unpack_grad_add_cols": (_i, [_i, _vp, _vp, _i] + [_vp] * 9),
     "cgx_peer_barrier": (_i, [_i, _i, _vp, C.c_uint32, _vp]),
     "cgx_bin_workspace_bytes": (_sz, [_i]),
     "cgx_bin_count_scan": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),

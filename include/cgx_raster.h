@@ -89,6 +89,26 @@ int cgx_preprocess_bwd(int P, const float* means3D, const float* scales, float s
                        float* dL_dmeans3D, float* dL_dscales, float* dL_drotations, float* dL_dopacity,
                        void* stream);
 
+/* The caller's per-camera loop around preprocess (gaussian_renderer/__init__.py:966-1023) as ONE launch over a
+ * batch of B <= 16 cameras: parameters are read once and projected into every camera (outputs per camera, same
+ * bits as cgx_preprocess_fwd; the camera-independent covariance is not written); the backward reads them once
+ * and writes the gradients already summed over the cameras.  Pointer arrays are host arrays of device pointers. */
+typedef struct cgx_camera {
+    const float* viewmatrix;   /* device, 16 floats */
+    const float* projmatrix;   /* device, 16 floats */
+    float tanfovx, tanfovy;
+    int W, H;
+} cgx_camera;
+int cgx_preprocess_fwd_batched(int P, int B, const float* means3D, const float* scales, float scale_modifier,
+                               const float* rotations, const float* opacities, const cgx_camera* cams,
+                               float* const* means2D, float* const* depths, int32_t* const* radii,
+                               float* const* conic_opacity, void* stream);
+int cgx_preprocess_bwd_batched(int P, int B, const float* means3D, const float* scales, float scale_modifier,
+                               const float* rotations, const cgx_camera* cams, const int32_t* const* radii,
+                               const float* const* dL_dmeans2D, const float* const* dL_dconic_opacity,
+                               float* dL_dmeans3D, float* dL_dscales, float* dL_drotations, float* dL_dopacity,
+                               void* stream);
+
 /* PGSR per-Gaussian plane descriptor [normal_cam(3), 1, plane distance] for one camera, forward only: the
  * tensor code of the reference's caller (gaussian_renderer/__init__.py:1501-1518) as one kernel.
  * radii optional: rows with radius <= 0 get zeros.  all_map (P,5). */
@@ -155,7 +175,7 @@ int cgx_pack_grad_rows(int n_segments, const int64_t* seg_start, const int64_t* 
  * (dst[j].first_row), in ascending source index.  It replaces cgx_local2j_pack + the all-to-all + cgx_unpack_rows
  * (gaussian_renderer/__init__.py:612-696).  send_index (optional, with send_row_offset) records the source row
  * of every sent row in local send order for the backward.  cgx_pack_grad_rows_to is the backward's transport:
- * segment r's 19-float gradient rows are stored at seg_rows[r] (host array of device pointers, typically in the
+ * segment r's gradient rows (ncols = 19 or 9 floats each) are stored at seg_rows[r] (host array of device pointers, typically in the
  * source rank's memory).  The caller orders these stores against the readers (stream-ordered barriers). */
 typedef struct cgx_peer_camera_dst {
     float* means2D;        /* (n,2) */
@@ -175,9 +195,15 @@ int cgx_local2j_pack_p2p(int P, int H, int W, int ws, const float* means2D, cons
                          const cgx_peer_camera_dst* dst /* host, ws entries */,
                          const int64_t* send_row_offset /* host, ws entries, optional */, int32_t* send_index,
                          void* workspace, size_t workspace_bytes, void* stream);
-int cgx_pack_grad_rows_to(int n_segments, float* const* seg_rows, const int64_t* seg_count,
+int cgx_pack_grad_rows_to(int n_segments, float* const* seg_rows, const int64_t* seg_count, int ncols,
                           const float* d_means2D, const float* d_rgb, const float* d_conic_opacity,
                           const float* d_means3D, const float* d_scales, const float* d_rotations, void* stream);
+/* cgx_unpack_grad_add for rows of `ncols` floats: 19 = every differentiable column, 9 = means2D | rgb |
+ * conic_opacity only (used when no gradient flows back to the 3-D parameters through the exchange). */
+int cgx_unpack_grad_add_cols(int n_ranges, const int64_t* range_start, const int64_t* range_stop, int ncols,
+                             const float* grad_rows, const int32_t* send_index, float* d_means2D, float* d_rgb,
+                             float* d_conic_opacity, float* d_means3D, float* d_scales, float* d_rotations,
+                             void* stream);
 
 /* Stream-ordered barrier over the ranks of one NVLink/NVSwitch domain (no counterpart in the reference, which
  * synchronises through its collectives).  flag_ptrs: host array of `ws` device pointers, flag_ptrs[r] = an array

@@ -363,3 +363,38 @@ def test_error_codes(cuda_device):
     from diff_gaussian_rasterization import _C
     with pytest.raises(RuntimeError, match="deprecated"):
         _C.get_distribution_strategy(48, 64, None, None, False, {})
+
+
+def test_batched_preprocess_equals_per_camera(cuda_device):
+    """The camera-batched operator: per-camera outputs bit-identical, summed gradients within tolerance."""
+    from cgx.batched import preprocess_gaussians_batched
+    from diff_gaussian_rasterization import GaussianRasterizer
+
+    g, cams = util.S.config(2, n_gaussians=60000, n_cameras=5, res=(320, 240))
+    dev = cuda_device
+    settings = [settings_for(c, dev) for c in cams]
+    gen = torch.Generator().manual_seed(3)
+    cot = [(torch.randn(60000, 2, generator=gen).to(dev), torch.randn(60000, 4, generator=gen).to(dev)) for _ in cams]
+
+    def leaves():
+        return [g[k].to(dev).clone().requires_grad_(True) for k in ("means3D", "scales", "rotations", "opacities")]
+
+    a = leaves()
+    outs_a = [GaussianRasterizer(s).preprocess_gaussians(a[0], a[1], a[2], torch.empty(0, device=dev), a[3], cuda_args())
+              for s in settings]
+    b = leaves()
+    outs_b = preprocess_gaussians_batched(b[0], b[1], b[2], torch.empty(0, device=dev), b[3], settings, cuda_args())
+    for (m2a, _, coa, ra, da), (m2b, _, cob, rb, db) in zip(outs_a, outs_b):
+        assert torch.equal(m2a, m2b) and torch.equal(coa, cob) and torch.equal(ra, rb) and torch.equal(da, db)
+    # camera 3 gets no cotangent at all: it must simply not contribute
+    heads_a, heads_b, gr = [], [], []
+    for k in range(len(cams)):
+        if k == 3:
+            continue
+        heads_a += [outs_a[k][0], outs_a[k][2]]
+        heads_b += [outs_b[k][0], outs_b[k][2]]
+        gr += list(cot[k])
+    torch.autograd.backward(heads_a, gr)
+    torch.autograd.backward(heads_b, gr)
+    for x, y in zip(a, b):
+        assert rel_l2(y.grad.cpu(), x.grad.cpu()) <= 1e-5
