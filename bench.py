@@ -52,6 +52,8 @@ def parse_args():
     ap.add_argument("--cameras", type=int, default=None, help="use only the first N cameras (profiling captures)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-stage-events", action="store_true", help="do not bracket library calls with CUDA events")
+    ap.add_argument("--no-clocks", action="store_true", help="do not sample nvidia-smi during the run")
     ap.add_argument("--cpu-sample-gaussians", type=int, default=None)
     return ap.parse_args()
 
@@ -224,12 +226,12 @@ def main():
     for _ in range(max(a.warmup, 3)):
         step.run()
     sampler = ClockSampler(local_rank)
-    if rank == 0:
+    if rank == 0 and not a.no_clocks:
         sampler.start()
     launches0 = lib.cgx_launch_count()
-    _C.PROFILE = []
+    _C.PROFILE = None if a.no_stage_events else []
     ms_total = timed(step.run, a.steps)
-    prof, _C.PROFILE = _C.PROFILE, None
+    prof, _C.PROFILE = (_C.PROFILE or []), None
     launches = (lib.cgx_launch_count() - launches0) // a.steps
     clocks = sampler.stop() if rank == 0 else None
     ms_step = ms_total / a.steps

@@ -200,7 +200,7 @@ sort_scan_rows_kernel(int nblocks, uint32_t* __restrict__ table, uint32_t* __res
 // Stable scatter of one 4096-pair tile.  Thread t of warp w owns the 16 consecutive "rounds" of the warp's
 // contiguous 512-pair chunk: in round r the warp looks at pairs [chunk + 32 r, chunk + 32 r + 32), so
 // (warp, round, lane) order is input order and ranks computed from match.any ballots are stable.
-__global__ void __launch_bounds__(SORT_THREADS, 3)
+__global__ void __launch_bounds__(SORT_THREADS)
 sort_scatter_kernel(int64_t n, int nblocks, int shift, uint32_t mask, const uint64_t* __restrict__ keys_in,
                     const uint32_t* __restrict__ vals_in, uint64_t* __restrict__ keys_out,
                     uint32_t* __restrict__ vals_out, const uint32_t* __restrict__ table,

@@ -428,8 +428,11 @@ __device__ __forceinline__ float warp_reduce16(float (&v)[16], int lane)
     return w1;
 }
 
-template <bool CULL>
-__global__ void __launch_bounds__(RENDER_THREADS, 4)
+#ifndef CGX_BWD_MIN_CTAS
+#define CGX_BWD_MIN_CTAS 3
+#endif
+template <bool CULL, bool CONTRACT, bool ADAPT>
+__global__ void __launch_bounds__(RENDER_THREADS, CGX_BWD_MIN_CTAS)
 render_bwd_kernel(const uint2* __restrict__ ranges, const uint32_t* __restrict__ point_list, int W, int H, float fx,
                   float fy, const float* __restrict__ bg_color, const Record* __restrict__ records,
                   const float* __restrict__ all_map_pixels, const float* __restrict__ final_Ts,
@@ -511,10 +514,19 @@ render_bwd_kernel(const uint2* __restrict__ ranges, const uint32_t* __restrict__
     float bg_dot_dpixel = 0;
     for (int i = 0; i < CGX_NCH; i++) bg_dot_dpixel += bg_color[i] * dL_dpixel[i];
 
-    // Suffix sum over the Gaussians behind the current one of alpha_j T_j (c_j . dL/dC): the reference carries the
-    // same information as eight per-channel "accumulated colour behind me" recurrences; contracting them with
-    // the pixel's cotangent first leaves one scalar recurrence (identical in exact arithmetic).
-    float S_behind = 0.f;
+    // The reference carries eight per-channel recurrences "colour accumulated behind me":
+    //   accum[ch] = last_alpha * last_colour[ch] + (1 - last_alpha) * accum[ch]
+    // and then contracts (colour - accum) with the pixel's cotangent (CONTRACT = false does exactly that, in the
+    // reference's operation order, and is the default).  CONTRACT = true uses the linearity of the recurrence: for
+    // the six channels of order one (rgb, plane normal) it is contracted with the cotangent first, one scalar
+    // recurrence over dot_j = colour_j . dL/dC; the constant-1 and plane-distance channels keep their own.  Fewer
+    // instructions, but where the plane-depth cotangent explodes (rays grazing the blended normal) the three normal
+    // terms cancel by many orders of magnitude and the different rounding shows up at the 1e-2 level.
+    float accum_dot = 0.f, last_dot = 0.f, last_alpha = 0.f;
+    float accum_m3 = 0.f, accum_m4 = 0.f, last_m3 = 0.f, last_m4 = 0.f;
+    // per-channel form of the same recurrences (CONTRACT = false), kept for A/B checks of the contraction
+    float accum_rec[CGX_NCH] = {0}, last_color[CGX_NCH] = {0};
+    float accum_all_map[CGX_NMAP] = {0}, last_all_map[CGX_NMAP] = {0};
     const float ddelx_dx = 0.5 * W;
     const float ddely_dy = 0.5 * H;
     bool failed = false;
@@ -576,22 +588,60 @@ render_bwd_kernel(const uint2* __restrict__ ranges, const uint32_t* __restrict__
                         T = T * inv_1ma;
                         const float dchannel_dcolor = alpha * T;
                         const float4 q2 = rec[j].q2;
-                        float dot = q1.z * dL_dpixel[0] + q1.w * dL_dpixel[1] + q2.x * dL_dpixel[2];
-#pragma unroll
-                        for (int ch = 0; ch < CGX_NCH; ch++) v[8 + ch] = dchannel_dcolor * dL_dpixel[ch];
-                        if (render_geo) {
-                            const float4 q3 = rec[j].q3;
-                            dot += q2.y * dL_dout_all_map[0] + q2.z * dL_dout_all_map[1] + q2.w * dL_dout_all_map[2] +
-                                   q3.x * dL_dout_all_map[3] + q3.y * dL_dout_all_map[4];
-#pragma unroll
-                            for (int ch = 0; ch < CGX_NMAP; ch++) v[11 + ch] = dchannel_dcolor * dL_dout_all_map[ch];
+                        float dL_dalpha;
+                        if (CONTRACT) {
+                            float dot = q1.z * dL_dpixel[0] + q1.w * dL_dpixel[1] + q2.x * dL_dpixel[2];
+    #pragma unroll
+                            for (int ch = 0; ch < CGX_NCH; ch++) v[8 + ch] = dchannel_dcolor * dL_dpixel[ch];
+                            float geo_tail = 0.f;
+                            if (render_geo) {
+                                const float4 q3 = rec[j].q3;
+                                dot += q2.y * dL_dout_all_map[0] + q2.z * dL_dout_all_map[1] + q2.w * dL_dout_all_map[2];
+                                accum_m3 = last_alpha * last_m3 + (1.f - last_alpha) * accum_m3;
+                                accum_m4 = last_alpha * last_m4 + (1.f - last_alpha) * accum_m4;
+                                last_m3 = q3.x;
+                                last_m4 = q3.y;
+                                geo_tail = (q3.x - accum_m3) * dL_dout_all_map[3] + (q3.y - accum_m4) * dL_dout_all_map[4];
+    #pragma unroll
+                                for (int ch = 0; ch < CGX_NMAP; ch++) v[11 + ch] = dchannel_dcolor * dL_dout_all_map[ch];
+                            } else {
+    #pragma unroll
+                                for (int ch = 0; ch < CGX_NMAP; ch++) v[11 + ch] = 0.f;
+                            }
+                            accum_dot = last_alpha * last_dot + (1.f - last_alpha) * accum_dot;
+                            last_dot = dot;
+                            last_alpha = alpha;
+                            dL_dalpha = ((dot - accum_dot) + geo_tail) * T;
                         } else {
+                            dL_dalpha = 0.0f;
+                            const float col[CGX_NCH] = {q1.z, q1.w, q2.x};
 #pragma unroll
-                            for (int ch = 0; ch < CGX_NMAP; ch++) v[11 + ch] = 0.f;
+                            for (int ch = 0; ch < CGX_NCH; ch++) {
+                                const float c = col[ch];
+                                accum_rec[ch] = last_alpha * last_color[ch] + (1.f - last_alpha) * accum_rec[ch];
+                                last_color[ch] = c;
+                                dL_dalpha += (c - accum_rec[ch]) * dL_dpixel[ch];
+                                v[8 + ch] = dchannel_dcolor * dL_dpixel[ch];
+                            }
+                            if (render_geo) {
+                                const float4 q3 = rec[j].q3;
+                                const float am[CGX_NMAP] = {q2.y, q2.z, q2.w, q3.x, q3.y};
+#pragma unroll
+                                for (int ch = 0; ch < CGX_NMAP; ch++) {
+                                    const float c = am[ch];
+                                    accum_all_map[ch] = last_alpha * last_all_map[ch] + (1.f - last_alpha) * accum_all_map[ch];
+                                    last_all_map[ch] = c;
+                                    dL_dalpha += (c - accum_all_map[ch]) * dL_dout_all_map[ch];
+                                    v[11 + ch] = dchannel_dcolor * dL_dout_all_map[ch];
+                                }
+                            } else {
+#pragma unroll
+                                for (int ch = 0; ch < CGX_NMAP; ch++) v[11 + ch] = 0.f;
+                            }
+                            dL_dalpha *= T;
+                            last_alpha = alpha;
                         }
-                        // dL/dalpha = T (c . dL) - (sum behind + T_final (bg . dL)) / (1 - alpha)
-                        const float dL_dalpha = T * dot - (S_behind + T_final * bg_dot_dpixel) * inv_1ma;
-                        S_behind += dchannel_dcolor * dot;
+                        dL_dalpha += (-T_final * inv_1ma) * bg_dot_dpixel;
 
                         const float dL_dG = con_o.w * dL_dalpha;
                         const float gdx = G * d.x;
@@ -611,7 +661,7 @@ render_bwd_kernel(const uint2* __restrict__ ranges, const uint32_t* __restrict__
             }
             const uint32_t vmask = __ballot_sync(0xffffffffu, valid);
             if (vmask == 0) continue;
-            if (__popc(vmask) <= 2) {
+            if (ADAPT && __popc(vmask) <= 2) {
                 // one or two contributing pixels: their own 16 atomics cost fewer issue slots than the butterfly
                 if (valid) {
                     const size_t g = (size_t)ids[j];
@@ -651,11 +701,15 @@ int fetch_render_status(int* out)
 }
 }  // namespace cgx
 
-static int g_render_variant = 1;  // 1: per-warp culling on (default), 0: off
+// bit 0: per-warp culling (default on); bit 1: contracted recurrences (backward; off: it changes the rounding of
+// pixels whose plane-depth cotangent blows up and leaves the 1e-3 parity band there); bit 2: direct atomics for
+// visits with one or two contributing pixels (backward; off: measured slower, the extra L2 atomics cost more than
+// the butterfly saves)
+static int g_render_variant = 1;
 
-extern "C" int cgx_set_render_variant(int cull)
+extern "C" int cgx_set_render_variant(int variant)
 {
-    g_render_variant = cull ? 1 : 0;
+    g_render_variant = variant & 7;
     return CGX_OK;
 }
 
@@ -685,7 +739,7 @@ extern "C" int cgx_render_fwd(int P, int W, int H, float tanfovx, float tanfovy,
     const dim3 block(RENDER_THREADS, 1, 1);
     const size_t smem = sizeof(FwdSmem);
     cudaError_t e;
-    if (g_render_variant) {
+    if (g_render_variant & 1) {
         e = cudaFuncSetAttribute(render_fwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) { set_cuda_error(e); return CGX_ECUDA; }
         render_fwd_kernel<true><<<grid, block, smem, st>>>(
@@ -760,18 +814,25 @@ extern "C" int cgx_render_bwd(int P, int W, int H, float tanfovx, float tanfovy,
     const dim3 grid((W + CGX_BLOCK_X - 1) / CGX_BLOCK_X, (H + CGX_BLOCK_Y - 1) / CGX_BLOCK_Y, 1);
     const dim3 block(RENDER_THREADS, 1, 1);
     const size_t smem = sizeof(BwdSmem);
-    if (g_render_variant) {
-        e = cudaFuncSetAttribute(render_bwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) { set_cuda_error(e); return CGX_ECUDA; }
-        render_bwd_kernel<true><<<grid, block, smem, st>>>(
-            (const uint2*)ranges, point_list, W, H, focal_x, focal_y, bg, (const Record*)records, all_map_pixels,
-            final_T, n_contrib, compute_locally, dL_dcolor, dL_dout_all_map, dL_dout_plane_depth, render_geo != 0, out);
-    } else {
-        e = cudaFuncSetAttribute(render_bwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) { set_cuda_error(e); return CGX_ECUDA; }
-        render_bwd_kernel<false><<<grid, block, smem, st>>>(
-            (const uint2*)ranges, point_list, W, H, focal_x, focal_y, bg, (const Record*)records, all_map_pixels,
-            final_T, n_contrib, compute_locally, dL_dcolor, dL_dout_all_map, dL_dout_plane_depth, render_geo != 0, out);
+#define CGX_LAUNCH_BWD(C, K, A)                                                                                      \
+    do {                                                                                                            \
+        e = cudaFuncSetAttribute(render_bwd_kernel<C, K, A>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        if (e != cudaSuccess) { set_cuda_error(e); return CGX_ECUDA; }                                              \
+        render_bwd_kernel<C, K, A><<<grid, block, smem, st>>>(                                                      \
+            (const uint2*)ranges, point_list, W, H, focal_x, focal_y, bg, (const Record*)records, all_map_pixels,   \
+            final_T, n_contrib, compute_locally, dL_dcolor, dL_dout_all_map, dL_dout_plane_depth, render_geo != 0,  \
+            out);                                                                                                   \
+    } while (0)
+    switch (g_render_variant & 7) {
+    case 0: CGX_LAUNCH_BWD(false, false, false); break;
+    case 1: CGX_LAUNCH_BWD(true, false, false); break;
+    case 2: CGX_LAUNCH_BWD(false, true, false); break;
+    case 3: CGX_LAUNCH_BWD(true, true, false); break;
+    case 4: CGX_LAUNCH_BWD(false, false, true); break;
+    case 5: CGX_LAUNCH_BWD(true, false, true); break;
+    case 6: CGX_LAUNCH_BWD(false, true, true); break;
+    default: CGX_LAUNCH_BWD(true, true, true); break;
     }
+#undef CGX_LAUNCH_BWD
     return check_launch();
 }

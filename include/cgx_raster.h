@@ -307,9 +307,12 @@ int cgx_render_bwd(int P, int W, int H, float tanfovx, float tanfovy, const uint
  * synchronise-and-throw (RAST/cuda_rasterizer/auxiliary.h:220-227); nothing ever traps. */
 int cgx_device_status(int* status_host, void* stream);
 
-/* 1 (default): blending kernels cull each batch per warp before blending; 0: blend every listed Gaussian.
- * Results are identical; the switch exists for A/B timing and tests. */
-int cgx_set_render_variant(int cull);
+/* A/B switches of the blending kernels (default 1 = culling only), for timing and tests:
+ *   bit 0  per-warp culling of each batch before blending (forward and backward; results bit-identical);
+ *   bit 1  backward: the per-channel "accumulated behind" recurrences contracted with the pixel cotangent
+ *          (faster; leaves the 1e-3 gradient parity band on pixels whose plane-depth cotangent blows up);
+ *   bit 2  backward: visits with one or two contributing pixels issue their atomics directly (measured slower). */
+int cgx_set_render_variant(int variant);
 
 #ifdef __cplusplus
 }

@@ -228,8 +228,10 @@ def test_cull_variant_is_identical(cuda_device):
     try:
         l.cgx_set_render_variant(1)
         a = run_ours(g, cam, cuda_device, cot=cotangents(cam))
-        l.cgx_set_render_variant(0)
+        l.cgx_set_render_variant(0)      # no culling
         b = run_ours(g, cam, cuda_device, cot=cotangents(cam))
+        l.cgx_set_render_variant(5)      # culling + direct atomics for sparse visits
+        c = run_ours(g, cam, cuda_device, cot=cotangents(cam))
     finally:
         l.cgx_set_render_variant(1)
     for k in ("color", "out_all_map", "out_plane_depth", "final_T", "n_contrib_px", "n_contrib2loss_px",
@@ -237,6 +239,7 @@ def test_cull_variant_is_identical(cuda_device):
         assert torch.equal(a[k], b[k]), k
     for k in GRADS:
         assert rel_l2(a[k], b[k]) <= 1e-5, k
+        assert rel_l2(a[k], c[k]) <= 1e-5, k
 
 
 def test_partial_compute_locally(cuda_device, reference_C):
