@@ -161,7 +161,10 @@ emit_keys_kernel(int P, int gx, int gy, const int* __restrict__ radii, const flo
 
 // ------------------------------------------------------------------------------------------------ sort
 constexpr int SORT_THREADS = 256;
-constexpr int SORT_ITEMS = 16;
+#ifndef CGX_SORT_ITEMS
+#define CGX_SORT_ITEMS 16
+#endif
+constexpr int SORT_ITEMS = CGX_SORT_ITEMS;
 constexpr int SORT_TILE = SORT_THREADS * SORT_ITEMS;  // 4096 pairs per CTA
 constexpr int RADIX_BITS = 8;
 constexpr int RADIX = 1 << RADIX_BITS;
@@ -306,6 +309,75 @@ sort_scatter_kernel(int64_t n, int nblocks, int shift, uint32_t mask, const uint
         const size_t dst = (size_t)s_global_base[d] + (p - s_digit_start[d]);
         keys_out[dst] = k;
         vals_out[dst] = s_vals[p];
+    }
+}
+
+// Scatter without staging: ranks are computed as above, but the keys are not kept in registers and the pairs are
+// written straight to their final positions.  Few registers (8 CTAs per SM); the scattered 8- and 4-byte stores are
+// merged in L2, which is the right trade while both ping-pong buffers fit in L2 (n * 24 bytes well below 126 MB).
+__global__ void __launch_bounds__(SORT_THREADS, 6)
+sort_scatter_direct_kernel(int64_t n, int nblocks, int shift, uint32_t mask, const uint64_t* __restrict__ keys_in,
+                           const uint32_t* __restrict__ vals_in, uint64_t* __restrict__ keys_out,
+                           uint32_t* __restrict__ vals_out, const uint32_t* __restrict__ table,
+                           const uint32_t* __restrict__ totals)
+{
+    __shared__ uint32_t s_warp_hist[SORT_WARPS][RADIX];  // per-warp digit counters, then global position of the
+                                                         // warp's first pair of each digit
+    __shared__ uint32_t s_w[SORT_WARPS];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (int i = threadIdx.x; i < SORT_WARPS * RADIX; i += SORT_THREADS) (&s_warp_hist[0][0])[i] = 0;
+    __syncthreads();
+
+    const int64_t tile_base = (int64_t)blockIdx.x * SORT_TILE;
+    const int64_t chunk = tile_base + (int64_t)warp * (32 * SORT_ITEMS);
+    uint16_t rank[SORT_ITEMS];
+#pragma unroll
+    for (int r = 0; r < SORT_ITEMS; r++) {
+        const int64_t i = chunk + r * 32 + lane;
+        const bool valid = i < n;
+        const uint32_t d = valid ? ((uint32_t)(keys_in[i] >> shift) & mask) : (uint32_t)RADIX;
+        const uint32_t peers = __match_any_sync(0xffffffffu, d);
+        const uint32_t before = __popc(peers & ((1u << lane) - 1u));
+        uint32_t prev = 0;
+        if (valid && before == 0) {
+            prev = s_warp_hist[warp][d];
+            s_warp_hist[warp][d] = prev + __popc(peers);
+        }
+        prev = __shfl_sync(0xffffffffu, prev, __ffs(peers) - 1);
+        rank[r] = (uint16_t)(prev + before);
+        __syncwarp();
+    }
+    __syncthreads();
+    {
+        // digit d: global base = totals of smaller digits + this CTA's offset in the digit row; then per warp
+        const int d = threadIdx.x;
+        const uint32_t t = totals[d];
+        const uint32_t incl = warp_incl_scan(t);
+        if (lane == 31) s_w[warp] = incl;
+        __syncthreads();
+        uint32_t wb = 0;
+#pragma unroll
+        for (int w = 0; w < SORT_WARPS; w++)
+            if (w < warp) wb += s_w[w];
+        uint32_t run = wb + incl - t + table[(size_t)d * nblocks + blockIdx.x];
+#pragma unroll
+        for (int w = 0; w < SORT_WARPS; w++) {
+            const uint32_t c = s_warp_hist[w][d];
+            s_warp_hist[w][d] = run;
+            run += c;
+        }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int r = 0; r < SORT_ITEMS; r++) {
+        const int64_t i = chunk + r * 32 + lane;
+        if (i < n) {
+            const uint64_t k = keys_in[i];
+            const uint32_t d = (uint32_t)(k >> shift) & mask;
+            const size_t dst = (size_t)s_warp_hist[warp][d] + rank[r];
+            keys_out[dst] = k;
+            vals_out[dst] = vals_in[i];
+        }
     }
 }
 
@@ -778,6 +850,14 @@ extern "C" int cgx_emit_keys(int P, int W, int H, const int32_t* radii, const fl
     return check_launch();
 }
 
+static int g_sort_variant = -1;  // -1: by size; 0: staged scatter; 1: unstaged scatter
+
+extern "C" int cgx_set_sort_variant(int variant)
+{
+    g_sort_variant = variant;
+    return CGX_OK;
+}
+
 extern "C" size_t cgx_sort_workspace_bytes(int64_t n)
 {
     const size_t nblocks = ((size_t)(n > 0 ? n : 1) + SORT_TILE - 1) / SORT_TILE;
@@ -798,6 +878,8 @@ extern "C" int cgx_sort_pairs(int64_t n, int end_bit, uint64_t* keys_in, uint32_
         if (e != cudaSuccess) { set_cuda_error(e); return CGX_ECUDA; }
     }
     const int nblocks = (int)((n + SORT_TILE - 1) / SORT_TILE);
+    // both ping-pong buffers in L2 -> unstaged scatter; otherwise stage each tile so digit runs leave as bursts
+    const bool direct = g_sort_variant == 1 || (g_sort_variant < 0 && n * 24 <= (int64_t)96 << 20);
     uint32_t* table = (uint32_t*)workspace;
     uint32_t* totals = (uint32_t*)((char*)workspace + align_up((size_t)nblocks * RADIX * sizeof(uint32_t), 256));
     int passes = (end_bit + RADIX_BITS - 1) / RADIX_BITS;
@@ -823,8 +905,12 @@ extern "C" int cgx_sort_pairs(int64_t n, int end_bit, uint64_t* keys_in, uint32_
         const uint32_t mask = (1u << bits) - 1u;
         sort_hist_kernel<<<nblocks, SORT_THREADS, 0, st>>>(n, nblocks, shift, mask, kin, table);
         sort_scan_rows_kernel<<<RADIX, 1024, 0, st>>>(nblocks, table, totals);
-        sort_scatter_kernel<<<nblocks, SORT_THREADS, SORT_SMEM, st>>>(n, nblocks, shift, mask, kin, vin, kout, vout, table,
-                                                             totals);
+        if (direct)
+            sort_scatter_direct_kernel<<<nblocks, SORT_THREADS, 0, st>>>(n, nblocks, shift, mask, kin, vin, kout, vout,
+                                                                        table, totals);
+        else
+            sort_scatter_kernel<<<nblocks, SORT_THREADS, SORT_SMEM, st>>>(n, nblocks, shift, mask, kin, vin, kout, vout,
+                                                                         table, totals);
         uint64_t* tk = kin; kin = kout; kout = tk;
         uint32_t* tv = vin; vin = vout; vout = tv;
     }

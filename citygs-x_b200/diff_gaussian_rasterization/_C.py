@@ -69,6 +69,9 @@ def _align(n, a=128):
     return (n + a - 1) // a * a
 
 
+_ITEMSIZE = {torch.uint8: 1, torch.bool: 1, torch.int32: 4, torch.float32: 4, torch.int64: 8}
+
+
 class _Carver:
     """Sub-arrays of one uint8 tensor, each starting on a 128-byte boundary, in declaration order."""
 
@@ -77,8 +80,8 @@ class _Carver:
 
     def add(self, name, dtype, count):
         off = _align(self.size)
-        nbytes = count * torch.empty((), dtype=dtype).element_size()
-        self.items.append((name, dtype, count, off))
+        nbytes = count * _ITEMSIZE[dtype]
+        self.items.append((name, dtype, nbytes, off))
         self.size = off + nbytes
         return self
 
@@ -86,13 +89,13 @@ class _Carver:
         return self.size + 128
 
     def views(self, buf):
-        out = {}
-        for name, dtype, count, off in self.items:
-            nbytes = count * torch.empty((), dtype=dtype).element_size()
-            out[name] = buf[off:off + nbytes].view(dtype)
-        return out
+        return {name: buf[off:off + nbytes].view(dtype) for name, dtype, nbytes, off in self.items}
 
 
+import functools
+
+
+@functools.lru_cache(maxsize=256)
 def geometry_layout(P):
     l = _lib.lib()
     return (_Carver().add("tiles_touched", torch.int32, P)
@@ -102,6 +105,7 @@ def geometry_layout(P):
             .add("records", torch.uint8, l.cgx_render_records_bytes(P)))
 
 
+@functools.lru_cache(maxsize=256)
 def binning_layout(R):
     l = _lib.lib()
     return (_Carver().add("point_list", torch.int32, R)
@@ -111,6 +115,7 @@ def binning_layout(R):
             .add("list_sorting_space", torch.uint8, l.cgx_sort_workspace_bytes(R)))
 
 
+@functools.lru_cache(maxsize=64)
 def image_layout(N, T):
     return (_Carver().add("accum_alpha", torch.float32, N)
             .add("n_contrib", torch.int32, N)

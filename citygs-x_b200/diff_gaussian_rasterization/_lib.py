@@ -77,6 +77,7 @@ SIGNATURES = {
     "cgx_sort_pairs": (_i, [_i64, _i, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "cgx_sort_pairs_static_max": (_i64, []),
     "cgx_sort_pairs_static": (_i, [_i64, _i, _vp, _vp, _vp, _vp, _vp]),
+    "cgx_set_sort_variant": (_i, [_i]),
     "cgx_tile_ranges": (_i, [_i64, _i, _vp, _vp, _vp]),
     "cgx_render_records_bytes": (_sz, [_i]),
     "cgx_render_fwd": (_i, [_i, _i, _i, _f, _f] + [_vp] * 9 + [_i] + [_vp] * 12),

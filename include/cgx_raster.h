@@ -242,6 +242,10 @@ size_t cgx_sort_workspace_bytes(int64_t n);
 int cgx_sort_pairs(int64_t n, int end_bit, uint64_t* keys_in, uint32_t* values_in, uint64_t* keys_out,
                    uint32_t* values_out, void* workspace, size_t workspace_bytes, void* stream);
 
+/* Scatter strategy of the sort, for A/B timing and tests: -1 (default) chooses by size (unstaged while both
+ * ping-pong buffers fit in L2, staged above), 0 always staged, 1 always unstaged.  Results are identical. */
+int cgx_set_sort_variant(int variant);
+
 /* No counterpart in the reference.  Same sort as cgx_sort_pairs for callers that may not allocate device
  * memory (an engine with a memory budget fixed at start-up, a plugin whose host has frozen the CUDA pools, a
  * latency path that must stay away from the allocator): the digit tables live in a fixed array inside the

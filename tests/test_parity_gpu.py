@@ -401,3 +401,36 @@ def test_batched_preprocess_equals_per_camera(cuda_device):
     torch.autograd.backward(heads_b, gr)
     for x, y in zip(a, b):
         assert rel_l2(y.grad.cpu(), x.grad.cpu()) <= 1e-5
+
+
+@pytest.mark.parametrize("n", [1, 255, 4096, 4097, 1_000_003])
+def test_sort_pairs_variants(n, cuda_device):
+    """Both scatter strategies of the radix sort: identical output, equal to a stable sort on the masked key."""
+    import ctypes as C
+
+    from diff_gaussian_rasterization import _lib
+
+    l = _lib.lib()
+    dev = cuda_device
+    gen = torch.Generator().manual_seed(n)
+    keys = (torch.randint(0, 8160, (n,), generator=gen, dtype=torch.int64) << 32) | \
+        torch.randint(0, 1 << 32, (n,), generator=gen, dtype=torch.int64)
+    keys |= torch.randint(0, 2, (n,), generator=gen, dtype=torch.int64) << 50       # above end_bit: must be ignored
+    vals = torch.arange(n, dtype=torch.int32)
+    st = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    outs = []
+    try:
+        for variant in (0, 1):
+            l.cgx_set_sort_variant(variant)
+            kin, vin = keys.to(dev), vals.to(dev)
+            kout, vout = torch.empty_like(kin), torch.empty_like(vin)
+            ws = torch.empty(l.cgx_sort_workspace_bytes(n), dtype=torch.uint8, device=dev)
+            assert l.cgx_sort_pairs(n, 45, kin.data_ptr(), vin.data_ptr(), kout.data_ptr(), vout.data_ptr(),
+                                    ws.data_ptr(), ws.numel(), st) == 0
+            torch.cuda.synchronize()
+            outs.append((kout.cpu(), vout.cpu()))
+    finally:
+        l.cgx_set_sort_variant(-1)
+    order = torch.sort(keys & ((1 << 45) - 1), stable=True)[1]
+    for k, v in outs:
+        assert torch.equal(v.long(), order) and torch.equal(k, keys[order])
