@@ -209,14 +209,26 @@ class TrainingStep:
         with torch.no_grad():
             for k, v in self.host.items():
                 self.params[k].copy_(v, non_blocking=True)
-            for k in range(len(self.cams)):
+            mine = self._my_cameras()
+            for k in mine:
                 for dst, src in zip(self.cot[k], self.cot_host[k]):
                     dst.copy_(src, non_blocking=True)
+            self.h2d_bytes = sum(v.numel() * 4 for v in self.host.values()) + \
+                sum(c.numel() * 4 for k in mine for c in self.cot_host[k])
         self.run()
         for k, v in self.params.items():
             self.grad_host[k].copy_(v.grad, non_blocking=True)
         torch.cuda.current_stream().synchronize()
         return self.grad_host
+
+    def _my_cameras(self):
+        """Cameras (part of) which this rank renders: all of them on one GPU, the balancer's choice otherwise."""
+        if self.ws == 1:
+            return list(range(len(self.cams)))
+        from . import workload_division as WD
+
+        strategies, _ = WD.start_strategy_final(self.cams, self.history, ctx=self.ctx)
+        return [k for k, s in enumerate(strategies) if self.rank in s.gpu_ids]
 
     def exchange_stats(self):
         return None if self.ws == 1 else dict(self._exchange)

@@ -162,10 +162,10 @@ emit_keys_kernel(int P, int gx, int gy, const int* __restrict__ radii, const flo
 // ------------------------------------------------------------------------------------------------ sort
 constexpr int SORT_THREADS = 256;
 #ifndef CGX_SORT_ITEMS
-#define CGX_SORT_ITEMS 16
+#define CGX_SORT_ITEMS 8
 #endif
 constexpr int SORT_ITEMS = CGX_SORT_ITEMS;
-constexpr int SORT_TILE = SORT_THREADS * SORT_ITEMS;  // 4096 pairs per CTA
+constexpr int SORT_TILE = SORT_THREADS * SORT_ITEMS;  // 2048 pairs per CTA (measured best of 1024 / 2048 / 4096)
 constexpr int RADIX_BITS = 8;
 constexpr int RADIX = 1 << RADIX_BITS;
 constexpr int SORT_WARPS = SORT_THREADS / 32;
@@ -200,8 +200,8 @@ sort_scan_rows_kernel(int nblocks, uint32_t* __restrict__ table, uint32_t* __res
     if (threadIdx.x == 0) totals[blockIdx.x] = total;
 }
 
-// Stable scatter of one 4096-pair tile.  Thread t of warp w owns the 16 consecutive "rounds" of the warp's
-// contiguous 512-pair chunk: in round r the warp looks at pairs [chunk + 32 r, chunk + 32 r + 32), so
+// Stable scatter of one tile of SORT_TILE pairs.  Warp w owns SORT_ITEMS consecutive "rounds" of its contiguous
+// chunk of 32*SORT_ITEMS pairs: in round r the warp looks at pairs [chunk + 32 r, chunk + 32 r + 32), so
 // (warp, round, lane) order is input order and ranks computed from match.any ballots are stable.
 __global__ void __launch_bounds__(SORT_THREADS)
 sort_scatter_kernel(int64_t n, int nblocks, int shift, uint32_t mask, const uint64_t* __restrict__ keys_in,
