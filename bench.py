@@ -44,7 +44,7 @@ WORKLOADS = {
 def parse_args():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS))
@@ -70,7 +70,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
-                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                          "--format=csv,noheader,nounits", "-lms", "50"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
@@ -223,11 +223,11 @@ def main():
         return ms
 
     # ---- device-resident measurement
-    for _ in range(max(a.warmup, 3)):
-        step.run()
     sampler = ClockSampler(local_rank)
     if rank == 0 and not a.no_clocks:
-        sampler.start()
+        sampler.start()                 # samples cover warm-up and the timed region (both under load)
+    for _ in range(max(a.warmup, 3)):
+        step.run()
     launches0 = lib.cgx_launch_count()
     _C.PROFILE = None if a.no_stage_events else []
     ms_total = timed(step.run, a.steps)

@@ -61,7 +61,7 @@ class _PreprocessBatched(torch.autograd.Function):
                 _lib.check(_lib.lib().cgx_preprocess_fwd_batched(
                     P, B, means3D.data_ptr(), scales.data_ptr(), float(settings[0].scale_modifier),
                     rotations.data_ptr(), opacities.data_ptr(), cams, _ptrs(m2), _ptrs(dep), _ptrs(rad), _ptrs(co),
-                    torch.cuda.current_stream().cuda_stream), "cgx_preprocess_fwd_batched")
+                    _lib.current_stream_ptr()), "cgx_preprocess_fwd_batched")
         ctx.settings = settings
         ctx.save_for_backward(means3D, scales, rotations, *rad)
         flat = []
@@ -94,7 +94,7 @@ class _PreprocessBatched(torch.autograd.Function):
                     P, len(use), means3D.data_ptr(), scales.data_ptr(), float(settings[0].scale_modifier),
                     rotations.data_ptr(), cams, _ptrs([rad[b] for b in use]), _ptrs(g_m2), _ptrs(g_co),
                     d_means.data_ptr(), d_scales.data_ptr(), d_rot.data_ptr(), d_op.data_ptr(),
-                    torch.cuda.current_stream().cuda_stream), "cgx_preprocess_bwd_batched")
+                    _lib.current_stream_ptr()), "cgx_preprocess_bwd_batched")
         else:
             for t in (d_means, d_scales, d_rot, d_op):
                 t.zero_()

@@ -38,6 +38,7 @@ from __future__ import annotations
 
 import ctypes as C
 
+import numpy as np
 import torch
 import torch.distributed as dist
 
@@ -61,7 +62,9 @@ class CudaPackBackend:
 
     @staticmethod
     def _st():
-        return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+        from diff_gaussian_rasterization._lib import current_stream_ptr
+
+        return current_stream_ptr()
 
     def _require_cuda(self, t):
         if not t.is_cuda:
@@ -123,26 +126,20 @@ class CudaPackBackend:
                                                   self._st()), "cgx_pack_grad_rows")
 
 
-    def pack_p2p(self, params, tile_bounds, H, W, avoid, dsts, row_offsets, send_index, workspace):
-        """dsts: per destination column a tuple (8 device pointers, first_row)."""
+    def pack_p2p(self, params, tile_bounds, H, W, avoid, dst_table, row_offsets, send_index, workspace):
+        """dst_table: (ws, 9) uint64 rows = the eight destination tensors' device addresses (means2D, rgb,
+        conic_opacity, means3D, scales, rotations, radii, depths) and the first row this rank writes there, i.e.
+        an array of `struct cgx_peer_camera_dst`."""
         means2D, rgb, conic_opacity, radii, depths, means3D, scales, rotation = [t.contiguous() for t in params]
         P, ws = means2D.shape[0], tile_bounds.numel() - 1
-
-        class Dst(C.Structure):
-            _fields_ = [(n, C.c_void_p) for n in ("means2D", "rgb", "conic_opacity", "means3D", "scales",
-                                                  "rotations", "radii", "depths")] + [("first_row", C.c_int64)]
-
-        arr = (Dst * ws)()
-        for j, (ptrs, first) in enumerate(dsts):
-            for name, p in zip(("means2D", "rgb", "conic_opacity", "means3D", "scales", "rotations", "radii",
-                                "depths"), ptrs):
-                setattr(arr[j], name, p)
-            arr[j].first_row = first
+        dst_table = np.ascontiguousarray(dst_table, dtype=np.uint64)
+        assert dst_table.shape == (ws, 9)
         offs = (C.c_int64 * ws)(*[int(o) for o in row_offsets])
         self._lib.check(self.l.cgx_local2j_pack_p2p(
             P, H, W, ws, self._p(means2D), self._p(rgb), self._p(conic_opacity), self._p(means3D), self._p(scales),
-            self._p(rotation), self._p(radii), self._p(depths), self._p(tile_bounds), int(avoid), arr, offs,
-            self._p(send_index), self._p(workspace), workspace.numel(), self._st()), "cgx_local2j_pack_p2p")
+            self._p(rotation), self._p(radii), self._p(depths), self._p(tile_bounds), int(avoid),
+            C.c_void_p(dst_table.ctypes.data), offs, self._p(send_index), self._p(workspace), workspace.numel(),
+            self._st()), "cgx_local2j_pack_p2p")
 
     def pack_grad_rows_to(self, seg_ptrs, seg_counts, ncols, grads):
         n = len(seg_ptrs)
@@ -178,18 +175,48 @@ def default_backend():
     return _default_backend
 
 
+_world_cache = {}
+
+
 def _world(group):
-    return dist.get_world_size(group), dist.get_rank(group)
+    key = id(group)
+    if key not in _world_cache:
+        _world_cache[key] = (dist.get_world_size(group), dist.get_rank(group))
+    return _world_cache[key]
 
 
-def _gather_sizes(local_sizes, group, device):
-    """local_sizes: (ws, bsz) int32 rows = destination rank -> (ws, ws, bsz) nested list [src][dst][cam]."""
-    ws = dist.get_world_size(group)
-    backend = dist.get_backend(group)
-    t = local_sizes.to(device if backend == "nccl" else "cpu").contiguous().view(-1)
-    out = torch.empty(ws * t.numel(), dtype=t.dtype, device=t.device)
-    dist.all_gather_into_tensor(out, t, group=group)
-    return out.view(ws, ws, -1).cpu()
+_pinned = {}
+
+
+def _gather_table(table, n_counts, piggyback, group, ws):
+    """All-gather every rank's `table` (int32: n_counts row counts, then len(piggyback) float32 bit patterns) and
+    read it on the host: the one host synchronisation of the exchange.  Returns (int64 array (ws, n_counts),
+    nested list (ws, len(piggyback)) of floats)."""
+    L = table.numel() - n_counts
+    if L:
+        if table.is_cuda:
+            stage = _pinned.get(L)
+            if stage is None:
+                stage = _pinned[L] = torch.empty(L, dtype=torch.float32).pin_memory()
+            stage.numpy()[:] = np.asarray(piggyback, dtype=np.float32)
+            # the staging buffer is free again after the host read below, i.e. before the next call fills it
+            table[n_counts:].view(torch.float32).copy_(stage, non_blocking=True)
+        else:
+            table[n_counts:].view(torch.float32).copy_(torch.tensor(list(piggyback), dtype=torch.float32))
+    out = torch.empty(ws * table.numel(), dtype=torch.int32, device=table.device)
+    dist.all_gather_into_tensor(out, table, group=group)
+    host = out.cpu().numpy().reshape(ws, -1)
+    extra = host[:, n_counts:].copy().view(np.float32).tolist() if L else [[] for _ in range(ws)]
+    return host[:, :n_counts].astype(np.int64), extra
+
+
+def _dense_cotangents(g8, n, dev):
+    """The six differentiable outputs' cotangents of one camera; the first three (means2D, rgb, conic_opacity) are
+    always read by the packing kernels, so an output nothing consumed gets zeros; the 3-D ones may stay None."""
+    widths = (2, 3, 4)
+    first = [g if g is not None else torch.zeros(n, w, dtype=torch.float32, device=dev)
+             for g, w in zip(g8[:3], widths)]
+    return (*first, g8[5], g8[6], g8[7])
 
 
 class _GaussianExchange(torch.autograd.Function):
@@ -234,7 +261,9 @@ class _GaussianExchange(torch.autograd.Function):
         grad_recv = torch.empty((n_recv, REC_DIFF), dtype=torch.float32, device=dev)
         for k, segs in enumerate(plan["recv_segments"]):
             g8 = gouts[8 * k: 8 * k + 8]
-            be.pack_grad_rows(segs, (g8[0], g8[1], g8[2], g8[5], g8[6], g8[7]), grad_recv)
+            n = sum(c for _, c in segs)
+            if n:
+                be.pack_grad_rows(segs, _dense_cotangents(g8, n, dev), grad_recv)
         grad_send = torch.empty((n_send, REC_DIFF), dtype=torch.float32, device=dev)
         dist.all_to_all_single(grad_send, grad_recv, output_split_sizes=plan["send_splits"],
                                input_split_sizes=plan["recv_splits"], group=group)
@@ -260,13 +289,20 @@ _CAM_FIELDS = (("means2D", 8), ("rgb", 12), ("conic_opacity", 16), ("means3D", 1
                ("radii", 4), ("depths", 4))
 
 
+_CAM_WIDTHS = np.array([w for _, w in _CAM_FIELDS], dtype=np.int64)
+
+
+def _camera_layouts(n_rows):
+    """For an integer array of row counts (any shape): byte offsets of the eight per-camera tensors inside an arena
+    region (shape + (8,)) and the region sizes (same shape).  Every tensor starts on a 256-byte boundary."""
+    nbytes = (np.asarray(n_rows, dtype=np.int64)[..., None] * _CAM_WIDTHS + 255) // 256 * 256
+    ends = np.cumsum(nbytes, axis=-1)
+    return ends - nbytes, ends[..., -1]
+
+
 def _camera_layout(n):
-    """Byte offsets of the eight per-camera tensors of n rows inside an arena region, and the region size."""
-    offs, cur = [], 0
-    for _, width in _CAM_FIELDS:
-        offs.append(cur)
-        cur = _align_up(cur + n * width)
-    return offs, cur
+    offs, size = _camera_layouts(n)
+    return [int(o) for o in offs], int(size)
 
 
 class PeerArena:
@@ -308,7 +344,7 @@ class PeerArena:
 
         self.epoch += 1
         _lib.check(_lib.lib().cgx_peer_barrier(self.ws, self.me, self._flag_ptrs, self.epoch,
-                                               C.c_void_p(torch.cuda.current_stream().cuda_stream)),
+                                               _lib.current_stream_ptr()),
                    "cgx_peer_barrier")
 
 
@@ -328,35 +364,34 @@ class _GaussianExchangeP2P(torch.autograd.Function):
     @staticmethod
     def forward(ctx, plan, *flat):
         be, arena = plan["backend"], plan["arena"]
-        me, ws, sizes = plan["me"], plan["ws"], plan["sizes"]
+        me = plan["me"]
         bsz = len(plan["strategies"])
+        peer_base = np.array([int(p) for p in arena.recv_hdl.buffer_ptrs], dtype=np.int64)
+        # address of field f of camera k in rank j's arena, and the first row this rank writes there
+        field_ptr = peer_base[:, None, None] + plan["cam_base"][:, :, None] + plan["field_off"]      # (ws, bsz, 8)
         arena.barrier()                       # every rank is done with the previous contents of the arenas
         for k in range(bsz):
-            strat = plan["strategies"][k]
-            dsts = []
-            for j in strat.gpu_ids:
-                base = arena.recv_hdl.buffer_ptrs[j] + plan["cam_base"][j][k]
-                offs, _ = _camera_layout(plan["n_recv"][j][k])
-                first = sum(sizes[i][j][k] for i in range(me))
-                dsts.append(([base + o for o in offs], first))
+            ids = plan["strategies"][k].gpu_ids
+            table = np.empty((len(ids), 9), dtype=np.uint64)
+            table[:, :8] = field_ptr[ids, k, :]
+            table[:, 8] = plan["first_row"][ids, k]
             be.pack_p2p(plan["params"][k], plan["bounds"][k], plan["hw"][k][0], plan["hw"][k][1], plan["avoid"][k],
-                        dsts, plan["send_offsets"][k], plan["send_index"], plan["scratch"][k])
+                        table, plan["send_off"][ids, k], plan["send_index"], plan["scratch"][k])
         arena.barrier()                       # every rank's rows have landed
         outs, nondiff = [], []
+        f32 = arena.recv.view(torch.float32)
+        i32 = arena.recv.view(torch.int32)
         for k in range(bsz):
-            n = plan["n_recv"][me][k]
-            offs, _ = _camera_layout(n)
-            base = plan["cam_base"][me][k]
-            ts = []
-            for (name, width), o in zip(_CAM_FIELDS, offs):
-                raw = arena.recv[base + o: base + o + n * width]
-                if name == "radii":
-                    ts.append(raw.view(torch.int32))
-                elif name == "depths":
-                    ts.append(raw.view(torch.float32))
-                else:
-                    ts.append(raw.view(torch.float32).view(n, width // 4))
-            m2, rgb, co, m3, sc, rot, rad, dep = ts
+            n = int(plan["n_recv"][me, k])
+            w = (plan["cam_base"][me, k] + plan["field_off"][me, k]) // 4          # offsets in 4-byte words
+            m2 = f32[w[0]: w[0] + 2 * n].view(n, 2)
+            rgb = f32[w[1]: w[1] + 3 * n].view(n, 3)
+            co = f32[w[2]: w[2] + 4 * n].view(n, 4)
+            m3 = f32[w[3]: w[3] + 3 * n].view(n, 3)
+            sc = f32[w[4]: w[4] + 3 * n].view(n, 3)
+            rot = f32[w[5]: w[5] + 4 * n].view(n, 4)
+            rad = i32[w[6]: w[6] + n]
+            dep = f32[w[7]: w[7] + n]
             outs += [m2, rgb, co, rad, dep, m3, sc, rot]
             nondiff += [rad, dep]
         ctx.plan = plan
@@ -368,20 +403,20 @@ class _GaussianExchangeP2P(torch.autograd.Function):
     def backward(ctx, *gouts):
         plan = ctx.plan
         be, arena = plan["backend"], plan["arena"]
-        me, ws, sizes = plan["me"], plan["ws"], plan["sizes"]
+        me, S = plan["me"], plan["S"]
         dev = arena.dev
         bsz = len(plan["strategies"])
         ncols = plan["grad_cols"]
+        owner_base = np.array([int(p) for p in arena.grad_hdl.buffer_ptrs], dtype=np.int64)
+        # segment (source i -> me, camera k) sits at row grad_row[i, k] of rank i's send order
+        seg_ptr = owner_base[:, None] + plan["grad_row"] * (ncols * 4)                                # (ws, bsz)
         for k in range(bsz):
+            counts = S[:, me, k]
+            if not counts.any():
+                continue                      # camera not rendered here: no gradient rows to return
             g8 = gouts[8 * k: 8 * k + 8]
-            ptrs, counts = [], []
-            for i in range(ws):
-                n = sizes[i][me][k]
-                # position of segment (i -> me, camera k) in rank i's send order: destination major, camera minor
-                row = sum(sum(sizes[i][j]) for j in range(me)) + sum(sizes[i][me][:k])
-                ptrs.append(arena.grad_hdl.buffer_ptrs[i] + row * ncols * 4)
-                counts.append(n)
-            be.pack_grad_rows_to(ptrs, counts, ncols, (g8[0], g8[1], g8[2], g8[5], g8[6], g8[7]))
+            be.pack_grad_rows_to(seg_ptr[:, k].tolist(), counts.tolist(), ncols,
+                                 _dense_cotangents(g8, int(plan["n_recv"][me, k]), dev))
         arena.barrier()                       # every rank's gradient rows have landed in their owners' buffers
         n_send = plan["n_send"]
         grad_send = arena.grad[: n_send * ncols * 4].view(torch.float32).view(n_send, ncols)
@@ -411,21 +446,27 @@ def _pick_transport(transport, group, dev, backend):
 
 
 def all_to_all_communication_final(batched_rasterizers, batched_screenspace_params, batched_cuda_args,
-                                   batched_strategies, group=None, backend=None, transport=None):
+                                   batched_strategies, group=None, backend=None, transport=None, piggyback=None):
     """See module docstring.  ``batched_screenspace_params[k]`` =
     (means2D, rgb, conic_opacity, radii, depths, means3D, scales, rotation) of camera k on this rank.
 
     Returns the reference's tuple: per-camera lists of means2D, rgb, conic_opacity, radii (int32), depths, means3D,
     scales, rotations (redistributed), then the size table [src][dst][cam] and the rows sent per destination and
     camera (the reference returns index tensors there; here the source indices stay on the device in one packed
-    tensor, returned next), and a dict of transfer statistics."""
+    tensor, returned next), and a dict of transfer statistics.
+
+    ``piggyback``: optional list of floats (same length on every rank) that rides on the size-table all-gather;
+    every rank's values come back as ``stats["piggyback"][rank]``.  The balancer's render times travel this way
+    instead of in a collective (and a host synchronisation) of their own."""
     backend = backend or default_backend()
     ws, me = _world(group)
     bsz = len(batched_rasterizers)
     dev = batched_screenspace_params[0][0].device
 
     # ---- 1. counts: one kernel pair per camera, results land in one (bsz, ws) table, ONE host read
-    counts_dev = torch.zeros(bsz, ws, dtype=torch.int32, device=dev)
+    n_extra = len(piggyback) if piggyback is not None else 0
+    table_dev = torch.zeros(bsz * ws + n_extra, dtype=torch.int32, device=dev)
+    counts_dev = table_dev[: bsz * ws].view(bsz, ws)
     scratch, bounds = [], []
     for k in range(bsz):
         strat = batched_strategies[k]
@@ -443,60 +484,49 @@ def all_to_all_communication_final(batched_rasterizers, batched_screenspace_para
             counts_dev[k, torch.as_tensor(strat.gpu_ids, device=dev, dtype=torch.long)] = c
         scratch.append(wspace)
         bounds.append(tb)
-    sizes = _gather_sizes(counts_dev.t().contiguous(), group, dev)   # (src, dst, cam) on the host
-    sizes_list = sizes.tolist()
-    my = sizes_list[me]                                              # [dst][cam]
+    if dist.get_backend(group) != "nccl":
+        table_dev = table_dev.cpu()
+    gathered, extra = _gather_table(table_dev, bsz * ws, piggyback, group, ws)
+    S = np.ascontiguousarray(gathered.reshape(ws, bsz, ws).transpose(0, 2, 1))     # [src][dst][cam]
+    sizes_list = S.tolist()
+    my = S[me]                                                       # [dst][cam]
 
     # ---- 2. send order: destination major, camera minor
-    send_splits = [sum(my[j]) for j in range(ws)]
-    recv_splits = [sum(sizes_list[i][me]) for i in range(ws)]
-    n_send = sum(send_splits)
-    dst_base = [0] * ws
-    for j in range(1, ws):
-        dst_base[j] = dst_base[j - 1] + send_splits[j - 1]
+    send_splits = my.sum(1).tolist()
+    recv_splits = S[:, me, :].sum(1).tolist()
+    n_send = int(my.sum())
+    ends = np.cumsum(my.reshape(-1))
+    send_off = (ends - my.reshape(-1)).reshape(ws, bsz)              # first send row of (destination, camera)
+    send_ranges = [[(int(send_off[j, k]), int(send_off[j, k] + my[j, k])) for j in batched_strategies[k].gpu_ids]
+                   for k in range(bsz)]
     flat = []
     for k in range(bsz):
         m2, rgb, co, radii, depths, m3, sc, rot = batched_screenspace_params[k]
         flat += [m2, rgb, co, m3, sc, rot]
-    sent_counts = [[my[j][k] for k in range(bsz)] for j in range(ws)]
-    self_rows = sum(my[me])
+    sent_counts = my.tolist()
+    self_rows = int(my[me].sum())
     stats = {"rows_sent": n_send, "rows_received": sum(recv_splits), "rows_to_self": self_rows,
-             "bytes_sent_fwd": (n_send - self_rows) * REC * 4, "bytes_sent_bwd": (n_send - self_rows) * REC_DIFF * 4}
+             "bytes_sent_fwd": (n_send - self_rows) * REC * 4, "bytes_sent_bwd": (n_send - self_rows) * REC_DIFF * 4,
+             "piggyback": extra}
 
     transport = _pick_transport(transport, group, dev, backend)
     stats["transport"] = transport
+    send_index = torch.empty(n_send, dtype=torch.int32, device=dev)
     if transport == "p2p":
-        n_recv = [[sum(sizes_list[i][j][k] for i in range(ws)) for k in range(bsz)] for j in range(ws)]
-        cam_base = []
-        for j in range(ws):
-            cur, bases = 0, []
-            for k in range(bsz):
-                bases.append(cur)
-                cur += _camera_layout(n_recv[j][k])[1]
-            cam_base.append(bases + [cur])
-        recv_need = max(cb[-1] for cb in cam_base)
-        grad_need = max(sum(sum(sizes_list[i][j]) for j in range(ws)) for i in range(ws)) * REC_DIFF * 4
+        n_recv = S.sum(0)                                            # [dst][cam]
+        field_off, cam_size = _camera_layouts(n_recv)
+        cam_end = np.cumsum(cam_size, axis=1)
+        per_src = S.reshape(ws, -1)
+        grad_row = (np.cumsum(per_src, axis=1) - per_src).reshape(ws, ws, bsz)[:, me, :]
         arena = _arena_for(group, dev)
-        arena.ensure(recv_need, grad_need)
-        send_index = torch.empty(n_send, dtype=torch.int32, device=dev)
-        send_offsets, send_ranges = [], []
-        cam_off = [0] * ws
-        for k in range(bsz):
-            strat = batched_strategies[k]
-            send_offsets.append([dst_base[j] + cam_off[j] for j in strat.gpu_ids])
-            per_dst = []
-            for j in strat.gpu_ids:
-                n = my[j][k]
-                per_dst.append((dst_base[j] + cam_off[j], dst_base[j] + cam_off[j] + n))
-                cam_off[j] += n
-            send_ranges.append(per_dst)
+        arena.ensure(int(cam_end[:, -1].max()), int(per_src.sum(1).max()) * REC_DIFF * 4)
         # gradient rows carry 19 columns only when some rank needs gradients for the 3-D parameters through the
         # exchange; every rank runs the same model code, so this is the same decision everywhere
         grad_cols = REC_DIFF if any(flat[6 * k + c].requires_grad for k in range(bsz) for c in (3, 4, 5)) else 9
-        plan = dict(backend=backend, arena=arena, me=me, ws=ws, sizes=sizes_list, strategies=batched_strategies,
-                    grad_cols=grad_cols,
-                    n_recv=n_recv, cam_base=cam_base, bounds=bounds, scratch=scratch, send_index=send_index,
-                    send_offsets=send_offsets, send_ranges=send_ranges, n_send=n_send,
+        plan = dict(backend=backend, arena=arena, me=me, ws=ws, S=S, strategies=batched_strategies,
+                    grad_cols=grad_cols, n_recv=n_recv, cam_base=cam_end - cam_size, field_off=field_off,
+                    first_row=S[:me].sum(0), grad_row=grad_row, bounds=bounds, scratch=scratch,
+                    send_index=send_index, send_off=send_off, send_ranges=send_ranges, n_send=n_send,
                     params=[tuple(t.detach() for t in p) for p in batched_screenspace_params],
                     hw=[(r.raster_settings.image_height, r.raster_settings.image_width) for r in batched_rasterizers],
                     avoid=[a["avoid_pixel_all2all"] for a in batched_cuda_args])
@@ -507,36 +537,17 @@ def all_to_all_communication_final(batched_rasterizers, batched_screenspace_para
     # ---- 2b. collective transport: send buffer packed by one kernel per camera
     send = torch.empty(n_send, REC_DIFF, dtype=torch.float32, device=dev)
     send_aux = torch.empty(n_send, REC - REC_DIFF, dtype=torch.float32, device=dev)
-    send_index = torch.empty(n_send, dtype=torch.int32, device=dev)
-    send_ranges = []
-    cam_off = [0] * ws
     for k in range(bsz):
-        strat = batched_strategies[k]
-        offs = [dst_base[j] + cam_off[j] for j in strat.gpu_ids]
         params = tuple(t.detach() for t in batched_screenspace_params[k])
         rs = batched_rasterizers[k].raster_settings
-        backend.pack(params, bounds[k], rs.image_height, rs.image_width,
-                     batched_cuda_args[k]["avoid_pixel_all2all"], offs, send, send_aux, send_index, scratch[k])
-        per_dst = []
-        for j in strat.gpu_ids:
-            n = my[j][k]
-            per_dst.append((dst_base[j] + cam_off[j], dst_base[j] + cam_off[j] + n))
-            cam_off[j] += n
-        send_ranges.append(per_dst)
+        backend.pack(params, bounds[k], rs.image_height, rs.image_width, batched_cuda_args[k]["avoid_pixel_all2all"],
+                     [a for a, _ in send_ranges[k]], send, send_aux, send_index, scratch[k])
 
     # ---- 3. receive layout: source major, camera minor -> per camera one segment per source
-    src_base = [0] * ws
-    for i in range(1, ws):
-        src_base[i] = src_base[i - 1] + recv_splits[i - 1]
-    recv_segments = []
-    cam_off = [0] * ws
-    for k in range(bsz):
-        segs = []
-        for i in range(ws):
-            n = sizes_list[i][me][k]
-            segs.append((src_base[i] + cam_off[i], n))
-            cam_off[i] += n
-        recv_segments.append(segs)
+    from_src = S[:, me, :]                                            # [src][cam]
+    ends = np.cumsum(from_src.reshape(-1))
+    recv_off = (ends - from_src.reshape(-1)).reshape(ws, bsz)
+    recv_segments = [[(int(recv_off[i, k]), int(from_src[i, k])) for i in range(ws)] for k in range(bsz)]
 
     plan = dict(backend=backend, group=group, send=send, send_aux=send_aux, send_index=send_index,
                 send_splits=send_splits, recv_splits=recv_splits, send_ranges=send_ranges,

@@ -31,6 +31,12 @@ class TrainingStep:
         self.dev, self.rank, self.ws = device, rank, world_size
         self.transport = transport      # None: peer-to-peer inside an NCCL group, collective otherwise
         self.batched = True             # camera-batched preprocess (False: the reference's per-camera loop)
+        # True: the per-camera render times of step t ride on the size-table all-gather of step t+1 (their CUDA
+        # events have completed by then and that collective is read on the host anyway), so the balancer costs no
+        # collective and no host synchronisation of its own; its heuristics then lag one step behind the
+        # reference's, which gathers the times at the end of every step.
+        self.lazy_balancer = True
+        self._pending_stats = None
         self.cams = cams
         # Gaussians are stored round-robin over ranks, like the reference's anchors (scene/gaussian_model.py:476-479)
         sel = slice(rank, None, world_size)
@@ -79,7 +85,7 @@ class TrainingStep:
             rs = self.settings[k]
             _lib.check(_lib.lib().cgx_all_map_fwd(P, means3D.data_ptr(), scales.data_ptr(), rotations.data_ptr(),
                                                   radii.data_ptr(), rs.viewmatrix.data_ptr(), rs.campos.data_ptr(),
-                                                  out.data_ptr(), torch.cuda.current_stream().cuda_stream),
+                                                  out.data_ptr(), _lib.current_stream_ptr()),
                        "cgx_all_map_fwd")
         return out
 
@@ -96,7 +102,7 @@ class TrainingStep:
             cp = cam.campos.to(self.dev)
             _lib.check(_lib.lib().cgx_sh_to_rgb(P, 3, 16, self.params["means3D"].data_ptr(), cp.data_ptr(),
                                                 sh.data_ptr(), rgb.data_ptr(), clamped.data_ptr(),
-                                                torch.cuda.current_stream().cuda_stream), "cgx_sh_to_rgb")
+                                                _lib.current_stream_ptr()), "cgx_sh_to_rgb")
         return rgb
 
     # ------------------------------------------------------------------ single-GPU step
@@ -148,7 +154,8 @@ class TrainingStep:
             self._step_single()
         else:
             self._step_distributed()
-            self.finish_balancer()
+            if not self.lazy_balancer:
+                self.finish_balancer()
         return self.params
 
     # ------------------------------------------------------------------ multi-GPU step
@@ -171,8 +178,15 @@ class TrainingStep:
             # as plain data (no gradient rows come back for them)
             screen.append((means2D, self.rgb[k], conic_opacity, radii, depths, p["means3D"].detach(),
                            p["scales"].detach(), p["rotations"].detach()))
+        pending, times = self._pending_stats, None
+        if self.lazy_balancer and pending is not None:
+            times = WD.local_running_times(pending[0], pending[1], ctx=self.ctx)
         (m2, rgb, co, rad, dep, m3, sc, rot, sizes, sent, send_index, stats) = \
-            exchange.all_to_all_communication_final(rasts, screen, args, strategies, transport=self.transport)
+            exchange.all_to_all_communication_final(rasts, screen, args, strategies, transport=self.transport,
+                                                    piggyback=times)
+        if times is not None:
+            WD.finish_strategy_final(self.cams, self.history, pending[0], pending[1], ctx=self.ctx,
+                                     gathered_times=stats["piggyback"])
         self._exchange.update(bytes_sent_fwd=stats["bytes_sent_fwd"], bytes_sent_bwd=stats["bytes_sent_bwd"],
                               transport=stats["transport"], rows_sent=stats["rows_sent"])
         heads, grads = [], []
@@ -180,9 +194,6 @@ class TrainingStep:
             local = strat.get_compute_locally()
             n_rows = m2[k].shape[0]
             if local is None or n_rows < 10:
-                # nothing to render here, but the reverse exchange must still run on every rank
-                heads.append(m2[k].sum() + co[k].sum())
-                grads.append(torch.zeros((), device=self.dev))
                 args[k]["stats_collector"].update(forward_render_time=0.0, backward_render_time=0.0)
                 continue
             all_map = self.all_map_for(k, m3[k].detach(), sc[k].detach(), rot[k].detach(), rad[k])
@@ -191,17 +202,25 @@ class TrainingStep:
                 m2[k], m2abs, co[k], rgb[k], all_map, dep[k], rad[k], local, None, args[k])
             heads += [color, out_all_map, plane_depth]
             grads += self.cot[k]
+        if not heads:
+            # nothing to render on this rank, but the reverse exchange is collective: keep its node in the graph
+            heads.append(m2[0].sum() * 0.0)
+            grads.append(torch.zeros((), device=self.dev))
         torch.autograd.backward(heads, grads)
         self.last = keep
         self._strategies = strategies
         self._stats = [a["stats_collector"] for a in args]
+        self._pending_stats = (self._strategies, self._stats) if self.lazy_balancer else None
 
     def finish_balancer(self):
         """Feed measured render times back into the division heuristics (one tiny all-gather)."""
+        if self.ws > 1:
+            self._finish(self._strategies, self._stats)
+
+    def _finish(self, strategies, stats):
         from . import workload_division as WD
 
-        if self.ws > 1:
-            WD.finish_strategy_final(self.cams, self.history, self._strategies, self._stats, ctx=self.ctx)
+        WD.finish_strategy_final(self.cams, self.history, strategies, stats, ctx=self.ctx)
 
     def run_e2e(self):
         """The same step with its host-side inputs copied in from pinned memory (Gaussian parameters and the

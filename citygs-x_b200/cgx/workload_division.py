@@ -78,6 +78,10 @@ def division_pos_heuristic(heuristic, tile_num, world_size, right=False):
     return [0] + division_indices.tolist() + [tile_num]
 
 
+_TILE_BOUNDS = {}
+_LOCAL_MASKS = {}
+
+
 class DivisionStrategyFinal:
     """Which GPUs render which tile rows of one camera."""
 
@@ -103,7 +107,15 @@ class DivisionStrategyFinal:
 
     def tile_bounds(self, device=None):
         """int32 (world_size+1) linear tile ids of the band boundaries (division_pos * TILE_X)."""
-        return (torch.tensor(self.division_pos, dtype=torch.int32) * self.ctx.tile_x).to(device or self.ctx.device or "cpu")
+        dev = torch.device(device or self.ctx.device or "cpu")
+        key = (tuple(self.division_pos), self.ctx.tile_x, dev)
+        t = _TILE_BOUNDS.get(key)
+        if t is None:                       # cuts rarely move: keep the device copies instead of one upload per call
+            if len(_TILE_BOUNDS) > 4096:
+                _TILE_BOUNDS.clear()
+            t = (torch.tensor(self.division_pos, dtype=torch.int32) * self.ctx.tile_x).to(dev)
+            _TILE_BOUNDS[key] = t
+        return t
 
     def get_local2j_ids(self, means2D, radii, raster_settings, cuda_args):
         """(list of index tensors per destination, (P, world_size) bool mask), as the reference returns them.
@@ -120,9 +132,16 @@ class DivisionStrategyFinal:
             return None
         rank = self.gpu_ids.index(self.ctx.rank)
         tx, ty = self.ctx.tile_x, self.ctx.tile_y
-        compute_locally = torch.zeros(ty * tx, dtype=torch.bool, device=self.ctx.device or "cpu")
-        compute_locally[self.division_pos[rank] * tx: self.division_pos[rank + 1] * tx] = True
-        return compute_locally.view(ty, tx)
+        dev = torch.device(self.ctx.device or "cpu")
+        key = (self.division_pos[rank], self.division_pos[rank + 1], tx, ty, dev)
+        m = _LOCAL_MASKS.get(key)
+        if m is None:                       # read-only downstream, so one tensor per distinct band is shared
+            if len(_LOCAL_MASKS) > 4096:
+                _LOCAL_MASKS.clear()
+            m = torch.zeros(ty * tx, dtype=torch.bool, device=dev)
+            m[self.division_pos[rank] * tx: self.division_pos[rank + 1] * tx] = True
+            m = _LOCAL_MASKS[key] = m.view(ty, tx)
+        return m
 
     def get_compute_locally_all(self):
         if self.ctx.rank not in self.gpu_ids:
@@ -230,18 +249,30 @@ def allgather_float_list(values, ctx):
     return out.view(ctx.world_size, -1).cpu().tolist()
 
 
-def finish_strategy_final(batched_cameras, strategy_history, batched_strategies, batched_statistic_collector, ctx=None):
-    """Feed the measured per-camera times back into the per-row heuristics."""
+def local_running_times(batched_strategies, batched_statistic_collector, ctx=None):
+    """This rank's render time per camera of the batch (forward + backward + twice the loss forward, the
+    reference's cost model, utils/workload_division.py finish_strategy_final); -1 for cameras it did not render."""
     ctx = _ctx(ctx)
-    batched_running_time = []
+    times = []
     for idx, strategy in enumerate(batched_strategies):
         if ctx.rank not in strategy.gpu_ids:
-            batched_running_time.append(-1.0)
+            times.append(-1.0)
             continue
         st = batched_statistic_collector[idx]
-        batched_running_time.append(float(st["forward_render_time"]) + float(st["backward_render_time"])
-                                    + float(st.get("forward_loss_time", 0.0)) * 2)
-    gpu_camera_running_time = allgather_float_list(batched_running_time, ctx)
+        times.append(float(st["forward_render_time"]) + float(st["backward_render_time"])
+                     + float(st.get("forward_loss_time", 0.0)) * 2)
+    return times
+
+
+def finish_strategy_final(batched_cameras, strategy_history, batched_strategies, batched_statistic_collector,
+                          ctx=None, gathered_times=None):
+    """Feed the measured per-camera times back into the per-row heuristics.  ``gathered_times`` ([rank][camera],
+    every rank's `local_running_times`) skips the all-gather when the caller already exchanged them."""
+    ctx = _ctx(ctx)
+    if gathered_times is None:
+        gathered_times = allgather_float_list(
+            local_running_times(batched_strategies, batched_statistic_collector, ctx), ctx)
+    gpu_camera_running_time = gathered_times
     strategy_history.store_stats(batched_cameras, gpu_camera_running_time, batched_strategies)
 
     if ((ctx.iteration <= ctx.adjust_strategy_warmp_iterations) or (ctx.world_size == 1) or ctx.no_heuristics_update

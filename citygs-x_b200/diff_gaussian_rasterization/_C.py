@@ -47,7 +47,7 @@ def _ptr(t):
 
 
 def _stream():
-    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    return _lib.current_stream_ptr()
 
 
 def _cuda_f32(t, name):

@@ -118,6 +118,14 @@ class CgxError(RuntimeError):
         self.status = status
 
 
+def current_stream_ptr() -> int:
+    """cudaStream_t of torch's current stream on the current device, as an integer (the raw getters: the
+    torch.cuda.current_stream() object costs tens of microseconds per call and this sits before every launch)."""
+    import torch
+
+    return torch._C._cuda_getCurrentRawStream(torch._C._cuda_getDevice())
+
+
 def check(status: int, where: str):
     if status != CGX_OK:
         raise CgxError(status, where)

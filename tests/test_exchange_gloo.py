@@ -73,7 +73,8 @@ def _worker(rank, ws, port, out_dir):
             leaves.append((m2, rgb, co, m3, sc, rot))
         rasts = [SimpleNamespace(raster_settings=SimpleNamespace(image_height=c.H, image_width=c.W)) for c in cams]
         args = [{"avoid_pixel_all2all": False} for _ in cams]
-        out = exchange.all_to_all_communication_final(rasts, screen, args, strategies, backend=OracleBackend())
+        out = exchange.all_to_all_communication_final(rasts, screen, args, strategies, backend=OracleBackend(),
+                                                      piggyback=[rank + 0.25, -1.0, 3.5e-3])
         m2r, rgbr, cor, radr, depr, m3r, scr, rotr, sizes, sent, send_index, stats = out
 
         result = {"sizes": sizes, "strategies": [(s.gpu_ids, s.division_pos) for s in strategies], "renders": {}}
@@ -121,6 +122,15 @@ def test_sizes_and_strategies_agree(two_rank_run):
     assert sizes[0][0][1] == 0 and sizes[1][0][1] == 0        # nobody sends camera-1 rows to rank 0
     assert r0["stats"]["rows_sent"] == sum(sizes[0][j][k] for j in range(2) for k in range(2))
     assert r0["stats"]["rows_received"] == sum(sizes[i][0][k] for i in range(2) for k in range(2))
+
+
+def test_piggybacked_floats_reach_every_rank(two_rank_run):
+    """Values riding on the size-table all-gather (the balancer's render times) come back bit-exact, per rank."""
+    import numpy as np
+
+    want = [[float(np.float32(v)) for v in (r + 0.25, -1.0, 3.5e-3)] for r in range(2)]
+    for r in two_rank_run:
+        assert r["stats"]["piggyback"] == want
 
 
 def test_row_order_is_source_major_then_local_index(two_rank_run):
