@@ -141,6 +141,27 @@ class CudaPackBackend:
             C.c_void_p(dst_table.ctypes.data), offs, self._p(send_index), self._p(workspace), workspace.numel(),
             self._st()), "cgx_local2j_pack_p2p")
 
+    def pack_p2p_batched(self, cameras, send_index):
+        """One launch for the whole batch.  cameras: list of dicts with keys params (the eight per-camera tensors),
+        bounds, H, W, avoid, dst_table ((ws_k, 9) uint64, see pack_p2p), row_offsets ((ws_k,) int64), workspace."""
+        n = len(cameras)
+        table = np.zeros((n, 18), dtype=np.uint64)          # rows = struct cgx_exchange_camera
+        keep = []
+        for k, c in enumerate(cameras):
+            means2D, rgb, conic_opacity, radii, depths, means3D, scales, rotation = [t.contiguous() for t in c["params"]]
+            dst = np.ascontiguousarray(c["dst_table"], dtype=np.uint64)
+            offs = np.ascontiguousarray(c["row_offsets"], dtype=np.int64)
+            ws = c["bounds"].numel() - 1
+            assert dst.shape == (ws, 9) and offs.shape == (ws,)
+            keep.append((means2D, rgb, conic_opacity, radii, depths, means3D, scales, rotation, dst, offs))
+            table[k] = (means2D.shape[0], c["H"], c["W"], ws, means2D.data_ptr(), rgb.data_ptr(),
+                        conic_opacity.data_ptr(), means3D.data_ptr(), scales.data_ptr(), rotation.data_ptr(),
+                        radii.data_ptr(), depths.data_ptr(), c["bounds"].data_ptr(), int(bool(c["avoid"])),
+                        dst.ctypes.data, offs.ctypes.data, c["workspace"].data_ptr(), c["workspace"].numel())
+        self._lib.check(self.l.cgx_local2j_pack_p2p_batched(n, C.c_void_p(table.ctypes.data), self._p(send_index),
+                                                            self._st()), "cgx_local2j_pack_p2p_batched")
+        del keep
+
     def pack_grad_rows_to(self, seg_ptrs, seg_counts, ncols, grads):
         n = len(seg_ptrs)
         if n == 0 or sum(seg_counts) == 0:
@@ -370,20 +391,29 @@ class _GaussianExchangeP2P(torch.autograd.Function):
         # address of field f of camera k in rank j's arena, and the first row this rank writes there
         field_ptr = peer_base[:, None, None] + plan["cam_base"][:, :, None] + plan["field_off"]      # (ws, bsz, 8)
         arena.barrier()                       # every rank is done with the previous contents of the arenas
+        cameras = []
         for k in range(bsz):
             ids = plan["strategies"][k].gpu_ids
             table = np.empty((len(ids), 9), dtype=np.uint64)
             table[:, :8] = field_ptr[ids, k, :]
             table[:, 8] = plan["first_row"][ids, k]
-            be.pack_p2p(plan["params"][k], plan["bounds"][k], plan["hw"][k][0], plan["hw"][k][1], plan["avoid"][k],
-                        table, plan["send_off"][ids, k], plan["send_index"], plan["scratch"][k])
+            cameras.append(dict(params=plan["params"][k], bounds=plan["bounds"][k], H=plan["hw"][k][0],
+                                W=plan["hw"][k][1], avoid=plan["avoid"][k], dst_table=table,
+                                row_offsets=plan["send_off"][ids, k], workspace=plan["scratch"][k]))
+        if hasattr(be, "pack_p2p_batched"):
+            be.pack_p2p_batched(cameras, plan["send_index"])
+        else:
+            for c in cameras:
+                be.pack_p2p(c["params"], c["bounds"], c["H"], c["W"], c["avoid"], c["dst_table"], c["row_offsets"],
+                            plan["send_index"], c["workspace"])
         arena.barrier()                       # every rank's rows have landed
         outs, nondiff = [], []
         f32 = arena.recv.view(torch.float32)
         i32 = arena.recv.view(torch.int32)
+        words = ((plan["cam_base"][me][:, None] + plan["field_off"][me]) // 4).tolist()   # offsets in 4-byte words
+        n_mine = plan["n_recv"][me].tolist()
         for k in range(bsz):
-            n = int(plan["n_recv"][me, k])
-            w = (plan["cam_base"][me, k] + plan["field_off"][me, k]) // 4          # offsets in 4-byte words
+            n, w = n_mine[k], words[k]
             m2 = f32[w[0]: w[0] + 2 * n].view(n, 2)
             rgb = f32[w[1]: w[1] + 3 * n].view(n, 3)
             co = f32[w[2]: w[2] + 4 * n].view(n, 4)

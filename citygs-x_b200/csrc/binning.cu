@@ -643,20 +643,21 @@ struct PeerDsts {
 // Selection + packing + transport in one pass: every selected row is stored straight into the final per-camera
 // tensors of the rank that renders it (its own memory for the local band), in ascending source index behind the
 // rows of lower source ranks.  No send buffer, no collective, no unpack on the receiver.
-__global__ void __launch_bounds__(PACK_TILE)
-local2j_pack_p2p_kernel(int P, int gx, int gy, int ws, int nblocks, const float2* __restrict__ means2D,
-                        const float* __restrict__ rgb, const float4* __restrict__ conic_opacity,
-                        const float* __restrict__ means3D, const float* __restrict__ scales,
-                        const float4* __restrict__ rotations, const int* __restrict__ radii,
-                        const float* __restrict__ depths, const int* __restrict__ bounds, bool avoid,
-                        const uint32_t* __restrict__ block_prefix, PeerDsts dsts, PackOffsets local_offs,
-                        int32_t* __restrict__ send_index)
+// `dsts` / `local_row`: per participating rank of this camera (kernel-parameter space).  `block`: this CTA's tile.
+__device__ __forceinline__ void
+pack_p2p_tile(int block, int P, int gx, int gy, int ws, int nblocks, const float2* __restrict__ means2D,
+              const float* __restrict__ rgb, const float4* __restrict__ conic_opacity,
+              const float* __restrict__ means3D, const float* __restrict__ scales,
+              const float4* __restrict__ rotations, const int* __restrict__ radii,
+              const float* __restrict__ depths, const int* __restrict__ bounds, bool avoid,
+              const uint32_t* __restrict__ block_prefix, const PeerCameraDst* dsts, const long long* local_row,
+              int32_t* __restrict__ send_index)
 {
     // The CTA's selected rows are compacted field by field in shared memory and leave as eight contiguous bursts
     // (consecutive threads store consecutive words): full-width transactions, local or across NVLink.
     __shared__ uint32_t s_warp_cnt[PACK_TILE / 32];
     __shared__ float s_f[21][PACK_TILE + 1];   // field-major staging: [m2 2 | rgb 3 | co 4 | m3 3 | sc 3 | rot 4 | radius | depth]
-    const int i = blockIdx.x * PACK_TILE + threadIdx.x;
+    const int i = block * PACK_TILE + threadIdx.x;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     uint32_t bits = 0;
     float rec[21];
@@ -698,14 +699,14 @@ local2j_pack_p2p_kernel(int P, int gx, int gy, int ws, int nblocks, const float2
             continue;
         }
         const uint32_t slot = wbase + __popc(b & ((1u << lane) - 1u));
-        const long long seg0 = (long long)block_prefix[(size_t)rk * nblocks + blockIdx.x];
+        const long long seg0 = (long long)block_prefix[(size_t)rk * nblocks + block];
         if (sel) {
 #pragma unroll
             for (int k = 0; k < 21; k++) s_f[k][slot] = rec[k];
-            if (send_index) send_index[local_offs.row[rk] + seg0 + slot] = i;
+            if (send_index) send_index[local_row[rk] + seg0 + slot] = i;
         }
         __syncthreads();
-        const PeerCameraDst& D = dsts.d[rk];
+        const PeerCameraDst& D = dsts[rk];
         const long long row0 = D.row + seg0;
         // field f of width w occupies words [row0*w, (row0+cnt)*w) of its destination array
         auto burst = [&](float* dst, int f0, int w) {
@@ -725,6 +726,52 @@ local2j_pack_p2p_kernel(int P, int gx, int gy, int ws, int nblocks, const float2
         }
         __syncthreads();
     }
+}
+
+__global__ void __launch_bounds__(PACK_TILE)
+local2j_pack_p2p_kernel(int P, int gx, int gy, int ws, int nblocks, const float2* __restrict__ means2D,
+                        const float* __restrict__ rgb, const float4* __restrict__ conic_opacity,
+                        const float* __restrict__ means3D, const float* __restrict__ scales,
+                        const float4* __restrict__ rotations, const int* __restrict__ radii,
+                        const float* __restrict__ depths, const int* __restrict__ bounds, bool avoid,
+                        const uint32_t* __restrict__ block_prefix, const __grid_constant__ PeerDsts dsts,
+                        const __grid_constant__ PackOffsets local_offs, int32_t* __restrict__ send_index)
+{
+    pack_p2p_tile(blockIdx.x, P, gx, gy, ws, nblocks, means2D, rgb, conic_opacity, means3D, scales, rotations, radii,
+                  depths, bounds, avoid, block_prefix, dsts.d, local_offs.row, send_index);
+}
+
+// All cameras of a batch in one launch: blockIdx.y = camera, blockIdx.x = tile of that camera's local Gaussians.
+constexpr int MAX_XCAMS = 16;      // cameras per launch
+constexpr int MAX_XENTRIES = 48;   // participating (camera, rank) pairs per launch: cuts are contiguous, so a batch
+                                   // of B cameras over ws ranks has at most B + ws - 1 of them
+struct ExchangeCamera {
+    const float2* means2D;
+    const float* rgb;
+    const float4* conic_opacity;
+    const float* means3D;
+    const float* scales;
+    const float4* rotations;
+    const int* radii;
+    const float* depths;
+    const int* bounds;
+    const uint32_t* block_prefix;
+    int P, gx, gy, ws, nblocks, avoid, entry0, pad;
+};
+struct ExchangeBatch {
+    ExchangeCamera cam[MAX_XCAMS];
+    PeerCameraDst dst[MAX_XENTRIES];
+    long long local_row[MAX_XENTRIES];
+};
+
+__global__ void __launch_bounds__(PACK_TILE)
+local2j_pack_p2p_batched_kernel(const __grid_constant__ ExchangeBatch b, int32_t* __restrict__ send_index)
+{
+    const ExchangeCamera& c = b.cam[blockIdx.y];
+    if ((int)blockIdx.x >= c.nblocks) return;          // uniform over the CTA
+    pack_p2p_tile(blockIdx.x, c.P, c.gx, c.gy, c.ws, c.nblocks, c.means2D, c.rgb, c.conic_opacity, c.means3D,
+                  c.scales, c.rotations, c.radii, c.depths, c.bounds, c.avoid != 0, c.block_prefix,
+                  b.dst + c.entry0, b.local_row + c.entry0, send_index);
 }
 
 struct GradSegments {
@@ -1101,6 +1148,76 @@ extern "C" int cgx_local2j_pack_p2p(int P, int H, int W, int ws, const float* me
         (const float4*)rotations, radii, depths, tile_bounds, avoid_pixel_all2all != 0, (const uint32_t*)workspace, dsts,
         offs, send_index);
     return check_launch();
+}
+
+extern "C" int cgx_local2j_pack_p2p_batched(int n_cameras, const cgx_exchange_camera* cams, int32_t* send_index,
+                                            void* stream)
+{
+    if (n_cameras < 0 || (n_cameras > 0 && !cams)) return CGX_EINVAL;
+    int k0 = 0;
+    while (k0 < n_cameras) {
+        // as many consecutive cameras per launch as the parameter block holds
+        ExchangeBatch b;
+        memset(&b, 0, sizeof(b));
+        int n = 0, entries = 0, max_blocks = 0;
+        while (k0 + n < n_cameras && n < MAX_XCAMS) {
+            const cgx_exchange_camera& c = cams[k0 + n];
+            if (c.P < 0 || c.W <= 0 || c.H <= 0 || c.ws <= 0 || c.ws > MAX_WS || !c.dst) return CGX_EINVAL;
+            if (entries + (int)c.ws > MAX_XENTRIES) break;
+            ExchangeCamera& x = b.cam[n];
+            x.P = (int)c.P;
+            x.ws = (int)c.ws;
+            x.gx = ((int)c.W + CGX_BLOCK_X - 1) / CGX_BLOCK_X;
+            x.gy = ((int)c.H + CGX_BLOCK_Y - 1) / CGX_BLOCK_Y;
+            x.nblocks = (x.P + PACK_TILE - 1) / PACK_TILE;
+            x.avoid = c.avoid_pixel_all2all != 0;
+            x.entry0 = entries;
+            if (x.P > 0) {
+                if (!c.means2D || !c.rgb || !c.conic_opacity || !c.means3D || !c.scales || !c.rotations || !c.radii ||
+                    !c.depths || !c.tile_bounds || !c.workspace)
+                    return CGX_EINVAL;
+                if (send_index && !c.send_row_offset) return CGX_EINVAL;
+                if (((uintptr_t)c.means2D & 7) || !aligned16(c.conic_opacity) || !aligned16(c.rotations))
+                    return CGX_EINVAL;
+                if ((size_t)c.workspace_bytes < cgx_local2j_workspace_bytes(x.P, x.ws)) return CGX_ENOMEM;
+            }
+            x.means2D = (const float2*)c.means2D;
+            x.rgb = c.rgb;
+            x.conic_opacity = (const float4*)c.conic_opacity;
+            x.means3D = c.means3D;
+            x.scales = c.scales;
+            x.rotations = (const float4*)c.rotations;
+            x.radii = c.radii;
+            x.depths = c.depths;
+            x.bounds = c.tile_bounds;
+            x.block_prefix = (const uint32_t*)c.workspace;
+            for (int j = 0; j < x.ws; j++) {
+                const cgx_peer_camera_dst& d = c.dst[j];
+                if (x.P > 0) {
+                    if (!d.means2D || !d.rgb || !d.conic_opacity || !d.means3D || !d.scales || !d.rotations ||
+                        !d.radii || !d.depths || d.first_row < 0)
+                        return CGX_EINVAL;
+                    if (((uintptr_t)d.means2D & 7) || !aligned16(d.conic_opacity) || !aligned16(d.rotations))
+                        return CGX_EINVAL;
+                }
+                b.dst[entries + j] = PeerCameraDst{d.means2D, d.rgb, d.conic_opacity, d.means3D, d.scales,
+                                                   d.rotations, d.radii, d.depths, (long long)d.first_row};
+                b.local_row[entries + j] = c.send_row_offset ? (long long)c.send_row_offset[j] : 0;
+            }
+            entries += x.ws;
+            if (x.nblocks > max_blocks) max_blocks = x.nblocks;
+            n++;
+        }
+        if (n == 0) return CGX_EINVAL;     // one camera with more ranks than a launch can describe
+        if (max_blocks > 0) {
+            local2j_pack_p2p_batched_kernel<<<dim3((unsigned)max_blocks, (unsigned)n), PACK_TILE, 0,
+                                              (cudaStream_t)stream>>>(b, send_index);
+            const int st = check_launch();
+            if (st != CGX_OK) return st;
+        }
+        k0 += n;
+    }
+    return CGX_OK;
 }
 
 extern "C" int cgx_pack_grad_rows_to(int n_segments, float* const* seg_rows, const int64_t* seg_count, int ncols,

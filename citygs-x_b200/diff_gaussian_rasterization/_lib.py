@@ -67,6 +67,7 @@ SIGNATURES = {
     "cgx_unpack_rows": (_i, [_i] + [_vp] * 13),
     "cgx_pack_grad_rows": (_i, [_i] + [_vp] * 10),
     "cgx_local2j_pack_p2p": (_i, [_i, _i, _i, _i] + [_vp] * 9 + [_i] + [_vp] * 4 + [_sz, _vp]),
+    "cgx_local2j_pack_p2p_batched": (_i, [_i, _vp, _vp, _vp]),
     "cgx_pack_grad_rows_to": (_i, [_i, _vp, _vp, _i] + [_vp] * 7),
     "cgx_unpack_grad_add_cols": (_i, [_i, _vp, _vp, _i] + [_vp] * 9),
     "cgx_peer_barrier": (_i, [_i, _i, _vp, C.c_uint32, _vp]),

@@ -195,6 +195,31 @@ int cgx_local2j_pack_p2p(int P, int H, int W, int ws, const float* means2D, cons
                          const cgx_peer_camera_dst* dst /* host, ws entries */,
                          const int64_t* send_row_offset /* host, ws entries, optional */, int32_t* send_index,
                          void* workspace, size_t workspace_bytes, void* stream);
+/* Every camera of a batch in ONE launch of the same kernel (the per-camera loop of
+ * gaussian_renderer/__init__.py:612-660 collapsed): cams[k] describes camera k as this rank sends it; each
+ * camera's workspace must have been filled by cgx_local2j_count with the same arguments.  All members are 8 bytes
+ * wide so that a host can build the array as a plain table of 64-bit words.  Cameras are launched together as
+ * long as their participating ranks add up to at most 48 (contiguous cuts give at most cameras + ranks - 1);
+ * beyond that the call splits into several launches. */
+typedef struct cgx_exchange_camera {
+    int64_t P, H, W, ws;
+    const float* means2D;
+    const float* rgb;
+    const float* conic_opacity;
+    const float* means3D;
+    const float* scales;
+    const float* rotations;
+    const int32_t* radii;
+    const float* depths;
+    const int32_t* tile_bounds;            /* device, ws + 1 entries */
+    int64_t avoid_pixel_all2all;
+    const cgx_peer_camera_dst* dst;        /* host, ws entries */
+    const int64_t* send_row_offset;        /* host, ws entries (optional when send_index is null) */
+    void* workspace;                       /* device, as left by cgx_local2j_count */
+    uint64_t workspace_bytes;
+} cgx_exchange_camera;
+int cgx_local2j_pack_p2p_batched(int n_cameras, const cgx_exchange_camera* cams /* host */, int32_t* send_index,
+                                 void* stream);
 int cgx_pack_grad_rows_to(int n_segments, float* const* seg_rows, const int64_t* seg_count, int ncols,
                           const float* d_means2D, const float* d_rgb, const float* d_conic_opacity,
                           const float* d_means3D, const float* d_scales, const float* d_rotations, void* stream);

@@ -1,0 +1,198 @@
+"""The exchange kernels on ONE GPU: the destination "ranks" are separate buffers of the same device, so selection,
+counting, packing (send-buffer form, direct-store form, per camera and batched) and the gradient transport can be
+checked against the CPU oracle's band mask without a second GPU.  Everything here is data movement: bit-exact."""
+import numpy as np
+import pytest
+import torch
+
+import util
+from oracle import cpu_raster as O
+
+pytestmark = pytest.mark.gpu
+
+W, H = 320, 192            # 20 x 12 tiles
+BOUNDS_ROWS = [0, 4, 7, 12]  # three bands of tile rows
+N = 30_000
+
+
+def _screen_state(cam_idx, dev):
+    g, cam = util.make_case(cfg=2, n=N, res=(W, H), cam_idx=cam_idx)
+    pre = O.preprocess_fwd(g["means3D"], g["scales"], g["rotations"], g["opacities"], cam.viewmatrix, cam.projmatrix,
+                           cam.W, cam.H, cam.tanfovx, cam.tanfovy)
+    means2D, depths, radii, _, conic_opacity = pre
+    cpu = (means2D, g["rgb"], conic_opacity, radii, depths, g["means3D"], g["scales"], g["rotations"])
+    return cpu, tuple(t.to(dev).contiguous() for t in cpu)
+
+
+def _expected_rows(cpu, bounds):
+    mask = O.local2j_mask(cpu[0], cpu[3], bounds, W, H)
+    return [mask[:, j].nonzero().flatten() for j in range(mask.shape[1])]
+
+
+@pytest.fixture(scope="module")
+def setup(cuda_device):
+    from cgx import exchange
+
+    be = exchange.CudaPackBackend()
+    tx = (W + 15) // 16
+    bounds = torch.tensor(BOUNDS_ROWS, dtype=torch.int32) * tx
+    cams = []
+    for k in range(3):
+        cpu, gpu = _screen_state(k, cuda_device)
+        want = _expected_rows(cpu, bounds)
+        ws = len(want)
+        wspace = be.workspace(N, ws, cuda_device)
+        counts = torch.zeros(ws, dtype=torch.int32, device=cuda_device)
+        be.count(gpu[0], gpu[3], bounds.to(cuda_device), H, W, False, counts, wspace)
+        cams.append(dict(cpu=cpu, gpu=gpu, want=want, wspace=wspace, counts=counts.cpu()))
+    return be, bounds.to(cuda_device), cams
+
+
+def test_counts_match_oracle_mask(setup):
+    _, _, cams = setup
+    for c in cams:
+        assert c["counts"].tolist() == [len(w) for w in c["want"]]
+        assert sum(len(w) for w in c["want"]) > N // 10           # the case actually selects rows
+
+
+def _alloc_dsts(want, dev, first_rows):
+    """Per destination the eight arrays (with room for first_rows[j] foreign rows in front) and the pointer table."""
+    widths = (2, 3, 4, 3, 3, 4, 1, 1)
+    arrays, table = [], np.zeros((len(want), 9), dtype=np.uint64)
+    for j, rows in enumerate(want):
+        n = first_rows[j] + len(rows)
+        arrs = [torch.full((n, w), -7.0, device=dev) for w in widths[:6]]
+        arrs.append(torch.full((n,), -7, dtype=torch.int32, device=dev))
+        arrs.append(torch.full((n,), -7.0, device=dev))
+        arrays.append(arrs)
+        table[j, :8] = [a.data_ptr() for a in arrs]
+        table[j, 8] = first_rows[j]
+    return arrays, table
+
+
+def _check_dsts(arrays, c, first_rows):
+    m2, rgb, co, rad, dep, m3, sc, rot = c["cpu"]
+    for j, rows in enumerate(c["want"]):
+        f = first_rows[j]
+        got = [a.cpu() for a in arrays[j]]
+        for a, src in zip(got, (m2, rgb, co, m3, sc, rot, rad, dep)):
+            assert torch.equal(a[f:], src[rows]), "rows differ from the oracle's selection"
+            assert (a[:f] == -7).all(), "rows in front of first_row were overwritten"
+
+
+def test_direct_store_pack_per_camera_and_batched(setup, cuda_device):
+    be, bounds, cams = setup
+    first_rows = [5, 0, 11]
+    ws = len(first_rows)
+    n_send = sum(len(w) for c in cams for w in c["want"])
+    # send order: destination major, camera minor
+    offs = np.zeros((ws, len(cams)), dtype=np.int64)
+    cur = 0
+    for j in range(ws):
+        for k, c in enumerate(cams):
+            offs[j, k] = cur
+            cur += len(c["want"][j])
+    expect_index = torch.cat([c["want"][j] for j in range(ws) for c in cams]).to(torch.int32)
+
+    # per camera
+    idx_a = torch.full((n_send,), -1, dtype=torch.int32, device=cuda_device)
+    per_cam = []
+    for k, c in enumerate(cams):
+        arrays, table = _alloc_dsts(c["want"], cuda_device, first_rows)
+        be.pack_p2p(c["gpu"], bounds, H, W, False, table, offs[:, k], idx_a, c["wspace"])
+        per_cam.append(arrays)
+    torch.cuda.synchronize()
+    for arrays, c in zip(per_cam, cams):
+        _check_dsts(arrays, c, first_rows)
+    assert torch.equal(idx_a.cpu(), expect_index)
+
+    # the whole batch in one launch
+    idx_b = torch.full((n_send,), -1, dtype=torch.int32, device=cuda_device)
+    batch, all_arrays = [], []
+    for k, c in enumerate(cams):
+        arrays, table = _alloc_dsts(c["want"], cuda_device, first_rows)
+        all_arrays.append(arrays)
+        batch.append(dict(params=c["gpu"], bounds=bounds, H=H, W=W, avoid=False, dst_table=table,
+                          row_offsets=offs[:, k], workspace=c["wspace"]))
+    be.pack_p2p_batched(batch, idx_b)
+    torch.cuda.synchronize()
+    for arrays, c in zip(all_arrays, cams):
+        _check_dsts(arrays, c, first_rows)
+    assert torch.equal(idx_b.cpu(), expect_index)
+
+
+def test_batched_pack_splits_large_batches(setup, cuda_device):
+    """More (camera, rank) pairs than one launch describes: the call must split and still fill every camera."""
+    be, bounds, cams = setup
+    reps = 18                                   # 18 cameras x 3 ranks = 54 pairs > 48, and > 16 cameras
+    first_rows = [0, 0, 0]
+    n_send = sum(len(w) for w in cams[0]["want"]) * reps
+    idx = torch.full((n_send,), -1, dtype=torch.int32, device=cuda_device)
+    c = cams[0]
+    per = sum(len(w) for w in c["want"])
+    batch, all_arrays = [], []
+    for r in range(reps):
+        arrays, table = _alloc_dsts(c["want"], cuda_device, first_rows)
+        all_arrays.append(arrays)
+        offs = np.cumsum([0] + [len(w) for w in c["want"]][:-1]) + r * per
+        batch.append(dict(params=c["gpu"], bounds=bounds, H=H, W=W, avoid=False, dst_table=table,
+                          row_offsets=offs, workspace=c["wspace"]))
+    be.pack_p2p_batched(batch, idx)
+    torch.cuda.synchronize()
+    for arrays in all_arrays:
+        _check_dsts(arrays, c, first_rows)
+    one = torch.cat(c["want"]).to(torch.int32)
+    assert torch.equal(idx.cpu(), one.repeat(reps))
+
+
+def test_send_buffer_pack_matches_oracle_mask(setup, cuda_device):
+    from cgx.exchange import REC, REC_DIFF
+
+    be, bounds, cams = setup
+    c = cams[1]
+    n = sum(len(w) for w in c["want"])
+    offs = np.cumsum([0] + [len(w) for w in c["want"]][:-1]).tolist()
+    send = torch.empty(n, REC_DIFF, device=cuda_device)
+    aux = torch.empty(n, REC - REC_DIFF, device=cuda_device)
+    idx = torch.empty(n, dtype=torch.int32, device=cuda_device)
+    be.pack(c["gpu"], bounds, H, W, False, offs, send, aux, idx, c["wspace"])
+    rows = torch.cat(c["want"])
+    m2, rgb, co, rad, dep, m3, sc, rot = c["cpu"]
+    assert torch.equal(send.cpu(), torch.cat([m2, rgb, co, m3, sc, rot], 1)[rows])
+    assert torch.equal(aux.cpu(), torch.stack([rad.float(), dep], 1)[rows])
+    assert torch.equal(idx.cpu(), rows.to(torch.int32))
+
+
+@pytest.mark.parametrize("ncols", [9, 19])
+def test_gradient_rows_round_trip(setup, cuda_device, ncols):
+    """Receiver side: cotangents of one camera's received rows -> per-source segments; owner side: segments
+    scatter-added through the send index.  A row sent to two ranks gets both contributions."""
+    be, bounds, cams = setup
+    c = cams[2]
+    want = c["want"]
+    gen = torch.Generator().manual_seed(5)
+    staging = torch.zeros(sum(len(w) for w in want), ncols, device=cuda_device)
+    expect = [torch.zeros(N, w, dtype=torch.float64) for w in (2, 3, 4, 3, 3, 4)]
+    start = 0
+    for rows in want:                      # every destination returns one segment of gradient rows
+        n = len(rows)
+        cot = [torch.randn(n, w, generator=gen) for w in (2, 3, 4, 3, 3, 4)]
+        use = cot if ncols == 19 else cot[:3] + [None, None, None]
+        seg_ptr = staging.data_ptr() + start * ncols * 4
+        be.pack_grad_rows_to([seg_ptr], [n], ncols, [None if t is None else t.to(cuda_device) for t in use])
+        for e, t in zip(expect, use):
+            if t is not None:
+                e.index_add_(0, rows, t.double())
+        start += n
+    index = torch.cat(want).to(torch.int32).to(cuda_device)
+    grads = [torch.zeros(N, w, device=cuda_device) for w in (2, 3, 4, 3, 3, 4)]
+    ranges, s = [], 0
+    for rows in want:
+        ranges.append((s, s + len(rows)))
+        s += len(rows)
+    be.unpack_grad_add_cols(staging, index, ranges, ncols, grads if ncols == 19 else grads[:3] + [None] * 3)
+    for k, (g, e) in enumerate(zip(grads, expect)):
+        if ncols == 9 and k >= 3:
+            assert not g.any()
+            continue
+        assert torch.allclose(g.cpu().double(), e, atol=1e-5, rtol=1e-6)
