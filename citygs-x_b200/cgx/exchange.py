@@ -158,8 +158,10 @@ class CudaPackBackend:
                         conic_opacity.data_ptr(), means3D.data_ptr(), scales.data_ptr(), rotation.data_ptr(),
                         radii.data_ptr(), depths.data_ptr(), c["bounds"].data_ptr(), int(bool(c["avoid"])),
                         dst.ctypes.data, offs.ctypes.data, c["workspace"].data_ptr(), c["workspace"].numel())
-        self._lib.check(self.l.cgx_local2j_pack_p2p_batched(n, C.c_void_p(table.ctypes.data), self._p(send_index),
-                                                            self._st()), "cgx_local2j_pack_p2p_batched")
+        from diff_gaussian_rasterization import _C          # per-stage events when a profile is being collected
+
+        _C._call("cgx_local2j_pack_p2p_batched", self.l.cgx_local2j_pack_p2p_batched, n,
+                 C.c_void_p(table.ctypes.data), self._p(send_index), self._st())
         del keep
 
     def pack_grad_rows_to(self, seg_ptrs, seg_counts, ncols, grads):
@@ -169,8 +171,10 @@ class CudaPackBackend:
         ptrs = (C.c_void_p * n)(*seg_ptrs)
         counts = (C.c_int64 * n)(*seg_counts)
         g = [None if t is None else t.contiguous() for t in grads]
-        self._lib.check(self.l.cgx_pack_grad_rows_to(n, ptrs, counts, ncols, *[self._p(t) for t in g], self._st()),
-                        "cgx_pack_grad_rows_to")
+        from diff_gaussian_rasterization import _C
+
+        _C._call("cgx_pack_grad_rows_to", self.l.cgx_pack_grad_rows_to, n, ptrs, counts, ncols,
+                 *[self._p(t) for t in g], self._st())
 
     def unpack_grad_add_cols(self, grad_rows, send_index, ranges, ncols, grads):
         ranges = [(a, b) for a, b in ranges if b > a]
@@ -553,6 +557,7 @@ def all_to_all_communication_final(batched_rasterizers, batched_screenspace_para
         # gradient rows carry 19 columns only when some rank needs gradients for the 3-D parameters through the
         # exchange; every rank runs the same model code, so this is the same decision everywhere
         grad_cols = REC_DIFF if any(flat[6 * k + c].requires_grad for k in range(bsz) for c in (3, 4, 5)) else 9
+        stats["bytes_sent_bwd"] = (n_send - self_rows) * grad_cols * 4
         plan = dict(backend=backend, arena=arena, me=me, ws=ws, S=S, strategies=batched_strategies,
                     grad_cols=grad_cols, n_recv=n_recv, cam_base=cam_end - cam_size, field_off=field_off,
                     first_row=S[:me].sum(0), grad_row=grad_row, bounds=bounds, scratch=scratch,

@@ -37,6 +37,7 @@ class TrainingStep:
         # reference's, which gathers the times at the end of every step.
         self.lazy_balancer = True
         self._pending_stats = None
+        self._copy_stream = self._cot_ready = None
         self.cams = cams
         # Gaussians are stored round-robin over ranks, like the reference's anchors (scene/gaussian_model.py:476-479)
         sel = slice(rank, None, world_size)
@@ -135,8 +136,14 @@ class TrainingStep:
             heads += [color, out_all_map, plane_depth]
             grads += self.cot[k]
             outs.append((radii, means2D))
+        self._await_cotangents()
         torch.autograd.backward(heads, grads)      # one backward over the batch, as one loss.backward() upstream
         self.last = outs
+
+    def _await_cotangents(self):
+        if self._cot_ready is not None:
+            torch.cuda.current_stream().wait_event(self._cot_ready)
+            self._cot_ready = None
 
     _local_cache = {}
 
@@ -206,6 +213,7 @@ class TrainingStep:
             # nothing to render on this rank, but the reverse exchange is collective: keep its node in the graph
             heads.append(m2[0].sum() * 0.0)
             grads.append(torch.zeros((), device=self.dev))
+        self._await_cotangents()
         torch.autograd.backward(heads, grads)
         self.last = keep
         self._strategies = strategies
@@ -225,13 +233,22 @@ class TrainingStep:
     def run_e2e(self):
         """The same step with its host-side inputs copied in from pinned memory (Gaussian parameters and the
         upstream-gradient images) and the parameter gradients read back, all inside the caller's timed region."""
+        main = torch.cuda.current_stream()
+        if self._copy_stream is None:
+            self._copy_stream = torch.cuda.Stream(device=self.dev)
         with torch.no_grad():
             for k, v in self.host.items():
                 self.params[k].copy_(v, non_blocking=True)
+            # the upstream-gradient images are first read by the backward pass: their copies run on a second
+            # stream beside the forward pass, and the backward waits for them (self._cot_ready)
             mine = self._my_cameras()
-            for k in mine:
-                for dst, src in zip(self.cot[k], self.cot_host[k]):
-                    dst.copy_(src, non_blocking=True)
+            self._copy_stream.wait_stream(main)          # the previous step's backward has finished reading them
+            with torch.cuda.stream(self._copy_stream):
+                for k in mine:
+                    for dst, src in zip(self.cot[k], self.cot_host[k]):
+                        dst.copy_(src, non_blocking=True)
+                self._cot_ready = torch.cuda.Event()
+                self._cot_ready.record(self._copy_stream)
             self.h2d_bytes = sum(v.numel() * 4 for v in self.host.values()) + \
                 sum(c.numel() * 4 for k in mine for c in self.cot_host[k])
         self.run()
