@@ -38,6 +38,9 @@ class TrainingStep:
         self.lazy_balancer = True
         self._pending_stats = None
         self._copy_stream = self._cot_ready = None
+        # True: gradients of the plane descriptors flow back to means3D / rotations (through the reverse exchange
+        # when distributed: 19-float gradient rows), as in the reference's training graph
+        self.plane_grads = True
         self.cams = cams
         # Gaussians are stored round-robin over ranks, like the reference's anchors (scene/gaussian_model.py:476-479)
         sel = slice(rank, None, world_size)
@@ -77,18 +80,14 @@ class TrainingStep:
             self.history = WD.DivisionStrategyHistoryFinal(cams, world_size, rank, ctx=self.ctx)
 
     def all_map_for(self, k, means3D, scales, rotations, radii):
-        """Plane descriptors of the rows about to be rendered for camera k (one kernel, no autograd)."""
-        from diff_gaussian_rasterization import _lib
+        """Plane descriptors of the rows about to be rendered for camera k: one kernel each way, differentiable
+        towards means3D and rotations as the reference's tensor code is (gaussian_renderer/__init__.py:1501-1518)."""
+        from .plane_map import plane_map
 
-        P = means3D.shape[0]
-        out = torch.empty(P, 5, device=self.dev)
-        if P:
-            rs = self.settings[k]
-            _lib.check(_lib.lib().cgx_all_map_fwd(P, means3D.data_ptr(), scales.data_ptr(), rotations.data_ptr(),
-                                                  radii.data_ptr(), rs.viewmatrix.data_ptr(), rs.campos.data_ptr(),
-                                                  out.data_ptr(), _lib.current_stream_ptr()),
-                       "cgx_all_map_fwd")
-        return out
+        rs = self.settings[k]
+        if not self.plane_grads:
+            means3D, scales, rotations = means3D.detach(), scales.detach(), rotations.detach()
+        return plane_map(means3D, scales, rotations, rs.viewmatrix, rs.campos, radii)
 
     def _colours(self, sh, cam):
         """View-dependent colours through the library's SH stage (degree 3), as activated RGB."""
@@ -130,7 +129,7 @@ class TrainingStep:
             TX, TY = (cam.W + 15) // 16, (cam.H + 15) // 16
             local = self._all_local(TY, TX)
             means2D_abs = torch.zeros(self.n_local, 3, device=self.dev, requires_grad=True)
-            all_map = self.all_map_for(k, p["means3D"].detach(), p["scales"].detach(), p["rotations"].detach(), radii)
+            all_map = self.all_map_for(k, p["means3D"], p["scales"], p["rotations"], radii)
             color, n_render, n_consider, n_contrib, observe, out_all_map, plane_depth = rast.render_gaussians(
                 means2D, means2D_abs, conic_opacity, self.rgb[k], all_map, depths, radii, local, None, args)
             heads += [color, out_all_map, plane_depth]
@@ -181,10 +180,12 @@ class TrainingStep:
             means2D, _, conic_opacity, radii, depths = pre[k]
             means2D.retain_grad()
             keep.append((radii, means2D))
-            # the plane descriptors are rebuilt on the receiver without autograd, so the 3-D parameters travel
-            # as plain data (no gradient rows come back for them)
-            screen.append((means2D, self.rgb[k], conic_opacity, radii, depths, p["means3D"].detach(),
-                           p["scales"].detach(), p["rotations"].detach()))
+            # the plane descriptors are rebuilt on the receiver from the 3-D parameters, which therefore travel
+            # differentiably (their gradient rows come back through the reverse exchange) unless switched off
+            m3, sc, rot = p["means3D"], p["scales"], p["rotations"]
+            if not self.plane_grads:
+                m3, sc, rot = m3.detach(), sc.detach(), rot.detach()
+            screen.append((means2D, self.rgb[k], conic_opacity, radii, depths, m3, sc, rot))
         pending, times = self._pending_stats, None
         if self.lazy_balancer and pending is not None:
             times = WD.local_running_times(pending[0], pending[1], ctx=self.ctx)
@@ -203,7 +204,7 @@ class TrainingStep:
             if local is None or n_rows < 10:
                 args[k]["stats_collector"].update(forward_render_time=0.0, backward_render_time=0.0)
                 continue
-            all_map = self.all_map_for(k, m3[k].detach(), sc[k].detach(), rot[k].detach(), rad[k])
+            all_map = self.all_map_for(k, m3[k], sc[k], rot[k], rad[k])
             m2abs = torch.zeros(n_rows, 3, device=self.dev, requires_grad=True)
             color, _, _, _, _, out_all_map, plane_depth = rasts[k].render_gaussians(
                 m2[k], m2abs, co[k], rgb[k], all_map, dep[k], rad[k], local, None, args[k])

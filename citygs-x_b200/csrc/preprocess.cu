@@ -291,6 +291,81 @@ all_map_kernel(int P, const float* __restrict__ means3D, const float* __restrict
     for (int k = 0; k < 5; k++) out[5 * (size_t)i + k] = o5[k];
 }
 
+// Backward of all_map_kernel: cotangent of the 5-vector -> cotangents of the mean (through the plane distance)
+// and of the raw quaternion (through the chosen rotation column and the normalisation).  The choice of the
+// column, the flip towards the camera and the sign of the distance are piecewise constant; scales get no gradient.
+// dL_dmeans3D / dL_drotations are written (rows with radius <= 0 get zeros).
+__global__ void __launch_bounds__(256)
+all_map_bwd_kernel(int P, const float* __restrict__ means3D, const float* __restrict__ scales,
+                   const float4* __restrict__ rotations, const int* __restrict__ radii,
+                   const float* __restrict__ viewmatrix, const float* __restrict__ campos,
+                   const float* __restrict__ dL_dall_map, float* __restrict__ dL_dmeans3D,
+                   float4* __restrict__ dL_drotations)
+{
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= P) return;
+    float3 dp = {0.f, 0.f, 0.f};
+    float4 dq = {0.f, 0.f, 0.f, 0.f};
+    if (!radii || radii[i] > 0) {
+        const float3 p = {means3D[3 * i], means3D[3 * i + 1], means3D[3 * i + 2]};
+        const float3 sc = {scales[3 * i], scales[3 * i + 1], scales[3 * i + 2]};
+        const float4 qraw = rotations[i];
+        const float qn = fmaxf(sqrtf(qraw.x * qraw.x + qraw.y * qraw.y + qraw.z * qraw.z + qraw.w * qraw.w), 1e-12f);
+        const float r = qraw.x / qn, x = qraw.y / qn, y = qraw.z / qn, z = qraw.w / qn;
+        int idx = 0;
+        float smin = sc.x;
+        if (sc.y < smin) { smin = sc.y; idx = 1; }
+        if (sc.z < smin) { smin = sc.z; idx = 2; }
+        // on the unit sphere the rotation column is a quadratic form with factor 2
+        float3 n;
+        if (idx == 0) n = {1.f - 2.f * (y * y + z * z), 2.f * (x * y + z * r), 2.f * (x * z - y * r)};
+        else if (idx == 1) n = {2.f * (x * y - z * r), 1.f - 2.f * (x * x + z * z), 2.f * (y * z + x * r)};
+        else n = {2.f * (x * z + y * r), 2.f * (y * z - x * r), 1.f - 2.f * (x * x + y * y)};
+        const float3 tc = {campos[0] - p.x, campos[1] - p.y, campos[2] - p.z};
+        const float flip = (n.x * tc.x + n.y * tc.y + n.z * tc.z < 0.0f) ? -1.f : 1.f;
+        n = {flip * n.x, flip * n.y, flip * n.z};
+        const float* V = viewmatrix;
+        const float3 ln = {n.x * V[0] + n.y * V[4] + n.z * V[8], n.x * V[1] + n.y * V[5] + n.z * V[9],
+                           n.x * V[2] + n.y * V[6] + n.z * V[10]};
+        const float3 pc = {p.x * V[0] + p.y * V[4] + p.z * V[8] + V[12], p.x * V[1] + p.y * V[5] + p.z * V[9] + V[13],
+                           p.x * V[2] + p.y * V[6] + p.z * V[10] + V[14]};
+        const float* g = dL_dall_map + 5 * (size_t)i;
+        const float dot = ln.x * pc.x + ln.y * pc.y + ln.z * pc.z;
+        const float gs = dot > 0.f ? g[4] : (dot < 0.f ? -g[4] : 0.f);          // d|t|/dt, 0 at t = 0 as torch.abs
+        const float3 dln = {g[0] + gs * pc.x, g[1] + gs * pc.y, g[2] + gs * pc.z};
+        const float3 dpc = {gs * ln.x, gs * ln.y, gs * ln.z};
+        dp = {dpc.x * V[0] + dpc.y * V[1] + dpc.z * V[2], dpc.x * V[4] + dpc.y * V[5] + dpc.z * V[6],
+              dpc.x * V[8] + dpc.y * V[9] + dpc.z * V[10]};
+        const float3 dc = {flip * (dln.x * V[0] + dln.y * V[1] + dln.z * V[2]),
+                           flip * (dln.x * V[4] + dln.y * V[5] + dln.z * V[6]),
+                           flip * (dln.x * V[8] + dln.y * V[9] + dln.z * V[10])};      // cotangent of the column
+        float gr, gx, gy, gz;
+        if (idx == 0) {
+            gr = 2.f * (z * dc.y - y * dc.z);
+            gx = 2.f * (y * dc.y + z * dc.z);
+            gy = -4.f * y * dc.x + 2.f * (x * dc.y - r * dc.z);
+            gz = -4.f * z * dc.x + 2.f * (r * dc.y + x * dc.z);
+        } else if (idx == 1) {
+            gr = 2.f * (x * dc.z - z * dc.x);
+            gx = 2.f * y * dc.x - 4.f * x * dc.y + 2.f * r * dc.z;
+            gy = 2.f * (x * dc.x + z * dc.z);
+            gz = -2.f * r * dc.x - 4.f * z * dc.y + 2.f * y * dc.z;
+        } else {
+            gr = 2.f * (y * dc.x - x * dc.y);
+            gx = 2.f * z * dc.x - 2.f * r * dc.y - 4.f * x * dc.z;
+            gy = 2.f * r * dc.x + 2.f * z * dc.y - 4.f * y * dc.z;
+            gz = 2.f * (x * dc.x + y * dc.y);
+        }
+        // through q / |q|: remove the radial part, divide by the norm
+        const float radial = r * gr + x * gx + y * gy + z * gz;
+        dq = {(gr - r * radial) / qn, (gx - x * radial) / qn, (gy - y * radial) / qn, (gz - z * radial) / qn};
+    }
+    dL_dmeans3D[3 * (size_t)i] = dp.x;
+    dL_dmeans3D[3 * (size_t)i + 1] = dp.y;
+    dL_dmeans3D[3 * (size_t)i + 2] = dp.z;
+    dL_drotations[i] = dq;
+}
+
 // Backward of one camera's projection for one Gaussian: conic cotangent -> 2-D covariance -> (accumulated into)
 // dL/dcov3D[6] and dL/dmean, plus the 2-D mean's cotangent through the perspective projection.
 __device__ __forceinline__ void bwd_project_one(const float3 mean, const float* cov3D, const float* view_matrix,
@@ -767,6 +842,21 @@ extern "C" int cgx_all_map_fwd(int P, const float* means3D, const float* scales,
         return CGX_EINVAL;
     all_map_kernel<<<(P + 255) / 256, 256, 0, (cudaStream_t)stream>>>(P, means3D, scales, (const float4*)rotations,
                                                                       radii, viewmatrix, campos, all_map);
+    return check_launch();
+}
+
+extern "C" int cgx_all_map_bwd(int P, const float* means3D, const float* scales, const float* rotations,
+                               const int32_t* radii, const float* viewmatrix, const float* campos,
+                               const float* dL_dall_map, float* dL_dmeans3D, float* dL_drotations, void* stream)
+{
+    if (P < 0) return CGX_EINVAL;
+    if (P == 0) return CGX_OK;
+    if (!means3D || !scales || !rotations || !viewmatrix || !campos || !dL_dall_map || !dL_dmeans3D ||
+        !dL_drotations || !aligned16(rotations) || !aligned16(dL_drotations))
+        return CGX_EINVAL;
+    all_map_bwd_kernel<<<(P + 255) / 256, 256, 0, (cudaStream_t)stream>>>(
+        P, means3D, scales, (const float4*)rotations, radii, viewmatrix, campos, dL_dall_map, dL_dmeans3D,
+        (float4*)dL_drotations);
     return check_launch();
 }
 

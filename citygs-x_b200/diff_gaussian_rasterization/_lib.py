@@ -59,6 +59,7 @@ SIGNATURES = {
     "cgx_preprocess_fwd_batched": (_i, [_i, _i, _vp, _vp, _f, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "cgx_preprocess_bwd_batched": (_i, [_i, _i, _vp, _vp, _f, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "cgx_all_map_fwd": (_i, [_i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "cgx_all_map_bwd": (_i, [_i] + [_vp] * 10),
     "cgx_local2j_mask": (_i, [_i, _i, _i, _i, _vp, _vp, _vp, _i, _vp, _vp]),
     "cgx_local2j_count": (_i, [_i, _i, _i, _i, _vp, _vp, _vp, _i, _vp, _vp, _sz, _vp]),
     "cgx_local2j_workspace_bytes": (_sz, [_i, _i]),

@@ -115,6 +115,11 @@ int cgx_preprocess_bwd_batched(int P, int B, const float* means3D, const float* 
 int cgx_all_map_fwd(int P, const float* means3D, const float* scales, const float* rotations,
                     const int32_t* radii, const float* viewmatrix, const float* campos, float* all_map,
                     void* stream);
+/* Its backward (the autograd graph of the same tensor code): cotangent of all_map (P,5) -> cotangents of means3D
+ * (P,3) and of the raw quaternions (P,4), both WRITTEN; scales receive no gradient (they only select the column). */
+int cgx_all_map_bwd(int P, const float* means3D, const float* scales, const float* rotations,
+                    const int32_t* radii, const float* viewmatrix, const float* campos, const float* dL_dall_map,
+                    float* dL_dmeans3D, float* dL_drotations, void* stream);
 
 /* ------------------------------------------------------------------ distribution */
 

@@ -434,3 +434,52 @@ def test_sort_pairs_variants(n, cuda_device):
     order = torch.sort(keys & ((1 << 45) - 1), stable=True)[1]
     for k, v in outs:
         assert torch.equal(v.long(), order) and torch.equal(k, keys[order])
+
+
+def test_plane_map_forward_and_backward(cuda_device):
+    """The fused plane-descriptor op against the tensor code it replaces (cgx.synthetic.build_all_map restates the
+    reference's caller), differentiated by torch autograd in float64."""
+    from cgx.plane_map import plane_map
+
+    g, cam = util.make_case(cfg=2, n=50_000, res=(320, 240))
+    dev = cuda_device
+    leaves = {k: g[k].to(dev).requires_grad_(True) for k in ("means3D", "scales", "rotations")}
+    radii = (torch.arange(50_000, device=dev) % 7 != 0).to(torch.int32)          # some rows skipped
+    out = plane_map(leaves["means3D"], leaves["scales"], leaves["rotations"], cam.viewmatrix.to(dev),
+                    cam.campos.to(dev), radii)
+    gen = torch.Generator().manual_seed(11)
+    cot = torch.randn(50_000, 5, generator=gen).to(dev)
+    (out * cot).sum().backward()
+
+    ref_leaves = {k: g[k].double().to(dev).requires_grad_(True) for k in ("means3D", "scales", "rotations")}
+    ref = _build_all_map_f64(ref_leaves["means3D"], ref_leaves["scales"], ref_leaves["rotations"],
+                             cam.viewmatrix.double().to(dev), cam.campos.double().to(dev))
+    keep = (radii > 0)[:, None]
+    ref = ref * keep
+    (ref * cot.double()).sum().backward()
+
+    # float32 forward: the distance reaches a few hundred metres, so the bound is relative there
+    assert torch.allclose(out, ref.float(), rtol=3e-6, atol=2e-5)
+    assert not out[radii == 0].any()
+    for k in ("means3D", "rotations"):
+        a, b = leaves[k].grad.double(), ref_leaves[k].grad
+        assert ((a - b).norm() / b.norm()).item() <= 1e-4, k
+    assert leaves["scales"].grad is None or not leaves["scales"].grad.any()
+
+
+def _build_all_map_f64(means3D, scales, rotations, V, campos):
+    """gaussian_renderer/__init__.py:1501-1518 in float64 (quaternion [r, x, y, z], row-vector view matrix)."""
+    q = torch.nn.functional.normalize(rotations, p=2, dim=-1)
+    r, x, y, z = q.unbind(-1)
+    two_s = 2.0 / (q * q).sum(-1)
+    Rm = torch.stack([1 - two_s * (y * y + z * z), two_s * (x * y - z * r), two_s * (x * z + y * r),
+                      two_s * (x * y + z * r), 1 - two_s * (x * x + z * z), two_s * (y * z - x * r),
+                      two_s * (x * z - y * r), two_s * (y * z + x * r), 1 - two_s * (x * x + y * y)], -1).view(-1, 3, 3)
+    idx = scales.min(dim=-1)[1][..., None, None].expand(-1, 3, -1)
+    normal = Rm.gather(2, idx).squeeze(2)
+    neg = (normal * (campos - means3D)).sum(-1) < 0.0
+    normal = torch.where(neg[:, None], -normal, normal)
+    local_normal = normal @ V[:3, :3]
+    pts = means3D @ V[:3, :3] + V[3, :3]
+    dist = (local_normal * pts).sum(-1).abs()
+    return torch.cat([local_normal, torch.ones_like(dist)[:, None], dist[:, None]], 1)
