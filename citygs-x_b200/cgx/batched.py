@@ -41,8 +41,10 @@ def _ptrs(tensors):
 
 
 class _PreprocessBatched(torch.autograd.Function):
+    """Outputs per camera: means2D, conic_opacity, radii, depths[, all_map when `planes`]."""
+
     @staticmethod
-    def forward(ctx, means3D, scales, rotations, opacities, settings, cuda_args):
+    def forward(ctx, means3D, scales, rotations, opacities, settings, cuda_args, planes):
         if means3D.ndim != 2 or means3D.shape[1] != 3:
             raise RuntimeError("means3D must have dimensions (num_points, 3)")
         if not means3D.is_cuda:
@@ -55,56 +57,75 @@ class _PreprocessBatched(torch.autograd.Function):
         dep = [torch.empty(P, device=dev) for _ in range(B)]
         rad = [torch.empty(P, dtype=torch.int32, device=dev) for _ in range(B)]
         co = [torch.empty(P, 4, device=dev) for _ in range(B)]
+        am = [torch.empty(P, 5, device=dev) for _ in range(B)] if planes else []
         if P:
             cams, keep = _cams(settings)
+            campos = [rs.campos.contiguous() for rs in settings] if planes else None
             with torch.cuda.device(dev):
-                _lib.check(_lib.lib().cgx_preprocess_fwd_batched(
+                _lib.check(_lib.lib().cgx_preprocess_fwd_batched_planes(
                     P, B, means3D.data_ptr(), scales.data_ptr(), float(settings[0].scale_modifier),
-                    rotations.data_ptr(), opacities.data_ptr(), cams, _ptrs(m2), _ptrs(dep), _ptrs(rad), _ptrs(co),
-                    _lib.current_stream_ptr()), "cgx_preprocess_fwd_batched")
-        ctx.settings = settings
+                    rotations.data_ptr(), opacities.data_ptr(), cams, _ptrs(campos) if planes else None, _ptrs(m2),
+                    _ptrs(dep), _ptrs(rad), _ptrs(co), _ptrs(am) if planes else None,
+                    _lib.current_stream_ptr()), "cgx_preprocess_fwd_batched_planes")
+        ctx.settings, ctx.planes = settings, planes
         ctx.save_for_backward(means3D, scales, rotations, *rad)
         flat = []
         for b in range(B):
-            flat += [m2[b], co[b], rad[b], dep[b]]
+            flat += [m2[b], co[b], rad[b], dep[b]] + ([am[b]] if planes else [])
         ctx.mark_non_differentiable(*rad, *dep)
         return tuple(flat)
 
     @staticmethod
     def backward(ctx, *grads):
         means3D, scales, rotations, *rad = ctx.saved_tensors
-        settings = ctx.settings
+        settings, planes = ctx.settings, ctx.planes
+        n_out = 5 if planes else 4
         P, dev = means3D.shape[0], means3D.device
         d_means = torch.empty(P, 3, device=dev)
         d_scales = torch.empty(P, 3, device=dev)
         d_rot = torch.empty(P, 4, device=dev)
         d_op = torch.empty(P, 1, device=dev)
-        use, g_m2, g_co = [], [], []
+        use, g_m2, g_co, g_am = [], [], [], []
         for b in range(len(settings)):
-            gm, gc = grads[4 * b], grads[4 * b + 1]
-            if gm is None and gc is None:
+            gm, gc = grads[n_out * b], grads[n_out * b + 1]
+            ga = grads[n_out * b + 4] if planes else None
+            if gm is None and gc is None and ga is None:
                 continue                      # this camera received no cotangent: it contributes nothing
             use.append(b)
             g_m2.append(gm.contiguous() if gm is not None else torch.zeros(P, 2, device=dev))
             g_co.append(gc.contiguous() if gc is not None else torch.zeros(P, 4, device=dev))
+            g_am.append(ga.contiguous() if ga is not None else None)
         if P and use:
             cams, keep = _cams([settings[b] for b in use])
+            with_planes = planes and any(g is not None for g in g_am)
+            campos = [settings[b].campos.contiguous() for b in use] if with_planes else None
+            am_ptrs = (C.c_void_p * len(use))(*[None if g is None else g.data_ptr() for g in g_am]) \
+                if with_planes else None
             with torch.cuda.device(dev):
-                _lib.check(_lib.lib().cgx_preprocess_bwd_batched(
+                _lib.check(_lib.lib().cgx_preprocess_bwd_batched_planes(
                     P, len(use), means3D.data_ptr(), scales.data_ptr(), float(settings[0].scale_modifier),
-                    rotations.data_ptr(), cams, _ptrs([rad[b] for b in use]), _ptrs(g_m2), _ptrs(g_co),
+                    rotations.data_ptr(), cams, _ptrs(campos) if with_planes else None,
+                    _ptrs([rad[b] for b in use]), _ptrs(g_m2), _ptrs(g_co), am_ptrs,
                     d_means.data_ptr(), d_scales.data_ptr(), d_rot.data_ptr(), d_op.data_ptr(),
-                    _lib.current_stream_ptr()), "cgx_preprocess_bwd_batched")
+                    _lib.current_stream_ptr()), "cgx_preprocess_bwd_batched_planes")
         else:
             for t in (d_means, d_scales, d_rot, d_op):
                 t.zero_()
-        return d_means, d_scales, d_rot, d_op, None, None
+        return d_means, d_scales, d_rot, d_op, None, None, None
 
 
-def preprocess_gaussians_batched(means3D, scales, rotations, shs, opacities, raster_settings_list, cuda_args=None):
+def preprocess_gaussians_batched(means3D, scales, rotations, shs, opacities, raster_settings_list, cuda_args=None,
+                                 planes=False):
     """One (means2D, rgb, conic_opacity, radii, depths) tuple per camera, as the per-camera operator returns them
-    (``rgb`` is the shared all-zero tensor the per-camera operator also returns: SH evaluation is compiled out)."""
+    (``rgb`` is the shared all-zero tensor the per-camera operator also returns: SH evaluation is compiled out).
+
+    ``planes=True`` appends the camera's plane descriptors ``all_map`` (P,5) to each tuple: what the reference's
+    caller builds after preprocessing (gaussian_renderer/__init__.py:1501-1518) comes out of the same launch, and
+    its gradient towards means3D / rotations is folded into the same backward launch (see cgx.plane_map for the
+    stand-alone op)."""
     settings = list(raster_settings_list)
-    flat = _PreprocessBatched.apply(means3D, scales, rotations, opacities, settings, cuda_args)
+    flat = _PreprocessBatched.apply(means3D, scales, rotations, opacities, settings, cuda_args, bool(planes))
     rgb = torch.zeros(means3D.shape[0], 3, device=means3D.device)
-    return [(flat[4 * b], rgb, flat[4 * b + 1], flat[4 * b + 2], flat[4 * b + 3]) for b in range(len(settings))]
+    n = 5 if planes else 4
+    return [(flat[n * b], rgb, flat[n * b + 1], flat[n * b + 2], flat[n * b + 3]) + ((flat[n * b + 4],) if planes else ())
+            for b in range(len(settings))]

@@ -132,8 +132,7 @@ class CudaPackBackend:
         an array of `struct cgx_peer_camera_dst`."""
         means2D, rgb, conic_opacity, radii, depths, means3D, scales, rotation = [t.contiguous() for t in params]
         P, ws = means2D.shape[0], tile_bounds.numel() - 1
-        dst_table = np.ascontiguousarray(dst_table, dtype=np.uint64)
-        assert dst_table.shape == (ws, 9)
+        dst_table = _dst_rows(dst_table, ws)
         offs = (C.c_int64 * ws)(*[int(o) for o in row_offsets])
         self._lib.check(self.l.cgx_local2j_pack_p2p(
             P, H, W, ws, self._p(means2D), self._p(rgb), self._p(conic_opacity), self._p(means3D), self._p(scales),
@@ -142,22 +141,30 @@ class CudaPackBackend:
             self._st()), "cgx_local2j_pack_p2p")
 
     def pack_p2p_batched(self, cameras, send_index):
-        """One launch for the whole batch.  cameras: list of dicts with keys params (the eight per-camera tensors),
-        bounds, H, W, avoid, dst_table ((ws_k, 9) uint64, see pack_p2p), row_offsets ((ws_k,) int64), workspace."""
+        """One launch for the whole batch.  cameras: list of dicts with keys params (the eight per-camera tensors, or
+        six in the plane-descriptor form: means2D, rgb, conic_opacity, radii, depths, all_map), bounds, H, W, avoid,
+        dst_table ((ws_k, 9 or 10) uint64, see pack_p2p), row_offsets ((ws_k,) int64), workspace."""
         n = len(cameras)
-        table = np.zeros((n, 18), dtype=np.uint64)          # rows = struct cgx_exchange_camera
+        table = np.zeros((n, 19), dtype=np.uint64)          # rows = struct cgx_exchange_camera
         keep = []
         for k, c in enumerate(cameras):
-            means2D, rgb, conic_opacity, radii, depths, means3D, scales, rotation = [t.contiguous() for t in c["params"]]
-            dst = np.ascontiguousarray(c["dst_table"], dtype=np.uint64)
-            offs = np.ascontiguousarray(c["row_offsets"], dtype=np.int64)
+            params = [t.contiguous() for t in c["params"]]
+            if len(params) == 6:
+                means2D, rgb, conic_opacity, radii, depths, all_map = params
+                m3 = sc = rot = am = 0
+                am = all_map.data_ptr()
+            else:
+                means2D, rgb, conic_opacity, radii, depths, means3D, scales, rotation = params
+                m3, sc, rot, am = means3D.data_ptr(), scales.data_ptr(), rotation.data_ptr(), 0
             ws = c["bounds"].numel() - 1
-            assert dst.shape == (ws, 9) and offs.shape == (ws,)
-            keep.append((means2D, rgb, conic_opacity, radii, depths, means3D, scales, rotation, dst, offs))
+            dst = _dst_rows(c["dst_table"], ws)
+            offs = np.ascontiguousarray(c["row_offsets"], dtype=np.int64)
+            assert offs.shape == (ws,)
+            keep.append((params, dst, offs))
             table[k] = (means2D.shape[0], c["H"], c["W"], ws, means2D.data_ptr(), rgb.data_ptr(),
-                        conic_opacity.data_ptr(), means3D.data_ptr(), scales.data_ptr(), rotation.data_ptr(),
-                        radii.data_ptr(), depths.data_ptr(), c["bounds"].data_ptr(), int(bool(c["avoid"])),
-                        dst.ctypes.data, offs.ctypes.data, c["workspace"].data_ptr(), c["workspace"].numel())
+                        conic_opacity.data_ptr(), m3, sc, rot, radii.data_ptr(), depths.data_ptr(),
+                        c["bounds"].data_ptr(), int(bool(c["avoid"])), dst.ctypes.data, offs.ctypes.data,
+                        c["workspace"].data_ptr(), c["workspace"].numel(), am)
         from diff_gaussian_rasterization import _C          # per-stage events when a profile is being collected
 
         _C._call("cgx_local2j_pack_p2p_batched", self.l.cgx_local2j_pack_p2p_batched, n,
@@ -188,6 +195,15 @@ class CudaPackBackend:
                                                         self._p(send_index), self._p(d_m2), self._p(d_rgb),
                                                         self._p(d_co), self._p(d_m3), self._p(d_sc), self._p(d_rot),
                                                         self._st()), "cgx_unpack_grad_add_cols")
+
+
+def _dst_rows(dst_table, ws):
+    """(ws, 10) uint64 rows = struct cgx_peer_camera_dst; a 9-column table (no plane descriptors) is padded."""
+    t = np.asarray(dst_table, dtype=np.uint64)
+    if t.shape == (ws, 9):
+        t = np.concatenate([t, np.zeros((ws, 1), dtype=np.uint64)], axis=1)
+    assert t.shape == (ws, 10)
+    return np.ascontiguousarray(t)
 
 
 _default_backend = None
@@ -310,23 +326,23 @@ def _align_up(v, a=256):
     return (v + a - 1) // a * a
 
 
+# per-camera tensors of a receive region: (name, bytes per row), in arena order
 _CAM_FIELDS = (("means2D", 8), ("rgb", 12), ("conic_opacity", 16), ("means3D", 12), ("scales", 12), ("rotations", 16),
                ("radii", 4), ("depths", 4))
+_CAM_FIELDS_PLANES = (("means2D", 8), ("rgb", 12), ("conic_opacity", 16), ("all_map", 20), ("radii", 4), ("depths", 4))
 
 
-_CAM_WIDTHS = np.array([w for _, w in _CAM_FIELDS], dtype=np.int64)
-
-
-def _camera_layouts(n_rows):
-    """For an integer array of row counts (any shape): byte offsets of the eight per-camera tensors inside an arena
-    region (shape + (8,)) and the region sizes (same shape).  Every tensor starts on a 256-byte boundary."""
-    nbytes = (np.asarray(n_rows, dtype=np.int64)[..., None] * _CAM_WIDTHS + 255) // 256 * 256
+def _camera_layouts(n_rows, fields=_CAM_FIELDS):
+    """For an integer array of row counts (any shape): byte offsets of the per-camera tensors inside an arena
+    region (shape + (len(fields),)) and the region sizes (same shape).  Every tensor starts on a 256-byte boundary."""
+    widths = np.array([w for _, w in fields], dtype=np.int64)
+    nbytes = (np.asarray(n_rows, dtype=np.int64)[..., None] * widths + 255) // 256 * 256
     ends = np.cumsum(nbytes, axis=-1)
     return ends - nbytes, ends[..., -1]
 
 
-def _camera_layout(n):
-    offs, size = _camera_layouts(n)
+def _camera_layout(n, fields=_CAM_FIELDS):
+    offs, size = _camera_layouts(n, fields)
     return [int(o) for o in offs], int(size)
 
 
@@ -391,15 +407,19 @@ class _GaussianExchangeP2P(torch.autograd.Function):
         be, arena = plan["backend"], plan["arena"]
         me = plan["me"]
         bsz = len(plan["strategies"])
+        planes = plan["planes"]
         peer_base = np.array([int(p) for p in arena.recv_hdl.buffer_ptrs], dtype=np.int64)
         # address of field f of camera k in rank j's arena, and the first row this rank writes there
-        field_ptr = peer_base[:, None, None] + plan["cam_base"][:, :, None] + plan["field_off"]      # (ws, bsz, 8)
+        field_ptr = peer_base[:, None, None] + plan["cam_base"][:, :, None] + plan["field_off"]      # (ws, bsz, F)
         arena.barrier()                       # every rank is done with the previous contents of the arenas
         cameras = []
         for k in range(bsz):
             ids = plan["strategies"][k].gpu_ids
-            table = np.empty((len(ids), 9), dtype=np.uint64)
-            table[:, :8] = field_ptr[ids, k, :]
+            table = np.zeros((len(ids), 10), dtype=np.uint64)      # rows = struct cgx_peer_camera_dst
+            if planes:
+                table[:, [0, 1, 2, 9, 6, 7]] = field_ptr[ids, k, :]
+            else:
+                table[:, :8] = field_ptr[ids, k, :]
             table[:, 8] = plan["first_row"][ids, k]
             cameras.append(dict(params=plan["params"][k], bounds=plan["bounds"][k], H=plan["hw"][k][0],
                                 W=plan["hw"][k][1], avoid=plan["avoid"][k], dst_table=table,
@@ -421,12 +441,18 @@ class _GaussianExchangeP2P(torch.autograd.Function):
             m2 = f32[w[0]: w[0] + 2 * n].view(n, 2)
             rgb = f32[w[1]: w[1] + 3 * n].view(n, 3)
             co = f32[w[2]: w[2] + 4 * n].view(n, 4)
-            m3 = f32[w[3]: w[3] + 3 * n].view(n, 3)
-            sc = f32[w[4]: w[4] + 3 * n].view(n, 3)
-            rot = f32[w[5]: w[5] + 4 * n].view(n, 4)
-            rad = i32[w[6]: w[6] + n]
-            dep = f32[w[7]: w[7] + n]
-            outs += [m2, rgb, co, rad, dep, m3, sc, rot]
+            if planes:
+                am = f32[w[3]: w[3] + 5 * n].view(n, 5)
+                rad = i32[w[4]: w[4] + n]
+                dep = f32[w[5]: w[5] + n]
+                outs += [m2, rgb, co, rad, dep, am]
+            else:
+                m3 = f32[w[3]: w[3] + 3 * n].view(n, 3)
+                sc = f32[w[4]: w[4] + 3 * n].view(n, 3)
+                rot = f32[w[5]: w[5] + 4 * n].view(n, 4)
+                rad = i32[w[6]: w[6] + n]
+                dep = f32[w[7]: w[7] + n]
+                outs += [m2, rgb, co, rad, dep, m3, sc, rot]
             nondiff += [rad, dep]
         ctx.plan = plan
         ctx.shapes = [t.shape for t in flat]
@@ -441,6 +467,8 @@ class _GaussianExchangeP2P(torch.autograd.Function):
         dev = arena.dev
         bsz = len(plan["strategies"])
         ncols = plan["grad_cols"]
+        planes = plan["planes"]
+        n_out, n_in = (6, 4) if planes else (8, 6)
         owner_base = np.array([int(p) for p in arena.grad_hdl.buffer_ptrs], dtype=np.int64)
         # segment (source i -> me, camera k) sits at row grad_row[i, k] of rank i's send order
         seg_ptr = owner_base[:, None] + plan["grad_row"] * (ncols * 4)                                # (ws, bsz)
@@ -448,22 +476,28 @@ class _GaussianExchangeP2P(torch.autograd.Function):
             counts = S[:, me, k]
             if not counts.any():
                 continue                      # camera not rendered here: no gradient rows to return
-            g8 = gouts[8 * k: 8 * k + 8]
-            be.pack_grad_rows_to(seg_ptr[:, k].tolist(), counts.tolist(), ncols,
-                                 _dense_cotangents(g8, int(plan["n_recv"][me, k]), dev))
+            g = gouts[n_out * k: n_out * k + n_out]
+            n = int(plan["n_recv"][me, k])
+            if planes:                        # the (n,5) plane-descriptor cotangent rides in the means3D slot
+                cot = _dense_cotangents((g[0], g[1], g[2], None, None, None, None, None), n, dev)[:3] + \
+                    (g[5] if g[5] is not None else torch.zeros(n, 5, device=dev), None, None)
+            else:
+                cot = _dense_cotangents(g, n, dev)
+            be.pack_grad_rows_to(seg_ptr[:, k].tolist(), counts.tolist(), ncols, cot)
         arena.barrier()                       # every rank's gradient rows have landed in their owners' buffers
         n_send = plan["n_send"]
         grad_send = arena.grad[: n_send * ncols * 4].view(torch.float32).view(n_send, ncols)
         grads = []
         for k, per_dst in enumerate(plan["send_ranges"]):
-            need = ctx.needs_input_grad[1 + 6 * k: 1 + 6 * k + 6]
-            g6 = [torch.zeros(s, dtype=torch.float32, device=dev) if nd else None
-                  for s, nd in zip(ctx.shapes[6 * k: 6 * k + 6], need)]
+            need = ctx.needs_input_grad[1 + n_in * k: 1 + n_in * k + n_in]
+            shapes = ctx.shapes[n_in * k: n_in * k + n_in]
+            gk = [torch.zeros(s, dtype=torch.float32, device=dev) if nd else None for s, nd in zip(shapes, need)]
             for c in (0, 2):                  # the scatter kernel always writes means2D and conic_opacity
-                if g6[c] is None:
-                    g6[c] = torch.zeros(ctx.shapes[6 * k + c], dtype=torch.float32, device=dev)
-            be.unpack_grad_add_cols(grad_send, plan["send_index"], per_dst, ncols, g6)
-            grads += [g if nd else None for g, nd in zip(g6, need)]
+                if gk[c] is None:
+                    gk[c] = torch.zeros(shapes[c], dtype=torch.float32, device=dev)
+            be.unpack_grad_add_cols(grad_send, plan["send_index"], per_dst, ncols,
+                                    gk + [None, None] if planes else gk)
+            grads += [g if nd else None for g, nd in zip(gk, need)]
         return (None,) + tuple(grads)
 
 
@@ -480,7 +514,8 @@ def _pick_transport(transport, group, dev, backend):
 
 
 def all_to_all_communication_final(batched_rasterizers, batched_screenspace_params, batched_cuda_args,
-                                   batched_strategies, group=None, backend=None, transport=None, piggyback=None):
+                                   batched_strategies, group=None, backend=None, transport=None, piggyback=None,
+                                   planes=False):
     """See module docstring.  ``batched_screenspace_params[k]`` =
     (means2D, rgb, conic_opacity, radii, depths, means3D, scales, rotation) of camera k on this rank.
 
@@ -491,7 +526,13 @@ def all_to_all_communication_final(batched_rasterizers, batched_screenspace_para
 
     ``piggyback``: optional list of floats (same length on every rank) that rides on the size-table all-gather;
     every rank's values come back as ``stats["piggyback"][rank]``.  The balancer's render times travel this way
-    instead of in a collective (and a host synchronisation) of their own."""
+    instead of in a collective (and a host synchronisation) of their own.
+
+    ``planes=True`` (peer-to-peer transport only): ``batched_screenspace_params[k]`` = (means2D, rgb,
+    conic_opacity, radii, depths, all_map) with the camera's plane descriptors already computed by the owner
+    (`cgx.batched.preprocess_gaussians_batched(planes=True)`).  The descriptors travel instead of the 3-D
+    parameters they would be rebuilt from on the receiver (16 floats per row instead of 21, 14 gradient columns
+    back instead of 19); the sixth returned list then holds ``all_map`` per camera and the last two are None."""
     backend = backend or default_backend()
     ws, me = _world(group)
     bsz = len(batched_rasterizers)
@@ -535,8 +576,12 @@ def all_to_all_communication_final(batched_rasterizers, batched_screenspace_para
                    for k in range(bsz)]
     flat = []
     for k in range(bsz):
-        m2, rgb, co, radii, depths, m3, sc, rot = batched_screenspace_params[k]
-        flat += [m2, rgb, co, m3, sc, rot]
+        if planes:
+            m2, rgb, co, radii, depths, am = batched_screenspace_params[k]
+            flat += [m2, rgb, co, am]
+        else:
+            m2, rgb, co, radii, depths, m3, sc, rot = batched_screenspace_params[k]
+            flat += [m2, rgb, co, m3, sc, rot]
     sent_counts = my.tolist()
     self_rows = int(my[me].sum())
     stats = {"rows_sent": n_send, "rows_received": sum(recv_splits), "rows_to_self": self_rows,
@@ -545,10 +590,12 @@ def all_to_all_communication_final(batched_rasterizers, batched_screenspace_para
 
     transport = _pick_transport(transport, group, dev, backend)
     stats["transport"] = transport
+    if planes and transport != "p2p":
+        raise RuntimeError("the plane-descriptor record form needs the peer-to-peer transport")
     send_index = torch.empty(n_send, dtype=torch.int32, device=dev)
     if transport == "p2p":
         n_recv = S.sum(0)                                            # [dst][cam]
-        field_off, cam_size = _camera_layouts(n_recv)
+        field_off, cam_size = _camera_layouts(n_recv, _CAM_FIELDS_PLANES if planes else _CAM_FIELDS)
         cam_end = np.cumsum(cam_size, axis=1)
         per_src = S.reshape(ws, -1)
         grad_row = (np.cumsum(per_src, axis=1) - per_src).reshape(ws, ws, bsz)[:, me, :]
@@ -556,17 +603,24 @@ def all_to_all_communication_final(batched_rasterizers, batched_screenspace_para
         arena.ensure(int(cam_end[:, -1].max()), int(per_src.sum(1).max()) * REC_DIFF * 4)
         # gradient rows carry 19 columns only when some rank needs gradients for the 3-D parameters through the
         # exchange; every rank runs the same model code, so this is the same decision everywhere
-        grad_cols = REC_DIFF if any(flat[6 * k + c].requires_grad for k in range(bsz) for c in (3, 4, 5)) else 9
+        if planes:
+            grad_cols = 14 if any(flat[4 * k + 3].requires_grad for k in range(bsz)) else 9
+            stats["bytes_sent_fwd"] = (n_send - self_rows) * 16 * 4
+        else:
+            grad_cols = REC_DIFF if any(flat[6 * k + c].requires_grad for k in range(bsz) for c in (3, 4, 5)) else 9
         stats["bytes_sent_bwd"] = (n_send - self_rows) * grad_cols * 4
         plan = dict(backend=backend, arena=arena, me=me, ws=ws, S=S, strategies=batched_strategies,
-                    grad_cols=grad_cols, n_recv=n_recv, cam_base=cam_end - cam_size, field_off=field_off,
+                    grad_cols=grad_cols, planes=planes, n_recv=n_recv, cam_base=cam_end - cam_size, field_off=field_off,
                     first_row=S[:me].sum(0), grad_row=grad_row, bounds=bounds, scratch=scratch,
                     send_index=send_index, send_off=send_off, send_ranges=send_ranges, n_send=n_send,
                     params=[tuple(t.detach() for t in p) for p in batched_screenspace_params],
                     hw=[(r.raster_settings.image_height, r.raster_settings.image_width) for r in batched_rasterizers],
                     avoid=[a["avoid_pixel_all2all"] for a in batched_cuda_args])
         outs = _GaussianExchangeP2P.apply(plan, *flat)
-        out = [[outs[8 * k + c] for k in range(bsz)] for c in range(8)]
+        if planes:
+            out = [[outs[6 * k + c] for k in range(bsz)] for c in range(6)] + [None, None]
+        else:
+            out = [[outs[8 * k + c] for k in range(bsz)] for c in range(8)]
         return (*out, sizes_list, sent_counts, send_index, stats)
 
     # ---- 2b. collective transport: send buffer packed by one kernel per camera

@@ -106,30 +106,37 @@ class TrainingStep:
         return rgb
 
     # ------------------------------------------------------------------ single-GPU step
-    def _preprocess_all(self, args):
-        """Screen-space state of the local Gaussians for every camera of the batch (one launch)."""
+    def _preprocess_all(self, args, planes=False):
+        """Screen-space state of the local Gaussians for every camera of the batch (one launch).  With `planes`
+        every camera's tuple ends with its differentiable plane descriptors (fused into the same launches when
+        batched, the stand-alone op otherwise)."""
         from .batched import preprocess_gaussians_batched
 
         p = self.params
         if self.batched:
             return preprocess_gaussians_batched(p["means3D"], p["scales"], p["rotations"], self.sh_dummy,
-                                                p["opacities"], self.settings, args)
-        return [GaussianRasterizer(s).preprocess_gaussians(p["means3D"], p["scales"], p["rotations"], self.sh_dummy,
-                                                           p["opacities"], args) for s in self.settings]
+                                                p["opacities"], self.settings, args, planes=planes)
+        out = [GaussianRasterizer(s).preprocess_gaussians(p["means3D"], p["scales"], p["rotations"], self.sh_dummy,
+                                                          p["opacities"], args) for s in self.settings]
+        if planes:
+            out = [t + (self.all_map_for(k, p["means3D"], p["scales"], p["rotations"], t[3]),)
+                   for k, t in enumerate(out)]
+        return out
 
     def _step_single(self):
         p = self.params
         args = make_cuda_args(self.rank, self.ws, self.iteration)
         outs, heads, grads = [], [], []
-        screen = self._preprocess_all(args)
+        screen = self._preprocess_all(args, planes=self.plane_grads)
         for k, cam in enumerate(self.cams):
             rast = GaussianRasterizer(self.settings[k])
-            means2D, _, conic_opacity, radii, depths = screen[k]
+            means2D, _, conic_opacity, radii, depths = screen[k][:5]
             means2D.retain_grad()          # the densifier reads means2D.grad
             TX, TY = (cam.W + 15) // 16, (cam.H + 15) // 16
             local = self._all_local(TY, TX)
             means2D_abs = torch.zeros(self.n_local, 3, device=self.dev, requires_grad=True)
-            all_map = self.all_map_for(k, p["means3D"], p["scales"], p["rotations"], radii)
+            all_map = screen[k][5] if self.plane_grads else \
+                self.all_map_for(k, p["means3D"], p["scales"], p["rotations"], radii)
             color, n_render, n_consider, n_contrib, observe, out_all_map, plane_depth = rast.render_gaussians(
                 means2D, means2D_abs, conic_opacity, self.rgb[k], all_map, depths, radii, local, None, args)
             heads += [color, out_all_map, plane_depth]
@@ -174,14 +181,20 @@ class TrainingStep:
         strategies, _ = WD.start_strategy_final(self.cams, self.history, ctx=self.ctx)
         rasts = [GaussianRasterizer(s) for s in self.settings]
         args = [make_cuda_args(self.rank, self.ws, self.iteration) for _ in self.cams]
+        # Plane descriptors: computed by the owner inside the preprocess launch and sent instead of the 3-D
+        # parameters when the exchange stores straight into peer memory; otherwise the 3-D parameters travel
+        # (differentiably) and the descriptors are rebuilt on the receiver, as the reference does.
+        fused = self.plane_grads and self.batched and \
+            exchange._pick_transport(self.transport, None, self.dev, exchange.default_backend()) == "p2p"
         screen, keep = [], []
-        pre = self._preprocess_all(args[0])
+        pre = self._preprocess_all(args[0], planes=fused)
         for k in range(len(self.cams)):
-            means2D, _, conic_opacity, radii, depths = pre[k]
+            means2D, _, conic_opacity, radii, depths = pre[k][:5]
             means2D.retain_grad()
             keep.append((radii, means2D))
-            # the plane descriptors are rebuilt on the receiver from the 3-D parameters, which therefore travel
-            # differentiably (their gradient rows come back through the reverse exchange) unless switched off
+            if fused:
+                screen.append((means2D, self.rgb[k], conic_opacity, radii, depths, pre[k][5]))
+                continue
             m3, sc, rot = p["means3D"], p["scales"], p["rotations"]
             if not self.plane_grads:
                 m3, sc, rot = m3.detach(), sc.detach(), rot.detach()
@@ -191,12 +204,14 @@ class TrainingStep:
             times = WD.local_running_times(pending[0], pending[1], ctx=self.ctx)
         (m2, rgb, co, rad, dep, m3, sc, rot, sizes, sent, send_index, stats) = \
             exchange.all_to_all_communication_final(rasts, screen, args, strategies, transport=self.transport,
-                                                    piggyback=times)
+                                                    piggyback=times, planes=fused)
         if times is not None:
             WD.finish_strategy_final(self.cams, self.history, pending[0], pending[1], ctx=self.ctx,
                                      gathered_times=stats["piggyback"])
         self._exchange.update(bytes_sent_fwd=stats["bytes_sent_fwd"], bytes_sent_bwd=stats["bytes_sent_bwd"],
-                              transport=stats["transport"], rows_sent=stats["rows_sent"])
+                              transport=stats["transport"], rows_sent=stats["rows_sent"],
+                              record="plane descriptors (16 floats fwd, 14 bwd)" if fused
+                              else "3-D parameters (21 floats fwd, 19 or 9 bwd)")
         heads, grads = [], []
         for k, strat in enumerate(strategies):
             local = strat.get_compute_locally()
@@ -204,7 +219,7 @@ class TrainingStep:
             if local is None or n_rows < 10:
                 args[k]["stats_collector"].update(forward_render_time=0.0, backward_render_time=0.0)
                 continue
-            all_map = self.all_map_for(k, m3[k], sc[k], rot[k], rad[k])
+            all_map = m3[k] if fused else self.all_map_for(k, m3[k], sc[k], rot[k], rad[k])
             m2abs = torch.zeros(n_rows, 3, device=self.dev, requires_grad=True)
             color, _, _, _, _, out_all_map, plane_depth = rasts[k].render_gaussians(
                 m2[k], m2abs, co[k], rgb[k], all_map, dep[k], rad[k], local, None, args[k])

@@ -635,6 +635,7 @@ struct PeerCameraDst {
     int* radii;
     float* depths;
     long long row;
+    float* all_map;      // plane-descriptor form of the record: replaces means3D / scales / rotations
 };
 struct PeerDsts {
     PeerCameraDst d[MAX_WS];
@@ -644,6 +645,9 @@ struct PeerDsts {
 // tensors of the rank that renders it (its own memory for the local band), in ascending source index behind the
 // rows of lower source ranks.  No send buffer, no collective, no unpack on the receiver.
 // `dsts` / `local_row`: per participating rank of this camera (kernel-parameter space).  `block`: this CTA's tile.
+// PLANES: the record carries the camera's plane descriptors (5 floats, read from `means3D`'s slot as a (P,5) array)
+// instead of the 3-D parameters (10 floats): [m2 2 | rgb 3 | co 4 | all_map 5 | radius | depth].
+template <bool PLANES>
 __device__ __forceinline__ void
 pack_p2p_tile(int block, int P, int gx, int gy, int ws, int nblocks, const float2* __restrict__ means2D,
               const float* __restrict__ rgb, const float4* __restrict__ conic_opacity,
@@ -656,11 +660,12 @@ pack_p2p_tile(int block, int P, int gx, int gy, int ws, int nblocks, const float
     // The CTA's selected rows are compacted field by field in shared memory and leave as eight contiguous bursts
     // (consecutive threads store consecutive words): full-width transactions, local or across NVLink.
     __shared__ uint32_t s_warp_cnt[PACK_TILE / 32];
-    __shared__ float s_f[21][PACK_TILE + 1];   // field-major staging: [m2 2 | rgb 3 | co 4 | m3 3 | sc 3 | rot 4 | radius | depth]
+    constexpr int NF = PLANES ? 16 : 21;       // staged fields; the last two are radius and depth
+    __shared__ float s_f[NF][PACK_TILE + 1];   // field-major staging: [m2 2 | rgb 3 | co 4 | m3 3 | sc 3 | rot 4 | radius | depth]
     const int i = block * PACK_TILE + threadIdx.x;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     uint32_t bits = 0;
-    float rec[21];
+    float rec[NF];
     if (i < P) {
         const float2 m2 = means2D[i];
         const int rad = radii[i];
@@ -673,15 +678,20 @@ pack_p2p_tile(int block, int P, int gx, int gy, int ws, int nblocks, const float
                 if (touches_band(tmin, tmax, bounds[rk], bounds[rk + 1], gx, avoid)) bits |= 1u << rk;
         if (bits) {
             const float4 co = conic_opacity[i];
-            const float4 q = rotations[i];
             rec[0] = m2.x; rec[1] = m2.y;
             rec[2] = rgb[3 * i]; rec[3] = rgb[3 * i + 1]; rec[4] = rgb[3 * i + 2];
             rec[5] = co.x; rec[6] = co.y; rec[7] = co.z; rec[8] = co.w;
-            rec[9] = means3D[3 * i]; rec[10] = means3D[3 * i + 1]; rec[11] = means3D[3 * i + 2];
-            rec[12] = scales[3 * i]; rec[13] = scales[3 * i + 1]; rec[14] = scales[3 * i + 2];
-            rec[15] = q.x; rec[16] = q.y; rec[17] = q.z; rec[18] = q.w;
-            rec[19] = __int_as_float(rad);
-            rec[20] = depths[i];
+            if (PLANES) {
+#pragma unroll
+                for (int k = 0; k < 5; k++) rec[9 + k] = means3D[5 * (size_t)i + k];
+            } else {
+                const float4 q = rotations[i];
+                rec[9] = means3D[3 * i]; rec[10] = means3D[3 * i + 1]; rec[11] = means3D[3 * i + 2];
+                rec[12] = scales[3 * i]; rec[13] = scales[3 * i + 1]; rec[14] = scales[3 * i + 2];
+                rec[15] = q.x; rec[16] = q.y; rec[17] = q.z; rec[18] = q.w;
+            }
+            rec[NF - 2] = __int_as_float(rad);
+            rec[NF - 1] = depths[i];
         }
     }
     for (int rk = 0; rk < ws; rk++) {
@@ -702,7 +712,7 @@ pack_p2p_tile(int block, int P, int gx, int gy, int ws, int nblocks, const float
         const long long seg0 = (long long)block_prefix[(size_t)rk * nblocks + block];
         if (sel) {
 #pragma unroll
-            for (int k = 0; k < 21; k++) s_f[k][slot] = rec[k];
+            for (int k = 0; k < NF; k++) s_f[k][slot] = rec[k];
             if (send_index) send_index[local_row[rk] + seg0 + slot] = i;
         }
         __syncthreads();
@@ -717,12 +727,16 @@ pack_p2p_tile(int block, int P, int gx, int gy, int ws, int nblocks, const float
         burst(D.means2D, 0, 2);
         burst(D.rgb, 2, 3);
         burst(D.conic_opacity, 5, 4);
-        burst(D.means3D, 9, 3);
-        burst(D.scales, 12, 3);
-        burst(D.rotations, 15, 4);
+        if (PLANES) {
+            burst(D.all_map, 9, 5);
+        } else {
+            burst(D.means3D, 9, 3);
+            burst(D.scales, 12, 3);
+            burst(D.rotations, 15, 4);
+        }
         for (int e = threadIdx.x; e < (int)cnt; e += PACK_TILE) {
-            D.radii[row0 + e] = __float_as_int(s_f[19][e]);
-            D.depths[row0 + e] = s_f[20][e];
+            D.radii[row0 + e] = __float_as_int(s_f[NF - 2][e]);
+            D.depths[row0 + e] = s_f[NF - 1][e];
         }
         __syncthreads();
     }
@@ -737,8 +751,8 @@ local2j_pack_p2p_kernel(int P, int gx, int gy, int ws, int nblocks, const float2
                         const uint32_t* __restrict__ block_prefix, const __grid_constant__ PeerDsts dsts,
                         const __grid_constant__ PackOffsets local_offs, int32_t* __restrict__ send_index)
 {
-    pack_p2p_tile(blockIdx.x, P, gx, gy, ws, nblocks, means2D, rgb, conic_opacity, means3D, scales, rotations, radii,
-                  depths, bounds, avoid, block_prefix, dsts.d, local_offs.row, send_index);
+    pack_p2p_tile<false>(blockIdx.x, P, gx, gy, ws, nblocks, means2D, rgb, conic_opacity, means3D, scales, rotations,
+                         radii, depths, bounds, avoid, block_prefix, dsts.d, local_offs.row, send_index);
 }
 
 // All cameras of a batch in one launch: blockIdx.y = camera, blockIdx.x = tile of that camera's local Gaussians.
@@ -764,14 +778,15 @@ struct ExchangeBatch {
     long long local_row[MAX_XENTRIES];
 };
 
+template <bool PLANES>
 __global__ void __launch_bounds__(PACK_TILE)
 local2j_pack_p2p_batched_kernel(const __grid_constant__ ExchangeBatch b, int32_t* __restrict__ send_index)
 {
     const ExchangeCamera& c = b.cam[blockIdx.y];
     if ((int)blockIdx.x >= c.nblocks) return;          // uniform over the CTA
-    pack_p2p_tile(blockIdx.x, c.P, c.gx, c.gy, c.ws, c.nblocks, c.means2D, c.rgb, c.conic_opacity, c.means3D,
-                  c.scales, c.rotations, c.radii, c.depths, c.bounds, c.avoid != 0, c.block_prefix,
-                  b.dst + c.entry0, b.local_row + c.entry0, send_index);
+    pack_p2p_tile<PLANES>(blockIdx.x, c.P, c.gx, c.gy, c.ws, c.nblocks, c.means2D, c.rgb, c.conic_opacity, c.means3D,
+                          c.scales, c.rotations, c.radii, c.depths, c.bounds, c.avoid != 0, c.block_prefix,
+                          b.dst + c.entry0, b.local_row + c.entry0, send_index);
 }
 
 struct GradSegments {
@@ -781,7 +796,8 @@ struct GradSegments {
 };
 
 // NCOLS = 19: all differentiable columns; NCOLS = 9: only means2D | rgb | conic_opacity (the 3-D parameters carry
-// no gradient back when the receiver builds its plane descriptors without autograd).
+// no gradient back when the receiver builds its plane descriptors without autograd); NCOLS = 14: means2D | rgb |
+// conic_opacity | plane descriptors (5), whose (n,5) array is passed in the means3D argument.
 template <int NCOLS>
 __global__ void __launch_bounds__(256)
 pack_grad_rows_to_kernel(GradSegments sg, const float* __restrict__ d_means2D, const float* __restrict__ d_rgb,
@@ -799,6 +815,7 @@ pack_grad_rows_to_kernel(GradSegments sg, const float* __restrict__ d_means2D, c
     if (c < 2) { if (d_means2D) v = d_means2D[2 * lrow + c]; }
     else if (c < 5) { if (d_rgb) v = d_rgb[3 * lrow + (c - 2)]; }
     else if (c < 9) { if (d_co) v = d_co[4 * lrow + (c - 5)]; }
+    else if (NCOLS == 14) { if (d_means3D) v = d_means3D[5 * lrow + (c - 9)]; }     // plane descriptors (n,5)
     else if (c < 12) { if (d_means3D) v = d_means3D[3 * lrow + (c - 9)]; }
     else if (c < 15) { if (d_scales) v = d_scales[3 * lrow + (c - 12)]; }
     else { if (d_rot) v = d_rot[4 * lrow + (c - 15)]; }
@@ -825,6 +842,7 @@ unpack_grad_add_cols_kernel(RowRanges rr, const float* __restrict__ g, const int
     if (c < 2) atomicAdd(d_means2D + 2 * i + c, v);
     else if (c < 5) { if (d_rgb) atomicAdd(d_rgb + 3 * i + (c - 2), v); }
     else if (c < 9) atomicAdd(d_co + 4 * i + (c - 5), v);
+    else if (NCOLS == 14) { if (d_means3D) atomicAdd(d_means3D + 5 * i + (c - 9), v); }   // plane descriptors (P,5)
     else if (c < 12) { if (d_means3D) atomicAdd(d_means3D + 3 * i + (c - 9), v); }
     else if (c < 15) { if (d_scales) atomicAdd(d_scales + 3 * i + (c - 12), v); }
     else { if (d_rot) atomicAdd(d_rot + 4 * i + (c - 15), v); }
@@ -1130,7 +1148,7 @@ extern "C" int cgx_local2j_pack_p2p(int P, int H, int W, int ws, const float* me
     for (int j = 0; j < MAX_WS; j++) {
         offs.row[j] = (j < ws && send_row_offset) ? (long long)send_row_offset[j] : 0;
         if (j >= ws) {
-            dsts.d[j] = PeerCameraDst{nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, 0};
+            dsts.d[j] = PeerCameraDst{nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, 0, nullptr};
             continue;
         }
         const cgx_peer_camera_dst& s = dst[j];
@@ -1139,7 +1157,7 @@ extern "C" int cgx_local2j_pack_p2p(int P, int H, int W, int ws, const float* me
             return CGX_EINVAL;
         if (((uintptr_t)s.means2D & 7) || !aligned16(s.conic_opacity) || !aligned16(s.rotations)) return CGX_EINVAL;
         dsts.d[j] = PeerCameraDst{s.means2D, s.rgb, s.conic_opacity, s.means3D, s.scales, s.rotations, s.radii,
-                                  s.depths, (long long)s.first_row};
+                                  s.depths, (long long)s.first_row, nullptr};
     }
     const int gx = (W + CGX_BLOCK_X - 1) / CGX_BLOCK_X, gy = (H + CGX_BLOCK_Y - 1) / CGX_BLOCK_Y;
     const int nblocks = (P + PACK_TILE - 1) / PACK_TILE;
@@ -1154,6 +1172,9 @@ extern "C" int cgx_local2j_pack_p2p_batched(int n_cameras, const cgx_exchange_ca
                                             void* stream)
 {
     if (n_cameras < 0 || (n_cameras > 0 && !cams)) return CGX_EINVAL;
+    const bool planes = n_cameras > 0 && cams[0].all_map != nullptr;
+    for (int k = 0; k < n_cameras; k++)
+        if ((cams[k].all_map != nullptr) != planes) return CGX_EINVAL;     // one record form per call
     int k0 = 0;
     while (k0 < n_cameras) {
         // as many consecutive cameras per launch as the parameter block holds
@@ -1173,18 +1194,17 @@ extern "C" int cgx_local2j_pack_p2p_batched(int n_cameras, const cgx_exchange_ca
             x.avoid = c.avoid_pixel_all2all != 0;
             x.entry0 = entries;
             if (x.P > 0) {
-                if (!c.means2D || !c.rgb || !c.conic_opacity || !c.means3D || !c.scales || !c.rotations || !c.radii ||
-                    !c.depths || !c.tile_bounds || !c.workspace)
+                if (!c.means2D || !c.rgb || !c.conic_opacity || !c.radii || !c.depths || !c.tile_bounds || !c.workspace)
                     return CGX_EINVAL;
+                if (!planes && (!c.means3D || !c.scales || !c.rotations || !aligned16(c.rotations))) return CGX_EINVAL;
                 if (send_index && !c.send_row_offset) return CGX_EINVAL;
-                if (((uintptr_t)c.means2D & 7) || !aligned16(c.conic_opacity) || !aligned16(c.rotations))
-                    return CGX_EINVAL;
+                if (((uintptr_t)c.means2D & 7) || !aligned16(c.conic_opacity)) return CGX_EINVAL;
                 if ((size_t)c.workspace_bytes < cgx_local2j_workspace_bytes(x.P, x.ws)) return CGX_ENOMEM;
             }
             x.means2D = (const float2*)c.means2D;
             x.rgb = c.rgb;
             x.conic_opacity = (const float4*)c.conic_opacity;
-            x.means3D = c.means3D;
+            x.means3D = planes ? c.all_map : c.means3D;
             x.scales = c.scales;
             x.rotations = (const float4*)c.rotations;
             x.radii = c.radii;
@@ -1194,14 +1214,14 @@ extern "C" int cgx_local2j_pack_p2p_batched(int n_cameras, const cgx_exchange_ca
             for (int j = 0; j < x.ws; j++) {
                 const cgx_peer_camera_dst& d = c.dst[j];
                 if (x.P > 0) {
-                    if (!d.means2D || !d.rgb || !d.conic_opacity || !d.means3D || !d.scales || !d.rotations ||
-                        !d.radii || !d.depths || d.first_row < 0)
+                    if (!d.means2D || !d.rgb || !d.conic_opacity || !d.radii || !d.depths || d.first_row < 0)
                         return CGX_EINVAL;
-                    if (((uintptr_t)d.means2D & 7) || !aligned16(d.conic_opacity) || !aligned16(d.rotations))
+                    if (planes ? !d.all_map : (!d.means3D || !d.scales || !d.rotations || !aligned16(d.rotations)))
                         return CGX_EINVAL;
+                    if (((uintptr_t)d.means2D & 7) || !aligned16(d.conic_opacity)) return CGX_EINVAL;
                 }
                 b.dst[entries + j] = PeerCameraDst{d.means2D, d.rgb, d.conic_opacity, d.means3D, d.scales,
-                                                   d.rotations, d.radii, d.depths, (long long)d.first_row};
+                                                   d.rotations, d.radii, d.depths, (long long)d.first_row, d.all_map};
                 b.local_row[entries + j] = c.send_row_offset ? (long long)c.send_row_offset[j] : 0;
             }
             entries += x.ws;
@@ -1210,8 +1230,12 @@ extern "C" int cgx_local2j_pack_p2p_batched(int n_cameras, const cgx_exchange_ca
         }
         if (n == 0) return CGX_EINVAL;     // one camera with more ranks than a launch can describe
         if (max_blocks > 0) {
-            local2j_pack_p2p_batched_kernel<<<dim3((unsigned)max_blocks, (unsigned)n), PACK_TILE, 0,
-                                              (cudaStream_t)stream>>>(b, send_index);
+            if (planes)
+                local2j_pack_p2p_batched_kernel<true><<<dim3((unsigned)max_blocks, (unsigned)n), PACK_TILE, 0,
+                                                        (cudaStream_t)stream>>>(b, send_index);
+            else
+                local2j_pack_p2p_batched_kernel<false><<<dim3((unsigned)max_blocks, (unsigned)n), PACK_TILE, 0,
+                                                         (cudaStream_t)stream>>>(b, send_index);
             const int st = check_launch();
             if (st != CGX_OK) return st;
         }
@@ -1225,7 +1249,7 @@ extern "C" int cgx_pack_grad_rows_to(int n_segments, float* const* seg_rows, con
                                      const float* d_means3D, const float* d_scales, const float* d_rotations,
                                      void* stream)
 {
-    if (n_segments < 0 || n_segments > MAX_WS || (ncols != 9 && ncols != 19)) return CGX_EINVAL;
+    if (n_segments < 0 || n_segments > MAX_WS || (ncols != 9 && ncols != 14 && ncols != 19)) return CGX_EINVAL;
     if (n_segments == 0) return CGX_OK;
     if (!seg_rows || !seg_count) return CGX_EINVAL;
     GradSegments sg;
@@ -1241,6 +1265,9 @@ extern "C" int cgx_pack_grad_rows_to(int n_segments, float* const* seg_rows, con
     if (ncols == 9)
         pack_grad_rows_to_kernel<9><<<(unsigned)((n * 9 + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
             sg, d_means2D, d_rgb, d_conic_opacity, d_means3D, d_scales, d_rotations);
+    else if (ncols == 14)
+        pack_grad_rows_to_kernel<14><<<(unsigned)((n * 14 + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+            sg, d_means2D, d_rgb, d_conic_opacity, d_means3D, nullptr, nullptr);
     else
         pack_grad_rows_to_kernel<19><<<(unsigned)((n * 19 + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
             sg, d_means2D, d_rgb, d_conic_opacity, d_means3D, d_scales, d_rotations);
@@ -1308,7 +1335,7 @@ extern "C" int cgx_unpack_grad_add_cols(int n_ranges, const int64_t* range_start
                                         float* d_rgb, float* d_conic_opacity, float* d_means3D, float* d_scales,
                                         float* d_rotations, void* stream)
 {
-    if (n_ranges < 0 || n_ranges > MAX_WS || (ncols != 9 && ncols != 19)) return CGX_EINVAL;
+    if (n_ranges < 0 || n_ranges > MAX_WS || (ncols != 9 && ncols != 14 && ncols != 19)) return CGX_EINVAL;
     if (n_ranges == 0) return CGX_OK;
     if (!range_start || !range_stop) return CGX_EINVAL;
     RowRanges rr;
@@ -1325,6 +1352,9 @@ extern "C" int cgx_unpack_grad_add_cols(int n_ranges, const int64_t* range_start
     if (ncols == 9)
         unpack_grad_add_cols_kernel<9><<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
             rr, grad_rows, send_index, d_means2D, d_rgb, d_conic_opacity, d_means3D, d_scales, d_rotations);
+    else if (ncols == 14)
+        unpack_grad_add_cols_kernel<14><<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+            rr, grad_rows, send_index, d_means2D, d_rgb, d_conic_opacity, d_means3D, nullptr, nullptr);
     else
         unpack_grad_add_cols_kernel<19><<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
             rr, grad_rows, send_index, d_means2D, d_rgb, d_conic_opacity, d_means3D, d_scales, d_rotations);

@@ -249,10 +249,95 @@ sh_to_rgb_kernel(int P, int deg, int M, const float* __restrict__ means3D, const
 }
 
 
-// PGSR plane descriptor of every Gaussian for one camera, as the reference's caller builds it in tensor code
-// (gaussian_renderer/__init__.py:1501-1518): the rotation-matrix column of the smallest scale axis, flipped to
-// face the camera, rotated into camera space; then [normal_cam(3), 1, |normal_cam . p_cam|].
-// The quaternion is normalised here (the caller normalises before converting).  Forward only.
+// PGSR per-Gaussian plane descriptor for one camera (the tensor code of gaussian_renderer/__init__.py:1501-1518):
+// the rotation-matrix column of the smallest scale is the plane normal in world space, flipped to face the camera,
+// rotated into camera space; then [normal_cam(3), 1, |normal_cam . p_cam|].  The quaternion is normalised here
+// (the caller normalises before converting).  V: 4x4 row-vector view matrix.
+__device__ __forceinline__ void plane_fwd(const float3 p, const float3 sc, float4 q, const float* V,
+                                          const float3 campos, float* o5)
+{
+    const float qn = fmaxf(sqrtf(q.x * q.x + q.y * q.y + q.z * q.z + q.w * q.w), 1e-12f);
+    q = {q.x / qn, q.y / qn, q.z / qn, q.w / qn};
+    const float r = q.x, x = q.y, y = q.z, z = q.w;
+    const float two_s = 2.0f / (r * r + x * x + y * y + z * z);
+    int idx = 0;
+    float smin = sc.x;
+    if (sc.y < smin) { smin = sc.y; idx = 1; }
+    if (sc.z < smin) { smin = sc.z; idx = 2; }
+    float3 n;
+    if (idx == 0) n = {1.f - two_s * (y * y + z * z), two_s * (x * y + z * r), two_s * (x * z - y * r)};
+    else if (idx == 1) n = {two_s * (x * y - z * r), 1.f - two_s * (x * x + z * z), two_s * (y * z + x * r)};
+    else n = {two_s * (x * z + y * r), two_s * (y * z - x * r), 1.f - two_s * (x * x + y * y)};
+    const float3 tc = {campos.x - p.x, campos.y - p.y, campos.z - p.z};
+    if (n.x * tc.x + n.y * tc.y + n.z * tc.z < 0.0f) n = {-n.x, -n.y, -n.z};
+    const float3 ln = {n.x * V[0] + n.y * V[4] + n.z * V[8], n.x * V[1] + n.y * V[5] + n.z * V[9],
+                       n.x * V[2] + n.y * V[6] + n.z * V[10]};
+    const float3 pc = {p.x * V[0] + p.y * V[4] + p.z * V[8] + V[12], p.x * V[1] + p.y * V[5] + p.z * V[9] + V[13],
+                       p.x * V[2] + p.y * V[6] + p.z * V[10] + V[14]};
+    o5[0] = ln.x; o5[1] = ln.y; o5[2] = ln.z; o5[3] = 1.0f;
+    o5[4] = fabsf(ln.x * pc.x + ln.y * pc.y + ln.z * pc.z);
+}
+
+// Backward of plane_fwd: cotangent g[5] -> ADDED to dp (mean, through the plane distance) and dq (raw quaternion,
+// through the chosen rotation column and the normalisation).  The choice of the column, the flip towards the
+// camera and the sign of the distance are piecewise constant; scales get no gradient.
+__device__ __forceinline__ void plane_bwd(const float3 p, const float3 sc, const float4 qraw, const float* V,
+                                          const float3 campos, const float* g, float3& dp, float4& dq)
+{
+    const float qn = fmaxf(sqrtf(qraw.x * qraw.x + qraw.y * qraw.y + qraw.z * qraw.z + qraw.w * qraw.w), 1e-12f);
+    const float r = qraw.x / qn, x = qraw.y / qn, y = qraw.z / qn, z = qraw.w / qn;
+    int idx = 0;
+    float smin = sc.x;
+    if (sc.y < smin) { smin = sc.y; idx = 1; }
+    if (sc.z < smin) { smin = sc.z; idx = 2; }
+    // on the unit sphere the rotation column is a quadratic form with factor 2
+    float3 n;
+    if (idx == 0) n = {1.f - 2.f * (y * y + z * z), 2.f * (x * y + z * r), 2.f * (x * z - y * r)};
+    else if (idx == 1) n = {2.f * (x * y - z * r), 1.f - 2.f * (x * x + z * z), 2.f * (y * z + x * r)};
+    else n = {2.f * (x * z + y * r), 2.f * (y * z - x * r), 1.f - 2.f * (x * x + y * y)};
+    const float3 tc = {campos.x - p.x, campos.y - p.y, campos.z - p.z};
+    const float flip = (n.x * tc.x + n.y * tc.y + n.z * tc.z < 0.0f) ? -1.f : 1.f;
+    n = {flip * n.x, flip * n.y, flip * n.z};
+    const float3 ln = {n.x * V[0] + n.y * V[4] + n.z * V[8], n.x * V[1] + n.y * V[5] + n.z * V[9],
+                       n.x * V[2] + n.y * V[6] + n.z * V[10]};
+    const float3 pc = {p.x * V[0] + p.y * V[4] + p.z * V[8] + V[12], p.x * V[1] + p.y * V[5] + p.z * V[9] + V[13],
+                       p.x * V[2] + p.y * V[6] + p.z * V[10] + V[14]};
+    const float dot = ln.x * pc.x + ln.y * pc.y + ln.z * pc.z;
+    const float gs = dot > 0.f ? g[4] : (dot < 0.f ? -g[4] : 0.f);          // d|t|/dt, 0 at t = 0 as torch.abs
+    const float3 dln = {g[0] + gs * pc.x, g[1] + gs * pc.y, g[2] + gs * pc.z};
+    const float3 dpc = {gs * ln.x, gs * ln.y, gs * ln.z};
+    dp.x += dpc.x * V[0] + dpc.y * V[1] + dpc.z * V[2];
+    dp.y += dpc.x * V[4] + dpc.y * V[5] + dpc.z * V[6];
+    dp.z += dpc.x * V[8] + dpc.y * V[9] + dpc.z * V[10];
+    const float3 dc = {flip * (dln.x * V[0] + dln.y * V[1] + dln.z * V[2]),
+                       flip * (dln.x * V[4] + dln.y * V[5] + dln.z * V[6]),
+                       flip * (dln.x * V[8] + dln.y * V[9] + dln.z * V[10])};      // cotangent of the column
+    float gr, gx, gy, gz;
+    if (idx == 0) {
+        gr = 2.f * (z * dc.y - y * dc.z);
+        gx = 2.f * (y * dc.y + z * dc.z);
+        gy = -4.f * y * dc.x + 2.f * (x * dc.y - r * dc.z);
+        gz = -4.f * z * dc.x + 2.f * (r * dc.y + x * dc.z);
+    } else if (idx == 1) {
+        gr = 2.f * (x * dc.z - z * dc.x);
+        gx = 2.f * y * dc.x - 4.f * x * dc.y + 2.f * r * dc.z;
+        gy = 2.f * (x * dc.x + z * dc.z);
+        gz = -2.f * r * dc.x - 4.f * z * dc.y + 2.f * y * dc.z;
+    } else {
+        gr = 2.f * (y * dc.x - x * dc.y);
+        gx = 2.f * z * dc.x - 2.f * r * dc.y - 4.f * x * dc.z;
+        gy = 2.f * r * dc.x + 2.f * z * dc.y - 4.f * y * dc.z;
+        gz = 2.f * (x * dc.x + y * dc.y);
+    }
+    // through q / |q|: remove the radial part, divide by the norm
+    const float radial = r * gr + x * gx + y * gy + z * gz;
+    dq.x += (gr - r * radial) / qn;
+    dq.y += (gx - x * radial) / qn;
+    dq.z += (gy - y * radial) / qn;
+    dq.w += (gz - z * radial) / qn;
+}
+
+// radii optional: rows with radius <= 0 (never rasterized) get zeros.
 __global__ void __launch_bounds__(256)
 all_map_kernel(int P, const float* __restrict__ means3D, const float* __restrict__ scales,
                const float4* __restrict__ rotations, const int* __restrict__ radii,
@@ -264,37 +349,13 @@ all_map_kernel(int P, const float* __restrict__ means3D, const float* __restrict
     if (!radii || radii[i] > 0) {
         const float3 p = {means3D[3 * i], means3D[3 * i + 1], means3D[3 * i + 2]};
         const float3 sc = {scales[3 * i], scales[3 * i + 1], scales[3 * i + 2]};
-        float4 q = rotations[i];
-        const float qn = fmaxf(sqrtf(q.x * q.x + q.y * q.y + q.z * q.z + q.w * q.w), 1e-12f);
-        q = {q.x / qn, q.y / qn, q.z / qn, q.w / qn};
-        const float r = q.x, x = q.y, y = q.z, z = q.w;
-        const float two_s = 2.0f / (r * r + x * x + y * y + z * z);
-        int idx = 0;
-        float smin = sc.x;
-        if (sc.y < smin) { smin = sc.y; idx = 1; }
-        if (sc.z < smin) { smin = sc.z; idx = 2; }
-        float3 n;
-        if (idx == 0) n = {1.f - two_s * (y * y + z * z), two_s * (x * y + z * r), two_s * (x * z - y * r)};
-        else if (idx == 1) n = {two_s * (x * y - z * r), 1.f - two_s * (x * x + z * z), two_s * (y * z + x * r)};
-        else n = {two_s * (x * z + y * r), two_s * (y * z - x * r), 1.f - two_s * (x * x + y * y)};
-        const float3 tc = {campos[0] - p.x, campos[1] - p.y, campos[2] - p.z};
-        if (n.x * tc.x + n.y * tc.y + n.z * tc.z < 0.0f) n = {-n.x, -n.y, -n.z};
-        const float* V = viewmatrix;
-        const float3 ln = {n.x * V[0] + n.y * V[4] + n.z * V[8], n.x * V[1] + n.y * V[5] + n.z * V[9],
-                           n.x * V[2] + n.y * V[6] + n.z * V[10]};
-        const float3 pc = {p.x * V[0] + p.y * V[4] + p.z * V[8] + V[12], p.x * V[1] + p.y * V[5] + p.z * V[9] + V[13],
-                           p.x * V[2] + p.y * V[6] + p.z * V[10] + V[14]};
-        o5[0] = ln.x; o5[1] = ln.y; o5[2] = ln.z; o5[3] = 1.0f;
-        o5[4] = fabsf(ln.x * pc.x + ln.y * pc.y + ln.z * pc.z);
+        plane_fwd(p, sc, rotations[i], viewmatrix, make_float3(campos[0], campos[1], campos[2]), o5);
     }
 #pragma unroll
     for (int k = 0; k < 5; k++) out[5 * (size_t)i + k] = o5[k];
 }
 
-// Backward of all_map_kernel: cotangent of the 5-vector -> cotangents of the mean (through the plane distance)
-// and of the raw quaternion (through the chosen rotation column and the normalisation).  The choice of the
-// column, the flip towards the camera and the sign of the distance are piecewise constant; scales get no gradient.
-// dL_dmeans3D / dL_drotations are written (rows with radius <= 0 get zeros).
+// dL_dmeans3D / dL_drotations are WRITTEN (rows with radius <= 0 get zeros).
 __global__ void __launch_bounds__(256)
 all_map_bwd_kernel(int P, const float* __restrict__ means3D, const float* __restrict__ scales,
                    const float4* __restrict__ rotations, const int* __restrict__ radii,
@@ -309,56 +370,10 @@ all_map_bwd_kernel(int P, const float* __restrict__ means3D, const float* __rest
     if (!radii || radii[i] > 0) {
         const float3 p = {means3D[3 * i], means3D[3 * i + 1], means3D[3 * i + 2]};
         const float3 sc = {scales[3 * i], scales[3 * i + 1], scales[3 * i + 2]};
-        const float4 qraw = rotations[i];
-        const float qn = fmaxf(sqrtf(qraw.x * qraw.x + qraw.y * qraw.y + qraw.z * qraw.z + qraw.w * qraw.w), 1e-12f);
-        const float r = qraw.x / qn, x = qraw.y / qn, y = qraw.z / qn, z = qraw.w / qn;
-        int idx = 0;
-        float smin = sc.x;
-        if (sc.y < smin) { smin = sc.y; idx = 1; }
-        if (sc.z < smin) { smin = sc.z; idx = 2; }
-        // on the unit sphere the rotation column is a quadratic form with factor 2
-        float3 n;
-        if (idx == 0) n = {1.f - 2.f * (y * y + z * z), 2.f * (x * y + z * r), 2.f * (x * z - y * r)};
-        else if (idx == 1) n = {2.f * (x * y - z * r), 1.f - 2.f * (x * x + z * z), 2.f * (y * z + x * r)};
-        else n = {2.f * (x * z + y * r), 2.f * (y * z - x * r), 1.f - 2.f * (x * x + y * y)};
-        const float3 tc = {campos[0] - p.x, campos[1] - p.y, campos[2] - p.z};
-        const float flip = (n.x * tc.x + n.y * tc.y + n.z * tc.z < 0.0f) ? -1.f : 1.f;
-        n = {flip * n.x, flip * n.y, flip * n.z};
-        const float* V = viewmatrix;
-        const float3 ln = {n.x * V[0] + n.y * V[4] + n.z * V[8], n.x * V[1] + n.y * V[5] + n.z * V[9],
-                           n.x * V[2] + n.y * V[6] + n.z * V[10]};
-        const float3 pc = {p.x * V[0] + p.y * V[4] + p.z * V[8] + V[12], p.x * V[1] + p.y * V[5] + p.z * V[9] + V[13],
-                           p.x * V[2] + p.y * V[6] + p.z * V[10] + V[14]};
-        const float* g = dL_dall_map + 5 * (size_t)i;
-        const float dot = ln.x * pc.x + ln.y * pc.y + ln.z * pc.z;
-        const float gs = dot > 0.f ? g[4] : (dot < 0.f ? -g[4] : 0.f);          // d|t|/dt, 0 at t = 0 as torch.abs
-        const float3 dln = {g[0] + gs * pc.x, g[1] + gs * pc.y, g[2] + gs * pc.z};
-        const float3 dpc = {gs * ln.x, gs * ln.y, gs * ln.z};
-        dp = {dpc.x * V[0] + dpc.y * V[1] + dpc.z * V[2], dpc.x * V[4] + dpc.y * V[5] + dpc.z * V[6],
-              dpc.x * V[8] + dpc.y * V[9] + dpc.z * V[10]};
-        const float3 dc = {flip * (dln.x * V[0] + dln.y * V[1] + dln.z * V[2]),
-                           flip * (dln.x * V[4] + dln.y * V[5] + dln.z * V[6]),
-                           flip * (dln.x * V[8] + dln.y * V[9] + dln.z * V[10])};      // cotangent of the column
-        float gr, gx, gy, gz;
-        if (idx == 0) {
-            gr = 2.f * (z * dc.y - y * dc.z);
-            gx = 2.f * (y * dc.y + z * dc.z);
-            gy = -4.f * y * dc.x + 2.f * (x * dc.y - r * dc.z);
-            gz = -4.f * z * dc.x + 2.f * (r * dc.y + x * dc.z);
-        } else if (idx == 1) {
-            gr = 2.f * (x * dc.z - z * dc.x);
-            gx = 2.f * y * dc.x - 4.f * x * dc.y + 2.f * r * dc.z;
-            gy = 2.f * (x * dc.x + z * dc.z);
-            gz = -2.f * r * dc.x - 4.f * z * dc.y + 2.f * y * dc.z;
-        } else {
-            gr = 2.f * (y * dc.x - x * dc.y);
-            gx = 2.f * z * dc.x - 2.f * r * dc.y - 4.f * x * dc.z;
-            gy = 2.f * r * dc.x + 2.f * z * dc.y - 4.f * y * dc.z;
-            gz = 2.f * (x * dc.x + y * dc.y);
-        }
-        // through q / |q|: remove the radial part, divide by the norm
-        const float radial = r * gr + x * gx + y * gy + z * gz;
-        dq = {(gr - r * radial) / qn, (gx - x * radial) / qn, (gy - y * radial) / qn, (gz - z * radial) / qn};
+        float g[5];
+#pragma unroll
+        for (int k = 0; k < 5; k++) g[k] = dL_dall_map[5 * (size_t)i + k];
+        plane_bwd(p, sc, rotations[i], viewmatrix, make_float3(campos[0], campos[1], campos[2]), g, dp, dq);
     }
     dL_dmeans3D[3 * (size_t)i] = dp.x;
     dL_dmeans3D[3 * (size_t)i + 1] = dp.y;
@@ -600,11 +615,18 @@ struct CamCotangents {
     const float2* dL_dmeans2D[MAX_CAMS];
     const float4* dL_dconic_opacity[MAX_CAMS];
 };
+// Optional plane descriptors per camera: forward output (P,5) / backward cotangent (P,5); null = not wanted.
+struct CamPlanes {
+    const float* campos[MAX_CAMS];
+    float* all_map[MAX_CAMS];
+    const float* dL_dall_map[MAX_CAMS];
+};
 
 __global__ void __launch_bounds__(CGX_BLOCK_SIZE)
 preprocess_fwd_batched_kernel(int P, const float* __restrict__ means3D, const float* __restrict__ scales,
                               const float scale_modifier, const float* __restrict__ rotations,
-                              const float* __restrict__ opacities, CamBatch cams, CamOutputs outs, int vec_mask)
+                              const float* __restrict__ opacities, CamBatch cams, CamOutputs outs, CamPlanes planes,
+                              int vec_mask)
 {
     __shared__ __align__(16) float s_mean[CGX_BLOCK_SIZE * 3];
     __shared__ __align__(16) float s_scale[CGX_BLOCK_SIZE * 3];
@@ -673,14 +695,25 @@ preprocess_fwd_batched_kernel(int P, const float* __restrict__ means3D, const fl
         outs.means2D[b][idx] = out_xy;
         outs.depths[b][idx] = out_depth;
         outs.conic_opacity[b][idx] = out_co;
+        if (planes.all_map[b]) {
+            float o5[5] = {0.f, 0.f, 0.f, 0.f, 0.f};
+            if (out_radius > 0) {
+                const float* cp = planes.campos[b];
+                plane_fwd(p_orig, sc, q, viewmatrix, make_float3(__ldg(cp), __ldg(cp + 1), __ldg(cp + 2)), o5);
+            }
+            float* o = planes.all_map[b] + 5 * (size_t)idx;
+#pragma unroll
+            for (int k = 0; k < 5; k++) o[k] = o5[k];
+        }
     }
 }
 
 __global__ void __launch_bounds__(CGX_BLOCK_SIZE)
 preprocess_bwd_batched_kernel(int P, const float* __restrict__ means3D, const float* __restrict__ scales,
                               const float scale_modifier, const float* __restrict__ rotations, CamBatch cams,
-                              CamCotangents cot, float* __restrict__ dL_dmeans, float* __restrict__ dL_dscales,
-                              float4* __restrict__ dL_drots, float* __restrict__ dL_dopacity, int vec_mask)
+                              CamCotangents cot, CamPlanes planes, float* __restrict__ dL_dmeans,
+                              float* __restrict__ dL_dscales, float4* __restrict__ dL_drots,
+                              float* __restrict__ dL_dopacity, int vec_mask)
 {
     __shared__ __align__(16) float s_mean[CGX_BLOCK_SIZE * 3];   // reused for dL_dmeans
     __shared__ __align__(16) float s_scale[CGX_BLOCK_SIZE * 3];  // reused for dL_dscales
@@ -713,6 +746,7 @@ preprocess_bwd_batched_kernel(int P, const float* __restrict__ means3D, const fl
         float dL_dcov[6] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
         float g_op = 0.f;
         bool any = false;
+        float4 g_rot_plane = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll 1
         for (int b = 0; b < cams.B; b++) {
             const float4 dco = __ldg(cot.dL_dconic_opacity[b] + idx);
@@ -721,9 +755,17 @@ preprocess_bwd_batched_kernel(int P, const float* __restrict__ means3D, const fl
                 any = true;
                 bwd_project_one(mean, cov3D, s_view[b], s_proj[b], cams.focal_x[b], cams.focal_y[b], cams.tan_fovx[b],
                                 cams.tan_fovy[b], dco, __ldg(cot.dL_dmeans2D[b] + idx), g_mean, dL_dcov);
+                if (planes.dL_dall_map[b]) {
+                    const float* gp = planes.dL_dall_map[b] + 5 * (size_t)idx;
+                    const float g5[5] = {__ldg(gp), __ldg(gp + 1), __ldg(gp + 2), __ldg(gp + 3), __ldg(gp + 4)};
+                    const float* cp = planes.campos[b];
+                    plane_bwd(mean, sc, rot, s_view[b], make_float3(__ldg(cp), __ldg(cp + 1), __ldg(cp + 2)), g5,
+                              g_mean, g_rot_plane);
+                }
             }
         }
         if (any) bwd_cov3d(sc, scale_modifier, rot, dL_dcov, g_scale, g_rot);   // linear in dL_dcov: once for all cameras
+        g_rot = {g_rot.x + g_rot_plane.x, g_rot.y + g_rot_plane.y, g_rot.z + g_rot_plane.z, g_rot.w + g_rot_plane.w};
         dL_dopacity[idx] = g_op;
         dL_drots[idx] = g_rot;
     }
@@ -878,10 +920,12 @@ static int fill_cams(CamBatch& cb, int B, const cgx_camera* cams)
     return CGX_OK;
 }
 
-extern "C" int cgx_preprocess_fwd_batched(int P, int B, const float* means3D, const float* scales,
-                                          float scale_modifier, const float* rotations, const float* opacities,
-                                          const cgx_camera* cams, float* const* means2D, float* const* depths,
-                                          int32_t* const* radii, float* const* conic_opacity, void* stream)
+extern "C" int cgx_preprocess_fwd_batched_planes(int P, int B, const float* means3D, const float* scales,
+                                                 float scale_modifier, const float* rotations,
+                                                 const float* opacities, const cgx_camera* cams,
+                                                 const float* const* campos, float* const* means2D,
+                                                 float* const* depths, int32_t* const* radii,
+                                                 float* const* conic_opacity, float* const* all_map, void* stream)
 {
     if (P < 0) return CGX_EINVAL;
     CamBatch cb;
@@ -890,7 +934,10 @@ extern "C" int cgx_preprocess_fwd_batched(int P, int B, const float* means3D, co
     if (P == 0) return CGX_OK;
     if (!means3D || !scales || !rotations || !opacities || !means2D || !depths || !radii || !conic_opacity)
         return CGX_EINVAL;
+    if ((all_map != nullptr) != (campos != nullptr)) return CGX_EINVAL;
     CamOutputs o;
+    CamPlanes pl;
+    memset(&pl, 0, sizeof(pl));
     for (int b = 0; b < B; b++) {
         if (!means2D[b] || !depths[b] || !radii[b] || !conic_opacity[b]) return CGX_EINVAL;
         if (((uintptr_t)means2D[b] & 7) || !aligned16(conic_opacity[b])) return CGX_EINVAL;
@@ -898,19 +945,36 @@ extern "C" int cgx_preprocess_fwd_batched(int P, int B, const float* means3D, co
         o.depths[b] = depths[b];
         o.radii[b] = radii[b];
         o.conic_opacity[b] = (float4*)conic_opacity[b];
+        if (all_map && all_map[b]) {
+            if (!campos[b]) return CGX_EINVAL;
+            pl.all_map[b] = all_map[b];
+            pl.campos[b] = campos[b];
+        }
     }
     const int vec_mask = (aligned16(means3D) ? 1 : 0) | (aligned16(scales) ? 2 : 0) | (aligned16(rotations) ? 4 : 0);
     preprocess_fwd_batched_kernel<<<(P + CGX_BLOCK_SIZE - 1) / CGX_BLOCK_SIZE, CGX_BLOCK_SIZE, 0,
                                     (cudaStream_t)stream>>>(P, means3D, scales, scale_modifier, rotations, opacities, cb,
-                                                            o, vec_mask);
+                                                            o, pl, vec_mask);
     return check_launch();
 }
 
-extern "C" int cgx_preprocess_bwd_batched(int P, int B, const float* means3D, const float* scales,
-                                          float scale_modifier, const float* rotations, const cgx_camera* cams,
-                                          const int32_t* const* radii, const float* const* dL_dmeans2D,
-                                          const float* const* dL_dconic_opacity, float* dL_dmeans3D, float* dL_dscales,
-                                          float* dL_drotations, float* dL_dopacity, void* stream)
+extern "C" int cgx_preprocess_fwd_batched(int P, int B, const float* means3D, const float* scales,
+                                          float scale_modifier, const float* rotations, const float* opacities,
+                                          const cgx_camera* cams, float* const* means2D, float* const* depths,
+                                          int32_t* const* radii, float* const* conic_opacity, void* stream)
+{
+    return cgx_preprocess_fwd_batched_planes(P, B, means3D, scales, scale_modifier, rotations, opacities, cams, nullptr,
+                                             means2D, depths, radii, conic_opacity, nullptr, stream);
+}
+
+extern "C" int cgx_preprocess_bwd_batched_planes(int P, int B, const float* means3D, const float* scales,
+                                                 float scale_modifier, const float* rotations, const cgx_camera* cams,
+                                                 const float* const* campos, const int32_t* const* radii,
+                                                 const float* const* dL_dmeans2D,
+                                                 const float* const* dL_dconic_opacity,
+                                                 const float* const* dL_dall_map, float* dL_dmeans3D,
+                                                 float* dL_dscales, float* dL_drotations, float* dL_dopacity,
+                                                 void* stream)
 {
     if (P < 0) return CGX_EINVAL;
     CamBatch cb;
@@ -920,19 +984,38 @@ extern "C" int cgx_preprocess_bwd_batched(int P, int B, const float* means3D, co
     if (!means3D || !scales || !rotations || !radii || !dL_dmeans2D || !dL_dconic_opacity || !dL_dmeans3D ||
         !dL_dscales || !dL_drotations || !dL_dopacity || !aligned16(dL_drotations))
         return CGX_EINVAL;
+    if ((dL_dall_map != nullptr) != (campos != nullptr)) return CGX_EINVAL;
     CamCotangents c;
+    CamPlanes pl;
+    memset(&pl, 0, sizeof(pl));
     for (int b = 0; b < B; b++) {
         if (!radii[b] || !dL_dmeans2D[b] || !dL_dconic_opacity[b]) return CGX_EINVAL;
         if (((uintptr_t)dL_dmeans2D[b] & 7) || !aligned16(dL_dconic_opacity[b])) return CGX_EINVAL;
         c.radii[b] = radii[b];
         c.dL_dmeans2D[b] = (const float2*)dL_dmeans2D[b];
         c.dL_dconic_opacity[b] = (const float4*)dL_dconic_opacity[b];
+        if (dL_dall_map && dL_dall_map[b]) {
+            if (!campos[b]) return CGX_EINVAL;
+            pl.dL_dall_map[b] = dL_dall_map[b];
+            pl.campos[b] = campos[b];
+        }
     }
     const int vec_mask = (aligned16(means3D) ? 1 : 0) | (aligned16(scales) ? 2 : 0) | (aligned16(rotations) ? 4 : 0) |
                          (aligned16(dL_dmeans3D) ? 8 : 0) | (aligned16(dL_dscales) ? 16 : 0);
     preprocess_bwd_batched_kernel<<<(P + CGX_BLOCK_SIZE - 1) / CGX_BLOCK_SIZE, CGX_BLOCK_SIZE, 0,
-                                    (cudaStream_t)stream>>>(P, means3D, scales, scale_modifier, rotations, cb, c,
+                                    (cudaStream_t)stream>>>(P, means3D, scales, scale_modifier, rotations, cb, c, pl,
                                                             dL_dmeans3D, dL_dscales, (float4*)dL_drotations,
                                                             dL_dopacity, vec_mask);
     return check_launch();
+}
+
+extern "C" int cgx_preprocess_bwd_batched(int P, int B, const float* means3D, const float* scales,
+                                          float scale_modifier, const float* rotations, const cgx_camera* cams,
+                                          const int32_t* const* radii, const float* const* dL_dmeans2D,
+                                          const float* const* dL_dconic_opacity, float* dL_dmeans3D, float* dL_dscales,
+                                          float* dL_drotations, float* dL_dopacity, void* stream)
+{
+    return cgx_preprocess_bwd_batched_planes(P, B, means3D, scales, scale_modifier, rotations, cams, nullptr, radii,
+                                             dL_dmeans2D, dL_dconic_opacity, nullptr, dL_dmeans3D, dL_dscales,
+                                             dL_drotations, dL_dopacity, stream);
 }

@@ -58,6 +58,8 @@ SIGNATURES = {
     "cgx_preprocess_bwd": (_i, [_i, _vp, _vp, _f, _vp, _vp, _vp, _vp, _i, _i, _f, _f, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "cgx_preprocess_fwd_batched": (_i, [_i, _i, _vp, _vp, _f, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "cgx_preprocess_bwd_batched": (_i, [_i, _i, _vp, _vp, _f, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "cgx_preprocess_fwd_batched_planes": (_i, [_i, _i, _vp, _vp, _f] + [_vp] * 10),
+    "cgx_preprocess_bwd_batched_planes": (_i, [_i, _i, _vp, _vp, _f] + [_vp] * 12),
     "cgx_all_map_fwd": (_i, [_i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "cgx_all_map_bwd": (_i, [_i] + [_vp] * 10),
     "cgx_local2j_mask": (_i, [_i, _i, _i, _i, _vp, _vp, _vp, _i, _vp, _vp]),

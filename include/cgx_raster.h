@@ -108,8 +108,24 @@ int cgx_preprocess_bwd_batched(int P, int B, const float* means3D, const float* 
                                const float* const* dL_dmeans2D, const float* const* dL_dconic_opacity,
                                float* dL_dmeans3D, float* dL_dscales, float* dL_drotations, float* dL_dopacity,
                                void* stream);
+/* The same two launches with the plane descriptors of cgx_all_map_fwd / cgx_all_map_bwd fused in: the forward
+ * also writes all_map[b] (P,5) for camera b (zeros where the radius is 0), the backward also takes
+ * dL_dall_map[b] (P,5) and adds its contribution to dL_dmeans3D and dL_drotations.  campos[b]: device pointer to
+ * camera b's centre (3 floats).  all_map / dL_dall_map (and campos with them) may be null, or hold null entries
+ * for cameras that need no descriptors. */
+int cgx_preprocess_fwd_batched_planes(int P, int B, const float* means3D, const float* scales, float scale_modifier,
+                                      const float* rotations, const float* opacities, const cgx_camera* cams,
+                                      const float* const* campos, float* const* means2D, float* const* depths,
+                                      int32_t* const* radii, float* const* conic_opacity, float* const* all_map,
+                                      void* stream);
+int cgx_preprocess_bwd_batched_planes(int P, int B, const float* means3D, const float* scales, float scale_modifier,
+                                      const float* rotations, const cgx_camera* cams, const float* const* campos,
+                                      const int32_t* const* radii, const float* const* dL_dmeans2D,
+                                      const float* const* dL_dconic_opacity, const float* const* dL_dall_map,
+                                      float* dL_dmeans3D, float* dL_dscales, float* dL_drotations,
+                                      float* dL_dopacity, void* stream);
 
-/* PGSR per-Gaussian plane descriptor [normal_cam(3), 1, plane distance] for one camera, forward only: the
+/* PGSR per-Gaussian plane descriptor [normal_cam(3), 1, plane distance] for one camera: the
  * tensor code of the reference's caller (gaussian_renderer/__init__.py:1501-1518) as one kernel.
  * radii optional: rows with radius <= 0 get zeros.  all_map (P,5). */
 int cgx_all_map_fwd(int P, const float* means3D, const float* scales, const float* rotations,
@@ -192,6 +208,8 @@ typedef struct cgx_peer_camera_dst {
     int32_t* radii;        /* (n)   */
     float* depths;         /* (n)   */
     int64_t first_row;     /* first row this rank writes in those arrays */
+    float* all_map;        /* (n,5): plane-descriptor form of the record (cgx_local2j_pack_p2p_batched with
+                              cgx_exchange_camera.all_map); then means3D / scales / rotations may be null */
 } cgx_peer_camera_dst;
 int cgx_local2j_pack_p2p(int P, int H, int W, int ws, const float* means2D, const float* rgb,
                          const float* conic_opacity, const float* means3D, const float* scales,
@@ -222,6 +240,9 @@ typedef struct cgx_exchange_camera {
     const int64_t* send_row_offset;        /* host, ws entries (optional when send_index is null) */
     void* workspace;                       /* device, as left by cgx_local2j_count */
     uint64_t workspace_bytes;
+    const float* all_map;                  /* (P,5) or null.  Given (for every camera of the call): the rows carry
+                                              this camera's plane descriptors instead of means3D / scales /
+                                              rotations, 16 floats per row instead of 21, and land in dst[].all_map */
 } cgx_exchange_camera;
 int cgx_local2j_pack_p2p_batched(int n_cameras, const cgx_exchange_camera* cams /* host */, int32_t* send_index,
                                  void* stream);
@@ -229,7 +250,9 @@ int cgx_pack_grad_rows_to(int n_segments, float* const* seg_rows, const int64_t*
                           const float* d_means2D, const float* d_rgb, const float* d_conic_opacity,
                           const float* d_means3D, const float* d_scales, const float* d_rotations, void* stream);
 /* cgx_unpack_grad_add for rows of `ncols` floats: 19 = every differentiable column, 9 = means2D | rgb |
- * conic_opacity only (used when no gradient flows back to the 3-D parameters through the exchange). */
+ * conic_opacity only (used when no gradient flows back to the 3-D parameters through the exchange), 14 = means2D |
+ * rgb | conic_opacity | plane descriptors (5): the (n,5) array takes the place of the means3D argument and the
+ * scales / rotations arguments are ignored.  The same three widths hold for cgx_pack_grad_rows_to. */
 int cgx_unpack_grad_add_cols(int n_ranges, const int64_t* range_start, const int64_t* range_stop, int ncols,
                              const float* grad_rows, const int32_t* send_index, float* d_means2D, float* d_rgb,
                              float* d_conic_opacity, float* d_means3D, float* d_scales, float* d_rotations,

@@ -166,33 +166,31 @@ def test_send_buffer_pack_matches_oracle_mask(setup, cuda_device):
 @pytest.mark.parametrize("ncols", [9, 19])
 def test_gradient_rows_round_trip(setup, cuda_device, ncols):
     """Receiver side: cotangents of one camera's received rows -> per-source segments; owner side: segments
-    scatter-added through the send index.  A row sent to two ranks gets both contributions."""
+    scatter-added through the send index.  A row sent to two ranks gets both contributions.  Row widths: 19 = all
+    differentiable columns, 9 = screen-space only, 14 = screen-space + plane descriptors (in the means3D slot)."""
     be, bounds, cams = setup
     c = cams[2]
     want = c["want"]
     gen = torch.Generator().manual_seed(5)
+    widths = {19: (2, 3, 4, 3, 3, 4), 9: (2, 3, 4), 14: (2, 3, 4, 5)}[ncols]
+    pad = [None] * (6 - len(widths))
     staging = torch.zeros(sum(len(w) for w in want), ncols, device=cuda_device)
-    expect = [torch.zeros(N, w, dtype=torch.float64) for w in (2, 3, 4, 3, 3, 4)]
+    expect = [torch.zeros(N, w, dtype=torch.float64) for w in widths]
     start = 0
     for rows in want:                      # every destination returns one segment of gradient rows
         n = len(rows)
-        cot = [torch.randn(n, w, generator=gen) for w in (2, 3, 4, 3, 3, 4)]
-        use = cot if ncols == 19 else cot[:3] + [None, None, None]
+        cot = [torch.randn(n, w, generator=gen) for w in widths]
         seg_ptr = staging.data_ptr() + start * ncols * 4
-        be.pack_grad_rows_to([seg_ptr], [n], ncols, [None if t is None else t.to(cuda_device) for t in use])
-        for e, t in zip(expect, use):
-            if t is not None:
-                e.index_add_(0, rows, t.double())
+        be.pack_grad_rows_to([seg_ptr], [n], ncols, [t.to(cuda_device) for t in cot] + pad)
+        for e, t in zip(expect, cot):
+            e.index_add_(0, rows, t.double())
         start += n
     index = torch.cat(want).to(torch.int32).to(cuda_device)
-    grads = [torch.zeros(N, w, device=cuda_device) for w in (2, 3, 4, 3, 3, 4)]
+    grads = [torch.zeros(N, w, device=cuda_device) for w in widths]
     ranges, s = [], 0
     for rows in want:
         ranges.append((s, s + len(rows)))
         s += len(rows)
-    be.unpack_grad_add_cols(staging, index, ranges, ncols, grads if ncols == 19 else grads[:3] + [None] * 3)
-    for k, (g, e) in enumerate(zip(grads, expect)):
-        if ncols == 9 and k >= 3:
-            assert not g.any()
-            continue
+    be.unpack_grad_add_cols(staging, index, ranges, ncols, grads + pad)
+    for g, e in zip(grads, expect):
         assert torch.allclose(g.cpu().double(), e, atol=1e-5, rtol=1e-6)

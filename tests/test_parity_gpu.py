@@ -458,8 +458,10 @@ def test_plane_map_forward_and_backward(cuda_device):
     ref = ref * keep
     (ref * cot.double()).sum().backward()
 
-    # float32 forward: the distance reaches a few hundred metres, so the bound is relative there
-    assert torch.allclose(out, ref.float(), rtol=3e-6, atol=2e-5)
+    # float32 forward against float64: unit normals to 1e-5; the distance is a dot product of coordinates of a few
+    # hundred metres whose terms cancel, so its float32 rounding is bounded by the coordinates' magnitude
+    assert (out[:, :4] - ref[:, :4].float()).abs().max().item() <= 1e-5
+    assert (out[:, 4] - ref[:, 4].float()).abs().max().item() <= 1e-6 * 4 * 300.0
     assert not out[radii == 0].any()
     for k in ("means3D", "rotations"):
         a, b = leaves[k].grad.double(), ref_leaves[k].grad
@@ -483,3 +485,43 @@ def _build_all_map_f64(means3D, scales, rotations, V, campos):
     pts = means3D @ V[:3, :3] + V[3, :3]
     dist = (local_normal * pts).sum(-1).abs()
     return torch.cat([local_normal, torch.ones_like(dist)[:, None], dist[:, None]], 1)
+
+
+def test_fused_plane_descriptors_equal_the_standalone_op(cuda_device):
+    """Batched preprocess with fused plane descriptors == batched preprocess + cgx.plane_map per camera, forward
+    and parameter gradients."""
+    from cgx.batched import preprocess_gaussians_batched
+    from cgx.plane_map import plane_map
+    from cgx import runtime as RT
+
+    n, res, B = 40_000, (320, 240), 3
+    g, cams = util.S.config(2, n_gaussians=n, n_cameras=B, res=res)
+    dev = cuda_device
+    settings = RT.TrainingStep(g, cams, dev).settings
+    gen = torch.Generator().manual_seed(3)
+    cots = [(torch.randn(n, 2, generator=gen).to(dev), torch.randn(n, 4, generator=gen).to(dev),
+             torch.randn(n, 5, generator=gen).to(dev)) for _ in range(B)]
+
+    def leaves():
+        return {k: g[k].to(dev).requires_grad_(True) for k in ("means3D", "scales", "rotations", "opacities")}
+
+    a = leaves()
+    fused = preprocess_gaussians_batched(a["means3D"], a["scales"], a["rotations"], None, a["opacities"], settings,
+                                         planes=True)
+    loss = sum((t[0] * c[0]).sum() + (t[2] * c[1]).sum() + (t[5] * c[2]).sum() for t, c in zip(fused, cots))
+    loss.backward()
+
+    b = leaves()
+    plain = preprocess_gaussians_batched(b["means3D"], b["scales"], b["rotations"], None, b["opacities"], settings)
+    maps = [plane_map(b["means3D"], b["scales"], b["rotations"], rs.viewmatrix, rs.campos, t[3])
+            for rs, t in zip(settings, plain)]
+    loss = sum((t[0] * c[0]).sum() + (t[2] * c[1]).sum() + (m * c[2]).sum() for t, m, c in zip(plain, maps, cots))
+    loss.backward()
+
+    for t, u, m in zip(fused, plain, maps):
+        assert torch.equal(t[3], u[3]) and torch.equal(t[0], u[0]) and torch.equal(t[2], u[2])
+        assert torch.allclose(t[5], m, rtol=1e-6, atol=1e-6)
+        assert (t[5][t[3] == 0] == 0).all()
+    for k in ("means3D", "scales", "rotations", "opacities"):
+        ga, gb = a[k].grad, b[k].grad
+        assert ((ga - gb).norm() / gb.norm()).item() <= 1e-5, k
