@@ -38,6 +38,7 @@ WORKLOADS = {
     "cfg1": (1, "1M Gaussians, 1 camera 1920x1080 (single-GPU rasterizer fwd+bwd)"),
     "cfg2": (2, "6M Gaussians, 8 cameras 1600x1200 on a ring (data-parallel step)"),
     "cfg3": (3, "20M clustered Gaussians, 16 cameras 3840x2160 (load-imbalance stress)"),
+    "cfg4": (4, "cfg2's scene at --gaussians N (capacity sweep), densification statistics updated every step"),
 }
 
 
@@ -55,6 +56,8 @@ def parse_args():
     ap.add_argument("--no-stage-events", action="store_true", help="do not bracket library calls with CUDA events")
     ap.add_argument("--no-clocks", action="store_true", help="do not sample nvidia-smi during the run")
     ap.add_argument("--cpu-sample-gaussians", type=int, default=None)
+    ap.add_argument("--densification-stats", action="store_true",
+                    help="update the densification statistics inside every step (always on for cfg4)")
     return ap.parse_args()
 
 
@@ -189,9 +192,15 @@ def main():
         raise SystemExit("bench.py needs a CUDA device: the rasterizer has no CPU path")
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
+    stdout_fd = None
     if world > 1:
         import torch.distributed as dist
         os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")   # plain peer stores only, no multicast objects
+        # libraries underneath (NCCL's version banner) write to file descriptor 1; the one JSON line must be alone
+        # on stdout, so everything else goes to stderr until that line is printed
+        sys.stdout.flush()
+        stdout_fd = os.dup(1)
+        os.dup2(2, 1)
         dist.init_process_group("nccl", device_id=dev)
     assert world == a.gpus or world == 1, "launch with torchrun --nproc-per-node N for --gpus N"
 
@@ -200,6 +209,8 @@ def main():
     if a.cameras:
         cams = cams[: a.cameras]
     step = RT.TrainingStep(g, cams, dev, rank=rank, world_size=world)
+    if a.densification_stats or a.workload == "cfg4":
+        step.enable_densification_stats()
     mpix = sum(c.W * c.H for c in cams) / 1e6
     n_scene = g["means3D"].shape[0]
 
@@ -301,6 +312,17 @@ def main():
         cpu = {"value": mp / dt, "unit": "Mpix/s", "cores": cores, "kind": "port", "sample": sample,
                "seconds": dt}
 
+    # balancer: per-rank render time (forward + backward, ms) of the first and the last recorded step
+    balancer = None
+    if world > 1 and step.history is not None and step.history.history:
+        def summary(entry):
+            t = entry["all_gpu_running_time"]
+            return {"iteration": entry["iteration"], "max_ms": max(t), "mean_ms": sum(t) / len(t),
+                    "per_rank_ms": [round(x, 3) for x in t]}
+        h = step.history.history
+        balancer = {"recorded_steps": len(h), "first": summary(h[0]), "last": summary(h[-1]),
+                    "division_pos_last": [c["division_pos"] for c in h[-1]["batched_camera_info"]]}
+
     if rank == 0:
         line = {
             "metric": "fwd+bwd Mpix/s", "value": mpix / (ms_step * 1e-3), "unit": "Mpix/s", "n_gpus": world,
@@ -312,8 +334,12 @@ def main():
                        "parallelism": f"gaussian-shard x tile-row split, ws={world}"},
             "gaussian_views_per_s": n_scene * len(cams) / (ms_step * 1e-3),
             "roofline": roofline, "stages": stage_out, "cpu_baseline": cpu, "e2e": e2e,
-            "gpu_launches": int(launches), "clocks": clocks, "exchange": ex,
+            "gpu_launches": int(launches), "clocks": clocks, "exchange": ex, "balancer": balancer,
+            "densification_stats": step.densification_summary(),
         }
+        if stdout_fd is not None:
+            sys.stdout.flush()
+            os.dup2(stdout_fd, 1)
         print(json.dumps(line), flush=True)
     if world > 1:
         torch.distributed.destroy_process_group()

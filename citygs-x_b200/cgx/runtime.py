@@ -41,6 +41,7 @@ class TrainingStep:
         # True: gradients of the plane descriptors flow back to means3D / rotations (through the reverse exchange
         # when distributed: 19-float gradient rows), as in the reference's training graph
         self.plane_grads = True
+        self.densify = None             # DensificationStats, updated after every step when enabled
         self.cams = cams
         # Gaussians are stored round-robin over ranks, like the reference's anchors (scene/gaussian_model.py:476-479)
         sel = slice(rank, None, world_size)
@@ -159,6 +160,21 @@ class TrainingStep:
             self._local_cache[key] = torch.ones(TY, TX, dtype=torch.bool, device=self.dev)
         return self._local_cache[key]
 
+    def enable_densification_stats(self):
+        from .densification import DensificationStats
+
+        self.densify = DensificationStats(self.n_local, self.dev)
+
+    def densification_summary(self):
+        """Small host-side digest of the accumulated statistics (one synchronising read; call outside timed code)."""
+        if self.densify is None:
+            return None
+        d = self.densify
+        seen = d.denom > 0
+        return {"gaussians_seen": int(seen.sum().item()), "visits": float(d.denom.sum().item()),
+                "mean_grad_norm": float(d.mean_gradient()[seen].mean().item()) if bool(seen.any()) else 0.0,
+                "max_radius": int(d.max_radii2D.max().item())}
+
     def run(self):
         self.iteration += 1
         for v in self.params.values():
@@ -169,6 +185,8 @@ class TrainingStep:
             self._step_distributed()
             if not self.lazy_balancer:
                 self.finish_balancer()
+        if self.densify is not None:
+            self.densify.update_batch(self.last)
         return self.params
 
     # ------------------------------------------------------------------ multi-GPU step

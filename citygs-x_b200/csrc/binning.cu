@@ -694,6 +694,7 @@ pack_p2p_tile(int block, int P, int gx, int gy, int ws, int nblocks, const float
             rec[NF - 1] = depths[i];
         }
     }
+    if (!__syncthreads_or(bits != 0)) return;   // nothing of this tile is visible to any rank (uniform over the CTA)
     for (int rk = 0; rk < ws; rk++) {
         const bool sel = (bits >> rk) & 1u;
         const uint32_t b = __ballot_sync(0xffffffffu, sel);

@@ -337,6 +337,22 @@ def render_gaussians(background, image_height, image_width, means2D, depths, rad
 def render_gaussians_backward(background, tan_fovx, tan_fovy, all_map_pixels, all_maps, R, geomBuffer, binningBuffer,
                               imageBuffer, compute_locally, dL_dout_color, dL_dout_all_map, dL_dout_plane_depth,
                               means2D, conic_opacity, rgb, render_geo, debug, args):
+    dL_dmeans2D, dL_dmeans2D_abs, dL_dconic_opacity, dL_dcolors, dL_dall_map = render_gaussians_backward_2d(
+        background, tan_fovx, tan_fovy, all_map_pixels, all_maps, R, geomBuffer, binningBuffer, imageBuffer,
+        compute_locally, dL_dout_color, dL_dout_all_map, dL_dout_plane_depth, means2D, conic_opacity, rgb, render_geo,
+        debug, args)
+    # the reference returns dL_dmeans2D as (P,3) with a zero third column and slices it in Python
+    dL_dmeans2D_3 = torch.zeros(means2D.shape[0], 3, dtype=torch.float32, device=means2D.device)
+    dL_dmeans2D_3[:, :2] = dL_dmeans2D
+    return dL_dmeans2D_3, dL_dmeans2D_abs, dL_dconic_opacity, dL_dcolors, dL_dall_map
+
+
+def render_gaussians_backward_2d(background, tan_fovx, tan_fovy, all_map_pixels, all_maps, R, geomBuffer,
+                                 binningBuffer, imageBuffer, compute_locally, dL_dout_color, dL_dout_all_map,
+                                 dL_dout_plane_depth, means2D, conic_opacity, rgb, render_geo, debug, args):
+    """render_gaussians_backward with dL_dmeans2D as the (P,2) tensor the kernel writes (not an entry point of the
+    reference's module: its autograd wrapper pads to (P,3) in C++ and slices back in Python; this package's wrapper
+    skips the round trip)."""
     l = _lib.lib()
     P, dev = means2D.shape[0], means2D.device
     H, W = dL_dout_color.shape[1], dL_dout_color.shape[2]
@@ -372,10 +388,7 @@ def render_gaussians_backward(background, tan_fovx, tan_fovy, all_map_pixels, al
                 stats["backward_render_time"] = _EventMs([(ev0, ev1)])
             if debug:
                 _check_device(dev)
-    # the reference returns dL_dmeans2D as (P,3) with a zero third column and slices it in Python
-    dL_dmeans2D_3 = torch.zeros(P, 3, **f32)
-    dL_dmeans2D_3[:, :2] = dL_dmeans2D
-    return dL_dmeans2D_3, dL_dmeans2D_abs, dL_dconic_opacity, dL_dcolors, dL_dall_map
+    return dL_dmeans2D, dL_dmeans2D_abs, dL_dconic_opacity, dL_dcolors, dL_dall_map
 
 
 def get_local2j_ids_bool(image_height, image_width, mp_rank, mp_world_size, means2D, radii, dist_global_strategy,

@@ -96,12 +96,11 @@ class _RenderGaussians(torch.autograd.Function):
             grad_out_all_map = torch.zeros(5, H, W, dtype=means2D.dtype, device=means2D.device)
         if grad_out_plane_depth is None:
             grad_out_plane_depth = torch.zeros(1, H, W, dtype=means2D.dtype, device=means2D.device)
-        dL_dmeans2D, dL_dmeans2D_abs, dL_dconic_opacity, dL_dcolors, dL_dall_map = _C.render_gaussians_backward(
+        dL_dmeans2D, dL_dmeans2D_abs, dL_dconic_opacity, dL_dcolors, dL_dall_map = _C.render_gaussians_backward_2d(
             rs.bg, rs.tanfovx, rs.tanfovy, all_map_pixels, all_maps, ctx.num_rendered, geomBuffer, binningBuffer,
             imgBuffer, compute_locally, grad_color, grad_out_all_map, grad_out_plane_depth, means2D, conic_opacity,
             rgb, rs.render_geo, rs.debug, ctx.cuda_args)
-        dL_dmeans2D = dL_dmeans2D[:, :2]
-        return (dL_dmeans2D.contiguous(), dL_dmeans2D_abs, dL_dconic_opacity, dL_dcolors, dL_dall_map,
+        return (dL_dmeans2D, dL_dmeans2D_abs, dL_dconic_opacity, dL_dcolors, dL_dall_map,
                 None, None, None, None, None, None)
 
 
