@@ -708,7 +708,12 @@ preprocess_fwd_batched_kernel(int P, const float* __restrict__ means3D, const fl
     }
 }
 
-__global__ void __launch_bounds__(CGX_BLOCK_SIZE)
+#ifndef CGX_PRE_BWD_MIN_CTAS
+#define CGX_PRE_BWD_MIN_CTAS 3
+#endif
+// 3 CTAs per SM: the kernel is latency-bound (dependent divisions and square roots per camera), so the third CTA's
+// warps matter more than the registers it costs.
+__global__ void __launch_bounds__(CGX_BLOCK_SIZE, CGX_PRE_BWD_MIN_CTAS)
 preprocess_bwd_batched_kernel(int P, const float* __restrict__ means3D, const float* __restrict__ scales,
                               const float scale_modifier, const float* __restrict__ rotations, CamBatch cams,
                               CamCotangents cot, CamPlanes planes, float* __restrict__ dL_dmeans,
