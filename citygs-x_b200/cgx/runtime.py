@@ -13,7 +13,7 @@ from __future__ import annotations
 
 import torch
 
-from diff_gaussian_rasterization import GaussianRasterizationSettings, GaussianRasterizer
+from diff_gaussian_rasterization import GaussianRasterizationSettings, GaussianRasterizer, _C
 
 from . import synthetic as S
 
@@ -42,6 +42,7 @@ class TrainingStep:
         # when distributed: 19-float gradient rows), as in the reference's training graph
         self.plane_grads = True
         self.densify = None             # DensificationStats, updated after every step when enabled
+        self.prefetch_counts = True     # start every camera's pair counting before the first host read of a count
         self.cams = cams
         # Gaussians are stored round-robin over ranks, like the reference's anchors (scene/gaussian_model.py:476-479)
         sel = slice(rank, None, world_size)
@@ -129,6 +130,10 @@ class TrainingStep:
         args = make_cuda_args(self.rank, self.ws, self.iteration)
         outs, heads, grads = [], [], []
         screen = self._preprocess_all(args, planes=self.plane_grads)
+        if self.prefetch_counts:
+            for k, cam in enumerate(self.cams):     # every camera's pair count is on its way before the first read
+                _C.prefetch_num_rendered(cam.H, cam.W, screen[k][0], screen[k][3],
+                                         self._all_local((cam.H + 15) // 16, (cam.W + 15) // 16))
         for k, cam in enumerate(self.cams):
             rast = GaussianRasterizer(self.settings[k])
             means2D, _, conic_opacity, radii, depths = screen[k][:5]
@@ -231,6 +236,11 @@ class TrainingStep:
                               record="plane descriptors (16 floats fwd, 14 bwd)" if fused
                               else "3-D parameters (21 floats fwd, 19 or 9 bwd)")
         heads, grads = [], []
+        if self.prefetch_counts:
+            for k, strat in enumerate(strategies):
+                local = strat.get_compute_locally()
+                if local is not None and m2[k].shape[0] >= 10:
+                    _C.prefetch_num_rendered(self.cams[k].H, self.cams[k].W, m2[k], rad[k], local)
         for k, strat in enumerate(strategies):
             local = strat.get_compute_locally()
             n_rows = m2[k].shape[0]

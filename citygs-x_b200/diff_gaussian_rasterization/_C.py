@@ -252,6 +252,54 @@ def _check_device(dev):
         raise _lib.CgxError(st.value, "device kernel")
 
 
+# ---- pair-count prefetch -------------------------------------------------------------------------------------
+# render_gaussians needs the number of (tile, Gaussian) pairs on the host to size its key buffers: one host
+# synchronisation per call, as in the reference (RAST/cuda_rasterizer/rasterizer_impl.cu:648-660).  A caller that
+# renders several cameras in a row can start the counting stage of ALL of them first (prefetch_num_rendered), so
+# that the first read-back covers every camera and the remaining launches queue back to back with no bubbles.
+# render_gaussians picks a prefetched count up by the identity of its inputs; nothing changes when none exists.
+_PREFETCH = {}
+_PREFETCH_SLOTS = 256
+_prefetch_pinned = None
+_prefetch_next = 0
+
+
+def _prefetch_key(means2D, radii, local, H, W):
+    return (means2D.data_ptr(), radii.data_ptr(), local.data_ptr(), means2D.shape[0], H, W, means2D.device.index)
+
+
+def prefetch_num_rendered(image_height, image_width, means2D, radii, compute_locally):
+    """Launch the tile-count + prefix-sum stage of a coming render_gaussians call with these same tensors and copy
+    the pair count to pinned host memory without waiting for it.  Not part of the reference's module."""
+    global _prefetch_pinned, _prefetch_next
+    l = _lib.lib()
+    means2D = _cuda_f32(means2D, "means2D")
+    radii = _cuda_any(radii, "radii")
+    local = _cuda_any(compute_locally, "compute_locally")
+    P, dev = means2D.shape[0], means2D.device
+    H, W = int(image_height), int(image_width)
+    if P == 0 or radii.dtype != torch.int32:
+        return
+    if _prefetch_pinned is None:
+        _prefetch_pinned = torch.zeros(_PREFETCH_SLOTS, dtype=torch.int32).pin_memory()
+    if len(_PREFETCH) >= _PREFETCH_SLOTS // 2:
+        _PREFETCH.clear()                       # counts nobody picked up
+    slot = _prefetch_next
+    _prefetch_next = (_prefetch_next + 1) % _PREFETCH_SLOTS
+    with torch.cuda.device(dev):
+        glay = geometry_layout(P)
+        geomBuffer = torch.empty(glay.total(), dtype=torch.uint8, device=dev)
+        g = glay.views(geomBuffer)
+        _call("cgx_bin_count_scan", l.cgx_bin_count_scan, P, W, H, _ptr(radii), _ptr(means2D), _ptr(local),
+              _ptr(g["tiles_touched"]), _ptr(g["num_rendered"]), _ptr(g["scanning_space"]),
+              g["scanning_space"].numel(), _stream(), info=dict(P=P))
+        _prefetch_pinned[slot:slot + 1].copy_(g["num_rendered"][0:1], non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+    # the tensors are kept alive with the entry, so their addresses cannot be reused while it exists
+    _PREFETCH[_prefetch_key(means2D, radii, local, H, W)] = (geomBuffer, slot, ev, (means2D, radii, local))
+
+
 def render_gaussians(background, image_height, image_width, means2D, depths, radii, conic_opacity, rgb,
                      compute_locally, viewmatrix, campos, tan_fovx, tan_fovy, all_map, render_geo, debug, args):
     l = _lib.lib()
@@ -292,17 +340,23 @@ def render_gaussians(background, image_height, image_width, means2D, depths, rad
     with torch.cuda.device(dev):
         st = _stream()
         glay = geometry_layout(P)
-        geomBuffer = torch.empty(glay.total(), dtype=torch.uint8, device=dev)
-        g = glay.views(geomBuffer)
         ilay = image_layout(W * H, T)
         imgBuffer = torch.empty(ilay.total(), dtype=torch.uint8, device=dev)
         im = ilay.views(imgBuffer)
-
-        _call("cgx_bin_count_scan", l.cgx_bin_count_scan, P, W, H, _ptr(radii), _ptr(means2D), _ptr(local), _ptr(g["tiles_touched"]),
-                                   _ptr(g["num_rendered"]), _ptr(g["scanning_space"]),
-                                   g["scanning_space"].numel(), st, info=dict(P=P))
-        # the key/value buffers are sized from the pair count: one host read, as in the reference
-        R = int(g["num_rendered"][0].item())
+        pre = _PREFETCH.pop(_prefetch_key(means2D, radii, local, H, W), None) if _PREFETCH else None
+        if pre is not None:
+            geomBuffer, slot, ev, _ = pre
+            g = glay.views(geomBuffer)
+            ev.synchronize()
+            R = int(_prefetch_pinned[slot])
+        else:
+            geomBuffer = torch.empty(glay.total(), dtype=torch.uint8, device=dev)
+            g = glay.views(geomBuffer)
+            _call("cgx_bin_count_scan", l.cgx_bin_count_scan, P, W, H, _ptr(radii), _ptr(means2D), _ptr(local),
+                  _ptr(g["tiles_touched"]), _ptr(g["num_rendered"]), _ptr(g["scanning_space"]),
+                  g["scanning_space"].numel(), st, info=dict(P=P))
+            # the key/value buffers are sized from the pair count: one host read, as in the reference
+            R = int(g["num_rendered"][0].item())
 
         blay = binning_layout(R)
         binningBuffer = torch.empty(blay.total(), dtype=torch.uint8, device=dev)

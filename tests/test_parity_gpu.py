@@ -525,3 +525,38 @@ def test_fused_plane_descriptors_equal_the_standalone_op(cuda_device):
     for k in ("means3D", "scales", "rotations", "opacities"):
         ga, gb = a[k].grad, b[k].grad
         assert ((ga - gb).norm() / gb.norm()).item() <= 1e-5, k
+
+
+def test_prefetched_pair_count_gives_the_same_render(cuda_device):
+    """Counting started ahead of render_gaussians (several cameras queued before the first host read) must be picked
+    up by identity of the inputs and change nothing; an unrelated call must not pick it up."""
+    from diff_gaussian_rasterization import GaussianRasterizer, _C
+
+    dev = cuda_device
+    g, cam = util.make_case(cfg=2, n=30_000, res=(320, 240))
+    rs = settings_for(cam, dev)
+    rast = GaussianRasterizer(rs)
+    gd = to_dev(g, dev)
+    args = cuda_args()
+    m2, _, co, radii, depths = rast.preprocess_gaussians(gd["means3D"], gd["scales"], gd["rotations"], gd["sh"],
+                                                         gd["opacities"], args)
+    TX, TY = (cam.W + 15) // 16, (cam.H + 15) // 16
+    local = torch.ones(TY, TX, dtype=torch.bool, device=dev)
+    half = local.clone()
+    half[TY // 2:] = False
+
+    def render(loc):
+        return _C.render_gaussians(rs.bg, cam.H, cam.W, m2.detach(), depths, radii, co.detach(), gd["rgb"], loc,
+                                   rs.viewmatrix, rs.campos, cam.tanfovx, cam.tanfovy, gd["all_map"], True, True, args)
+
+    plain_full, plain_half = render(local), render(half)
+    _C.prefetch_num_rendered(cam.H, cam.W, m2.detach(), radii, local)
+    _C.prefetch_num_rendered(cam.H, cam.W, m2.detach(), radii, half)
+    assert len(_C._PREFETCH) == 2
+    pre_half, pre_full = render(half), render(local)          # picked up out of order, by identity
+    assert len(_C._PREFETCH) == 0
+    for a, b in ((plain_full, pre_full), (plain_half, pre_half)):
+        assert a[0] == b[0] and a[0] > 0
+        for x, y in zip(a[1:8], b[1:8]):
+            assert torch.equal(x, y)
+    assert plain_half[0] < plain_full[0]
