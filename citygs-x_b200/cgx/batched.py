@@ -36,15 +36,45 @@ def _cams(settings):
     return arr, keep
 
 
-def _ptrs(tensors):
-    return (C.c_void_p * len(tensors))(*[t.data_ptr() for t in tensors])
+def _ptrs(tensors, row0=0):
+    """Host array of device pointers to row `row0` of each (contiguous, row-major) tensor; None entries stay null."""
+    return (C.c_void_p * len(tensors))(*[None if t is None else t.data_ptr() + row0 * t.stride(0) * t.element_size()
+                                         for t in tensors])
+
+
+def _row(t, row0):
+    return t.data_ptr() + row0 * t.stride(0) * t.element_size()
+
+
+def chunk_bounds(P, chunks):
+    """[(lo, hi)] covering range(P) in `chunks` pieces whose starts are multiples of 256 rows (whole CTAs, and every
+    row offset stays 16-byte aligned for the vectorised loads)."""
+    chunks = max(1, int(chunks))
+    per_chunk = -(-P // chunks)                               # ceil
+    step = max(256, (per_chunk + 255) // 256 * 256)
+    out, lo = [], 0
+    while lo < P:
+        out.append((lo, min(P, lo + step)))
+        lo += step
+    return out or [(0, 0)]
+
+
+class Pipeline:
+    """Optional hooks that let a caller overlap host<->device copies with the two launches, chunk by chunk over the
+    Gaussians: `bounds` = chunk_bounds(P, n); `ready[i]` = CUDA event after which chunk i of the parameters may be
+    read (the forward waits for it on the launching stream); `done(i, lo, hi, grads)` is called right after chunk i
+    of the backward has been queued, with the four full gradient tensors (rows lo:hi are final once the launch
+    completes)."""
+
+    def __init__(self, bounds, ready=None, done=None):
+        self.bounds, self.ready, self.done = bounds, ready, done
 
 
 class _PreprocessBatched(torch.autograd.Function):
     """Outputs per camera: means2D, conic_opacity, radii, depths[, all_map when `planes`]."""
 
     @staticmethod
-    def forward(ctx, means3D, scales, rotations, opacities, settings, cuda_args, planes):
+    def forward(ctx, means3D, scales, rotations, opacities, settings, cuda_args, planes, pipeline=None):
         if means3D.ndim != 2 or means3D.shape[1] != 3:
             raise RuntimeError("means3D must have dimensions (num_points, 3)")
         if not means3D.is_cuda:
@@ -61,13 +91,18 @@ class _PreprocessBatched(torch.autograd.Function):
         if P:
             cams, keep = _cams(settings)
             campos = [rs.campos.contiguous() for rs in settings] if planes else None
+            bounds = pipeline.bounds if pipeline is not None else [(0, P)]
             with torch.cuda.device(dev):
-                _lib.check(_lib.lib().cgx_preprocess_fwd_batched_planes(
-                    P, B, means3D.data_ptr(), scales.data_ptr(), float(settings[0].scale_modifier),
-                    rotations.data_ptr(), opacities.data_ptr(), cams, _ptrs(campos) if planes else None, _ptrs(m2),
-                    _ptrs(dep), _ptrs(rad), _ptrs(co), _ptrs(am) if planes else None,
-                    _lib.current_stream_ptr()), "cgx_preprocess_fwd_batched_planes")
-        ctx.settings, ctx.planes = settings, planes
+                for i, (lo, hi) in enumerate(bounds):
+                    if pipeline is not None and pipeline.ready is not None:
+                        torch.cuda.current_stream().wait_event(pipeline.ready[i])
+                    _lib.check(_lib.lib().cgx_preprocess_fwd_batched_planes(
+                        hi - lo, B, _row(means3D, lo), _row(scales, lo), float(settings[0].scale_modifier),
+                        _row(rotations, lo), _row(opacities, lo), cams, _ptrs(campos) if planes else None,
+                        _ptrs(m2, lo), _ptrs(dep, lo), _ptrs(rad, lo), _ptrs(co, lo),
+                        _ptrs(am, lo) if planes else None, _lib.current_stream_ptr()),
+                        "cgx_preprocess_fwd_batched_planes")
+        ctx.settings, ctx.planes, ctx.pipeline = settings, planes, pipeline
         ctx.save_for_backward(means3D, scales, rotations, *rad)
         flat = []
         for b in range(B):
@@ -99,32 +134,37 @@ class _PreprocessBatched(torch.autograd.Function):
             cams, keep = _cams([settings[b] for b in use])
             with_planes = planes and any(g is not None for g in g_am)
             campos = [settings[b].campos.contiguous() for b in use] if with_planes else None
-            am_ptrs = (C.c_void_p * len(use))(*[None if g is None else g.data_ptr() for g in g_am]) \
-                if with_planes else None
+            pipeline = ctx.pipeline
+            bounds = pipeline.bounds if pipeline is not None else [(0, P)]
             with torch.cuda.device(dev):
-                _lib.check(_lib.lib().cgx_preprocess_bwd_batched_planes(
-                    P, len(use), means3D.data_ptr(), scales.data_ptr(), float(settings[0].scale_modifier),
-                    rotations.data_ptr(), cams, _ptrs(campos) if with_planes else None,
-                    _ptrs([rad[b] for b in use]), _ptrs(g_m2), _ptrs(g_co), am_ptrs,
-                    d_means.data_ptr(), d_scales.data_ptr(), d_rot.data_ptr(), d_op.data_ptr(),
-                    _lib.current_stream_ptr()), "cgx_preprocess_bwd_batched_planes")
+                for i, (lo, hi) in enumerate(bounds):
+                    _lib.check(_lib.lib().cgx_preprocess_bwd_batched_planes(
+                        hi - lo, len(use), _row(means3D, lo), _row(scales, lo), float(settings[0].scale_modifier),
+                        _row(rotations, lo), cams, _ptrs(campos) if with_planes else None,
+                        _ptrs([rad[b] for b in use], lo), _ptrs(g_m2, lo), _ptrs(g_co, lo),
+                        _ptrs(g_am, lo) if with_planes else None,
+                        _row(d_means, lo), _row(d_scales, lo), _row(d_rot, lo), _row(d_op, lo),
+                        _lib.current_stream_ptr()), "cgx_preprocess_bwd_batched_planes")
+                    if pipeline is not None and pipeline.done is not None:
+                        pipeline.done(i, lo, hi, (d_means, d_scales, d_rot, d_op))
         else:
             for t in (d_means, d_scales, d_rot, d_op):
                 t.zero_()
-        return d_means, d_scales, d_rot, d_op, None, None, None
+        return d_means, d_scales, d_rot, d_op, None, None, None, None
 
 
 def preprocess_gaussians_batched(means3D, scales, rotations, shs, opacities, raster_settings_list, cuda_args=None,
-                                 planes=False):
+                                 planes=False, pipeline=None):
     """One (means2D, rgb, conic_opacity, radii, depths) tuple per camera, as the per-camera operator returns them
     (``rgb`` is the shared all-zero tensor the per-camera operator also returns: SH evaluation is compiled out).
 
     ``planes=True`` appends the camera's plane descriptors ``all_map`` (P,5) to each tuple: what the reference's
     caller builds after preprocessing (gaussian_renderer/__init__.py:1501-1518) comes out of the same launch, and
     its gradient towards means3D / rotations is folded into the same backward launch (see cgx.plane_map for the
-    stand-alone op)."""
+    stand-alone op).  ``pipeline`` (a `Pipeline`) splits both launches into chunks of Gaussians so that a caller
+    can overlap its host-to-device parameter copies and device-to-host gradient copies with them."""
     settings = list(raster_settings_list)
-    flat = _PreprocessBatched.apply(means3D, scales, rotations, opacities, settings, cuda_args, bool(planes))
+    flat = _PreprocessBatched.apply(means3D, scales, rotations, opacities, settings, cuda_args, bool(planes), pipeline)
     rgb = torch.zeros(means3D.shape[0], 3, device=means3D.device)
     n = 5 if planes else 4
     return [(flat[n * b], rgb, flat[n * b + 1], flat[n * b + 2], flat[n * b + 3]) + ((flat[n * b + 4],) if planes else ())

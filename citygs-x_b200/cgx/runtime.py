@@ -108,6 +108,8 @@ class TrainingStep:
         return rgb
 
     # ------------------------------------------------------------------ single-GPU step
+    _pipeline = None        # cgx.batched.Pipeline while an end-to-end step is in flight
+
     def _preprocess_all(self, args, planes=False):
         """Screen-space state of the local Gaussians for every camera of the batch (one launch).  With `planes`
         every camera's tuple ends with its differentiable plane descriptors (fused into the same launches when
@@ -117,7 +119,8 @@ class TrainingStep:
         p = self.params
         if self.batched:
             return preprocess_gaussians_batched(p["means3D"], p["scales"], p["rotations"], self.sh_dummy,
-                                                p["opacities"], self.settings, args, planes=planes)
+                                                p["opacities"], self.settings, args, planes=planes,
+                                                pipeline=self._pipeline)
         out = [GaussianRasterizer(s).preprocess_gaussians(p["means3D"], p["scales"], p["rotations"], self.sh_dummy,
                                                           p["opacities"], args) for s in self.settings]
         if planes:
@@ -274,31 +277,68 @@ class TrainingStep:
 
         WD.finish_strategy_final(self.cams, self.history, strategies, stats, ctx=self.ctx)
 
-    def run_e2e(self):
+    def run_e2e(self, chunks=4):
         """The same step with its host-side inputs copied in from pinned memory (Gaussian parameters and the
-        upstream-gradient images) and the parameter gradients read back, all inside the caller's timed region."""
+        upstream-gradient images) and the parameter gradients read back, all inside the caller's timed region.
+
+        Copies run on a second stream and overlap the kernels where the data flow allows it: the parameters arrive in
+        `chunks` pieces and the batched preprocess starts on each piece as it lands; the upstream-gradient images,
+        first read by the backward pass, are copied beside the forward pass; the parameter gradients leave piece by
+        piece behind the chunks of the batched preprocess backward."""
+        from .batched import Pipeline, chunk_bounds
+
         main = torch.cuda.current_stream()
         if self._copy_stream is None:
             self._copy_stream = torch.cuda.Stream(device=self.dev)
+        copy = self._copy_stream
+        # piecewise gradient read-back needs the batched preprocess backward to be the ONLY producer of the parameter
+        # gradients: true when the plane descriptors are fused into it (or switched off)
+        from . import exchange
+        fused = self.ws == 1 or not self.plane_grads or \
+            exchange._pick_transport(self.transport, None, self.dev, exchange.default_backend()) == "p2p"
+        pipelined = self.batched and chunks > 1 and fused
+        bounds = chunk_bounds(self.n_local, chunks if pipelined else 1)
+        names = ("means3D", "scales", "rotations", "opacities")
         with torch.no_grad():
-            for k, v in self.host.items():
-                self.params[k].copy_(v, non_blocking=True)
-            # the upstream-gradient images are first read by the backward pass: their copies run on a second
-            # stream beside the forward pass, and the backward waits for them (self._cot_ready)
-            mine = self._my_cameras()
-            self._copy_stream.wait_stream(main)          # the previous step's backward has finished reading them
-            with torch.cuda.stream(self._copy_stream):
+            copy.wait_stream(main)                    # the previous step has finished with parameters and images
+            ready = []
+            with torch.cuda.stream(copy):
+                for lo, hi in bounds:
+                    for k in names:
+                        self.params[k][lo:hi].copy_(self.host[k][lo:hi], non_blocking=True)
+                    ev = torch.cuda.Event()
+                    ev.record(copy)
+                    ready.append(ev)
+                mine = self._my_cameras()
                 for k in mine:
                     for dst, src in zip(self.cot[k], self.cot_host[k]):
                         dst.copy_(src, non_blocking=True)
                 self._cot_ready = torch.cuda.Event()
-                self._cot_ready.record(self._copy_stream)
+                self._cot_ready.record(copy)
             self.h2d_bytes = sum(v.numel() * 4 for v in self.host.values()) + \
                 sum(c.numel() * 4 for k in mine for c in self.cot_host[k])
-        self.run()
-        for k, v in self.params.items():
-            self.grad_host[k].copy_(v.grad, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
+
+        def gradients_out(i, lo, hi, grads):
+            ev = torch.cuda.Event()
+            ev.record(torch.cuda.current_stream())
+            with torch.cuda.stream(copy):
+                copy.wait_event(ev)
+                for k, g in zip(names, grads):
+                    self.grad_host[k][lo:hi].copy_(g[lo:hi], non_blocking=True)
+
+        if pipelined:
+            self._pipeline = Pipeline(bounds, ready=ready, done=gradients_out)
+        else:
+            main.wait_event(ready[-1])
+        try:
+            self.run()
+        finally:
+            self._pipeline = None
+        if not pipelined:
+            for k, v in self.params.items():
+                self.grad_host[k].copy_(v.grad, non_blocking=True)
+        copy.synchronize()
+        main.synchronize()
         return self.grad_host
 
     def _my_cameras(self):

@@ -560,3 +560,41 @@ def test_prefetched_pair_count_gives_the_same_render(cuda_device):
         for x, y in zip(a[1:8], b[1:8]):
             assert torch.equal(x, y)
     assert plain_half[0] < plain_full[0]
+
+
+def test_chunked_batched_preprocess_is_identical(cuda_device):
+    """The same two launches split into chunks of Gaussians (the hooks an end-to-end caller uses to overlap its host
+    copies): bit-identical outputs and gradients, hooks called once per chunk with the right rows."""
+    from cgx.batched import Pipeline, chunk_bounds, preprocess_gaussians_batched
+    from cgx import runtime as RT
+
+    n, B = 10_000, 2
+    g, cams = util.S.config(2, n_gaussians=n, n_cameras=B, res=(320, 240))
+    dev = cuda_device
+    settings = RT.TrainingStep(g, cams, dev).settings
+    gen = torch.Generator().manual_seed(8)
+    cots = [(torch.randn(n, 2, generator=gen).to(dev), torch.randn(n, 4, generator=gen).to(dev),
+             torch.randn(n, 5, generator=gen).to(dev)) for _ in range(B)]
+    results = []
+    for chunks in (1, 3):
+        leaves = {k: g[k].to(dev).requires_grad_(True) for k in ("means3D", "scales", "rotations", "opacities")}
+        bounds = chunk_bounds(n, chunks)
+        seen = []
+        ready = []
+        for _ in bounds:
+            ev = torch.cuda.Event()
+            ev.record()
+            ready.append(ev)
+        pipe = Pipeline(bounds, ready=ready, done=lambda i, lo, hi, grads: seen.append((i, lo, hi, len(grads))))
+        out = preprocess_gaussians_batched(leaves["means3D"], leaves["scales"], leaves["rotations"], None,
+                                           leaves["opacities"], settings, planes=True, pipeline=pipe)
+        sum((t[0] * c[0]).sum() + (t[2] * c[1]).sum() + (t[5] * c[2]).sum() for t, c in zip(out, cots)).backward()
+        assert seen == [(i, lo, hi, 4) for i, (lo, hi) in enumerate(bounds)]
+        results.append((out, {k: v.grad.clone() for k, v in leaves.items()}))
+    assert len(chunk_bounds(n, 3)) == 3
+    (a, ga), (b, gb) = results
+    for ta, tb in zip(a, b):
+        for x, y in zip(ta, tb):
+            assert torch.equal(x, y)
+    for k in ga:
+        assert torch.equal(ga[k], gb[k]), k
