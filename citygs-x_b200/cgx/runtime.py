@@ -26,6 +26,21 @@ def make_cuda_args(rank=0, world_size=1, iteration=1):
             "avoid_pixel_all2all": False, "stats_collector": {}}
 
 
+class _AwaitEvent(torch.autograd.Function):
+    """Identity whose backward makes the current stream wait for a CUDA event first: placed on a camera's rendered
+    images, it holds that camera's backward pass until the upstream-gradient images it reads have arrived."""
+
+    @staticmethod
+    def forward(ctx, event, *tensors):
+        ctx.event = event
+        return tuple(t.view_as(t) for t in tensors)
+
+    @staticmethod
+    def backward(ctx, *grads):
+        torch.cuda.current_stream().wait_event(ctx.event)
+        return (None,) + grads
+
+
 class TrainingStep:
     def __init__(self, g, cams, device, rank=0, world_size=1, seed=4242, transport=None):
         self.dev, self.rank, self.ws = device, rank, world_size
@@ -37,7 +52,8 @@ class TrainingStep:
         # reference's, which gathers the times at the end of every step.
         self.lazy_balancer = True
         self._pending_stats = None
-        self._copy_stream = self._cot_ready = None
+        self._copy_stream = None
+        self._cot_events = None         # per camera: event after which its upstream-gradient images are on the device
         # True: gradients of the plane descriptors flow back to means3D / rotations (through the reverse exchange
         # when distributed: 19-float gradient rows), as in the reference's training graph
         self.plane_grads = True
@@ -148,17 +164,14 @@ class TrainingStep:
                 self.all_map_for(k, p["means3D"], p["scales"], p["rotations"], radii)
             color, n_render, n_consider, n_contrib, observe, out_all_map, plane_depth = rast.render_gaussians(
                 means2D, means2D_abs, conic_opacity, self.rgb[k], all_map, depths, radii, local, None, args)
+            if self._cot_events is not None and k in self._cot_events:
+                color, out_all_map, plane_depth = _AwaitEvent.apply(self._cot_events[k], color, out_all_map,
+                                                                    plane_depth)
             heads += [color, out_all_map, plane_depth]
             grads += self.cot[k]
             outs.append((radii, means2D))
-        self._await_cotangents()
         torch.autograd.backward(heads, grads)      # one backward over the batch, as one loss.backward() upstream
         self.last = outs
-
-    def _await_cotangents(self):
-        if self._cot_ready is not None:
-            torch.cuda.current_stream().wait_event(self._cot_ready)
-            self._cot_ready = None
 
     _local_cache = {}
 
@@ -254,13 +267,15 @@ class TrainingStep:
             m2abs = torch.zeros(n_rows, 3, device=self.dev, requires_grad=True)
             color, _, _, _, _, out_all_map, plane_depth = rasts[k].render_gaussians(
                 m2[k], m2abs, co[k], rgb[k], all_map, dep[k], rad[k], local, None, args[k])
+            if self._cot_events is not None and k in self._cot_events:
+                color, out_all_map, plane_depth = _AwaitEvent.apply(self._cot_events[k], color, out_all_map,
+                                                                    plane_depth)
             heads += [color, out_all_map, plane_depth]
             grads += self.cot[k]
         if not heads:
             # nothing to render on this rank, but the reverse exchange is collective: keep its node in the graph
             heads.append(m2[0].sum() * 0.0)
             grads.append(torch.zeros((), device=self.dev))
-        self._await_cotangents()
         torch.autograd.backward(heads, grads)
         self.last = keep
         self._strategies = strategies
@@ -283,8 +298,9 @@ class TrainingStep:
 
         Copies run on a second stream and overlap the kernels where the data flow allows it: the parameters arrive in
         `chunks` pieces and the batched preprocess starts on each piece as it lands; the upstream-gradient images,
-        first read by the backward pass, are copied beside the forward pass; the parameter gradients leave piece by
-        piece behind the chunks of the batched preprocess backward."""
+        first read by the backward pass, are copied beside the forward pass in the order the backward consumes them,
+        and each camera's backward waits for its own images only; the parameter gradients leave piece by piece
+        behind the chunks of the batched preprocess backward."""
         from .batched import Pipeline, chunk_bounds
 
         main = torch.cuda.current_stream()
@@ -309,12 +325,16 @@ class TrainingStep:
                     ev = torch.cuda.Event()
                     ev.record(copy)
                     ready.append(ev)
+                # the backward pass walks the cameras last to first, so their images are sent in that order and
+                # each camera's backward waits for its own images only
                 mine = self._my_cameras()
-                for k in mine:
+                events = {}
+                for k in reversed(mine):
                     for dst, src in zip(self.cot[k], self.cot_host[k]):
                         dst.copy_(src, non_blocking=True)
-                self._cot_ready = torch.cuda.Event()
-                self._cot_ready.record(copy)
+                    events[k] = torch.cuda.Event()
+                    events[k].record(copy)
+                self._cot_events = events
             self.h2d_bytes = sum(v.numel() * 4 for v in self.host.values()) + \
                 sum(c.numel() * 4 for k in mine for c in self.cot_host[k])
 
@@ -334,6 +354,7 @@ class TrainingStep:
             self.run()
         finally:
             self._pipeline = None
+            self._cot_events = None
         if not pipelined:
             for k, v in self.params.items():
                 self.grad_host[k].copy_(v.grad, non_blocking=True)
