@@ -15,7 +15,7 @@ ROOT = PKG.parent
 CSRC = ROOT / "csrc"
 LIBDIR = ROOT / "lib"
 SO = LIBDIR / "libcgx_raster.so"
-SOURCES = ["cabi.cu", "preprocess.cu", "binning.cu", "render.cu", "peer.cu"]
+SOURCES = ["cabi.cu", "preprocess.cu", "binning.cu", "render.cu", "peer.cu", "loss.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-shared", "-Xcompiler", "-fPIC"]
 
@@ -62,6 +62,8 @@ SIGNATURES = {
     "cgx_preprocess_bwd_batched_planes": (_i, [_i, _i, _vp, _vp, _f] + [_vp] * 12),
     "cgx_all_map_fwd": (_i, [_i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "cgx_all_map_bwd": (_i, [_i] + [_vp] * 10),
+    "cgx_strip_loss_fwd": (_i, [_i, _i, _i] + [_vp] * 8),
+    "cgx_strip_loss_bwd": (_i, [_i, _i, _i] + [_vp] * 9),
     "cgx_local2j_mask": (_i, [_i, _i, _i, _i, _vp, _vp, _vp, _i, _vp, _vp]),
     "cgx_local2j_count": (_i, [_i, _i, _i, _i, _vp, _vp, _vp, _i, _vp, _vp, _sz, _vp]),
     "cgx_local2j_workspace_bytes": (_sz, [_i, _i]),
