@@ -62,3 +62,40 @@ class _StripLoss(torch.autograd.Function):
 def strip_loss_sums(image, gt, mask=None):
     """(sum of mask * |image - gt|, sum of mask * SSIM map) over a (C, H, W) strip; `mask` (H, W) bool or None."""
     return _StripLoss.apply(image, gt, mask)
+
+
+class _DepthNormal(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, depth, fx, fy, cx, cy):
+        if not depth.is_cuda or depth.dtype != torch.float32 or depth.ndim != 2:
+            raise RuntimeError("depth_normal: depth must be a (H, W) float32 CUDA tensor (no CPU path)")
+        depth = depth.contiguous()
+        H, W = depth.shape
+        normal = torch.empty(3, H, W, device=depth.device)
+        if H * W:
+            with torch.cuda.device(depth.device):
+                _lib.check(_lib.lib().cgx_depth_normal_fwd(H, W, fx, fy, cx, cy, depth.data_ptr(), normal.data_ptr(),
+                                                           _lib.current_stream_ptr()), "cgx_depth_normal_fwd")
+        ctx.save_for_backward(depth)
+        ctx.k = (fx, fy, cx, cy)
+        return normal
+
+    @staticmethod
+    def backward(ctx, g):
+        (depth,) = ctx.saved_tensors
+        H, W = depth.shape
+        out = torch.empty_like(depth)
+        if H * W:
+            g = g.contiguous()
+            with torch.cuda.device(depth.device):
+                _lib.check(_lib.lib().cgx_depth_normal_bwd(H, W, *ctx.k, depth.data_ptr(), g.data_ptr(),
+                                                           out.data_ptr(), _lib.current_stream_ptr()),
+                           "cgx_depth_normal_bwd")
+        return out, None, None, None, None
+
+
+def depth_normal(depth, fx, fy, cx, cy):
+    """(3, H, W) camera-space normals of a (H, W) depth image: the reference's ``render_normal`` at scale 1 without
+    offsets (gaussian_renderer/__init__.py:1311-1323; utils/graphics_utils.py:87-152), differentiable towards the
+    depth (this is where the plane-depth cotangent of the rasterizer comes from in training)."""
+    return _DepthNormal.apply(depth, float(fx), float(fy), float(cx), float(cy))

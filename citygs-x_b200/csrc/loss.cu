@@ -185,6 +185,102 @@ strip_loss_bwd_kernel(int H, int W, const float* __restrict__ img, const float* 
     dL_dimg[o] = weights[0] * m * sgn + weights[1] * (a + 2.f * x * b + y * d);
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// Normal image from a depth image (render_normal, gaussian_renderer/__init__.py:1311-1323 with scale = 1 and no
+// offsets -> normal_from_depth_image / depth_pcd2normal, utils/graphics_utils.py:87-152): camera-space points
+// p(x,y) = z * ((x - cx)/fx, (y - cy)/fy, 1), normal = normalize((p_right - p_left) x (p_top - p_bottom)) with
+// bottom = row + 1, top = row - 1, zero on the one-pixel border.
+struct Pinhole {
+    float fx, fy, cx, cy;
+};
+
+__device__ __forceinline__ float3 depth_point(const float* __restrict__ depth, int W, int x, int y, const Pinhole k)
+{
+    const float z = depth[(size_t)y * W + x];
+    return make_float3(z * (((float)x - k.cx) / k.fx), z * (((float)y - k.cy) / k.fy), z);
+}
+
+__device__ __forceinline__ float3 cross3(const float3 a, const float3 b)
+{
+    return make_float3(a.y * b.z - a.z * b.y, a.z * b.x - a.x * b.z, a.x * b.y - a.y * b.x);
+}
+
+// a = right - left, b = top - bottom, c = a x b of the interior pixel (x, y)
+__device__ __forceinline__ void normal_frame(const float* __restrict__ depth, int W, int x, int y, const Pinhole k,
+                                             float3& a, float3& b, float3& c)
+{
+    const float3 pr = depth_point(depth, W, x + 1, y, k), pl = depth_point(depth, W, x - 1, y, k);
+    const float3 pt = depth_point(depth, W, x, y - 1, k), pb = depth_point(depth, W, x, y + 1, k);
+    a = make_float3(pr.x - pl.x, pr.y - pl.y, pr.z - pl.z);
+    b = make_float3(pt.x - pb.x, pt.y - pb.y, pt.z - pb.z);
+    c = cross3(a, b);
+}
+
+__global__ void __launch_bounds__(256)
+depth_normal_fwd_kernel(int H, int W, Pinhole k, const float* __restrict__ depth, float* __restrict__ normal)
+{
+    const int x = blockIdx.x * 32 + (threadIdx.x & 31), y = blockIdx.y * 8 + (threadIdx.x >> 5);
+    if (x >= W || y >= H) return;
+    float3 n = make_float3(0.f, 0.f, 0.f);
+    if (x > 0 && x < W - 1 && y > 0 && y < H - 1) {
+        float3 a, b, c;
+        normal_frame(depth, W, x, y, k, a, b, c);
+        const float len = fmaxf(sqrtf(c.x * c.x + c.y * c.y + c.z * c.z), 1e-12f);
+        n = make_float3(c.x / len, c.y / len, c.z / len);
+    }
+    const size_t HW = (size_t)H * W, o = (size_t)y * W + x;
+    normal[o] = n.x;
+    normal[HW + o] = n.y;
+    normal[2 * HW + o] = n.z;
+}
+
+// Cotangent of the cross product c of interior pixel (x, y) given the cotangent g of its unit normal.
+__device__ __forceinline__ bool normal_cotangent(const float* __restrict__ depth, const float* __restrict__ g, int H,
+                                                 int W, int x, int y, const Pinhole k, float3& a, float3& b,
+                                                 float3& gc)
+{
+    if (x <= 0 || x >= W - 1 || y <= 0 || y >= H - 1) return false;
+    float3 c;
+    normal_frame(depth, W, x, y, k, a, b, c);
+    const float len = sqrtf(c.x * c.x + c.y * c.y + c.z * c.z);
+    if (!(len > 1e-12f)) return false;            // clamped norm: the direction carries no gradient
+    const size_t HW = (size_t)H * W, o = (size_t)y * W + x;
+    const float3 gn = make_float3(g[o], g[HW + o], g[2 * HW + o]);
+    const float3 n = make_float3(c.x / len, c.y / len, c.z / len);
+    const float d = n.x * gn.x + n.y * gn.y + n.z * gn.z;
+    gc = make_float3((gn.x - n.x * d) / len, (gn.y - n.y * d) / len, (gn.z - n.z * d) / len);
+    return true;
+}
+
+// Gather form: a depth pixel is the right / left / top / bottom point of four neighbouring normals.
+__global__ void __launch_bounds__(256)
+depth_normal_bwd_kernel(int H, int W, Pinhole k, const float* __restrict__ depth, const float* __restrict__ g,
+                        float* __restrict__ dL_ddepth)
+{
+    const int x = blockIdx.x * 32 + (threadIdx.x & 31), y = blockIdx.y * 8 + (threadIdx.x >> 5);
+    if (x >= W || y >= H) return;
+    float3 gp = make_float3(0.f, 0.f, 0.f);       // cotangent of this pixel's camera-space point
+    float3 a, b, gc;
+    // c = a x b:  dL/da = b x gc,  dL/db = gc x a
+    if (normal_cotangent(depth, g, H, W, x - 1, y, k, a, b, gc)) {        // right point of (x-1, y): +dL/da
+        const float3 t = cross3(b, gc);
+        gp.x += t.x; gp.y += t.y; gp.z += t.z;
+    }
+    if (normal_cotangent(depth, g, H, W, x + 1, y, k, a, b, gc)) {        // left point of (x+1, y): -dL/da
+        const float3 t = cross3(b, gc);
+        gp.x -= t.x; gp.y -= t.y; gp.z -= t.z;
+    }
+    if (normal_cotangent(depth, g, H, W, x, y + 1, k, a, b, gc)) {        // top point of (x, y+1): +dL/db
+        const float3 t = cross3(gc, a);
+        gp.x += t.x; gp.y += t.y; gp.z += t.z;
+    }
+    if (normal_cotangent(depth, g, H, W, x, y - 1, k, a, b, gc)) {        // bottom point of (x, y-1): -dL/db
+        const float3 t = cross3(gc, a);
+        gp.x -= t.x; gp.y -= t.y; gp.z -= t.z;
+    }
+    dL_ddepth[(size_t)y * W + x] = gp.x * (((float)x - k.cx) / k.fx) + gp.y * (((float)y - k.cy) / k.fy) + gp.z;
+}
+
 static int upload_window()
 {
     int dev = 0;
@@ -242,5 +338,24 @@ extern "C" int cgx_strip_loss_bwd(int C, int H, int W, const float* img, const f
     dim3 grid((W + LB - 1) / LB, (H + LB - 1) / LB, C), block(LB, LB);
     strip_loss_bwd_kernel<<<grid, block, 0, (cudaStream_t)stream>>>(H, W, img, gt, mask, weights, d_mu, d_xx, d_xy,
                                                                     dL_dimg);
+    return check_launch();
+}
+
+extern "C" int cgx_depth_normal_fwd(int H, int W, float fx, float fy, float cx, float cy, const float* depth,
+                                    float* normal, void* stream)
+{
+    if (H <= 0 || W <= 0 || !depth || !normal || fx == 0.f || fy == 0.f) return CGX_EINVAL;
+    dim3 grid((W + 31) / 32, (H + 7) / 8);
+    depth_normal_fwd_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(H, W, Pinhole{fx, fy, cx, cy}, depth, normal);
+    return check_launch();
+}
+
+extern "C" int cgx_depth_normal_bwd(int H, int W, float fx, float fy, float cx, float cy, const float* depth,
+                                    const float* dL_dnormal, float* dL_ddepth, void* stream)
+{
+    if (H <= 0 || W <= 0 || !depth || !dL_dnormal || !dL_ddepth || fx == 0.f || fy == 0.f) return CGX_EINVAL;
+    dim3 grid((W + 31) / 32, (H + 7) / 8);
+    depth_normal_bwd_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(H, W, Pinhole{fx, fy, cx, cy}, depth, dL_dnormal,
+                                                                    dL_ddepth);
     return check_launch();
 }

@@ -64,6 +64,8 @@ SIGNATURES = {
     "cgx_all_map_bwd": (_i, [_i] + [_vp] * 10),
     "cgx_strip_loss_fwd": (_i, [_i, _i, _i] + [_vp] * 8),
     "cgx_strip_loss_bwd": (_i, [_i, _i, _i] + [_vp] * 9),
+    "cgx_depth_normal_fwd": (_i, [_i, _i, _f, _f, _f, _f, _vp, _vp, _vp]),
+    "cgx_depth_normal_bwd": (_i, [_i, _i, _f, _f, _f, _f, _vp, _vp, _vp, _vp]),
     "cgx_local2j_mask": (_i, [_i, _i, _i, _i, _vp, _vp, _vp, _i, _vp, _vp]),
     "cgx_local2j_count": (_i, [_i, _i, _i, _i, _vp, _vp, _vp, _i, _vp, _vp, _sz, _vp]),
     "cgx_local2j_workspace_bytes": (_sz, [_i, _i]),

@@ -153,6 +153,16 @@ int cgx_strip_loss_bwd(int C, int H, int W, const float* img, const float* gt, c
                        const float* weights, const float* d_mu, const float* d_xx, const float* d_xy, float* dL_dimg,
                        void* stream);
 
+/* Normal image of a depth image and its backward: render_normal (gaussian_renderer/__init__.py:1311-1323) at
+ * scale 1 without offsets, i.e. normal_from_depth_image / depth_pcd2normal (utils/graphics_utils.py:87-152):
+ * camera-space points z * ((x - cx)/fx, (y - cy)/fy, 1), normalised cross product of the horizontal and vertical
+ * central differences, zero on the one-pixel border.  depth (H,W) -> normal (3,H,W); dL_dnormal (3,H,W) ->
+ * dL_ddepth (H,W), written. */
+int cgx_depth_normal_fwd(int H, int W, float fx, float fy, float cx, float cy, const float* depth, float* normal,
+                         void* stream);
+int cgx_depth_normal_bwd(int H, int W, float fx, float fy, float cx, float cy, const float* depth,
+                         const float* dL_dnormal, float* dL_ddepth, void* stream);
+
 /* ------------------------------------------------------------------ distribution */
 
 /* GetLocal2jIdsBoolCUDA -> getTouchedIdsBool (RAST/rasterize_points.cu:445-524).

@@ -67,3 +67,45 @@ def test_strip_loss_refuses_cpu_tensors():
 
     with pytest.raises(RuntimeError, match="CUDA"):
         strip_loss_sums(torch.zeros(3, 8, 8), torch.zeros(3, 8, 8))
+
+
+def _reference_normal(depth, fx, fy, cx, cy):
+    """utils/graphics_utils.py:87-152 (depth2point_cam / ndc_2_cam / depth_pcd2normal without offsets)."""
+    H, W = depth.shape
+    xs = torch.arange(W, dtype=depth.dtype, device=depth.device)
+    ys = torch.arange(H, dtype=depth.dtype, device=depth.device)
+    gx, gy = torch.meshgrid(xs, ys, indexing="xy")
+    xyz = torch.stack([(gx - cx) / fx * depth, (gy - cy) / fy * depth, depth], -1)
+    bottom, top = xyz[2:H, 1:W - 1], xyz[0:H - 2, 1:W - 1]
+    right, left = xyz[1:H - 1, 2:W], xyz[1:H - 1, 0:W - 2]
+    n = torch.cross(right - left, top - bottom, dim=-1)
+    n = F.normalize(n, p=2, dim=-1)
+    return F.pad(n.permute(2, 0, 1), (1, 1, 1, 1), mode="constant")
+
+
+@pytest.mark.parametrize("shape", [(60, 90), (3, 3), (2, 5), (240, 320)])
+def test_depth_normal_matches_tensor_form(cuda_device, shape):
+    from cgx.strip_loss import depth_normal
+
+    H, W = shape
+    gen = torch.Generator().manual_seed(H * W)
+    yy, xx = torch.meshgrid(torch.arange(H, dtype=torch.float32), torch.arange(W, dtype=torch.float32), indexing="ij")
+    depth = 20.0 + 0.05 * xx + 0.03 * yy + torch.rand(H, W, generator=gen)        # a tilted, rough surface
+    fx, fy, cx, cy = 0.8 * W, 0.8 * W, W / 2.0, H / 2.0
+    cot = torch.randn(3, H, W, generator=gen)
+
+    d = depth.to(cuda_device).requires_grad_(True)
+    n = depth_normal(d, fx, fy, cx, cy)
+    (n * cot.to(cuda_device)).sum().backward()
+
+    d64 = depth.double().to(cuda_device).requires_grad_(True)
+    n64 = _reference_normal(d64, fx, fy, cx, cy)
+    (n64 * cot.double().to(cuda_device)).sum().backward()
+
+    assert n.shape == (3, H, W)
+    assert (n - n64.float()).abs().max().item() <= 2e-5
+    if H > 2 and W > 2:
+        ga, gb = d.grad.double(), d64.grad
+        assert ((ga - gb).norm() / gb.norm()).item() <= 1e-3          # float32 differences of nearby points
+    else:
+        assert not n.any() and not d.grad.any()
