@@ -346,6 +346,30 @@ def _camera_layout(n, fields=_CAM_FIELDS):
     return [int(o) for o in offs], int(size)
 
 
+def p2p_layout(S, me, fields=_CAM_FIELDS):
+    """Where everything goes in the peer-to-peer exchange, from the gathered size table S[src, dst, cam] (pure
+    integer arithmetic, the same on every rank except for the rows that depend on `me`):
+
+    n_recv[dst, cam]       rows rank dst receives for camera cam (all sources)
+    cam_base[dst, cam]     byte offset of camera cam's region in rank dst's receive arena
+    field_off[dst, cam, f] byte offset of tensor f inside that region (256-byte aligned)
+    recv_bytes             arena size that holds every rank's regions
+    first_row[dst, cam]    first row rank `me` writes in (dst, cam)'s tensors: behind the rows of lower source ranks
+    grad_row[src, cam]     row, in rank src's gradient staging buffer (= its send order: destination major, camera
+                           minor), of the segment whose gradients rank `me` returns to src for camera cam
+    grad_rows_max          rows of the largest staging buffer
+    """
+    S = np.asarray(S, dtype=np.int64)
+    ws, _, bsz = S.shape
+    n_recv = S.sum(0)
+    field_off, cam_size = _camera_layouts(n_recv, fields)
+    cam_end = np.cumsum(cam_size, axis=1)
+    per_src = S.reshape(ws, -1)
+    grad_row = (np.cumsum(per_src, axis=1) - per_src).reshape(ws, ws, bsz)[:, me, :]
+    return dict(n_recv=n_recv, cam_base=cam_end - cam_size, field_off=field_off, recv_bytes=int(cam_end[:, -1].max()),
+                first_row=S[:me].sum(0), grad_row=grad_row, grad_rows_max=int(per_src.sum(1).max()))
+
+
 class PeerArena:
     """Symmetric-memory receive arena (forward rows) and gradient staging buffer (backward rows) of one group."""
 
@@ -594,13 +618,10 @@ def all_to_all_communication_final(batched_rasterizers, batched_screenspace_para
         raise RuntimeError("the plane-descriptor record form needs the peer-to-peer transport")
     send_index = torch.empty(n_send, dtype=torch.int32, device=dev)
     if transport == "p2p":
-        n_recv = S.sum(0)                                            # [dst][cam]
-        field_off, cam_size = _camera_layouts(n_recv, _CAM_FIELDS_PLANES if planes else _CAM_FIELDS)
-        cam_end = np.cumsum(cam_size, axis=1)
-        per_src = S.reshape(ws, -1)
-        grad_row = (np.cumsum(per_src, axis=1) - per_src).reshape(ws, ws, bsz)[:, me, :]
+        lay = p2p_layout(S, me, _CAM_FIELDS_PLANES if planes else _CAM_FIELDS)
+        n_recv, field_off, grad_row = lay["n_recv"], lay["field_off"], lay["grad_row"]
         arena = _arena_for(group, dev)
-        arena.ensure(int(cam_end[:, -1].max()), int(per_src.sum(1).max()) * REC_DIFF * 4)
+        arena.ensure(lay["recv_bytes"], lay["grad_rows_max"] * REC_DIFF * 4)
         # gradient rows carry 19 columns only when some rank needs gradients for the 3-D parameters through the
         # exchange; every rank runs the same model code, so this is the same decision everywhere
         if planes:
@@ -610,8 +631,8 @@ def all_to_all_communication_final(batched_rasterizers, batched_screenspace_para
             grad_cols = REC_DIFF if any(flat[6 * k + c].requires_grad for k in range(bsz) for c in (3, 4, 5)) else 9
         stats["bytes_sent_bwd"] = (n_send - self_rows) * grad_cols * 4
         plan = dict(backend=backend, arena=arena, me=me, ws=ws, S=S, strategies=batched_strategies,
-                    grad_cols=grad_cols, planes=planes, n_recv=n_recv, cam_base=cam_end - cam_size, field_off=field_off,
-                    first_row=S[:me].sum(0), grad_row=grad_row, bounds=bounds, scratch=scratch,
+                    grad_cols=grad_cols, planes=planes, n_recv=n_recv, cam_base=lay["cam_base"], field_off=field_off,
+                    first_row=lay["first_row"], grad_row=grad_row, bounds=bounds, scratch=scratch,
                     send_index=send_index, send_off=send_off, send_ranges=send_ranges, n_send=n_send,
                     params=[tuple(t.detach() for t in p) for p in batched_screenspace_params],
                     hw=[(r.raster_settings.image_height, r.raster_settings.image_width) for r in batched_rasterizers],

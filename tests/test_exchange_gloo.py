@@ -223,3 +223,50 @@ def test_cuda_backend_refuses_cpu_tensors():
     with pytest.raises(RuntimeError, match="CUDA"):
         b.count(torch.zeros(4, 2), torch.zeros(4, dtype=torch.int32), torch.tensor([0, 4], dtype=torch.int32), 16, 16,
                 False, torch.zeros(1, dtype=torch.int32), torch.zeros(1, dtype=torch.uint8))
+
+
+def test_p2p_layout_is_consistent_across_ranks():
+    """The arena layout of the peer-to-peer transport, computed independently by every rank from the same size
+    table, must tile each destination tensor without gaps or overlaps, and the gradient rows every receiver
+    returns must land exactly on the sender's send order."""
+    import numpy as np
+    from cgx import exchange as EX
+
+    rng = np.random.default_rng(3)
+    ws, bsz = 5, 3
+    S = rng.integers(0, 400, size=(ws, ws, bsz))
+    S[:, 2, 1] = 0                         # a camera rank 2 takes no part in
+    S[3] = 0                               # a rank that sends nothing
+    for fields in (EX._CAM_FIELDS, EX._CAM_FIELDS_PLANES):
+        lays = [EX.p2p_layout(S, me, fields) for me in range(ws)]
+        widths = [w for _, w in fields]
+        for a in lays[1:]:                 # rank-independent parts agree
+            for key in ("n_recv", "cam_base", "field_off"):
+                assert np.array_equal(a[key], lays[0][key])
+            assert a["recv_bytes"] == lays[0]["recv_bytes"] and a["grad_rows_max"] == lays[0]["grad_rows_max"]
+        L = lays[0]
+        for j in range(ws):
+            spans = []
+            for k in range(bsz):
+                # the sources' row ranges tile [0, n_recv) in source order
+                cur = 0
+                for i in range(ws):
+                    assert lays[i]["first_row"][j, k] == cur
+                    cur += S[i, j, k]
+                assert cur == L["n_recv"][j, k]
+                for f, w in enumerate(widths):
+                    lo = L["cam_base"][j, k] + L["field_off"][j, k, f]
+                    assert lo % 256 == 0
+                    spans.append((lo, lo + L["n_recv"][j, k] * w))
+            spans.sort()
+            for (a0, a1), (b0, b1) in zip(spans, spans[1:]):
+                assert a1 <= b0                                      # tensors of one arena never overlap
+            assert spans[-1][1] <= L["recv_bytes"]
+        # gradient rows: receiver `me` returns segment (src i, camera k) to row grad_row[i, k] of i's staging buffer,
+        # which must be where i's own send order (destination major, camera minor) put those rows
+        for i in range(ws):
+            order = np.cumsum(S[i].reshape(-1)) - S[i].reshape(-1)
+            for me in range(ws):
+                for k in range(bsz):
+                    assert lays[me]["grad_row"][i, k] == order[me * bsz + k]
+            assert S[i].sum() <= L["grad_rows_max"]
