@@ -1,6 +1,6 @@
-"""Multi-GPU equivalence (NCCL): the data-parallel step on 2 ranks must reproduce the single-GPU step.
+"""Multi-GPU equivalence (NCCL): the data-parallel step on 2, 3 or 4 ranks must reproduce the single-GPU step.
 
-Runs as child processes, one per GPU, only where at least two GPUs are visible.  NVLS is switched off for NCCL
+Runs as child processes, one per GPU, only where enough GPUs are visible.  NVLS is switched off for NCCL
 in these children (plain peer transport is all the exchange needs) and symmetric memory is set up without
 multicast objects."""
 import os
@@ -56,37 +56,44 @@ def _worker(rank, ws, port, out_dir, transport):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("transport", ["p2p", "collective"])
-def test_two_gpu_step_equals_single_gpu_step(tmp_path, transport):
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs two GPUs")
+@pytest.mark.parametrize("transport,ws", [("p2p", 2), ("collective", 2), ("p2p", 4), ("p2p", 3)])
+def test_multi_gpu_step_equals_single_gpu_step(tmp_path, transport, ws):
+    """ws = 3 does not divide the 4 cameras: a camera is split between two ranks (tile-row bands)."""
+    if torch.cuda.device_count() < ws:
+        pytest.skip(f"needs {ws} GPUs")
     import torch.multiprocessing as mp
     import util
     from cgx import runtime as RT
     from cgx import synthetic as S
 
     port = _free_port()
-    mp.spawn(_worker, args=(2, port, str(tmp_path), transport), nprocs=2, join=True)
-    parts = [torch.load(tmp_path / f"rank{r}.pt", weights_only=False) for r in range(2)]
+    mp.spawn(_worker, args=(ws, port, str(tmp_path), transport), nprocs=ws, join=True)
+    parts = [torch.load(tmp_path / f"rank{r}.pt", weights_only=False) for r in range(ws)]
 
     dev = torch.device("cuda:0")
     g, cams = S.config(2, n_gaussians=N_GAUSS, n_cameras=N_CAMS, res=RES)
     single = RT.TrainingStep(g, cams, dev, rank=0, world_size=1)
     single.run()
     torch.cuda.synchronize()
-    # 4 cameras over 2 ranks: two whole cameras each
-    assert parts[0]["strategies"] == [([0], [0, 30]), ([0], [0, 30]), ([1], [0, 30]), ([1], [0, 30])]
+    if ws == 2:      # 4 cameras over 2 ranks: two whole cameras each
+        assert parts[0]["strategies"] == [([0], [0, 30]), ([0], [0, 30]), ([1], [0, 30]), ([1], [0, 30])]
+    elif ws == 4:    # one whole camera each
+        assert [s[0] for s in parts[0]["strategies"]] == [[0], [1], [2], [3]]
+    else:            # some camera is shared by two ranks
+        assert any(len(s[0]) > 1 for s in parts[0]["strategies"])
+    for r in range(1, ws):
+        assert parts[r]["strategies"] == parts[0]["strategies"]
     assert parts[0]["ex"]["bytes_sent_fwd"] > 0 and parts[0]["ex"]["transport"] == transport
     for name, full in single.params.items():
         full = full.grad.cpu()
         merged = torch.zeros_like(full)
-        for r in range(2):
-            merged[r::2] = parts[r]["grads"][name]
+        for r in range(ws):
+            merged[r::ws] = parts[r]["grads"][name]
         assert util.rel_l2(merged, full) <= 1e-3, (name, util.rel_l2(merged, full))
     # densification statistics: radii and means2D.grad of every camera land on the owning rank
     for k in range(N_CAMS):
         radii_full, m2_full = single.last[k][0].cpu(), single.last[k][1].grad.cpu()
-        for r in range(2):
+        for r in range(ws):
             radii_r, m2g_r = parts[r]["m2"][k]
-            assert torch.equal(radii_r, radii_full[r::2])
-            assert util.rel_l2(m2g_r, m2_full[r::2]) <= 1e-3
+            assert torch.equal(radii_r, radii_full[r::ws])
+            assert util.rel_l2(m2g_r, m2_full[r::ws]) <= 1e-3
