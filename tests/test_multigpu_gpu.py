@@ -13,7 +13,7 @@ import torch
 
 pytestmark = pytest.mark.gpu
 ROOT = Path(__file__).resolve().parent.parent
-N_GAUSS, RES, N_CAMS = 200_000, (640, 480), 4
+N_GAUSS, RES = 200_000, (640, 480)
 
 
 def _free_port():
@@ -22,7 +22,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, ws, port, out_dir, transport):
+def _worker(rank, ws, port, out_dir, transport, n_cams):
     for p in (ROOT, ROOT / "citygs-x_b200", ROOT / "tests"):
         sys.path.insert(0, str(p))
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0",
@@ -36,7 +36,7 @@ def _worker(rank, ws, port, out_dir, transport):
         from cgx import runtime as RT
         from cgx import synthetic as S
 
-        g, cams = S.config(2, n_gaussians=N_GAUSS, n_cameras=N_CAMS, res=RES)
+        g, cams = S.config(2, n_gaussians=N_GAUSS, n_cameras=n_cams, res=RES)
         step = RT.TrainingStep(g, cams, dev, rank=rank, world_size=ws, transport=transport)
         step.run()
         step.run()          # twice: the second step reuses the exchange arenas
@@ -56,9 +56,11 @@ def _worker(rank, ws, port, out_dir, transport):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("transport,ws", [("p2p", 2), ("collective", 2), ("p2p", 4), ("p2p", 3)])
-def test_multi_gpu_step_equals_single_gpu_step(tmp_path, transport, ws):
-    """ws = 3 does not divide the 4 cameras: a camera is split between two ranks (tile-row bands)."""
+@pytest.mark.parametrize("transport,ws,n_cams", [("p2p", 2, 4), ("collective", 2, 4), ("p2p", 2, 3),
+                                                  ("collective", 2, 3), ("p2p", 4, 4), ("p2p", 3, 4)])
+def test_multi_gpu_step_equals_single_gpu_step(tmp_path, transport, ws, n_cams):
+    """Where ws does not divide the cameras, one camera is split between two ranks (tile-row bands): Gaussians
+    straddling the cut go to both, and their gradient rows come back from both."""
     if torch.cuda.device_count() < ws:
         pytest.skip(f"needs {ws} GPUs")
     import torch.multiprocessing as mp
@@ -67,16 +69,18 @@ def test_multi_gpu_step_equals_single_gpu_step(tmp_path, transport, ws):
     from cgx import synthetic as S
 
     port = _free_port()
-    mp.spawn(_worker, args=(ws, port, str(tmp_path), transport), nprocs=ws, join=True)
+    mp.spawn(_worker, args=(ws, port, str(tmp_path), transport, n_cams), nprocs=ws, join=True)
     parts = [torch.load(tmp_path / f"rank{r}.pt", weights_only=False) for r in range(ws)]
 
     dev = torch.device("cuda:0")
-    g, cams = S.config(2, n_gaussians=N_GAUSS, n_cameras=N_CAMS, res=RES)
+    g, cams = S.config(2, n_gaussians=N_GAUSS, n_cameras=n_cams, res=RES)
     single = RT.TrainingStep(g, cams, dev, rank=0, world_size=1)
     single.run()
     torch.cuda.synchronize()
-    if ws == 2:      # 4 cameras over 2 ranks: two whole cameras each
+    if (ws, n_cams) == (2, 4):      # 4 cameras over 2 ranks: two whole cameras each
         assert parts[0]["strategies"] == [([0], [0, 30]), ([0], [0, 30]), ([1], [0, 30]), ([1], [0, 30])]
+    elif (ws, n_cams) == (2, 3):    # the middle camera is cut in half
+        assert parts[0]["strategies"] == [([0], [0, 30]), ([0, 1], [0, 15, 30]), ([1], [0, 30])]
     elif ws == 4:    # one whole camera each
         assert [s[0] for s in parts[0]["strategies"]] == [[0], [1], [2], [3]]
     else:            # some camera is shared by two ranks
@@ -91,7 +95,7 @@ def test_multi_gpu_step_equals_single_gpu_step(tmp_path, transport, ws):
             merged[r::ws] = parts[r]["grads"][name]
         assert util.rel_l2(merged, full) <= 1e-3, (name, util.rel_l2(merged, full))
     # densification statistics: radii and means2D.grad of every camera land on the owning rank
-    for k in range(N_CAMS):
+    for k in range(n_cams):
         radii_full, m2_full = single.last[k][0].cpu(), single.last[k][1].grad.cpu()
         for r in range(ws):
             radii_r, m2g_r = parts[r]["m2"][k]
