@@ -8,7 +8,7 @@ from test_parity_gpu import FWD_TOL, GRAD_TOL, GRADS, run_ours
 
 pytestmark = pytest.mark.gpu
 
-GOLDEN_FILES = sorted(util.GOLDEN.glob("*.npz"))
+GOLDEN_FILES = sorted(util.GOLDEN.glob("cfg*.npz"))     # rasterizer cases (the loss cases are loss_*.npz)
 
 
 @pytest.mark.parametrize("path", GOLDEN_FILES, ids=lambda p: p.stem)

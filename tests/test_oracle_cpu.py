@@ -195,7 +195,7 @@ def test_local2j_mask_semantics():
                              [False, False]]       # culled row (means2D = 0, radius 0): empty span
 
 
-GOLDEN_FILES = sorted(util.GOLDEN.glob("*.npz"))
+GOLDEN_FILES = sorted(util.GOLDEN.glob("cfg*.npz"))     # rasterizer cases (the loss cases are loss_*.npz)
 
 
 @pytest.mark.parametrize("path", GOLDEN_FILES, ids=lambda p: p.stem)
