@@ -31,7 +31,8 @@ from pathlib import Path
 HERE = Path(__file__).resolve().parent
 OUT = HERE / "_ref"
 MODULE = "cityx_ref_C"
-DEFAULT_SRC = "/root/reference/submodule_cityx/diff-gaussian-rasterization"
+# default location: a checkout of the reference next to this repository (<parent>/reference)
+DEFAULT_SRC = str(HERE.parent.parent / "reference" / "submodule_cityx" / "diff-gaussian-rasterization")
 
 SOURCES = [
     "cuda_rasterizer/rasterizer_impl.cu",
