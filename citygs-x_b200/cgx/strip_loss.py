@@ -28,7 +28,7 @@ class _StripLoss(torch.autograd.Function):
             if mask.shape != (H, W) or not mask.is_cuda:
                 raise RuntimeError("strip_loss: mask must be a (H, W) CUDA tensor")
             mask = mask.to(torch.bool).contiguous()
-        sums = torch.empty(2, device=image.device)
+        sums = torch.empty(2, device=image.device, dtype=torch.float64)
         need = image.requires_grad
         maps = torch.empty(3, C, H, W, device=image.device) if need else None
         if C * H * W:
@@ -40,6 +40,7 @@ class _StripLoss(torch.autograd.Function):
         else:
             sums.zero_()
         ctx.save_for_backward(image, gt, mask, maps)
+        sums = sums.to(torch.float32)
         return sums[0], sums[1]
 
     @staticmethod

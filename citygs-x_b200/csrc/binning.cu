@@ -425,7 +425,10 @@ local2j_mask_kernel(int P, int gx, int gy, int ws, const float2* __restrict__ me
 }
 
 constexpr int MAX_WS = 32;
-constexpr int PACK_TILE = 256;  // rows per CTA
+#ifndef CGX_PACK_TILE
+#define CGX_PACK_TILE 256
+#endif
+constexpr int PACK_TILE = CGX_PACK_TILE;  // rows per CTA (and threads per CTA) of the exchange's count / pack kernels
 
 // counts[j] (global) and per-CTA counts block_counts[j * nblocks + b]
 __global__ void __launch_bounds__(PACK_TILE)

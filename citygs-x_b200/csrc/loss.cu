@@ -46,7 +46,7 @@ __device__ __forceinline__ float block_sum_256(float v, int tid, float* s_red)
 
 __global__ void __launch_bounds__(LB * LB)
 strip_loss_fwd_kernel(int H, int W, const float* __restrict__ img, const float* __restrict__ gt,
-                      const uint8_t* __restrict__ mask, float* __restrict__ sums, float* __restrict__ d_mu,
+                      const uint8_t* __restrict__ mask, double* __restrict__ sums, float* __restrict__ d_mu,
                       float* __restrict__ d_xx, float* __restrict__ d_xy)
 {
     __shared__ float s_x[LT][LT + 1];
@@ -120,9 +120,9 @@ strip_loss_fwd_kernel(int H, int W, const float* __restrict__ img, const float* 
     }
     const float t1 = block_sum_256(l1, tid, s_red);
     const float t2 = block_sum_256(ss, tid, s_red);
-    if (tid == 0) {
-        atomicAdd(sums, t1);
-        atomicAdd(sums + 1, t2);
+    if (tid == 0) {      // thousands of CTA partial sums: accumulated in double so that their order does not matter
+        atomicAdd(sums, (double)t1);
+        atomicAdd(sums + 1, (double)t2);
     }
 }
 
@@ -311,13 +311,13 @@ static int upload_window()
 using namespace cgx;
 
 extern "C" int cgx_strip_loss_fwd(int C, int H, int W, const float* img, const float* gt, const uint8_t* mask,
-                                  float* sums, float* d_mu, float* d_xx, float* d_xy, void* stream)
+                                  double* sums, float* d_mu, float* d_xx, float* d_xy, void* stream)
 {
     if (C <= 0 || H <= 0 || W <= 0 || !img || !gt || !sums) return CGX_EINVAL;
     if ((d_mu != nullptr) != (d_xx != nullptr) || (d_mu != nullptr) != (d_xy != nullptr)) return CGX_EINVAL;
     int st = upload_window();
     if (st != CGX_OK) return st;
-    cudaError_t e = cudaMemsetAsync(sums, 0, 2 * sizeof(float), (cudaStream_t)stream);
+    cudaError_t e = cudaMemsetAsync(sums, 0, 2 * sizeof(double), (cudaStream_t)stream);
     if (e != cudaSuccess) {
         set_cuda_error(e);
         return CGX_ECUDA;

@@ -142,12 +142,13 @@ int cgx_all_map_bwd(int P, const float* means3D, const float* scales, const floa
 /* Masked L1 and masked 11x11 Gaussian-window SSIM sums of a rendered strip against its ground truth, and the
  * gradient towards the rendered strip: pixelwise_l1_with_mask / pixelwise_ssim_with_mask (utils/loss_utils.py:88-132,
  * window from :27-43, zero padding as conv2d(padding=5)) and their autograd backward as two kernels.
- * img, gt: (C,H,W) float; mask: (H,W) bytes, 0 = excluded, optional.  sums[0] = sum mask*|img-gt|, sums[1] = sum
- * mask*SSIM (both written).  d_mu / d_xx / d_xy: (C,H,W) each, written by the forward when given (all three or
- * none): the masked partial derivatives of the SSIM map with respect to the window moments E[x], E[x^2], E[xy],
- * which is all the backward needs.  weights: 2 floats ON THE DEVICE = dL/dsums[0], dL/dsums[1] (no host read of the
- * incoming gradient).  dL_dimg (C,H,W) is written. */
-int cgx_strip_loss_fwd(int C, int H, int W, const float* img, const float* gt, const uint8_t* mask, float* sums,
+ * img, gt: (C,H,W) float; mask: (H,W) bytes, 0 = excluded, optional.  sums: two DOUBLES, both written,
+ * sums[0] = sum mask*|img-gt|, sums[1] = sum mask*SSIM (the per-CTA partial sums are accumulated in double, so
+ * the result does not depend on their order).  d_mu / d_xx / d_xy: (C,H,W) each, written by the forward when given
+ * (all three or none): the masked partial derivatives of the SSIM map with respect to the window moments E[x],
+ * E[x^2], E[xy], which is all the backward needs.  weights: 2 floats ON THE DEVICE = dL/dsums[0], dL/dsums[1] (no
+ * host read of the incoming gradient).  dL_dimg (C,H,W) is written. */
+int cgx_strip_loss_fwd(int C, int H, int W, const float* img, const float* gt, const uint8_t* mask, double* sums,
                        float* d_mu, float* d_xx, float* d_xy, void* stream);
 int cgx_strip_loss_bwd(int C, int H, int W, const float* img, const float* gt, const uint8_t* mask,
                        const float* weights, const float* d_mu, const float* d_xx, const float* d_xy, float* dL_dimg,
