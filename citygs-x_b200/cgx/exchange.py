@@ -229,10 +229,11 @@ def _world(group):
 _pinned = {}
 
 
-def _gather_table(table, n_counts, piggyback, group, ws):
+def _gather_table(table, n_counts, piggyback, group, ws, overlap=None):
     """All-gather every rank's `table` (int32: n_counts row counts, then len(piggyback) float32 bit patterns) and
     read it on the host: the one host synchronisation of the exchange.  Returns (int64 array (ws, n_counts),
-    nested list (ws, len(piggyback)) of floats)."""
+    nested list (ws, len(piggyback)) of floats).  `overlap`: called after the read-back has been queued and before
+    the host waits for it, for launches that do not depend on the table (they run while the host plans)."""
     L = table.numel() - n_counts
     if L:
         if table.is_cuda:
@@ -246,7 +247,21 @@ def _gather_table(table, n_counts, piggyback, group, ws):
             table[n_counts:].view(torch.float32).copy_(torch.tensor(list(piggyback), dtype=torch.float32))
     out = torch.empty(ws * table.numel(), dtype=torch.int32, device=table.device)
     dist.all_gather_into_tensor(out, table, group=group)
-    host = out.cpu().numpy().reshape(ws, -1)
+    if out.is_cuda:
+        stage = _pinned.get(("table", out.numel()))
+        if stage is None:
+            stage = _pinned[("table", out.numel())] = torch.empty(out.numel(), dtype=torch.int32).pin_memory()
+        stage.copy_(out, non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        if overlap is not None:
+            overlap()
+        ev.synchronize()
+        host = stage.numpy().reshape(ws, -1).copy()
+    else:
+        if overlap is not None:
+            overlap()
+        host = out.numpy().reshape(ws, -1)
     extra = host[:, n_counts:].copy().view(np.float32).tolist() if L else [[] for _ in range(ws)]
     return host[:, :n_counts].astype(np.int64), extra
 
@@ -435,7 +450,8 @@ class _GaussianExchangeP2P(torch.autograd.Function):
         peer_base = np.array([int(p) for p in arena.recv_hdl.buffer_ptrs], dtype=np.int64)
         # address of field f of camera k in rank j's arena, and the first row this rank writes there
         field_ptr = peer_base[:, None, None] + plan["cam_base"][:, :, None] + plan["field_off"]      # (ws, bsz, F)
-        arena.barrier()                       # every rank is done with the previous contents of the arenas
+        # (the barrier "every rank is done with the previous contents of the arenas" was queued by the caller,
+        # behind the size read-back)
         cameras = []
         for k in range(bsz):
             ids = plan["strategies"][k].gpu_ids
@@ -585,7 +601,14 @@ def all_to_all_communication_final(batched_rasterizers, batched_screenspace_para
         bounds.append(tb)
     if dist.get_backend(group) != "nccl":
         table_dev = table_dev.cpu()
-    gathered, extra = _gather_table(table_dev, bsz * ws, piggyback, group, ws)
+    transport = _pick_transport(transport, group, dev, backend)
+    if planes and transport != "p2p":
+        raise RuntimeError("the plane-descriptor record form needs the peer-to-peer transport")
+    arena = _arena_for(group, dev) if transport == "p2p" else None
+    # the barrier "every rank is done with the previous contents of the arenas" does not depend on the sizes: it is
+    # queued behind the size read-back and runs while the host lays out the exchange
+    gathered, extra = _gather_table(table_dev, bsz * ws, piggyback, group, ws,
+                                    overlap=arena.barrier if arena is not None else None)
     S = np.ascontiguousarray(gathered.reshape(ws, bsz, ws).transpose(0, 2, 1))     # [src][dst][cam]
     sizes_list = S.tolist()
     my = S[me]                                                       # [dst][cam]
@@ -612,15 +635,11 @@ def all_to_all_communication_final(batched_rasterizers, batched_screenspace_para
              "bytes_sent_fwd": (n_send - self_rows) * REC * 4, "bytes_sent_bwd": (n_send - self_rows) * REC_DIFF * 4,
              "piggyback": extra}
 
-    transport = _pick_transport(transport, group, dev, backend)
     stats["transport"] = transport
-    if planes and transport != "p2p":
-        raise RuntimeError("the plane-descriptor record form needs the peer-to-peer transport")
     send_index = torch.empty(n_send, dtype=torch.int32, device=dev)
     if transport == "p2p":
         lay = p2p_layout(S, me, _CAM_FIELDS_PLANES if planes else _CAM_FIELDS)
         n_recv, field_off, grad_row = lay["n_recv"], lay["field_off"], lay["grad_row"]
-        arena = _arena_for(group, dev)
         arena.ensure(lay["recv_bytes"], lay["grad_rows_max"] * REC_DIFF * 4)
         # gradient rows carry 19 columns only when some rank needs gradients for the 3-D parameters through the
         # exchange; every rank runs the same model code, so this is the same decision everywhere
