@@ -121,6 +121,49 @@ def test_direct_store_pack_per_camera_and_batched(setup, cuda_device):
     assert torch.equal(idx_b.cpu(), expect_index)
 
 
+def test_plane_descriptor_record_form(setup, cuda_device):
+    """Rows that carry (means2D, rgb, conic_opacity, all_map, radius, depth): 16 floats instead of 21."""
+    be, bounds, cams = setup
+    first_rows = [3, 0, 2]
+    ws = len(first_rows)
+    gen = torch.Generator().manual_seed(9)
+    batch, all_arrays, maps = [], [], []
+    cur, offs_all = 0, []
+    for j in range(ws):
+        for c in cams:
+            offs_all.append(cur)
+            cur += len(c["want"][j])
+    offs = np.array(offs_all, dtype=np.int64).reshape(ws, len(cams))
+    idx = torch.full((cur,), -1, dtype=torch.int32, device=cuda_device)
+    for k, c in enumerate(cams):
+        am = torch.randn(N, 5, generator=gen)
+        maps.append(am)
+        arrays, table = [], np.zeros((ws, 10), dtype=np.uint64)
+        for j, rows in enumerate(c["want"]):
+            n = first_rows[j] + len(rows)
+            arrs = [torch.full((n, w), -7.0, device=cuda_device) for w in (2, 3, 4, 5)]
+            arrs.append(torch.full((n,), -7, dtype=torch.int32, device=cuda_device))
+            arrs.append(torch.full((n,), -7.0, device=cuda_device))
+            arrays.append(arrs)
+            table[j, [0, 1, 2, 9, 6, 7]] = [a.data_ptr() for a in arrs]
+            table[j, 8] = first_rows[j]
+        all_arrays.append(arrays)
+        m2, rgb, co, rad, dep = c["gpu"][:5]
+        batch.append(dict(params=(m2, rgb, co, rad, dep, am.to(cuda_device)), bounds=bounds, H=H, W=W, avoid=False,
+                          dst_table=table, row_offsets=offs[:, k], workspace=c["wspace"]))
+    be.pack_p2p_batched(batch, idx)
+    torch.cuda.synchronize()
+    for arrays, c, am in zip(all_arrays, cams, maps):
+        m2, rgb, co, rad, dep = c["cpu"][:5]
+        for j, rows in enumerate(c["want"]):
+            f = first_rows[j]
+            for a, src in zip(arrays[j], (m2, rgb, co, am, rad, dep)):
+                a = a.cpu()
+                assert torch.equal(a[f:], src[rows])
+                assert (a[:f] == -7).all()
+    assert torch.equal(idx.cpu(), torch.cat([c["want"][j] for j in range(ws) for c in cams]).to(torch.int32))
+
+
 def test_batched_pack_splits_large_batches(setup, cuda_device):
     """More (camera, rank) pairs than one launch describes: the call must split and still fill every camera."""
     be, bounds, cams = setup
@@ -163,7 +206,7 @@ def test_send_buffer_pack_matches_oracle_mask(setup, cuda_device):
     assert torch.equal(idx.cpu(), rows.to(torch.int32))
 
 
-@pytest.mark.parametrize("ncols", [9, 19])
+@pytest.mark.parametrize("ncols", [9, 14, 19])
 def test_gradient_rows_round_trip(setup, cuda_device, ncols):
     """Receiver side: cotangents of one camera's received rows -> per-source segments; owner side: segments
     scatter-added through the send index.  A row sent to two ranks gets both contributions.  Row widths: 19 = all
