@@ -56,6 +56,9 @@ def parse_args():
     ap.add_argument("--no-stage-events", action="store_true", help="do not bracket library calls with CUDA events")
     ap.add_argument("--no-clocks", action="store_true", help="do not sample nvidia-smi during the run")
     ap.add_argument("--cpu-sample-gaussians", type=int, default=None)
+    ap.add_argument("--kernel-table", action="store_true",
+                    help="after the measurement, profile 3 more steps with torch.profiler on every rank and print "
+                         "rank 0's per-kernel device times to stderr (for multi-GPU runs, where ncu is not used)")
     ap.add_argument("--densification-stats", action="store_true",
                     help="update the densification statistics inside every step (always on for cfg4)")
     return ap.parse_args()
@@ -311,6 +314,19 @@ def main():
         dt, mp, sample = cpu_step_sample(cfg, a.cpu_sample_gaussians or a.gaussians, cam_idx=0)
         cpu = {"value": mp / dt, "unit": "Mpix/s", "cores": cores, "kind": "port", "sample": sample,
                "seconds": dt}
+
+    if a.kernel_table:
+        from torch.profiler import ProfilerActivity, profile
+
+        barrier()
+        with profile(activities=[ProfilerActivity.CPU, ProfilerActivity.CUDA]) as prof:
+            for _ in range(3):
+                step.run()
+            torch.cuda.synchronize()
+        if rank == 0:
+            print("per-kernel device time over 3 steps (torch.profiler, rank 0):", file=sys.stderr)
+            print(prof.key_averages().table(sort_by="cuda_time_total", row_limit=40, max_name_column_width=70),
+                  file=sys.stderr, flush=True)
 
     # balancer: per-rank render time (forward + backward, ms) of the first and the last recorded step
     balancer = None
