@@ -55,6 +55,27 @@ def test_counts_match_oracle_mask(setup):
         assert sum(len(w) for w in c["want"]) > N // 10           # the case actually selects rows
 
 
+@pytest.mark.parametrize("avoid", [False, True])
+def test_mask_equals_reference_kernel(setup, cuda_device, reference_C, avoid):
+    """The (P, ws) band mask against the reference's own getTouchedIdsBool (rasterize_points.cu:445-524), bit for
+    bit, with and without the one-tile-row widening of `avoid_pixel_all2all`; and the oracle's mask against both."""
+    from diff_gaussian_rasterization import _C
+
+    assert reference_C is not None, "oracle/_ref/cityx_ref_C.so is missing: build it with oracle/build_ref.py"
+    _, bounds, cams = setup
+    args = util.cuda_args()
+    args["avoid_pixel_all2all"] = avoid
+    ws = bounds.numel() - 1
+    for c in cams:
+        m2, rad = c["gpu"][0], c["gpu"][3]
+        ours = _C.get_local2j_ids_bool(H, W, 0, ws, m2, rad, bounds, args)
+        ref = reference_C.get_local2j_ids_bool(H, W, 0, ws, m2, rad, bounds, args)
+        assert ours.dtype == torch.bool and ours.shape == ref.shape == (N, ws)
+        assert torch.equal(ours, ref)
+        assert bool(ref.any()) and not bool(ref.all())
+        assert torch.equal(O.local2j_mask(c["cpu"][0], c["cpu"][3], bounds.cpu(), W, H, avoid), ref.cpu())
+
+
 def _alloc_dsts(want, dev, first_rows):
     """Per destination the eight arrays (with room for first_rows[j] foreign rows in front) and the pointer table."""
     widths = (2, 3, 4, 3, 3, 4, 1, 1)

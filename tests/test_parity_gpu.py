@@ -26,6 +26,10 @@ CASES = [
     dict(cfg=0, n=50000, res=(256, 144)),
     dict(cfg=1, n=30000, res=(333, 211), big_scales=True),     # not multiples of 16, many tiles per splat
     dict(cfg=2, n=300000, res=(800, 600)),
+    # the named configurations at their own resolution: 1M Gaussians at 1920x1080 (8160 tiles, 45 key bits), and
+    # the clustered city on a 3840x2160 grid (32400 tiles -> 15 tile bits, 47 key bits) with a reduced Gaussian count
+    dict(cfg=1, n=1_000_000, res=(1920, 1080)),
+    dict(cfg=3, n=2_000_000, res=(3840, 2160), cam_idx=5),
 ]
 
 
@@ -136,8 +140,7 @@ def masked_local(x, cam, local):
 
 @pytest.mark.parametrize("case", CASES, ids=lambda c: f"cfg{c['cfg']}-{c['n']}-{c['res'][0]}x{c['res'][1]}")
 def test_against_reference_extension(case, cuda_device, reference_C):
-    if reference_C is None:
-        pytest.skip("reference CUDA extension not built (oracle/_ref)")
+    assert reference_C is not None, "oracle/_ref/cityx_ref_C.so is missing: build it with oracle/build_ref.py"
     g, cam = make_case(**case)
     cot = cotangents(cam)
     ours = run_ours(g, cam, cuda_device, cot=cot)
@@ -217,6 +220,37 @@ def test_against_cpu_oracle(case, cuda_device):
                           rb["dL_dconic_opacity"])
     for k in ("dL_dmeans3D", "dL_dscales", "dL_drotations", "dL_dopacity"):
         assert rel_l2(ours[k], pb[k]) <= ORACLE_GRAD_TOL, (k, rel_l2(ours[k], pb[k]))
+
+
+def test_reference_extension_is_present(reference_C):
+    """The parity tests above are only as good as their checker: a box without the reference's compiled extension
+    must fail, not skip."""
+    assert reference_C is not None, "oracle/_ref/cityx_ref_C.so is missing: build it with oracle/build_ref.py"
+    assert reference_C.get_block_XY() == (16, 16, 256)
+
+
+def test_stats_collector_gets_render_times(cuda_device):
+    """The op fills args["stats_collector"] with the forward and backward blending times in milliseconds
+    (cuda_rasterizer/rasterizer_impl.cu:754-755, 924-926); the balancer divides work by them."""
+    from diff_gaussian_rasterization import GaussianRasterizer
+
+    g, cam = make_case(cfg=2, n=100_000, res=(640, 480))
+    dev = cuda_device
+    rast = GaussianRasterizer(settings_for(cam, dev))
+    gd = to_dev(g, dev)
+    stats = {}
+    args = cuda_args(stats)
+    m2, _, co, radii, depths = rast.preprocess_gaussians(gd["means3D"].requires_grad_(True), gd["scales"],
+                                                         gd["rotations"], gd["sh"], gd["opacities"], args)
+    TX, TY = (cam.W + 15) // 16, (cam.H + 15) // 16
+    local = torch.ones(TY, TX, dtype=torch.bool, device=dev)
+    m2abs = torch.zeros(m2.shape[0], 3, device=dev, requires_grad=True)
+    color, *_ = rast.render_gaussians(m2, m2abs, co, gd["rgb"], gd["all_map"], depths, radii, local, None, args)
+    assert "forward_render_time" in stats and "backward_render_time" not in stats
+    color.sum().backward()
+    fwd, bwd = float(stats["forward_render_time"]), float(stats["backward_render_time"])
+    assert 0.0 < fwd < 1000.0 and 0.0 < bwd < 1000.0
+    assert stats["forward_render_time"] + stats["backward_render_time"] == pytest.approx(fwd + bwd)
 
 
 def test_cull_variant_is_identical(cuda_device):

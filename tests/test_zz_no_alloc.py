@@ -13,12 +13,12 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-def _sorted_both_ways(n, end_bit, seed, dev):
+def _sorted_both_ways(n, end_bit, seed, dev, tiles_max=7500):
     from diff_gaussian_rasterization import _lib
 
     l = _lib.lib()
     gen = torch.Generator().manual_seed(seed)
-    tiles = torch.randint(0, 7500, (n,), generator=gen, dtype=torch.int64)
+    tiles = torch.randint(0, tiles_max, (n,), generator=gen, dtype=torch.int64)
     depth = torch.rand(n, generator=gen).mul(50).add(0.1).view(torch.int32).to(torch.int64) & 0xFFFFFFFF
     keys = ((tiles << 32) | depth).to(dev)
     vals = torch.arange(n, dtype=torch.int32, device=dev)
@@ -47,6 +47,15 @@ def test_static_sort_matches_workspace_sort_twice_in_a_row(cuda_device):
         assert torch.equal(k_st, k_ref) and torch.equal(v_st, v_ref)          # integer work: bit-exact
         order = torch.sort(keys & ((1 << 45) - 1), stable=True)[1]
         assert torch.equal(v_st.long(), order)
+
+
+def test_static_sort_at_its_ceiling_with_the_widest_keys(cuda_device):
+    # exactly as many pairs as the fixed scratch is sized for, keys of a 3840x2160 tile grid (47 sorted bits)
+    n = 1 << 22
+    (k_ref, v_ref), (k_st, v_st), keys = _sorted_both_ways(n, 47, 13, cuda_device, tiles_max=32400)
+    assert torch.equal(k_st, k_ref) and torch.equal(v_st, v_ref)
+    order = torch.sort(keys & ((1 << 47) - 1), stable=True)[1]
+    assert torch.equal(v_st.long(), order)
 
 
 def test_static_sort_rejects_sizes_beyond_its_scratch(cuda_device):
