@@ -12,7 +12,7 @@ import ctypes as C
 
 import torch
 
-from diff_gaussian_rasterization import _lib
+from diff_gaussian_rasterization import _C, _lib
 
 MAX_CAMS = 16
 
@@ -96,12 +96,12 @@ class _PreprocessBatched(torch.autograd.Function):
                 for i, (lo, hi) in enumerate(bounds):
                     if pipeline is not None and pipeline.ready is not None:
                         torch.cuda.current_stream().wait_event(pipeline.ready[i])
-                    _lib.check(_lib.lib().cgx_preprocess_fwd_batched_planes(
+                    _C._call("cgx_preprocess_fwd_batched", _lib.lib().cgx_preprocess_fwd_batched_planes,
                         hi - lo, B, _row(means3D, lo), _row(scales, lo), float(settings[0].scale_modifier),
                         _row(rotations, lo), _row(opacities, lo), cams, _ptrs(campos) if planes else None,
                         _ptrs(m2, lo), _ptrs(dep, lo), _ptrs(rad, lo), _ptrs(co, lo),
-                        _ptrs(am, lo) if planes else None, _lib.current_stream_ptr()),
-                        "cgx_preprocess_fwd_batched_planes")
+                        _ptrs(am, lo) if planes else None, _lib.current_stream_ptr(),
+                        info=dict(P=hi - lo, B=B, planes=planes))
         ctx.settings, ctx.planes, ctx.pipeline = settings, planes, pipeline
         ctx.save_for_backward(means3D, scales, rotations, *rad)
         flat = []
@@ -138,13 +138,13 @@ class _PreprocessBatched(torch.autograd.Function):
             bounds = pipeline.bounds if pipeline is not None else [(0, P)]
             with torch.cuda.device(dev):
                 for i, (lo, hi) in enumerate(bounds):
-                    _lib.check(_lib.lib().cgx_preprocess_bwd_batched_planes(
+                    _C._call("cgx_preprocess_bwd_batched", _lib.lib().cgx_preprocess_bwd_batched_planes,
                         hi - lo, len(use), _row(means3D, lo), _row(scales, lo), float(settings[0].scale_modifier),
                         _row(rotations, lo), cams, _ptrs(campos) if with_planes else None,
                         _ptrs([rad[b] for b in use], lo), _ptrs(g_m2, lo), _ptrs(g_co, lo),
                         _ptrs(g_am, lo) if with_planes else None,
                         _row(d_means, lo), _row(d_scales, lo), _row(d_rot, lo), _row(d_op, lo),
-                        _lib.current_stream_ptr()), "cgx_preprocess_bwd_batched_planes")
+                        _lib.current_stream_ptr(), info=dict(P=hi - lo, B=len(use), planes=with_planes))
                     if pipeline is not None and pipeline.done is not None:
                         pipeline.done(i, lo, hi, (d_means, d_scales, d_rot, d_op))
         else:

@@ -252,11 +252,13 @@ def _gather_table(table, n_counts, piggyback, group, ws, overlap=None):
         if stage is None:
             stage = _pinned[("table", out.numel())] = torch.empty(out.numel(), dtype=torch.int32).pin_memory()
         stage.copy_(out, non_blocking=True)
+        status = _queue_status_read()
         ev = torch.cuda.Event()
         ev.record()
         if overlap is not None:
             overlap()
         ev.synchronize()
+        _raise_on_device_status(status)
         host = stage.numpy().reshape(ws, -1).copy()
     else:
         if overlap is not None:
@@ -264,6 +266,31 @@ def _gather_table(table, n_counts, piggyback, group, ws, overlap=None):
         host = out.numpy().reshape(ws, -1)
     extra = host[:, n_counts:].copy().view(np.float32).tolist() if L else [[] for _ in range(ws)]
     return host[:, :n_counts].astype(np.int64), extra
+
+
+def _queue_status_read():
+    """Queue a copy of the library's device status words (set when a bounded device-side wait gave up) into pinned
+    memory, in front of a host synchronisation the caller performs anyway."""
+    from diff_gaussian_rasterization import _lib
+
+    stage = _pinned.get("status")
+    if stage is None:
+        stage = _pinned["status"] = torch.zeros(2, dtype=torch.int32).pin_memory()
+    _lib.check(_lib.lib().cgx_device_status_async(C.c_void_p(stage.data_ptr()), _lib.current_stream_ptr()),
+               "cgx_device_status_async")
+    return stage
+
+
+def _raise_on_device_status(stage):
+    """After the synchronisation: a wait that ran out earlier on this stream (a peer that never signalled, a bulk
+    copy that never completed) means rows may not have landed, so the step must not go on silently."""
+    if stage[0].item() or stage[1].item():
+        from diff_gaussian_rasterization import _lib
+
+        code = C.c_int(0)
+        _lib.lib().cgx_device_status(C.byref(code), _lib.current_stream_ptr())      # reads and clears
+        where = "the blending kernels" if stage[0].item() else "the peer barrier of the Gaussian exchange"
+        raise _lib.CgxError(_lib.CGX_ETIMEDOUT, f"a bounded device-side wait in {where}")
 
 
 def _dense_cotangents(g8, n, dev):
@@ -403,7 +430,11 @@ class PeerArena:
         torch.cuda.synchronize(device)
         self.flags_hdl = symm.rendezvous(self.flags, self.group)
         dist.barrier(group=self.group)
-        self.epoch = 0
+        # One exchange = one step of the arena.  The three barriers of step s carry the epochs 3s+1 (every rank is
+        # done with the arena's previous contents), 3s+2 (forward rows have landed) and 3s+3 (gradient rows have
+        # landed): absolute numbers, so a rank whose backward pass did not run (nothing of what it received reached
+        # its loss) cannot fall one barrier behind the others for the rest of the run.
+        self.step = 0
         self._flag_ptrs = (C.c_void_p * self.ws)(*[int(p) for p in self.flags_hdl.buffer_ptrs])
 
     def _alloc(self, nbytes):
@@ -418,13 +449,18 @@ class PeerArena:
         if self.grad is None or self.grad.numel() < grad_bytes:
             self.grad, self.grad_hdl = self._alloc(grad_bytes)
 
-    def barrier(self):
+    def begin_step(self):
+        """Start the next exchange: from here on the arena's previous contents (the tensors the previous exchange
+        returned, and its gradient rows) are dead."""
+        self.step += 1
+        self.barrier(1)
+
+    def barrier(self, phase):
         """Stream-ordered barrier over the group: work queued before it on every rank is complete after it."""
         from diff_gaussian_rasterization import _lib
 
-        self.epoch += 1
-        _lib.check(_lib.lib().cgx_peer_barrier(self.ws, self.me, self._flag_ptrs, self.epoch,
-                                               _lib.current_stream_ptr()),
+        epoch = (3 * self.step + phase) & 0xFFFFFFFF
+        _lib.check(_lib.lib().cgx_peer_barrier(self.ws, self.me, self._flag_ptrs, epoch, _lib.current_stream_ptr()),
                    "cgx_peer_barrier")
 
 
@@ -470,7 +506,7 @@ class _GaussianExchangeP2P(torch.autograd.Function):
             for c in cameras:
                 be.pack_p2p(c["params"], c["bounds"], c["H"], c["W"], c["avoid"], c["dst_table"], c["row_offsets"],
                             plan["send_index"], c["workspace"])
-        arena.barrier()                       # every rank's rows have landed
+        arena.barrier(2)                      # every rank's rows have landed
         outs, nondiff = [], []
         f32 = arena.recv.view(torch.float32)
         i32 = arena.recv.view(torch.int32)
@@ -509,6 +545,11 @@ class _GaussianExchangeP2P(torch.autograd.Function):
         ncols = plan["grad_cols"]
         planes = plan["planes"]
         n_out, n_in = (6, 4) if planes else (8, 6)
+        if arena.step != plan["arena_step"]:
+            raise RuntimeError(
+                "cgx.exchange: the backward pass of a peer-to-peer exchange ran after a later exchange of the same "
+                "group had started; the tensors it returned (views of the receive arena) were overwritten.  Keep "
+                "one exchange in flight per group (backward before the next forward), or use transport='collective'")
         owner_base = np.array([int(p) for p in arena.grad_hdl.buffer_ptrs], dtype=np.int64)
         # segment (source i -> me, camera k) sits at row grad_row[i, k] of rank i's send order
         seg_ptr = owner_base[:, None] + plan["grad_row"] * (ncols * 4)                                # (ws, bsz)
@@ -524,7 +565,7 @@ class _GaussianExchangeP2P(torch.autograd.Function):
             else:
                 cot = _dense_cotangents(g, n, dev)
             be.pack_grad_rows_to(seg_ptr[:, k].tolist(), counts.tolist(), ncols, cot)
-        arena.barrier()                       # every rank's gradient rows have landed in their owners' buffers
+        arena.barrier(3)                      # every rank's gradient rows have landed in their owners' buffers
         n_send = plan["n_send"]
         grad_send = arena.grad[: n_send * ncols * 4].view(torch.float32).view(n_send, ncols)
         grads = []
@@ -608,7 +649,7 @@ def all_to_all_communication_final(batched_rasterizers, batched_screenspace_para
     # the barrier "every rank is done with the previous contents of the arenas" does not depend on the sizes: it is
     # queued behind the size read-back and runs while the host lays out the exchange
     gathered, extra = _gather_table(table_dev, bsz * ws, piggyback, group, ws,
-                                    overlap=arena.barrier if arena is not None else None)
+                                    overlap=arena.begin_step if arena is not None else None)
     S = np.ascontiguousarray(gathered.reshape(ws, bsz, ws).transpose(0, 2, 1))     # [src][dst][cam]
     sizes_list = S.tolist()
     my = S[me]                                                       # [dst][cam]
@@ -649,7 +690,7 @@ def all_to_all_communication_final(batched_rasterizers, batched_screenspace_para
         else:
             grad_cols = REC_DIFF if any(flat[6 * k + c].requires_grad for k in range(bsz) for c in (3, 4, 5)) else 9
         stats["bytes_sent_bwd"] = (n_send - self_rows) * grad_cols * 4
-        plan = dict(backend=backend, arena=arena, me=me, ws=ws, S=S, strategies=batched_strategies,
+        plan = dict(backend=backend, arena=arena, arena_step=arena.step, me=me, ws=ws, S=S, strategies=batched_strategies,
                     grad_cols=grad_cols, planes=planes, n_recv=n_recv, cam_base=lay["cam_base"], field_off=field_off,
                     first_row=lay["first_row"], grad_row=grad_row, bounds=bounds, scratch=scratch,
                     send_index=send_index, send_off=send_off, send_ranges=send_ranges, n_send=n_send,

@@ -382,21 +382,24 @@ sort_scatter_direct_kernel(int64_t n, int nblocks, int shift, uint32_t mask, con
 }
 
 __global__ void __launch_bounds__(256)
-tile_ranges_kernel(int64_t L, const uint64_t* __restrict__ keys, uint2* __restrict__ ranges)
+tile_ranges_kernel(int64_t L, uint32_t T, const uint64_t* __restrict__ keys, uint2* __restrict__ ranges)
 {
+    // A tile id beyond the grid can only come from a key nobody emitted (a caller that passed a pair count larger
+    // than the emitted one): such a key never writes, so nothing outside `ranges` is touched.
     const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= L) return;
     const uint32_t currtile = (uint32_t)(keys[idx] >> 32);
-    if (idx == 0)
-        ranges[currtile].x = 0;
-    else {
+    const bool cur_ok = currtile < T;
+    if (idx == 0) {
+        if (cur_ok) ranges[currtile].x = 0;
+    } else {
         const uint32_t prevtile = (uint32_t)(keys[idx - 1] >> 32);
         if (currtile != prevtile) {
-            ranges[prevtile].y = (uint32_t)idx;
-            ranges[currtile].x = (uint32_t)idx;
+            if (prevtile < T) ranges[prevtile].y = (uint32_t)idx;
+            if (cur_ok) ranges[currtile].x = (uint32_t)idx;
         }
     }
-    if (idx == L - 1) ranges[currtile].y = (uint32_t)L;
+    if (idx == L - 1 && cur_ok) ranges[currtile].y = (uint32_t)L;
 }
 
 // ------------------------------------------------------------------------------------------------ distribution
@@ -994,7 +997,7 @@ extern "C" int cgx_tile_ranges(int64_t n, int T, const uint64_t* keys_sorted, ui
     if (e != cudaSuccess) { set_cuda_error(e); return CGX_ECUDA; }
     if (n == 0) return CGX_OK;
     if (!keys_sorted) return CGX_EINVAL;
-    tile_ranges_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(n, keys_sorted, (uint2*)ranges);
+    tile_ranges_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(n, (uint32_t)T, keys_sorted, (uint2*)ranges);
     return check_launch();
 }
 

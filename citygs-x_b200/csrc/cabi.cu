@@ -66,7 +66,17 @@ extern "C" int cgx_block_xy(int* block_x, int* block_y, int* one_dim_block)
 namespace cgx {
 int fetch_render_status(int* out);  // render.cu
 int fetch_peer_status(int* out);    // peer.cu
+int fetch_render_status_async(int* out_pinned, cudaStream_t st);
+int fetch_peer_status_async(int* out_pinned, cudaStream_t st);
 }  // namespace cgx
+
+extern "C" int cgx_device_status_async(int* status_pinned_host2, void* stream)
+{
+    if (!status_pinned_host2) return CGX_EINVAL;
+    int st = cgx::fetch_render_status_async(status_pinned_host2, (cudaStream_t)stream);
+    if (st == CGX_OK) st = cgx::fetch_peer_status_async(status_pinned_host2 + 1, (cudaStream_t)stream);
+    return st;
+}
 
 extern "C" int cgx_device_status(int* status_host, void* stream)
 {

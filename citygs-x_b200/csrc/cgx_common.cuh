@@ -7,6 +7,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include "../../include/cgx_raster.h"
+#include "../../include/cgx_raster_testing.h"
 
 #define CGX_BLOCK_X 16
 #define CGX_BLOCK_Y 16

@@ -15,7 +15,7 @@ struct PeerFlags {
 };
 
 __global__ void __launch_bounds__(PEER_MAX)
-peer_barrier_kernel(PeerFlags flags, int ws, int rank, uint32_t epoch)
+peer_barrier_kernel(PeerFlags flags, int ws, int rank, uint32_t epoch, unsigned long long limit_cycles)
 {
     const int t = threadIdx.x;
     if (t >= ws) return;
@@ -30,12 +30,19 @@ peer_barrier_kernel(PeerFlags flags, int ws, int rank, uint32_t epoch)
         uint32_t v;
         asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
         if ((int32_t)(v - epoch) >= 0) break;
-        if ((unsigned long long)(clock64() - t0) > PEER_WAIT_LIMIT_CYCLES) {
+        if ((unsigned long long)(clock64() - t0) > limit_cycles) {
             atomicExch(&g_peer_status, CGX_ETIMEDOUT);
             break;
         }
     }
     __threadfence_system();
+}
+
+int fetch_peer_status_async(int* out_pinned, cudaStream_t st)
+{
+    cudaError_t e = cudaMemcpyFromSymbolAsync(out_pinned, g_peer_status, sizeof(int), 0, cudaMemcpyDeviceToHost, st);
+    if (e != cudaSuccess) { set_cuda_error(e); return CGX_ECUDA; }
+    return CGX_OK;
 }
 
 int fetch_peer_status(int* out)
@@ -51,14 +58,21 @@ int fetch_peer_status(int* out)
 
 }  // namespace cgx
 
-extern "C" int cgx_peer_barrier(int ws, int rank, uint32_t* const* flag_ptrs, uint32_t epoch, void* stream)
+extern "C" int cgx_peer_barrier_limited(int ws, int rank, uint32_t* const* flag_ptrs, uint32_t epoch,
+                                        unsigned long long wait_limit_cycles, void* stream)
 {
+    if (wait_limit_cycles == 0) wait_limit_cycles = cgx::PEER_WAIT_LIMIT_CYCLES;
     if (ws <= 0 || ws > cgx::PEER_MAX || rank < 0 || rank >= ws || !flag_ptrs) return CGX_EINVAL;
     cgx::PeerFlags f;
     for (int r = 0; r < cgx::PEER_MAX; r++) {
         f.p[r] = r < ws ? flag_ptrs[r] : nullptr;
         if (r < ws && (!f.p[r] || ((uintptr_t)f.p[r] & 3))) return CGX_EINVAL;
     }
-    cgx::peer_barrier_kernel<<<1, cgx::PEER_MAX, 0, (cudaStream_t)stream>>>(f, ws, rank, epoch);
+    cgx::peer_barrier_kernel<<<1, cgx::PEER_MAX, 0, (cudaStream_t)stream>>>(f, ws, rank, epoch, wait_limit_cycles);
     return cgx::check_launch();
+}
+
+extern "C" int cgx_peer_barrier(int ws, int rank, uint32_t* const* flag_ptrs, uint32_t epoch, void* stream)
+{
+    return cgx_peer_barrier_limited(ws, rank, flag_ptrs, epoch, 0ull, stream);
 }

@@ -689,6 +689,12 @@ using namespace cgx;
 extern "C" size_t cgx_render_records_bytes(int P) { return (size_t)(P > 0 ? P : 0) * sizeof(Record); }
 
 namespace cgx {
+int fetch_render_status_async(int* out_pinned, cudaStream_t st)
+{
+    cudaError_t e = cudaMemcpyFromSymbolAsync(out_pinned, g_status, sizeof(int), 0, cudaMemcpyDeviceToHost, st);
+    if (e != cudaSuccess) { set_cuda_error(e); return CGX_ECUDA; }
+    return CGX_OK;
+}
 int fetch_render_status(int* out)
 {
     cudaError_t e = cudaMemcpyFromSymbol(out, g_status, sizeof(int));

@@ -265,7 +265,9 @@ _prefetch_next = 0
 
 
 def _prefetch_key(means2D, radii, local, H, W):
-    return (means2D.data_ptr(), radii.data_ptr(), local.data_ptr(), means2D.shape[0], H, W, means2D.device.index)
+    # the version counters make a count taken before an in-place update of its inputs unfindable
+    return (means2D.data_ptr(), radii.data_ptr(), local.data_ptr(), means2D.shape[0], H, W, means2D.device.index,
+            means2D._version, radii._version, local._version)
 
 
 def prefetch_num_rendered(image_height, image_width, means2D, radii, compute_locally):
@@ -378,7 +380,8 @@ def render_gaussians(background, image_height, image_width, means2D, depths, rad
                                int(bool(render_geo)), _ptr(g["records"]), _ptr(im["accum_alpha"]),
                                _ptr(im["n_contrib"]), _ptr(im["n_contrib2loss"]), _ptr(out_color), _ptr(out_observe),
                                _ptr(out_all_map), _ptr(out_plane_depth), _ptr(n_render), _ptr(n_consider),
-                               _ptr(n_contrib), st, info=dict(P=P, R=R, HW=H * W))
+                               _ptr(n_contrib), st,
+                               info=dict(P=P, R=R, HW=H * W, local=local, n_consider=n_consider, n_contrib=n_contrib))
         if stats is not None:
             ev1.record()
             stats["forward_render_time"] = _EventMs([(ev0, ev1)])
@@ -422,6 +425,7 @@ def render_gaussians_backward_2d(background, tan_fovx, tan_fovy, all_map_pixels,
         b = binning_layout(R).views(binningBuffer)
         im = image_layout(W * H, TX * TY).views(imageBuffer)
         stats = _stats(args)
+        local = _cuda_any(compute_locally, "compute_locally")
         with torch.cuda.device(dev):
             st = _stream()
             if stats is not None:
@@ -431,12 +435,13 @@ def render_gaussians_backward_2d(background, tan_fovx, tan_fovy, all_map_pixels,
             _call("cgx_render_bwd", l.cgx_render_bwd, P, W, H, float(tan_fovx), float(tan_fovy), _ptr(im["ranges"]), _ptr(b["point_list"]),
                                    _ptr(_cuda_f32(background, "background")), _ptr(g["records"]),
                                    _ptr(_cuda_f32(all_map_pixels, "all_map_pixels")), _ptr(im["accum_alpha"]),
-                                   _ptr(im["n_contrib"]), _ptr(_cuda_any(compute_locally, "compute_locally")),
+                                   _ptr(im["n_contrib"]), _ptr(local),
                                    _ptr(_cuda_f32(dL_dout_color, "dL_dout_color")),
                                    _ptr(_cuda_f32(dL_dout_all_map, "dL_dout_all_map")),
                                    _ptr(_cuda_f32(dL_dout_plane_depth, "dL_dout_plane_depth")),
                                    int(bool(render_geo)), _ptr(dL_dmeans2D), _ptr(dL_dmeans2D_abs),
-                                   _ptr(dL_dconic_opacity), _ptr(dL_dcolors), _ptr(dL_dall_map), st, info=dict(P=P, R=R, HW=H * W))
+                                   _ptr(dL_dconic_opacity), _ptr(dL_dcolors), _ptr(dL_dall_map), st,
+                                   info=dict(P=P, R=R, HW=H * W, local=local))
             if stats is not None:
                 ev1.record()
                 stats["backward_render_time"] = _EventMs([(ev0, ev1)])

@@ -29,7 +29,8 @@ def sources():
 def build(force: bool = False, verbose: bool = False) -> Path:
     """Compile the CUDA sources into lib/libcgx_raster.so when out of date."""
     srcs = sources()
-    deps = srcs + [CSRC / "cgx_common.cuh", ROOT.parent / "include" / "cgx_raster.h"]
+    deps = srcs + [CSRC / "cgx_common.cuh", ROOT.parent / "include" / "cgx_raster.h",
+                   ROOT.parent / "include" / "cgx_raster_testing.h"]
     newest = max(p.stat().st_mtime for p in deps if p.exists())
     if not force and SO.exists() and SO.stat().st_mtime >= newest:
         return SO
@@ -78,6 +79,7 @@ SIGNATURES = {
     "cgx_pack_grad_rows_to": (_i, [_i, _vp, _vp, _i] + [_vp] * 7),
     "cgx_unpack_grad_add_cols": (_i, [_i, _vp, _vp, _i] + [_vp] * 9),
     "cgx_peer_barrier": (_i, [_i, _i, _vp, C.c_uint32, _vp]),
+    "cgx_peer_barrier_limited": (_i, [_i, _i, _vp, C.c_uint32, C.c_uint64, _vp]),
     "cgx_bin_workspace_bytes": (_sz, [_i]),
     "cgx_bin_count_scan": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "cgx_emit_keys": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _vp, _vp]),
@@ -93,6 +95,7 @@ SIGNATURES = {
     "cgx_tile_stats": (_i, [_i, _i] + [_vp] * 8),
     "cgx_render_bwd": (_i, [_i, _i, _i, _f, _f] + [_vp] * 11 + [_i] + [_vp] * 6),
     "cgx_device_status": (_i, [_vp, _vp]),
+    "cgx_device_status_async": (_i, [_vp, _vp]),
     "cgx_set_render_variant": (_i, [_i]),
 }
 

@@ -292,6 +292,11 @@ int cgx_unpack_grad_add_cols(int n_ranges, const int64_t* range_start, const int
  * queued before its own call is complete and visible.  The wait is bounded (about 2 s): on expiry the device
  * status word is set (cgx_device_status) and the kernel returns. */
 int cgx_peer_barrier(int ws, int rank, uint32_t* const* flag_ptrs, uint32_t epoch, void* stream);
+/* The same barrier with the caller's own bound on the wait, in SM clock cycles (0 = the default of about 2 s).
+ * A rank that knows its peers are a few microseconds away can fail fast; a test can watch the wait run out:
+ * when a peer never signals, the kernel returns after the limit and cgx_device_status reports CGX_ETIMEDOUT. */
+int cgx_peer_barrier_limited(int ws, int rank, uint32_t* const* flag_ptrs, uint32_t epoch,
+                             unsigned long long wait_limit_cycles, void* stream);
 
 /* ------------------------------------------------------------------ binning */
 
@@ -322,9 +327,6 @@ size_t cgx_sort_workspace_bytes(int64_t n);
 int cgx_sort_pairs(int64_t n, int end_bit, uint64_t* keys_in, uint32_t* values_in, uint64_t* keys_out,
                    uint32_t* values_out, void* workspace, size_t workspace_bytes, void* stream);
 
-/* Scatter strategy of the sort, for A/B timing and tests: -1 (default) chooses by size (unstaged while both
- * ping-pong buffers fit in L2, staged above), 0 always staged, 1 always unstaged.  Results are identical. */
-int cgx_set_sort_variant(int variant);
 
 /* No counterpart in the reference.  Same sort as cgx_sort_pairs for callers that may not allocate device
  * memory (an engine with a memory budget fixed at start-up, a plugin whose host has frozen the CUDA pools, a
@@ -391,12 +393,11 @@ int cgx_render_bwd(int P, int W, int H, float tanfovx, float tanfovy, const uint
  * synchronise-and-throw (RAST/cuda_rasterizer/auxiliary.h:220-227); nothing ever traps. */
 int cgx_device_status(int* status_host, void* stream);
 
-/* A/B switches of the blending kernels (default 1 = culling only), for timing and tests:
- *   bit 0  per-warp culling of each batch before blending (forward and backward; results bit-identical);
- *   bit 1  backward: the per-channel "accumulated behind" recurrences contracted with the pixel cotangent
- *          (faster; leaves the 1e-3 gradient parity band on pixels whose plane-depth cotangent blows up);
- *   bit 2  backward: visits with one or two contributing pixels issue their atomics directly (measured slower). */
-int cgx_set_render_variant(int variant);
+/* The same two status words without waiting: queues their copies on `stream` into status_pinned_host2[0..1]
+ * (page-locked host memory: blending kernels, peer barrier).  The caller looks at them after a synchronisation
+ * it performs anyway (0 = ok); the words are not cleared (cgx_device_status clears them). */
+int cgx_device_status_async(int* status_pinned_host2, void* stream);
+
 
 #ifdef __cplusplus
 }

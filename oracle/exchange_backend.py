@@ -1,6 +1,8 @@
-"""Test-only CPU packing backend for cgx.exchange: selection by the oracle's mask, packing by tensor indexing.
-It lets the gloo tests exercise the exchange's host logic (sizes, layout, collectives, autograd, ordering) without
-a GPU.  The shipped package never imports this file."""
+"""CPU packing backend for cgx.exchange: selection by the oracle's mask, packing by tensor indexing.
+
+TEST INFRASTRUCTURE, like the rest of this directory: it lets the gloo tests exercise the exchange's host logic
+(sizes, layout, collectives, autograd, ordering) without a GPU, and it is what the benchmark's CPU-baseline leg
+times for the two-rank gloo configuration.  The shipped package never imports this file."""
 import torch
 
 from oracle import cpu_raster as O
@@ -34,12 +36,10 @@ class OracleBackend:
                 continue
             idx = send_index[a:b].long()
             g = grad_rows[a:b]
-            d_m2.index_add_(0, idx, g[:, 0:2])
-            d_rgb.index_add_(0, idx, g[:, 2:5])
-            d_co.index_add_(0, idx, g[:, 5:9])
-            d_m3.index_add_(0, idx, g[:, 9:12])
-            d_sc.index_add_(0, idx, g[:, 12:15])
-            d_rot.index_add_(0, idx, g[:, 15:19])
+            for d, (lo, hi) in zip((d_m2, d_rgb, d_co, d_m3, d_sc, d_rot),
+                                   ((0, 2), (2, 5), (5, 9), (9, 12), (12, 15), (15, 19))):
+                if d is not None:          # inputs that need no gradient get none
+                    d.index_add_(0, idx, g[:, lo:hi])
 
     def unpack_rows(self, segments, recv, recv_aux, outs):
         rows = torch.cat([recv[a:a + c] for a, c in segments]) if segments else recv[:0]

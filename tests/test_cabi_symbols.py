@@ -6,10 +6,14 @@ from pathlib import Path
 ROOT = Path(__file__).resolve().parent.parent
 
 
-def declared_symbols():
-    text = (ROOT / "include" / "cgx_raster.h").read_text()
-    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
-    return sorted(set(re.findall(r"\b(cgx_\w+)\s*\(", text)))
+def declared_symbols(headers=("cgx_raster.h", "cgx_raster_testing.h")):
+    """Entry points of the drop-in boundary (cgx_raster.h) and of the test-only switches (cgx_raster_testing.h)."""
+    names = set()
+    for h in headers:
+        text = (ROOT / "include" / h).read_text()
+        text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+        names |= set(re.findall(r"\b(cgx_\w+)\s*\(", text))
+    return sorted(names)
 
 
 def test_header_symbols_are_exported():
@@ -27,6 +31,8 @@ def test_binding_table_matches_header():
     from diff_gaussian_rasterization import _lib
 
     assert sorted(_lib.SIGNATURES) == declared_symbols()
+    # the public header holds no process-wide switches: those live in the test-only header
+    assert not [n for n in declared_symbols(("cgx_raster.h",)) if "_set_" in n]
 
 
 def test_host_only_entry_points():

@@ -46,7 +46,7 @@ def _worker(rank, ws, port, out_dir):
     dist.init_process_group("gloo", rank=rank, world_size=ws)
     try:
         import util
-        from cpu_backend import OracleBackend
+        from oracle.exchange_backend import OracleBackend
         from cgx import exchange
         from cgx import workload_division as WD
         from oracle import cpu_raster as O
