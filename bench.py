@@ -61,6 +61,8 @@ def parse_args():
     ap.add_argument("--no-parity", action="store_true", help="N>1: skip the correctness run on the reduced scene")
     ap.add_argument("--no-stage-events", action="store_true", help="do not bracket library calls with CUDA events")
     ap.add_argument("--no-clocks", action="store_true", help="do not sample nvidia-smi during the run")
+    ap.add_argument("--render-variant", type=int, default=None,
+                    help="A/B timing: select a blending kernel variant through the library's test-only switch")
     ap.add_argument("--cpu-sample-gaussians", type=int, default=None)
     ap.add_argument("--kernel-table", action="store_true",
                     help="after the measurement, profile 3 more steps with torch.profiler on every rank and print "
@@ -642,6 +644,8 @@ def main():
 
     from diff_gaussian_rasterization import _C, _lib
     lib = _lib.lib()
+    if a.render_variant is not None:
+        lib.cgx_set_render_variant(a.render_variant)
 
     def barrier():
         if world > 1:

@@ -275,7 +275,7 @@ def _queue_status_read():
 
     stage = _pinned.get("status")
     if stage is None:
-        stage = _pinned["status"] = torch.zeros(2, dtype=torch.int32).pin_memory()
+        stage = _pinned["status"] = torch.zeros(4, dtype=torch.int32).pin_memory()
     _lib.check(_lib.lib().cgx_device_status_async(C.c_void_p(stage.data_ptr()), _lib.current_stream_ptr()),
                "cgx_device_status_async")
     return stage
@@ -284,12 +284,13 @@ def _queue_status_read():
 def _raise_on_device_status(stage):
     """After the synchronisation: a wait that ran out earlier on this stream (a peer that never signalled, a bulk
     copy that never completed) means rows may not have landed, so the step must not go on silently."""
-    if stage[0].item() or stage[1].item():
+    if stage[0].item() or stage[1].item() or stage[2].item():
         from diff_gaussian_rasterization import _lib
 
         code = C.c_int(0)
         _lib.lib().cgx_device_status(C.byref(code), _lib.current_stream_ptr())      # reads and clears
-        where = "the blending kernels" if stage[0].item() else "the peer barrier of the Gaussian exchange"
+        where = "the blending kernels" if stage[0].item() else \
+            ("the peer barrier of the Gaussian exchange" if stage[1].item() else "the sort's look-back")
         raise _lib.CgxError(_lib.CGX_ETIMEDOUT, f"a bounded device-side wait in {where}")
 
 

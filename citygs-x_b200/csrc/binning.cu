@@ -381,6 +381,173 @@ sort_scatter_direct_kernel(int64_t n, int nblocks, int shift, uint32_t mask, con
     }
 }
 
+// ------------------------------------------------------------------------------------------------ one-sweep sort
+// One read of the keys builds the digit histograms of ALL passes (global totals only).  Each pass is then ONE
+// kernel: a CTA takes the next tile (a ticket, so every tile it will ever wait for is already running), ranks its
+// pairs by digit on chip (match.any ballots, per-warp counters), publishes its per-digit counts, finds the number
+// of same-digit pairs in earlier tiles by decoupled look-back over the published counts, and scatters.  Per pass
+// the pairs are read once and written once; nothing else touches HBM but 1 KB of counts per tile.
+// The look-back is the only place a CTA waits for another one; the wait is bounded (clock64) and sets the device
+// status word when it gives up.
+constexpr int OS_THREADS = 256;
+#ifndef CGX_OS_ITEMS
+#define CGX_OS_ITEMS 16
+#endif
+constexpr int OS_ITEMS = CGX_OS_ITEMS;
+constexpr int OS_TILE = OS_THREADS * OS_ITEMS;
+constexpr int OS_WARPS = OS_THREADS / 32;
+constexpr int OS_MAX_PASSES = 8;
+constexpr uint32_t OS_FLAG_AGG = 1u << 30;      // value = pairs of this digit in this tile
+constexpr uint32_t OS_FLAG_PREFIX = 2u << 30;   // value = pairs of this digit in this tile and all earlier ones
+constexpr uint32_t OS_VALUE_MASK = (1u << 30) - 1u;
+constexpr unsigned long long OS_WAIT_LIMIT_CYCLES = 1ull << 28;   // ~0.14 s at B200 clocks
+
+__device__ int g_sort_status = 0;   // CGX_ETIMEDOUT when a look-back wait gave up
+
+__device__ __forceinline__ uint32_t ld_relaxed_gpu(const uint32_t* p)
+{
+    uint32_t v;
+    asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_relaxed_gpu(uint32_t* p, uint32_t v)
+{
+    asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+// ghist[pass * RADIX + digit] += number of keys with that digit in that pass.
+__global__ void __launch_bounds__(OS_THREADS)
+os_hist_kernel(int64_t n, int passes, int end_bit, const uint64_t* __restrict__ keys, uint32_t* __restrict__ ghist)
+{
+    __shared__ uint32_t s_hist[OS_MAX_PASSES * RADIX];
+    for (int i = threadIdx.x; i < passes * RADIX; i += OS_THREADS) s_hist[i] = 0;
+    __syncthreads();
+    const int64_t stride = (int64_t)gridDim.x * OS_THREADS;
+    const int lane = threadIdx.x & 31;
+    // i0 is the same for all lanes of a warp, so every lane takes part in every vote
+    for (int64_t i0 = (int64_t)blockIdx.x * OS_THREADS + (threadIdx.x & ~31); i0 < n; i0 += stride) {
+        const bool valid = i0 + lane < n;
+        const uint64_t k = valid ? keys[i0 + lane] : 0ull;
+        for (int p = 0; p < passes; p++) {
+            const int shift = p * RADIX_BITS;
+            const int bits = min(RADIX_BITS, end_bit - shift);
+            const uint32_t d = valid ? ((uint32_t)(k >> shift) & ((1u << bits) - 1u)) : (uint32_t)RADIX;
+            // lanes of a warp often share a digit in the high passes (few tiles, few exponents): one add per group
+            const uint32_t peers = __match_any_sync(0xffffffffu, d);
+            if (valid && lane == __ffs(peers) - 1) atomicAdd(&s_hist[p * RADIX + d], (uint32_t)__popc(peers));
+        }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < passes * RADIX; i += OS_THREADS) {
+        const uint32_t c = s_hist[i];
+        if (c) atomicAdd(&ghist[i], c);
+    }
+}
+
+__global__ void __launch_bounds__(OS_THREADS, 2)
+os_pass_kernel(int64_t n, int shift, uint32_t mask, const uint64_t* __restrict__ keys_in,
+               const uint32_t* __restrict__ vals_in, uint64_t* __restrict__ keys_out, uint32_t* __restrict__ vals_out,
+               const uint32_t* __restrict__ ghist, uint32_t* __restrict__ ticket, uint32_t* __restrict__ status,
+               unsigned long long wait_limit)
+{
+    __shared__ uint32_t s_warp_hist[OS_WARPS][RADIX];  // per-warp digit counters, then exclusive offsets over warps
+    __shared__ uint32_t s_base[RADIX];                 // global position of the tile's first pair of each digit
+    __shared__ uint32_t s_w[OS_WARPS];
+    __shared__ uint32_t s_tile;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (threadIdx.x == 0) s_tile = atomicAdd(ticket, 1u);
+    for (int i = threadIdx.x; i < OS_WARPS * RADIX; i += OS_THREADS) (&s_warp_hist[0][0])[i] = 0;
+    __syncthreads();
+    const uint32_t tile = s_tile;
+    const int64_t tile_base = (int64_t)tile * OS_TILE;
+    if (tile_base >= n) return;                        // uniform over the CTA (cannot happen with an exact grid)
+    const int64_t chunk = tile_base + (int64_t)warp * (32 * OS_ITEMS);
+
+    uint64_t key[OS_ITEMS];
+    uint16_t rank[OS_ITEMS];
+#pragma unroll
+    for (int r = 0; r < OS_ITEMS; r++) {
+        const int64_t i = chunk + r * 32 + lane;
+        key[r] = i < n ? keys_in[i] : ~0ull;
+    }
+#pragma unroll
+    for (int r = 0; r < OS_ITEMS; r++) {
+        const int64_t i = chunk + r * 32 + lane;
+        const bool valid = i < n;
+        // invalid tail lanes take a digit of their own (RADIX) so they never match a real digit
+        const uint32_t d = valid ? ((uint32_t)(key[r] >> shift) & mask) : (uint32_t)RADIX;
+        const uint32_t peers = __match_any_sync(0xffffffffu, d);
+        const uint32_t before = __popc(peers & ((1u << lane) - 1u));
+        uint32_t prev = 0;
+        if (valid && before == 0) {  // first lane of its digit group updates the warp counter
+            prev = s_warp_hist[warp][d];
+            s_warp_hist[warp][d] = prev + __popc(peers);
+        }
+        prev = __shfl_sync(0xffffffffu, prev, __ffs(peers) - 1);
+        rank[r] = (uint16_t)(prev + before);
+        __syncwarp();
+    }
+    __syncthreads();
+
+    bool failed = false;
+    {
+        const int d = threadIdx.x;  // OS_THREADS == RADIX
+        uint32_t cnt = 0;
+#pragma unroll
+        for (int w = 0; w < OS_WARPS; w++) {
+            const uint32_t c = s_warp_hist[w][d];
+            s_warp_hist[w][d] = cnt;
+            cnt += c;
+        }
+        uint32_t* my_status = status + (size_t)tile * RADIX + d;
+        st_relaxed_gpu(my_status, (tile == 0 ? OS_FLAG_PREFIX : OS_FLAG_AGG) | cnt);
+        // first pair of digit d in the whole array: totals of the smaller digits
+        const uint32_t t = ghist[d];
+        const uint32_t incl = warp_incl_scan(t);
+        if (lane == 31) s_w[warp] = incl;
+        __syncthreads();
+        uint32_t digit_base = incl - t;
+#pragma unroll
+        for (int w = 0; w < OS_WARPS; w++)
+            if (w < warp) digit_base += s_w[w];
+        // pairs of digit d in earlier tiles: walk back until a tile that already knows its inclusive prefix
+        uint32_t excl = 0;
+        if (tile > 0) {
+            const long long t0 = clock64();
+            for (int64_t b = (int64_t)tile - 1; b >= 0; b--) {
+                const uint32_t* p = status + (size_t)b * RADIX + d;
+                uint32_t v = ld_relaxed_gpu(p);
+                while ((v >> 30) == 0) {
+                    if ((unsigned long long)(clock64() - t0) > wait_limit) {
+                        failed = true;
+                        break;
+                    }
+                    v = ld_relaxed_gpu(p);
+                }
+                if (failed) break;
+                excl += v & OS_VALUE_MASK;
+                if (v & OS_FLAG_PREFIX) break;
+            }
+            if (!failed) st_relaxed_gpu(my_status, OS_FLAG_PREFIX | (excl + cnt));
+        }
+        s_base[d] = digit_base + excl;
+    }
+    if (__syncthreads_or(failed)) {
+        if (threadIdx.x == 0) atomicExch(&g_sort_status, CGX_ETIMEDOUT);
+        return;      // nothing is scattered: the output of this tile is undefined and the status word says so
+    }
+#pragma unroll
+    for (int r = 0; r < OS_ITEMS; r++) {
+        const int64_t i = chunk + r * 32 + lane;
+        if (i < n) {
+            const uint32_t d = (uint32_t)(key[r] >> shift) & mask;
+            const size_t dst = (size_t)s_base[d] + s_warp_hist[warp][d] + rank[r];
+            keys_out[dst] = key[r];
+            vals_out[dst] = vals_in[i];
+        }
+    }
+}
+
 __global__ void __launch_bounds__(256)
 tile_ranges_kernel(int64_t L, uint32_t T, const uint64_t* __restrict__ keys, uint2* __restrict__ ranges)
 {
@@ -922,7 +1089,8 @@ extern "C" int cgx_emit_keys(int P, int W, int H, const int32_t* radii, const fl
     return check_launch();
 }
 
-static int g_sort_variant = -1;  // -1: by size; 0: staged scatter; 1: unstaged scatter
+static int g_sort_variant = -1;  // test-only switch: -1 one-sweep (default); 0 three-kernel passes, staged scatter;
+                                 // 1 three-kernel passes, unstaged scatter
 
 extern "C" int cgx_set_sort_variant(int variant)
 {
@@ -930,20 +1098,80 @@ extern "C" int cgx_set_sort_variant(int variant)
     return CGX_OK;
 }
 
-extern "C" size_t cgx_sort_workspace_bytes(int64_t n)
+extern "C" int cgx_sort_passes(int end_bit) { return end_bit <= 0 ? 0 : (end_bit + RADIX_BITS - 1) / RADIX_BITS; }
+
+static size_t legacy_sort_bytes(int64_t n)
 {
     const size_t nblocks = ((size_t)(n > 0 ? n : 1) + SORT_TILE - 1) / SORT_TILE;
     return align_up(nblocks * RADIX * sizeof(uint32_t), 256) + align_up(RADIX * sizeof(uint32_t), 256);
 }
 
-extern "C" int cgx_sort_pairs(int64_t n, int end_bit, uint64_t* keys_in, uint32_t* values_in, uint64_t* keys_out,
-                              uint32_t* values_out, void* workspace, size_t workspace_bytes, void* stream)
+static size_t onesweep_head_bytes() { return align_up(OS_MAX_PASSES * RADIX * sizeof(uint32_t), 256) + 256; }
+
+static size_t onesweep_sort_bytes(int64_t n, int passes)
 {
-    if (n < 0 || end_bit < 0 || end_bit > 64 || n > 0x7fffffffLL) return CGX_EINVAL;
-    if (n == 0) return CGX_OK;
-    if (!keys_in || !values_in || !keys_out || !values_out || !workspace) return CGX_EINVAL;
-    if (workspace_bytes < cgx_sort_workspace_bytes(n)) return CGX_ENOMEM;
-    cudaStream_t st = (cudaStream_t)stream;
+    const size_t ntiles = ((size_t)(n > 0 ? n : 1) + OS_TILE - 1) / OS_TILE;
+    return onesweep_head_bytes() + (size_t)passes * ntiles * RADIX * sizeof(uint32_t);
+}
+
+extern "C" size_t cgx_sort_workspace_bytes(int64_t n)
+{
+    const size_t a = legacy_sort_bytes(n), b = onesweep_sort_bytes(n, OS_MAX_PASSES);
+    return a > b ? a : b;
+}
+
+namespace cgx {
+int fetch_sort_status_async(int* out_pinned, cudaStream_t st)
+{
+    cudaError_t e = cudaMemcpyFromSymbolAsync(out_pinned, g_sort_status, sizeof(int), 0, cudaMemcpyDeviceToHost, st);
+    if (e != cudaSuccess) { set_cuda_error(e); return CGX_ECUDA; }
+    return CGX_OK;
+}
+int fetch_sort_status(int* out)
+{
+    cudaError_t e = cudaMemcpyFromSymbol(out, g_sort_status, sizeof(int));
+    if (e != cudaSuccess) { set_cuda_error(e); return CGX_ECUDA; }
+    if (*out != 0) {
+        int zero = 0;
+        cudaMemcpyToSymbol(g_sort_status, &zero, sizeof(int));
+    }
+    return CGX_OK;
+}
+}  // namespace cgx
+
+// The pairs start in (ka, va).  After `passes` passes they are in (ka, va) when `passes` is even, else in (kb, vb).
+// variant: see g_sort_variant; the one-sweep path needs onesweep_sort_bytes(n, passes) of workspace.
+static int sort_passes_run(int variant, int64_t n, int end_bit, uint64_t* ka, uint32_t* va, uint64_t* kb, uint32_t* vb,
+                           void* workspace, size_t workspace_bytes, unsigned long long wait_limit, cudaStream_t st)
+{
+    const int passes = cgx_sort_passes(end_bit);
+    if (passes == 0) return CGX_OK;
+    uint64_t *kin = ka, *kout = kb;
+    uint32_t *vin = va, *vout = vb;
+    const bool onesweep = variant < 0 && passes <= OS_MAX_PASSES && n < ((int64_t)1 << 30) &&
+                          workspace_bytes >= onesweep_sort_bytes(n, passes);
+    if (onesweep) {
+        const int ntiles = (int)((n + OS_TILE - 1) / OS_TILE);
+        uint32_t* ghist = (uint32_t*)workspace;
+        uint32_t* tickets = (uint32_t*)((char*)workspace + align_up(OS_MAX_PASSES * RADIX * sizeof(uint32_t), 256));
+        uint32_t* status = (uint32_t*)((char*)workspace + onesweep_head_bytes());
+        cudaError_t e = cudaMemsetAsync(workspace, 0, onesweep_sort_bytes(n, passes), st);
+        if (e != cudaSuccess) { set_cuda_error(e); return CGX_ECUDA; }
+        const int hist_grid = ntiles < 148 * 8 ? ntiles : 148 * 8;
+        os_hist_kernel<<<hist_grid, OS_THREADS, 0, st>>>(n, passes, end_bit, kin, ghist);
+        for (int p = 0; p < passes; p++) {
+            const int shift = p * RADIX_BITS;
+            const int bits = (end_bit - shift) < RADIX_BITS ? (end_bit - shift) : RADIX_BITS;
+            os_pass_kernel<<<ntiles, OS_THREADS, 0, st>>>(n, shift, (1u << bits) - 1u, kin, vin, kout, vout,
+                                                         ghist + p * RADIX, tickets + p,
+                                                         status + (size_t)p * ntiles * RADIX,
+                                                         wait_limit ? wait_limit : OS_WAIT_LIMIT_CYCLES);
+            uint64_t* tk = kin; kin = kout; kout = tk;
+            uint32_t* tv = vin; vin = vout; vout = tv;
+        }
+        return check_launch(1 + passes);
+    }
+    if (workspace_bytes < legacy_sort_bytes(n)) return CGX_ENOMEM;
     {
         // opt in to > 48 KB of dynamic shared memory (per device, cheap and idempotent)
         cudaError_t e = cudaFuncSetAttribute(sort_scatter_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SORT_SMEM);
@@ -951,26 +1179,9 @@ extern "C" int cgx_sort_pairs(int64_t n, int end_bit, uint64_t* keys_in, uint32_
     }
     const int nblocks = (int)((n + SORT_TILE - 1) / SORT_TILE);
     // both ping-pong buffers in L2 -> unstaged scatter; otherwise stage each tile so digit runs leave as bursts
-    const bool direct = g_sort_variant == 1 || (g_sort_variant < 0 && n * 24 <= (int64_t)96 << 20);
+    const bool direct = variant == 1 || (variant != 0 && n * 24 <= (int64_t)96 << 20);
     uint32_t* table = (uint32_t*)workspace;
     uint32_t* totals = (uint32_t*)((char*)workspace + align_up((size_t)nblocks * RADIX * sizeof(uint32_t), 256));
-    int passes = (end_bit + RADIX_BITS - 1) / RADIX_BITS;
-    // The result must land in keys_out: with an odd number of passes start from keys_in, otherwise copy first.
-    uint64_t* kin = keys_in;
-    uint32_t* vin = values_in;
-    uint64_t* kout = keys_out;
-    uint32_t* vout = values_out;
-    if (passes == 0) {
-        cudaMemcpyAsync(keys_out, keys_in, n * sizeof(uint64_t), cudaMemcpyDeviceToDevice, st);
-        cudaMemcpyAsync(values_out, values_in, n * sizeof(uint32_t), cudaMemcpyDeviceToDevice, st);
-        return check_launch(0);
-    }
-    if (passes % 2 == 0) {
-        // even: in -> out -> in ... ends in `in`; swap roles by first moving the data to `out`
-        cudaMemcpyAsync(keys_out, keys_in, n * sizeof(uint64_t), cudaMemcpyDeviceToDevice, st);
-        cudaMemcpyAsync(values_out, values_in, n * sizeof(uint32_t), cudaMemcpyDeviceToDevice, st);
-        kin = keys_out; vin = values_out; kout = keys_in; vout = values_in;
-    }
     for (int p = 0; p < passes; p++) {
         const int shift = p * RADIX_BITS;
         const int bits = (end_bit - shift) < RADIX_BITS ? (end_bit - shift) : RADIX_BITS;
@@ -987,6 +1198,51 @@ extern "C" int cgx_sort_pairs(int64_t n, int end_bit, uint64_t* keys_in, uint32_
         uint32_t* tv = vin; vin = vout; vout = tv;
     }
     return check_launch(3 * passes);
+}
+
+static int sort_pairs_into_out(int variant, int64_t n, int end_bit, uint64_t* keys_in, uint32_t* values_in,
+                               uint64_t* keys_out, uint32_t* values_out, void* workspace, size_t workspace_bytes,
+                               void* stream)
+{
+    if (n < 0 || end_bit < 0 || end_bit > 64 || n > 0x7fffffffLL) return CGX_EINVAL;
+    if (n == 0) return CGX_OK;
+    if (!keys_in || !values_in || !keys_out || !values_out || !workspace) return CGX_EINVAL;
+    cudaStream_t st = (cudaStream_t)stream;
+    const int passes = cgx_sort_passes(end_bit);
+    if (passes % 2 == 0) {
+        // an even number of passes ends where it started: start from `out` (callers that own both buffers avoid
+        // this copy with cgx_sort_pairs_pingpong)
+        cudaMemcpyAsync(keys_out, keys_in, n * sizeof(uint64_t), cudaMemcpyDeviceToDevice, st);
+        cudaMemcpyAsync(values_out, values_in, n * sizeof(uint32_t), cudaMemcpyDeviceToDevice, st);
+        if (passes == 0) return check_launch(0);
+        return sort_passes_run(variant, n, end_bit, keys_out, values_out, keys_in, values_in, workspace,
+                               workspace_bytes, 0ull, st);
+    }
+    return sort_passes_run(variant, n, end_bit, keys_in, values_in, keys_out, values_out, workspace, workspace_bytes,
+                           0ull, st);
+}
+
+extern "C" int cgx_sort_pairs(int64_t n, int end_bit, uint64_t* keys_in, uint32_t* values_in, uint64_t* keys_out,
+                              uint32_t* values_out, void* workspace, size_t workspace_bytes, void* stream)
+{
+    if (n > 0 && workspace && workspace_bytes < legacy_sort_bytes(n) &&
+        workspace_bytes < onesweep_sort_bytes(n, cgx_sort_passes(end_bit)))
+        return CGX_ENOMEM;
+    return sort_pairs_into_out(g_sort_variant, n, end_bit, keys_in, values_in, keys_out, values_out, workspace,
+                               workspace_bytes, stream);
+}
+
+extern "C" int cgx_sort_pairs_pingpong(int64_t n, int end_bit, uint64_t* keys_a, uint32_t* values_a, uint64_t* keys_b,
+                                       uint32_t* values_b, void* workspace, size_t workspace_bytes,
+                                       unsigned long long wait_limit_cycles, void* stream)
+{
+    if (n < 0 || end_bit < 0 || end_bit > 64 || n > 0x7fffffffLL) return CGX_EINVAL;
+    if (n == 0) return CGX_OK;
+    if (!keys_a || !values_a || !keys_b || !values_b || !workspace) return CGX_EINVAL;
+    if (workspace_bytes < legacy_sort_bytes(n) && workspace_bytes < onesweep_sort_bytes(n, cgx_sort_passes(end_bit)))
+        return CGX_ENOMEM;
+    return sort_passes_run(g_sort_variant, n, end_bit, keys_a, values_a, keys_b, values_b, workspace, workspace_bytes,
+                           wait_limit_cycles, (cudaStream_t)stream);
 }
 
 extern "C" int cgx_tile_ranges(int64_t n, int T, const uint64_t* keys_sorted, uint32_t* ranges, void* stream)
@@ -1334,7 +1590,9 @@ extern "C" int cgx_sort_pairs_static(int64_t n, int end_bit, uint64_t* keys_in, 
     void* scratch = nullptr;
     const int st = sort_static_scratch_ptr(&scratch);
     if (st != CGX_OK) return st;
-    return cgx_sort_pairs(n, end_bit, keys_in, values_in, keys_out, values_out, scratch, cgx::SORT_STATIC_BYTES, stream);
+    // the fixed scratch is sized for the three-kernel passes (digit tables only)
+    return sort_pairs_into_out(g_sort_variant < 0 ? 2 : g_sort_variant, n, end_bit, keys_in, values_in, keys_out, values_out,
+                               scratch, cgx::SORT_STATIC_BYTES, stream);
 }
 
 extern "C" int cgx_unpack_grad_add_cols(int n_ranges, const int64_t* range_start, const int64_t* range_stop, int ncols,

@@ -66,15 +66,19 @@ extern "C" int cgx_block_xy(int* block_x, int* block_y, int* one_dim_block)
 namespace cgx {
 int fetch_render_status(int* out);  // render.cu
 int fetch_peer_status(int* out);    // peer.cu
+int fetch_sort_status(int* out);    // binning.cu
 int fetch_render_status_async(int* out_pinned, cudaStream_t st);
 int fetch_peer_status_async(int* out_pinned, cudaStream_t st);
+int fetch_sort_status_async(int* out_pinned, cudaStream_t st);
 }  // namespace cgx
 
-extern "C" int cgx_device_status_async(int* status_pinned_host2, void* stream)
+extern "C" int cgx_device_status_async(int* status_pinned_host4, void* stream)
 {
-    if (!status_pinned_host2) return CGX_EINVAL;
-    int st = cgx::fetch_render_status_async(status_pinned_host2, (cudaStream_t)stream);
-    if (st == CGX_OK) st = cgx::fetch_peer_status_async(status_pinned_host2 + 1, (cudaStream_t)stream);
+    if (!status_pinned_host4) return CGX_EINVAL;
+    int st = cgx::fetch_render_status_async(status_pinned_host4, (cudaStream_t)stream);
+    if (st == CGX_OK) st = cgx::fetch_peer_status_async(status_pinned_host4 + 1, (cudaStream_t)stream);
+    if (st == CGX_OK) st = cgx::fetch_sort_status_async(status_pinned_host4 + 2, (cudaStream_t)stream);
+    status_pinned_host4[3] = 0;
     return st;
 }
 
@@ -83,10 +87,11 @@ extern "C" int cgx_device_status(int* status_host, void* stream)
     if (!status_host) return CGX_EINVAL;
     cudaError_t e = cudaStreamSynchronize((cudaStream_t)stream);
     if (e != cudaSuccess) { cgx::set_cuda_error(e); return CGX_ECUDA; }
-    int a = 0, b = 0;
+    int a = 0, b = 0, c = 0;
     int st = cgx::fetch_render_status(&a);
     if (st == CGX_OK) st = cgx::fetch_peer_status(&b);
+    if (st == CGX_OK) st = cgx::fetch_sort_status(&c);
     if (st != CGX_OK) return st;
-    *status_host = a ? a : b;
+    *status_host = a ? a : (b ? b : c);
     return CGX_OK;
 }

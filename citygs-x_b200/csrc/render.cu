@@ -1,20 +1,22 @@
-// Per-tile alpha compositing, forward and backward (FP32-pipe bound).
+// Per-tile alpha compositing, forward and backward (instruction-issue bound).
 //
 // One CTA (256 threads, one pixel each) per 16x16 tile, like the reference, but:
 //  * the five per-Gaussian inputs are first packed into one 64-byte record per Gaussian
-//    [x y | a b c opacity | r g b | m0..m4 | pad pad]; a tile's batch of 256 records is then staged into
+//    [x y | a b c opacity | r g b | m0..m4 | cull extents]; a tile's batch of 256 records is then staged into
 //    shared memory by 256 asynchronous 64-byte bulk copies (cp.async.bulk, completion on an mbarrier),
-//    double-buffered so the gather of batch i+1 overlaps the blending of batch i; colours and the
-//    plane map channels are read from shared memory instead of per-pixel global loads;
+//    double-buffered so the gather of batch i+1 overlaps the blending of batch i;
 //  * each warp owns an 8x4 pixel block of the tile and first culls the batch against it with an exact-safe bound
-//    (a Gaussian is dropped for the block only if alpha < 1/255 is guaranteed there; the half extents are
-//    computed once per Gaussian when its record is packed), 32 Gaussians per
-//    ballot, and blends only the survivors;
-//  * the per-tile statistics (sum of per-pixel counters) are reduced in the epilogue;
-//  * the backward reduces the 16 gradient terms of a Gaussian over the warp's 32 pixels with a
-//    transposing butterfly (16 shuffles) and issues ONE atomic per term per warp (visits with only one or two
-//    contributing pixels issue their atomics directly, which costs fewer issue slots), straight into the
-//    caller's gradient tensors (which also performs the (P,2,2)+(P,1) -> (P,4) repack).
+//    (a Gaussian is dropped for the block only if alpha < 1/255 is guaranteed there), 32 Gaussians per ballot;
+//  * the survivors ("visits") are processed 32 at a time in two phases.  Phase 1: every lane evaluates alpha of
+//    its pixel against each visit and keeps one bit per visit.  Phase 2: every lane walks only its OWN set bits,
+//    in list order, so the expensive part (blending; gradient terms in the backward) is executed as often as the
+//    busiest pixel of the block contributes, not once per visit: on aerial scenes a visit has 1-5 contributing
+//    pixels out of 32;
+//  * the backward stages the 16 gradient terms of every contribution in a per-warp shared-memory table (rows
+//    grouped by visit through ballot prefix sums), then half-warps sum each visit's rows, one lane per term, and
+//    issue ONE atomic per term per Gaussian per warp straight into the caller's gradient tensors (which also
+//    performs the (P,2,2)+(P,1) -> (P,4) repack);
+//  * the per-tile statistics (sum of per-pixel counters) are reduced in the forward's epilogue.
 //
 // Every wait on an mbarrier is bounded: when the limit is hit the CTA records an error in the device
 // status word, stops blending and returns.
@@ -90,6 +92,20 @@ __device__ __forceinline__ float2 cull_extent(float a, float b, float c, float o
     return {ex, ey};
 }
 
+// alpha of one Gaussian at one pixel, in the reference's operation order (cuda_rasterizer/forward.cu:376-389).
+// Returns false when the pixel is skipped (power > 0 or alpha < 1/255).  Both phases of the blending loops go
+// through this one function, so they take the same decision on the same bits.
+__device__ __forceinline__ bool eval_alpha(const float4 q0, const float2 q1xy, const float2 pixf, float2& d, float& G,
+                                           float& alpha)
+{
+    d = {q0.x - pixf.x, q0.y - pixf.y};
+    const float power = -0.5f * (q0.z * d.x * d.x + q1xy.x * d.y * d.y) - q0.w * d.x * d.y;
+    if (power > 0.0f) return false;
+    G = exp(power);
+    alpha = min(0.99f, q1xy.y * G);
+    return !(alpha < 1.0f / 255.0f);
+}
+
 // ------------------------------------------------------------------------------------------------ pack
 __global__ void __launch_bounds__(256)
 pack_records_kernel(int P, const int* __restrict__ radii, const float2* __restrict__ means2D,
@@ -130,7 +146,10 @@ struct FwdSmem {
     int red[2][RENDER_WARPS];
 };
 
-template <bool CULL>
+// MODE 0: every pixel looks at every Gaussian of the batch (the reference's loop); MODE 1: per-warp culling, then
+// every lane looks at every surviving Gaussian; MODE 2 (default): per-warp culling, then the two-phase walk.
+// All three produce identical bits.
+template <int MODE>
 __global__ void __launch_bounds__(RENDER_THREADS, 4)
 render_fwd_kernel(const uint2* __restrict__ ranges, const uint32_t* __restrict__ point_list, int W, int H,
                   const float focal_x, const float focal_y, const float cx, const float cy,
@@ -227,7 +246,7 @@ render_fwd_kernel(const uint2* __restrict__ ranges, const uint32_t* __restrict__
         const int* ids = sm.id[buf];
         const uint32_t contributor_base = (uint32_t)i * CGX_BLOCK_SIZE;
 
-        if (CULL) {
+        if (MODE >= 1) {
             // every warp compacts the Gaussians whose safe box meets its strip (order preserved)
             uint8_t* my_hits = sm.hits[warp];
             int n_hits = 0;
@@ -244,6 +263,52 @@ render_fwd_kernel(const uint2* __restrict__ ranges, const uint32_t* __restrict__
                 n_hits += __popc(m);
             }
             __syncwarp();
+            if (MODE == 2) {
+                for (int base = 0; base < n_hits; base += 32) {
+                    if (__all_sync(0xffffffffu, done)) break;
+                    const int g = min(32, n_hits - base);
+                    // phase 1: one bit per visit whose alpha passes both tests at this pixel
+                    uint32_t mine = 0;
+                    if (!done) {
+                        for (int v = 0; v < g; v++) {
+                            const int j = my_hits[base + v];
+                            const float4 q0 = rec[j].q0;
+                            const float2 q1xy = *reinterpret_cast<const float2*>(&rec[j].q1);
+                            float2 d;
+                            float G, alpha;
+                            if (eval_alpha(q0, q1xy, pixf, d, G, alpha)) mine |= 1u << v;
+                        }
+                    }
+                    // phase 2: this pixel's own contributors, front to back
+                    while (mine) {
+                        const int v = __ffs(mine) - 1;
+                        mine &= mine - 1;
+                        const int j = my_hits[base + v];
+                        const float4 q0 = rec[j].q0;
+                        const float4 q1 = rec[j].q1;
+                        float2 d;
+                        float G, alpha;
+                        if (!eval_alpha(q0, make_float2(q1.x, q1.y), pixf, d, G, alpha)) continue;
+                        float test_T = T * (1 - alpha);
+                        if (test_T < 0.0001f) {
+                            done = true;
+                            break;
+                        }
+                        thread_n_contrib2loss++;
+                        const float4 q2 = rec[j].q2;
+                        const float feat[CGX_NCH] = {q1.z, q1.w, q2.x};
+                        for (int ch = 0; ch < CGX_NCH; ch++) C[ch] += feat[ch] * alpha * T;
+                        if (render_geo) {
+                            const float4 q3 = rec[j].q3;
+                            const float am[CGX_NMAP] = {q2.y, q2.z, q2.w, q3.x, q3.y};
+                            for (int ch = 0; ch < CGX_NMAP; ch++) All_map[ch] += am[ch] * alpha * T;
+                        }
+                        if (T > 0.5) atomicAdd(&(out_observe[ids[j]]), 1);
+                        T = test_T;
+                        last_contributor = contributor_base + j + 1;
+                    }
+                }
+            } else
             for (int k = 0; !done && k < n_hits; k++) {
                 const int j = my_hits[k];
                 const float4 q0 = rec[j].q0;
@@ -431,7 +496,179 @@ __device__ __forceinline__ float warp_reduce16(float (&v)[16], int lane)
 #ifndef CGX_BWD_MIN_CTAS
 #define CGX_BWD_MIN_CTAS 3
 #endif
-template <bool CULL, bool CONTRACT, bool ADAPT>
+
+// Per-pixel state of the backward walk (cuda_rasterizer/backward.cu:408-443): everything one pixel carries from
+// one contributor to the next, back to front.
+struct BwdPixel {
+    float2 pixf;
+    float T, T_final, last_alpha, bg_dot_dpixel;
+    float dL_dpixel[CGX_NCH], dL_dout_all_map[CGX_NMAP];
+    float accum_rec[CGX_NCH], last_color[CGX_NCH];
+    float accum_all_map[CGX_NMAP], last_all_map[CGX_NMAP];
+};
+
+// One contribution (cuda_rasterizer/backward.cu:476-563 in the reference's operation order): advances the pixel's
+// recurrences and writes the 16 gradient terms of (this pixel, this Gaussian) to v[]:
+//   0,1 dL/dmean2D   2,3 |dL/dmean2D|   4,5,6 dL/dconic (xx, xy, yy)   7 dL/dopacity   8-10 dL/drgb   11-15 dL/dall_map
+__device__ __forceinline__ void bwd_contribution(BwdPixel& px, const Record& r, const float2 d, const float G,
+                                                 const float alpha, const bool render_geo, const float ddelx_dx,
+                                                 const float ddely_dy, float (&v)[16])
+{
+    const float4 q0 = r.q0, q1 = r.q1, q2 = r.q2;
+    // gradients carry a 1e-3 tolerance: one correctly rounded reciprocal serves both quotients
+    const float inv_1ma = __frcp_rn(1.f - alpha);
+    px.T = px.T * inv_1ma;
+    const float dchannel_dcolor = alpha * px.T;
+    float dL_dalpha = 0.0f;
+    const float col[CGX_NCH] = {q1.z, q1.w, q2.x};
+#pragma unroll
+    for (int ch = 0; ch < CGX_NCH; ch++) {
+        const float c = col[ch];
+        px.accum_rec[ch] = px.last_alpha * px.last_color[ch] + (1.f - px.last_alpha) * px.accum_rec[ch];
+        px.last_color[ch] = c;
+        dL_dalpha += (c - px.accum_rec[ch]) * px.dL_dpixel[ch];
+        v[8 + ch] = dchannel_dcolor * px.dL_dpixel[ch];
+    }
+    if (render_geo) {
+        const float4 q3 = r.q3;
+        const float am[CGX_NMAP] = {q2.y, q2.z, q2.w, q3.x, q3.y};
+#pragma unroll
+        for (int ch = 0; ch < CGX_NMAP; ch++) {
+            const float c = am[ch];
+            px.accum_all_map[ch] = px.last_alpha * px.last_all_map[ch] + (1.f - px.last_alpha) * px.accum_all_map[ch];
+            px.last_all_map[ch] = c;
+            dL_dalpha += (c - px.accum_all_map[ch]) * px.dL_dout_all_map[ch];
+            v[11 + ch] = dchannel_dcolor * px.dL_dout_all_map[ch];
+        }
+    } else {
+#pragma unroll
+        for (int ch = 0; ch < CGX_NMAP; ch++) v[11 + ch] = 0.f;
+    }
+    dL_dalpha *= px.T;
+    px.last_alpha = alpha;
+    dL_dalpha += (-px.T_final * inv_1ma) * px.bg_dot_dpixel;
+
+    const float dL_dG = q1.y * dL_dalpha;
+    const float gdx = G * d.x;
+    const float gdy = G * d.y;
+    const float dG_ddelx = -gdx * q0.z - gdy * q0.w;
+    const float dG_ddely = -gdy * q1.x - gdx * q0.w;
+    v[0] = dL_dG * dG_ddelx * ddelx_dx;
+    v[1] = dL_dG * dG_ddely * ddely_dy;
+    v[2] = fabs(dL_dG * dG_ddelx * ddelx_dx);
+    v[3] = fabs(dL_dG * dG_ddely * ddely_dy);
+    v[4] = -0.5f * gdx * d.x * dL_dG;
+    v[5] = -0.5f * gdx * d.y * dL_dG;
+    v[6] = -0.5f * gdy * d.y * dL_dG;
+    v[7] = G * dL_dalpha;
+}
+
+// Loads the pixel's cotangents and folds the plane-depth cotangent into the plane-map channels
+// (cuda_rasterizer/backward.cu:379-443).
+__device__ __forceinline__ void bwd_pixel_init(BwdPixel& px, bool inside, uint32_t pix_id, size_t HW, float2 ray,
+                                               const float* __restrict__ bg_color, const float* __restrict__ final_Ts,
+                                               const float* __restrict__ all_map_pixels,
+                                               const float* __restrict__ dL_dpixels,
+                                               const float* __restrict__ dL_dout_all_maps,
+                                               const float* __restrict__ dL_dout_plane_depths, bool render_geo)
+{
+    px.T_final = inside ? final_Ts[pix_id] : 0;
+    px.T = px.T_final;
+    px.last_alpha = 0.f;
+#pragma unroll
+    for (int i = 0; i < CGX_NCH; i++) px.dL_dpixel[i] = px.accum_rec[i] = px.last_color[i] = 0.f;
+#pragma unroll
+    for (int i = 0; i < CGX_NMAP; i++) px.dL_dout_all_map[i] = px.accum_all_map[i] = px.last_all_map[i] = 0.f;
+    if (inside) {
+        for (int i = 0; i < CGX_NCH; i++) px.dL_dpixel[i] = dL_dpixels[i * HW + pix_id];
+        if (render_geo) {
+            for (int i = 0; i < CGX_NMAP; i++) px.dL_dout_all_map[i] = dL_dout_all_maps[i * HW + pix_id];
+            const float3 normal = {all_map_pixels[pix_id], all_map_pixels[HW + pix_id], all_map_pixels[2 * HW + pix_id]};
+            const float distance = all_map_pixels[4 * HW + pix_id];
+            const float tmp = (normal.x * ray.x + normal.y * ray.y + normal.z + 1.0e-8);
+            px.dL_dout_all_map[CGX_NMAP - 1] += (-dL_dout_plane_depths[pix_id] / tmp);
+            px.dL_dout_all_map[0] += dL_dout_plane_depths[pix_id] * (distance / (tmp * tmp) * ray.x);
+            px.dL_dout_all_map[1] += dL_dout_plane_depths[pix_id] * (distance / (tmp * tmp) * ray.y);
+            px.dL_dout_all_map[2] += dL_dout_plane_depths[pix_id] * (distance / (tmp * tmp));
+        }
+    }
+    px.bg_dot_dpixel = 0;
+    for (int i = 0; i < CGX_NCH; i++) px.bg_dot_dpixel += bg_color[i] * px.dL_dpixel[i];
+}
+
+// The common head of both backward kernels: tile / pixel coordinates and the staging pipeline.
+#define CGX_BWD_PROLOGUE()                                                                                           \
+    const uint32_t horizontal_blocks = (W + CGX_BLOCK_X - 1) / CGX_BLOCK_X;                                          \
+    const uint32_t block_id = blockIdx.y * horizontal_blocks + blockIdx.x;                                           \
+    if (!compute_locally[block_id]) return;                                                                          \
+    const int tid = threadIdx.x;                                                                                     \
+    const int lane = tid & 31, warp = tid >> 5;                                                                      \
+    const uint32_t lx = (warp & 1) * 8 + (lane & 7), ly = (warp >> 1) * 4 + (lane >> 3); /* 8x4 block per warp */    \
+    const uint2 pix_min = {blockIdx.x * CGX_BLOCK_X, blockIdx.y * CGX_BLOCK_Y};                                      \
+    const uint2 pix = {pix_min.x + lx, pix_min.y + ly};                                                              \
+    const uint32_t pix_id = W * pix.y + pix.x;                                                                       \
+    const float2 pixf = {(float)pix.x, (float)pix.y};                                                                \
+    /* double arithmetic (W * 0.5 is a double expression), narrowed to float afterwards */                           \
+    const float2 ray = {(float)((pixf.x - W * 0.5) / fx), (float)((pixf.y - H * 0.5) / fy)};                         \
+    const bool inside = pix.x < W && pix.y < H;                                                                      \
+    const uint2 range = ranges[block_id];                                                                            \
+    const size_t HW = (size_t)H * W;                                                                                 \
+    const int rounds = ((range.y - range.x + CGX_BLOCK_SIZE - 1) / CGX_BLOCK_SIZE);                                  \
+    int toDo = range.y - range.x;                                                                                    \
+    if (tid == 0) {                                                                                                  \
+        mbar_init(&sm.bar[0], 1);                                                                                    \
+        mbar_init(&sm.bar[1], 1);                                                                                    \
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");                                           \
+    }                                                                                                                \
+    __syncthreads();                                                                                                 \
+    const float sx0 = (float)(pix_min.x + (warp & 1) * 8), sx1 = sx0 + 7.f;                                          \
+    const float sy0 = (float)(pix_min.y + (warp >> 1) * 4), sy1 = sy0 + 3.f;                                         \
+    auto issue = [&](int batch, int buf) {                                                                           \
+        const int progress = batch * CGX_BLOCK_SIZE + tid;                                                           \
+        const int n_valid = min(CGX_BLOCK_SIZE, (int)(range.y - range.x) - batch * CGX_BLOCK_SIZE);                  \
+        if (tid == 0) mbar_expect_tx(&sm.bar[buf], (uint32_t)n_valid * 64u);                                         \
+        if (range.x + progress < range.y) {                                                                          \
+            const int coll_id = point_list[range.y - progress - 1]; /* back to front */                              \
+            sm.id[buf][tid] = coll_id;                                                                               \
+            bulk_load_64(&sm.rec[buf][tid], records + coll_id, &sm.bar[buf]);                                        \
+        }                                                                                                            \
+    };                                                                                                               \
+    const uint32_t total = range.y - range.x;                                                                        \
+    /* pixels outside the image take part in the votes only: nothing is ever "before their last contributor" */     \
+    const int last_contributor = inside ? n_contrib[pix_id] : 0;                                                     \
+    BwdPixel px;                                                                                                     \
+    px.pixf = pixf;                                                                                                  \
+    bwd_pixel_init(px, inside, pix_id, HW, ray, bg_color, final_Ts, all_map_pixels, dL_dpixels, dL_dout_all_maps,    \
+                   dL_dout_plane_depths, render_geo);                                                                \
+    const float ddelx_dx = 0.5 * W;                                                                                  \
+    const float ddely_dy = 0.5 * H;                                                                                  \
+    bool failed = false;                                                                                             \
+    if (rounds > 0) issue(0, 0)
+
+// Culls the staged batch against this warp's 8x4 pixel block: slots whose safe box meets the block, in order.
+__device__ __forceinline__ int cull_batch(const Record* rec, int nb, int lane, float sx0, float sx1, float sy0,
+                                          float sy1, uint8_t* my_hits)
+{
+    int n_hits = 0;
+    for (int j0 = 0; j0 < nb; j0 += 32) {
+        const int j = j0 + lane;
+        bool hit = false;
+        if (j < nb) {
+            const float4 q0 = rec[j].q0;
+            const float4 q3 = rec[j].q3;
+            hit = (q0.x + q3.z >= sx0) && (q0.x - q3.z <= sx1) && (q0.y + q3.w >= sy0) && (q0.y - q3.w <= sy1);
+        }
+        const uint32_t m = __ballot_sync(0xffffffffu, hit);
+        if (hit) my_hits[n_hits + __popc(m & ((1u << lane) - 1u))] = (uint8_t)j;
+        n_hits += __popc(m);
+    }
+    __syncwarp();
+    return n_hits;
+}
+
+// Reference-shaped walk: every lane looks at every (surviving) Gaussian; the 16 terms are reduced over the warp
+// with the transposing butterfly.  Kept as the A/B partner of the two-phase kernel below.
+template <bool CULL>
 __global__ void __launch_bounds__(RENDER_THREADS, CGX_BWD_MIN_CTAS)
 render_bwd_kernel(const uint2* __restrict__ ranges, const uint32_t* __restrict__ point_list, int W, int H, float fx,
                   float fy, const float* __restrict__ bg_color, const Record* __restrict__ records,
@@ -442,96 +679,13 @@ render_bwd_kernel(const uint2* __restrict__ ranges, const uint32_t* __restrict__
 {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     BwdSmem& sm = *reinterpret_cast<BwdSmem*>(smem_raw);
-
-    const uint32_t horizontal_blocks = (W + CGX_BLOCK_X - 1) / CGX_BLOCK_X;
-    const uint32_t block_id = blockIdx.y * horizontal_blocks + blockIdx.x;
-    if (!compute_locally[block_id]) return;
-    const int tid = threadIdx.x;
-    const int lane = tid & 31, warp = tid >> 5;
-    const uint32_t lx = (warp & 1) * 8 + (lane & 7), ly = (warp >> 1) * 4 + (lane >> 3);   // 8x4 block per warp
-
-    const uint2 pix_min = {blockIdx.x * CGX_BLOCK_X, blockIdx.y * CGX_BLOCK_Y};
-    const uint2 pix = {pix_min.x + lx, pix_min.y + ly};
-    const uint32_t pix_id = W * pix.y + pix.x;
-    const float2 pixf = {(float)pix.x, (float)pix.y};
-    // double arithmetic (W * 0.5 is a double expression), narrowed to float afterwards
-    const float2 ray = {(float)((pixf.x - W * 0.5) / fx), (float)((pixf.y - H * 0.5) / fy)};
-    const bool inside = pix.x < W && pix.y < H;
-    const uint2 range = ranges[block_id];
-    const size_t HW = (size_t)H * W;
-
-    const int rounds = ((range.y - range.x + CGX_BLOCK_SIZE - 1) / CGX_BLOCK_SIZE);
-    bool done = !inside;
-    int toDo = range.y - range.x;
-
-    if (tid == 0) {
-        mbar_init(&sm.bar[0], 1);
-        mbar_init(&sm.bar[1], 1);
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    __syncthreads();
+    CGX_BWD_PROLOGUE();
 
     // destination of the term this lane owns after the butterfly
     const int my_term = ((lane >> 4) & 1) * 8 + ((lane >> 3) & 1) * 4 + ((lane >> 2) & 1) * 2 + ((lane >> 1) & 1);
     float* my_ptr = out.ptr[my_term];
     const int my_stride = out.stride[my_term];
     const bool my_write = (lane & 1) == 0 && my_ptr != nullptr;
-
-    const float sx0 = (float)(pix_min.x + (warp & 1) * 8), sx1 = sx0 + 7.f;
-    const float sy0 = (float)(pix_min.y + (warp >> 1) * 4), sy1 = sy0 + 3.f;
-
-    auto issue = [&](int batch, int buf) {
-        const int progress = batch * CGX_BLOCK_SIZE + tid;
-        const int n_valid = min(CGX_BLOCK_SIZE, (int)(range.y - range.x) - batch * CGX_BLOCK_SIZE);
-        if (tid == 0) mbar_expect_tx(&sm.bar[buf], (uint32_t)n_valid * 64u);
-        if (range.x + progress < range.y) {
-            const int coll_id = point_list[range.y - progress - 1];  // back to front
-            sm.id[buf][tid] = coll_id;
-            bulk_load_64(&sm.rec[buf][tid], records + coll_id, &sm.bar[buf]);
-        }
-    };
-
-    const float T_final = inside ? final_Ts[pix_id] : 0;
-    float T = T_final;
-    const uint32_t total = range.y - range.x;
-    const int last_contributor = inside ? n_contrib[pix_id] : 0;
-
-    float dL_dpixel[CGX_NCH] = {0};
-    float dL_dout_all_map[CGX_NMAP] = {0};
-    if (inside) {
-        for (int i = 0; i < CGX_NCH; i++) dL_dpixel[i] = dL_dpixels[i * HW + pix_id];
-        if (render_geo) {
-            for (int i = 0; i < CGX_NMAP; i++) dL_dout_all_map[i] = dL_dout_all_maps[i * HW + pix_id];
-            const float3 normal = {all_map_pixels[pix_id], all_map_pixels[HW + pix_id], all_map_pixels[2 * HW + pix_id]};
-            const float distance = all_map_pixels[4 * HW + pix_id];
-            const float tmp = (normal.x * ray.x + normal.y * ray.y + normal.z + 1.0e-8);
-            dL_dout_all_map[CGX_NMAP - 1] += (-dL_dout_plane_depths[pix_id] / tmp);
-            dL_dout_all_map[0] += dL_dout_plane_depths[pix_id] * (distance / (tmp * tmp) * ray.x);
-            dL_dout_all_map[1] += dL_dout_plane_depths[pix_id] * (distance / (tmp * tmp) * ray.y);
-            dL_dout_all_map[2] += dL_dout_plane_depths[pix_id] * (distance / (tmp * tmp));
-        }
-    }
-    float bg_dot_dpixel = 0;
-    for (int i = 0; i < CGX_NCH; i++) bg_dot_dpixel += bg_color[i] * dL_dpixel[i];
-
-    // The reference carries eight per-channel recurrences "colour accumulated behind me":
-    //   accum[ch] = last_alpha * last_colour[ch] + (1 - last_alpha) * accum[ch]
-    // and then contracts (colour - accum) with the pixel's cotangent (CONTRACT = false does exactly that, in the
-    // reference's operation order, and is the default).  CONTRACT = true uses the linearity of the recurrence: for
-    // the six channels of order one (rgb, plane normal) it is contracted with the cotangent first, one scalar
-    // recurrence over dot_j = colour_j . dL/dC; the constant-1 and plane-distance channels keep their own.  Fewer
-    // instructions, but where the plane-depth cotangent explodes (rays grazing the blended normal) the three normal
-    // terms cancel by many orders of magnitude and the different rounding shows up at the 1e-2 level.
-    float accum_dot = 0.f, last_dot = 0.f, last_alpha = 0.f;
-    float accum_m3 = 0.f, accum_m4 = 0.f, last_m3 = 0.f, last_m4 = 0.f;
-    // per-channel form of the same recurrences (CONTRACT = false), kept for A/B checks of the contraction
-    float accum_rec[CGX_NCH] = {0}, last_color[CGX_NCH] = {0};
-    float accum_all_map[CGX_NMAP] = {0}, last_all_map[CGX_NMAP] = {0};
-    const float ddelx_dx = 0.5 * W;
-    const float ddely_dy = 0.5 * H;
-    bool failed = false;
-
-    if (rounds > 0) issue(0, 0);
 
     for (int i = 0; i < rounds; i++, toDo -= CGX_BLOCK_SIZE) {
         const int buf = i & 1;
@@ -546,131 +700,24 @@ render_bwd_kernel(const uint2* __restrict__ ranges, const uint32_t* __restrict__
         // batch slot j holds sorted position range.y - 1 - (i*256 + j); its 0-based index in the tile list is
         // total - 1 - (i*256 + j), which is the reference's `contributor` after its decrement.
         const uint32_t idx_base = total - 1 - (uint32_t)i * CGX_BLOCK_SIZE;
-
         uint8_t* my_hits = sm.hits[warp];
-        int n_hits = nb;
-        if (CULL) {
-            n_hits = 0;
-            for (int j0 = 0; j0 < nb; j0 += 32) {
-                const int j = j0 + lane;
-                bool hit = false;
-                if (j < nb) {
-                    const float4 q0 = rec[j].q0;
-                    const float4 q3 = rec[j].q3;
-                    hit = (q0.x + q3.z >= sx0) && (q0.x - q3.z <= sx1) && (q0.y + q3.w >= sy0) && (q0.y - q3.w <= sy1);
-                }
-                const uint32_t m = __ballot_sync(0xffffffffu, hit);
-                if (hit) my_hits[n_hits + __popc(m & ((1u << lane) - 1u))] = (uint8_t)j;
-                n_hits += __popc(m);
-            }
-            __syncwarp();
-        }
+        const int n_hits = CULL ? cull_batch(rec, nb, lane, sx0, sx1, sy0, sy1, my_hits) : nb;
 
         for (int k = 0; k < n_hits; k++) {
             const int j = CULL ? (int)my_hits[k] : k;
             const uint32_t contributor = idx_base - (uint32_t)j;
             float v[16];
             bool valid = false;
-            if (!done && contributor < (uint32_t)last_contributor) {
-                const float4 q0 = rec[j].q0;
-                const float4 q1 = rec[j].q1;
-                const float2 xy = {q0.x, q0.y};
-                const float2 d = {xy.x - pixf.x, xy.y - pixf.y};
-                const float4 con_o = {q0.z, q0.w, q1.x, q1.y};
-                const float power = -0.5f * (con_o.x * d.x * d.x + con_o.z * d.y * d.y) - con_o.y * d.x * d.y;
-                if (!(power > 0.0f)) {
-                    const float G = exp(power);
-                    const float alpha = min(0.99f, con_o.w * G);
-                    if (!(alpha < 1.0f / 255.0f)) {
-                        valid = true;
-                        // gradients carry a 1e-3 tolerance: one correctly rounded reciprocal serves both quotients
-                        const float inv_1ma = __frcp_rn(1.f - alpha);
-                        T = T * inv_1ma;
-                        const float dchannel_dcolor = alpha * T;
-                        const float4 q2 = rec[j].q2;
-                        float dL_dalpha;
-                        if (CONTRACT) {
-                            float dot = q1.z * dL_dpixel[0] + q1.w * dL_dpixel[1] + q2.x * dL_dpixel[2];
-    #pragma unroll
-                            for (int ch = 0; ch < CGX_NCH; ch++) v[8 + ch] = dchannel_dcolor * dL_dpixel[ch];
-                            float geo_tail = 0.f;
-                            if (render_geo) {
-                                const float4 q3 = rec[j].q3;
-                                dot += q2.y * dL_dout_all_map[0] + q2.z * dL_dout_all_map[1] + q2.w * dL_dout_all_map[2];
-                                accum_m3 = last_alpha * last_m3 + (1.f - last_alpha) * accum_m3;
-                                accum_m4 = last_alpha * last_m4 + (1.f - last_alpha) * accum_m4;
-                                last_m3 = q3.x;
-                                last_m4 = q3.y;
-                                geo_tail = (q3.x - accum_m3) * dL_dout_all_map[3] + (q3.y - accum_m4) * dL_dout_all_map[4];
-    #pragma unroll
-                                for (int ch = 0; ch < CGX_NMAP; ch++) v[11 + ch] = dchannel_dcolor * dL_dout_all_map[ch];
-                            } else {
-    #pragma unroll
-                                for (int ch = 0; ch < CGX_NMAP; ch++) v[11 + ch] = 0.f;
-                            }
-                            accum_dot = last_alpha * last_dot + (1.f - last_alpha) * accum_dot;
-                            last_dot = dot;
-                            last_alpha = alpha;
-                            dL_dalpha = ((dot - accum_dot) + geo_tail) * T;
-                        } else {
-                            dL_dalpha = 0.0f;
-                            const float col[CGX_NCH] = {q1.z, q1.w, q2.x};
-#pragma unroll
-                            for (int ch = 0; ch < CGX_NCH; ch++) {
-                                const float c = col[ch];
-                                accum_rec[ch] = last_alpha * last_color[ch] + (1.f - last_alpha) * accum_rec[ch];
-                                last_color[ch] = c;
-                                dL_dalpha += (c - accum_rec[ch]) * dL_dpixel[ch];
-                                v[8 + ch] = dchannel_dcolor * dL_dpixel[ch];
-                            }
-                            if (render_geo) {
-                                const float4 q3 = rec[j].q3;
-                                const float am[CGX_NMAP] = {q2.y, q2.z, q2.w, q3.x, q3.y};
-#pragma unroll
-                                for (int ch = 0; ch < CGX_NMAP; ch++) {
-                                    const float c = am[ch];
-                                    accum_all_map[ch] = last_alpha * last_all_map[ch] + (1.f - last_alpha) * accum_all_map[ch];
-                                    last_all_map[ch] = c;
-                                    dL_dalpha += (c - accum_all_map[ch]) * dL_dout_all_map[ch];
-                                    v[11 + ch] = dchannel_dcolor * dL_dout_all_map[ch];
-                                }
-                            } else {
-#pragma unroll
-                                for (int ch = 0; ch < CGX_NMAP; ch++) v[11 + ch] = 0.f;
-                            }
-                            dL_dalpha *= T;
-                            last_alpha = alpha;
-                        }
-                        dL_dalpha += (-T_final * inv_1ma) * bg_dot_dpixel;
-
-                        const float dL_dG = con_o.w * dL_dalpha;
-                        const float gdx = G * d.x;
-                        const float gdy = G * d.y;
-                        const float dG_ddelx = -gdx * con_o.x - gdy * con_o.y;
-                        const float dG_ddely = -gdy * con_o.z - gdx * con_o.y;
-                        v[0] = dL_dG * dG_ddelx * ddelx_dx;
-                        v[1] = dL_dG * dG_ddely * ddely_dy;
-                        v[2] = fabs(dL_dG * dG_ddelx * ddelx_dx);
-                        v[3] = fabs(dL_dG * dG_ddely * ddely_dy);
-                        v[4] = -0.5f * gdx * d.x * dL_dG;
-                        v[5] = -0.5f * gdx * d.y * dL_dG;
-                        v[6] = -0.5f * gdy * d.y * dL_dG;
-                        v[7] = G * dL_dalpha;
-                    }
+            if (contributor < (uint32_t)last_contributor) {
+                float2 d;
+                float G, alpha;
+                if (eval_alpha(rec[j].q0, *reinterpret_cast<const float2*>(&rec[j].q1), pixf, d, G, alpha)) {
+                    valid = true;
+                    bwd_contribution(px, rec[j], d, G, alpha, render_geo, ddelx_dx, ddely_dy, v);
                 }
             }
             const uint32_t vmask = __ballot_sync(0xffffffffu, valid);
             if (vmask == 0) continue;
-            if (ADAPT && __popc(vmask) <= 2) {
-                // one or two contributing pixels: their own 16 atomics cost fewer issue slots than the butterfly
-                if (valid) {
-                    const size_t g = (size_t)ids[j];
-#pragma unroll
-                    for (int t = 0; t < 16; t++)
-                        if (out.ptr[t]) atomicAdd(out.ptr[t] + g * out.stride[t], v[t]);
-                }
-                continue;
-            }
             if (!valid) {
 #pragma unroll
                 for (int t = 0; t < 16; t++) v[t] = 0.f;
@@ -680,6 +727,163 @@ render_bwd_kernel(const uint2* __restrict__ ranges, const uint32_t* __restrict__
         }
     }
     if (failed && lane == 0) atomicExch(&g_status, CGX_ETIMEDOUT);
+}
+
+// ---- two-phase backward
+#ifndef CGX_BWD_CAP
+#define CGX_BWD_CAP 60
+#endif
+constexpr int BWD_CAP = CGX_BWD_CAP;  // gradient rows a warp stages per group of visits (a visit adds at most 32);
+                                      // 60 rows keep the CTA at 75 KB of shared memory: three CTAs per SM
+constexpr int BWD_RS = 20;            // floats per staged row: 16 terms, 80-byte pitch (spreads rows over the banks)
+static_assert(BWD_CAP >= 32 && BWD_CAP % 4 == 0, "a group must hold at least one full visit");
+
+struct BwdSmem2 {
+    Record rec[2][CGX_BLOCK_SIZE];
+    int id[2][CGX_BLOCK_SIZE];
+    float stage[RENDER_WARPS][BWD_CAP * BWD_RS];
+    uint8_t hits[RENDER_WARPS][CGX_BLOCK_SIZE];
+    uint64_t bar[2];
+};
+
+__global__ void __launch_bounds__(RENDER_THREADS, CGX_BWD_MIN_CTAS)
+render_bwd2_kernel(const uint2* __restrict__ ranges, const uint32_t* __restrict__ point_list, int W, int H, float fx,
+                   float fy, const float* __restrict__ bg_color, const Record* __restrict__ records,
+                   const float* __restrict__ all_map_pixels, const float* __restrict__ final_Ts,
+                   const uint32_t* __restrict__ n_contrib, const uint8_t* __restrict__ compute_locally,
+                   const float* __restrict__ dL_dpixels, const float* __restrict__ dL_dout_all_maps,
+                   const float* __restrict__ dL_dout_plane_depths, const bool render_geo, BwdOut out)
+{
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    BwdSmem2& sm = *reinterpret_cast<BwdSmem2*>(smem_raw);
+    CGX_BWD_PROLOGUE();
+
+    // phase 3: lane t (and t + 16) owns gradient term t
+    const int half = lane >> 4, term = lane & 15;
+    float* my_ptr = out.ptr[term];
+    const int my_stride = out.stride[term];
+    const uint32_t lanes_below = (1u << lane) - 1u;
+    float* stage = sm.stage[warp];
+    // a warp none of whose pixels has a contributor has nothing to do in any batch
+    const bool warp_idle = __all_sync(0xffffffffu, last_contributor == 0);
+
+    for (int i = 0; i < rounds; i++, toDo -= CGX_BLOCK_SIZE) {
+        const int buf = i & 1;
+        if (!mbar_wait(&sm.bar[buf], (i >> 1) & 1)) failed = true;
+        const int any_failed = __syncthreads_or(failed);
+        if (any_failed) break;
+        if (i + 1 < rounds) issue(i + 1, buf ^ 1);
+        if (warp_idle) continue;
+
+        const int nb = min(CGX_BLOCK_SIZE, toDo);
+        const Record* rec = sm.rec[buf];
+        const int* ids = sm.id[buf];
+        // batch slot j holds sorted position range.y - 1 - (i*256 + j); its 0-based index in the tile list is
+        // total - 1 - (i*256 + j), which is the reference's `contributor` after its decrement.
+        const uint32_t idx_base = total - 1 - (uint32_t)i * CGX_BLOCK_SIZE;
+        uint8_t* my_hits = sm.hits[warp];
+        const int n_hits = cull_batch(rec, nb, lane, sx0, sx1, sy0, sy1, my_hits);
+
+        int base = 0;
+        while (base < n_hits) {
+            // ---- phase 1: which pixels does each visit reach?  Lane v keeps the pixel mask of visit v, every lane
+            // keeps the visit mask of its own pixel.  The group ends after 32 visits or when its rows fill the table.
+            uint32_t mine = 0, visit_mask = 0;
+            int rows = 0, g = 0;
+            while (g < 32 && base + g < n_hits && rows <= BWD_CAP - 32) {
+                const int j = my_hits[base + g];
+                bool valid = false;
+                if (idx_base - (uint32_t)j < (uint32_t)last_contributor) {
+                    float2 d;
+                    float G, alpha;
+                    valid = eval_alpha(rec[j].q0, *reinterpret_cast<const float2*>(&rec[j].q1), pixf, d, G, alpha);
+                }
+                const uint32_t m = __ballot_sync(0xffffffffu, valid);
+                if (lane == g) visit_mask = m;
+                mine |= (valid ? 1u : 0u) << g;
+                rows += __popc(m);
+                g++;
+            }
+            if (rows) {
+                // first row of visit v = contributions of the visits before it (exclusive scan over the lanes)
+                const int cnt = __popc(visit_mask);
+                int incl = cnt;
+#pragma unroll
+                for (int dd = 1; dd < 32; dd <<= 1) {
+                    const int n = __shfl_up_sync(0xffffffffu, incl, dd);
+                    if (lane >= dd) incl += n;
+                }
+                const int first_row = incl - cnt;
+
+                // ---- phase 2: every lane walks its own contributors, back to front, and stages their terms
+                for (;;) {
+                    const bool act = mine != 0;
+                    if (!__any_sync(0xffffffffu, act)) break;
+                    const int v = act ? __ffs(mine) - 1 : 0;
+                    const uint32_t mv = __shfl_sync(0xffffffffu, visit_mask, v);
+                    const int rv = __shfl_sync(0xffffffffu, first_row, v);
+                    if (act) {
+                        mine &= mine - 1;
+                        const int j = my_hits[base + v];
+                        float2 d;
+                        float G, alpha;
+                        eval_alpha(rec[j].q0, *reinterpret_cast<const float2*>(&rec[j].q1), pixf, d, G, alpha);
+                        float val[16];
+                        bwd_contribution(px, rec[j], d, G, alpha, render_geo, ddelx_dx, ddely_dy, val);
+                        float4* row = reinterpret_cast<float4*>(stage + (rv + __popc(mv & lanes_below)) * BWD_RS);
+                        row[0] = make_float4(val[0], val[1], val[2], val[3]);
+                        row[1] = make_float4(val[4], val[5], val[6], val[7]);
+                        row[2] = make_float4(val[8], val[9], val[10], val[11]);
+                        row[3] = make_float4(val[12], val[13], val[14], val[15]);
+                    }
+                }
+                __syncwarp();
+
+                // ---- phase 3: two visits at a time, one half-warp each, lane = term: sum the visit's rows and add
+                // the total to the Gaussian's gradient with one atomic per term
+                for (int v0 = 0; v0 < g; v0 += 2) {
+                    const int v = v0 + half;          // v == g (odd group) reads an empty mask
+                    const uint32_t mv = __shfl_sync(0xffffffffu, visit_mask, v & 31);
+                    const int rv = __shfl_sync(0xffffffffu, first_row, v & 31);
+                    const int n = v < g ? __popc(mv) : 0;
+                    if (n) {
+                        const float* p = stage + rv * BWD_RS + term;
+                        float sum = 0.f;
+                        for (int r = 0; r < n; r++) sum += p[r * BWD_RS];
+                        if (my_ptr) atomicAdd(my_ptr + (size_t)ids[my_hits[base + v]] * my_stride, sum);
+                    }
+                }
+                __syncwarp();
+            }
+            base += g;
+        }
+    }
+    if (failed && lane == 0) atomicExch(&g_status, CGX_ETIMEDOUT);
+}
+
+// Clears up to five float arrays in one launch (grid-stride over the concatenated index space).
+struct ZeroJobs {
+    float* ptr[5];
+    long long n[5];
+};
+__global__ void __launch_bounds__(256) zero_arrays_kernel(ZeroJobs z)
+{
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    const long long t0 = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+#pragma unroll
+    for (int k = 0; k < 5; k++) {
+        float* p = z.ptr[k];
+        const long long n = z.n[k];
+        if (!p) continue;
+        if ((reinterpret_cast<uintptr_t>(p) & 15u) == 0) {
+            float4* p4 = reinterpret_cast<float4*>(p);
+            const long long n4 = n >> 2;
+            for (long long i = t0; i < n4; i += stride) p4[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (long long i = (n4 << 2) + t0; i < n; i += stride) p[i] = 0.f;
+        } else {
+            for (long long i = t0; i < n; i += stride) p[i] = 0.f;
+        }
+    }
 }
 
 }  // namespace cgx
@@ -707,15 +911,14 @@ int fetch_render_status(int* out)
 }
 }  // namespace cgx
 
-// bit 0: per-warp culling (default on); bit 1: contracted recurrences (backward; off: it changes the rounding of
-// pixels whose plane-depth cotangent blows up and leaves the 1e-3 parity band there); bit 2: direct atomics for
-// visits with one or two contributing pixels (backward; off: measured slower, the extra L2 atomics cost more than
-// the butterfly saves)
+// Test-only switch (cgx_raster_testing.h).  bit 0: per-warp culling; bit 1: the reference-shaped walk (every lane
+// looks at every surviving Gaussian, butterfly reduction in the backward) instead of the two-phase walk.
+// Default 1 = culling + two-phase.  All variants give the same forward bits and gradients equal to rounding.
 static int g_render_variant = 1;
 
 extern "C" int cgx_set_render_variant(int variant)
 {
-    g_render_variant = variant & 7;
+    g_render_variant = variant & 3;
     return CGX_OK;
 }
 
@@ -744,22 +947,23 @@ extern "C" int cgx_render_fwd(int P, int W, int H, float tanfovx, float tanfovy,
     const dim3 grid((W + CGX_BLOCK_X - 1) / CGX_BLOCK_X, (H + CGX_BLOCK_Y - 1) / CGX_BLOCK_Y, 1);
     const dim3 block(RENDER_THREADS, 1, 1);
     const size_t smem = sizeof(FwdSmem);
-    cudaError_t e;
-    if (g_render_variant & 1) {
-        e = cudaFuncSetAttribute(render_fwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) { set_cuda_error(e); return CGX_ECUDA; }
-        render_fwd_kernel<true><<<grid, block, smem, st>>>(
-            (const uint2*)ranges, point_list, W, H, focal_x, focal_y, float(W * 0.5f), float(H * 0.5f),
-            (const Record*)records, final_T, n_contrib, n_contrib2loss, compute_locally, bg, out_color, out_observe,
-            out_all_map, out_plane_depth, render_geo != 0, n_render_t, n_consider_t, n_contrib_t);
-    } else {
-        e = cudaFuncSetAttribute(render_fwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) { set_cuda_error(e); return CGX_ECUDA; }
-        render_fwd_kernel<false><<<grid, block, smem, st>>>(
-            (const uint2*)ranges, point_list, W, H, focal_x, focal_y, float(W * 0.5f), float(H * 0.5f),
-            (const Record*)records, final_T, n_contrib, n_contrib2loss, compute_locally, bg, out_color, out_observe,
-            out_all_map, out_plane_depth, render_geo != 0, n_render_t, n_consider_t, n_contrib_t);
-    }
+    cudaError_t e = cudaSuccess;
+#define CGX_LAUNCH_FWD(MODE)                                                                                         \
+    do {                                                                                                            \
+        e = cudaFuncSetAttribute(render_fwd_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);  \
+        if (e != cudaSuccess) { set_cuda_error(e); return CGX_ECUDA; }                                              \
+        render_fwd_kernel<MODE><<<grid, block, smem, st>>>(                                                         \
+            (const uint2*)ranges, point_list, W, H, focal_x, focal_y, float(W * 0.5f), float(H * 0.5f),             \
+            (const Record*)records, final_T, n_contrib, n_contrib2loss, compute_locally, bg, out_color, out_observe, \
+            out_all_map, out_plane_depth, render_geo != 0, n_render_t, n_consider_t, n_contrib_t);                  \
+    } while (0)
+    if (!(g_render_variant & 1))
+        CGX_LAUNCH_FWD(0);
+    else if (g_render_variant & 2)
+        CGX_LAUNCH_FWD(1);
+    else
+        CGX_LAUNCH_FWD(2);
+#undef CGX_LAUNCH_FWD
     return check_launch(P > 0 ? 2 : 1);
 }
 
@@ -795,12 +999,18 @@ extern "C" int cgx_render_bwd(int P, int W, int H, float tanfovx, float tanfovy,
     if (render_geo && (!all_map_pixels || !dL_dout_all_map || !dL_dout_plane_depth)) return CGX_EINVAL;
     if (!aligned16(records)) return CGX_EINVAL;
     cudaStream_t st = (cudaStream_t)stream;
-    cudaError_t e = cudaMemsetAsync(dL_dmeans2D, 0, (size_t)P * 2 * sizeof(float), st);
-    if (e == cudaSuccess) e = cudaMemsetAsync(dL_dmeans2D_abs, 0, (size_t)P * 3 * sizeof(float), st);
-    if (e == cudaSuccess) e = cudaMemsetAsync(dL_dconic_opacity, 0, (size_t)P * 4 * sizeof(float), st);
-    if (e == cudaSuccess) e = cudaMemsetAsync(dL_drgb, 0, (size_t)P * 3 * sizeof(float), st);
-    if (e == cudaSuccess) e = cudaMemsetAsync(dL_dall_map, 0, (size_t)P * 5 * sizeof(float), st);
-    if (e != cudaSuccess) { set_cuda_error(e); return CGX_ECUDA; }
+    cudaError_t e = cudaSuccess;
+    {
+        // the five gradient arrays start at zero: one launch clears all of them
+        ZeroJobs z;
+        float* arrs[5] = {dL_dmeans2D, dL_dmeans2D_abs, dL_dconic_opacity, dL_drgb, dL_dall_map};
+        const int widths[5] = {2, 3, 4, 3, 5};
+        for (int k = 0; k < 5; k++) {
+            z.ptr[k] = arrs[k];
+            z.n[k] = (long long)P * widths[k];
+        }
+        zero_arrays_kernel<<<148 * 8, 256, 0, st>>>(z);
+    }
 
     BwdOut out;
     float* ptrs[16] = {dL_dmeans2D, dL_dmeans2D + 1, dL_dmeans2D_abs, dL_dmeans2D_abs + 1,
@@ -819,26 +1029,21 @@ extern "C" int cgx_render_bwd(int P, int W, int H, float tanfovx, float tanfovy,
     const float focal_x = W / (2.0f * tanfovx);
     const dim3 grid((W + CGX_BLOCK_X - 1) / CGX_BLOCK_X, (H + CGX_BLOCK_Y - 1) / CGX_BLOCK_Y, 1);
     const dim3 block(RENDER_THREADS, 1, 1);
-    const size_t smem = sizeof(BwdSmem);
-#define CGX_LAUNCH_BWD(C, K, A)                                                                                      \
+#define CGX_LAUNCH_BWD(KERNEL, SMEM)                                                                                 \
     do {                                                                                                            \
-        e = cudaFuncSetAttribute(render_bwd_kernel<C, K, A>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        e = cudaFuncSetAttribute(KERNEL, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(SMEM));                 \
         if (e != cudaSuccess) { set_cuda_error(e); return CGX_ECUDA; }                                              \
-        render_bwd_kernel<C, K, A><<<grid, block, smem, st>>>(                                                      \
+        KERNEL<<<grid, block, (SMEM), st>>>(                                                                        \
             (const uint2*)ranges, point_list, W, H, focal_x, focal_y, bg, (const Record*)records, all_map_pixels,   \
             final_T, n_contrib, compute_locally, dL_dcolor, dL_dout_all_map, dL_dout_plane_depth, render_geo != 0,  \
             out);                                                                                                   \
     } while (0)
-    switch (g_render_variant & 7) {
-    case 0: CGX_LAUNCH_BWD(false, false, false); break;
-    case 1: CGX_LAUNCH_BWD(true, false, false); break;
-    case 2: CGX_LAUNCH_BWD(false, true, false); break;
-    case 3: CGX_LAUNCH_BWD(true, true, false); break;
-    case 4: CGX_LAUNCH_BWD(false, false, true); break;
-    case 5: CGX_LAUNCH_BWD(true, false, true); break;
-    case 6: CGX_LAUNCH_BWD(false, true, true); break;
-    default: CGX_LAUNCH_BWD(true, true, true); break;
-    }
+    if (!(g_render_variant & 1))
+        CGX_LAUNCH_BWD(render_bwd_kernel<false>, sizeof(BwdSmem));
+    else if (g_render_variant & 2)
+        CGX_LAUNCH_BWD(render_bwd_kernel<true>, sizeof(BwdSmem));
+    else
+        CGX_LAUNCH_BWD(render_bwd2_kernel, sizeof(BwdSmem2));
 #undef CGX_LAUNCH_BWD
-    return check_launch();
+    return check_launch(2);
 }

@@ -367,13 +367,19 @@ def render_gaussians(background, image_height, image_width, means2D, depths, rad
             ev0 = torch.cuda.Event(enable_timing=True)
             ev1 = torch.cuda.Event(enable_timing=True)
             ev0.record()
-        _call("cgx_emit_keys", l.cgx_emit_keys, P, W, H, _ptr(radii), _ptr(means2D), _ptr(depths), _ptr(g["tiles_touched"]),
-                              _ptr(local), _ptr(g["point_offsets"]), _ptr(b["point_list_keys_unsorted"]),
-                              _ptr(b["point_list_unsorted"]), R, _ptr(g["scanning_space"]), st, info=dict(P=P, R=R))
+        # the sort ping-pongs between the two key/value arrays: the pairs are emitted into whichever array makes
+        # the last pass land in point_list_keys / point_list (no copy, whatever the number of passes)
         bit = int(l.cgx_higher_msb(T))
-        _call("cgx_sort_pairs", l.cgx_sort_pairs, R, 32 + bit, _ptr(b["point_list_keys_unsorted"]), _ptr(b["point_list_unsorted"]),
-                               _ptr(b["point_list_keys"]), _ptr(b["point_list"]), _ptr(b["list_sorting_space"]),
-                               b["list_sorting_space"].numel(), st, info=dict(R=R, bits=32 + bit))
+        first = ("point_list_keys", "point_list") if l.cgx_sort_passes(32 + bit) % 2 == 0 else \
+            ("point_list_keys_unsorted", "point_list_unsorted")
+        other = ("point_list_keys_unsorted", "point_list_unsorted") if first[0] == "point_list_keys" else \
+            ("point_list_keys", "point_list")
+        _call("cgx_emit_keys", l.cgx_emit_keys, P, W, H, _ptr(radii), _ptr(means2D), _ptr(depths), _ptr(g["tiles_touched"]),
+                              _ptr(local), _ptr(g["point_offsets"]), _ptr(b[first[0]]), _ptr(b[first[1]]), R,
+                              _ptr(g["scanning_space"]), st, info=dict(P=P, R=R))
+        _call("cgx_sort_pairs", l.cgx_sort_pairs_pingpong, R, 32 + bit, _ptr(b[first[0]]), _ptr(b[first[1]]),
+                               _ptr(b[other[0]]), _ptr(b[other[1]]), _ptr(b["list_sorting_space"]),
+                               b["list_sorting_space"].numel(), 0, st, info=dict(R=R, bits=32 + bit))
         _call("cgx_tile_ranges", l.cgx_tile_ranges, R, T, _ptr(b["point_list_keys"]), _ptr(im["ranges"]), st, info=dict(R=R, T=T))
         _call("cgx_render_fwd", l.cgx_render_fwd, P, W, H, float(tan_fovx), float(tan_fovy), _ptr(im["ranges"]), _ptr(b["point_list"]),
                                _ptr(radii), _ptr(means2D), _ptr(rgb), _ptr(all_map), _ptr(conic_opacity), _ptr(local), _ptr(bg),

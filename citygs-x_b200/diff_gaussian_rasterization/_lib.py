@@ -85,6 +85,8 @@ SIGNATURES = {
     "cgx_emit_keys": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _vp, _vp]),
     "cgx_sort_workspace_bytes": (_sz, [_i64]),
     "cgx_sort_pairs": (_i, [_i64, _i, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
+    "cgx_sort_passes": (_i, [_i]),
+    "cgx_sort_pairs_pingpong": (_i, [_i64, _i, _vp, _vp, _vp, _vp, _vp, _sz, C.c_uint64, _vp]),
     "cgx_sort_pairs_static_max": (_i64, []),
     "cgx_sort_pairs_static": (_i, [_i64, _i, _vp, _vp, _vp, _vp, _vp]),
     "cgx_set_sort_variant": (_i, [_i]),

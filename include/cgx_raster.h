@@ -321,11 +321,23 @@ int cgx_emit_keys(int P, int W, int H, const int32_t* radii, const float* means2
                   const void* workspace, void* stream);
 
 /* cub::DeviceRadixSort::SortPairs call site (RAST/cuda_rasterizer/rasterizer_impl.cu:679-684):
- * stable ascending sort of (key, value) pairs on key bits [0, end_bit).  keys_in/values_in are
- * clobbered (used as ping-pong buffers); the result is in keys_out/values_out. */
+ * stable ascending sort of (key, value) pairs on key bits [0, end_bit), 8 bits per pass.  keys_in/values_in are
+ * clobbered (used as ping-pong buffers); the result is in keys_out/values_out.  One read of the keys builds the
+ * digit totals of all passes; every pass is then one kernel whose CTAs find their output positions by bounded
+ * look-back over the counts earlier tiles published (on expiry: device status word, see cgx_device_status). */
 size_t cgx_sort_workspace_bytes(int64_t n);
 int cgx_sort_pairs(int64_t n, int end_bit, uint64_t* keys_in, uint32_t* values_in, uint64_t* keys_out,
                    uint32_t* values_out, void* workspace, size_t workspace_bytes, void* stream);
+
+/* The same sort for a caller that owns both buffers and can choose where its pairs start (same call site: the
+ * reference's BinningState holds both the unsorted and the sorted arrays, rasterizer_impl.cu:188-205).  The pairs
+ * start in (keys_a, values_a); the result lands in (keys_a, values_a) when cgx_sort_passes(end_bit) is even and in
+ * (keys_b, values_b) when it is odd, so no copy is ever needed.  wait_limit_cycles: bound of the look-back wait in
+ * SM clock cycles, 0 = default (about 0.14 s). */
+int cgx_sort_passes(int end_bit);
+int cgx_sort_pairs_pingpong(int64_t n, int end_bit, uint64_t* keys_a, uint32_t* values_a, uint64_t* keys_b,
+                            uint32_t* values_b, void* workspace, size_t workspace_bytes,
+                            unsigned long long wait_limit_cycles, void* stream);
 
 
 /* No counterpart in the reference.  Same sort as cgx_sort_pairs for callers that may not allocate device
@@ -389,14 +401,15 @@ int cgx_render_bwd(int P, int W, int H, float tanfovx, float tanfovy, const uint
 /* ------------------------------------------------------------------ diagnostics */
 
 /* Host-synchronous.  Waits for `stream`, reads and clears the device status word that kernels set when a
- * bounded wait (blending mbarriers, peer barrier) gives up (0 = ok, CGX_ETIMEDOUT otherwise).  Replaces the reference's debug-mode
+ * bounded wait (blending mbarriers, peer barrier, the sort's look-back) gives up (0 = ok, CGX_ETIMEDOUT otherwise).  Replaces the reference's debug-mode
  * synchronise-and-throw (RAST/cuda_rasterizer/auxiliary.h:220-227); nothing ever traps. */
 int cgx_device_status(int* status_host, void* stream);
 
-/* The same two status words without waiting: queues their copies on `stream` into status_pinned_host2[0..1]
- * (page-locked host memory: blending kernels, peer barrier).  The caller looks at them after a synchronisation
- * it performs anyway (0 = ok); the words are not cleared (cgx_device_status clears them). */
-int cgx_device_status_async(int* status_pinned_host2, void* stream);
+/* The same status words without waiting: queues their copies on `stream` into status_pinned_host4[0..2]
+ * (page-locked host memory: blending kernels, peer barrier, sort look-back; [3] is reserved and set to 0).  The
+ * caller looks at them after a synchronisation it performs anyway (0 = ok); the words are not cleared
+ * (cgx_device_status clears them). */
+int cgx_device_status_async(int* status_pinned_host4, void* stream);
 
 
 #ifdef __cplusplus

@@ -9,15 +9,17 @@
 extern "C" {
 #endif
 
-/* Scatter strategy of the sort, for A/B timing and tests: -1 (default) chooses by size (unstaged while both
- * ping-pong buffers fit in L2, staged above), 0 always staged, 1 always unstaged.  Results are identical. */
+/* Pass structure of the sort, for A/B timing and tests: -1 (default) one kernel per pass with look-back
+ * ("one-sweep"); 0 three kernels per pass (histogram, scan, staged scatter); 1 three kernels per pass with the
+ * unstaged scatter.  Results are identical. */
 int cgx_set_sort_variant(int variant);
 
-/* A/B switches of the blending kernels (default 1 = culling only), for timing and tests:
- *   bit 0  per-warp culling of each batch before blending (forward and backward; results bit-identical);
- *   bit 1  backward: the per-channel "accumulated behind" recurrences contracted with the pixel cotangent
- *          (faster; leaves the 1e-3 gradient parity band on pixels whose plane-depth cotangent blows up);
- *   bit 2  backward: visits with one or two contributing pixels issue their atomics directly (measured slower). */
+/* A/B switch of the blending kernels (default 1):
+ *   bit 0  per-warp culling of each batch before blending (forward and backward);
+ *   bit 1  the reference-shaped walk (every lane looks at every surviving Gaussian; butterfly reduction of the
+ *          gradient terms in the backward) instead of the two-phase walk (every lane walks only its own
+ *          contributors; gradient terms staged in shared memory and summed per Gaussian).
+ * Forward outputs are bit-identical across the variants; gradients differ by the order of their sums. */
 int cgx_set_render_variant(int variant);
 
 #ifdef __cplusplus

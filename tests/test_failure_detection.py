@@ -39,10 +39,10 @@ def test_peer_barrier_wait_runs_out_and_reports(cuda_device):
     torch.cuda.synchronize()
     assert time.perf_counter() - t0 < 5.0                        # returned: did not wait for the default 2 s bound
     # the asynchronous read (pinned memory, no clearing) and the synchronous one agree
-    pinned = torch.zeros(2, dtype=torch.int32).pin_memory()
+    pinned = torch.zeros(4, dtype=torch.int32).pin_memory()
     assert l.cgx_device_status_async(C.c_void_p(pinned.data_ptr()), st) == 0
     torch.cuda.synchronize()
-    assert pinned.tolist() == [0, _lib.CGX_ETIMEDOUT]
+    assert pinned.tolist() == [0, _lib.CGX_ETIMEDOUT, 0, 0]
     assert l.cgx_device_status(C.byref(status), st) == 0 and status.value == _lib.CGX_ETIMEDOUT
     assert l.cgx_device_status(C.byref(status), st) == 0 and status.value == 0      # read clears
     assert int(mine[0]) == 1 and int(silent[0]) == 1 and int(mine[1]) == 0          # signalled, never answered

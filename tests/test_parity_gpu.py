@@ -254,23 +254,25 @@ def test_stats_collector_gets_render_times(cuda_device):
 
 
 def test_cull_variant_is_identical(cuda_device):
-    """Per-warp culling must not change a single bit of the forward outputs."""
+    """Per-warp culling and the two-phase walk must not change a single bit of the forward outputs, and the
+    gradients only by the order of their sums."""
     from diff_gaussian_rasterization import _lib
 
     g, cam = make_case(cfg=1, n=100000, res=(640, 360), big_scales=True)
     l = _lib.lib()
     try:
-        l.cgx_set_render_variant(1)
+        l.cgx_set_render_variant(1)      # default: culling + two-phase walk
         a = run_ours(g, cam, cuda_device, cot=cotangents(cam))
-        l.cgx_set_render_variant(0)      # no culling
+        l.cgx_set_render_variant(0)      # no culling, every lane looks at every Gaussian
         b = run_ours(g, cam, cuda_device, cot=cotangents(cam))
-        l.cgx_set_render_variant(5)      # culling + direct atomics for sparse visits
+        l.cgx_set_render_variant(3)      # culling, every lane looks at every surviving Gaussian
         c = run_ours(g, cam, cuda_device, cot=cotangents(cam))
     finally:
         l.cgx_set_render_variant(1)
     for k in ("color", "out_all_map", "out_plane_depth", "final_T", "n_contrib_px", "n_contrib2loss_px",
               "out_observe", "n_consider", "n_contrib"):
         assert torch.equal(a[k], b[k]), k
+        assert torch.equal(a[k], c[k]), k
     for k in GRADS:
         assert rel_l2(a[k], b[k]) <= 1e-5, k
         assert rel_l2(a[k], c[k]) <= 1e-5, k
@@ -437,9 +439,11 @@ def test_batched_preprocess_equals_per_camera(cuda_device):
         assert rel_l2(y.grad.cpu(), x.grad.cpu()) <= 1e-5
 
 
-@pytest.mark.parametrize("n", [1, 255, 4096, 4097, 1_000_003])
-def test_sort_pairs_variants(n, cuda_device):
-    """Both scatter strategies of the radix sort: identical output, equal to a stable sort on the masked key."""
+@pytest.mark.parametrize("n,end_bit", [(1, 45), (255, 45), (4096, 45), (4097, 45), (1_000_003, 45), (300_007, 47),
+                                       (70_001, 40), (5000, 33), (2_500_000, 47)])
+def test_sort_pairs_variants(n, end_bit, cuda_device):
+    """The one-sweep passes and both three-kernel scatter strategies: identical output, equal to a stable sort on
+    the masked key; through the copy-free ping-pong entry point and through the in -> out one."""
     import ctypes as C
 
     from diff_gaussian_rasterization import _lib
@@ -447,27 +451,38 @@ def test_sort_pairs_variants(n, cuda_device):
     l = _lib.lib()
     dev = cuda_device
     gen = torch.Generator().manual_seed(n)
-    keys = (torch.randint(0, 8160, (n,), generator=gen, dtype=torch.int64) << 32) | \
+    tiles = 32400 if end_bit == 47 else 8160
+    keys = (torch.randint(0, tiles, (n,), generator=gen, dtype=torch.int64) << 32) | \
         torch.randint(0, 1 << 32, (n,), generator=gen, dtype=torch.int64)
+    # few distinct depths in a part of the array: long runs of equal keys test stability
+    keys[: n // 3] &= ~torch.tensor(0xFFFFF, dtype=torch.int64)
     keys |= torch.randint(0, 2, (n,), generator=gen, dtype=torch.int64) << 50       # above end_bit: must be ignored
     vals = torch.arange(n, dtype=torch.int32)
     st = C.c_void_p(torch.cuda.current_stream().cuda_stream)
-    outs = []
+    order = torch.sort(keys & ((1 << end_bit) - 1), stable=True)[1]
+    passes = l.cgx_sort_passes(end_bit)
+    assert passes == (end_bit + 7) // 8
     try:
-        for variant in (0, 1):
+        for variant in (-1, 0, 1):
             l.cgx_set_sort_variant(variant)
+            ws = torch.empty(l.cgx_sort_workspace_bytes(n), dtype=torch.uint8, device=dev)
             kin, vin = keys.to(dev), vals.to(dev)
             kout, vout = torch.empty_like(kin), torch.empty_like(vin)
-            ws = torch.empty(l.cgx_sort_workspace_bytes(n), dtype=torch.uint8, device=dev)
-            assert l.cgx_sort_pairs(n, 45, kin.data_ptr(), vin.data_ptr(), kout.data_ptr(), vout.data_ptr(),
+            assert l.cgx_sort_pairs(n, end_bit, kin.data_ptr(), vin.data_ptr(), kout.data_ptr(), vout.data_ptr(),
                                     ws.data_ptr(), ws.numel(), st) == 0
             torch.cuda.synchronize()
-            outs.append((kout.cpu(), vout.cpu()))
+            assert torch.equal(vout.cpu().long(), order) and torch.equal(kout.cpu(), keys[order]), variant
+            ka, va = keys.to(dev), vals.to(dev)
+            kb, vb = torch.zeros_like(ka), torch.zeros_like(va)
+            assert l.cgx_sort_pairs_pingpong(n, end_bit, ka.data_ptr(), va.data_ptr(), kb.data_ptr(), vb.data_ptr(),
+                                             ws.data_ptr(), ws.numel(), 0, st) == 0
+            torch.cuda.synchronize()
+            k, v = (ka, va) if passes % 2 == 0 else (kb, vb)
+            assert torch.equal(v.cpu().long(), order) and torch.equal(k.cpu(), keys[order]), variant
     finally:
         l.cgx_set_sort_variant(-1)
-    order = torch.sort(keys & ((1 << 45) - 1), stable=True)[1]
-    for k, v in outs:
-        assert torch.equal(v.long(), order) and torch.equal(k, keys[order])
+    status = C.c_int(-1)
+    assert l.cgx_device_status(C.byref(status), st) == 0 and status.value == 0
 
 
 def test_plane_map_forward_and_backward(cuda_device):
