@@ -40,6 +40,8 @@ WORKLOADS = {
     "cfg2": (2, "6M Gaussians, 8 cameras 1600x1200 on a ring (data-parallel step)"),
     "cfg3": (3, "20M clustered Gaussians, 16 cameras 3840x2160 (load-imbalance stress)"),
     "cfg4": (4, "cfg2's scene at --gaussians N (capacity sweep), densification statistics updated every step"),
+    "redistribute": (None, "anchor redistribution: --gaussians rows per job (default 6M) of model state (parameters + "
+                           "both Adam moments + level tags, 916 bytes per row) moved to rank i % N in one exchange"),
 }
 
 
@@ -61,6 +63,8 @@ def parse_args():
     ap.add_argument("--no-parity", action="store_true", help="N>1: skip the correctness run on the reduced scene")
     ap.add_argument("--no-stage-events", action="store_true", help="do not bracket library calls with CUDA events")
     ap.add_argument("--no-clocks", action="store_true", help="do not sample nvidia-smi during the run")
+    ap.add_argument("--sort-variant", type=int, default=None,
+                    help="A/B timing: select a sort variant through the library's test-only switch")
     ap.add_argument("--render-variant", type=int, default=None,
                     help="A/B timing: select a blending kernel variant through the library's test-only switch")
     ap.add_argument("--cpu-sample-gaussians", type=int, default=None)
@@ -604,10 +608,77 @@ def multi_gpu_parity(dev, rank, world):
     return out
 
 
+def run_redistribute(a):
+    """Times cgx.exchange.redistribute_rows on a model-state-shaped list of tensors; one JSON line with GB/s."""
+    import torch.distributed as dist
+
+    from cgx import exchange
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+    if world == 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29533")
+    stdout_fd = os.dup(1)
+    os.dup2(2, 1)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    n = (a.gaussians or 6_000_000) // world
+    gen = torch.Generator(device=dev).manual_seed(7 + rank)
+    widths = {"anchor": 3, "offset": 30, "anchor_feat": 32, "opacity": 1, "scaling": 6, "rotation": 4}
+    tensors = []
+    for w in widths.values():                       # parameter, exp_avg, exp_avg_sq
+        tensors += [torch.randn(n, w, device=dev, generator=gen) for _ in range(3)]
+    tensors += [torch.randint(0, 6, (n, 1), device=dev, dtype=torch.int32, generator=gen),
+                torch.rand(n, device=dev, generator=gen)]
+    row_bytes = sum(t[0].numel() * t.element_size() for t in tensors)
+    # the reference's destination rule (scene/gaussian_model.py:1660-1662), applied to a shard that is NOT yet round-robin
+    dest = (torch.arange(n, device=dev) + rank) % world
+
+    def one():
+        out, _ = exchange.redistribute_rows(tensors, dest)
+        return out
+
+    for _ in range(max(a.warmup, 3)):
+        one()
+    dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(a.steps):
+        one()
+    e1.record()
+    dist.barrier()
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1) / a.steps], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    moved = n * world * row_bytes
+    if rank == 0:
+        line = {"metric": "anchor redistribution GB/s (rows x 916 B moved per second, whole job)",
+                "value": moved / (ms * 1e-3) / 1e9, "unit": "GB/s", "n_gpus": world, "steps": a.steps,
+                "warmup": max(a.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+                "vs_baseline": None, "dtype": "u32", "data": "synthetic",
+                "config": {"workload": "redistribute", "description": WORKLOADS["redistribute"][1],
+                           "rows": n * world, "row_bytes": row_bytes, "tensors": len(tensors),
+                           "rows_leaving_each_rank": n - n // world if world > 1 else 0},
+                "gpu_launches": 4}
+        sys.stdout.flush()
+        os.dup2(stdout_fd, 1)
+        print(json.dumps(line), flush=True)
+    dist.destroy_process_group()
+
+
 def main():
     a = parse_args()
     if a.impl == "reference":
         run_reference_arm(a)
+        return
+    if a.workload == "redistribute":
+        run_redistribute(a)
         return
 
     from cgx import synthetic as S
@@ -646,6 +717,8 @@ def main():
     lib = _lib.lib()
     if a.render_variant is not None:
         lib.cgx_set_render_variant(a.render_variant)
+    if a.sort_variant is not None:
+        lib.cgx_set_sort_variant(a.sort_variant)
 
     def barrier():
         if world > 1:

@@ -726,3 +726,136 @@ def all_to_all_communication_final(batched_rasterizers, batched_screenspace_para
     outs = _GaussianExchange.apply(plan, *flat)
     out = [[outs[8 * k + c] for k in range(bsz)] for c in range(8)]
     return (*out, sizes_list, sent_counts, send_index, stats)
+
+
+# ----------------------------------------------------------------------------------------------------------------
+# Row redistribution by a destination vector (the reference's anchor redistribution)
+def _as_words(t):
+    """A (N, ...) tensor as rows of 4-byte words: (tensor to move, words per row, how to turn received words back).
+    Rows whose byte size is not a multiple of 4 (bool / int8 / int16 tags) travel widened to int32."""
+    n = t.shape[0]
+    row_bytes = (t.numel() // n if n else int(np.prod(t.shape[1:], dtype=np.int64))) * t.element_size()
+    if t.dtype == torch.bool or row_bytes % 4:
+        wide = t.to(torch.int32).contiguous()
+        return wide, int(np.prod(t.shape[1:], dtype=np.int64)), (torch.int32, t.dtype)
+    return t.contiguous(), row_bytes // 4, (t.dtype, t.dtype)
+
+
+class _CudaRowsBackend:
+    """Counting / packing / splitting of redistributed rows on the GPU through the C ABI."""
+
+    def __init__(self):
+        from diff_gaussian_rasterization import _lib
+
+        self._lib, self.l = _lib, _lib.lib()
+
+    def count(self, dest32, ws):
+        n, dev = dest32.numel(), dest32.device
+        if not dest32.is_cuda:
+            raise RuntimeError("cgx.exchange: the row packing backend needs CUDA tensors (no CPU path)")
+        counts = torch.empty(ws + 1, dtype=torch.int32, device=dev)
+        work = torch.empty(self.l.cgx_rows_workspace_bytes(n, ws), dtype=torch.uint8, device=dev)
+        self._lib.check(self.l.cgx_rows_dest_count(n, ws, C.c_void_p(dest32.data_ptr()), C.c_void_p(counts.data_ptr()),
+                                                   C.c_void_p(work.data_ptr()), work.numel(),
+                                                   self._lib.current_stream_ptr()), "cgx_rows_dest_count")
+        return counts, work
+
+    def pack(self, dest32, ws, tensors, words, dst_base, first_row, work):
+        """dst_base: the (rows, row_words) int32 send buffer every destination's segment lives in, or one device
+        address per destination (a peer's arena)."""
+        n, k = dest32.numel(), len(tensors)
+        if isinstance(dst_base, torch.Tensor):
+            dst_base = [dst_base.data_ptr()] * ws
+        ptrs = (C.c_void_p * k)(*[t.data_ptr() for t in tensors])
+        w = (C.c_int32 * k)(*words)
+        base = (C.c_void_p * ws)(*[int(b) for b in dst_base])
+        first = (C.c_int64 * ws)(*[int(f) for f in first_row])
+        self._lib.check(self.l.cgx_rows_pack(n, ws, C.c_void_p(dest32.data_ptr()), k, ptrs, w, base, first,
+                                             C.c_void_p(work.data_ptr()), self._lib.current_stream_ptr()),
+                        "cgx_rows_pack")
+
+    def unpack(self, rows_ptr, n, outs, words):
+        k = len(outs)
+        ptrs = (C.c_void_p * k)(*[t.data_ptr() for t in outs])
+        w = (C.c_int32 * k)(*words)
+        if isinstance(rows_ptr, torch.Tensor):
+            rows_ptr = rows_ptr.data_ptr()
+        self._lib.check(self.l.cgx_rows_unpack(n, C.c_void_p(int(rows_ptr)), k, ptrs, w,
+                                               self._lib.current_stream_ptr()), "cgx_rows_unpack")
+
+
+_rows_backend = None
+
+
+def redistribute_rows(tensors, destination, group=None, backend=None, transport=None):
+    """Move row i of every tensor to rank ``destination[i]``: the reference's anchor redistribution
+    (scene/gaussian_model.py:1485-1558 ``all2all_gaussian_state`` applied to every parameter, both Adam moments and
+    the level tags by ``redistribute_gaussians`` :1683-1764 — about eighteen list all-to-alls) as ONE exchange.
+
+    ``tensors``: list of tensors with the same number of rows N (any shape behind the first dimension, any dtype);
+    ``destination``: (N,) integer tensor of ranks.  Returns ``(new_tensors, i2j_send_size)``: every tensor with the
+    rows this rank received — sources in ascending rank order, within a source ascending local index, exactly the
+    reference's ``torch.cat(state_from_gpuj)`` — and the (ws, ws) table of rows sent from i to j as nested lists.
+
+    One counting kernel, one host read of the gathered counts (the reference does the same read), one packing kernel
+    for all tensors (a travelling row is the concatenation of the tensors' rows), then either one
+    ``all_to_all_single`` (``transport="collective"``, any backend) or direct stores into the peers' symmetric-memory
+    arenas bracketed by the bounded device barrier (``"p2p"``, the default inside an NCCL group), one splitting kernel."""
+    global _rows_backend
+    ws, me = _world(group)
+    if backend is None:
+        if _rows_backend is None:
+            _rows_backend = _CudaRowsBackend()
+        backend = _rows_backend
+    n = destination.numel()
+    dev = destination.device
+    for t in tensors:
+        if t.shape[0] != n:
+            raise RuntimeError("redistribute_rows: every tensor needs one row per entry of `destination`")
+    dest32 = destination.to(torch.int32).contiguous()
+    moved = [_as_words(t.detach()) for t in tensors]
+    words = [m[1] for m in moved]
+    row_words = sum(words)
+
+    counts, work = backend.count(dest32, ws)
+    table = counts if dist.get_backend(group) == "nccl" else counts.cpu()
+    out = torch.empty(ws * (ws + 1), dtype=torch.int32, device=table.device)
+    dist.all_gather_into_tensor(out, table, group=group)
+    host = out.cpu().numpy().reshape(ws, ws + 1).astype(np.int64)          # the one host synchronisation
+    if host[:, ws].any():
+        raise RuntimeError("redistribute_rows: a destination outside [0, world_size)")
+    S = host[:, :ws]                                                        # S[i][j] = rows i sends to j
+    n_recv, n_send = int(S[:, me].sum()), int(S[me].sum())
+    if n_send != n:
+        raise RuntimeError("redistribute_rows: counted rows do not add up to the number of rows")
+
+    if transport is None:
+        import os
+
+        forced = os.environ.get("CGX_EXCHANGE", "").lower() in ("collective", "nccl")
+        transport = "p2p" if (not forced and dev.type == "cuda" and dist.get_backend(group) == "nccl") else "collective"
+    if transport == "p2p":
+        arena = _arena_for(group, dev)
+        arena.ensure(int(S.sum(0).max()) * row_words * 4, 0)
+        arena.begin_step()                     # every rank is done with whatever the arenas held
+        bases = [int(p) for p in arena.recv_hdl.buffer_ptrs]
+        if n:
+            backend.pack(dest32, ws, [m[0] for m in moved], words, bases, S[:me].sum(0).tolist(), work)
+        arena.barrier(2)                       # every rank's rows have landed
+        rows_ptr = arena.recv.data_ptr()
+        keep = arena.recv
+    else:
+        send = torch.empty(max(n_send, 1), max(row_words, 1), dtype=torch.int32, device=dev)
+        first = (np.cumsum(S[me]) - S[me]).tolist()
+        if n:
+            backend.pack(dest32, ws, [m[0] for m in moved], words, send, first, work)
+        recv = torch.empty(max(n_recv, 1), max(row_words, 1), dtype=torch.int32, device=dev)
+        dist.all_to_all_single(recv[:n_recv], send[:n_send], output_split_sizes=S[:, me].tolist(),
+                               input_split_sizes=S[me].tolist(), group=group)
+        rows_ptr, keep = recv.data_ptr(), recv
+    outs = [torch.empty((n_recv,) + tuple(t.shape[1:]), dtype=m[2][0], device=dev) for t, m in zip(tensors, moved)]
+    if n_recv:
+        backend.unpack(rows_ptr if transport == "p2p" else keep, n_recv, outs, words)
+    del keep
+    outs = [o if m[2][0] == m[2][1] else o.to(m[2][1]) for o, m in zip(outs, moved)]
+    return outs, S.tolist()

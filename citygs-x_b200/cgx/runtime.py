@@ -211,7 +211,15 @@ class TrainingStep:
         return self.params
 
     # ------------------------------------------------------------------ multi-GPU step
-    def _step_distributed(self):
+    def forward_only(self):
+        """The distributed forward pass without a graph (an evaluation render, or the reference's second exchange
+        for the nearest-view cameras, gaussian_renderer/__init__.py:1026,1439-1458): preprocess, exchange, render of
+        the local tile rows; no reverse exchange follows.  Returns the rendered (color, all_map, plane_depth) per
+        camera (None where this rank renders nothing)."""
+        with torch.no_grad():
+            return self._step_distributed(backward=False)
+
+    def _step_distributed(self, backward=True):
         from . import exchange
         from . import workload_division as WD
 
@@ -229,7 +237,8 @@ class TrainingStep:
         pre = self._preprocess_all(args[0], planes=fused)
         for k in range(len(self.cams)):
             means2D, _, conic_opacity, radii, depths = pre[k][:5]
-            means2D.retain_grad()
+            if means2D.requires_grad:
+                means2D.retain_grad()
             keep.append((radii, means2D))
             if fused:
                 screen.append((means2D, self.rgb[k], conic_opacity, radii, depths, pre[k][5]))
@@ -239,7 +248,7 @@ class TrainingStep:
                 m3, sc, rot = m3.detach(), sc.detach(), rot.detach()
             screen.append((means2D, self.rgb[k], conic_opacity, radii, depths, m3, sc, rot))
         pending, times = self._pending_stats, None
-        if self.lazy_balancer and pending is not None:
+        if backward and self.lazy_balancer and pending is not None:
             times = WD.local_running_times(pending[0], pending[1], ctx=self.ctx)
         (m2, rgb, co, rad, dep, m3, sc, rot, sizes, sent, send_index, stats) = \
             exchange.all_to_all_communication_final(rasts, screen, args, strategies, transport=self.transport,
@@ -252,6 +261,7 @@ class TrainingStep:
                               record="plane descriptors (16 floats fwd, 14 bwd)" if fused
                               else "3-D parameters (21 floats fwd, 19 or 9 bwd)")
         heads, grads = [], []
+        images = [None] * len(self.cams)
         if self.prefetch_counts:
             for k, strat in enumerate(strategies):
                 local = strat.get_compute_locally()
@@ -272,6 +282,9 @@ class TrainingStep:
                                                                     plane_depth)
             heads += [color, out_all_map, plane_depth]
             grads += self.cot[k]
+            images[k] = (color, out_all_map, plane_depth)
+        if not backward:
+            return images
         if not heads:
             # nothing to render on this rank, but the reverse exchange is collective: keep its node in the graph
             heads.append(m2[0].sum() * 0.0)

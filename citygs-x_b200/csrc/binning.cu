@@ -393,6 +393,9 @@ constexpr int OS_THREADS = 256;
 #ifndef CGX_OS_ITEMS
 #define CGX_OS_ITEMS 16
 #endif
+#ifndef CGX_OS_MIN_CTAS
+#define CGX_OS_MIN_CTAS 2
+#endif
 constexpr int OS_ITEMS = CGX_OS_ITEMS;
 constexpr int OS_TILE = OS_THREADS * OS_ITEMS;
 constexpr int OS_WARPS = OS_THREADS / 32;
@@ -444,7 +447,7 @@ os_hist_kernel(int64_t n, int passes, int end_bit, const uint64_t* __restrict__ 
     }
 }
 
-__global__ void __launch_bounds__(OS_THREADS, 2)
+__global__ void __launch_bounds__(OS_THREADS, CGX_OS_MIN_CTAS)
 os_pass_kernel(int64_t n, int shift, uint32_t mask, const uint64_t* __restrict__ keys_in,
                const uint32_t* __restrict__ vals_in, uint64_t* __restrict__ keys_out, uint32_t* __restrict__ vals_out,
                const uint32_t* __restrict__ ghist, uint32_t* __restrict__ ticket, uint32_t* __restrict__ status,
@@ -1089,8 +1092,8 @@ extern "C" int cgx_emit_keys(int P, int W, int H, const int32_t* radii, const fl
     return check_launch();
 }
 
-static int g_sort_variant = -1;  // test-only switch: -1 one-sweep (default); 0 three-kernel passes, staged scatter;
-                                 // 1 three-kernel passes, unstaged scatter
+static int g_sort_variant = -1;  // test-only switch: -1 three-kernel passes, scatter chosen by size (default);
+                                 // 0 staged scatter; 1 unstaged scatter; 2 one-sweep passes
 
 extern "C" int cgx_set_sort_variant(int variant)
 {
@@ -1148,7 +1151,7 @@ static int sort_passes_run(int variant, int64_t n, int end_bit, uint64_t* ka, ui
     if (passes == 0) return CGX_OK;
     uint64_t *kin = ka, *kout = kb;
     uint32_t *vin = va, *vout = vb;
-    const bool onesweep = variant < 0 && passes <= OS_MAX_PASSES && n < ((int64_t)1 << 30) &&
+    const bool onesweep = variant == 2 && passes <= OS_MAX_PASSES && n < ((int64_t)1 << 30) &&
                           workspace_bytes >= onesweep_sort_bytes(n, passes);
     if (onesweep) {
         const int ntiles = (int)((n + OS_TILE - 1) / OS_TILE);
@@ -1591,8 +1594,8 @@ extern "C" int cgx_sort_pairs_static(int64_t n, int end_bit, uint64_t* keys_in, 
     const int st = sort_static_scratch_ptr(&scratch);
     if (st != CGX_OK) return st;
     // the fixed scratch is sized for the three-kernel passes (digit tables only)
-    return sort_pairs_into_out(g_sort_variant < 0 ? 2 : g_sort_variant, n, end_bit, keys_in, values_in, keys_out, values_out,
-                               scratch, cgx::SORT_STATIC_BYTES, stream);
+    return sort_pairs_into_out(g_sort_variant == 2 ? -1 : g_sort_variant, n, end_bit, keys_in, values_in, keys_out,
+                               values_out, scratch, cgx::SORT_STATIC_BYTES, stream);
 }
 
 extern "C" int cgx_unpack_grad_add_cols(int n_ranges, const int64_t* range_start, const int64_t* range_stop, int ncols,

@@ -14,8 +14,9 @@ PKG = Path(__file__).resolve().parent
 ROOT = PKG.parent
 CSRC = ROOT / "csrc"
 LIBDIR = ROOT / "lib"
-SO = LIBDIR / "libcgx_raster.so"
-SOURCES = ["cabi.cu", "preprocess.cu", "binning.cu", "render.cu", "peer.cu", "loss.cu"]
+# CGX_RASTER_LIB: load another build of the same library (A/B timing of compile-time tile sizes); never a fallback
+SO = Path(os.environ["CGX_RASTER_LIB"]) if os.environ.get("CGX_RASTER_LIB") else LIBDIR / "libcgx_raster.so"
+SOURCES = ["cabi.cu", "preprocess.cu", "binning.cu", "render.cu", "peer.cu", "loss.cu", "redistribute.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-shared", "-Xcompiler", "-fPIC"]
 
@@ -78,6 +79,10 @@ SIGNATURES = {
     "cgx_local2j_pack_p2p_batched": (_i, [_i, _vp, _vp, _vp]),
     "cgx_pack_grad_rows_to": (_i, [_i, _vp, _vp, _i] + [_vp] * 7),
     "cgx_unpack_grad_add_cols": (_i, [_i, _vp, _vp, _i] + [_vp] * 9),
+    "cgx_rows_workspace_bytes": (_sz, [_i64, _i]),
+    "cgx_rows_dest_count": (_i, [_i64, _i, _vp, _vp, _vp, _sz, _vp]),
+    "cgx_rows_pack": (_i, [_i64, _i, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "cgx_rows_unpack": (_i, [_i64, _vp, _i, _vp, _vp, _vp]),
     "cgx_peer_barrier": (_i, [_i, _i, _vp, C.c_uint32, _vp]),
     "cgx_peer_barrier_limited": (_i, [_i, _i, _vp, C.c_uint32, C.c_uint64, _vp]),
     "cgx_bin_workspace_bytes": (_sz, [_i]),

@@ -285,6 +285,27 @@ int cgx_unpack_grad_add_cols(int n_ranges, const int64_t* range_start, const int
                              float* d_conic_opacity, float* d_means3D, float* d_scales, float* d_rotations,
                              void* stream);
 
+/* Row redistribution by a destination vector: the reference's anchor redistribution
+ * (scene/gaussian_model.py:1485-1558 all2all_gaussian_state -- `state[destination == j]` per destination, one list
+ * all-to-all per tensor -- driven by redistribute_gaussians :1683-1764) with all tensors packed into one exchange.
+ * A travelling row is the concatenation of the row of every tensor, in 4-byte words.
+ *   cgx_rows_dest_count  counts[j] = rows with destination j (j < ws), counts[ws] = 1 if some destination lies
+ *                        outside [0, ws) (such rows are dropped); leaves per-CTA prefixes in `workspace`.
+ *   cgx_rows_pack        stores row i of every tensor at row  dst_first_row[d] + (rows of destination d before i)
+ *                        of dst_base[d] (d = destination[i]; rows of `row_words` = sum of words_per_row words):
+ *                        ascending local index per destination, as the reference's boolean indexing.  dst_base[d] may
+ *                        be a segment owner's send buffer or another GPU's mapped memory (plain stores).
+ *   cgx_rows_unpack      splits n received rows back into the tensors.
+ * At most 32 destinations and 32 tensors per call; tensors are (rows, words_per_row[t]) arrays of 4-byte words. */
+size_t cgx_rows_workspace_bytes(int64_t n, int ws);
+int cgx_rows_dest_count(int64_t n, int ws, const int32_t* destination, int32_t* counts, void* workspace,
+                        size_t workspace_bytes, void* stream);
+int cgx_rows_pack(int64_t n, int ws, const int32_t* destination, int n_tensors, void* const* tensors,
+                  const int32_t* words_per_row, uint32_t* const* dst_base, const int64_t* dst_first_row,
+                  const void* workspace, void* stream);
+int cgx_rows_unpack(int64_t n, const uint32_t* rows, int n_tensors, void* const* tensors,
+                    const int32_t* words_per_row, void* stream);
+
 /* Stream-ordered barrier over the ranks of one NVLink/NVSwitch domain (no counterpart in the reference, which
  * synchronises through its collectives).  flag_ptrs: host array of `ws` device pointers, flag_ptrs[r] = an array
  * of at least 32 zero-initialised uint32 words living in rank r's memory and mapped in this process.  Call with
@@ -322,9 +343,8 @@ int cgx_emit_keys(int P, int W, int H, const int32_t* radii, const float* means2
 
 /* cub::DeviceRadixSort::SortPairs call site (RAST/cuda_rasterizer/rasterizer_impl.cu:679-684):
  * stable ascending sort of (key, value) pairs on key bits [0, end_bit), 8 bits per pass.  keys_in/values_in are
- * clobbered (used as ping-pong buffers); the result is in keys_out/values_out.  One read of the keys builds the
- * digit totals of all passes; every pass is then one kernel whose CTAs find their output positions by bounded
- * look-back over the counts earlier tiles published (on expiry: device status word, see cgx_device_status). */
+ * clobbered (used as ping-pong buffers); the result is in keys_out/values_out.  Per pass: per-tile digit
+ * histograms kept on chip, a scan of the digit rows, and a stable scatter; no kernel waits for another CTA. */
 size_t cgx_sort_workspace_bytes(int64_t n);
 int cgx_sort_pairs(int64_t n, int end_bit, uint64_t* keys_in, uint32_t* values_in, uint64_t* keys_out,
                    uint32_t* values_out, void* workspace, size_t workspace_bytes, void* stream);
@@ -332,8 +352,8 @@ int cgx_sort_pairs(int64_t n, int end_bit, uint64_t* keys_in, uint32_t* values_i
 /* The same sort for a caller that owns both buffers and can choose where its pairs start (same call site: the
  * reference's BinningState holds both the unsorted and the sorted arrays, rasterizer_impl.cu:188-205).  The pairs
  * start in (keys_a, values_a); the result lands in (keys_a, values_a) when cgx_sort_passes(end_bit) is even and in
- * (keys_b, values_b) when it is odd, so no copy is ever needed.  wait_limit_cycles: bound of the look-back wait in
- * SM clock cycles, 0 = default (about 0.14 s). */
+ * (keys_b, values_b) when it is odd, so no copy is ever needed.  wait_limit_cycles: only used by the test-only
+ * one-sweep variant (bound of its look-back wait in SM clock cycles, 0 = default of about 0.14 s). */
 int cgx_sort_passes(int end_bit);
 int cgx_sort_pairs_pingpong(int64_t n, int end_bit, uint64_t* keys_a, uint32_t* values_a, uint64_t* keys_b,
                             uint32_t* values_b, void* workspace, size_t workspace_bytes,

@@ -57,3 +57,39 @@ class OracleBackend:
         for a, c in segments:
             rows[a:a + c] = full[off:off + c]
             off += c
+
+
+class OracleRowsBackend:
+    """CPU stand-in for the row-redistribution kernels (cgx.exchange.redistribute_rows): tensor indexing only."""
+
+    def count(self, dest32, ws):
+        d = dest32.long()
+        bad = ((d < 0) | (d >= ws)).any().to(torch.int32).reshape(1)
+        counts = torch.bincount(d[(d >= 0) & (d < ws)], minlength=ws).to(torch.int32)
+        return torch.cat([counts, bad]), None
+
+    def pack(self, dest32, ws, tensors, words, dst_base, first_row, work):
+        assert isinstance(dst_base, torch.Tensor), "the CPU backend only serves the collective transport"
+        n = dest32.numel()
+        rows = torch.cat([t.reshape(n, -1).view(torch.int32) for t in tensors], dim=1)
+        for j in range(ws):
+            idx = (dest32 == j).nonzero().flatten()
+            dst_base[first_row[j]: first_row[j] + idx.numel()] = rows[idx]
+
+    def unpack(self, rows, n, outs, words):
+        off = 0
+        for o, w in zip(outs, words):
+            o.view(torch.int32).reshape(n, w).copy_(rows[:n, off:off + w])
+            off += w
+
+
+def redistribute_reference(states_per_rank, destinations_per_rank):
+    """The reference's loops, restated for all ranks of a group at once (scene/gaussian_model.py:1485-1515):
+    rank i sends state[destination == j] to rank j; rank j concatenates what it received, sources ascending.
+    states_per_rank[i]: list of tensors of rank i; returns the per-rank lists after the exchange."""
+    ws = len(states_per_rank)
+    out = []
+    for j in range(ws):
+        out.append([torch.cat([states_per_rank[i][t][destinations_per_rank[i] == j] for i in range(ws)], dim=0)
+                    for t in range(len(states_per_rank[0]))])
+    return out

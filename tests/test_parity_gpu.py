@@ -442,7 +442,7 @@ def test_batched_preprocess_equals_per_camera(cuda_device):
 @pytest.mark.parametrize("n,end_bit", [(1, 45), (255, 45), (4096, 45), (4097, 45), (1_000_003, 45), (300_007, 47),
                                        (70_001, 40), (5000, 33), (2_500_000, 47)])
 def test_sort_pairs_variants(n, end_bit, cuda_device):
-    """The one-sweep passes and both three-kernel scatter strategies: identical output, equal to a stable sort on
+    """Both three-kernel scatter strategies and the one-sweep passes: identical output, equal to a stable sort on
     the masked key; through the copy-free ping-pong entry point and through the in -> out one."""
     import ctypes as C
 
@@ -463,7 +463,7 @@ def test_sort_pairs_variants(n, end_bit, cuda_device):
     passes = l.cgx_sort_passes(end_bit)
     assert passes == (end_bit + 7) // 8
     try:
-        for variant in (-1, 0, 1):
+        for variant in (-1, 0, 1, 2):
             l.cgx_set_sort_variant(variant)
             ws = torch.empty(l.cgx_sort_workspace_bytes(n), dtype=torch.uint8, device=dev)
             kin, vin = keys.to(dev), vals.to(dev)

@@ -1,0 +1,113 @@
+"""Row redistribution by a destination vector (the reference's anchor redistribution, scene/gaussian_model.py:
+1485-1558 and 1683-1764): two gloo ranks on CPU against the restated reference loops, and the three kernels on one
+GPU against the same restatement (the "ranks" are separate buffers of one device).  Data movement: bit-exact."""
+import ctypes as C
+import os
+import socket
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def _states(rank, n, seed=5):
+    """A model-state-like list: parameters of several widths, Adam moments, integer and boolean tags."""
+    gen = torch.Generator().manual_seed(seed + rank)
+    anchor = torch.randn(n, 3, generator=gen)
+    offset = torch.randn(n, 10, 3, generator=gen)
+    feat = torch.randn(n, 32, generator=gen)
+    exp_avg = torch.randn(n, 32, generator=gen) * 1e-3
+    level = torch.randint(0, 6, (n, 1), generator=gen, dtype=torch.int32)
+    extra = torch.rand(n, generator=gen)
+    mask = torch.rand(n, generator=gen) > 0.5
+    ident = torch.arange(n, dtype=torch.int64) + 1_000_000 * rank
+    dest = torch.randint(0, 2, (n,), generator=gen, dtype=torch.int64)
+    return [anchor, offset, feat, exp_avg, level, extra, mask, ident], dest
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, ws, port, out_dir, sizes):
+    for p in (ROOT, ROOT / "citygs-x_b200", ROOT / "tests"):
+        sys.path.insert(0, str(p))
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=ws)
+    try:
+        from cgx import exchange
+        from oracle.exchange_backend import OracleRowsBackend
+
+        states, dest = _states(rank, sizes[rank])
+        out, table = exchange.redistribute_rows(states, dest, backend=OracleRowsBackend())
+        torch.save({"out": out, "table": table}, os.path.join(out_dir, f"rank{rank}.pt"))
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("sizes", [(1000, 777), (5, 0)])
+def test_two_gloo_ranks_match_the_reference_loops(tmp_path, sizes):
+    from oracle.exchange_backend import redistribute_reference
+
+    mp.spawn(_worker, args=(2, _free_port(), str(tmp_path), sizes), nprocs=2, join=True)
+    parts = [torch.load(tmp_path / f"rank{r}.pt", weights_only=False) for r in range(2)]
+    per_rank = [_states(r, sizes[r]) for r in range(2)]
+    want = redistribute_reference([s for s, _ in per_rank], [d for _, d in per_rank])
+    for r in range(2):
+        assert parts[r]["table"] == [[int((per_rank[i][1] == j).sum()) for j in range(2)] for i in range(2)]
+        for got, exp in zip(parts[r]["out"], want[r]):
+            assert got.dtype == exp.dtype and got.shape == exp.shape
+            assert torch.equal(got, exp)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("n", [0, 1, 255, 257, 100_003])
+def test_kernels_on_one_gpu(n, cuda_device):
+    """Three destinations as three buffers of the same device, with foreign rows in front of this rank's rows."""
+    from cgx.exchange import _CudaRowsBackend, _as_words
+    from oracle.exchange_backend import redistribute_reference
+
+    dev, ws = cuda_device, 3
+    states, _ = _states(0, n)
+    gen = torch.Generator().manual_seed(n)
+    dest = torch.randint(0, ws, (n,), generator=gen, dtype=torch.int64)
+    be = _CudaRowsBackend()
+    moved = [_as_words(t.to(dev)) for t in states]
+    words = [m[1] for m in moved]
+    row_words = sum(words)
+    d32 = dest.to(torch.int32).to(dev)
+    counts, work = be.count(d32, ws)
+    torch.cuda.synchronize()
+    assert counts.cpu().tolist() == [int((dest == j).sum()) for j in range(ws)] + [0]
+    if n == 0:
+        return
+    first = [3, 0, 11]
+    bufs = [torch.full((first[j] + int((dest == j).sum()), row_words), -7, dtype=torch.int32, device=dev)
+            for j in range(ws)]
+    be.pack(d32, ws, [m[0] for m in moved], words, [b.data_ptr() for b in bufs], first, work)
+    want = redistribute_reference([states] + [[t[:0] for t in states]] * (ws - 1),
+                                  [dest] + [dest[:0]] * (ws - 1))
+    for j in range(ws):
+        nj = int((dest == j).sum())
+        assert (bufs[j][: first[j]] == -7).all()
+        outs = [torch.empty((nj,) + tuple(t.shape[1:]), dtype=m[2][0], device=dev) for t, m in zip(states, moved)]
+        if nj:
+            be.unpack(bufs[j][first[j]:].contiguous(), nj, outs, words)
+        torch.cuda.synchronize()
+        for o, m, exp in zip(outs, moved, want[j]):
+            got = o if m[2][0] == m[2][1] else o.to(m[2][1])
+            assert torch.equal(got.cpu(), exp)
+    # a destination outside the group is reported, not followed
+    bad = d32.clone()
+    bad[n // 2] = ws
+    counts, _ = be.count(bad, ws)
+    assert int(counts[ws]) == 1
