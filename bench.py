@@ -741,9 +741,6 @@ def main():
             ms = float(t.item())
         return ms
 
-    # ---- multi-GPU: correctness of the distributed step on a reduced scene, before anything is timed
-    parity = multi_gpu_parity(dev, rank, world) if world > 1 and not a.no_parity else None
-
     # ---- device-resident measurement
     sampler = ClockSampler(local_rank)
     if rank == 0 and not a.no_clocks:
@@ -821,6 +818,10 @@ def main():
         ms_e2e = timed(step.run_e2e, a.steps) / a.steps
         e2e = {"value": mpix / (ms_e2e * 1e-3), "unit": "Mpix/s", "ms_per_step": ms_e2e,
                "h2d_bytes_per_step": step.h2d_bytes, "d2h_bytes_per_step": step.d2h_bytes}
+
+    # ---- multi-GPU: correctness of the distributed step on a reduced scene (after the timed regions: its
+    # allocations and collectives must not disturb them)
+    parity = multi_gpu_parity(dev, rank, world) if world > 1 and not a.no_parity else None
 
     # ---- the reference's own CUDA extension on the same GPU, same workload (rank 0, N=1 only)
     ref_gpu = None

@@ -27,8 +27,8 @@ the ranks' receive arenas are symmetric memory mapped into every peer, and ONE k
 packing and transport by storing each selected row straight into the final per-camera tensors of the rank that
 renders it (`cgx_local2j_pack_p2p`); the backward stores gradient rows straight into the source rank's staging
 buffer (`cgx_pack_grad_rows_to`).  Stream-ordered device barriers (symmetric-memory signal pads) order writers
-and readers; no send buffer, no collective, no unpack.  Tensors returned in this mode are views of the arena and
-stay valid until the next exchange of the same group.
+and readers; no send buffer, no collective, no unpack.  Tensors returned in this mode are views of one of two
+receive arenas that alternate exchanges use: they stay valid until the exchange after the next one of the group.
 
 The packing backend is injected (`backend=`): the product backend drives the CUDA kernels of the C ABI
 (cgx_local2j_count / cgx_local2j_pack / cgx_unpack_grad_add) and refuses CPU tensors; the CPU tests inject
@@ -79,6 +79,16 @@ class CudaPackBackend:
         self._lib.check(self.l.cgx_local2j_count(P, H, W, ws, self._p(means2D), self._p(radii), self._p(tile_bounds),
                                                  int(avoid), self._p(counts_out), self._p(workspace),
                                                  workspace.numel(), self._st()), "cgx_local2j_count")
+
+    def count_batched(self, cameras):
+        """cameras: list of (means2D, radii, tile_bounds, H, W, avoid, counts_out, workspace): two launches for all."""
+        table = np.zeros((len(cameras), 11), dtype=np.uint64)          # rows = struct cgx_count_camera
+        for k, (means2D, radii, tb, H, W, avoid, counts_out, workspace) in enumerate(cameras):
+            self._require_cuda(means2D)
+            table[k] = (means2D.shape[0], H, W, tb.numel() - 1, means2D.data_ptr(), radii.data_ptr(), tb.data_ptr(),
+                        int(bool(avoid)), counts_out.data_ptr(), workspace.data_ptr(), workspace.numel())
+        self._lib.check(self.l.cgx_local2j_count_batched(len(cameras), C.c_void_p(table.ctypes.data), self._st()),
+                        "cgx_local2j_count_batched")
 
     def pack(self, params, tile_bounds, H, W, avoid, row_offsets, send, send_aux, send_index, workspace):
         means2D, rgb, conic_opacity, radii, depths, means3D, scales, rotation = [t.contiguous() for t in params]
@@ -422,8 +432,13 @@ class PeerArena:
         self._symm = symm
         self.group = group if group is not None else dist.group.WORLD
         self.dev = device
-        self.recv = self.grad = None
-        self.recv_hdl = self.grad_hdl = None
+        # Two receive arenas, used by alternate steps: while a rank still reads what step s delivered (its render and
+        # backward passes), a peer that is already in step s + 1 writes into the other one; a peer can only reach
+        # step s + 2 through the "rows have landed" barrier of step s + 1, which this rank joins after it has queued
+        # everything of step s.  So no barrier is needed before the stores of a step.
+        self._recv = [None, None]
+        self._recv_hdl = [None, None]
+        self.grad = self.grad_hdl = None
         self.ws, self.me = dist.get_world_size(self.group), dist.get_rank(self.group)
         # flag words for the stream-ordered barrier: zeroed before any rank can signal
         self.flags = symm.empty(64, dtype=torch.int32, device=device)
@@ -431,11 +446,12 @@ class PeerArena:
         torch.cuda.synchronize(device)
         self.flags_hdl = symm.rendezvous(self.flags, self.group)
         dist.barrier(group=self.group)
-        # One exchange = one step of the arena.  The three barriers of step s carry the epochs 3s+1 (every rank is
-        # done with the arena's previous contents), 3s+2 (forward rows have landed) and 3s+3 (gradient rows have
-        # landed): absolute numbers, so a rank whose backward pass did not run (nothing of what it received reached
-        # its loss) cannot fall one barrier behind the others for the rest of the run.
+        # One exchange = one step of the arena.  The two barriers of step s carry the epochs 3s+2 (forward rows have
+        # landed) and 3s+3 (gradient rows have landed): absolute numbers, so a rank whose backward pass did not run
+        # (nothing of what it received reached its loss) cannot fall one barrier behind the others for the rest of
+        # the run.
         self.step = 0
+        self.last_grad_step = -1       # step of the latest exchange that built an autograd node
         self._flag_ptrs = (C.c_void_p * self.ws)(*[int(p) for p in self.flags_hdl.buffer_ptrs])
 
     def _alloc(self, nbytes):
@@ -443,18 +459,26 @@ class PeerArena:
         t = self._symm.empty(nbytes, dtype=torch.uint8, device=self.dev)
         return t, self._symm.rendezvous(t, self.group)
 
+    @property
+    def recv(self):
+        return self._recv[self.step & 1]
+
+    @property
+    def recv_hdl(self):
+        return self._recv_hdl[self.step & 1]
+
     def ensure(self, recv_bytes, grad_bytes):
         """Grow (collectively: every rank passes the same numbers) so that every rank's arenas hold these sizes."""
-        if self.recv is None or self.recv.numel() < recv_bytes:
-            self.recv, self.recv_hdl = self._alloc(recv_bytes)
-        if self.grad is None or self.grad.numel() < grad_bytes:
+        for p in (0, 1):
+            if self._recv[p] is None or self._recv[p].numel() < recv_bytes:
+                self._recv[p], self._recv_hdl[p] = self._alloc(recv_bytes)
+        if grad_bytes and (self.grad is None or self.grad.numel() < grad_bytes):
             self.grad, self.grad_hdl = self._alloc(grad_bytes)
 
     def begin_step(self):
-        """Start the next exchange: from here on the arena's previous contents (the tensors the previous exchange
-        returned, and its gradient rows) are dead."""
+        """Start the next exchange: it uses the other receive arena.  The tensors the exchange before the previous one
+        returned are dead from here on."""
         self.step += 1
-        self.barrier(1)
 
     def barrier(self, phase):
         """Stream-ordered barrier over the group: work queued before it on every rank is complete after it."""
@@ -546,11 +570,13 @@ class _GaussianExchangeP2P(torch.autograd.Function):
         ncols = plan["grad_cols"]
         planes = plan["planes"]
         n_out, n_in = (6, 4) if planes else (8, 6)
-        if arena.step != plan["arena_step"]:
+        if arena.last_grad_step != plan["arena_step"] or arena.step - plan["arena_step"] > 1:
             raise RuntimeError(
-                "cgx.exchange: the backward pass of a peer-to-peer exchange ran after a later exchange of the same "
-                "group had started; the tensors it returned (views of the receive arena) were overwritten.  Keep "
-                "one exchange in flight per group (backward before the next forward), or use transport='collective'")
+                "cgx.exchange: the backward pass of a peer-to-peer exchange ran too late: another exchange with a "
+                "graph, or two exchanges without one, have used the same group since its forward pass, and the "
+                "tensors it returned (views of a receive arena) or its gradient staging buffer were overwritten.  "
+                "Keep one differentiable exchange in flight per group (at most one forward-only exchange may come "
+                "between its forward and backward passes), or use transport='collective'")
         owner_base = np.array([int(p) for p in arena.grad_hdl.buffer_ptrs], dtype=np.int64)
         # segment (source i -> me, camera k) sits at row grad_row[i, k] of rank i's send order
         seg_ptr = owner_base[:, None] + plan["grad_row"] * (ncols * 4)                                # (ws, bsz)
@@ -624,7 +650,7 @@ def all_to_all_communication_final(batched_rasterizers, batched_screenspace_para
     n_extra = len(piggyback) if piggyback is not None else 0
     table_dev = torch.zeros(bsz * ws + n_extra, dtype=torch.int32, device=dev)
     counts_dev = table_dev[: bsz * ws].view(bsz, ws)
-    scratch, bounds = [], []
+    scratch, bounds, jobs, scattered = [], [], [], []
     for k in range(bsz):
         strat = batched_strategies[k]
         rs = batched_rasterizers[k].raster_settings
@@ -635,12 +661,19 @@ def all_to_all_communication_final(batched_rasterizers, batched_screenspace_para
         g0 = strat.gpu_ids[0]
         contiguous_ranks = list(strat.gpu_ids) == list(range(g0, g0 + wsk))
         c = counts_dev[k, g0:g0 + wsk] if contiguous_ranks else torch.zeros(wsk, dtype=torch.int32, device=dev)
-        backend.count(means2D.detach().contiguous(), radii.contiguous(), tb, rs.image_height, rs.image_width,
-                      batched_cuda_args[k]["avoid_pixel_all2all"], c, wspace)
+        jobs.append((means2D.detach().contiguous(), radii.contiguous(), tb, rs.image_height, rs.image_width,
+                     batched_cuda_args[k]["avoid_pixel_all2all"], c, wspace))
         if not contiguous_ranks:
-            counts_dev[k, torch.as_tensor(strat.gpu_ids, device=dev, dtype=torch.long)] = c
+            scattered.append((k, strat.gpu_ids, c))
         scratch.append(wspace)
         bounds.append(tb)
+    if hasattr(backend, "count_batched"):
+        backend.count_batched(jobs)              # every camera's counts in two launches
+    else:
+        for job in jobs:
+            backend.count(*job)
+    for k, ids, c in scattered:
+        counts_dev[k, torch.as_tensor(ids, device=dev, dtype=torch.long)] = c
     if dist.get_backend(group) != "nccl":
         table_dev = table_dev.cpu()
     transport = _pick_transport(transport, group, dev, backend)
@@ -698,6 +731,8 @@ def all_to_all_communication_final(batched_rasterizers, batched_screenspace_para
                     params=[tuple(t.detach() for t in p) for p in batched_screenspace_params],
                     hw=[(r.raster_settings.image_height, r.raster_settings.image_width) for r in batched_rasterizers],
                     avoid=[a["avoid_pixel_all2all"] for a in batched_cuda_args])
+        if torch.is_grad_enabled() and any(t.requires_grad for t in flat):
+            arena.last_grad_step = arena.step
         outs = _GaussianExchangeP2P.apply(plan, *flat)
         if planes:
             out = [[outs[6 * k + c] for k in range(bsz)] for c in range(6)] + [None, None]
@@ -837,7 +872,7 @@ def redistribute_rows(tensors, destination, group=None, backend=None, transport=
     if transport == "p2p":
         arena = _arena_for(group, dev)
         arena.ensure(int(S.sum(0).max()) * row_words * 4, 0)
-        arena.begin_step()                     # every rank is done with whatever the arenas held
+        arena.begin_step()
         bases = [int(p) for p in arena.recv_hdl.buffer_ptrs]
         if n:
             backend.pack(dest32, ws, [m[0] for m in moved], words, bases, S[:me].sum(0).tolist(), work)

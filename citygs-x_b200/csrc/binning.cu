@@ -639,6 +639,56 @@ local2j_scan_kernel(int nblocks, uint32_t* __restrict__ block_counts, int32_t* _
     if (threadIdx.x == 0) counts[blockIdx.x] = (int32_t)total;
 }
 
+// The counting stage of every camera of a batch in two launches (blockIdx.y = camera).
+constexpr int MAX_COUNT_CAMS = 16;
+struct CountCamera {
+    const float2* means2D;
+    const int* radii;
+    const int* bounds;
+    uint32_t* block_counts;
+    int32_t* counts;
+    int P, gx, gy, ws, nblocks, avoid;
+};
+struct CountBatch {
+    CountCamera cam[MAX_COUNT_CAMS];
+};
+
+__global__ void __launch_bounds__(PACK_TILE)
+local2j_count_batched_kernel(const __grid_constant__ CountBatch b)
+{
+    const CountCamera& c = b.cam[blockIdx.y];
+    if ((int)blockIdx.x >= c.nblocks) return;          // uniform over the CTA
+    __shared__ uint32_t s_cnt[MAX_WS];
+    if (threadIdx.x < MAX_WS) s_cnt[threadIdx.x] = 0;
+    __syncthreads();
+    const int i = blockIdx.x * PACK_TILE + threadIdx.x;
+    uint32_t bits = 0;
+    if (i < c.P) {
+        uint2 rect_min, rect_max;
+        get_rect(c.means2D[i], c.radii[i], rect_min, rect_max, c.gx, c.gy);
+        const int tmin = rect_min.y * c.gx + rect_min.x;
+        const int tmax = ((int)rect_max.y - 1) * c.gx + (int)rect_max.x - 1;
+        if (!(tmax < tmin))
+            for (int rk = 0; rk < c.ws; rk++)
+                if (touches_band(tmin, tmax, c.bounds[rk], c.bounds[rk + 1], c.gx, c.avoid != 0)) bits |= 1u << rk;
+    }
+    for (int rk = 0; rk < c.ws; rk++) {
+        const uint32_t m = __ballot_sync(0xffffffffu, (bits >> rk) & 1u);
+        if ((threadIdx.x & 31) == 0 && m) atomicAdd(&s_cnt[rk], __popc(m));
+    }
+    __syncthreads();
+    if (threadIdx.x < c.ws) c.block_counts[(size_t)threadIdx.x * c.nblocks + blockIdx.x] = s_cnt[threadIdx.x];
+}
+
+__global__ void __launch_bounds__(1024)
+local2j_scan_batched_kernel(const __grid_constant__ CountBatch b)
+{
+    const CountCamera& c = b.cam[blockIdx.y];
+    if ((int)blockIdx.x >= c.ws) return;               // uniform over the CTA
+    const uint32_t total = scan_row_inplace(c.block_counts + (size_t)blockIdx.x * c.nblocks, c.nblocks);
+    if (threadIdx.x == 0) c.counts[blockIdx.x] = (int32_t)total;
+}
+
 struct PackOffsets {
     long long row[MAX_WS];
 };
@@ -1297,6 +1347,52 @@ extern "C" int cgx_local2j_count(int P, int H, int W, int ws, const float* means
                                                         tile_bounds, avoid_pixel_all2all != 0, (uint32_t*)workspace);
     local2j_scan_kernel<<<ws, 1024, 0, st>>>(nblocks, (uint32_t*)workspace, counts);
     return check_launch(2);
+}
+
+extern "C" int cgx_local2j_count_batched(int n_cameras, const cgx_count_camera* cams, void* stream)
+{
+    if (n_cameras < 0 || (n_cameras > 0 && !cams)) return CGX_EINVAL;
+    cudaStream_t st = (cudaStream_t)stream;
+    int k0 = 0;
+    while (k0 < n_cameras) {
+        CountBatch b;
+        memset(&b, 0, sizeof(b));
+        int n = 0, max_blocks = 0, max_ws = 0;
+        for (; k0 + n < n_cameras && n < MAX_COUNT_CAMS; n++) {
+            const cgx_count_camera& c = cams[k0 + n];
+            if (c.P < 0 || c.W <= 0 || c.H <= 0 || c.ws <= 0 || c.ws > MAX_WS || !c.counts) return CGX_EINVAL;
+            CountCamera& x = b.cam[n];
+            x.P = (int)c.P;
+            x.ws = (int)c.ws;
+            x.gx = ((int)c.W + CGX_BLOCK_X - 1) / CGX_BLOCK_X;
+            x.gy = ((int)c.H + CGX_BLOCK_Y - 1) / CGX_BLOCK_Y;
+            x.nblocks = (x.P + PACK_TILE - 1) / PACK_TILE;
+            x.avoid = c.avoid_pixel_all2all != 0;
+            x.counts = c.counts;
+            if (x.P == 0) {
+                cudaError_t e = cudaMemsetAsync(c.counts, 0, x.ws * sizeof(int32_t), st);
+                if (e != cudaSuccess) { set_cuda_error(e); return CGX_ECUDA; }
+                x.ws = 0;                      // nothing to scan for this camera
+                continue;
+            }
+            if (!c.means2D || !c.radii || !c.tile_bounds || !c.workspace || ((uintptr_t)c.means2D & 7)) return CGX_EINVAL;
+            if ((size_t)c.workspace_bytes < cgx_local2j_workspace_bytes(x.P, x.ws)) return CGX_ENOMEM;
+            x.means2D = (const float2*)c.means2D;
+            x.radii = c.radii;
+            x.bounds = c.tile_bounds;
+            x.block_counts = (uint32_t*)c.workspace;
+            if (x.nblocks > max_blocks) max_blocks = x.nblocks;
+            if (x.ws > max_ws) max_ws = x.ws;
+        }
+        if (max_blocks > 0) {
+            local2j_count_batched_kernel<<<dim3((unsigned)max_blocks, (unsigned)n), PACK_TILE, 0, st>>>(b);
+            local2j_scan_batched_kernel<<<dim3((unsigned)max_ws, (unsigned)n), 1024, 0, st>>>(b);
+            const int rc = check_launch(2);
+            if (rc != CGX_OK) return rc;
+        }
+        k0 += n;
+    }
+    return CGX_OK;
 }
 
 extern "C" int cgx_local2j_pack(int P, int H, int W, int ws, const float* means2D, const float* rgb,

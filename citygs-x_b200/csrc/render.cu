@@ -22,6 +22,10 @@
 // status word, stops blending and returns.
 #include "cgx_common.cuh"
 
+#ifndef CGX_EXPERIMENT
+#define CGX_EXPERIMENT 0   // timing experiments only: bit 0 skip phase 1, bit 1 skip phase 2, bit 2 skip phase 3
+#endif
+
 namespace cgx {
 
 __device__ int g_status = 0;  // 0 ok; CGX_ETIMEDOUT when a bounded wait gave up
@@ -33,6 +37,13 @@ struct __align__(16) Record {
     float4 q1;  // conic c, opacity, r, g
     float4 q2;  // b, m0, m1, m2
     float4 q3;  // m3, m4, cull half-extent x, cull half-extent y (see cull_extent)
+};
+
+// A record as the forward kernel keeps it in shared memory: 80-byte pitch.  In the two-phase walk every lane reads
+// the record of a DIFFERENT Gaussian; at the natural 64-byte pitch eight lanes of a quarter-warp would hit the same
+// two groups of four banks, at 80 bytes consecutive records fall into all eight groups.
+struct __align__(16) RecSlot : Record {
+    float4 pad;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -106,6 +117,24 @@ __device__ __forceinline__ bool eval_alpha(const float4 q0, const float2 q1xy, c
     return !(alpha < 1.0f / 255.0f);
 }
 
+// Pixel mask of one Gaussian over a warp's 8x4 pixel block (bit y * 8 + x = lane of that pixel): alpha is evaluated
+// only at the pixels inside the Gaussian's safe box, by ONE lane, so 32 Gaussians are tested at once and a small
+// splat costs a handful of evaluations instead of 32.  Same eval_alpha as the pixel's own walk: same bits.
+__device__ __forceinline__ uint32_t block_pixel_mask(const float4 q0, const float2 q1xy, const float ex, const float ey,
+                                                     const float sx0, const float sy0)
+{
+    const int x0 = max(0, (int)ceilf(q0.x - ex - sx0)), x1 = min(7, (int)floorf(q0.x + ex - sx0));
+    const int y0 = max(0, (int)ceilf(q0.y - ey - sy0)), y1 = min(3, (int)floorf(q0.y + ey - sy0));
+    uint32_t pm = 0;
+    for (int y = y0; y <= y1; y++)
+        for (int x = x0; x <= x1; x++) {
+            float2 d;
+            float G, alpha;
+            if (eval_alpha(q0, q1xy, make_float2(sx0 + (float)x, sy0 + (float)y), d, G, alpha)) pm |= 1u << (y * 8 + x);
+        }
+    return pm;
+}
+
 // ------------------------------------------------------------------------------------------------ pack
 __global__ void __launch_bounds__(256)
 pack_records_kernel(int P, const int* __restrict__ radii, const float2* __restrict__ means2D,
@@ -139,7 +168,7 @@ constexpr int RENDER_THREADS = CGX_BLOCK_SIZE;
 constexpr int RENDER_WARPS = RENDER_THREADS / 32;
 
 struct FwdSmem {
-    Record rec[2][CGX_BLOCK_SIZE];
+    RecSlot rec[2][CGX_BLOCK_SIZE];
     int id[2][CGX_BLOCK_SIZE];
     uint8_t hits[RENDER_WARPS][CGX_BLOCK_SIZE];
     uint64_t bar[2];
@@ -242,7 +271,7 @@ render_fwd_kernel(const uint2* __restrict__ ranges, const uint32_t* __restrict__
         if (i + 1 < rounds) issue(i + 1, buf ^ 1);
 
         const int nb = min(CGX_BLOCK_SIZE, toDo);
-        const Record* rec = sm.rec[buf];
+        const RecSlot* rec = sm.rec[buf];
         const int* ids = sm.id[buf];
         const uint32_t contributor_base = (uint32_t)i * CGX_BLOCK_SIZE;
 
@@ -267,19 +296,20 @@ render_fwd_kernel(const uint2* __restrict__ ranges, const uint32_t* __restrict__
                 for (int base = 0; base < n_hits; base += 32) {
                     if (__all_sync(0xffffffffu, done)) break;
                     const int g = min(32, n_hits - base);
-                    // phase 1: one bit per visit whose alpha passes both tests at this pixel
-                    uint32_t mine = 0;
-                    if (!done) {
-                        for (int v = 0; v < g; v++) {
-                            const int j = my_hits[base + v];
-                            const float4 q0 = rec[j].q0;
-                            const float2 q1xy = *reinterpret_cast<const float2*>(&rec[j].q1);
-                            float2 d;
-                            float G, alpha;
-                            if (eval_alpha(q0, q1xy, pixf, d, G, alpha)) mine |= 1u << v;
-                        }
+                    // phase 1: lane v tests Gaussian v against the block's pixels (only those in its safe box) ...
+                    uint32_t pm = 0;
+                    if (lane < g && !(CGX_EXPERIMENT & 1)) {
+                        const int j = my_hits[base + lane];
+                        const float4 q3 = rec[j].q3;
+                        pm = block_pixel_mask(rec[j].q0, *reinterpret_cast<const float2*>(&rec[j].q1), q3.z, q3.w, sx0,
+                                              sy0);
                     }
+                    // ... and every pixel collects its own bit of each mask: one bit per visit that reaches it
+                    uint32_t mine = 0;
+                    for (int v = 0; v < g; v++) mine |= ((__shfl_sync(0xffffffffu, pm, v) >> lane) & 1u) << v;
+                    if (done || (CGX_EXPERIMENT & 2)) mine = 0;
                     // phase 2: this pixel's own contributors, front to back
+                    uint32_t seen_clear = 0;      // visits this pixel blended while its transmittance was above 0.5
                     while (mine) {
                         const int v = __ffs(mine) - 1;
                         mine &= mine - 1;
@@ -303,9 +333,19 @@ render_fwd_kernel(const uint2* __restrict__ ranges, const uint32_t* __restrict__
                             const float am[CGX_NMAP] = {q2.y, q2.z, q2.w, q3.x, q3.y};
                             for (int ch = 0; ch < CGX_NMAP; ch++) All_map[ch] += am[ch] * alpha * T;
                         }
-                        if (T > 0.5) atomicAdd(&(out_observe[ids[j]]), 1);
+                        if (T > 0.5) seen_clear |= 1u << v;
                         T = test_T;
                         last_contributor = contributor_base + j + 1;
+                    }
+                    // out_observe: one atomic per Gaussian with the number of such pixels (lanes walking their own
+                    // lists would otherwise issue one atomic per pixel, to as many addresses as lanes)
+                    if (__any_sync(0xffffffffu, seen_clear != 0)) {
+                        int cnt = 0;
+                        for (int v = 0; v < g; v++) {
+                            const int c = __popc(__ballot_sync(0xffffffffu, (seen_clear >> v) & 1u));
+                            if (lane == v) cnt = c;
+                        }
+                        if (cnt) atomicAdd(&(out_observe[ids[my_hits[base + lane]]]), cnt);
                     }
                 }
             } else
@@ -646,7 +686,8 @@ __device__ __forceinline__ void bwd_pixel_init(BwdPixel& px, bool inside, uint32
     if (rounds > 0) issue(0, 0)
 
 // Culls the staged batch against this warp's 8x4 pixel block: slots whose safe box meets the block, in order.
-__device__ __forceinline__ int cull_batch(const Record* rec, int nb, int lane, float sx0, float sx1, float sy0,
+template <typename REC>
+__device__ __forceinline__ int cull_batch(const REC* rec, int nb, int lane, float sx0, float sx1, float sy0,
                                           float sy1, uint8_t* my_hits)
 {
     int n_hits = 0;
@@ -738,8 +779,17 @@ constexpr int BWD_CAP = CGX_BWD_CAP;  // gradient rows a warp stages per group o
 constexpr int BWD_RS = 20;            // floats per staged row: 16 terms, 80-byte pitch (spreads rows over the banks)
 static_assert(BWD_CAP >= 32 && BWD_CAP % 4 == 0, "a group must hold at least one full visit");
 
+#ifndef CGX_BWD_REC80
+#define CGX_BWD_REC80 0     // 1: 80-byte record pitch in the backward as well (needs a smaller gradient table)
+#endif
+#if CGX_BWD_REC80
+typedef RecSlot BwdRec;
+#else
+typedef Record BwdRec;
+#endif
+
 struct BwdSmem2 {
-    Record rec[2][CGX_BLOCK_SIZE];
+    BwdRec rec[2][CGX_BLOCK_SIZE];
     int id[2][CGX_BLOCK_SIZE];
     float stage[RENDER_WARPS][BWD_CAP * BWD_RS];
     uint8_t hits[RENDER_WARPS][CGX_BLOCK_SIZE];
@@ -776,7 +826,7 @@ render_bwd2_kernel(const uint2* __restrict__ ranges, const uint32_t* __restrict_
         if (warp_idle) continue;
 
         const int nb = min(CGX_BLOCK_SIZE, toDo);
-        const Record* rec = sm.rec[buf];
+        const BwdRec* rec = sm.rec[buf];
         const int* ids = sm.id[buf];
         // batch slot j holds sorted position range.y - 1 - (i*256 + j); its 0-based index in the tile list is
         // total - 1 - (i*256 + j), which is the reference's `contributor` after its decrement.
@@ -784,20 +834,26 @@ render_bwd2_kernel(const uint2* __restrict__ ranges, const uint32_t* __restrict_
         uint8_t* my_hits = sm.hits[warp];
         const int n_hits = cull_batch(rec, nb, lane, sx0, sx1, sy0, sy1, my_hits);
 
-        int base = 0;
-        while (base < n_hits) {
+        for (int base = 0; base < n_hits; base += 32) {
             // ---- phase 1: which pixels does each visit reach?  Lane v keeps the pixel mask of visit v, every lane
-            // keeps the visit mask of its own pixel.  The group ends after 32 visits or when its rows fill the table.
+            // keeps the visit mask of its own pixel.  A chunk of 32 visits is cut into groups whose rows fit the table.
+            // Lane v tests Gaussian v against the block's pixels; then every pixel keeps its own bit of each mask if
+            // the Gaussian lies before the pixel's last contributor.
+            const int g_max = min(32, n_hits - base);
+            uint32_t pm = 0;
+            if (lane < g_max && !(CGX_EXPERIMENT & 1)) {
+                const int j = my_hits[base + lane];
+                const float4 q3 = rec[j].q3;
+                pm = block_pixel_mask(rec[j].q0, *reinterpret_cast<const float2*>(&rec[j].q1), q3.z, q3.w, sx0, sy0);
+            }
+            int v0 = 0;      // visits [v0, v0 + g) of this chunk form the current group
+            while (v0 < g_max) {
             uint32_t mine = 0, visit_mask = 0;
             int rows = 0, g = 0;
-            while (g < 32 && base + g < n_hits && rows <= BWD_CAP - 32) {
-                const int j = my_hits[base + g];
-                bool valid = false;
-                if (idx_base - (uint32_t)j < (uint32_t)last_contributor) {
-                    float2 d;
-                    float G, alpha;
-                    valid = eval_alpha(rec[j].q0, *reinterpret_cast<const float2*>(&rec[j].q1), pixf, d, G, alpha);
-                }
+            while (v0 + g < g_max && rows <= BWD_CAP - 32) {
+                const int j = my_hits[base + v0 + g];
+                const bool valid = ((__shfl_sync(0xffffffffu, pm, v0 + g) >> lane) & 1u) &&
+                                   (idx_base - (uint32_t)j < (uint32_t)last_contributor);
                 const uint32_t m = __ballot_sync(0xffffffffu, valid);
                 if (lane == g) visit_mask = m;
                 mine |= (valid ? 1u : 0u) << g;
@@ -816,6 +872,7 @@ render_bwd2_kernel(const uint2* __restrict__ ranges, const uint32_t* __restrict_
                 const int first_row = incl - cnt;
 
                 // ---- phase 2: every lane walks its own contributors, back to front, and stages their terms
+                if (CGX_EXPERIMENT & 2) mine = 0;
                 for (;;) {
                     const bool act = mine != 0;
                     if (!__any_sync(0xffffffffu, act)) break;
@@ -824,7 +881,7 @@ render_bwd2_kernel(const uint2* __restrict__ ranges, const uint32_t* __restrict_
                     const int rv = __shfl_sync(0xffffffffu, first_row, v);
                     if (act) {
                         mine &= mine - 1;
-                        const int j = my_hits[base + v];
+                        const int j = my_hits[base + v0 + v];
                         float2 d;
                         float G, alpha;
                         eval_alpha(rec[j].q0, *reinterpret_cast<const float2*>(&rec[j].q1), pixf, d, G, alpha);
@@ -841,8 +898,8 @@ render_bwd2_kernel(const uint2* __restrict__ ranges, const uint32_t* __restrict_
 
                 // ---- phase 3: two visits at a time, one half-warp each, lane = term: sum the visit's rows and add
                 // the total to the Gaussian's gradient with one atomic per term
-                for (int v0 = 0; v0 < g; v0 += 2) {
-                    const int v = v0 + half;          // v == g (odd group) reads an empty mask
+                for (int pair0 = 0; pair0 < ((CGX_EXPERIMENT & 4) ? 0 : g); pair0 += 2) {
+                    const int v = pair0 + half;       // v == g (odd group) reads an empty mask
                     const uint32_t mv = __shfl_sync(0xffffffffu, visit_mask, v & 31);
                     const int rv = __shfl_sync(0xffffffffu, first_row, v & 31);
                     const int n = v < g ? __popc(mv) : 0;
@@ -850,12 +907,13 @@ render_bwd2_kernel(const uint2* __restrict__ ranges, const uint32_t* __restrict_
                         const float* p = stage + rv * BWD_RS + term;
                         float sum = 0.f;
                         for (int r = 0; r < n; r++) sum += p[r * BWD_RS];
-                        if (my_ptr) atomicAdd(my_ptr + (size_t)ids[my_hits[base + v]] * my_stride, sum);
+                        if (my_ptr) atomicAdd(my_ptr + (size_t)ids[my_hits[base + v0 + v]] * my_stride, sum);
                     }
                 }
                 __syncwarp();
             }
-            base += g;
+            v0 += g;
+            }
         }
     }
     if (failed && lane == 0) atomicExch(&g_status, CGX_ETIMEDOUT);

@@ -70,6 +70,7 @@ SIGNATURES = {
     "cgx_depth_normal_bwd": (_i, [_i, _i, _f, _f, _f, _f, _vp, _vp, _vp, _vp]),
     "cgx_local2j_mask": (_i, [_i, _i, _i, _i, _vp, _vp, _vp, _i, _vp, _vp]),
     "cgx_local2j_count": (_i, [_i, _i, _i, _i, _vp, _vp, _vp, _i, _vp, _vp, _sz, _vp]),
+    "cgx_local2j_count_batched": (_i, [_i, _vp, _vp]),
     "cgx_local2j_workspace_bytes": (_sz, [_i, _i]),
     "cgx_local2j_pack": (_i, [_i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "cgx_unpack_grad_add": (_i, [_i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),

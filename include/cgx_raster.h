@@ -273,6 +273,20 @@ typedef struct cgx_exchange_camera {
 } cgx_exchange_camera;
 int cgx_local2j_pack_p2p_batched(int n_cameras, const cgx_exchange_camera* cams /* host */, int32_t* send_index,
                                  void* stream);
+/* The counting stage (cgx_local2j_count) of every camera of a batch in two launches; same reference call site,
+ * gaussian_renderer/workload_division.py:721-744 inside the camera loop of gaussian_renderer/__init__.py:612-660.
+ * All members are 8 bytes wide; counts: device, ws entries per camera (they may lie anywhere, e.g. in one table). */
+typedef struct cgx_count_camera {
+    int64_t P, H, W, ws;
+    const float* means2D;
+    const int32_t* radii;
+    const int32_t* tile_bounds;            /* device, ws + 1 entries */
+    int64_t avoid_pixel_all2all;
+    int32_t* counts;                       /* device, ws entries */
+    void* workspace;                       /* device, cgx_local2j_workspace_bytes(P, ws) */
+    uint64_t workspace_bytes;
+} cgx_count_camera;
+int cgx_local2j_count_batched(int n_cameras, const cgx_count_camera* cams /* host */, void* stream);
 int cgx_pack_grad_rows_to(int n_segments, float* const* seg_rows, const int64_t* seg_count, int ncols,
                           const float* d_means2D, const float* d_rgb, const float* d_conic_opacity,
                           const float* d_means3D, const float* d_scales, const float* d_rotations, void* stream);

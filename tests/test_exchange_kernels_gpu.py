@@ -55,6 +55,20 @@ def test_counts_match_oracle_mask(setup):
         assert sum(len(w) for w in c["want"]) > N // 10           # the case actually selects rows
 
 
+def test_batched_count_equals_per_camera_count(setup, cuda_device):
+    """Every camera's counts in two launches, written into one (cameras, ranks) table."""
+    be, bounds, cams = setup
+    ws = bounds.numel() - 1
+    table = torch.full((len(cams), ws), -1, dtype=torch.int32, device=cuda_device)
+    spaces = [be.workspace(N, ws, cuda_device) for _ in cams]
+    be.count_batched([(c["gpu"][0], c["gpu"][3], bounds, H, W, False, table[k], spaces[k]) for k, c in enumerate(cams)])
+    torch.cuda.synchronize()
+    for k, c in enumerate(cams):
+        assert table[k].cpu().tolist() == c["counts"].tolist()
+        used = (N + 255) // 256 * ws * 4                               # bytes of per-tile prefixes (the rest is padding)
+        assert torch.equal(spaces[k][:used].cpu(), c["wspace"][:used].cpu())     # what the pack kernel reads
+
+
 @pytest.mark.parametrize("avoid", [False, True])
 def test_mask_equals_reference_kernel(setup, cuda_device, reference_C, avoid):
     """The (P, ws) band mask against the reference's own getTouchedIdsBool (rasterize_points.cu:445-524), bit for

@@ -174,8 +174,10 @@ def _forward_only_worker(rank, ws, port, out_dir):
         assert any(im is not None for im in images)
         step.run()
         torch.cuda.synchronize()
-        same = all(torch.allclose(first[k], v.grad, rtol=1e-4, atol=1e-7) for k, v in step.params.items())
-        torch.save({"same": same}, os.path.join(out_dir, f"rank{rank}.pt"))
+        # the balancer may have moved its cut between the two steps: same sums in another order
+        err = max(float((first[k].double() - v.grad.double()).norm() / first[k].double().norm())
+                  for k, v in step.params.items())
+        torch.save({"same": err <= 1e-3, "err": err}, os.path.join(out_dir, f"rank{rank}.pt"))
         dist.barrier()
     finally:
         dist.destroy_process_group()
@@ -187,4 +189,5 @@ def test_forward_only_exchange_between_steps(tmp_path):
     import torch.multiprocessing as mp
 
     mp.spawn(_forward_only_worker, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
-    assert all(torch.load(tmp_path / f"rank{r}.pt", weights_only=False)["same"] for r in range(2))
+    parts = [torch.load(tmp_path / f"rank{r}.pt", weights_only=False) for r in range(2)]
+    assert all(p["same"] for p in parts), [p["err"] for p in parts]
