@@ -63,6 +63,8 @@ def parse_args():
     ap.add_argument("--no-parity", action="store_true", help="N>1: skip the correctness run on the reduced scene")
     ap.add_argument("--no-stage-events", action="store_true", help="do not bracket library calls with CUDA events")
     ap.add_argument("--no-clocks", action="store_true", help="do not sample nvidia-smi during the run")
+    ap.add_argument("--render-streams", type=int, default=None,
+                    help="single-GPU step: cameras alternate between this many CUDA streams")
     ap.add_argument("--sort-variant", type=int, default=None,
                     help="A/B timing: select a sort variant through the library's test-only switch")
     ap.add_argument("--render-variant", type=int, default=None,
@@ -710,6 +712,8 @@ def main():
     step = RT.TrainingStep(g, cams, dev, rank=rank, world_size=world)
     if a.densification_stats or a.workload == "cfg4":
         step.enable_densification_stats()
+    if a.render_streams is not None:
+        step.render_streams = a.render_streams
     mpix = sum(c.W * c.H for c in cams) / 1e6
     n_scene = g["means3D"].shape[0]
 
@@ -725,13 +729,16 @@ def main():
             torch.distributed.barrier()
         torch.cuda.synchronize()
 
-    def timed(fn, steps):
-        """K steps bracketed by barrier+sync; device time by CUDA events; max over ranks."""
+    def timed(fn, steps, join=None):
+        """K steps bracketed by barrier+sync; device time by CUDA events; max over ranks.  `join`: called after the
+        last step and before the closing event, to put that event behind work queued on other streams."""
         barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         for _ in range(steps):
             fn()
+        if join is not None:
+            join()
         e1.record()
         barrier()
         ms = e0.elapsed_time(e1)
@@ -815,7 +822,7 @@ def main():
     if not a.no_e2e:
         for _ in range(2):
             step.run_e2e()
-        ms_e2e = timed(step.run_e2e, a.steps) / a.steps
+        ms_e2e = timed(step.run_e2e, a.steps, join=step.join_e2e) / a.steps
         e2e = {"value": mpix / (ms_e2e * 1e-3), "unit": "Mpix/s", "ms_per_step": ms_e2e,
                "h2d_bytes_per_step": step.h2d_bytes, "d2h_bytes_per_step": step.d2h_bytes}
 

@@ -53,6 +53,7 @@ class TrainingStep:
         self.lazy_balancer = True
         self._pending_stats = None
         self._copy_stream = None
+        self._d2h_stream = None
         self._cot_events = None         # per camera: event after which its upstream-gradient images are on the device
         # True: gradients of the plane descriptors flow back to means3D / rotations (through the reverse exchange
         # when distributed: 19-float gradient rows), as in the reference's training graph
@@ -153,25 +154,47 @@ class TrainingStep:
             for k, cam in enumerate(self.cams):     # every camera's pair count is on its way before the first read
                 _C.prefetch_num_rendered(cam.H, cam.W, screen[k][0], screen[k][3],
                                          self._all_local((cam.H + 15) // 16, (cam.W + 15) // 16))
+        # Cameras are independent until the parameter gradients are summed: they alternate between `render_streams`
+        # CUDA streams, so that the binning / sorting of one camera (memory- and launch-bound) runs beside the
+        # blending of another (instruction-bound).  Autograd runs each camera's backward on the stream of its forward.
+        main = torch.cuda.current_stream()
+        streams = self._streams(main)
+        for s in streams:
+            s.wait_stream(main)
         for k, cam in enumerate(self.cams):
-            rast = GaussianRasterizer(self.settings[k])
-            means2D, _, conic_opacity, radii, depths = screen[k][:5]
-            means2D.retain_grad()          # the densifier reads means2D.grad
-            TX, TY = (cam.W + 15) // 16, (cam.H + 15) // 16
-            local = self._all_local(TY, TX)
-            means2D_abs = torch.zeros(self.n_local, 3, device=self.dev, requires_grad=True)
-            all_map = screen[k][5] if self.plane_grads else \
-                self.all_map_for(k, p["means3D"], p["scales"], p["rotations"], radii)
-            color, n_render, n_consider, n_contrib, observe, out_all_map, plane_depth = rast.render_gaussians(
-                means2D, means2D_abs, conic_opacity, self.rgb[k], all_map, depths, radii, local, None, args)
-            if self._cot_events is not None and k in self._cot_events:
-                color, out_all_map, plane_depth = _AwaitEvent.apply(self._cot_events[k], color, out_all_map,
-                                                                    plane_depth)
-            heads += [color, out_all_map, plane_depth]
-            grads += self.cot[k]
-            outs.append((radii, means2D))
+            with torch.cuda.stream(streams[k % len(streams)]):
+                rast = GaussianRasterizer(self.settings[k])
+                means2D, _, conic_opacity, radii, depths = screen[k][:5]
+                means2D.retain_grad()          # the densifier reads means2D.grad
+                TX, TY = (cam.W + 15) // 16, (cam.H + 15) // 16
+                local = self._all_local(TY, TX)
+                means2D_abs = torch.zeros(self.n_local, 3, device=self.dev, requires_grad=True)
+                all_map = screen[k][5] if self.plane_grads else \
+                    self.all_map_for(k, p["means3D"], p["scales"], p["rotations"], radii)
+                color, n_render, n_consider, n_contrib, observe, out_all_map, plane_depth = rast.render_gaussians(
+                    means2D, means2D_abs, conic_opacity, self.rgb[k], all_map, depths, radii, local, None, args)
+                if self._cot_events is not None and k in self._cot_events:
+                    color, out_all_map, plane_depth = _AwaitEvent.apply(self._cot_events[k], color, out_all_map,
+                                                                        plane_depth)
+                heads += [color, out_all_map, plane_depth]
+                grads += self.cot[k]
+                outs.append((radii, means2D))
+        for s in streams:
+            main.wait_stream(s)
         torch.autograd.backward(heads, grads)      # one backward over the batch, as one loss.backward() upstream
+        for s in streams:                          # the backward kernels of the side streams precede whatever follows
+            main.wait_stream(s)
         self.last = outs
+
+    render_streams = 1      # > 1: cameras of the single-GPU step alternate between that many CUDA streams
+    _side_streams = None
+
+    def _streams(self, main):
+        if self.render_streams <= 1:
+            return [main]
+        if self._side_streams is None or len(self._side_streams) != self.render_streams:
+            self._side_streams = [torch.cuda.Stream(device=self.dev) for _ in range(self.render_streams)]
+        return self._side_streams
 
     _local_cache = {}
 
@@ -313,13 +336,17 @@ class TrainingStep:
         `chunks` pieces and the batched preprocess starts on each piece as it lands; the upstream-gradient images,
         first read by the backward pass, are copied beside the forward pass in the order the backward consumes them,
         and each camera's backward waits for its own images only; the parameter gradients leave piece by piece
-        behind the chunks of the batched preprocess backward."""
+        behind the chunks of the batched preprocess backward, on a stream of their own: the call returns without
+        waiting for them, so that the read-back of step t (device to host) runs beside the uploads of step t + 1
+        (host to device) when steps follow each other.  `finish_e2e()` waits for everything; `grad_host` is
+        complete after it."""
         from .batched import Pipeline, chunk_bounds
 
         main = torch.cuda.current_stream()
         if self._copy_stream is None:
             self._copy_stream = torch.cuda.Stream(device=self.dev)
-        copy = self._copy_stream
+            self._d2h_stream = torch.cuda.Stream(device=self.dev)
+        copy, down = self._copy_stream, self._d2h_stream
         # piecewise gradient read-back needs the batched preprocess backward to be the ONLY producer of the parameter
         # gradients: true when the plane descriptors are fused into it (or switched off)
         from . import exchange
@@ -354,9 +381,10 @@ class TrainingStep:
         def gradients_out(i, lo, hi, grads):
             ev = torch.cuda.Event()
             ev.record(torch.cuda.current_stream())
-            with torch.cuda.stream(copy):
-                copy.wait_event(ev)
+            with torch.cuda.stream(down):
+                down.wait_event(ev)
                 for k, g in zip(names, grads):
+                    g.record_stream(down)
                     self.grad_host[k][lo:hi].copy_(g[lo:hi], non_blocking=True)
 
         if pipelined:
@@ -369,11 +397,26 @@ class TrainingStep:
             self._pipeline = None
             self._cot_events = None
         if not pipelined:
-            for k, v in self.params.items():
-                self.grad_host[k].copy_(v.grad, non_blocking=True)
-        copy.synchronize()
-        main.synchronize()
+            down.wait_stream(main)
+            with torch.cuda.stream(down):
+                for k, v in self.params.items():
+                    v.grad.record_stream(down)
+                    self.grad_host[k].copy_(v.grad, non_blocking=True)
         return self.grad_host
+
+    def join_e2e(self):
+        """Make the current stream wait for the copies of the end-to-end steps queued so far (no host wait): an
+        event recorded on the current stream afterwards lies behind the last gradient's arrival on the host."""
+        for s in (self._copy_stream, self._d2h_stream):
+            if s is not None:
+                torch.cuda.current_stream().wait_stream(s)
+
+    def finish_e2e(self):
+        """Wait for the copies and kernels of the end-to-end steps queued so far."""
+        for s in (self._copy_stream, self._d2h_stream):
+            if s is not None:
+                s.synchronize()
+        torch.cuda.current_stream().synchronize()
 
     def _my_cameras(self):
         """Cameras (part of) which this rank renders: all of them on one GPU, the balancer's choice otherwise."""

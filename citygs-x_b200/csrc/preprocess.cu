@@ -88,8 +88,11 @@ preprocess_fwd_kernel(int P, const float* __restrict__ means3D, const float* __r
                       const float* __restrict__ projmatrix_g, const int W, int H, const float tan_fovx,
                       float tan_fovy, const float focal_x, float focal_y, int* __restrict__ radii,
                       float2* __restrict__ points_xy_image, float* __restrict__ depths,
-                      float* __restrict__ cov3Ds, float4* __restrict__ conic_opacity, int vec_mask)
+                      float* __restrict__ cov3Ds, float4* __restrict__ conic_opacity, int vec_mask,
+                      const float* __restrict__ cov3D_precomp)
 {
+    // cov3D_precomp (filter only): six floats per Gaussian given by the caller instead of scales and rotations
+    // (cuda_rasterizer/forward.cu:585-595 of the reference)
     __shared__ __align__(16) float s_mean[CGX_BLOCK_SIZE * 3];
     __shared__ __align__(16) float s_scale[CGX_BLOCK_SIZE * 3];
     __shared__ __align__(16) float s_rot[CGX_BLOCK_SIZE * 4];
@@ -102,8 +105,10 @@ preprocess_fwd_kernel(int P, const float* __restrict__ means3D, const float* __r
     if (threadIdx.x < 16) viewmatrix[threadIdx.x] = viewmatrix_g[threadIdx.x];
     else if (threadIdx.x < 32) projmatrix[threadIdx.x - 16] = projmatrix_g[threadIdx.x - 16];
     block_load_rows<3>(means3D + (size_t)base * 3, s_mean, count, vec_mask & 1);
-    block_load_rows<3>(scales + (size_t)base * 3, s_scale, count, vec_mask & 2);
-    block_load_rows<4>(rotations + (size_t)base * 4, s_rot, count, vec_mask & 4);
+    if (!(FILTER && cov3D_precomp)) {
+        block_load_rows<3>(scales + (size_t)base * 3, s_scale, count, vec_mask & 2);
+        block_load_rows<4>(rotations + (size_t)base * 4, s_rot, count, vec_mask & 4);
+    }
     __syncthreads();
 
     const int t = threadIdx.x;
@@ -124,9 +129,14 @@ preprocess_fwd_kernel(int P, const float* __restrict__ means3D, const float* __r
             float3 p_view = transform_point_4x3(p_orig, viewmatrix);
             if (p_view.z <= 0.0f) break;
 
-            const float3 sc = {s_scale[3 * t], s_scale[3 * t + 1], s_scale[3 * t + 2]};
-            const float4 q = {s_rot[4 * t], s_rot[4 * t + 1], s_rot[4 * t + 2], s_rot[4 * t + 3]};
-            compute_cov3d(sc, scale_modifier, q, cov3D);
+            if (FILTER && cov3D_precomp) {
+#pragma unroll
+                for (int k = 0; k < 6; k++) cov3D[k] = __ldg(cov3D_precomp + 6 * (size_t)idx + k);
+            } else {
+                const float3 sc = {s_scale[3 * t], s_scale[3 * t + 1], s_scale[3 * t + 2]};
+                const float4 q = {s_rot[4 * t], s_rot[4 * t + 1], s_rot[4 * t + 2], s_rot[4 * t + 3]};
+                compute_cov3d(sc, scale_modifier, q, cov3D);
+            }
 
             float3 cov = compute_cov2d(p_orig, focal_x, focal_y, tan_fovx, tan_fovy, cov3D, viewmatrix);
 
@@ -801,11 +811,13 @@ extern "C" int cgx_mark_visible(int P, const float* means3D, const float* viewma
 static int preprocess_launch(bool filter, int P, const float* means3D, const float* scales, float scale_modifier,
                              const float* rotations, const float* opacities, const float* viewmatrix,
                              const float* projmatrix, int W, int H, float tanfovx, float tanfovy, float* means2D,
-                             float* depths, int32_t* radii, float* cov3D, float* conic_opacity, void* stream)
+                             float* depths, int32_t* radii, float* cov3D, float* conic_opacity, void* stream,
+                             const float* cov3D_precomp = nullptr)
 {
     if (P < 0 || W <= 0 || H <= 0) return CGX_EINVAL;
     if (P == 0) return CGX_OK;
-    if (!means3D || !scales || !rotations || !viewmatrix || !projmatrix || !radii) return CGX_EINVAL;
+    if (!means3D || !viewmatrix || !projmatrix || !radii) return CGX_EINVAL;
+    if (!(filter && cov3D_precomp) && (!scales || !rotations)) return CGX_EINVAL;
     if (!filter && (!opacities || !means2D || !depths || !cov3D || !conic_opacity)) return CGX_EINVAL;
     if (!filter && (((uintptr_t)means2D & 7) || !aligned16(conic_opacity))) return CGX_EINVAL;
     // focal lengths are computed on the host in fp32, as the reference does before launching
@@ -818,11 +830,11 @@ static int preprocess_launch(bool filter, int P, const float* means3D, const flo
     if (filter)
         preprocess_fwd_kernel<true><<<grid, CGX_BLOCK_SIZE, 0, st>>>(
             P, means3D, scales, scale_modifier, rotations, opacities, viewmatrix, projmatrix, W, H, tanfovx, tanfovy,
-            focal_x, focal_y, radii, (float2*)means2D, depths, cov3D, (float4*)conic_opacity, vec_mask);
+            focal_x, focal_y, radii, (float2*)means2D, depths, cov3D, (float4*)conic_opacity, vec_mask, cov3D_precomp);
     else
         preprocess_fwd_kernel<false><<<grid, CGX_BLOCK_SIZE, 0, st>>>(
             P, means3D, scales, scale_modifier, rotations, opacities, viewmatrix, projmatrix, W, H, tanfovx, tanfovy,
-            focal_x, focal_y, radii, (float2*)means2D, depths, cov3D, (float4*)conic_opacity, vec_mask);
+            focal_x, focal_y, radii, (float2*)means2D, depths, cov3D, (float4*)conic_opacity, vec_mask, nullptr);
     return check_launch();
 }
 
@@ -842,6 +854,15 @@ extern "C" int cgx_filter_preprocess(int P, const float* means3D, const float* s
 {
     return preprocess_launch(true, P, means3D, scales, scale_modifier, rotations, nullptr, viewmatrix, projmatrix, W,
                              H, tanfovx, tanfovy, nullptr, nullptr, radii, nullptr, nullptr, stream);
+}
+
+extern "C" int cgx_filter_preprocess_cov3d(int P, const float* means3D, const float* cov3D_precomp,
+                                           const float* viewmatrix, const float* projmatrix, int W, int H,
+                                           float tanfovx, float tanfovy, int32_t* radii, void* stream)
+{
+    if (P > 0 && !cov3D_precomp) return CGX_EINVAL;
+    return preprocess_launch(true, P, means3D, nullptr, 1.0f, nullptr, nullptr, viewmatrix, projmatrix, W, H, tanfovx,
+                             tanfovy, nullptr, nullptr, radii, nullptr, nullptr, stream, cov3D_precomp);
 }
 
 extern "C" int cgx_sh_to_rgb(int P, int degree, int M, const float* means3D, const float* campos, const float* sh,

@@ -549,9 +549,17 @@ def rasterize_aussians_filter(means3D, scales, rotations, scale_modifier, cov3D_
     means3D = _cuda_f32(means3D, "means3D")
     P, dev = means3D.shape[0], means3D.device
     radii = torch.empty(P, dtype=torch.int32, device=dev)
-    if P:
+    if P and cov3D_precomp is not None and cov3D_precomp.numel():
+        cov = _cuda_f32(cov3D_precomp, "cov3D_precomp")
+        if cov.numel() != 6 * P:
+            raise RuntimeError("cov3D_precomp must hold six floats per Gaussian")
+        with torch.cuda.device(dev):
+            _call("cgx_filter_preprocess", _lib.lib().cgx_filter_preprocess_cov3d, P, _ptr(means3D), _ptr(cov),
+                  _ptr(_cuda_f32(viewmatrix, "viewmatrix")), _ptr(_cuda_f32(projmatrix, "projmatrix")), int(image_width),
+                  int(image_height), float(tan_fovx), float(tan_fovy), _ptr(radii), _stream())
+    elif P:
         if scales is None or scales.numel() == 0 or rotations is None or rotations.numel() == 0:
-            raise RuntimeError("visible_filter needs scales and rotations (precomputed covariances are not supported)")
+            raise RuntimeError("visible_filter needs scales and rotations, or precomputed covariances")
         with torch.cuda.device(dev):
             _call("cgx_filter_preprocess", _lib.lib().cgx_filter_preprocess, 
                 P, _ptr(means3D), _ptr(_cuda_f32(scales, "scales")), float(scale_modifier),

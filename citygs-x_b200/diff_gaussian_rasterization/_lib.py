@@ -56,6 +56,7 @@ SIGNATURES = {
     "cgx_mark_visible": (_i, [_i, _vp, _vp, _vp, _vp]),
     "cgx_preprocess_fwd": (_i, [_i, _vp, _vp, _f, _vp, _vp, _vp, _vp, _i, _i, _f, _f, _vp, _vp, _vp, _vp, _vp, _vp]),
     "cgx_filter_preprocess": (_i, [_i, _vp, _vp, _f, _vp, _vp, _vp, _i, _i, _f, _f, _vp, _vp]),
+    "cgx_filter_preprocess_cov3d": (_i, [_i, _vp, _vp, _vp, _vp, _i, _i, _f, _f, _vp, _vp]),
     "cgx_sh_to_rgb": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp]),
     "cgx_preprocess_bwd": (_i, [_i, _vp, _vp, _f, _vp, _vp, _vp, _vp, _i, _i, _f, _f, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "cgx_preprocess_fwd_batched": (_i, [_i, _i, _vp, _vp, _f, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),

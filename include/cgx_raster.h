@@ -70,6 +70,12 @@ int cgx_preprocess_fwd(int P, const float* means3D, const float* scales, float s
 int cgx_filter_preprocess(int P, const float* means3D, const float* scales, float scale_modifier,
                           const float* rotations, const float* viewmatrix, const float* projmatrix,
                           int W, int H, float tanfovx, float tanfovy, int32_t* radii, void* stream);
+/* The same filter for callers that hold precomputed 3-D covariances (six floats per Gaussian, upper triangle) instead
+ * of scales and rotations: the `cov3D_precomp` branch of filter_preprocessCUDA
+ * (RAST/cuda_rasterizer/forward.cu:585-595). */
+int cgx_filter_preprocess_cov3d(int P, const float* means3D, const float* cov3D_precomp, const float* viewmatrix,
+                                const float* projmatrix, int W, int H, float tanfovx, float tanfovy,
+                                int32_t* radii, void* stream);
 
 /* Optional SH stage, computeColorFromSH (RAST/cuda_rasterizer/forward.cu:21-72; compiled out of the
  * reference's kernel, kept here as a switchable stage).  sh (P,M,3), campos 3 floats (device),

@@ -32,3 +32,21 @@ def test_camera_without_gradient_is_skipped():
     stats = DensificationStats(4, "cpu", track_max_radii=False)
     stats.update(torch.ones(4, dtype=torch.int32), torch.zeros(4, 2, requires_grad=True))
     assert not stats.denom.any() and stats.max_radii2D is None
+
+
+def test_anchor_statistics_match_the_reference_method():
+    """cgx.densification.AnchorStatistics against golden vectors made by the reference's own training_statis body
+    (tests/golden/make_statis_golden.py): three calls in a row, accumulators carried over."""
+    import numpy as np
+
+    from cgx.densification import AnchorStatistics
+
+    z = np.load(util.GOLDEN / "anchor_statis.npz")
+    st = AnchorStatistics(int(z["N"]), int(z["K"]), "cpu")
+    for call in range(3):
+        t = {k: torch.from_numpy(z[f"{k}{call}"]) for k in ("avm", "opacity", "sel", "upd", "grad")}
+        st.training_statis(t["grad"], t["opacity"], t["upd"], t["sel"], t["avm"])
+    for name in ("opacity_accum", "anchor_demon", "offset_gradient_accum", "offset_denom"):
+        got, want = getattr(st, name), torch.from_numpy(z[name])
+        assert torch.allclose(got, want, rtol=1e-6, atol=1e-6), name
+    assert float(st.offset_denom.sum()) > 0 and float(st.opacity_accum.sum()) > 0

@@ -362,6 +362,19 @@ def test_filter_and_mark_visible(cuda_device, reference_C):
                                                       cam.tanfovy, cam.H, cam.W, False, False).cpu()
         assert torch.equal(radii_f, r_ref)
         assert torch.equal(vis, reference_C.mark_visible(gd["means3D"], V, Pm).cpu())
+    # precomputed 3-D covariances instead of scales and rotations (forward.cu:585-595): same radii
+    from diff_gaussian_rasterization import _C
+    rs = rast.raster_settings
+    cov3D = _C.preprocess_gaussians(gd["means3D"], gd["scales"], gd["rotations"], gd["sh"], gd["opacities"], 1.0,
+                                    rs.viewmatrix, rs.projmatrix, cam.tanfovx, cam.tanfovy, cam.H, cam.W, 3, rs.campos,
+                                    False, False, cuda_args())[4]
+    radii_c = rast.visible_filter(gd["means3D"], cov3D_precomp=cov3D).cpu()
+    assert torch.equal(radii_c, radii_f)
+    if reference_C is not None:
+        e = torch.empty(0, device=cuda_device)
+        r_ref_c = reference_C.rasterize_aussians_filter(gd["means3D"], e, e, 1.0, cov3D, V, Pm, cam.tanfovx, cam.tanfovy,
+                                                        cam.H, cam.W, False, False).cpu()
+        assert torch.equal(radii_c, r_ref_c)
 
 
 def test_sh_stage(cuda_device):
