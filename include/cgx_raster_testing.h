@@ -17,10 +17,13 @@ int cgx_set_sort_variant(int variant);
 
 /* A/B switch of the blending kernels (default 1):
  *   bit 0  per-warp culling of each batch before blending (forward and backward);
- *   bit 1  the reference-shaped walk (every lane looks at every surviving Gaussian; butterfly reduction of the
- *          gradient terms in the backward) instead of the two-phase walk (every lane walks only its own
- *          contributors; gradient terms staged in shared memory and summed per Gaussian).
- * Forward outputs are bit-identical across the variants; gradients differ by the order of their sums. */
+ *   bit 1  always the reference-shaped walk (every lane looks at every surviving Gaussian; butterfly reduction of
+ *          the gradient terms in the backward);
+ *   bit 2  always the two-phase walk (every lane walks only its own contributors; gradient terms staged in shared
+ *          memory and summed per Gaussian).
+ * With neither bit 1 nor bit 2 the walk follows the density the forward pass measures (pixels reached per visit):
+ * per chunk of visits in the forward, per launch in the backward.  Forward outputs are bit-identical across the
+ * variants; gradients differ by the order of their sums. */
 int cgx_set_render_variant(int variant);
 
 #ifdef __cplusplus

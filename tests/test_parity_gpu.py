@@ -261,21 +261,25 @@ def test_cull_variant_is_identical(cuda_device):
     g, cam = make_case(cfg=1, n=100000, res=(640, 360), big_scales=True)
     l = _lib.lib()
     try:
-        l.cgx_set_render_variant(1)      # default: culling + two-phase walk
+        l.cgx_set_render_variant(1)      # default: culling, walk chosen from the measured density
         a = run_ours(g, cam, cuda_device, cot=cotangents(cam))
         l.cgx_set_render_variant(0)      # no culling, every lane looks at every Gaussian
         b = run_ours(g, cam, cuda_device, cot=cotangents(cam))
         l.cgx_set_render_variant(3)      # culling, every lane looks at every surviving Gaussian
         c = run_ours(g, cam, cuda_device, cot=cotangents(cam))
+        l.cgx_set_render_variant(5)      # culling, two-phase walk whatever the density
+        e = run_ours(g, cam, cuda_device, cot=cotangents(cam))
     finally:
         l.cgx_set_render_variant(1)
     for k in ("color", "out_all_map", "out_plane_depth", "final_T", "n_contrib_px", "n_contrib2loss_px",
               "out_observe", "n_consider", "n_contrib"):
         assert torch.equal(a[k], b[k]), k
         assert torch.equal(a[k], c[k]), k
+        assert torch.equal(a[k], e[k]), k
     for k in GRADS:
         assert rel_l2(a[k], b[k]) <= 1e-5, k
         assert rel_l2(a[k], c[k]) <= 1e-5, k
+        assert rel_l2(a[k], e[k]) <= 1e-5, k
 
 
 def test_partial_compute_locally(cuda_device, reference_C):
