@@ -87,17 +87,18 @@ class DivisionStrategyFinal:
 
     def __init__(self, camera, world_size, gpu_ids, division_pos, gpu_for_this_camera_tilelr, ctx=None):
         ctx = _ctx(ctx)
-        assert world_size > 0, "The world_size must be greater than 0."
-        assert len(gpu_ids) == world_size, "The number of gpu_ids must be equal to the world_size."
-        assert len(division_pos) == world_size + 1, "The number of division_pos must be equal to the world_size+1."
-        assert division_pos[0] == 0, "The first element of division_pos must be 0."
-        assert division_pos[-1] == ctx.tile_y, "The last element of division_pos must be equal to the total number of tiles."
-        for i in range(1, len(division_pos)):
-            assert division_pos[i] > division_pos[i - 1], "The division_pos must be in ascending order."
-        for idx in range(len(gpu_for_this_camera_tilelr)):
-            assert (gpu_for_this_camera_tilelr[idx][0] == division_pos[idx]
-                    and gpu_for_this_camera_tilelr[idx][1] == division_pos[idx + 1]), \
-                "The division_pos must be consistent with gpu_for_this_camera_tilelr."
+        cuts = [int(c) for c in division_pos]
+        bands = list(zip(cuts[:-1], cuts[1:]))
+        problems = []
+        if world_size <= 0 or len(gpu_ids) != world_size:
+            problems.append(f"{len(gpu_ids)} gpu ids for world_size {world_size}")
+        if len(cuts) != world_size + 1 or cuts[:1] != [0] or cuts[-1:] != [ctx.tile_y]:
+            problems.append(f"cuts {cuts} do not run from 0 to {ctx.tile_y} in {world_size} bands")
+        if any(hi <= lo for lo, hi in bands):
+            problems.append(f"cuts {cuts} are not strictly ascending")
+        if [tuple(map(int, lr)) for lr in gpu_for_this_camera_tilelr] != bands:
+            problems.append(f"row ranges {list(gpu_for_this_camera_tilelr)} do not match cuts {cuts}")
+        assert not problems, "invalid division of a camera: " + "; ".join(problems)
         self.ctx = ctx
         self.camera = camera
         self.world_size = world_size
@@ -167,22 +168,18 @@ class DivisionStrategyHistoryFinal:
         self.history = []
 
     def store_stats(self, batched_cameras, gpu_camera_running_time, batched_strategies):
-        batched_camera_info = []
-        all_camera_running_time = [0 for _ in range(len(batched_cameras))]
-        all_gpu_running_time = [0 for _ in range(self.world_size)]
-        for camera_id, camera in enumerate(batched_cameras):
-            each_gpu_running_time = []
-            for gpu_i in batched_strategies[camera_id].gpu_ids:
-                t = gpu_camera_running_time[gpu_i][camera_id]
-                all_camera_running_time[camera_id] += t
-                all_gpu_running_time[gpu_i] += t
-                each_gpu_running_time.append(t)
-            batched_camera_info.append({"camera_id": camera.uid, "gpu_ids": batched_strategies[camera_id].gpu_ids,
-                                        "division_pos": batched_strategies[camera_id].division_pos,
-                                        "each_gpu_running_time": each_gpu_running_time})
-        self.history.append({"iteration": self.ctx.iteration, "all_gpu_running_time": all_gpu_running_time,
-                             "all_camera_running_time": all_camera_running_time,
-                             "batched_camera_info": batched_camera_info})
+        """Append one log entry: per camera who rendered which rows in how many ms, per rank and per camera totals."""
+        per_rank = [0.0] * self.world_size
+        per_camera, info = [], []
+        for k, (camera, strategy) in enumerate(zip(batched_cameras, batched_strategies)):
+            ms = [gpu_camera_running_time[rank][k] for rank in strategy.gpu_ids]
+            for rank, t in zip(strategy.gpu_ids, ms):
+                per_rank[rank] += t
+            per_camera.append(sum(ms))
+            info.append({"camera_id": camera.uid, "gpu_ids": strategy.gpu_ids, "division_pos": strategy.division_pos,
+                         "each_gpu_running_time": ms})
+        self.history.append({"iteration": self.ctx.iteration, "all_gpu_running_time": per_rank,
+                             "all_camera_running_time": per_camera, "batched_camera_info": info})
 
     def to_json(self):
         return self.history
@@ -206,32 +203,32 @@ def start_strategy_final(batched_cameras, strategy_history, ctx=None):
                                                             [(0, n_tiles_per_image)], ctx=ctx))
         return batched_strategies, gpuid2tasks
 
-    catted = torch.cat([strategy_history.accum_heuristic[camera.uid] for camera in batched_cameras], dim=0)
-    division_pos = division_pos_heuristic(catted, total_tiles, ws, right=True)
-    # snap cuts that fall within border_divpos_coeff rows of an image border onto the border
-    for i in range(1, len(division_pos) - 1):
-        if division_pos[i] % n_tiles_per_image + ctx.border_divpos_coeff >= n_tiles_per_image:
-            division_pos[i] = division_pos[i] // n_tiles_per_image * n_tiles_per_image + n_tiles_per_image
-        elif division_pos[i] % n_tiles_per_image - ctx.border_divpos_coeff <= 0:
-            division_pos[i] = division_pos[i] // n_tiles_per_image * n_tiles_per_image
-    for i in range(0, len(division_pos) - 1):
-        assert division_pos[i] + ctx.border_divpos_coeff < division_pos[i + 1], \
-            "Each part between division_pos must be large enough."
+    rows = n_tiles_per_image
+    cost = torch.cat([strategy_history.accum_heuristic[camera.uid] for camera in batched_cameras], dim=0)
+    cuts = division_pos_heuristic(cost, total_tiles, ws, right=True)
+    # a cut closer than border_divpos_coeff rows to an image border moves onto the border
+    margin = ctx.border_divpos_coeff
+    for i in range(1, ws):
+        image, row = divmod(cuts[i], rows)
+        if row + margin >= rows:
+            cuts[i] = (image + 1) * rows
+        elif row <= margin:
+            cuts[i] = image * rows
+    too_thin = [i for i in range(ws) if cuts[i + 1] - cuts[i] <= margin]
+    assert not too_thin, f"ranks {too_thin} would get {margin} tile rows or fewer: cuts {cuts}"
 
     for idx, camera in enumerate(batched_cameras):
-        offset = idx * n_tiles_per_image
-        gpu_for_this_camera, tilelr = [], []
-        for gpu_id in range(ws):
-            gpu_tile_l, gpu_tile_r = division_pos[gpu_id], division_pos[gpu_id + 1]
-            if gpu_tile_r <= offset or offset + n_tiles_per_image <= gpu_tile_l:
-                continue
-            gpu_for_this_camera.append(gpu_id)
-            local_l = max(gpu_tile_l, offset) - offset
-            local_r = min(gpu_tile_r, offset + n_tiles_per_image) - offset
-            tilelr.append((local_l, local_r))
-            gpuid2tasks[gpu_id].append((idx, local_l, local_r))
-        batched_strategies.append(DivisionStrategyFinal(camera, len(gpu_for_this_camera), gpu_for_this_camera,
-                                                        [0] + [t[1] for t in tilelr], tilelr, ctx=ctx))
+        first = idx * rows                                    # this camera's rows in the concatenated batch
+        ranks, bands = [], []
+        for rank in range(ws):
+            lo, hi = max(cuts[rank], first) - first, min(cuts[rank + 1], first + rows) - first
+            if hi <= lo:
+                continue                                      # rank's range does not reach into this camera
+            ranks.append(rank)
+            bands.append((lo, hi))
+            gpuid2tasks[rank].append((idx, lo, hi))
+        batched_strategies.append(DivisionStrategyFinal(camera, len(ranks), ranks, [0] + [hi for _, hi in bands],
+                                                        bands, ctx=ctx))
     return batched_strategies, gpuid2tasks
 
 
@@ -280,14 +277,11 @@ def finish_strategy_final(batched_cameras, strategy_history, batched_strategies,
             or (ctx.image_height <= 600 or ctx.image_width <= 1000)):
         return
 
-    for camera_id, (camera, strategy) in enumerate(zip(batched_cameras, batched_strategies)):
-        new_heuristic = torch.zeros((ctx.tile_y,), dtype=torch.float32)
-        for local_id, gpu_id in enumerate(strategy.gpu_ids):
-            l, r = strategy.division_pos[local_id], strategy.division_pos[local_id + 1]
-            new_heuristic[l:r] = gpu_camera_running_time[gpu_id][camera_id] / (r - l)
-        if ctx.heuristic_decay == 0:
-            strategy_history.accum_heuristic[camera.uid] = new_heuristic
-        else:
-            strategy_history.accum_heuristic[camera.uid] = (
-                strategy_history.accum_heuristic[camera.uid] * ctx.heuristic_decay
-                + new_heuristic * (1 - ctx.heuristic_decay))
+    keep = ctx.heuristic_decay
+    for k, (camera, strategy) in enumerate(zip(batched_cameras, batched_strategies)):
+        # every row of a band costs the band's time divided by its height
+        per_row = torch.zeros((ctx.tile_y,), dtype=torch.float32)
+        for rank, lo, hi in zip(strategy.gpu_ids, strategy.division_pos[:-1], strategy.division_pos[1:]):
+            per_row[lo:hi] = gpu_camera_running_time[rank][k] / (hi - lo)
+        old = strategy_history.accum_heuristic[camera.uid]
+        strategy_history.accum_heuristic[camera.uid] = per_row if keep == 0 else old * keep + per_row * (1 - keep)
