@@ -153,7 +153,7 @@ class TrainingStep:
         if self.prefetch_counts:
             for k, cam in enumerate(self.cams):     # every camera's pair count is on its way before the first read
                 _C.prefetch_num_rendered(cam.H, cam.W, screen[k][0], screen[k][3],
-                                         self._all_local((cam.H + 15) // 16, (cam.W + 15) // 16))
+                                         self._all_local((cam.H + 15) // 16, (cam.W + 15) // 16), depths=screen[k][4])
         # Cameras are independent until the parameter gradients are summed: they alternate between `render_streams`
         # CUDA streams, so that the binning / sorting of one camera (memory- and launch-bound) runs beside the
         # blending of another (instruction-bound).  Autograd runs each camera's backward on the stream of its forward.
@@ -289,7 +289,7 @@ class TrainingStep:
             for k, strat in enumerate(strategies):
                 local = strat.get_compute_locally()
                 if local is not None and m2[k].shape[0] >= 10:
-                    _C.prefetch_num_rendered(self.cams[k].H, self.cams[k].W, m2[k], rad[k], local)
+                    _C.prefetch_num_rendered(self.cams[k].H, self.cams[k].W, m2[k], rad[k], local, depths=dep[k])
         for k, strat in enumerate(strategies):
             local = strat.get_compute_locally()
             n_rows = m2[k].shape[0]

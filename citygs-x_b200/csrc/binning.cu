@@ -15,16 +15,66 @@ namespace cgx {
 constexpr int SCAN_ITEMS = 4;                              // Gaussians per thread in count / emit
 constexpr int SCAN_TILE = CGX_BLOCK_SIZE * SCAN_ITEMS;     // Gaussians per CTA
 
+// The local-tile mask as a band of whole tile rows [row0, row1), when it is one (it always is for the workload
+// division's row bands and for a single GPU): valid = 1 lets the counting and emission kernels replace one mask
+// lookup per tile by two comparisons per splat.  Any other mask (valid = 0) goes through the lookups.
+struct MaskBand {
+    int valid, row0, row1, pad;
+};
+
+__global__ void __launch_bounds__(1024)
+analyse_mask_kernel(int gx, int gy, const uint8_t* __restrict__ local, MaskBand* __restrict__ band)
+{
+    __shared__ int s_partial, s_first, s_last, s_full;
+    if (threadIdx.x == 0) {
+        s_partial = 0;
+        s_first = gy;
+        s_last = -1;
+        s_full = 0;
+    }
+    __syncthreads();
+    for (int y = threadIdx.x; y < gy; y += blockDim.x) {
+        int set = 0;
+        for (int x = 0; x < gx; x++) set += local[y * gx + x] ? 1 : 0;
+        if (set == gx) {
+            atomicMin(&s_first, y);
+            atomicMax(&s_last, y);
+            atomicAdd(&s_full, 1);
+        } else if (set != 0) {
+            atomicExch(&s_partial, 1);
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        MaskBand b;
+        b.pad = 0;
+        if (s_full == 0 && !s_partial) {
+            b.valid = 1; b.row0 = 0; b.row1 = 0;                    // nothing is local
+        } else {
+            b.valid = (!s_partial && s_full == s_last - s_first + 1) ? 1 : 0;
+            b.row0 = s_first;
+            b.row1 = s_last + 1;
+        }
+        *band = b;
+    }
+}
+
 __device__ __forceinline__ uint32_t count_local_tiles(const float2 xy, int radius, const uint8_t* __restrict__ local,
-                                                      int gx, int gy)
+                                                      int gx, int gy, const MaskBand band)
 {
     uint32_t cnt = 0;
     if (radius > 0) {
         uint2 rect_min, rect_max;
         get_rect(xy, radius, rect_min, rect_max, gx, gy);
-        for (int y = rect_min.y; y < rect_max.y; y++)
-            for (int x = rect_min.x; x < rect_max.x; x++)
-                if (local[y * gx + x]) cnt++;
+        if (band.valid) {
+            const int rows = min((int)rect_max.y, band.row1) - max((int)rect_min.y, band.row0);
+            const int cols = (int)rect_max.x - (int)rect_min.x;
+            cnt = (rows > 0 && cols > 0) ? (uint32_t)(rows * cols) : 0u;
+        } else {
+            for (int y = rect_min.y; y < rect_max.y; y++)
+                for (int x = rect_min.x; x < rect_max.x; x++)
+                    if (local[y * gx + x]) cnt++;
+        }
     }
     return cnt;
 }
@@ -61,23 +111,50 @@ __device__ __forceinline__ uint32_t block_excl_scan(uint32_t v, uint32_t* s_warp
 __global__ void __launch_bounds__(CGX_BLOCK_SIZE)
 tile_count_kernel(int P, int gx, int gy, const int* __restrict__ radii, const float2* __restrict__ means2D,
                   const uint8_t* __restrict__ local, uint32_t* __restrict__ tiles_touched,
-                  uint32_t* __restrict__ block_sums)
+                  uint32_t* __restrict__ block_sums, const MaskBand* __restrict__ band_ptr,
+                  const float* __restrict__ depths, uint32_t* __restrict__ depth_range)
 {
     __shared__ uint32_t s_warp[8];
+    const MaskBand band = *band_ptr;
     const int base = blockIdx.x * SCAN_TILE;
     uint32_t sum = 0;
+    uint32_t dmin = 0xffffffffu, dmax = 0u;     // bit patterns of the depths of the splats that emit keys
 #pragma unroll
     for (int k = 0; k < SCAN_ITEMS; k++) {
         const int idx = base + k * CGX_BLOCK_SIZE + threadIdx.x;
         if (idx < P) {
-            const uint32_t c = count_local_tiles(means2D[idx], radii[idx], local, gx, gy);
+            const uint32_t c = count_local_tiles(means2D[idx], radii[idx], local, gx, gy, band);
             tiles_touched[idx] = c;
             sum += c;
+            if (depths && c) {
+                const uint32_t b = __float_as_uint(depths[idx]);
+                dmin = min(dmin, b);
+                dmax = max(dmax, b);
+            }
         }
     }
     uint32_t total;
     block_excl_scan(sum, s_warp, total);
     if (threadIdx.x == 0) block_sums[blockIdx.x] = total;
+    if (depths) {
+        // per-CTA range, left beside the CTA's sum: the one-CTA scan kernel reduces them (no atomics on one word)
+        __shared__ uint32_t s_min[8], s_max[8];
+        dmin = __reduce_min_sync(0xffffffffu, dmin);
+        dmax = __reduce_max_sync(0xffffffffu, dmax);
+        if ((threadIdx.x & 31) == 0) {
+            s_min[threadIdx.x >> 5] = dmin;
+            s_max[threadIdx.x >> 5] = dmax;
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            for (int w = 1; w < 8; w++) {
+                dmin = min(dmin, s_min[w]);
+                dmax = max(dmax, s_max[w]);
+            }
+            depth_range[2 * blockIdx.x] = dmin;
+            depth_range[2 * blockIdx.x + 1] = dmax;
+        }
+    }
 }
 
 
@@ -111,11 +188,36 @@ __device__ __forceinline__ uint32_t scan_row_inplace(uint32_t* __restrict__ row,
 }
 
 // One CTA: in-place exclusive scan of the CTA partial sums; writes the grand total.
+// block_ranges (optional): per-CTA (min, max) depth bit patterns -> total_out[1], total_out[2].
 __global__ void __launch_bounds__(1024)
-scan_partials_kernel(int n, uint32_t* __restrict__ sums, uint32_t* __restrict__ total_out)
+scan_partials_kernel(int n, uint32_t* __restrict__ sums, uint32_t* __restrict__ total_out,
+                     const uint32_t* __restrict__ block_ranges)
 {
     const uint32_t total = scan_row_inplace(sums, n);
-    if (threadIdx.x == 0) *total_out = total;
+    if (threadIdx.x == 0) total_out[0] = total;
+    if (block_ranges) {
+        __shared__ uint32_t s_min[32], s_max[32];
+        uint32_t lo = 0xffffffffu, hi = 0u;
+        for (int i = threadIdx.x; i < n; i += blockDim.x) {
+            lo = min(lo, block_ranges[2 * i]);
+            hi = max(hi, block_ranges[2 * i + 1]);
+        }
+        lo = __reduce_min_sync(0xffffffffu, lo);
+        hi = __reduce_max_sync(0xffffffffu, hi);
+        if ((threadIdx.x & 31) == 0) {
+            s_min[threadIdx.x >> 5] = lo;
+            s_max[threadIdx.x >> 5] = hi;
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            for (int w = 1; w < 32; w++) {
+                lo = min(lo, s_min[w]);
+                hi = max(hi, s_max[w]);
+            }
+            total_out[1] = lo;
+            total_out[2] = hi;
+        }
+    }
 }
 
 __global__ void __launch_bounds__(CGX_BLOCK_SIZE)
@@ -123,9 +225,10 @@ emit_keys_kernel(int P, int gx, int gy, const int* __restrict__ radii, const flo
                  const float* __restrict__ depths, const uint32_t* __restrict__ tiles_touched,
                  const uint8_t* __restrict__ local, const uint32_t* __restrict__ block_prefix,
                  uint32_t* __restrict__ point_offsets, uint64_t* __restrict__ keys, uint32_t* __restrict__ values,
-                 uint32_t capacity)
+                 uint32_t capacity, const MaskBand* __restrict__ band_ptr)
 {
     __shared__ uint32_t s_warp[8];
+    const MaskBand band = *band_ptr;
     const int base = blockIdx.x * SCAN_TILE;
     uint32_t running = block_prefix[blockIdx.x];
 #pragma unroll 1
@@ -142,9 +245,12 @@ emit_keys_kernel(int P, int gx, int gy, const int* __restrict__ radii, const flo
                 uint2 rect_min, rect_max;
                 get_rect(xy, radii[idx], rect_min, rect_max, gx, gy);
                 const uint64_t dbits = (uint64_t)__float_as_uint(depths[idx]);
-                for (int y = rect_min.y; y < rect_max.y; y++)
+                // a band of whole rows: its rows of the rectangle are local, the others are not
+                const int y0 = band.valid ? max((int)rect_min.y, band.row0) : (int)rect_min.y;
+                const int y1 = band.valid ? min((int)rect_max.y, band.row1) : (int)rect_max.y;
+                for (int y = y0; y < y1; y++)
                     for (int x = rect_min.x; x < rect_max.x; x++)
-                        if (local[y * gx + x]) {
+                        if (band.valid || local[y * gx + x]) {
                             if (off < capacity) {
                                 uint64_t key = y * gx + x;
                                 key <<= 32;
@@ -171,9 +277,37 @@ constexpr int RADIX = 1 << RADIX_BITS;
 constexpr int SORT_WARPS = SORT_THREADS / 32;
 constexpr int SORT_SMEM = SORT_TILE * (sizeof(uint64_t) + sizeof(uint32_t));
 
+// Digit of a key.  Keys are (tile << 32) | depth bits.  When the caller knows that bits [low_bits, 32) of the low
+// word are the same in every key (depths of one view share their sign, most of their exponent ...), those bits
+// cannot change the order and are squeezed out: the sort then runs over low_bits + tile bits, often one pass fewer.
+// Which bits of the two key words make up the digit of a pass is worked out on the host once per pass:
+//   digit = ((lo >> s_lo) & m_lo) | (((hi >> r_hi) << l_hi) & m_hi)
+struct DigitSpec {
+    uint32_t s_lo, m_lo, r_hi, l_hi, m_hi;
+};
+
+__host__ __device__ __forceinline__ DigitSpec digit_spec(int shift, uint32_t mask, int low_bits)
+{
+    DigitSpec d;
+    if (shift >= low_bits) {                 // the whole digit comes from the high word
+        d = {0u, 0u, (uint32_t)(shift - low_bits), 0u, mask};
+    } else {
+        const int from_lo = low_bits - shift;            // bits the low word still has at this shift
+        const uint32_t m_lo = from_lo >= 32 ? 0xffffffffu : ((1u << from_lo) - 1u);
+        d = {(uint32_t)shift, m_lo & mask, 0u, (uint32_t)(from_lo >= 32 ? 0 : from_lo), from_lo >= 32 ? 0u : (mask & ~m_lo)};
+    }
+    return d;
+}
+
+__device__ __forceinline__ uint32_t sort_digit(uint64_t k, const DigitSpec d)
+{
+    const uint32_t lo = (uint32_t)k, hi = (uint32_t)(k >> 32);
+    return ((lo >> d.s_lo) & d.m_lo) | (((hi >> d.r_hi) << d.l_hi) & d.m_hi);
+}
+
 // table layout: counts[digit * nblocks + block]
 __global__ void __launch_bounds__(SORT_THREADS)
-sort_hist_kernel(int64_t n, int nblocks, int shift, uint32_t mask, const uint64_t* __restrict__ keys,
+sort_hist_kernel(int64_t n, int nblocks, const DigitSpec dg, const uint64_t* __restrict__ keys,
                  uint32_t* __restrict__ table)
 {
     __shared__ uint32_t s_hist[RADIX];
@@ -184,7 +318,7 @@ sort_hist_kernel(int64_t n, int nblocks, int shift, uint32_t mask, const uint64_
     for (int k = 0; k < SORT_ITEMS; k++) {
         const int64_t i = base + k * SORT_THREADS + threadIdx.x;
         if (i < n) {
-            const uint32_t d = (uint32_t)(keys[i] >> shift) & mask;
+            const uint32_t d = sort_digit(keys[i], dg);
             atomicAdd(&s_hist[d], 1u);
         }
     }
@@ -204,7 +338,7 @@ sort_scan_rows_kernel(int nblocks, uint32_t* __restrict__ table, uint32_t* __res
 // chunk of 32*SORT_ITEMS pairs: in round r the warp looks at pairs [chunk + 32 r, chunk + 32 r + 32), so
 // (warp, round, lane) order is input order and ranks computed from match.any ballots are stable.
 __global__ void __launch_bounds__(SORT_THREADS)
-sort_scatter_kernel(int64_t n, int nblocks, int shift, uint32_t mask, const uint64_t* __restrict__ keys_in,
+sort_scatter_kernel(int64_t n, int nblocks, const DigitSpec dg, const uint64_t* __restrict__ keys_in,
                     const uint32_t* __restrict__ vals_in, uint64_t* __restrict__ keys_out,
                     uint32_t* __restrict__ vals_out, const uint32_t* __restrict__ table,
                     const uint32_t* __restrict__ totals)
@@ -253,7 +387,7 @@ sort_scatter_kernel(int64_t n, int nblocks, int shift, uint32_t mask, const uint
         const int64_t i = chunk + r * 32 + lane;
         const bool valid = i < n;
         // invalid tail lanes take a digit of their own (RADIX) so they never match a real digit
-        const uint32_t d = valid ? ((uint32_t)(key[r] >> shift) & mask) : (uint32_t)RADIX;
+        const uint32_t d = valid ? sort_digit(key[r], dg) : (uint32_t)RADIX;
         const uint32_t peers = __match_any_sync(0xffffffffu, d);
         const uint32_t before = __popc(peers & ((1u << lane) - 1u));
         uint32_t prev = 0;
@@ -294,7 +428,7 @@ sort_scatter_kernel(int64_t n, int nblocks, int shift, uint32_t mask, const uint
     for (int r = 0; r < SORT_ITEMS; r++) {
         const int64_t i = chunk + r * 32 + lane;
         if (i < n) {
-            const uint32_t d = (uint32_t)(key[r] >> shift) & mask;
+            const uint32_t d = sort_digit(key[r], dg);
             const uint32_t pos = s_digit_start[d] + s_warp_hist[warp][d] + rank[r];
             s_keys[pos] = key[r];
             s_vals[pos] = val[r];
@@ -305,7 +439,7 @@ sort_scatter_kernel(int64_t n, int nblocks, int shift, uint32_t mask, const uint
     const int valid_n = (int)min((int64_t)SORT_TILE, n - tile_base);
     for (int p = threadIdx.x; p < valid_n; p += SORT_THREADS) {
         const uint64_t k = s_keys[p];
-        const uint32_t d = (uint32_t)(k >> shift) & mask;
+        const uint32_t d = sort_digit(k, dg);
         const size_t dst = (size_t)s_global_base[d] + (p - s_digit_start[d]);
         keys_out[dst] = k;
         vals_out[dst] = s_vals[p];
@@ -316,7 +450,7 @@ sort_scatter_kernel(int64_t n, int nblocks, int shift, uint32_t mask, const uint
 // written straight to their final positions.  Few registers (8 CTAs per SM); the scattered 8- and 4-byte stores are
 // merged in L2, which is the right trade while both ping-pong buffers fit in L2 (n * 24 bytes well below 126 MB).
 __global__ void __launch_bounds__(SORT_THREADS, 6)
-sort_scatter_direct_kernel(int64_t n, int nblocks, int shift, uint32_t mask, const uint64_t* __restrict__ keys_in,
+sort_scatter_direct_kernel(int64_t n, int nblocks, const DigitSpec dg, const uint64_t* __restrict__ keys_in,
                            const uint32_t* __restrict__ vals_in, uint64_t* __restrict__ keys_out,
                            uint32_t* __restrict__ vals_out, const uint32_t* __restrict__ table,
                            const uint32_t* __restrict__ totals)
@@ -335,7 +469,7 @@ sort_scatter_direct_kernel(int64_t n, int nblocks, int shift, uint32_t mask, con
     for (int r = 0; r < SORT_ITEMS; r++) {
         const int64_t i = chunk + r * 32 + lane;
         const bool valid = i < n;
-        const uint32_t d = valid ? ((uint32_t)(keys_in[i] >> shift) & mask) : (uint32_t)RADIX;
+        const uint32_t d = valid ? sort_digit(keys_in[i], dg) : (uint32_t)RADIX;
         const uint32_t peers = __match_any_sync(0xffffffffu, d);
         const uint32_t before = __popc(peers & ((1u << lane) - 1u));
         uint32_t prev = 0;
@@ -373,7 +507,7 @@ sort_scatter_direct_kernel(int64_t n, int nblocks, int shift, uint32_t mask, con
         const int64_t i = chunk + r * 32 + lane;
         if (i < n) {
             const uint64_t k = keys_in[i];
-            const uint32_t d = (uint32_t)(k >> shift) & mask;
+            const uint32_t d = sort_digit(k, dg);
             const size_t dst = (size_t)s_warp_hist[warp][d] + rank[r];
             keys_out[dst] = k;
             vals_out[dst] = vals_in[i];
@@ -420,7 +554,8 @@ __device__ __forceinline__ void st_relaxed_gpu(uint32_t* p, uint32_t v)
 
 // ghist[pass * RADIX + digit] += number of keys with that digit in that pass.
 __global__ void __launch_bounds__(OS_THREADS)
-os_hist_kernel(int64_t n, int passes, int end_bit, const uint64_t* __restrict__ keys, uint32_t* __restrict__ ghist)
+os_hist_kernel(int64_t n, int passes, int end_bit, int low_bits, const uint64_t* __restrict__ keys,
+               uint32_t* __restrict__ ghist)
 {
     __shared__ uint32_t s_hist[OS_MAX_PASSES * RADIX];
     for (int i = threadIdx.x; i < passes * RADIX; i += OS_THREADS) s_hist[i] = 0;
@@ -434,7 +569,7 @@ os_hist_kernel(int64_t n, int passes, int end_bit, const uint64_t* __restrict__ 
         for (int p = 0; p < passes; p++) {
             const int shift = p * RADIX_BITS;
             const int bits = min(RADIX_BITS, end_bit - shift);
-            const uint32_t d = valid ? ((uint32_t)(k >> shift) & ((1u << bits) - 1u)) : (uint32_t)RADIX;
+            const uint32_t d = valid ? sort_digit(k, digit_spec(shift, (1u << bits) - 1u, low_bits)) : (uint32_t)RADIX;
             // lanes of a warp often share a digit in the high passes (few tiles, few exponents): one add per group
             const uint32_t peers = __match_any_sync(0xffffffffu, d);
             if (valid && lane == __ffs(peers) - 1) atomicAdd(&s_hist[p * RADIX + d], (uint32_t)__popc(peers));
@@ -448,7 +583,7 @@ os_hist_kernel(int64_t n, int passes, int end_bit, const uint64_t* __restrict__ 
 }
 
 __global__ void __launch_bounds__(OS_THREADS, CGX_OS_MIN_CTAS)
-os_pass_kernel(int64_t n, int shift, uint32_t mask, const uint64_t* __restrict__ keys_in,
+os_pass_kernel(int64_t n, const DigitSpec dg, const uint64_t* __restrict__ keys_in,
                const uint32_t* __restrict__ vals_in, uint64_t* __restrict__ keys_out, uint32_t* __restrict__ vals_out,
                const uint32_t* __restrict__ ghist, uint32_t* __restrict__ ticket, uint32_t* __restrict__ status,
                unsigned long long wait_limit)
@@ -478,7 +613,7 @@ os_pass_kernel(int64_t n, int shift, uint32_t mask, const uint64_t* __restrict__
         const int64_t i = chunk + r * 32 + lane;
         const bool valid = i < n;
         // invalid tail lanes take a digit of their own (RADIX) so they never match a real digit
-        const uint32_t d = valid ? ((uint32_t)(key[r] >> shift) & mask) : (uint32_t)RADIX;
+        const uint32_t d = valid ? sort_digit(key[r], dg) : (uint32_t)RADIX;
         const uint32_t peers = __match_any_sync(0xffffffffu, d);
         const uint32_t before = __popc(peers & ((1u << lane) - 1u));
         uint32_t prev = 0;
@@ -543,7 +678,7 @@ os_pass_kernel(int64_t n, int shift, uint32_t mask, const uint64_t* __restrict__
     for (int r = 0; r < OS_ITEMS; r++) {
         const int64_t i = chunk + r * 32 + lane;
         if (i < n) {
-            const uint32_t d = (uint32_t)(key[r] >> shift) & mask;
+            const uint32_t d = sort_digit(key[r], dg);
             const size_t dst = (size_t)s_base[d] + s_warp_hist[warp][d] + rank[r];
             keys_out[dst] = key[r];
             vals_out[dst] = vals_in[i];
@@ -1096,20 +1231,28 @@ extern "C" uint32_t cgx_higher_msb(uint32_t n)
     return msb;
 }
 
-extern "C" size_t cgx_bin_workspace_bytes(int P)
+// CTA partial sums, then the analysed mask (MaskBand) on the next 256-byte boundary
+static size_t bin_band_offset(int P)
 {
     const size_t nblocks = ((size_t)(P > 0 ? P : 1) + SCAN_TILE - 1) / SCAN_TILE;
     return align_up(nblocks * sizeof(uint32_t), 256);
 }
 
-extern "C" int cgx_bin_count_scan(int P, int W, int H, const int32_t* radii, const float* means2D,
-                                  const uint8_t* compute_locally, uint32_t* tiles_touched, uint32_t* num_rendered,
-                                  void* workspace, size_t workspace_bytes, void* stream)
+// ... then the per-CTA depth ranges (two words per CTA)
+extern "C" size_t cgx_bin_workspace_bytes(int P)
+{
+    const size_t nblocks = ((size_t)(P > 0 ? P : 1) + SCAN_TILE - 1) / SCAN_TILE;
+    return bin_band_offset(P) + 256 + align_up(2 * nblocks * sizeof(uint32_t), 256);
+}
+
+static int bin_count_scan(int P, int W, int H, const int32_t* radii, const float* means2D, const float* depths,
+                          const uint8_t* compute_locally, uint32_t* tiles_touched, uint32_t* num_rendered,
+                          void* workspace, size_t workspace_bytes, void* stream)
 {
     if (P < 0 || W <= 0 || H <= 0 || !num_rendered) return CGX_EINVAL;
     cudaStream_t st = (cudaStream_t)stream;
     if (P == 0) {
-        cudaError_t e = cudaMemsetAsync(num_rendered, 0, sizeof(uint32_t), st);
+        cudaError_t e = cudaMemsetAsync(num_rendered, 0, (depths ? 3 : 1) * sizeof(uint32_t), st);
         if (e != cudaSuccess) { set_cuda_error(e); return CGX_ECUDA; }
         return CGX_OK;
     }
@@ -1119,10 +1262,30 @@ extern "C" int cgx_bin_count_scan(int P, int W, int H, const int32_t* radii, con
     const int gx = (W + CGX_BLOCK_X - 1) / CGX_BLOCK_X, gy = (H + CGX_BLOCK_Y - 1) / CGX_BLOCK_Y;
     const int nblocks = (P + SCAN_TILE - 1) / SCAN_TILE;
     uint32_t* sums = (uint32_t*)workspace;
+    MaskBand* band = (MaskBand*)((char*)workspace + bin_band_offset(P));
+    uint32_t* block_ranges = depths ? (uint32_t*)((char*)workspace + bin_band_offset(P) + 256) : nullptr;
+    analyse_mask_kernel<<<1, 1024, 0, st>>>(gx, gy, compute_locally, band);
     tile_count_kernel<<<nblocks, CGX_BLOCK_SIZE, 0, st>>>(P, gx, gy, radii, (const float2*)means2D, compute_locally,
-                                                          tiles_touched, sums);
-    scan_partials_kernel<<<1, 1024, 0, st>>>(nblocks, sums, num_rendered);
-    return check_launch(2);
+                                                          tiles_touched, sums, band, depths, block_ranges);
+    scan_partials_kernel<<<1, 1024, 0, st>>>(nblocks, sums, num_rendered, block_ranges);
+    return check_launch(3);
+}
+
+extern "C" int cgx_bin_count_scan(int P, int W, int H, const int32_t* radii, const float* means2D,
+                                  const uint8_t* compute_locally, uint32_t* tiles_touched, uint32_t* num_rendered,
+                                  void* workspace, size_t workspace_bytes, void* stream)
+{
+    return bin_count_scan(P, W, H, radii, means2D, nullptr, compute_locally, tiles_touched, num_rendered, workspace,
+                          workspace_bytes, stream);
+}
+
+extern "C" int cgx_bin_count_scan_depths(int P, int W, int H, const int32_t* radii, const float* means2D,
+                                         const float* depths, const uint8_t* compute_locally, uint32_t* tiles_touched,
+                                         uint32_t* num_rendered3, void* workspace, size_t workspace_bytes, void* stream)
+{
+    if (P > 0 && !depths) return CGX_EINVAL;
+    return bin_count_scan(P, W, H, radii, means2D, depths, compute_locally, tiles_touched, num_rendered3, workspace,
+                          workspace_bytes, stream);
 }
 
 extern "C" int cgx_emit_keys(int P, int W, int H, const int32_t* radii, const float* means2D, const float* depths,
@@ -1138,7 +1301,8 @@ extern "C" int cgx_emit_keys(int P, int W, int H, const int32_t* radii, const fl
     const int nblocks = (P + SCAN_TILE - 1) / SCAN_TILE;
     emit_keys_kernel<<<nblocks, CGX_BLOCK_SIZE, 0, (cudaStream_t)stream>>>(
         P, gx, gy, radii, (const float2*)means2D, depths, tiles_touched, compute_locally, (const uint32_t*)workspace,
-        point_offsets, keys, values, (uint32_t)capacity);
+        point_offsets, keys, values, (uint32_t)capacity,
+        (const MaskBand*)((const char*)workspace + bin_band_offset(P)));
     return check_launch();
 }
 
@@ -1194,9 +1358,14 @@ int fetch_sort_status(int* out)
 
 // The pairs start in (ka, va).  After `passes` passes they are in (ka, va) when `passes` is even, else in (kb, vb).
 // variant: see g_sort_variant; the one-sweep path needs onesweep_sort_bytes(n, passes) of workspace.
-static int sort_passes_run(int variant, int64_t n, int end_bit, uint64_t* ka, uint32_t* va, uint64_t* kb, uint32_t* vb,
-                           void* workspace, size_t workspace_bytes, unsigned long long wait_limit, cudaStream_t st)
+static int sort_passes_run(int variant, int64_t n, int end_bit, int low_bits, uint64_t* ka, uint32_t* va, uint64_t* kb,
+                           uint32_t* vb, void* workspace, size_t workspace_bytes, unsigned long long wait_limit,
+                           cudaStream_t st)
 {
+    // bits [low_bits, 32) are equal in all keys: the sort runs over the squeezed key of end_bit - (32 - low_bits) bits
+    if (low_bits < 0 || low_bits > 32) return CGX_EINVAL;
+    if (end_bit <= 32) low_bits = 32;
+    end_bit -= 32 - low_bits;
     const int passes = cgx_sort_passes(end_bit);
     if (passes == 0) return CGX_OK;
     uint64_t *kin = ka, *kout = kb;
@@ -1211,11 +1380,11 @@ static int sort_passes_run(int variant, int64_t n, int end_bit, uint64_t* ka, ui
         cudaError_t e = cudaMemsetAsync(workspace, 0, onesweep_sort_bytes(n, passes), st);
         if (e != cudaSuccess) { set_cuda_error(e); return CGX_ECUDA; }
         const int hist_grid = ntiles < 148 * 8 ? ntiles : 148 * 8;
-        os_hist_kernel<<<hist_grid, OS_THREADS, 0, st>>>(n, passes, end_bit, kin, ghist);
+        os_hist_kernel<<<hist_grid, OS_THREADS, 0, st>>>(n, passes, end_bit, low_bits, kin, ghist);
         for (int p = 0; p < passes; p++) {
             const int shift = p * RADIX_BITS;
             const int bits = (end_bit - shift) < RADIX_BITS ? (end_bit - shift) : RADIX_BITS;
-            os_pass_kernel<<<ntiles, OS_THREADS, 0, st>>>(n, shift, (1u << bits) - 1u, kin, vin, kout, vout,
+            os_pass_kernel<<<ntiles, OS_THREADS, 0, st>>>(n, digit_spec(shift, (1u << bits) - 1u, low_bits), kin, vin, kout, vout,
                                                          ghist + p * RADIX, tickets + p,
                                                          status + (size_t)p * ntiles * RADIX,
                                                          wait_limit ? wait_limit : OS_WAIT_LIMIT_CYCLES);
@@ -1239,13 +1408,14 @@ static int sort_passes_run(int variant, int64_t n, int end_bit, uint64_t* ka, ui
         const int shift = p * RADIX_BITS;
         const int bits = (end_bit - shift) < RADIX_BITS ? (end_bit - shift) : RADIX_BITS;
         const uint32_t mask = (1u << bits) - 1u;
-        sort_hist_kernel<<<nblocks, SORT_THREADS, 0, st>>>(n, nblocks, shift, mask, kin, table);
+        const DigitSpec dg = digit_spec(shift, mask, low_bits);
+        sort_hist_kernel<<<nblocks, SORT_THREADS, 0, st>>>(n, nblocks, dg, kin, table);
         sort_scan_rows_kernel<<<RADIX, 1024, 0, st>>>(nblocks, table, totals);
         if (direct)
-            sort_scatter_direct_kernel<<<nblocks, SORT_THREADS, 0, st>>>(n, nblocks, shift, mask, kin, vin, kout, vout,
+            sort_scatter_direct_kernel<<<nblocks, SORT_THREADS, 0, st>>>(n, nblocks, dg, kin, vin, kout, vout,
                                                                         table, totals);
         else
-            sort_scatter_kernel<<<nblocks, SORT_THREADS, SORT_SMEM, st>>>(n, nblocks, shift, mask, kin, vin, kout, vout,
+            sort_scatter_kernel<<<nblocks, SORT_THREADS, SORT_SMEM, st>>>(n, nblocks, dg, kin, vin, kout, vout,
                                                                          table, totals);
         uint64_t* tk = kin; kin = kout; kout = tk;
         uint32_t* tv = vin; vin = vout; vout = tv;
@@ -1268,11 +1438,11 @@ static int sort_pairs_into_out(int variant, int64_t n, int end_bit, uint64_t* ke
         cudaMemcpyAsync(keys_out, keys_in, n * sizeof(uint64_t), cudaMemcpyDeviceToDevice, st);
         cudaMemcpyAsync(values_out, values_in, n * sizeof(uint32_t), cudaMemcpyDeviceToDevice, st);
         if (passes == 0) return check_launch(0);
-        return sort_passes_run(variant, n, end_bit, keys_out, values_out, keys_in, values_in, workspace,
+        return sort_passes_run(variant, n, end_bit, 32, keys_out, values_out, keys_in, values_in, workspace,
                                workspace_bytes, 0ull, st);
     }
-    return sort_passes_run(variant, n, end_bit, keys_in, values_in, keys_out, values_out, workspace, workspace_bytes,
-                           0ull, st);
+    return sort_passes_run(variant, n, end_bit, 32, keys_in, values_in, keys_out, values_out, workspace,
+                           workspace_bytes, 0ull, st);
 }
 
 extern "C" int cgx_sort_pairs(int64_t n, int end_bit, uint64_t* keys_in, uint32_t* values_in, uint64_t* keys_out,
@@ -1285,17 +1455,17 @@ extern "C" int cgx_sort_pairs(int64_t n, int end_bit, uint64_t* keys_in, uint32_
                                workspace_bytes, stream);
 }
 
-extern "C" int cgx_sort_pairs_pingpong(int64_t n, int end_bit, uint64_t* keys_a, uint32_t* values_a, uint64_t* keys_b,
-                                       uint32_t* values_b, void* workspace, size_t workspace_bytes,
+extern "C" int cgx_sort_pairs_pingpong(int64_t n, int end_bit, int low_bits, uint64_t* keys_a, uint32_t* values_a,
+                                       uint64_t* keys_b, uint32_t* values_b, void* workspace, size_t workspace_bytes,
                                        unsigned long long wait_limit_cycles, void* stream)
 {
-    if (n < 0 || end_bit < 0 || end_bit > 64 || n > 0x7fffffffLL) return CGX_EINVAL;
+    if (n < 0 || end_bit < 0 || end_bit > 64 || n > 0x7fffffffLL || low_bits < 0 || low_bits > 32) return CGX_EINVAL;
     if (n == 0) return CGX_OK;
     if (!keys_a || !values_a || !keys_b || !values_b || !workspace) return CGX_EINVAL;
     if (workspace_bytes < legacy_sort_bytes(n) && workspace_bytes < onesweep_sort_bytes(n, cgx_sort_passes(end_bit)))
         return CGX_ENOMEM;
-    return sort_passes_run(g_sort_variant, n, end_bit, keys_a, values_a, keys_b, values_b, workspace, workspace_bytes,
-                           wait_limit_cycles, (cudaStream_t)stream);
+    return sort_passes_run(g_sort_variant, n, end_bit, low_bits, keys_a, values_a, keys_b, values_b, workspace,
+                           workspace_bytes, wait_limit_cycles, (cudaStream_t)stream);
 }
 
 extern "C" int cgx_tile_ranges(int64_t n, int T, const uint64_t* keys_sorted, uint32_t* ranges, void* stream)

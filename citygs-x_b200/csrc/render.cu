@@ -146,9 +146,23 @@ __device__ __forceinline__ uint32_t block_pixel_mask(const float4 q0, const floa
 #ifndef CGX_DENSE_PIXELS_PER_VISIT
 #define CGX_DENSE_PIXELS_PER_VISIT 6
 #endif
+#ifndef CGX_FWD_MIN_LIST_CHUNK
+#define CGX_FWD_MIN_LIST_CHUNK 20
+#endif
+#ifndef CGX_DENSE_PIXELS_PER_VISIT_FWD
+#define CGX_DENSE_PIXELS_PER_VISIT_FWD 7
+#endif
+constexpr int DENSITY_SLOTS = 32;     // CTAs add into slot (tile id mod 32): no single hot address
+constexpr size_t DENSITY_BYTES = DENSITY_SLOTS * 2 * sizeof(unsigned long long);
 __device__ __forceinline__ bool density_says_dense(const unsigned long long* density)
 {
-    return density[0] > (unsigned long long)CGX_DENSE_PIXELS_PER_VISIT * density[1];
+    unsigned long long pixels = 0, visits = 0;
+#pragma unroll 4
+    for (int k = 0; k < DENSITY_SLOTS; k++) {
+        pixels += density[2 * k];
+        visits += density[2 * k + 1];
+    }
+    return pixels > (unsigned long long)CGX_DENSE_PIXELS_PER_VISIT * visits;
 }
 
 // ------------------------------------------------------------------------------------------------ pack
@@ -159,11 +173,7 @@ pack_records_kernel(int P, const int* __restrict__ radii, const float2* __restri
                     int* __restrict__ out_observe)
 {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i == 0) {
-        unsigned long long* density = reinterpret_cast<unsigned long long*>(records + P);
-        density[0] = 0ull;
-        density[1] = 0ull;
-    }
+    if (i < 2 * DENSITY_SLOTS) reinterpret_cast<unsigned long long*>(records + P)[i] = 0ull;
     if (i >= P) return;
     if (out_observe) out_observe[i] = 0;
     // Gaussians without a radius never enter a tile list: their record is never read, so it is not written
@@ -193,7 +203,7 @@ struct FwdSmem {
     int id[2][CGX_BLOCK_SIZE];
     uint8_t hits[RENDER_WARPS][CGX_BLOCK_SIZE];
     uint64_t bar[2];
-    int red[2][RENDER_WARPS];
+    int red[4][RENDER_WARPS];
 };
 
 // MODE 0: every pixel looks at every Gaussian of the batch (the reference's loop); MODE 1: per-warp culling, then
@@ -281,7 +291,10 @@ render_fwd_kernel(const uint2* __restrict__ ranges, const uint32_t* __restrict__
     float C[CGX_NCH] = {0};
     float All_map[CGX_NMAP] = {0};
     bool failed = false;
-    uint32_t dens_rows = 0, dens_visits = 0;   // this lane's share of the density counters
+    uint32_t dens_rows = 0, dens_visits = 0;   // this warp's measured chunks: pixels reached, visits (warp-uniform)
+    bool warp_dense = false;
+    uint32_t chunk_no = 0;
+    uint32_t lane_rows = 0;                    // pixels this lane blended in chunks that were not measured
 
     if (rounds > 0) issue(0, 0);
 
@@ -319,17 +332,27 @@ render_fwd_kernel(const uint2* __restrict__ ranges, const uint32_t* __restrict__
                 for (int base = 0; base < n_hits; base += 32) {
                     if (__all_sync(0xffffffffu, done)) break;
                     const int g = min(32, n_hits - base);
+                    // This warp's choice of walk follows the density of its own block so far (pixels reached per
+                    // visit).  While it walks densely it measures one chunk in four.
+                    // A short chunk gives per-pixel lists nothing to skip: it is walked by every pixel as well.
+                    const bool short_chunk = g < CGX_FWD_MIN_LIST_CHUNK;
+                    const bool measure = !short_chunk && (!warp_dense || (chunk_no++ & 3) == 0);
                     // phase 1: lane v tests Gaussian v against the block's pixels (only those in its safe box) ...
                     uint32_t pm = 0;
-                    if (lane < g && !(CGX_EXPERIMENT & 1)) {
+                    if (measure && lane < g && !(CGX_EXPERIMENT & 1)) {
                         const int j = my_hits[base + lane];
                         const float4 q3 = rec[j].q3;
                         pm = block_pixel_mask(rec[j].q0, *reinterpret_cast<const float2*>(&rec[j].q1), q3.z, q3.w, sx0,
                                               sy0);
                     }
-                    dens_rows += __popc(pm);
-                    if (lane == 0) dens_visits += g;
-                    if (__reduce_add_sync(0xffffffffu, __popc(pm)) > (unsigned)(CGX_DENSE_PIXELS_PER_VISIT * g)) {
+                    if (measure) {
+                        dens_rows += __reduce_add_sync(0xffffffffu, __popc(pm));
+                        dens_visits += g;
+                        warp_dense = dens_rows > (unsigned)CGX_DENSE_PIXELS_PER_VISIT_FWD * dens_visits;
+                    }
+                    const bool use_dense = warp_dense || short_chunk;
+                    if (use_dense && !measure) dens_visits += g;      // its pixels are counted as they are blended
+                    if (use_dense) {
                         // splats that cover most of the block: every pixel looks at every visit (no lists to build)
                         for (int v = 0; v < g; v++) {
                             if (done) continue;
@@ -345,6 +368,7 @@ render_fwd_kernel(const uint2* __restrict__ ranges, const uint32_t* __restrict__
                                 continue;
                             }
                             thread_n_contrib2loss++;
+                            if (!measure) lane_rows++;
                             const float4 q2 = rec[j].q2;
                             const float feat[CGX_NCH] = {q1.z, q1.w, q2.x};
                             for (int ch = 0; ch < CGX_NCH; ch++) C[ch] += feat[ch] * alpha * T;
@@ -464,13 +488,6 @@ render_fwd_kernel(const uint2* __restrict__ ranges, const uint32_t* __restrict__
             }
         }
     }
-    if (MODE == 2 && density) {
-        const uint32_t r = __reduce_add_sync(0xffffffffu, dens_rows);
-        if (lane == 0 && dens_visits) {
-            atomicAdd(density, (unsigned long long)r);
-            atomicAdd(density + 1, (unsigned long long)dens_visits);
-        }
-    }
     if (failed && lane == 0) atomicExch(&g_status, CGX_ETIMEDOUT);
 
     if (inside) {
@@ -495,20 +512,31 @@ render_fwd_kernel(const uint2* __restrict__ ranges, const uint32_t* __restrict__
         a += __shfl_xor_sync(0xffffffffu, a, o);
         b += __shfl_xor_sync(0xffffffffu, b, o);
     }
+    dens_rows += __reduce_add_sync(0xffffffffu, lane_rows);
     if (lane == 0) {
         sm.red[0][warp] = a;
         sm.red[1][warp] = b;
+        sm.red[2][warp] = (int)dens_rows;      // lane 0 adds the unmeasured chunks' pixels below
+        sm.red[3][warp] = (int)dens_visits;
     }
     __syncthreads();
     if (tid == 0) {
         int sa = 0, sb = 0;
+        unsigned long long dr = 0, dv = 0;
         for (int w = 0; w < RENDER_WARPS; w++) {
             sa += sm.red[0][w];
             sb += sm.red[1][w];
+            dr += (unsigned)sm.red[2][w];
+            dv += (unsigned)sm.red[3][w];
         }
         n_render_t[block_id] = range.y - range.x;
         n_consider_t[block_id] = sa;
         n_contrib_t[block_id] = sb;
+        if (MODE == 2 && density && dv) {
+            unsigned long long* slot = density + 2 * (block_id % DENSITY_SLOTS);
+            atomicAdd(slot, dr);
+            atomicAdd(slot + 1, dv);
+        }
     }
 }
 
@@ -701,7 +729,12 @@ __device__ __forceinline__ void bwd_pixel_init(BwdPixel& px, bool inside, uint32
 // The common head of both backward kernels: tile / pixel coordinates and the staging pipeline.
 #define CGX_BWD_PROLOGUE()                                                                                           \
     /* two walks are launched when the forward pass measured the density: only the suitable one works */            \
-    if (density && density_says_dense(density) != (want_dense != 0)) return;                                         \
+    if (density) {                                                                                                   \
+        __shared__ int s_not_mine;                                                                                   \
+        if (threadIdx.x == 0) s_not_mine = density_says_dense(density) != (want_dense != 0);                         \
+        __syncthreads();                                                                                             \
+        if (s_not_mine) return;                                                                                      \
+    }                                                                                                                \
     const uint32_t horizontal_blocks = (W + CGX_BLOCK_X - 1) / CGX_BLOCK_X;                                          \
     const uint32_t block_id = blockIdx.y * horizontal_blocks + blockIdx.x;                                           \
     if (!compute_locally[block_id]) return;                                                                          \
@@ -1014,8 +1047,11 @@ __global__ void __launch_bounds__(256) zero_arrays_kernel(ZeroJobs z)
 
 using namespace cgx;
 
-// P records, then two 64-bit counters the forward pass leaves for the backward pass (see Density below)
-extern "C" size_t cgx_render_records_bytes(int P) { return (size_t)(P > 0 ? P : 0) * sizeof(Record) + 128; }
+// P records, then the density counters the forward pass leaves for the backward pass
+extern "C" int cgx_render_density_words(void) { return 2 * DENSITY_SLOTS; }
+extern "C" int cgx_render_dense_threshold(void) { return CGX_DENSE_PIXELS_PER_VISIT; }
+
+extern "C" size_t cgx_render_records_bytes(int P) { return (size_t)(P > 0 ? P : 0) * sizeof(Record) + DENSITY_BYTES; }
 
 namespace cgx {
 int fetch_render_status_async(int* out_pinned, cudaStream_t st)
@@ -1115,9 +1151,9 @@ extern "C" int cgx_render_bwd(int P, int W, int H, float tanfovx, float tanfovy,
                               const uint8_t* compute_locally, const float* dL_dcolor, const float* dL_dout_all_map,
                               const float* dL_dout_plane_depth, int render_geo, float* dL_dmeans2D,
                               float* dL_dmeans2D_abs, float* dL_dconic_opacity, float* dL_drgb, float* dL_dall_map,
-                              void* stream)
+                              int walk, void* stream)
 {
-    if (P < 0 || W <= 0 || H <= 0) return CGX_EINVAL;
+    if (P < 0 || W <= 0 || H <= 0 || walk < 0 || walk > 2) return CGX_EINVAL;
     if (P == 0) return CGX_OK;
     if (!ranges) return CGX_EINVAL;
     if (!bg || !records || !final_T || !n_contrib || !compute_locally || !dL_dcolor || !dL_dmeans2D ||
@@ -1175,6 +1211,10 @@ extern "C" int cgx_render_bwd(int P, int W, int H, float tanfovx, float tanfovy,
         CGX_LAUNCH_BWD(render_bwd_kernel<true>, sizeof(BwdSmem), nullptr, 0);
     else if (g_render_variant & 4)
         CGX_LAUNCH_BWD(render_bwd2_kernel, sizeof(BwdSmem2), nullptr, 0);
+    else if (walk == 1)
+        CGX_LAUNCH_BWD(render_bwd2_kernel, sizeof(BwdSmem2), nullptr, 0);       // the caller has read the density
+    else if (walk == 2)
+        CGX_LAUNCH_BWD(render_bwd_kernel<true>, sizeof(BwdSmem), nullptr, 0);
     else {
         CGX_LAUNCH_BWD(render_bwd2_kernel, sizeof(BwdSmem2), density, 0);
         CGX_LAUNCH_BWD(render_bwd_kernel<true>, sizeof(BwdSmem), density, 1);

@@ -270,9 +270,18 @@ def _prefetch_key(means2D, radii, local, H, W):
             means2D._version, radii._version, local._version)
 
 
-def prefetch_num_rendered(image_height, image_width, means2D, radii, compute_locally):
+def _low_bits(dmin, dmax):
+    """Varying low bits of the depth words of the sort keys, from the smallest and largest depth bit pattern."""
+    dmin, dmax = dmin & 0xFFFFFFFF, dmax & 0xFFFFFFFF
+    if dmin > dmax:
+        return 32                      # no pairs
+    return max(1, (dmin ^ dmax).bit_length())
+
+
+def prefetch_num_rendered(image_height, image_width, means2D, radii, compute_locally, depths=None):
     """Launch the tile-count + prefix-sum stage of a coming render_gaussians call with these same tensors and copy
-    the pair count to pinned host memory without waiting for it.  Not part of the reference's module."""
+    the pair count (and, when `depths` is given, the depth range that lets the sort skip a pass) to pinned host
+    memory without waiting for it.  Not part of the reference's module."""
     global _prefetch_pinned, _prefetch_next
     l = _lib.lib()
     means2D = _cuda_f32(means2D, "means2D")
@@ -283,7 +292,7 @@ def prefetch_num_rendered(image_height, image_width, means2D, radii, compute_loc
     if P == 0 or radii.dtype != torch.int32:
         return
     if _prefetch_pinned is None:
-        _prefetch_pinned = torch.zeros(_PREFETCH_SLOTS, dtype=torch.int32).pin_memory()
+        _prefetch_pinned = torch.zeros(_PREFETCH_SLOTS, 3, dtype=torch.int32).pin_memory()
     if len(_PREFETCH) >= _PREFETCH_SLOTS // 2:
         _PREFETCH.clear()                       # counts nobody picked up
     slot = _prefetch_next
@@ -292,14 +301,26 @@ def prefetch_num_rendered(image_height, image_width, means2D, radii, compute_loc
         glay = geometry_layout(P)
         geomBuffer = torch.empty(glay.total(), dtype=torch.uint8, device=dev)
         g = glay.views(geomBuffer)
-        _call("cgx_bin_count_scan", l.cgx_bin_count_scan, P, W, H, _ptr(radii), _ptr(means2D), _ptr(local),
-              _ptr(g["tiles_touched"]), _ptr(g["num_rendered"]), _ptr(g["scanning_space"]),
-              g["scanning_space"].numel(), _stream(), info=dict(P=P))
-        _prefetch_pinned[slot:slot + 1].copy_(g["num_rendered"][0:1], non_blocking=True)
+        _count_scan(l, P, W, H, radii, means2D, None if depths is None else _cuda_f32(depths, "depths"), local, g,
+                    _stream())
+        _prefetch_pinned[slot].copy_(g["num_rendered"][0:3], non_blocking=True)      # [1:3] only meaningful with depths
         ev = torch.cuda.Event()
         ev.record()
     # the tensors are kept alive with the entry, so their addresses cannot be reused while it exists
-    _PREFETCH[_prefetch_key(means2D, radii, local, H, W)] = (geomBuffer, slot, ev, (means2D, radii, local))
+    _PREFETCH[_prefetch_key(means2D, radii, local, H, W)] = (geomBuffer, slot, ev, (means2D, radii, local),
+                                                             depths is not None)
+
+
+def _count_scan(l, P, W, H, radii, means2D, depths, local, g, st):
+    """Tile counting + prefix sum; with depths also their range (num_rendered[1:3])."""
+    if depths is None:
+        _call("cgx_bin_count_scan", l.cgx_bin_count_scan, P, W, H, _ptr(radii), _ptr(means2D), _ptr(local),
+              _ptr(g["tiles_touched"]), _ptr(g["num_rendered"]), _ptr(g["scanning_space"]),
+              g["scanning_space"].numel(), st, info=dict(P=P))
+    else:
+        _call("cgx_bin_count_scan", l.cgx_bin_count_scan_depths, P, W, H, _ptr(radii), _ptr(means2D), _ptr(depths),
+              _ptr(local), _ptr(g["tiles_touched"]), _ptr(g["num_rendered"]), _ptr(g["scanning_space"]),
+              g["scanning_space"].numel(), st, info=dict(P=P))
 
 
 def render_gaussians(background, image_height, image_width, means2D, depths, radii, conic_opacity, rgb,
@@ -347,18 +368,18 @@ def render_gaussians(background, image_height, image_width, means2D, depths, rad
         im = ilay.views(imgBuffer)
         pre = _PREFETCH.pop(_prefetch_key(means2D, radii, local, H, W), None) if _PREFETCH else None
         if pre is not None:
-            geomBuffer, slot, ev, _ = pre
+            geomBuffer, slot, ev, _, has_range = pre
             g = glay.views(geomBuffer)
             ev.synchronize()
-            R = int(_prefetch_pinned[slot])
+            R, dmin, dmax = _prefetch_pinned[slot].tolist()
+            if not has_range:
+                dmin, dmax = -1, 0
         else:
             geomBuffer = torch.empty(glay.total(), dtype=torch.uint8, device=dev)
             g = glay.views(geomBuffer)
-            _call("cgx_bin_count_scan", l.cgx_bin_count_scan, P, W, H, _ptr(radii), _ptr(means2D), _ptr(local),
-                  _ptr(g["tiles_touched"]), _ptr(g["num_rendered"]), _ptr(g["scanning_space"]),
-                  g["scanning_space"].numel(), st, info=dict(P=P))
+            _count_scan(l, P, W, H, radii, means2D, depths, local, g, st)
             # the key/value buffers are sized from the pair count: one host read, as in the reference
-            R = int(g["num_rendered"][0].item())
+            R, dmin, dmax = g["num_rendered"][0:3].tolist()
 
         blay = binning_layout(R)
         binningBuffer = torch.empty(blay.total(), dtype=torch.uint8, device=dev)
@@ -370,16 +391,18 @@ def render_gaussians(background, image_height, image_width, means2D, depths, rad
         # the sort ping-pongs between the two key/value arrays: the pairs are emitted into whichever array makes
         # the last pass land in point_list_keys / point_list (no copy, whatever the number of passes)
         bit = int(l.cgx_higher_msb(T))
-        first = ("point_list_keys", "point_list") if l.cgx_sort_passes(32 + bit) % 2 == 0 else \
+        # depths of one view share their leading bits: the sort squeezes them out of its digits
+        low_bits = _low_bits(dmin, dmax)
+        first = ("point_list_keys", "point_list") if l.cgx_sort_passes(low_bits + bit) % 2 == 0 else \
             ("point_list_keys_unsorted", "point_list_unsorted")
         other = ("point_list_keys_unsorted", "point_list_unsorted") if first[0] == "point_list_keys" else \
             ("point_list_keys", "point_list")
         _call("cgx_emit_keys", l.cgx_emit_keys, P, W, H, _ptr(radii), _ptr(means2D), _ptr(depths), _ptr(g["tiles_touched"]),
                               _ptr(local), _ptr(g["point_offsets"]), _ptr(b[first[0]]), _ptr(b[first[1]]), R,
                               _ptr(g["scanning_space"]), st, info=dict(P=P, R=R))
-        _call("cgx_sort_pairs", l.cgx_sort_pairs_pingpong, R, 32 + bit, _ptr(b[first[0]]), _ptr(b[first[1]]),
-                               _ptr(b[other[0]]), _ptr(b[other[1]]), _ptr(b["list_sorting_space"]),
-                               b["list_sorting_space"].numel(), 0, st, info=dict(R=R, bits=32 + bit))
+        _call("cgx_sort_pairs", l.cgx_sort_pairs_pingpong, R, 32 + bit, low_bits, _ptr(b[first[0]]),
+                               _ptr(b[first[1]]), _ptr(b[other[0]]), _ptr(b[other[1]]), _ptr(b["list_sorting_space"]),
+                               b["list_sorting_space"].numel(), 0, st, info=dict(R=R, bits=low_bits + bit))
         _call("cgx_tile_ranges", l.cgx_tile_ranges, R, T, _ptr(b["point_list_keys"]), _ptr(im["ranges"]), st, info=dict(R=R, T=T))
         _call("cgx_render_fwd", l.cgx_render_fwd, P, W, H, float(tan_fovx), float(tan_fovy), _ptr(im["ranges"]), _ptr(b["point_list"]),
                                _ptr(radii), _ptr(means2D), _ptr(rgb), _ptr(all_map), _ptr(conic_opacity), _ptr(local), _ptr(bg),
@@ -391,10 +414,48 @@ def render_gaussians(background, image_height, image_width, means2D, depths, rad
         if stats is not None:
             ev1.record()
             stats["forward_render_time"] = _EventMs([(ev0, ev1)])
+        _density_copy(geomBuffer, g["records"], P)
         if debug:
             _check_device(dev)
     return (R, out_color, n_render, n_consider, n_contrib, out_observe, out_all_map, out_plane_depth,
             geomBuffer, binningBuffer, imgBuffer)
+
+
+# ---- density hand-over --------------------------------------------------------------------------------------
+# The forward pass measures how densely the splats cover the pixel blocks they touch and leaves the counters behind
+# its records; the backward pass picks its walk from them.  It can do so on the device (both kernels queued, one
+# returns at once).  Cheaper: the counters are copied to pinned memory right behind the forward pass, and if they
+# have arrived by the time the backward pass is queued (they have whenever something else ran in between) the
+# choice is made here and one kernel is launched.  The copy is never waited for.
+_DENSITY = {}
+_density_pinned = None
+_density_next = 0
+_DENSITY_SLOTS = 256
+
+
+def _density_copy(geomBuffer, records, P):
+    global _density_pinned, _density_next
+    n = _lib.lib().cgx_render_density_words()
+    if _density_pinned is None:
+        _density_pinned = torch.zeros(_DENSITY_SLOTS, n, dtype=torch.int64).pin_memory()
+    if len(_DENSITY) >= _DENSITY_SLOTS // 2:
+        _DENSITY.clear()                        # forward passes whose backward never came
+    slot = _density_next
+    _density_next = (_density_next + 1) % _DENSITY_SLOTS
+    _density_pinned[slot].copy_(records[P * 64: P * 64 + 8 * n].view(torch.int64), non_blocking=True)
+    ev = torch.cuda.Event()
+    ev.record()
+    _DENSITY[geomBuffer.data_ptr()] = (slot, ev)
+
+
+def _density_walk(geomBuffer):
+    """0: let the device decide; 1: per-pixel lists; 2: every pixel looks at every visit."""
+    hit = _DENSITY.pop(geomBuffer.data_ptr(), None)
+    if hit is None or not hit[1].query():
+        return 0
+    c = _density_pinned[hit[0]]
+    pixels, visits = int(c[0::2].sum()), int(c[1::2].sum())
+    return 2 if pixels > _lib.lib().cgx_render_dense_threshold() * visits else 1
 
 
 def render_gaussians_backward(background, tan_fovx, tan_fovy, all_map_pixels, all_maps, R, geomBuffer, binningBuffer,
@@ -446,8 +507,8 @@ def render_gaussians_backward_2d(background, tan_fovx, tan_fovy, all_map_pixels,
                                    _ptr(_cuda_f32(dL_dout_all_map, "dL_dout_all_map")),
                                    _ptr(_cuda_f32(dL_dout_plane_depth, "dL_dout_plane_depth")),
                                    int(bool(render_geo)), _ptr(dL_dmeans2D), _ptr(dL_dmeans2D_abs),
-                                   _ptr(dL_dconic_opacity), _ptr(dL_dcolors), _ptr(dL_dall_map), st,
-                                   info=dict(P=P, R=R, HW=H * W, local=local))
+                                   _ptr(dL_dconic_opacity), _ptr(dL_dcolors), _ptr(dL_dall_map),
+                                   _density_walk(geomBuffer), st, info=dict(P=P, R=R, HW=H * W, local=local))
             if stats is not None:
                 ev1.record()
                 stats["backward_render_time"] = _EventMs([(ev0, ev1)])

@@ -89,11 +89,12 @@ SIGNATURES = {
     "cgx_peer_barrier_limited": (_i, [_i, _i, _vp, C.c_uint32, C.c_uint64, _vp]),
     "cgx_bin_workspace_bytes": (_sz, [_i]),
     "cgx_bin_count_scan": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
+    "cgx_bin_count_scan_depths": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "cgx_emit_keys": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _vp, _vp]),
     "cgx_sort_workspace_bytes": (_sz, [_i64]),
     "cgx_sort_pairs": (_i, [_i64, _i, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "cgx_sort_passes": (_i, [_i]),
-    "cgx_sort_pairs_pingpong": (_i, [_i64, _i, _vp, _vp, _vp, _vp, _vp, _sz, C.c_uint64, _vp]),
+    "cgx_sort_pairs_pingpong": (_i, [_i64, _i, _i, _vp, _vp, _vp, _vp, _vp, _sz, C.c_uint64, _vp]),
     "cgx_sort_pairs_static_max": (_i64, []),
     "cgx_sort_pairs_static": (_i, [_i64, _i, _vp, _vp, _vp, _vp, _vp]),
     "cgx_set_sort_variant": (_i, [_i]),
@@ -102,7 +103,9 @@ SIGNATURES = {
     "cgx_render_fwd": (_i, [_i, _i, _i, _f, _f] + [_vp] * 9 + [_i] + [_vp] * 12),
     "cgx_launch_count": (C.c_uint64, []),
     "cgx_tile_stats": (_i, [_i, _i] + [_vp] * 8),
-    "cgx_render_bwd": (_i, [_i, _i, _i, _f, _f] + [_vp] * 11 + [_i] + [_vp] * 6),
+    "cgx_render_bwd": (_i, [_i, _i, _i, _f, _f] + [_vp] * 11 + [_i] + [_vp] * 5 + [_i, _vp]),
+    "cgx_render_density_words": (_i, []),
+    "cgx_render_dense_threshold": (_i, []),
     "cgx_device_status": (_i, [_vp, _vp]),
     "cgx_device_status_async": (_i, [_vp, _vp]),
     "cgx_set_render_variant": (_i, [_i]),

@@ -349,6 +349,14 @@ size_t cgx_bin_workspace_bytes(int P);
 int cgx_bin_count_scan(int P, int W, int H, const int32_t* radii, const float* means2D,
                        const uint8_t* compute_locally, uint32_t* tiles_touched, uint32_t* num_rendered,
                        void* workspace, size_t workspace_bytes, void* stream);
+/* The same stage, also reducing the depths of the splats that will emit keys: num_rendered3[0] = pairs,
+ * [1] / [2] = smallest / largest bit pattern of their (positive) depths (0xffffffff / 0 when there are none).  The
+ * caller reads all three in the host read it makes anyway; the leading bits the two patterns share are equal in
+ * every sort key, which is what cgx_sort_pairs_pingpong's low_bits wants:
+ * low_bits = 32 - clz(min ^ max)  (at least 1). */
+int cgx_bin_count_scan_depths(int P, int W, int H, const int32_t* radii, const float* means2D, const float* depths,
+                              const uint8_t* compute_locally, uint32_t* tiles_touched, uint32_t* num_rendered3,
+                              void* workspace, size_t workspace_bytes, void* stream);
 
 /* duplicateWithKeys (RAST/cuda_rasterizer/rasterizer_impl.cu:74-117): writes point_offsets u32 (P)
  * (inclusive sum, as the reference's GeometryState::point_offsets), keys u64 (R) =
@@ -371,12 +379,17 @@ int cgx_sort_pairs(int64_t n, int end_bit, uint64_t* keys_in, uint32_t* values_i
 
 /* The same sort for a caller that owns both buffers and can choose where its pairs start (same call site: the
  * reference's BinningState holds both the unsorted and the sorted arrays, rasterizer_impl.cu:188-205).  The pairs
- * start in (keys_a, values_a); the result lands in (keys_a, values_a) when cgx_sort_passes(end_bit) is even and in
- * (keys_b, values_b) when it is odd, so no copy is ever needed.  wait_limit_cycles: only used by the test-only
- * one-sweep variant (bound of its look-back wait in SM clock cycles, 0 = default of about 0.14 s). */
+ * start in (keys_a, values_a); the result lands in (keys_a, values_a) when the number of passes is even and in
+ * (keys_b, values_b) when it is odd, so no copy is ever needed.
+ * low_bits (1..32; 32 = plain sort): the caller asserts that bits [low_bits, 32) of every key are equal (for
+ * (tile << 32 | depth) keys: the sign, the leading exponent bits ... that all depths of a view share; see
+ * cgx_bin_count_scan_depths).  Equal bits cannot change a stable order, so they are squeezed out of the digits:
+ * passes = cgx_sort_passes(end_bit - (32 - low_bits)), often one fewer.  The keys themselves are moved unchanged.
+ * wait_limit_cycles: only used by the test-only one-sweep variant (bound of its look-back wait in SM clock cycles,
+ * 0 = default of about 0.14 s). */
 int cgx_sort_passes(int end_bit);
-int cgx_sort_pairs_pingpong(int64_t n, int end_bit, uint64_t* keys_a, uint32_t* values_a, uint64_t* keys_b,
-                            uint32_t* values_b, void* workspace, size_t workspace_bytes,
+int cgx_sort_pairs_pingpong(int64_t n, int end_bit, int low_bits, uint64_t* keys_a, uint32_t* values_a,
+                            uint64_t* keys_b, uint32_t* values_b, void* workspace, size_t workspace_bytes,
                             unsigned long long wait_limit_cycles, void* stream);
 
 
@@ -436,7 +449,17 @@ int cgx_render_bwd(int P, int W, int H, float tanfovx, float tanfovy, const uint
                    const uint8_t* compute_locally, const float* dL_dcolor, const float* dL_dout_all_map,
                    const float* dL_dout_plane_depth, int render_geo,
                    float* dL_dmeans2D, float* dL_dmeans2D_abs, float* dL_dconic_opacity, float* dL_drgb,
-                   float* dL_dall_map, void* stream);
+                   float* dL_dall_map, int walk, void* stream);
+
+/* How the backward pass chooses its walk.  cgx_render_fwd leaves, behind the P records of its `records` buffer,
+ * cgx_render_density_words() 64-bit counters: pairs (pixels that passed the alpha test, visits of a Gaussian to an
+ * 8x4 pixel block), spread over slots.  walk = 0: cgx_render_bwd queues both of its kernels and the one the
+ * counters do not call for returns at once (no host read).  A caller that has the counters on the host anyway
+ * (copied behind the forward pass; by the time of the backward pass they have usually arrived) sums the pairs and
+ * passes walk = 2 (every pixel looks at every visit) when pixels > cgx_render_dense_threshold() * visits, else
+ * walk = 1 (every pixel walks its own list): one launch instead of two. */
+int cgx_render_density_words(void);
+int cgx_render_dense_threshold(void);
 
 /* ------------------------------------------------------------------ diagnostics */
 

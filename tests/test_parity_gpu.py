@@ -282,16 +282,25 @@ def test_cull_variant_is_identical(cuda_device):
         assert rel_l2(a[k], e[k]) <= 1e-5, k
 
 
-def test_partial_compute_locally(cuda_device, reference_C):
-    """Only a band of tile rows is local: keys only for local tiles, other pixels zero."""
+@pytest.mark.parametrize("shape", ["band", "scattered", "none"])
+def test_partial_compute_locally(shape, cuda_device, reference_C):
+    """Only some tiles are local: keys only for local tiles, other pixels zero.  A band of whole tile rows (what the
+    workload division produces) takes the library's row-band shortcut, scattered tiles the per-tile lookups."""
     from oracle import cpu_raster as O
 
     g, cam = make_case(cfg=1, n=50000, res=(640, 360))
     TX, TY = (cam.W + 15) // 16, (cam.H + 15) // 16
     local = torch.zeros(TY, TX, dtype=torch.bool)
-    local[5:13] = True
+    if shape == "band":
+        local[5:13] = True
+    elif shape == "scattered":
+        local[:] = torch.rand(TY, TX, generator=torch.Generator().manual_seed(5)) > 0.5
+        local[7] = True          # a full row among partial ones
     cot = cotangents(cam)
     ours = run_ours(g, cam, cuda_device, local=local, cot=cot)
+    if shape == "none":
+        assert ours["R"] == 0 and ours["color"].abs().max().item() == 0.0
+        return
     b = O.bin_and_sort(ours["means2D"], ours["depths"], ours["radii"], local, cam.W, cam.H)
     assert b["R"] == ours["R"]
     assert torch.equal(b["keys"], ours["keys"]) and torch.equal(b["point_list"], ours["point_list"])
@@ -491,11 +500,24 @@ def test_sort_pairs_variants(n, end_bit, cuda_device):
             assert torch.equal(vout.cpu().long(), order) and torch.equal(kout.cpu(), keys[order]), variant
             ka, va = keys.to(dev), vals.to(dev)
             kb, vb = torch.zeros_like(ka), torch.zeros_like(va)
-            assert l.cgx_sort_pairs_pingpong(n, end_bit, ka.data_ptr(), va.data_ptr(), kb.data_ptr(), vb.data_ptr(),
-                                             ws.data_ptr(), ws.numel(), 0, st) == 0
+            assert l.cgx_sort_pairs_pingpong(n, end_bit, 32, ka.data_ptr(), va.data_ptr(), kb.data_ptr(),
+                                             vb.data_ptr(), ws.data_ptr(), ws.numel(), 0, st) == 0
             torch.cuda.synchronize()
             k, v = (ka, va) if passes % 2 == 0 else (kb, vb)
             assert torch.equal(v.cpu().long(), order) and torch.equal(k.cpu(), keys[order]), variant
+            if end_bit > 32:
+                # keys whose depth words share their 7 leading bits (as the depths of one view do): the sort is told
+                # so and runs over 25 + tile bits, the keys travel unchanged and the order is that of the full sort
+                low = 25
+                shared = (keys & ~torch.tensor(0xFE000000, dtype=torch.int64)) | 0x42000000
+                want = torch.sort(shared & ((1 << end_bit) - 1), stable=True)[1]
+                ka, va = shared.to(dev), vals.to(dev)
+                kb, vb = torch.zeros_like(ka), torch.zeros_like(va)
+                assert l.cgx_sort_pairs_pingpong(n, end_bit, low, ka.data_ptr(), va.data_ptr(), kb.data_ptr(),
+                                                 vb.data_ptr(), ws.data_ptr(), ws.numel(), 0, st) == 0
+                torch.cuda.synchronize()
+                k, v = (ka, va) if l.cgx_sort_passes(end_bit - (32 - low)) % 2 == 0 else (kb, vb)
+                assert torch.equal(v.cpu().long(), want) and torch.equal(k.cpu(), shared[want]), variant
     finally:
         l.cgx_set_sort_variant(-1)
     status = C.c_int(-1)
