@@ -261,7 +261,11 @@ def _gather_table(table, n_counts, piggyback, group, ws, overlap=None):
         stage = _pinned.get(("table", out.numel()))
         if stage is None:
             stage = _pinned[("table", out.numel())] = torch.empty(out.numel(), dtype=torch.int32).pin_memory()
-        stage.copy_(out, non_blocking=True)
+        from diff_gaussian_rasterization import _lib
+
+        # carried by a kernel: a copy-engine transfer would queue behind bulk read-backs of other streams
+        _lib.check(_lib.lib().cgx_post_words(C.c_void_p(out.data_ptr()), C.c_void_p(stage.data_ptr()), out.numel(),
+                                             _lib.current_stream_ptr()), "cgx_post_words")
         status = _queue_status_read()
         ev = torch.cuda.Event()
         ev.record()

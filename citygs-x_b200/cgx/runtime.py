@@ -126,6 +126,7 @@ class TrainingStep:
 
     # ------------------------------------------------------------------ single-GPU step
     _pipeline = None        # cgx.batched.Pipeline while an end-to-end step is in flight
+    _e2e_sets = None        # two (parameters, upstream-gradient images) buffer sets that end-to-end steps alternate
 
     def _preprocess_all(self, args, planes=False):
         """Screen-space state of the local Gaussians for every camera of the batch (one launch).  With `planes`
@@ -186,7 +187,7 @@ class TrainingStep:
             main.wait_stream(s)
         self.last = outs
 
-    render_streams = 1      # > 1: cameras of the single-GPU step alternate between that many CUDA streams
+    render_streams = 2      # cameras of the single-GPU step alternate between that many CUDA streams (1: one stream)
     _side_streams = None
 
     def _streams(self, main):
@@ -338,8 +339,10 @@ class TrainingStep:
         and each camera's backward waits for its own images only; the parameter gradients leave piece by piece
         behind the chunks of the batched preprocess backward, on a stream of their own: the call returns without
         waiting for them, so that the read-back of step t (device to host) runs beside the uploads of step t + 1
-        (host to device) when steps follow each other.  `finish_e2e()` waits for everything; `grad_host` is
-        complete after it."""
+        (host to device) when steps follow each other.  Parameters and images land in one of two buffer sets that
+        alternate between calls, so the uploads of a call do not wait for the kernels of the call before it: they
+        run beside its backward pass (the host is free as soon as that pass is queued).  `finish_e2e()` waits for
+        everything; `grad_host` is complete after it.  `self.params` names the set of the latest call."""
         from .batched import Pipeline, chunk_bounds
 
         main = torch.cuda.current_stream()
@@ -355,8 +358,23 @@ class TrainingStep:
         pipelined = self.batched and chunks > 1 and fused
         bounds = chunk_bounds(self.n_local, chunks if pipelined else 1)
         names = ("means3D", "scales", "rotations", "opacities")
+        # Two sets of device buffers alternate between steps: the uploads of step t + 1 wait only for the kernels of
+        # step t - 1 (the last user of their set) and so run beside the kernels of step t.
+        if self._e2e_sets is None:
+            with torch.no_grad():
+                other = ({k: v.detach().clone().requires_grad_(True) for k, v in self.params.items()},
+                         [[c.clone() for c in cs] for cs in self.cot])
+            self._e2e_sets = [(self.params, self.cot), other]
+            self._e2e_free = [None, None]
+            self._e2e_count = 0
+        which = self._e2e_count & 1
+        self._e2e_count += 1
+        self.params, self.cot = self._e2e_sets[which]
         with torch.no_grad():
-            copy.wait_stream(main)                    # the previous step has finished with parameters and images
+            if self._e2e_free[which] is not None:
+                copy.wait_event(self._e2e_free[which])   # the step before last has finished with this set
+            else:
+                copy.wait_stream(main)
             ready = []
             with torch.cuda.stream(copy):
                 for lo, hi in bounds:
@@ -396,6 +414,8 @@ class TrainingStep:
         finally:
             self._pipeline = None
             self._cot_events = None
+        self._e2e_free[which] = torch.cuda.Event()
+        self._e2e_free[which].record(main)
         if not pipelined:
             down.wait_stream(main)
             with torch.cuda.stream(down):

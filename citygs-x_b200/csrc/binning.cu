@@ -1340,9 +1340,10 @@ extern "C" size_t cgx_sort_workspace_bytes(int64_t n)
 namespace cgx {
 int fetch_sort_status_async(int* out_pinned, cudaStream_t st)
 {
-    cudaError_t e = cudaMemcpyFromSymbolAsync(out_pinned, g_sort_status, sizeof(int), 0, cudaMemcpyDeviceToHost, st);
+    void* word = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&word, g_sort_status);
     if (e != cudaSuccess) { set_cuda_error(e); return CGX_ECUDA; }
-    return CGX_OK;
+    return post_words(word, out_pinned, 1, st);
 }
 int fetch_sort_status(int* out)
 {

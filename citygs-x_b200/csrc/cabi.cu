@@ -72,6 +72,31 @@ int fetch_peer_status_async(int* out_pinned, cudaStream_t st);
 int fetch_sort_status_async(int* out_pinned, cudaStream_t st);
 }  // namespace cgx
 
+namespace cgx {
+__global__ void post_words_kernel(const uint32_t* __restrict__ src, volatile uint32_t* dst, int n)
+{
+    for (int i = threadIdx.x; i < n; i += blockDim.x) dst[i] = src[i];
+    __threadfence_system();
+}
+
+int post_words(const void* src_dev, void* dst_host_pinned, int n_words, cudaStream_t st)
+{
+    if (n_words < 0 || (n_words && (!src_dev || !dst_host_pinned))) return CGX_EINVAL;
+    if (((uintptr_t)src_dev | (uintptr_t)dst_host_pinned) & 3u) return CGX_EINVAL;
+    if (n_words == 0) return CGX_OK;
+    void* mapped = nullptr;     // fails for pageable memory: the caller must pass page-locked memory
+    cudaError_t e = cudaHostGetDevicePointer(&mapped, dst_host_pinned, 0);
+    if (e != cudaSuccess || !mapped) { (void)cudaGetLastError(); return CGX_EINVAL; }
+    post_words_kernel<<<1, 128, 0, st>>>((const uint32_t*)src_dev, (volatile uint32_t*)mapped, n_words);
+    return check_launch();
+}
+}  // namespace cgx
+
+extern "C" int cgx_post_words(const void* src_device, void* dst_host_pinned, int n_words32, void* stream)
+{
+    return cgx::post_words(src_device, dst_host_pinned, n_words32, (cudaStream_t)stream);
+}
+
 extern "C" int cgx_device_status_async(int* status_pinned_host4, void* stream)
 {
     if (!status_pinned_host4) return CGX_EINVAL;

@@ -22,6 +22,9 @@ void set_error_text(const char* text);  // free-form text behind cgx_last_cuda_e
 // Checks for a launch error; `launched` = number of kernels the entry point just queued (bookkeeping for
 // cgx_launch_count()).
 int check_launch(int launched = 1);
+// A few 32-bit words from device memory to page-locked host memory by a one-CTA kernel (stores through the host
+// mapping), so that the read-back does not queue behind bulk copies on the device-to-host copy engine.
+int post_words(const void* src_dev, void* dst_host_pinned, int n_words, cudaStream_t st);
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 

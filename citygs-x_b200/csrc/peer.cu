@@ -40,9 +40,10 @@ peer_barrier_kernel(PeerFlags flags, int ws, int rank, uint32_t epoch, unsigned 
 
 int fetch_peer_status_async(int* out_pinned, cudaStream_t st)
 {
-    cudaError_t e = cudaMemcpyFromSymbolAsync(out_pinned, g_peer_status, sizeof(int), 0, cudaMemcpyDeviceToHost, st);
+    void* word = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&word, g_peer_status);
     if (e != cudaSuccess) { set_cuda_error(e); return CGX_ECUDA; }
-    return CGX_OK;
+    return post_words(word, out_pinned, 1, st);
 }
 
 int fetch_peer_status(int* out)

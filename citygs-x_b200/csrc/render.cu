@@ -23,7 +23,8 @@
 #include "cgx_common.cuh"
 
 #ifndef CGX_EXPERIMENT
-#define CGX_EXPERIMENT 0   // timing experiments only: bit 0 skip phase 1, bit 1 skip phase 2, bit 2 skip phase 3
+#define CGX_EXPERIMENT 0   // timing experiments only: bit 0 skip phase 1, bit 1 skip phase 2, bit 2 skip phase 3,
+                           // bit 3 skip the gradient atomics of phase 3
 #endif
 
 namespace cgx {
@@ -578,15 +579,21 @@ tile_stats_kernel(int W, int H, const uint2* __restrict__ ranges, const uint32_t
 }
 
 // ------------------------------------------------------------------------------------------------ backward
+#ifndef CGX_BWD_BATCH
+#define CGX_BWD_BATCH 256
+#endif
+constexpr int BWD_BATCH = CGX_BWD_BATCH;   // records the backward kernels stage per round (per buffer)
+static_assert(BWD_BATCH % 32 == 0 && BWD_BATCH <= RENDER_THREADS && BWD_BATCH <= 256, "one thread stages one record");
+
 struct BwdOut {
     float* ptr[16];   // destination array of gradient term k
     int stride[16];   // floats per Gaussian in that array
 };
 
 struct BwdSmem {
-    Record rec[2][CGX_BLOCK_SIZE];
-    int id[2][CGX_BLOCK_SIZE];
-    uint8_t hits[RENDER_WARPS][CGX_BLOCK_SIZE];
+    Record rec[2][BWD_BATCH];
+    int id[2][BWD_BATCH];
+    uint8_t hits[RENDER_WARPS][BWD_BATCH];
     uint64_t bar[2];
 };
 
@@ -750,7 +757,7 @@ __device__ __forceinline__ void bwd_pixel_init(BwdPixel& px, bool inside, uint32
     const bool inside = pix.x < W && pix.y < H;                                                                      \
     const uint2 range = ranges[block_id];                                                                            \
     const size_t HW = (size_t)H * W;                                                                                 \
-    const int rounds = ((range.y - range.x + CGX_BLOCK_SIZE - 1) / CGX_BLOCK_SIZE);                                  \
+    const int rounds = ((range.y - range.x + BWD_BATCH - 1) / BWD_BATCH);                                  \
     int toDo = range.y - range.x;                                                                                    \
     if (tid == 0) {                                                                                                  \
         mbar_init(&sm.bar[0], 1);                                                                                    \
@@ -761,10 +768,10 @@ __device__ __forceinline__ void bwd_pixel_init(BwdPixel& px, bool inside, uint32
     const float sx0 = (float)(pix_min.x + (warp & 1) * 8), sx1 = sx0 + 7.f;                                          \
     const float sy0 = (float)(pix_min.y + (warp >> 1) * 4), sy1 = sy0 + 3.f;                                         \
     auto issue = [&](int batch, int buf) {                                                                           \
-        const int progress = batch * CGX_BLOCK_SIZE + tid;                                                           \
-        const int n_valid = min(CGX_BLOCK_SIZE, (int)(range.y - range.x) - batch * CGX_BLOCK_SIZE);                  \
+        const int progress = batch * BWD_BATCH + tid;                                                           \
+        const int n_valid = min(BWD_BATCH, (int)(range.y - range.x) - batch * BWD_BATCH);                  \
         if (tid == 0) mbar_expect_tx(&sm.bar[buf], (uint32_t)n_valid * 64u);                                         \
-        if (range.x + progress < range.y) {                                                                          \
+        if (tid < BWD_BATCH && range.x + progress < range.y) {                                                       \
             const int coll_id = point_list[range.y - progress - 1]; /* back to front */                              \
             sm.id[buf][tid] = coll_id;                                                                               \
             bulk_load_64(&sm.rec[buf][tid], records + coll_id, &sm.bar[buf]);                                        \
@@ -826,19 +833,19 @@ render_bwd_kernel(const uint2* __restrict__ ranges, const uint32_t* __restrict__
     const int my_stride = out.stride[my_term];
     const bool my_write = (lane & 1) == 0 && my_ptr != nullptr;
 
-    for (int i = 0; i < rounds; i++, toDo -= CGX_BLOCK_SIZE) {
+    for (int i = 0; i < rounds; i++, toDo -= BWD_BATCH) {
         const int buf = i & 1;
         if (!mbar_wait(&sm.bar[buf], (i >> 1) & 1)) failed = true;
         const int any_failed = __syncthreads_or(failed);
         if (any_failed) break;
         if (i + 1 < rounds) issue(i + 1, buf ^ 1);
 
-        const int nb = min(CGX_BLOCK_SIZE, toDo);
+        const int nb = min(BWD_BATCH, toDo);
         const Record* rec = sm.rec[buf];
         const int* ids = sm.id[buf];
         // batch slot j holds sorted position range.y - 1 - (i*256 + j); its 0-based index in the tile list is
         // total - 1 - (i*256 + j), which is the reference's `contributor` after its decrement.
-        const uint32_t idx_base = total - 1 - (uint32_t)i * CGX_BLOCK_SIZE;
+        const uint32_t idx_base = total - 1 - (uint32_t)i * BWD_BATCH;
         uint8_t* my_hits = sm.hits[warp];
         const int n_hits = CULL ? cull_batch(rec, nb, lane, sx0, sx1, sy0, sy1, my_hits) : nb;
 
@@ -887,10 +894,10 @@ typedef Record BwdRec;
 #endif
 
 struct BwdSmem2 {
-    BwdRec rec[2][CGX_BLOCK_SIZE];
-    int id[2][CGX_BLOCK_SIZE];
+    BwdRec rec[2][BWD_BATCH];
+    int id[2][BWD_BATCH];
     float stage[RENDER_WARPS][BWD_CAP * BWD_RS];
-    uint8_t hits[RENDER_WARPS][CGX_BLOCK_SIZE];
+    uint8_t hits[RENDER_WARPS][BWD_BATCH];
     uint64_t bar[2];
 };
 
@@ -916,7 +923,7 @@ render_bwd2_kernel(const uint2* __restrict__ ranges, const uint32_t* __restrict_
     // a warp none of whose pixels has a contributor has nothing to do in any batch
     const bool warp_idle = __all_sync(0xffffffffu, last_contributor == 0);
 
-    for (int i = 0; i < rounds; i++, toDo -= CGX_BLOCK_SIZE) {
+    for (int i = 0; i < rounds; i++, toDo -= BWD_BATCH) {
         const int buf = i & 1;
         if (!mbar_wait(&sm.bar[buf], (i >> 1) & 1)) failed = true;
         const int any_failed = __syncthreads_or(failed);
@@ -924,12 +931,12 @@ render_bwd2_kernel(const uint2* __restrict__ ranges, const uint32_t* __restrict_
         if (i + 1 < rounds) issue(i + 1, buf ^ 1);
         if (warp_idle) continue;
 
-        const int nb = min(CGX_BLOCK_SIZE, toDo);
+        const int nb = min(BWD_BATCH, toDo);
         const BwdRec* rec = sm.rec[buf];
         const int* ids = sm.id[buf];
         // batch slot j holds sorted position range.y - 1 - (i*256 + j); its 0-based index in the tile list is
         // total - 1 - (i*256 + j), which is the reference's `contributor` after its decrement.
-        const uint32_t idx_base = total - 1 - (uint32_t)i * CGX_BLOCK_SIZE;
+        const uint32_t idx_base = total - 1 - (uint32_t)i * BWD_BATCH;
         uint8_t* my_hits = sm.hits[warp];
         const int n_hits = cull_batch(rec, nb, lane, sx0, sx1, sy0, sy1, my_hits);
 
@@ -1006,7 +1013,8 @@ render_bwd2_kernel(const uint2* __restrict__ ranges, const uint32_t* __restrict_
                         const float* p = stage + rv * BWD_RS + term;
                         float sum = 0.f;
                         for (int r = 0; r < n; r++) sum += p[r * BWD_RS];
-                        if (my_ptr) atomicAdd(my_ptr + (size_t)ids[my_hits[base + v0 + v]] * my_stride, sum);
+                        if (my_ptr && (!(CGX_EXPERIMENT & 8) || sum == 1.2345e-33f))
+                            atomicAdd(my_ptr + (size_t)ids[my_hits[base + v0 + v]] * my_stride, sum);
                     }
                 }
                 __syncwarp();
@@ -1056,9 +1064,10 @@ extern "C" size_t cgx_render_records_bytes(int P) { return (size_t)(P > 0 ? P : 
 namespace cgx {
 int fetch_render_status_async(int* out_pinned, cudaStream_t st)
 {
-    cudaError_t e = cudaMemcpyFromSymbolAsync(out_pinned, g_status, sizeof(int), 0, cudaMemcpyDeviceToHost, st);
+    void* word = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&word, g_status);
     if (e != cudaSuccess) { set_cuda_error(e); return CGX_ECUDA; }
-    return CGX_OK;
+    return post_words(word, out_pinned, 1, st);
 }
 int fetch_render_status(int* out)
 {

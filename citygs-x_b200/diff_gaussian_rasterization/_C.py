@@ -303,7 +303,9 @@ def prefetch_num_rendered(image_height, image_width, means2D, radii, compute_loc
         g = glay.views(geomBuffer)
         _count_scan(l, P, W, H, radii, means2D, None if depths is None else _cuda_f32(depths, "depths"), local, g,
                     _stream())
-        _prefetch_pinned[slot].copy_(g["num_rendered"][0:3], non_blocking=True)      # [1:3] only meaningful with depths
+        # [1:3] only meaningful with depths; a kernel carries the words so they do not wait behind bulk read-backs
+        _lib.check(l.cgx_post_words(_ptr(g["num_rendered"]), C.c_void_p(_prefetch_pinned[slot].data_ptr()), 3,
+                                    _stream()), "cgx_post_words")
         ev = torch.cuda.Event()
         ev.record()
     # the tensors are kept alive with the entry, so their addresses cannot be reused while it exists
@@ -442,7 +444,9 @@ def _density_copy(geomBuffer, records, P):
         _DENSITY.clear()                        # forward passes whose backward never came
     slot = _density_next
     _density_next = (_density_next + 1) % _DENSITY_SLOTS
-    _density_pinned[slot].copy_(records[P * 64: P * 64 + 8 * n].view(torch.int64), non_blocking=True)
+    _lib.check(_lib.lib().cgx_post_words(C.c_void_p(records.data_ptr() + P * 64),
+                                         C.c_void_p(_density_pinned[slot].data_ptr()), 2 * n, _stream()),
+               "cgx_post_words")
     ev = torch.cuda.Event()
     ev.record()
     _DENSITY[geomBuffer.data_ptr()] = (slot, ev)

@@ -108,6 +108,7 @@ SIGNATURES = {
     "cgx_render_dense_threshold": (_i, []),
     "cgx_device_status": (_i, [_vp, _vp]),
     "cgx_device_status_async": (_i, [_vp, _vp]),
+    "cgx_post_words": (_i, [_vp, _vp, _i, _vp]),
     "cgx_set_render_variant": (_i, [_i]),
 }
 

@@ -474,6 +474,13 @@ int cgx_device_status(int* status_host, void* stream);
  * (cgx_device_status clears them). */
 int cgx_device_status_async(int* status_pinned_host4, void* stream);
 
+/* Copies n_words32 32-bit words from device memory to page-locked host memory with a one-CTA kernel that stores
+ * through the host mapping (CGX_EINVAL for pageable memory or misaligned pointers).  For the few words a host waits
+ * for inside a step (the pair count, the exchange's size table, the status words): a copy-engine transfer of them
+ * queues behind bulk device-to-host copies of other streams, a kernel does not.  The reference reads its pair
+ * count with a blocking cudaMemcpy (RAST/cuda_rasterizer/rasterizer_impl.cu:652-653). */
+int cgx_post_words(const void* src_device, void* dst_host_pinned, int n_words32, void* stream);
+
 
 #ifdef __cplusplus
 }

@@ -97,3 +97,25 @@ def test_surviving_rank_gets_an_error_when_its_peer_dies(tmp_path):
     outcome, seconds = (tmp_path / "rank0.txt").read_text().split()
     assert outcome.startswith("raised:"), outcome
     assert float(seconds) < 60.0
+
+
+@pytest.mark.gpu
+def test_small_read_back_by_kernel(cuda_device):
+    """cgx_post_words: device words arrive in page-locked host memory once the stream has been waited for; pageable
+    memory and misaligned pointers are refused without a launch."""
+    from diff_gaussian_rasterization import _lib
+
+    l = _lib.lib()
+    st = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    src = torch.arange(1000, dtype=torch.int32, device=cuda_device) * 7 - 3
+    dst = torch.zeros(1000, dtype=torch.int32).pin_memory()
+    assert l.cgx_post_words(C.c_void_p(src.data_ptr()), C.c_void_p(dst.data_ptr()), 1000, st) == 0
+    torch.cuda.synchronize()
+    assert torch.equal(dst, src.cpu())
+    assert l.cgx_post_words(C.c_void_p(src.data_ptr()), C.c_void_p(dst.data_ptr()), 0, st) == 0
+    pageable = torch.zeros(16, dtype=torch.int32)
+    assert l.cgx_post_words(C.c_void_p(src.data_ptr()), C.c_void_p(pageable.data_ptr()), 16, st) == _lib.CGX_EINVAL
+    assert l.cgx_post_words(C.c_void_p(src.data_ptr() + 2), C.c_void_p(dst.data_ptr()), 4, st) == _lib.CGX_EINVAL
+    torch.cuda.synchronize()
+    status = C.c_int(-1)
+    assert l.cgx_device_status(C.byref(status), st) == 0 and status.value == 0

@@ -686,3 +686,74 @@ def test_chunked_batched_preprocess_is_identical(cuda_device):
             assert torch.equal(x, y)
     for k in ga:
         assert torch.equal(ga[k], gb[k]), k
+
+
+def test_end_to_end_steps_follow_their_host_inputs(cuda_device):
+    """`TrainingStep.run_e2e` (host parameters and upstream-gradient images in, host gradients out; uploads of one call
+    run beside the kernels of the call before it, in alternating device buffers): the gradients that arrive on the
+    host are those of a device-resident step on the same inputs, call after call, also when the host inputs change
+    between calls that are still in flight."""
+    from cgx import runtime as RT
+
+    dev = cuda_device
+    g, cams = util.S.config(2, n_gaussians=30_000, n_cameras=3, res=(320, 240))
+    names = ("means3D", "scales", "rotations", "opacities")
+
+    def resident(host, cot_host):
+        step = RT.TrainingStep(g, cams, dev)
+        with torch.no_grad():
+            for k in names:
+                step.params[k].copy_(host[k])
+            for dst, src in zip(step.cot, cot_host):
+                for d, s in zip(dst, src):
+                    d.copy_(s)
+        step.run()
+        torch.cuda.synchronize()
+        return {k: step.params[k].grad.cpu() for k in names}
+
+    step = RT.TrainingStep(g, cams, dev)
+    want = [resident(step.host, step.cot_host)]
+    got = []
+    for call in range(5):
+        if call in (2, 4):                      # new host inputs between groups of back-to-back calls
+            step.finish_e2e()                   # the pinned buffers are being read until the uploads have run
+            step.host["opacities"].mul_(0.8)
+            step.host["means3D"].add_(0.01)
+            for cs in step.cot_host:
+                cs[0].mul_(-0.5)
+            want.append(resident(step.host, step.cot_host))
+        step.run_e2e(chunks=3)
+        if call in (1, 3, 4):
+            step.finish_e2e()
+            got.append({k: v.clone() for k, v in step.grad_host.items()})
+    assert len(got) == len(want) == 3
+    for a, b in zip(got, want):
+        for k in names:
+            rel = ((a[k] - b[k]).norm() / b[k].norm()).item()
+            assert rel <= 1e-5, (k, rel)
+    assert ((want[0]["opacities"] - want[1]["opacities"]).norm() / want[0]["opacities"].norm()).item() > 1e-2
+
+
+def test_camera_streams_do_not_change_the_step(cuda_device):
+    """The single-GPU step with its cameras on one, two or three CUDA streams: same radii, same parameter gradients
+    (the atomics' order differs, nothing else), repeated so that buffers are reused across steps."""
+    from cgx import runtime as RT
+
+    dev = cuda_device
+    g, cams = util.S.config(2, n_gaussians=40_000, n_cameras=5, res=(320, 240))
+    names = ("means3D", "scales", "rotations", "opacities")
+    results = []
+    for n_streams in (1, 2, 3):
+        step = RT.TrainingStep(g, cams, dev)
+        step.render_streams = n_streams
+        for _ in range(3):
+            step.run()
+        torch.cuda.synchronize()
+        results.append(({k: step.params[k].grad.clone() for k in names}, [r.clone() for r, _ in step.last]))
+    base_grads, base_radii = results[0]
+    for grads, radii in results[1:]:
+        for a, b in zip(radii, base_radii):
+            assert torch.equal(a, b)
+        for k in names:
+            rel = ((grads[k] - base_grads[k]).norm() / base_grads[k].norm()).item()
+            assert rel <= 1e-5, (k, rel)
