@@ -787,6 +787,14 @@ def main():
             # useful FP32 work of the blending: ~10 instructions per (pixel, Gaussian) pair examined up to the
             # pixel's last contributor, ~11 more per pair that contributes; both sums are outputs of the operator
             s["fp32"] += 10.0 * info["n_consider_sum"] + 11.0 * info["n_contrib_sum"]
+            s["pairs"] = s.get("pairs", 0.0) + info["n_consider_sum"]
+            s["contrib"] = s.get("contrib", 0.0) + info["n_contrib_sum"]
+    # the backward blend walks the same pairs as the forward launches of the same pass (one backward per forward):
+    # ~10 instructions per pair examined (the alpha test), ~90 per pair that contributes (recurrences + 16 terms)
+    if "cgx_render_bwd" in stages and stages.get("cgx_render_fwd", {}).get("pairs"):
+        f, b = stages["cgx_render_fwd"], stages["cgx_render_bwd"]
+        if f["launches"] == b["launches"]:
+            b["fp32"] = 10.0 * f["pairs"] + 90.0 * f["contrib"]
     peaks_path = ROOT / "MEASURED_PEAKS.json"
     if peaks_path.exists():
         peak, peak_src = json.loads(peaks_path.read_text())["hbm_gbs"], "measured"
