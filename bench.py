@@ -765,7 +765,8 @@ def main():
     prof, stage_pass = [], None
     if not a.no_stage_events:
         streams_default, step.render_streams = step.render_streams, 1
-        step.run()
+        for _ in range(3):          # the allocator's pools are per stream: let the one-stream pass fill its own
+            step.run()
         _C.PROFILE = []
         ms_stage_pass = timed(step.run, a.steps) / a.steps
         prof, _C.PROFILE = (_C.PROFILE or []), None

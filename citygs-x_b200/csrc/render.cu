@@ -914,10 +914,11 @@ render_bwd2_kernel(const uint2* __restrict__ ranges, const uint32_t* __restrict_
     BwdSmem2& sm = *reinterpret_cast<BwdSmem2*>(smem_raw);
     CGX_BWD_PROLOGUE();
 
-    // phase 3: lane t (and t + 16) owns gradient term t
-    const int half = lane >> 4, term = lane & 15;
-    float* my_ptr = out.ptr[term];
-    const int my_stride = out.stride[term];
+    // phase 3: four visits at a time, eight lanes each; lane t of a quarter owns gradient terms 2t and 2t + 1
+    const int quarter = lane >> 3, term2 = (lane & 7) * 2;
+    float* my_ptr0 = out.ptr[term2];
+    float* my_ptr1 = out.ptr[term2 + 1];
+    const int my_stride0 = out.stride[term2], my_stride1 = out.stride[term2 + 1];
     const uint32_t lanes_below = (1u << lane) - 1u;
     float* stage = sm.stage[warp];
     // a warp none of whose pixels has a contributor has nothing to do in any batch
@@ -1002,19 +1003,25 @@ render_bwd2_kernel(const uint2* __restrict__ ranges, const uint32_t* __restrict_
                 }
                 __syncwarp();
 
-                // ---- phase 3: two visits at a time, one half-warp each, lane = term: sum the visit's rows and add
-                // the total to the Gaussian's gradient with one atomic per term
-                for (int pair0 = 0; pair0 < ((CGX_EXPERIMENT & 4) ? 0 : g); pair0 += 2) {
-                    const int v = pair0 + half;       // v == g (odd group) reads an empty mask
+                // ---- phase 3: four visits at a time, a quarter-warp each, lane = two terms: sum the visit's rows and
+                // add the totals to the Gaussian's gradient with one atomic per term
+                for (int quad0 = 0; quad0 < ((CGX_EXPERIMENT & 4) ? 0 : g); quad0 += 4) {
+                    const int v = quad0 + quarter;    // v >= g (last, partial quad) reads an empty mask
                     const uint32_t mv = __shfl_sync(0xffffffffu, visit_mask, v & 31);
                     const int rv = __shfl_sync(0xffffffffu, first_row, v & 31);
                     const int n = v < g ? __popc(mv) : 0;
                     if (n) {
-                        const float* p = stage + rv * BWD_RS + term;
-                        float sum = 0.f;
-                        for (int r = 0; r < n; r++) sum += p[r * BWD_RS];
-                        if (my_ptr && (!(CGX_EXPERIMENT & 8) || sum == 1.2345e-33f))
-                            atomicAdd(my_ptr + (size_t)ids[my_hits[base + v0 + v]] * my_stride, sum);
+                        const float2* p = reinterpret_cast<const float2*>(stage + rv * BWD_RS + term2);
+                        float2 sum = p[0];
+                        for (int r = 1; r < n; r++) {
+                            const float2 x = p[r * (BWD_RS / 2)];
+                            sum.x += x.x;
+                            sum.y += x.y;
+                        }
+                        const size_t gid = (size_t)ids[my_hits[base + v0 + v]];
+                        const bool go = !(CGX_EXPERIMENT & 8) || sum.x == 1.2345e-33f;
+                        if (my_ptr0 && go) atomicAdd(my_ptr0 + gid * my_stride0, sum.x);
+                        if (my_ptr1 && go) atomicAdd(my_ptr1 + gid * my_stride1, sum.y);
                     }
                 }
                 __syncwarp();
