@@ -510,6 +510,9 @@ ALGO_BYTES = {
     # radius 4 + dL/dmeans2D 8 + dL/dconic_opacity 16 = 28 B in (+20 B), parameter gradients 44 B out
     "cgx_preprocess_fwd_batched": lambda i: i["P"] * (44 + (52 if i["planes"] else 32) * i["B"]),
     "cgx_preprocess_bwd_batched": lambda i: i["P"] * (88 + (48 if i["planes"] else 28) * i["B"]),
+    # row-driven owner backward: per returned row its columns, its index, 44 B of gathered parameters and 56 B of
+    # partial sums; per Gaussian 56 B of sums and 28 B of parameters in, 44 B of gradients out
+    "cgx_preprocess_bwd_rows": lambda i: i["rows"] * (4 * i["ncols"] + 4 + 44 + 56) + i["P"] * (56 + 28 + 44),
     "cgx_bin_count_scan": lambda i: 16 * i["P"],
     "cgx_emit_keys": lambda i: 20 * i["P"] + 12 * i["R"],
     "cgx_sort_pairs": lambda i: i["R"] * (8 + 24 * ((i["bits"] + 7) // 8)),
@@ -581,10 +584,12 @@ def multi_gpu_parity(dev, rank, world):
         dist.all_reduce(full[k])
     radii = torch.zeros(len(cams), n, dtype=torch.int32, device=dev)
     m2g = torch.zeros(len(cams), n, 2, device=dev)
+    have_m2 = False
     for c, (rad, m2) in enumerate(step.last):
         radii[c, rank::world] = rad
         if m2.grad is not None:
             m2g[c, rank::world] = m2.grad
+            have_m2 = True
     dist.all_reduce(radii)
     dist.all_reduce(m2g)
     torch.cuda.synchronize()
@@ -598,10 +603,12 @@ def multi_gpu_parity(dev, rank, world):
             return float((a.double() - b.double()).norm() / b.double().norm().clamp_min(1e-30))
 
         errs = {k: rel(full[k], single.params[k].grad) for k in names}
-        errs["means2D"] = max(rel(m2g[c], single.last[c][1].grad) for c in range(len(cams)))
+        if have_m2:     # owner-side screen-space gradients exist only when the rows are scattered into dense arrays
+            errs["means2D"] = max(rel(m2g[c], single.last[c][1].grad) for c in range(len(cams)))
         out = {"grad_rel_l2_max": max(errs.values()), "grad_rel_l2": errs,
                "radii_equal": all(bool(torch.equal(radii[c], single.last[c][0])) for c in range(len(cams))),
                "split_cameras": split, "transport": transport,
+               "owner_backward": "row-driven, inside the exchange's backward" if not have_m2 else "dense cotangents",
                "case": f"{n} Gaussians, {len(cams)} cameras {res[0]}x{res[1]}, {world} ranks vs 1 GPU"}
         del single
     del step

@@ -181,7 +181,48 @@ class CudaPackBackend:
                  C.c_void_p(table.ctypes.data), self._p(send_index), self._st())
         del keep
 
-    def pack_grad_rows_to(self, seg_ptrs, seg_counts, ncols, grads):
+    def prepare_pack_p2p(self, cameras, order):
+        """Everything of `pack_p2p_batched` that does not depend on the size table: `cameras` as there, without
+        dst_table / row_offsets; `order` = the order in which the launch works through the cameras.  Returns the
+        object `pack_p2p_prepared` takes."""
+        n = len(cameras)
+        table = np.zeros((n, 19), dtype=np.uint64)          # rows = struct cgx_exchange_camera
+        keep, n_dst = [], []
+        for row, k in enumerate(order):
+            c = cameras[k]
+            params = [t.contiguous() for t in c["params"]]
+            if len(params) == 6:
+                means2D, rgb, conic_opacity, radii, depths, all_map = params
+                m3 = sc = rot = 0
+                am = all_map.data_ptr()
+            else:
+                means2D, rgb, conic_opacity, radii, depths, means3D, scales, rotation = params
+                m3, sc, rot, am = means3D.data_ptr(), scales.data_ptr(), rotation.data_ptr(), 0
+            ws = c["bounds"].numel() - 1
+            keep.append(params)
+            n_dst.append(ws)
+            table[row] = (means2D.shape[0], c["H"], c["W"], ws, means2D.data_ptr(), rgb.data_ptr(),
+                          conic_opacity.data_ptr(), m3, sc, rot, radii.data_ptr(), depths.data_ptr(),
+                          c["bounds"].data_ptr(), int(bool(c["avoid"])), 0, 0,
+                          c["workspace"].data_ptr(), c["workspace"].numel(), am)
+        entry0 = np.concatenate([[0], np.cumsum(n_dst)]).astype(np.int64)
+        return dict(table=table, keep=keep, entry0=entry0, n=n)
+
+    def pack_p2p_prepared(self, prep, dst_rows, row_offsets, send_index):
+        """The launch of `pack_p2p_batched` from a prepared table: dst_rows (entries, 10) uint64 and row_offsets
+        (entries,) int64 hold the cameras' destination rows one camera after the other, in the prepared order."""
+        table, entry0 = prep["table"], prep["entry0"]
+        dst_rows = np.ascontiguousarray(dst_rows, dtype=np.uint64)
+        row_offsets = np.ascontiguousarray(row_offsets, dtype=np.int64)
+        assert dst_rows.shape == (int(entry0[-1]), 10) and row_offsets.shape == (int(entry0[-1]),)
+        table[:, 14] = (dst_rows.ctypes.data + entry0[:-1] * 80).astype(np.uint64)
+        table[:, 15] = (row_offsets.ctypes.data + entry0[:-1] * 8).astype(np.uint64)
+        from diff_gaussian_rasterization import _C
+
+        _C._call("cgx_local2j_pack_p2p_batched", self.l.cgx_local2j_pack_p2p_batched, prep["n"],
+                 C.c_void_p(table.ctypes.data), self._p(send_index), self._st())
+
+    def pack_grad_rows_to(self, seg_ptrs, seg_counts, ncols, grads, first_segment=0):
         n = len(seg_ptrs)
         if n == 0 or sum(seg_counts) == 0:
             return
@@ -191,7 +232,7 @@ class CudaPackBackend:
         from diff_gaussian_rasterization import _C
 
         _C._call("cgx_pack_grad_rows_to", self.l.cgx_pack_grad_rows_to, n, ptrs, counts, ncols,
-                 *[self._p(t) for t in g], self._st())
+                 int(first_segment) % n, *[self._p(t) for t in g], self._st())
 
     def unpack_grad_add_cols(self, grad_rows, send_index, ranges, ncols, grads):
         ranges = [(a, b) for a, b in ranges if b > a]
@@ -503,20 +544,34 @@ def _arena_for(group, device):
     return _arenas[key]
 
 
-class _GaussianExchangeP2P(torch.autograd.Function):
-    """Same contract as _GaussianExchange, transport by direct stores into peer memory."""
+def _camera_order(strategies, me, ws):
+    """The order in which a rank's pack launch works through the cameras: first those the rank after it renders,
+    its own last, so that at any time the ranks store into different peers (all of them sending camera 0's rows
+    first would queue on the links of the rank that renders camera 0)."""
+    return sorted(range(len(strategies)), key=lambda k: ((strategies[k].gpu_ids[0] - me - 1) % ws, k))
 
-    @staticmethod
-    def forward(ctx, plan, *flat):
-        be, arena = plan["backend"], plan["arena"]
-        me = plan["me"]
-        bsz = len(plan["strategies"])
-        planes = plan["planes"]
-        peer_base = np.array([int(p) for p in arena.recv_hdl.buffer_ptrs], dtype=np.int64)
-        # address of field f of camera k in rank j's arena, and the first row this rank writes there
-        field_ptr = peer_base[:, None, None] + plan["cam_base"][:, :, None] + plan["field_off"]      # (ws, bsz, F)
-        # (the barrier "every rank is done with the previous contents of the arenas" was queued by the caller,
-        # behind the size read-back)
+
+def _p2p_forward(plan):
+    """Pack this rank's rows into the peers' receive arenas, wait until every rank's rows have landed, and return
+    (per-camera views of this rank's arena, the non-differentiable ones among them)."""
+    be, arena = plan["backend"], plan["arena"]
+    me = plan["me"]
+    bsz = len(plan["strategies"])
+    planes = plan["planes"]
+    peer_base = np.array([int(p) for p in arena.recv_hdl.buffer_ptrs], dtype=np.int64)
+    # address of field f of camera k in rank j's arena, and the first row this rank writes there
+    field_ptr = peer_base[:, None, None] + plan["cam_base"][:, :, None] + plan["field_off"]      # (ws, bsz, F)
+    # (the barrier "every rank is done with the previous contents of the arenas" was queued by the caller,
+    # behind the size read-back)
+    prep = plan.get("prepared")
+    if prep is not None:
+        # destination rows of every (camera, rendering rank) pair at once, in the prepared camera order
+        cam, dst = prep["entry_cam"], prep["entry_dst"]
+        rows = np.zeros((cam.size, 10), dtype=np.uint64)      # rows = struct cgx_peer_camera_dst
+        rows[:, [0, 1, 2, 9, 6, 7] if planes else list(range(8))] = field_ptr[dst, cam, :]
+        rows[:, 8] = plan["first_row"][dst, cam]
+        be.pack_p2p_prepared(prep, rows, plan["send_off"][dst, cam], plan["send_index"])
+    else:
         cameras = []
         for k in range(bsz):
             ids = plan["strategies"][k].gpu_ids
@@ -529,36 +584,84 @@ class _GaussianExchangeP2P(torch.autograd.Function):
             cameras.append(dict(params=plan["params"][k], bounds=plan["bounds"][k], H=plan["hw"][k][0],
                                 W=plan["hw"][k][1], avoid=plan["avoid"][k], dst_table=table,
                                 row_offsets=plan["send_off"][ids, k], workspace=plan["scratch"][k]))
+        cameras = [cameras[k] for k in _camera_order(plan["strategies"], me, plan["ws"])]
         if hasattr(be, "pack_p2p_batched"):
             be.pack_p2p_batched(cameras, plan["send_index"])
         else:
             for c in cameras:
                 be.pack_p2p(c["params"], c["bounds"], c["H"], c["W"], c["avoid"], c["dst_table"], c["row_offsets"],
                             plan["send_index"], c["workspace"])
-        arena.barrier(2)                      # every rank's rows have landed
-        outs, nondiff = [], []
-        f32 = arena.recv.view(torch.float32)
-        i32 = arena.recv.view(torch.int32)
-        words = ((plan["cam_base"][me][:, None] + plan["field_off"][me]) // 4).tolist()   # offsets in 4-byte words
-        n_mine = plan["n_recv"][me].tolist()
-        for k in range(bsz):
-            n, w = n_mine[k], words[k]
-            m2 = f32[w[0]: w[0] + 2 * n].view(n, 2)
-            rgb = f32[w[1]: w[1] + 3 * n].view(n, 3)
-            co = f32[w[2]: w[2] + 4 * n].view(n, 4)
-            if planes:
-                am = f32[w[3]: w[3] + 5 * n].view(n, 5)
-                rad = i32[w[4]: w[4] + n]
-                dep = f32[w[5]: w[5] + n]
-                outs += [m2, rgb, co, rad, dep, am]
-            else:
-                m3 = f32[w[3]: w[3] + 3 * n].view(n, 3)
-                sc = f32[w[4]: w[4] + 3 * n].view(n, 3)
-                rot = f32[w[5]: w[5] + 4 * n].view(n, 4)
-                rad = i32[w[6]: w[6] + n]
-                dep = f32[w[7]: w[7] + n]
-                outs += [m2, rgb, co, rad, dep, m3, sc, rot]
-            nondiff += [rad, dep]
+    arena.barrier(2)                      # every rank's rows have landed
+    outs, nondiff = [], []
+    f32 = arena.recv.view(torch.float32)
+    i32 = arena.recv.view(torch.int32)
+    words = ((plan["cam_base"][me][:, None] + plan["field_off"][me]) // 4).tolist()   # offsets in 4-byte words
+    n_mine = plan["n_recv"][me].tolist()
+    for k in range(bsz):
+        n, w = n_mine[k], words[k]
+        m2 = f32[w[0]: w[0] + 2 * n].view(n, 2)
+        rgb = f32[w[1]: w[1] + 3 * n].view(n, 3)
+        co = f32[w[2]: w[2] + 4 * n].view(n, 4)
+        if planes:
+            am = f32[w[3]: w[3] + 5 * n].view(n, 5)
+            rad = i32[w[4]: w[4] + n]
+            dep = f32[w[5]: w[5] + n]
+            outs += [m2, rgb, co, rad, dep, am]
+        else:
+            m3 = f32[w[3]: w[3] + 3 * n].view(n, 3)
+            sc = f32[w[4]: w[4] + 3 * n].view(n, 3)
+            rot = f32[w[5]: w[5] + 4 * n].view(n, 4)
+            rad = i32[w[6]: w[6] + n]
+            dep = f32[w[7]: w[7] + n]
+            outs += [m2, rgb, co, rad, dep, m3, sc, rot]
+        nondiff += [rad, dep]
+    return outs, nondiff
+
+
+def _p2p_send_gradients(plan, gouts):
+    """Reverse leg: store the cotangent rows of what this rank received into their owners' staging buffers and wait
+    until every rank's rows have landed.  Returns the rows this rank owns, (n_send, grad_cols), in send order."""
+    be, arena = plan["backend"], plan["arena"]
+    me, S = plan["me"], plan["S"]
+    dev = arena.dev
+    bsz = len(plan["strategies"])
+    ncols = plan["grad_cols"]
+    planes = plan["planes"]
+    n_out = 6 if planes else 8
+    if arena.last_grad_step != plan["arena_step"] or arena.step - plan["arena_step"] > 1:
+        raise RuntimeError(
+            "cgx.exchange: the backward pass of a peer-to-peer exchange ran too late: another exchange with a "
+            "graph, or two exchanges without one, have used the same group since its forward pass, and the "
+            "tensors it returned (views of a receive arena) or its gradient staging buffer were overwritten.  "
+            "Keep one differentiable exchange in flight per group (at most one forward-only exchange may come "
+            "between its forward and backward passes), or use transport='collective'")
+    owner_base = np.array([int(p) for p in arena.grad_hdl.buffer_ptrs], dtype=np.int64)
+    # segment (source i -> me, camera k) sits at row grad_row[i, k] of rank i's send order
+    seg_ptr = owner_base[:, None] + plan["grad_row"] * (ncols * 4)                                # (ws, bsz)
+    for k in range(bsz):
+        counts = S[:, me, k]
+        if not counts.any():
+            continue                      # camera not rendered here: no gradient rows to return
+        g = gouts[n_out * k: n_out * k + n_out]
+        n = int(plan["n_recv"][me, k])
+        if planes:                        # the (n,5) plane-descriptor cotangent rides in the means3D slot
+            cot = _dense_cotangents((g[0], g[1], g[2], None, None, None, None, None), n, dev)[:3] + \
+                (g[5] if g[5] is not None else torch.zeros(n, 5, device=dev), None, None)
+        else:
+            cot = _dense_cotangents(g, n, dev)
+        # every rank starts with the rows of the rank after it: the ranks' stores go to different peers at any time
+        be.pack_grad_rows_to(seg_ptr[:, k].tolist(), counts.tolist(), ncols, cot, first_segment=me + 1)
+    arena.barrier(3)                      # every rank's gradient rows have landed in their owners' buffers
+    n_send = plan["n_send"]
+    return arena.grad[: n_send * ncols * 4].view(torch.float32).view(n_send, ncols)
+
+
+class _GaussianExchangeP2P(torch.autograd.Function):
+    """Same contract as _GaussianExchange, transport by direct stores into peer memory."""
+
+    @staticmethod
+    def forward(ctx, plan, *flat):
+        outs, nondiff = _p2p_forward(plan)
         ctx.plan = plan
         ctx.shapes = [t.shape for t in flat]
         ctx.mark_non_differentiable(*nondiff)
@@ -567,38 +670,9 @@ class _GaussianExchangeP2P(torch.autograd.Function):
     @staticmethod
     def backward(ctx, *gouts):
         plan = ctx.plan
-        be, arena = plan["backend"], plan["arena"]
-        me, S = plan["me"], plan["S"]
-        dev = arena.dev
-        bsz = len(plan["strategies"])
-        ncols = plan["grad_cols"]
-        planes = plan["planes"]
-        n_out, n_in = (6, 4) if planes else (8, 6)
-        if arena.last_grad_step != plan["arena_step"] or arena.step - plan["arena_step"] > 1:
-            raise RuntimeError(
-                "cgx.exchange: the backward pass of a peer-to-peer exchange ran too late: another exchange with a "
-                "graph, or two exchanges without one, have used the same group since its forward pass, and the "
-                "tensors it returned (views of a receive arena) or its gradient staging buffer were overwritten.  "
-                "Keep one differentiable exchange in flight per group (at most one forward-only exchange may come "
-                "between its forward and backward passes), or use transport='collective'")
-        owner_base = np.array([int(p) for p in arena.grad_hdl.buffer_ptrs], dtype=np.int64)
-        # segment (source i -> me, camera k) sits at row grad_row[i, k] of rank i's send order
-        seg_ptr = owner_base[:, None] + plan["grad_row"] * (ncols * 4)                                # (ws, bsz)
-        for k in range(bsz):
-            counts = S[:, me, k]
-            if not counts.any():
-                continue                      # camera not rendered here: no gradient rows to return
-            g = gouts[n_out * k: n_out * k + n_out]
-            n = int(plan["n_recv"][me, k])
-            if planes:                        # the (n,5) plane-descriptor cotangent rides in the means3D slot
-                cot = _dense_cotangents((g[0], g[1], g[2], None, None, None, None, None), n, dev)[:3] + \
-                    (g[5] if g[5] is not None else torch.zeros(n, 5, device=dev), None, None)
-            else:
-                cot = _dense_cotangents(g, n, dev)
-            be.pack_grad_rows_to(seg_ptr[:, k].tolist(), counts.tolist(), ncols, cot)
-        arena.barrier(3)                      # every rank's gradient rows have landed in their owners' buffers
-        n_send = plan["n_send"]
-        grad_send = arena.grad[: n_send * ncols * 4].view(torch.float32).view(n_send, ncols)
+        be, dev, planes, ncols = plan["backend"], plan["arena"].dev, plan["planes"], plan["grad_cols"]
+        n_in = 4 if planes else 6
+        grad_send = _p2p_send_gradients(plan, gouts)
         grads = []
         for k, per_dst in enumerate(plan["send_ranges"]):
             need = ctx.needs_input_grad[1 + n_in * k: 1 + n_in * k + n_in]
@@ -611,6 +685,66 @@ class _GaussianExchangeP2P(torch.autograd.Function):
                                     gk + [None, None] if planes else gk)
             grads += [g if nd else None for g, nd in zip(gk, need)]
         return (None,) + tuple(grads)
+
+
+class _RowSegment(C.Structure):
+    _fields_ = [("start", C.c_longlong), ("count", C.c_longlong), ("camera", C.c_int), ("reserved", C.c_int)]
+
+
+class _OwnerExchangeP2P(torch.autograd.Function):
+    """The peer-to-peer exchange of plane-descriptor records with the owner's preprocess backward folded into its
+    backward pass: inputs are the four parameter tensors the camera-batched preprocess read (its outputs enter the
+    exchange detached), outputs are the received per-camera tensors.  In the backward the gradient rows that come
+    back are consumed where they land (`cgx_preprocess_bwd_rows`): no dense per-camera cotangent arrays, no
+    scatter, and only pairs that were visible somewhere do any work."""
+
+    @staticmethod
+    def forward(ctx, plan, owner, means3D, scales, rotations, opacities):
+        outs, nondiff = _p2p_forward(plan)
+        ctx.plan, ctx.owner = plan, owner
+        ctx.save_for_backward(means3D, scales, rotations)
+        ctx.op_shape = opacities.shape
+        ctx.mark_non_differentiable(*nondiff)
+        return tuple(outs)
+
+    @staticmethod
+    def backward(ctx, *gouts):
+        from diff_gaussian_rasterization import _C, _lib
+
+        from .batched import _cams, _ptrs
+
+        plan, owner = ctx.plan, ctx.owner
+        means3D, scales, rotations = ctx.saved_tensors
+        means3D, scales, rotations = means3D.contiguous(), scales.contiguous(), rotations.contiguous()
+        rows = _p2p_send_gradients(plan, gouts)
+        settings = owner["settings"]
+        P, dev, ncols = means3D.shape[0], means3D.device, plan["grad_cols"]
+        segs = [(a, b - a, k) for k, per_dst in enumerate(plan["send_ranges"]) for a, b in per_dst if b > a]
+        arr = (_RowSegment * max(len(segs), 1))()
+        for e, (a, n, k) in zip(arr, segs):
+            e.start, e.count, e.camera = a, n, k
+        d_means = torch.empty(P, 3, device=dev)
+        d_scales = torch.empty(P, 3, device=dev)
+        d_rot = torch.empty(P, 4, device=dev)
+        d_op = torch.empty(ctx.op_shape, device=dev)
+        if P:
+            l = _lib.lib()
+            cams, keep = _cams(settings)
+            campos = [rs.campos.contiguous() for rs in settings]
+            work = torch.empty(l.cgx_preprocess_bwd_rows_workspace_bytes(P), dtype=torch.uint8, device=dev)
+            with torch.cuda.device(dev):
+                _C._call("cgx_preprocess_bwd_rows", l.cgx_preprocess_bwd_rows, P, len(segs), arr, ncols,
+                         C.c_void_p(rows.data_ptr()), C.c_void_p(plan["send_index"].data_ptr()),
+                         C.c_void_p(means3D.data_ptr()), C.c_void_p(scales.data_ptr()),
+                         float(settings[0].scale_modifier), C.c_void_p(rotations.data_ptr()), len(settings), cams,
+                         _ptrs(campos), C.c_void_p(work.data_ptr()), work.numel(), C.c_void_p(d_means.data_ptr()),
+                         C.c_void_p(d_scales.data_ptr()), C.c_void_p(d_rot.data_ptr()), C.c_void_p(d_op.data_ptr()),
+                         _lib.current_stream_ptr(), info=dict(P=P, rows=rows.shape[0], ncols=ncols))
+            pipeline = owner.get("pipeline")
+            if pipeline is not None and pipeline.done is not None:
+                for i, (lo, hi) in enumerate(pipeline.bounds):
+                    pipeline.done(i, lo, hi, (d_means, d_scales, d_rot, d_op))
+        return None, None, d_means, d_scales, d_rot, d_op
 
 
 def _pick_transport(transport, group, dev, backend):
@@ -627,7 +761,7 @@ def _pick_transport(transport, group, dev, backend):
 
 def all_to_all_communication_final(batched_rasterizers, batched_screenspace_params, batched_cuda_args,
                                    batched_strategies, group=None, backend=None, transport=None, piggyback=None,
-                                   planes=False):
+                                   planes=False, owner=None):
     """See module docstring.  ``batched_screenspace_params[k]`` =
     (means2D, rgb, conic_opacity, radii, depths, means3D, scales, rotation) of camera k on this rank.
 
@@ -644,7 +778,13 @@ def all_to_all_communication_final(batched_rasterizers, batched_screenspace_para
     conic_opacity, radii, depths, all_map) with the camera's plane descriptors already computed by the owner
     (`cgx.batched.preprocess_gaussians_batched(planes=True)`).  The descriptors travel instead of the 3-D
     parameters they would be rebuilt from on the receiver (16 floats per row instead of 21, 14 gradient columns
-    back instead of 19); the sixth returned list then holds ``all_map`` per camera and the last two are None."""
+    back instead of 19); the sixth returned list then holds ``all_map`` per camera and the last two are None.
+
+    ``owner`` (with ``planes=True``): ``dict(params=(means3D, scales, rotations, opacities), settings=[raster settings
+    of every camera], pipeline=None)`` of the camera-batched preprocess call that produced the (then detached)
+    screen-space tensors.  The exchange becomes the one autograd node between the parameters and the received
+    tensors, and its backward pass runs the owner's preprocess backward straight over the gradient rows that come
+    back (`cgx_preprocess_bwd_rows`).  The owner-side screen-space tensors get no ``.grad`` in this form."""
     backend = backend or default_backend()
     ws, me = _world(group)
     bsz = len(batched_rasterizers)
@@ -686,20 +826,8 @@ def all_to_all_communication_final(batched_rasterizers, batched_screenspace_para
     arena = _arena_for(group, dev) if transport == "p2p" else None
     # the barrier "every rank is done with the previous contents of the arenas" does not depend on the sizes: it is
     # queued behind the size read-back and runs while the host lays out the exchange
-    gathered, extra = _gather_table(table_dev, bsz * ws, piggyback, group, ws,
-                                    overlap=arena.begin_step if arena is not None else None)
-    S = np.ascontiguousarray(gathered.reshape(ws, bsz, ws).transpose(0, 2, 1))     # [src][dst][cam]
-    sizes_list = S.tolist()
-    my = S[me]                                                       # [dst][cam]
-
-    # ---- 2. send order: destination major, camera minor
-    send_splits = my.sum(1).tolist()
-    recv_splits = S[:, me, :].sum(1).tolist()
-    n_send = int(my.sum())
-    ends = np.cumsum(my.reshape(-1))
-    send_off = (ends - my.reshape(-1)).reshape(ws, bsz)              # first send row of (destination, camera)
-    send_ranges = [[(int(send_off[j, k]), int(send_off[j, k] + my[j, k])) for j in batched_strategies[k].gpu_ids]
-                   for k in range(bsz)]
+    # While the host waits for the size table it prepares everything of the pack launch that does not depend on it
+    # (and the flat argument lists): what is left between the table's arrival and the launch is a few array operations.
     flat = []
     for k in range(bsz):
         if planes:
@@ -708,14 +836,46 @@ def all_to_all_communication_final(batched_rasterizers, batched_screenspace_para
         else:
             m2, rgb, co, radii, depths, m3, sc, rot = batched_screenspace_params[k]
             flat += [m2, rgb, co, m3, sc, rot]
-    sent_counts = my.tolist()
-    self_rows = int(my[me].sum())
-    stats = {"rows_sent": n_send, "rows_received": sum(recv_splits), "rows_to_self": self_rows,
-             "bytes_sent_fwd": (n_send - self_rows) * REC * 4, "bytes_sent_bwd": (n_send - self_rows) * REC_DIFF * 4,
-             "piggyback": extra}
+    early = {}
 
-    stats["transport"] = transport
+    def while_waiting():
+        arena.begin_step()
+        early["params"] = [tuple(t.detach() for t in p) for p in batched_screenspace_params]
+        early["hw"] = [(r.raster_settings.image_height, r.raster_settings.image_width) for r in batched_rasterizers]
+        early["avoid"] = [a["avoid_pixel_all2all"] for a in batched_cuda_args]
+        if hasattr(backend, "prepare_pack_p2p"):
+            order = _camera_order(batched_strategies, me, ws)
+            cams = [dict(params=early["params"][k], bounds=bounds[k], H=early["hw"][k][0], W=early["hw"][k][1],
+                         avoid=early["avoid"][k], workspace=scratch[k]) for k in range(bsz)]
+            prep = backend.prepare_pack_p2p(cams, order)
+            ids = [batched_strategies[k].gpu_ids for k in order]
+            prep["entry_cam"] = np.repeat(np.asarray(order, dtype=np.int64), [len(i) for i in ids])
+            prep["entry_dst"] = np.concatenate([np.asarray(i, dtype=np.int64) for i in ids])
+            early["prepared"] = prep
+
+    gathered, extra = _gather_table(table_dev, bsz * ws, piggyback, group, ws,
+                                    overlap=while_waiting if arena is not None else None)
+    S = np.ascontiguousarray(gathered.reshape(ws, bsz, ws).transpose(0, 2, 1))     # [src][dst][cam]
+    my = S[me]                                                       # [dst][cam]
+
+    # ---- 2. send order: destination major, camera minor
+    send_splits = my.sum(1).tolist()
+    recv_splits = S[:, me, :].sum(1).tolist()
+    n_send = int(my.sum())
+    ends = np.cumsum(my.reshape(-1))
+    send_off = (ends - my.reshape(-1)).reshape(ws, bsz)              # first send row of (destination, camera)
     send_index = torch.empty(n_send, dtype=torch.int32, device=dev)
+
+    def bookkeeping():
+        """What the caller and the backward pass want to know; nothing the forward launches need."""
+        send_ranges = [[(int(send_off[j, k]), int(send_off[j, k] + my[j, k])) for j in batched_strategies[k].gpu_ids]
+                       for k in range(bsz)]
+        self_rows = int(my[me].sum())
+        stats = {"rows_sent": n_send, "rows_received": sum(recv_splits), "rows_to_self": self_rows,
+                 "bytes_sent_fwd": (n_send - self_rows) * REC * 4, "bytes_sent_bwd": (n_send - self_rows) * REC_DIFF * 4,
+                 "piggyback": extra, "transport": transport}
+        return send_ranges, S.tolist(), my.tolist(), stats
+
     if transport == "p2p":
         lay = p2p_layout(S, me, _CAM_FIELDS_PLANES if planes else _CAM_FIELDS)
         n_recv, field_off, grad_row = lay["n_recv"], lay["field_off"], lay["grad_row"]
@@ -723,21 +883,30 @@ def all_to_all_communication_final(batched_rasterizers, batched_screenspace_para
         # gradient rows carry 19 columns only when some rank needs gradients for the 3-D parameters through the
         # exchange; every rank runs the same model code, so this is the same decision everywhere
         if planes:
-            grad_cols = 14 if any(flat[4 * k + 3].requires_grad for k in range(bsz)) else 9
-            stats["bytes_sent_fwd"] = (n_send - self_rows) * 16 * 4
+            grad_cols = 14 if owner is not None or any(flat[4 * k + 3].requires_grad for k in range(bsz)) else 9
         else:
             grad_cols = REC_DIFF if any(flat[6 * k + c].requires_grad for k in range(bsz) for c in (3, 4, 5)) else 9
-        stats["bytes_sent_bwd"] = (n_send - self_rows) * grad_cols * 4
+        # send_ranges (read by the backward pass only) joins the plan after the launches have been queued
         plan = dict(backend=backend, arena=arena, arena_step=arena.step, me=me, ws=ws, S=S, strategies=batched_strategies,
                     grad_cols=grad_cols, planes=planes, n_recv=n_recv, cam_base=lay["cam_base"], field_off=field_off,
                     first_row=lay["first_row"], grad_row=grad_row, bounds=bounds, scratch=scratch,
-                    send_index=send_index, send_off=send_off, send_ranges=send_ranges, n_send=n_send,
-                    params=[tuple(t.detach() for t in p) for p in batched_screenspace_params],
-                    hw=[(r.raster_settings.image_height, r.raster_settings.image_width) for r in batched_rasterizers],
-                    avoid=[a["avoid_pixel_all2all"] for a in batched_cuda_args])
-        if torch.is_grad_enabled() and any(t.requires_grad for t in flat):
-            arena.last_grad_step = arena.step
-        outs = _GaussianExchangeP2P.apply(plan, *flat)
+                    send_index=send_index, send_off=send_off, n_send=n_send, params=early["params"], hw=early["hw"],
+                    avoid=early["avoid"], prepared=early.get("prepared"))
+        if owner is not None:
+            if not planes:
+                raise RuntimeError("owner= needs the plane-descriptor record form (planes=True)")
+            if torch.is_grad_enabled() and any(t.requires_grad for t in owner["params"]):
+                arena.last_grad_step = arena.step
+            outs = _OwnerExchangeP2P.apply(plan, owner, *owner["params"])
+        else:
+            if torch.is_grad_enabled() and any(t.requires_grad for t in flat):
+                arena.last_grad_step = arena.step
+            outs = _GaussianExchangeP2P.apply(plan, *flat)
+        plan["send_ranges"], sizes_list, sent_counts, stats = bookkeeping()
+        self_rows = stats["rows_to_self"]
+        if planes:
+            stats["bytes_sent_fwd"] = (n_send - self_rows) * 16 * 4
+        stats["bytes_sent_bwd"] = (n_send - self_rows) * grad_cols * 4
         if planes:
             out = [[outs[6 * k + c] for k in range(bsz)] for c in range(6)] + [None, None]
         else:
@@ -745,6 +914,7 @@ def all_to_all_communication_final(batched_rasterizers, batched_screenspace_para
         return (*out, sizes_list, sent_counts, send_index, stats)
 
     # ---- 2b. collective transport: send buffer packed by one kernel per camera
+    send_ranges, sizes_list, sent_counts, stats = bookkeeping()
     send = torch.empty(n_send, REC_DIFF, dtype=torch.float32, device=dev)
     send_aux = torch.empty(n_send, REC - REC_DIFF, dtype=torch.float32, device=dev)
     for k in range(bsz):

@@ -235,6 +235,8 @@ class TrainingStep:
         return self.params
 
     # ------------------------------------------------------------------ multi-GPU step
+    owner_backward = True   # fold the owner's preprocess backward into the exchange's backward when nothing reads
+                            # the owner-side screen-space gradients
     def forward_only(self):
         """The distributed forward pass without a graph (an evaluation render, or the reference's second exchange
         for the nearest-view cameras, gaussian_renderer/__init__.py:1026,1439-1458): preprocess, exchange, render of
@@ -257,8 +259,17 @@ class TrainingStep:
         # (differentiably) and the descriptors are rebuilt on the receiver, as the reference does.
         fused = self.plane_grads and self.batched and \
             exchange._pick_transport(self.transport, None, self.dev, exchange.default_backend()) == "p2p"
+        # With the fused record form and no consumer of the owner-side screen-space gradients (the densifier reads
+        # means2D.grad), the preprocess runs outside the graph and the exchange's backward does its backward too.
+        owner = None
+        if fused and backward and torch.is_grad_enabled() and self.owner_backward and self.densify is None:
+            with torch.no_grad():
+                pre = self._preprocess_all(args[0], planes=True)
+            owner = dict(params=(p["means3D"], p["scales"], p["rotations"], p["opacities"]), settings=self.settings,
+                         pipeline=self._pipeline)
+        else:
+            pre = self._preprocess_all(args[0], planes=fused)
         screen, keep = [], []
-        pre = self._preprocess_all(args[0], planes=fused)
         for k in range(len(self.cams)):
             means2D, _, conic_opacity, radii, depths = pre[k][:5]
             if means2D.requires_grad:
@@ -276,7 +287,7 @@ class TrainingStep:
             times = WD.local_running_times(pending[0], pending[1], ctx=self.ctx)
         (m2, rgb, co, rad, dep, m3, sc, rot, sizes, sent, send_index, stats) = \
             exchange.all_to_all_communication_final(rasts, screen, args, strategies, transport=self.transport,
-                                                    piggyback=times, planes=fused)
+                                                    piggyback=times, planes=fused, owner=owner)
         if times is not None:
             WD.finish_strategy_final(self.cams, self.history, pending[0], pending[1], ctx=self.ctx,
                                      gathered_times=stats["piggyback"])

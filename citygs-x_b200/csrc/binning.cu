@@ -1155,6 +1155,8 @@ struct GradSegments {
     int n;
     float* rows[MAX_WS];           // where segment r's 19-float gradient rows go (possibly another GPU's memory)
     long long prefix[MAX_WS + 1];  // rows of this camera in segments before r
+    long long first_row;           // the grid starts at this row and wraps around: ranks that start at different
+                                   // segments do not all store into the same peer at the same time
 };
 
 // NCOLS = 19: all differentiable columns; NCOLS = 9: only means2D | rgb | conic_opacity (the 3-D parameters carry
@@ -1169,8 +1171,10 @@ pack_grad_rows_to_kernel(GradSegments sg, const float* __restrict__ d_means2D, c
     const long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     const long long n = sg.prefix[sg.n];
     if (e >= n * NCOLS) return;
-    const long long lrow = e / NCOLS;
-    const int c = (int)(e - lrow * NCOLS);
+    const long long lrow0 = e / NCOLS;
+    const int c = (int)(e - lrow0 * NCOLS);
+    long long lrow = lrow0 + sg.first_row;
+    if (lrow >= n) lrow -= n;
     int r = 0;
     while (r + 1 < sg.n && lrow >= sg.prefix[r + 1]) r++;
     float v = 0.f;
@@ -1778,11 +1782,12 @@ extern "C" int cgx_local2j_pack_p2p_batched(int n_cameras, const cgx_exchange_ca
 }
 
 extern "C" int cgx_pack_grad_rows_to(int n_segments, float* const* seg_rows, const int64_t* seg_count, int ncols,
-                                     const float* d_means2D, const float* d_rgb, const float* d_conic_opacity,
-                                     const float* d_means3D, const float* d_scales, const float* d_rotations,
-                                     void* stream)
+                                     int first_segment, const float* d_means2D, const float* d_rgb,
+                                     const float* d_conic_opacity, const float* d_means3D, const float* d_scales,
+                                     const float* d_rotations, void* stream)
 {
     if (n_segments < 0 || n_segments > MAX_WS || (ncols != 9 && ncols != 14 && ncols != 19)) return CGX_EINVAL;
+    if (first_segment < 0 || (n_segments > 0 && first_segment >= n_segments)) return CGX_EINVAL;
     if (n_segments == 0) return CGX_OK;
     if (!seg_rows || !seg_count) return CGX_EINVAL;
     GradSegments sg;
@@ -1795,6 +1800,7 @@ extern "C" int cgx_pack_grad_rows_to(int n_segments, float* const* seg_rows, con
     }
     const long long n = sg.prefix[n_segments];
     if (n == 0) return CGX_OK;
+    sg.first_row = sg.prefix[first_segment] < n ? sg.prefix[first_segment] : 0;
     if (ncols == 9)
         pack_grad_rows_to_kernel<9><<<(unsigned)((n * 9 + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
             sg, d_means2D, d_rgb, d_conic_opacity, d_means3D, d_scales, d_rotations);

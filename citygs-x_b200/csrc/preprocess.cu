@@ -794,6 +794,104 @@ preprocess_bwd_batched_kernel(int P, const float* __restrict__ means3D, const fl
     block_store_rows<3>(dL_dscales + (size_t)base * 3, s_scale, count, vec_mask & 16);
 }
 
+// ------------------------------------------------------------------------------------------------ row-driven backward
+// The owner's backward over the gradient rows that came back from the ranks that rendered its Gaussians (the
+// exchange's reverse leg): one thread per returned row instead of one per (Gaussian, camera) pair.  Only pairs that
+// were visible somewhere do any work, a Gaussian that went to two ranks for one camera simply has two rows, and no
+// dense per-camera cotangent arrays are built.  Per-Gaussian partial results are summed with 16-byte vector atomics
+// in a (P,16) table [dL/dmean 3 | dL/dcov3D 6 | dL/drot from the plane descriptors 4 | dL/dopacity 1 | 2 unused]; a second kernel runs the
+// covariance backward once per Gaussian (it is linear in dL/dcov3D) and writes the parameter gradients.
+constexpr int MAX_ROW_SEGS = 64;
+constexpr int ROW_ACC = 16;      // floats per Gaussian in the table: 14 used, rows stay 16-byte aligned for vector atomics
+struct RowSegments {
+    long long start[MAX_ROW_SEGS];   // first row of the segment in the row table
+    int count[MAX_ROW_SEGS];
+    int cam[MAX_ROW_SEGS];           // camera the segment's rows belong to
+};
+
+template <int NCOLS>   // 14: means2D 2 | rgb 3 | conic_opacity 4 | plane descriptors 5;  9: without the descriptors
+__global__ void __launch_bounds__(256)
+preprocess_bwd_rows_kernel(const __grid_constant__ RowSegments segs, const float* __restrict__ rows,
+                           const int* __restrict__ row_gaussian, const float* __restrict__ means3D,
+                           const float* __restrict__ scales, const float scale_modifier,
+                           const float4* __restrict__ rotations, const __grid_constant__ CamBatch cams,
+                           const __grid_constant__ CamPlanes planes, float* __restrict__ acc)
+{
+    const int s = blockIdx.y;
+    const int n = segs.count[s];
+    if ((int)blockIdx.x * 256 >= n) return;                 // uniform over the CTA
+    const int b = segs.cam[s];
+    __shared__ float s_view[16], s_proj[16];
+    if (threadIdx.x < 16) s_view[threadIdx.x] = cams.view[b][threadIdx.x];
+    else if (threadIdx.x < 32) s_proj[threadIdx.x - 16] = cams.proj[b][threadIdx.x - 16];
+    __syncthreads();
+    // the CTA's rows are one contiguous piece of the table: staged with coalesced loads
+    __shared__ float s_rows[256 * NCOLS];
+    const int n_cta = min(256, n - (int)blockIdx.x * 256);
+    const float* src = rows + (segs.start[s] + (long long)blockIdx.x * 256) * NCOLS;
+    for (int e = threadIdx.x; e < n_cta * NCOLS; e += 256) s_rows[e] = __ldg(src + e);
+    __syncthreads();
+    const int r = blockIdx.x * 256 + threadIdx.x;
+    if (r >= n) return;
+    const long long row = segs.start[s] + r;
+    const int i = __ldg(row_gaussian + row);
+    const float* g = s_rows + threadIdx.x * NCOLS;
+    const float2 dm2 = {g[0], g[1]};
+    const float4 dco = {g[5], g[6], g[7], g[8]};
+    const float3 mean = {__ldg(means3D + 3 * (size_t)i), __ldg(means3D + 3 * (size_t)i + 1),
+                         __ldg(means3D + 3 * (size_t)i + 2)};
+    const float3 sc = {__ldg(scales + 3 * (size_t)i), __ldg(scales + 3 * (size_t)i + 1),
+                       __ldg(scales + 3 * (size_t)i + 2)};
+    const float4 rot = __ldg(rotations + i);
+    float cov3D[6];
+    compute_cov3d(sc, scale_modifier, rot, cov3D);
+    float3 g_mean = {0.f, 0.f, 0.f};
+    float dL_dcov[6] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    float4 g_rot_plane = {0.f, 0.f, 0.f, 0.f};
+    bwd_project_one(mean, cov3D, s_view, s_proj, cams.focal_x[b], cams.focal_y[b], cams.tan_fovx[b],
+                    cams.tan_fovy[b], dco, dm2, g_mean, dL_dcov);
+    if (NCOLS == 14 && planes.campos[b]) {
+        const float g5[5] = {g[9], g[10], g[11], g[12], g[13]};
+        const float* cp = planes.campos[b];
+        plane_bwd(mean, sc, rot, s_view, make_float3(__ldg(cp), __ldg(cp + 1), __ldg(cp + 2)), g5, g_mean,
+                  g_rot_plane);
+    }
+    float4* a = reinterpret_cast<float4*>(acc + (size_t)i * ROW_ACC);
+    atomicAdd(a + 0, make_float4(g_mean.x, g_mean.y, g_mean.z, dL_dcov[0]));
+    atomicAdd(a + 1, make_float4(dL_dcov[1], dL_dcov[2], dL_dcov[3], dL_dcov[4]));
+    atomicAdd(a + 2, make_float4(dL_dcov[5], g_rot_plane.x, g_rot_plane.y, g_rot_plane.z));
+    atomicAdd(a + 3, make_float4(g_rot_plane.w, dco.w, 0.f, 0.f));
+}
+
+__global__ void __launch_bounds__(256)
+preprocess_bwd_rows_finish_kernel(int P, const float* __restrict__ scales, const float scale_modifier,
+                                  const float4* __restrict__ rotations, const float* __restrict__ acc,
+                                  float* __restrict__ dL_dmeans, float* __restrict__ dL_dscales,
+                                  float4* __restrict__ dL_drots, float* __restrict__ dL_dopacity)
+{
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= P) return;
+    const float* a = acc + (size_t)i * ROW_ACC;
+    float dL_dcov[6];
+    bool any = false;
+#pragma unroll
+    for (int k = 0; k < 6; k++) {
+        dL_dcov[k] = a[3 + k];
+        any |= dL_dcov[k] != 0.f;
+    }
+    float3 g_scale = {0.f, 0.f, 0.f};
+    float4 g_rot = {0.f, 0.f, 0.f, 0.f};
+    if (any) {
+        const float3 sc = {scales[3 * (size_t)i], scales[3 * (size_t)i + 1], scales[3 * (size_t)i + 2]};
+        bwd_cov3d(sc, scale_modifier, rotations[i], dL_dcov, g_scale, g_rot);
+    }
+    dL_dmeans[3 * (size_t)i] = a[0]; dL_dmeans[3 * (size_t)i + 1] = a[1]; dL_dmeans[3 * (size_t)i + 2] = a[2];
+    dL_dscales[3 * (size_t)i] = g_scale.x; dL_dscales[3 * (size_t)i + 1] = g_scale.y;
+    dL_dscales[3 * (size_t)i + 2] = g_scale.z;
+    dL_drots[i] = {g_rot.x + a[9], g_rot.y + a[10], g_rot.z + a[11], g_rot.w + a[12]};
+    dL_dopacity[i] = a[13];
+}
+
 }  // namespace cgx
 
 
@@ -1044,4 +1142,64 @@ extern "C" int cgx_preprocess_bwd_batched(int P, int B, const float* means3D, co
     return cgx_preprocess_bwd_batched_planes(P, B, means3D, scales, scale_modifier, rotations, cams, nullptr, radii,
                                              dL_dmeans2D, dL_dconic_opacity, nullptr, dL_dmeans3D, dL_dscales,
                                              dL_drotations, dL_dopacity, stream);
+}
+
+extern "C" size_t cgx_preprocess_bwd_rows_workspace_bytes(int P) { return (size_t)(P > 0 ? P : 0) * ROW_ACC * sizeof(float); }
+
+extern "C" int cgx_preprocess_bwd_rows(int P, int n_segments, const cgx_row_segment* segments, int ncols,
+                                       const float* rows, const int32_t* row_gaussian, const float* means3D,
+                                       const float* scales, float scale_modifier, const float* rotations, int B,
+                                       const cgx_camera* cams, const float* const* campos, void* workspace,
+                                       size_t workspace_bytes, float* dL_dmeans3D, float* dL_dscales,
+                                       float* dL_drotations, float* dL_dopacity, void* stream)
+{
+    if (P < 0 || n_segments < 0 || n_segments > MAX_ROW_SEGS || (ncols != 14 && ncols != 9)) return CGX_EINVAL;
+    CamBatch cb;
+    int st = fill_cams(cb, B, cams);
+    if (st != CGX_OK) return st;
+    if (P == 0) return CGX_OK;
+    if (!means3D || !scales || !rotations || !dL_dmeans3D || !dL_dscales || !dL_drotations || !dL_dopacity ||
+        !workspace || !aligned16(workspace) || !aligned16(rotations) || !aligned16(dL_drotations))
+        return CGX_EINVAL;
+    if (workspace_bytes < cgx_preprocess_bwd_rows_workspace_bytes(P)) return CGX_ENOMEM;
+    if (n_segments && (!segments || !rows || !row_gaussian)) return CGX_EINVAL;
+    RowSegments sg;
+    memset(&sg, 0, sizeof(sg));
+    CamPlanes pl;
+    memset(&pl, 0, sizeof(pl));
+    int longest = 0;
+    for (int k = 0; k < n_segments; k++) {
+        const cgx_row_segment& e = segments[k];
+        if (e.start < 0 || e.count < 0 || e.count > 0x7fffffffLL || e.camera < 0 || e.camera >= B) return CGX_EINVAL;
+        sg.start[k] = e.start;
+        sg.count[k] = (int)e.count;
+        sg.cam[k] = e.camera;
+        if ((int)e.count > longest) longest = (int)e.count;
+    }
+    if (ncols == 14) {
+        if (!campos) return CGX_EINVAL;
+        for (int b = 0; b < B; b++) {
+            if (!campos[b]) return CGX_EINVAL;
+            pl.campos[b] = campos[b];
+        }
+    }
+    cudaStream_t cs = (cudaStream_t)stream;
+    cudaError_t e = cudaMemsetAsync(workspace, 0, cgx_preprocess_bwd_rows_workspace_bytes(P), cs);
+    if (e != cudaSuccess) { set_cuda_error(e); return CGX_ECUDA; }
+    int launched = 0;
+    if (longest > 0) {
+        const dim3 grid((unsigned)((longest + 255) / 256), (unsigned)n_segments);
+        if (ncols == 14)
+            preprocess_bwd_rows_kernel<14><<<grid, 256, 0, cs>>>(sg, rows, row_gaussian, means3D, scales, scale_modifier,
+                                                                 (const float4*)rotations, cb, pl, (float*)workspace);
+        else
+            preprocess_bwd_rows_kernel<9><<<grid, 256, 0, cs>>>(sg, rows, row_gaussian, means3D, scales, scale_modifier,
+                                                                (const float4*)rotations, cb, pl, (float*)workspace);
+        launched++;
+    }
+    preprocess_bwd_rows_finish_kernel<<<(P + 255) / 256, 256, 0, cs>>>(P, scales, scale_modifier,
+                                                                       (const float4*)rotations,
+                                                                       (const float*)workspace, dL_dmeans3D, dL_dscales,
+                                                                       (float4*)dL_drotations, dL_dopacity);
+    return check_launch(launched + 1);
 }

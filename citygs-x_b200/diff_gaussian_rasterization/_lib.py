@@ -63,6 +63,9 @@ SIGNATURES = {
     "cgx_preprocess_bwd_batched": (_i, [_i, _i, _vp, _vp, _f, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "cgx_preprocess_fwd_batched_planes": (_i, [_i, _i, _vp, _vp, _f] + [_vp] * 10),
     "cgx_preprocess_bwd_batched_planes": (_i, [_i, _i, _vp, _vp, _f] + [_vp] * 12),
+    "cgx_preprocess_bwd_rows_workspace_bytes": (_sz, [_i]),
+    "cgx_preprocess_bwd_rows": (_i, [_i, _i, _vp, _i, _vp, _vp, _vp, _vp, _f, _vp, _i, _vp, _vp, _vp, _sz,
+                                     _vp, _vp, _vp, _vp, _vp]),
     "cgx_all_map_fwd": (_i, [_i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "cgx_all_map_bwd": (_i, [_i] + [_vp] * 10),
     "cgx_strip_loss_fwd": (_i, [_i, _i, _i] + [_vp] * 8),
@@ -79,7 +82,7 @@ SIGNATURES = {
     "cgx_pack_grad_rows": (_i, [_i] + [_vp] * 10),
     "cgx_local2j_pack_p2p": (_i, [_i, _i, _i, _i] + [_vp] * 9 + [_i] + [_vp] * 4 + [_sz, _vp]),
     "cgx_local2j_pack_p2p_batched": (_i, [_i, _vp, _vp, _vp]),
-    "cgx_pack_grad_rows_to": (_i, [_i, _vp, _vp, _i] + [_vp] * 7),
+    "cgx_pack_grad_rows_to": (_i, [_i, _vp, _vp, _i, _i] + [_vp] * 7),
     "cgx_unpack_grad_add_cols": (_i, [_i, _vp, _vp, _i] + [_vp] * 9),
     "cgx_rows_workspace_bytes": (_sz, [_i64, _i]),
     "cgx_rows_dest_count": (_i, [_i64, _i, _vp, _vp, _vp, _sz, _vp]),

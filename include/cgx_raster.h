@@ -131,6 +131,29 @@ int cgx_preprocess_bwd_batched_planes(int P, int B, const float* means3D, const 
                                       float* dL_dmeans3D, float* dL_dscales, float* dL_drotations,
                                       float* dL_dopacity, void* stream);
 
+/* The owner's backward driven by the gradient rows that came back through the exchange, instead of by dense
+ * per-camera cotangent arrays: rows[r] = ncols floats [dL/dmeans2D 2 | dL/drgb 3 (ignored) | dL/dconic_opacity 4 |
+ * dL/dall_map 5 when ncols = 14], row_gaussian[r] = local index of the Gaussian the row belongs to, segments[] says
+ * which rows belong to which camera (at most 64 segments per call, host array).  A Gaussian may own several rows of
+ * one camera (it was sent to two ranks); Gaussians without rows get zero gradients.  Replaces, for the
+ * peer-to-peer exchange, the scatter of returned rows into (P, .) arrays followed by preprocessBackward per camera
+ * (autograd through the differentiable all_to_all of gaussian_renderer/__init__.py:660-676; cuda_rasterizer/backward.cu:203-321,80-198).
+ * workspace: cgx_preprocess_bwd_rows_workspace_bytes(P) bytes, 16-byte aligned, cleared by the call.  Sums over rows
+ * use atomics:
+ * results agree with cgx_preprocess_bwd_batched_planes to float rounding, not bit for bit. */
+typedef struct cgx_row_segment {
+    long long start;   /* first row of the segment */
+    long long count;   /* rows in the segment */
+    int camera;        /* index into cams[] */
+    int reserved;
+} cgx_row_segment;
+size_t cgx_preprocess_bwd_rows_workspace_bytes(int P);
+int cgx_preprocess_bwd_rows(int P, int n_segments, const cgx_row_segment* segments, int ncols, const float* rows,
+                            const int32_t* row_gaussian, const float* means3D, const float* scales,
+                            float scale_modifier, const float* rotations, int B, const cgx_camera* cams,
+                            const float* const* campos, void* workspace, size_t workspace_bytes, float* dL_dmeans3D,
+                            float* dL_dscales, float* dL_drotations, float* dL_dopacity, void* stream);
+
 /* PGSR per-Gaussian plane descriptor [normal_cam(3), 1, plane distance] for one camera: the
  * tensor code of the reference's caller (gaussian_renderer/__init__.py:1501-1518) as one kernel.
  * radii optional: rows with radius <= 0 get zeros.  all_map (P,5). */
@@ -293,9 +316,13 @@ typedef struct cgx_count_camera {
     uint64_t workspace_bytes;
 } cgx_count_camera;
 int cgx_local2j_count_batched(int n_cameras, const cgx_count_camera* cams /* host */, void* stream);
+/* first_segment: the launch works through the rows starting with this segment and wraps around (the result is
+ * the same for every value); ranks that pass different values, e.g. (rank + 1) % n_segments, do not all store into
+ * the same peer at the same time. */
 int cgx_pack_grad_rows_to(int n_segments, float* const* seg_rows, const int64_t* seg_count, int ncols,
-                          const float* d_means2D, const float* d_rgb, const float* d_conic_opacity,
-                          const float* d_means3D, const float* d_scales, const float* d_rotations, void* stream);
+                          int first_segment, const float* d_means2D, const float* d_rgb,
+                          const float* d_conic_opacity, const float* d_means3D, const float* d_scales,
+                          const float* d_rotations, void* stream);
 /* cgx_unpack_grad_add for rows of `ncols` floats: 19 = every differentiable column, 9 = means2D | rgb |
  * conic_opacity only (used when no gradient flows back to the 3-D parameters through the exchange), 14 = means2D |
  * rgb | conic_opacity | plane descriptors (5): the (n,5) array takes the place of the means3D argument and the

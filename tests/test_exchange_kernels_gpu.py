@@ -272,3 +272,25 @@ def test_gradient_rows_round_trip(setup, cuda_device, ncols):
     be.unpack_grad_add_cols(staging, index, ranges, ncols, grads + pad)
     for g, e in zip(grads, expect):
         assert torch.allclose(g.cpu().double(), e, atol=1e-5, rtol=1e-6)
+
+
+@pytest.mark.parametrize("first", [0, 1, 2, 3])
+def test_gradient_rows_to_several_owners_in_any_starting_order(cuda_device, first):
+    """One launch of cgx_pack_grad_rows_to with four segments (one empty): whichever segment the grid starts with,
+    every segment receives exactly its rows."""
+    from cgx import exchange
+
+    be = exchange.default_backend()
+    gen = torch.Generator().manual_seed(11)
+    counts = [700, 0, 1300, 257]
+    n = sum(counts)
+    cot = [torch.randn(n, w, generator=gen).to(cuda_device) for w in (2, 3, 4, 5)]
+    segs = [torch.full((max(c, 1), 14), float("nan"), device=cuda_device) for c in counts]
+    be.pack_grad_rows_to([s.data_ptr() for s in segs], counts, 14, cot + [None, None], first_segment=first)
+    torch.cuda.synchronize()
+    want = torch.cat(cot, 1)
+    start = 0
+    for s, c in zip(segs, counts):
+        if c:
+            assert torch.equal(s[:c], want[start:start + c])
+        start += c

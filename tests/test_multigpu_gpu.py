@@ -22,7 +22,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, ws, port, out_dir, transport, n_cams):
+def _worker(rank, ws, port, out_dir, transport, n_cams, owner_backward):
     for p in (ROOT, ROOT / "citygs-x_b200", ROOT / "tests"):
         sys.path.insert(0, str(p))
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0",
@@ -38,6 +38,7 @@ def _worker(rank, ws, port, out_dir, transport, n_cams):
 
         g, cams = S.config(2, n_gaussians=N_GAUSS, n_cameras=n_cams, res=RES)
         step = RT.TrainingStep(g, cams, dev, rank=rank, world_size=ws, transport=transport)
+        step.owner_backward = owner_backward
         step.run()
         step.run()          # twice: the second step reuses the exchange arenas
         torch.cuda.synchronize()
@@ -56,11 +57,14 @@ def _worker(rank, ws, port, out_dir, transport, n_cams):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("transport,ws,n_cams", [("p2p", 2, 4), ("collective", 2, 4), ("p2p", 2, 3),
-                                                  ("collective", 2, 3), ("p2p", 4, 4), ("p2p", 3, 4)])
-def test_multi_gpu_step_equals_single_gpu_step(tmp_path, transport, ws, n_cams):
+@pytest.mark.parametrize("transport,ws,n_cams,owner_backward",
+                         [("p2p", 2, 4, True), ("collective", 2, 4, False), ("p2p", 2, 3, True), ("p2p", 2, 3, False),
+                          ("collective", 2, 3, False), ("p2p", 4, 4, True), ("p2p", 3, 4, True), ("p2p", 3, 4, False)])
+def test_multi_gpu_step_equals_single_gpu_step(tmp_path, transport, ws, n_cams, owner_backward):
     """Where ws does not divide the cameras, one camera is split between two ranks (tile-row bands): Gaussians
-    straddling the cut go to both, and their gradient rows come back from both."""
+    straddling the cut go to both, and their gradient rows come back from both.  `owner_backward`: the owner's
+    preprocess backward runs inside the exchange's backward, straight over the returned rows (then the owner-side
+    screen-space tensors carry no gradient); otherwise the rows are scattered into dense cotangents first."""
     if torch.cuda.device_count() < ws:
         pytest.skip(f"needs {ws} GPUs")
     import torch.multiprocessing as mp
@@ -69,7 +73,7 @@ def test_multi_gpu_step_equals_single_gpu_step(tmp_path, transport, ws, n_cams):
     from cgx import synthetic as S
 
     port = _free_port()
-    mp.spawn(_worker, args=(ws, port, str(tmp_path), transport, n_cams), nprocs=ws, join=True)
+    mp.spawn(_worker, args=(ws, port, str(tmp_path), transport, n_cams, owner_backward), nprocs=ws, join=True)
     parts = [torch.load(tmp_path / f"rank{r}.pt", weights_only=False) for r in range(ws)]
 
     dev = torch.device("cuda:0")
@@ -100,7 +104,10 @@ def test_multi_gpu_step_equals_single_gpu_step(tmp_path, transport, ws, n_cams):
         for r in range(ws):
             radii_r, m2g_r = parts[r]["m2"][k]
             assert torch.equal(radii_r, radii_full[r::ws])
-            assert util.rel_l2(m2g_r, m2_full[r::ws]) <= 1e-3
+            if owner_backward and transport == "p2p":
+                assert m2g_r is None
+            else:
+                assert util.rel_l2(m2g_r, m2_full[r::ws]) <= 1e-3
 
 
 def _redistribute_worker(rank, ws, port, out_dir, transport):

@@ -757,3 +757,77 @@ def test_camera_streams_do_not_change_the_step(cuda_device):
         for k in names:
             rel = ((grads[k] - base_grads[k]).norm() / base_grads[k].norm()).item()
             assert rel <= 1e-5, (k, rel)
+
+
+def test_row_driven_preprocess_backward_equals_dense(cuda_device):
+    """cgx_preprocess_bwd_rows (one thread per returned gradient row, sums by atomics) against the camera-batched
+    backward over dense per-camera cotangents built from the same rows: several segments per camera, Gaussians with
+    two rows for one camera (sent to two ranks), Gaussians with no row at all."""
+    import ctypes as C
+
+    from cgx.batched import _cams, _ptrs, preprocess_gaussians_batched
+    from cgx.exchange import _RowSegment
+    from cgx import runtime as RT
+    from diff_gaussian_rasterization import _lib
+
+    n, B = 30_000, 3
+    g, cams = util.S.config(2, n_gaussians=n, n_cameras=B, res=(320, 240))
+    dev = cuda_device
+    settings = RT.TrainingStep(g, cams, dev).settings
+    names = ("means3D", "scales", "rotations", "opacities")
+    leaves = {k: g[k].to(dev).requires_grad_(True) for k in names}
+    out = preprocess_gaussians_batched(leaves["means3D"], leaves["scales"], leaves["rotations"], None,
+                                       leaves["opacities"], settings, planes=True)
+    gen = torch.Generator().manual_seed(5)
+    rows, index, segs, start = [], [], [], 0
+    dense = [(torch.zeros(n, 2, device=dev), torch.zeros(n, 4, device=dev), torch.zeros(n, 5, device=dev))
+             for _ in range(B)]
+    for b in range(B):
+        vis = (out[b][3] > 0).nonzero().flatten().cpu()
+        pick = vis[torch.rand(len(vis), generator=gen) < 0.7]
+        assert len(pick) > 1000
+        for part in (pick, pick[::7]):                        # the second segment repeats every seventh Gaussian
+            r = torch.randn(len(part), 14, generator=gen).to(dev)
+            idx = part.to(dev)
+            rows.append(r)
+            index.append(idx.to(torch.int32))
+            segs.append((start, len(part), b))
+            start += len(part)
+            dense[b][0].index_add_(0, idx, r[:, 0:2])
+            dense[b][1].index_add_(0, idx, r[:, 5:9])
+            dense[b][2].index_add_(0, idx, r[:, 9:14])
+    segs.insert(2, (start, 0, 1))                             # an empty segment is legal
+    sum((t[0] * d[0]).sum() + (t[2] * d[1]).sum() + (t[5] * d[2]).sum() for t, d in zip(out, dense)).backward()
+    want = {k: leaves[k].grad for k in names}
+
+    rows, index = torch.cat(rows).contiguous(), torch.cat(index).contiguous()
+    arr = (_RowSegment * len(segs))()
+    for e, (a, cnt, b) in zip(arr, segs):
+        e.start, e.count, e.camera = a, cnt, b
+    l = _lib.lib()
+    got = {"means3D": torch.empty(n, 3, device=dev), "scales": torch.empty(n, 3, device=dev),
+           "rotations": torch.empty(n, 4, device=dev), "opacities": torch.empty(n, 1, device=dev)}
+    work = torch.empty(l.cgx_preprocess_bwd_rows_workspace_bytes(n), dtype=torch.uint8, device=dev)
+    cam_arr, keep = _cams(settings)
+    campos = [rs.campos.contiguous() for rs in settings]
+    p = {k: leaves[k].detach().contiguous() for k in names}
+
+    def call(nbytes, ncols=14):
+        return l.cgx_preprocess_bwd_rows(
+            n, len(segs), arr, ncols, C.c_void_p(rows.data_ptr()), C.c_void_p(index.data_ptr()),
+            C.c_void_p(p["means3D"].data_ptr()), C.c_void_p(p["scales"].data_ptr()), 1.0,
+            C.c_void_p(p["rotations"].data_ptr()), B, cam_arr, _ptrs(campos), C.c_void_p(work.data_ptr()), nbytes,
+            C.c_void_p(got["means3D"].data_ptr()), C.c_void_p(got["scales"].data_ptr()),
+            C.c_void_p(got["rotations"].data_ptr()), C.c_void_p(got["opacities"].data_ptr()),
+            C.c_void_p(torch.cuda.current_stream().cuda_stream))
+
+    assert call(work.numel() - 1) == _lib.CGX_ENOMEM
+    assert call(work.numel(), ncols=12) == _lib.CGX_EINVAL
+    assert call(work.numel()) == 0
+    torch.cuda.synchronize()
+    for k in names:
+        rel = ((got[k] - want[k]).norm() / want[k].norm()).item()
+        assert rel <= 1e-5, (k, rel)
+    untouched = torch.ones(n, dtype=torch.bool, device=dev)
+    untouched[index.long()] = False
+    assert untouched.any() and (got["means3D"][untouched] == 0).all() and (got["opacities"][untouched] == 0).all()
