@@ -957,14 +957,16 @@ render_bwd2_kernel(const uint2* __restrict__ ranges, const uint32_t* __restrict_
             while (v0 < g_max) {
             uint32_t mine = 0, visit_mask = 0;
             int rows = 0, g = 0;
-            while (v0 + g < g_max && rows <= BWD_CAP - 32) {
+            while (v0 + g < g_max) {
                 const int j = my_hits[base + v0 + g];
                 const bool valid = ((__shfl_sync(0xffffffffu, pm, v0 + g) >> lane) & 1u) &&
                                    (idx_base - (uint32_t)j < (uint32_t)last_contributor);
                 const uint32_t m = __ballot_sync(0xffffffffu, valid);
+                const int c = __popc(m);
+                if (rows + c > BWD_CAP) break;      // the table is full (a visit alone always fits): next group
                 if (lane == g) visit_mask = m;
                 mine |= (valid ? 1u : 0u) << g;
-                rows += __popc(m);
+                rows += c;
                 g++;
             }
             if (rows) {
