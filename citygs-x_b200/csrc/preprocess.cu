@@ -718,6 +718,9 @@ preprocess_fwd_batched_kernel(int P, const float* __restrict__ means3D, const fl
     }
 }
 
+#ifndef CGX_PRE_BWD_COMPACT
+#define CGX_PRE_BWD_COMPACT 1     // 1: the CTA-compacted kernel below serves cgx_preprocess_bwd_batched*; 0: the walk per Gaussian
+#endif
 #ifndef CGX_PRE_BWD_MIN_CTAS
 #define CGX_PRE_BWD_MIN_CTAS 3
 #endif
@@ -783,6 +786,149 @@ preprocess_bwd_batched_kernel(int P, const float* __restrict__ means3D, const fl
         g_rot = {g_rot.x + g_rot_plane.x, g_rot.y + g_rot_plane.y, g_rot.z + g_rot_plane.z, g_rot.w + g_rot_plane.w};
         dL_dopacity[idx] = g_op;
         dL_drots[idx] = g_rot;
+    }
+    __syncthreads();
+    if (t < count) {
+        s_mean[3 * t] = g_mean.x; s_mean[3 * t + 1] = g_mean.y; s_mean[3 * t + 2] = g_mean.z;
+        s_scale[3 * t] = g_scale.x; s_scale[3 * t + 1] = g_scale.y; s_scale[3 * t + 2] = g_scale.z;
+    }
+    __syncthreads();
+    block_store_rows<3>(dL_dmeans + (size_t)base * 3, s_mean, count, vec_mask & 8);
+    block_store_rows<3>(dL_dscales + (size_t)base * 3, s_scale, count, vec_mask & 16);
+}
+
+// The same backward with the work compacted inside the CTA.  In the kernel above a thread owns a Gaussian and walks
+// the cameras; a Gaussian is visible in a minority of them and its neighbours in memory are visible in OTHER ones, so
+// most lanes of a warp idle through every camera's arithmetic.  Here the CTA first lists its visible (Gaussian,
+// camera) pairs in shared memory, then its threads work through the list (every lane busy) and add each pair's
+// partial results to per-Gaussian sums in shared memory; the covariance backward and the stores follow per Gaussian.
+constexpr int PRE_ACC = 15;      // floats per Gaussian: dL/dmean 3 | dL/dcov3D 6 | plane dL/drot 4 | dL/dopacity 1, odd pitch
+#ifndef CGX_PRE_BWDC_MIN_CTAS
+#define CGX_PRE_BWDC_MIN_CTAS 4
+#endif
+__global__ void __launch_bounds__(CGX_BLOCK_SIZE, CGX_PRE_BWDC_MIN_CTAS)
+preprocess_bwd_batched_compact_kernel(int P, const float* __restrict__ means3D, const float* __restrict__ scales,
+                                      const float scale_modifier, const float* __restrict__ rotations,
+                                      const __grid_constant__ CamBatch cams, const __grid_constant__ CamCotangents cot,
+                                      const __grid_constant__ CamPlanes planes, float* __restrict__ dL_dmeans,
+                                      float* __restrict__ dL_dscales, float4* __restrict__ dL_drots,
+                                      float* __restrict__ dL_dopacity, int vec_mask)
+{
+    __shared__ __align__(16) float s_mean[CGX_BLOCK_SIZE * 3];   // reused for dL_dmeans
+    __shared__ __align__(16) float s_scale[CGX_BLOCK_SIZE * 3];  // reused for dL_dscales
+    __shared__ __align__(16) float s_rot[CGX_BLOCK_SIZE * 4];
+    __shared__ float s_cov[CGX_BLOCK_SIZE * 6 + 1];
+    __shared__ float s_acc[CGX_BLOCK_SIZE * PRE_ACC];
+    __shared__ float s_view[MAX_CAMS][16];
+    __shared__ float s_proj[MAX_CAMS][16];
+    __shared__ uint16_t s_list[CGX_BLOCK_SIZE * MAX_CAMS];       // (camera << 8) | Gaussian of the CTA
+    __shared__ int s_count;
+
+    const int base = blockIdx.x * CGX_BLOCK_SIZE;
+    const int count = min(CGX_BLOCK_SIZE, P - base);
+    const int t = threadIdx.x, lane = t & 31;
+    for (int i = t; i < cams.B * 32; i += blockDim.x) {
+        const int b = i >> 5, e = i & 31;
+        if (e < 16) s_view[b][e] = cams.view[b][e];
+        else s_proj[b][e - 16] = cams.proj[b][e - 16];
+    }
+    for (int i = t; i < CGX_BLOCK_SIZE * PRE_ACC; i += blockDim.x) s_acc[i] = 0.f;
+    if (t == 0) s_count = 0;
+    block_load_rows<3>(means3D + (size_t)base * 3, s_mean, count, vec_mask & 1);
+    block_load_rows<3>(scales + (size_t)base * 3, s_scale, count, vec_mask & 2);
+    block_load_rows<4>(rotations + (size_t)base * 4, s_rot, count, vec_mask & 4);
+    __syncthreads();
+
+    // ---- list the visible pairs (warp-aggregated append; the order inside the list does not matter)
+    const int idx = base + t;
+    if (t < count) {
+        const float3 sc = {s_scale[3 * t], s_scale[3 * t + 1], s_scale[3 * t + 2]};
+        const float4 rot = {s_rot[4 * t], s_rot[4 * t + 1], s_rot[4 * t + 2], s_rot[4 * t + 3]};
+        float cov3D[6];
+        compute_cov3d(sc, scale_modifier, rot, cov3D);
+#pragma unroll
+        for (int k = 0; k < 6; k++) s_cov[6 * t + k] = cov3D[k];
+    }
+    // all radii first, then the opacity cotangents of the cameras this Gaussian is not visible in (the reference's
+    // glue returns a plain slice of dL/dconic_opacity, whatever the radius): independent loads, two round trips
+    uint32_t vis_mask = 0;
+#pragma unroll
+    for (int b = 0; b < MAX_CAMS; b++)
+        if (b < cams.B && t < count && __ldg(cot.radii[b] + idx) > 0) vis_mask |= 1u << b;
+    float g_op_rest = 0.f;
+#pragma unroll
+    for (int b = 0; b < MAX_CAMS; b++)
+        if (b < cams.B && t < count && !((vis_mask >> b) & 1u))
+            g_op_rest += __ldg(reinterpret_cast<const float*>(cot.dL_dconic_opacity[b] + idx) + 3);
+    for (int b = 0; b < cams.B; b++) {
+        const bool vis = (vis_mask >> b) & 1u;
+        const uint32_t m = __ballot_sync(0xffffffffu, vis);
+        if (m) {
+            int at = 0;
+            if (lane == 0) at = atomicAdd(&s_count, __popc(m));
+            at = __shfl_sync(0xffffffffu, at, 0);
+            if (vis) s_list[at + __popc(m & ((1u << lane) - 1u))] = (uint16_t)((b << 8) | t);
+        }
+    }
+    __syncthreads();
+
+    // ---- one pair per thread and turn
+    const int n_pairs = s_count;
+    for (int p = t; p < n_pairs; p += CGX_BLOCK_SIZE) {
+        const int e = s_list[p];
+        const int b = e >> 8, g = e & 255;
+        const int gi = base + g;
+        const float3 mean = {s_mean[3 * g], s_mean[3 * g + 1], s_mean[3 * g + 2]};
+        float cov3D[6];
+#pragma unroll
+        for (int k = 0; k < 6; k++) cov3D[k] = s_cov[6 * g + k];
+        const float4 dco = __ldg(cot.dL_dconic_opacity[b] + gi);
+        const float2 dm2 = __ldg(cot.dL_dmeans2D[b] + gi);
+        float3 g_mean = {0.f, 0.f, 0.f};
+        float dL_dcov[6] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        float4 g_rot_plane = {0.f, 0.f, 0.f, 0.f};
+        bwd_project_one(mean, cov3D, s_view[b], s_proj[b], cams.focal_x[b], cams.focal_y[b], cams.tan_fovx[b],
+                        cams.tan_fovy[b], dco, dm2, g_mean, dL_dcov);
+        if (planes.dL_dall_map[b]) {
+            const float3 sc = {s_scale[3 * g], s_scale[3 * g + 1], s_scale[3 * g + 2]};
+            const float4 rot = {s_rot[4 * g], s_rot[4 * g + 1], s_rot[4 * g + 2], s_rot[4 * g + 3]};
+            const float* gp = planes.dL_dall_map[b] + 5 * (size_t)gi;
+            const float g5[5] = {__ldg(gp), __ldg(gp + 1), __ldg(gp + 2), __ldg(gp + 3), __ldg(gp + 4)};
+            const float* cp = planes.campos[b];
+            plane_bwd(mean, sc, rot, s_view[b], make_float3(__ldg(cp), __ldg(cp + 1), __ldg(cp + 2)), g5, g_mean,
+                      g_rot_plane);
+        }
+        float* a = s_acc + g * PRE_ACC;
+        atomicAdd(a + 0, g_mean.x); atomicAdd(a + 1, g_mean.y); atomicAdd(a + 2, g_mean.z);
+#pragma unroll
+        for (int k = 0; k < 6; k++) atomicAdd(a + 3 + k, dL_dcov[k]);
+        atomicAdd(a + 9, g_rot_plane.x); atomicAdd(a + 10, g_rot_plane.y);
+        atomicAdd(a + 11, g_rot_plane.z); atomicAdd(a + 12, g_rot_plane.w);
+        atomicAdd(a + 13, dco.w);
+    }
+    __syncthreads();
+
+    // ---- per Gaussian: covariance backward (linear in dL/dcov3D: once for all cameras) and the stores
+    float3 g_mean = {0.f, 0.f, 0.f}, g_scale = {0.f, 0.f, 0.f};
+    if (t < count) {
+        const float* a = s_acc + t * PRE_ACC;
+        const float g_op = a[13] + g_op_rest;
+        float dL_dcov[6];
+        bool any = false;
+#pragma unroll
+        for (int k = 0; k < 6; k++) {
+            dL_dcov[k] = a[3 + k];
+            any |= dL_dcov[k] != 0.f;
+        }
+        float4 g_rot = {0.f, 0.f, 0.f, 0.f};
+        if (any) {
+            const float3 sc = {s_scale[3 * t], s_scale[3 * t + 1], s_scale[3 * t + 2]};
+            const float4 rot = {s_rot[4 * t], s_rot[4 * t + 1], s_rot[4 * t + 2], s_rot[4 * t + 3]};
+            bwd_cov3d(sc, scale_modifier, rot, dL_dcov, g_scale, g_rot);
+        }
+        g_mean = {a[0], a[1], a[2]};
+        dL_dopacity[idx] = g_op;
+        dL_drots[idx] = {g_rot.x + a[9], g_rot.y + a[10], g_rot.z + a[11], g_rot.w + a[12]};
     }
     __syncthreads();
     if (t < count) {
@@ -1126,10 +1272,17 @@ extern "C" int cgx_preprocess_bwd_batched_planes(int P, int B, const float* mean
     }
     const int vec_mask = (aligned16(means3D) ? 1 : 0) | (aligned16(scales) ? 2 : 0) | (aligned16(rotations) ? 4 : 0) |
                          (aligned16(dL_dmeans3D) ? 8 : 0) | (aligned16(dL_dscales) ? 16 : 0);
+#if CGX_PRE_BWD_COMPACT
+    preprocess_bwd_batched_compact_kernel<<<(P + CGX_BLOCK_SIZE - 1) / CGX_BLOCK_SIZE, CGX_BLOCK_SIZE, 0,
+                                            (cudaStream_t)stream>>>(P, means3D, scales, scale_modifier, rotations, cb,
+                                                                    c, pl, dL_dmeans3D, dL_dscales,
+                                                                    (float4*)dL_drotations, dL_dopacity, vec_mask);
+#else
     preprocess_bwd_batched_kernel<<<(P + CGX_BLOCK_SIZE - 1) / CGX_BLOCK_SIZE, CGX_BLOCK_SIZE, 0,
                                     (cudaStream_t)stream>>>(P, means3D, scales, scale_modifier, rotations, cb, c, pl,
                                                             dL_dmeans3D, dL_dscales, (float4*)dL_drotations,
                                                             dL_dopacity, vec_mask);
+#endif
     return check_launch();
 }
 
