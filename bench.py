@@ -528,8 +528,8 @@ DRAM_TRAFFIC_PER_ALGO_BYTE = {"cgx_render_bwd": NCU_BWD_TRAFFIC / NCU_BWD_ALGO, 
 
 # ncu counters of one launch of each blending kernel on one camera of the default workload (the same captures)
 NCU_PIPE_COUNTERS = {
-    "cgx_render_bwd": {"issue_active_pct": 69.7, "pipe_fma_pct": 31.1, "dram_throughput_pct": 15.3,
-                       "warp_instructions": 1.145e9},
+    "cgx_render_bwd": {"issue_active_pct": 65.6, "pipe_fma_pct": 28.9, "dram_throughput_pct": 15.8,
+                       "warp_instructions": 1.047e9},
     "cgx_render_fwd": {"issue_active_pct": 81.1, "pipe_fma_pct": 33.5, "dram_throughput_pct": 9.3,
                        "warp_instructions": 0.514e9},
 }

@@ -956,7 +956,7 @@ struct RowSegments {
 };
 
 template <int NCOLS>   // 14: means2D 2 | rgb 3 | conic_opacity 4 | plane descriptors 5;  9: without the descriptors
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 4)
 preprocess_bwd_rows_kernel(const __grid_constant__ RowSegments segs, const float* __restrict__ rows,
                            const int* __restrict__ row_gaussian, const float* __restrict__ means3D,
                            const float* __restrict__ scales, const float scale_modifier,
