@@ -136,6 +136,21 @@ __device__ __forceinline__ uint32_t block_pixel_mask(const float4 q0, const floa
     return pm;
 }
 
+// 32 x 32 bit matrix held one row per lane -> one column per lane (five exchanges of off-diagonal blocks).  Turns
+// "lane v holds the pixel mask of visit v" into "lane p holds the visit mask of pixel p" and back.
+__device__ __forceinline__ uint32_t warp_transpose32(uint32_t a, const int lane)
+{
+#pragma unroll
+    for (int s = 0; s < 5; s++) {
+        const int j = 16 >> s;
+        const uint32_t m0 = s == 0 ? 0x0000FFFFu : s == 1 ? 0x00FF00FFu : s == 2 ? 0x0F0F0F0Fu
+                          : s == 3 ? 0x33333333u : 0x55555555u;
+        const uint32_t other = __shfl_xor_sync(0xffffffffu, a, j);
+        a = (lane & j) ? ((a & ~m0) | ((other >> j) & m0)) : ((a & m0) | ((other & m0) << j));
+    }
+    return a;
+}
+
 // How densely the scene's splats cover the 8x4 pixel blocks they touch, measured by the forward pass: [0] = sum
 // over visits of the pixels that pass the alpha test, [1] = visits.  The backward pass picks its walk from it
 // without the host ever reading it: where a visit reaches most of its block (large splats: close or high-resolution
@@ -385,8 +400,7 @@ render_fwd_kernel(const uint2* __restrict__ ranges, const uint32_t* __restrict__
                         continue;
                     }
                     // ... and every pixel collects its own bit of each mask: one bit per visit that reaches it
-                    uint32_t mine = 0;
-                    for (int v = 0; v < g; v++) mine |= ((__shfl_sync(0xffffffffu, pm, v) >> lane) & 1u) << v;
+                    uint32_t mine = warp_transpose32(pm, lane);      // pm is zero in the lanes beyond the chunk
                     if (done || (CGX_EXPERIMENT & 2)) mine = 0;
                     // phase 2: this pixel's own contributors, front to back
                     uint32_t seen_clear = 0;      // visits this pixel blended while its transmittance was above 0.5
@@ -420,11 +434,7 @@ render_fwd_kernel(const uint2* __restrict__ ranges, const uint32_t* __restrict__
                     // out_observe: one atomic per Gaussian with the number of such pixels (lanes walking their own
                     // lists would otherwise issue one atomic per pixel, to as many addresses as lanes)
                     if (__any_sync(0xffffffffu, seen_clear != 0)) {
-                        int cnt = 0;
-                        for (int v = 0; v < g; v++) {
-                            const int c = __popc(__ballot_sync(0xffffffffu, (seen_clear >> v) & 1u));
-                            if (lane == v) cnt = c;
-                        }
+                        const int cnt = __popc(warp_transpose32(seen_clear, lane));   // lane v: pixels of visit v
                         if (cnt) atomicAdd(&(out_observe[ids[my_hits[base + lane]]]), cnt);
                     }
                 }
@@ -944,8 +954,7 @@ render_bwd2_kernel(const uint2* __restrict__ ranges, const uint32_t* __restrict_
         for (int base = 0; base < n_hits; base += 32) {
             // ---- phase 1: which pixels does each visit reach?  Lane v keeps the pixel mask of visit v, every lane
             // keeps the visit mask of its own pixel.  A chunk of 32 visits is cut into groups whose rows fit the table.
-            // Lane v tests Gaussian v against the block's pixels; then every pixel keeps its own bit of each mask if
-            // the Gaussian lies before the pixel's last contributor.
+            // Lane v tests Gaussian v against the block's pixels.
             const int g_max = min(32, n_hits - base);
             uint32_t pm = 0;
             if (lane < g_max && !(CGX_EXPERIMENT & 1)) {
@@ -953,32 +962,38 @@ render_bwd2_kernel(const uint2* __restrict__ ranges, const uint32_t* __restrict_
                 const float4 q3 = rec[j].q3;
                 pm = block_pixel_mask(rec[j].q0, *reinterpret_cast<const float2*>(&rec[j].q1), q3.z, q3.w, sx0, sy0);
             }
+            // Every pixel's bits of the chunk's masks at once (a bit-matrix transpose), cut down to the visits that lie
+            // before the pixel's last contributor: the hits are in back-to-front order, so those are the visits from
+            // some v_cut on, found by a search over the chunk's slots.  Transposed back, lane v holds the pixels
+            // visit v really contributes to; a scan of their counts gives every visit its first table row.
+            uint32_t mine_all = warp_transpose32(pm, lane);
+            {
+                const int thr = (int)idx_base - (int)last_contributor;   // valid: slot j > thr
+                int lo = 0, hi = g_max;
+                while (lo < hi) {
+                    const int mid = (lo + hi) >> 1;
+                    if ((int)my_hits[base + mid] <= thr) lo = mid + 1;
+                    else hi = mid;
+                }
+                mine_all = lo >= 32 ? 0u : (mine_all & (0xffffffffu << lo));
+            }
+            const uint32_t visit_mask = warp_transpose32(mine_all, lane);
+            const int cnt = __popc(visit_mask);
+            int cum = cnt;
+#pragma unroll
+            for (int dd = 1; dd < 32; dd <<= 1) {
+                const int n = __shfl_up_sync(0xffffffffu, cum, dd);
+                if (lane >= dd) cum += n;
+            }
             int v0 = 0;      // visits [v0, v0 + g) of this chunk form the current group
             while (v0 < g_max) {
-            uint32_t mine = 0, visit_mask = 0;
-            int rows = 0, g = 0;
-            while (v0 + g < g_max) {
-                const int j = my_hits[base + v0 + g];
-                const bool valid = ((__shfl_sync(0xffffffffu, pm, v0 + g) >> lane) & 1u) &&
-                                   (idx_base - (uint32_t)j < (uint32_t)last_contributor);
-                const uint32_t m = __ballot_sync(0xffffffffu, valid);
-                const int c = __popc(m);
-                if (rows + c > BWD_CAP) break;      // the table is full (a visit alone always fits): next group
-                if (lane == g) visit_mask = m;
-                mine |= (valid ? 1u : 0u) << g;
-                rows += c;
-                g++;
-            }
+            // the group: as many visits from v0 on as the table holds (a visit alone always fits)
+            const int before = v0 ? __shfl_sync(0xffffffffu, cum, v0 - 1) : 0;
+            const int g = __popc(__ballot_sync(0xffffffffu, lane >= v0 && lane < g_max && cum - before <= BWD_CAP));
+            const int rows = __shfl_sync(0xffffffffu, cum, v0 + g - 1) - before;
+            uint32_t mine = (mine_all >> v0) & (g == 32 ? 0xffffffffu : ((1u << g) - 1u));
             if (rows) {
-                // first row of visit v = contributions of the visits before it (exclusive scan over the lanes)
-                const int cnt = __popc(visit_mask);
-                int incl = cnt;
-#pragma unroll
-                for (int dd = 1; dd < 32; dd <<= 1) {
-                    const int n = __shfl_up_sync(0xffffffffu, incl, dd);
-                    if (lane >= dd) incl += n;
-                }
-                const int first_row = incl - cnt;
+                const int first_row = cum - cnt - before;      // of visit `lane`, for the lanes of this group
 
                 // ---- phase 2: every lane walks its own contributors, back to front, and stages their terms
                 if (CGX_EXPERIMENT & 2) mine = 0;
@@ -986,8 +1001,8 @@ render_bwd2_kernel(const uint2* __restrict__ ranges, const uint32_t* __restrict_
                     const bool act = mine != 0;
                     if (!__any_sync(0xffffffffu, act)) break;
                     const int v = act ? __ffs(mine) - 1 : 0;
-                    const uint32_t mv = __shfl_sync(0xffffffffu, visit_mask, v);
-                    const int rv = __shfl_sync(0xffffffffu, first_row, v);
+                    const uint32_t mv = __shfl_sync(0xffffffffu, visit_mask, v0 + v);
+                    const int rv = __shfl_sync(0xffffffffu, first_row, v0 + v);
                     if (act) {
                         mine &= mine - 1;
                         const int j = my_hits[base + v0 + v];
@@ -1009,8 +1024,8 @@ render_bwd2_kernel(const uint2* __restrict__ ranges, const uint32_t* __restrict_
                 // add the totals to the Gaussian's gradient with one atomic per term
                 for (int quad0 = 0; quad0 < ((CGX_EXPERIMENT & 4) ? 0 : g); quad0 += 4) {
                     const int v = quad0 + quarter;    // v >= g (last, partial quad) reads an empty mask
-                    const uint32_t mv = __shfl_sync(0xffffffffu, visit_mask, v & 31);
-                    const int rv = __shfl_sync(0xffffffffu, first_row, v & 31);
+                    const uint32_t mv = __shfl_sync(0xffffffffu, visit_mask, (v0 + v) & 31);
+                    const int rv = __shfl_sync(0xffffffffu, first_row, (v0 + v) & 31);
                     const int n = v < g ? __popc(mv) : 0;
                     if (n) {
                         const float2* p = reinterpret_cast<const float2*>(stage + rv * BWD_RS + term2);
