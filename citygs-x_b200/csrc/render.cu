@@ -1021,13 +1021,21 @@ render_bwd2_kernel(const uint2* __restrict__ ranges, const uint32_t* __restrict_
                 __syncwarp();
 
                 // ---- phase 3: four visits at a time, a quarter-warp each, lane = two terms: sum the visit's rows and
-                // add the totals to the Gaussian's gradient with one atomic per term
-                for (int quad0 = 0; quad0 < ((CGX_EXPERIMENT & 4) ? 0 : g); quad0 += 4) {
-                    const int v = quad0 + quarter;    // v >= g (last, partial quad) reads an empty mask
-                    const uint32_t mv = __shfl_sync(0xffffffffu, visit_mask, (v0 + v) & 31);
-                    const int rv = __shfl_sync(0xffffffffu, first_row, (v0 + v) & 31);
-                    const int n = v < g ? __popc(mv) : 0;
-                    if (n) {
+                // add the totals to the Gaussian's gradient with one atomic per term.  Visits without rows (no pixel
+                // above the alpha threshold, or all of them behind their last contributor) are skipped: the quarters
+                // take the next four visits that have some.
+                uint32_t todo = __ballot_sync(0xffffffffu, lane >= v0 && lane < v0 + g && cnt > 0);
+                if (CGX_EXPERIMENT & 4) todo = 0;
+                while (todo) {
+                    uint32_t t = todo;
+                    if (quarter >= 1) t &= t - 1;
+                    if (quarter >= 2) t &= t - 1;
+                    if (quarter >= 3) t &= t - 1;
+                    const int src = t ? __ffs(t) - 1 : 0;       // lane (= visit of the chunk) this quarter sums
+                    const uint32_t mv = __shfl_sync(0xffffffffu, visit_mask, src);
+                    const int rv = __shfl_sync(0xffffffffu, first_row, src);
+                    if (t) {
+                        const int n = __popc(mv);
                         const float2* p = reinterpret_cast<const float2*>(stage + rv * BWD_RS + term2);
                         float2 sum = p[0];
                         for (int r = 1; r < n; r++) {
@@ -1035,11 +1043,15 @@ render_bwd2_kernel(const uint2* __restrict__ ranges, const uint32_t* __restrict_
                             sum.x += x.x;
                             sum.y += x.y;
                         }
-                        const size_t gid = (size_t)ids[my_hits[base + v0 + v]];
+                        const size_t gid = (size_t)ids[my_hits[base + src]];
                         const bool go = !(CGX_EXPERIMENT & 8) || sum.x == 1.2345e-33f;
                         if (my_ptr0 && go) atomicAdd(my_ptr0 + gid * my_stride0, sum.x);
                         if (my_ptr1 && go) atomicAdd(my_ptr1 + gid * my_stride1, sum.y);
                     }
+                    todo &= todo - 1;
+                    todo &= todo - 1;
+                    todo &= todo - 1;
+                    todo &= todo - 1;
                 }
                 __syncwarp();
             }
