@@ -499,7 +499,7 @@ def run_reference_arm(a):
 # ----------------------------------------------------------------------------- our arm
 # ncu capture of one launch each, one camera of the default workload (GB moved / GB algorithmic)
 NCU_BWD_TRAFFIC, NCU_BWD_ALGO = 1.80, 0.827
-NCU_FWD_TRAFFIC, NCU_FWD_ALGO = 0.430, 0.348
+NCU_FWD_TRAFFIC, NCU_FWD_ALGO = 0.432, 0.348
 
 ALGO_BYTES = {
     # algorithmic bytes per launch (API-boundary tensors touched once); HW = pixels of the locally rendered tiles
@@ -528,10 +528,10 @@ DRAM_TRAFFIC_PER_ALGO_BYTE = {"cgx_render_bwd": NCU_BWD_TRAFFIC / NCU_BWD_ALGO, 
 
 # ncu counters of one launch of each blending kernel on one camera of the default workload (the same captures)
 NCU_PIPE_COUNTERS = {
-    "cgx_render_bwd": {"issue_active_pct": 65.6, "pipe_fma_pct": 28.9, "dram_throughput_pct": 15.8,
-                       "warp_instructions": 1.047e9},
-    "cgx_render_fwd": {"issue_active_pct": 81.1, "pipe_fma_pct": 33.5, "dram_throughput_pct": 9.3,
-                       "warp_instructions": 0.514e9},
+    "cgx_render_bwd": {"issue_active_pct": 67.7, "pipe_fma_pct": 32.4, "dram_throughput_pct": 17.9,
+                       "warp_instructions": 0.949e9},
+    "cgx_render_fwd": {"issue_active_pct": 78.4, "pipe_fma_pct": 35.2, "dram_throughput_pct": 9.9,
+                       "warp_instructions": 0.470e9},
 }
 
 # FP32 instruction issue peak: 148 SMs x 128 FP32 lanes x 1.965 GHz (one FMA = one instruction)
@@ -862,7 +862,7 @@ def main():
     # ---- the reference's own CUDA extension on the same GPU, same workload (rank 0, N=1 only)
     ref_gpu = None
     if rank == 0 and world == 1 and not a.no_ref_gpu:
-        ref_gpu = measure_reference_gpu(a, g, cams, dev, min(a.steps, 5), 3, e2e=False)
+        ref_gpu = measure_reference_gpu(a, g, cams, dev, min(a.steps, 10), 3, e2e=False)
 
     # ---- CPU baseline (rank 0, N=1 only): bounded sample
     cpu = None
