@@ -112,24 +112,50 @@ __global__ void __launch_bounds__(CGX_BLOCK_SIZE)
 tile_count_kernel(int P, int gx, int gy, const int* __restrict__ radii, const float2* __restrict__ means2D,
                   const uint8_t* __restrict__ local, uint32_t* __restrict__ tiles_touched,
                   uint32_t* __restrict__ block_sums, const MaskBand* __restrict__ band_ptr,
-                  const float* __restrict__ depths, uint32_t* __restrict__ depth_range)
+                  const float* __restrict__ depths, uint32_t* __restrict__ depth_range, const int vec_ok)
 {
     __shared__ uint32_t s_warp[8];
     const MaskBand band = *band_ptr;
     const int base = blockIdx.x * SCAN_TILE;
     uint32_t sum = 0;
     uint32_t dmin = 0xffffffffu, dmax = 0u;     // bit patterns of the depths of the splats that emit keys
+    // a thread owns SCAN_ITEMS consecutive Gaussians: its loads and its store are 128-bit wide
+    const int idx0 = base + threadIdx.x * SCAN_ITEMS;
+    if (idx0 + SCAN_ITEMS <= P && vec_ok) {
+        const float4 m01 = *reinterpret_cast<const float4*>(means2D + idx0);
+        const float4 m23 = *reinterpret_cast<const float4*>(means2D + idx0 + 2);
+        const int4 rad = *reinterpret_cast<const int4*>(radii + idx0);
+        uint4 c;
+        c.x = count_local_tiles(make_float2(m01.x, m01.y), rad.x, local, gx, gy, band);
+        c.y = count_local_tiles(make_float2(m01.z, m01.w), rad.y, local, gx, gy, band);
+        c.z = count_local_tiles(make_float2(m23.x, m23.y), rad.z, local, gx, gy, band);
+        c.w = count_local_tiles(make_float2(m23.z, m23.w), rad.w, local, gx, gy, band);
+        *reinterpret_cast<uint4*>(tiles_touched + idx0) = c;
+        sum = c.x + c.y + c.z + c.w;
+        if (depths && sum) {
+            const float4 d = *reinterpret_cast<const float4*>(depths + idx0);
+            const uint32_t cs[4] = {c.x, c.y, c.z, c.w};
+            const float ds[4] = {d.x, d.y, d.z, d.w};
 #pragma unroll
-    for (int k = 0; k < SCAN_ITEMS; k++) {
-        const int idx = base + k * CGX_BLOCK_SIZE + threadIdx.x;
-        if (idx < P) {
-            const uint32_t c = count_local_tiles(means2D[idx], radii[idx], local, gx, gy, band);
-            tiles_touched[idx] = c;
-            sum += c;
-            if (depths && c) {
-                const uint32_t b = __float_as_uint(depths[idx]);
-                dmin = min(dmin, b);
-                dmax = max(dmax, b);
+            for (int k = 0; k < SCAN_ITEMS; k++)
+                if (cs[k]) {
+                    const uint32_t b = __float_as_uint(ds[k]);
+                    dmin = min(dmin, b);
+                    dmax = max(dmax, b);
+                }
+        }
+    } else {
+        for (int k = 0; k < SCAN_ITEMS; k++) {
+            const int idx = idx0 + k;
+            if (idx < P) {
+                const uint32_t c = count_local_tiles(means2D[idx], radii[idx], local, gx, gy, band);
+                tiles_touched[idx] = c;
+                sum += c;
+                if (depths && c) {
+                    const uint32_t b = __float_as_uint(depths[idx]);
+                    dmin = min(dmin, b);
+                    dmax = max(dmax, b);
+                }
             }
         }
     }
@@ -225,42 +251,60 @@ emit_keys_kernel(int P, int gx, int gy, const int* __restrict__ radii, const flo
                  const float* __restrict__ depths, const uint32_t* __restrict__ tiles_touched,
                  const uint8_t* __restrict__ local, const uint32_t* __restrict__ block_prefix,
                  uint32_t* __restrict__ point_offsets, uint64_t* __restrict__ keys, uint32_t* __restrict__ values,
-                 uint32_t capacity, const MaskBand* __restrict__ band_ptr)
+                 uint32_t capacity, const MaskBand* __restrict__ band_ptr, const int vec_ok)
 {
     __shared__ uint32_t s_warp[8];
     const MaskBand band = *band_ptr;
     const int base = blockIdx.x * SCAN_TILE;
-    uint32_t running = block_prefix[blockIdx.x];
+    // a thread owns SCAN_ITEMS consecutive Gaussians (as in the counting kernel): one CTA-wide scan of the threads'
+    // sums gives every thread its first output position, the counts inside the thread give the rest
+    const int idx0 = base + threadIdx.x * SCAN_ITEMS;
+    const bool vec = idx0 + SCAN_ITEMS <= P && vec_ok;
+    uint32_t c[SCAN_ITEMS];
+    if (vec) {
+        const uint4 t = *reinterpret_cast<const uint4*>(tiles_touched + idx0);
+        c[0] = t.x; c[1] = t.y; c[2] = t.z; c[3] = t.w;
+    } else {
+#pragma unroll
+        for (int k = 0; k < SCAN_ITEMS; k++) c[k] = idx0 + k < P ? tiles_touched[idx0 + k] : 0;
+    }
+    uint32_t total;
+    uint32_t off = block_prefix[blockIdx.x] + block_excl_scan(c[0] + c[1] + c[2] + c[3], s_warp, total);
+    if (vec) {
+        *reinterpret_cast<uint4*>(point_offsets + idx0) =
+            make_uint4(off + c[0], off + c[0] + c[1], off + c[0] + c[1] + c[2], off + c[0] + c[1] + c[2] + c[3]);
+    } else {
+        uint32_t run = off;
+        for (int k = 0; k < SCAN_ITEMS; k++)
+            if (idx0 + k < P) {
+                run += c[k];
+                point_offsets[idx0 + k] = run;
+            }
+    }
+    if (c[0] + c[1] + c[2] + c[3] == 0) return;
 #pragma unroll 1
     for (int k = 0; k < SCAN_ITEMS; k++) {
-        const int idx = base + k * CGX_BLOCK_SIZE + threadIdx.x;
-        const uint32_t c = idx < P ? tiles_touched[idx] : 0;
-        uint32_t total;
-        uint32_t off = running + block_excl_scan(c, s_warp, total);
-        running += total;
-        if (idx < P) {
-            point_offsets[idx] = off + c;
-            if (c > 0) {
-                const float2 xy = means2D[idx];
-                uint2 rect_min, rect_max;
-                get_rect(xy, radii[idx], rect_min, rect_max, gx, gy);
-                const uint64_t dbits = (uint64_t)__float_as_uint(depths[idx]);
-                // a band of whole rows: its rows of the rectangle are local, the others are not
-                const int y0 = band.valid ? max((int)rect_min.y, band.row0) : (int)rect_min.y;
-                const int y1 = band.valid ? min((int)rect_max.y, band.row1) : (int)rect_max.y;
-                for (int y = y0; y < y1; y++)
-                    for (int x = rect_min.x; x < rect_max.x; x++)
-                        if (band.valid || local[y * gx + x]) {
-                            if (off < capacity) {
-                                uint64_t key = y * gx + x;
-                                key <<= 32;
-                                key |= dbits;
-                                keys[off] = key;
-                                values[off] = idx;
-                            }
-                            off++;
+        const int idx = idx0 + k;
+        if (c[k] > 0) {
+            const float2 xy = means2D[idx];
+            uint2 rect_min, rect_max;
+            get_rect(xy, radii[idx], rect_min, rect_max, gx, gy);
+            const uint64_t dbits = (uint64_t)__float_as_uint(depths[idx]);
+            // a band of whole rows: its rows of the rectangle are local, the others are not
+            const int y0 = band.valid ? max((int)rect_min.y, band.row0) : (int)rect_min.y;
+            const int y1 = band.valid ? min((int)rect_max.y, band.row1) : (int)rect_max.y;
+            for (int y = y0; y < y1; y++)
+                for (int x = rect_min.x; x < rect_max.x; x++)
+                    if (band.valid || local[y * gx + x]) {
+                        if (off < capacity) {
+                            uint64_t key = y * gx + x;
+                            key <<= 32;
+                            key |= dbits;
+                            keys[off] = key;
+                            values[off] = idx;
                         }
-            }
+                        off++;
+                    }
         }
     }
 }
@@ -1269,8 +1313,9 @@ static int bin_count_scan(int P, int W, int H, const int32_t* radii, const float
     MaskBand* band = (MaskBand*)((char*)workspace + bin_band_offset(P));
     uint32_t* block_ranges = depths ? (uint32_t*)((char*)workspace + bin_band_offset(P) + 256) : nullptr;
     analyse_mask_kernel<<<1, 1024, 0, st>>>(gx, gy, compute_locally, band);
+    const int vec_ok = aligned16(radii) && aligned16(means2D) && aligned16(tiles_touched) && (!depths || aligned16(depths));
     tile_count_kernel<<<nblocks, CGX_BLOCK_SIZE, 0, st>>>(P, gx, gy, radii, (const float2*)means2D, compute_locally,
-                                                          tiles_touched, sums, band, depths, block_ranges);
+                                                          tiles_touched, sums, band, depths, block_ranges, vec_ok);
     scan_partials_kernel<<<1, 1024, 0, st>>>(nblocks, sums, num_rendered, block_ranges);
     return check_launch(3);
 }
@@ -1306,7 +1351,8 @@ extern "C" int cgx_emit_keys(int P, int W, int H, const int32_t* radii, const fl
     emit_keys_kernel<<<nblocks, CGX_BLOCK_SIZE, 0, (cudaStream_t)stream>>>(
         P, gx, gy, radii, (const float2*)means2D, depths, tiles_touched, compute_locally, (const uint32_t*)workspace,
         point_offsets, keys, values, (uint32_t)capacity,
-        (const MaskBand*)((const char*)workspace + bin_band_offset(P)));
+        (const MaskBand*)((const char*)workspace + bin_band_offset(P)),
+        aligned16(tiles_touched) && aligned16(point_offsets) ? 1 : 0);
     return check_launch();
 }
 
