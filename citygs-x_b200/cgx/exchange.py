@@ -551,6 +551,15 @@ def _camera_order(strategies, me, ws):
     return sorted(range(len(strategies)), key=lambda k: ((strategies[k].gpu_ids[0] - me - 1) % ws, k))
 
 
+def _destination_rows(field_ptr, first_row, cam, dst, planes):
+    """Rows of struct cgx_peer_camera_dst for the (camera, rendering rank) pairs (cam[e], dst[e]): the addresses of
+    the camera's tensors in that rank's arena (field_ptr[rank, camera, field]) and the first row this rank writes."""
+    rows = np.zeros((cam.size, 10), dtype=np.uint64)
+    rows[:, [0, 1, 2, 9, 6, 7] if planes else list(range(8))] = field_ptr[dst, cam, :]
+    rows[:, 8] = first_row[dst, cam]
+    return rows
+
+
 def _p2p_forward(plan):
     """Pack this rank's rows into the peers' receive arenas, wait until every rank's rows have landed, and return
     (per-camera views of this rank's arena, the non-differentiable ones among them)."""
@@ -567,9 +576,7 @@ def _p2p_forward(plan):
     if prep is not None:
         # destination rows of every (camera, rendering rank) pair at once, in the prepared camera order
         cam, dst = prep["entry_cam"], prep["entry_dst"]
-        rows = np.zeros((cam.size, 10), dtype=np.uint64)      # rows = struct cgx_peer_camera_dst
-        rows[:, [0, 1, 2, 9, 6, 7] if planes else list(range(8))] = field_ptr[dst, cam, :]
-        rows[:, 8] = plan["first_row"][dst, cam]
+        rows = _destination_rows(field_ptr, plan["first_row"], cam, dst, planes)
         be.pack_p2p_prepared(prep, rows, plan["send_off"][dst, cam], plan["send_index"])
     else:
         cameras = []

@@ -270,3 +270,49 @@ def test_p2p_layout_is_consistent_across_ranks():
                 for k in range(bsz):
                     assert lays[me]["grad_row"][i, k] == order[me * bsz + k]
             assert S[i].sum() <= L["grad_rows_max"]
+
+
+def test_store_order_and_destination_rows_of_the_pack_launch():
+    """Host side of the peer-to-peer pack launch: every rank works through the cameras starting with those the rank
+    after it renders (no two ranks store into the same peer at the same time while each rank renders the same number
+    of cameras), and the destination rows built for all (camera, rank) pairs at once equal the per-camera tables."""
+    import numpy as np
+    from types import SimpleNamespace as NS
+    from cgx import exchange as EX
+
+    ws, bsz = 4, 8
+    strategies = [NS(gpu_ids=[k // 2]) for k in range(bsz)]            # two whole cameras per rank
+    orders = [EX._camera_order(strategies, me, ws) for me in range(ws)]
+    for me, order in enumerate(orders):
+        assert sorted(order) == list(range(bsz))
+        assert [strategies[k].gpu_ids[0] for k in order[-2:]] == [me, me]          # its own cameras last
+    for slot in range(bsz):                                                          # at any time: four different peers
+        assert len({strategies[orders[me][slot]].gpu_ids[0] for me in range(ws)}) == ws
+    # a camera cut between ranks 1 and 2 is ordered by its first rank
+    cut = [NS(gpu_ids=[0]), NS(gpu_ids=[1, 2]), NS(gpu_ids=[3])]
+    assert EX._camera_order(cut, 0, ws) == [1, 2, 0]
+    assert EX._camera_order(cut, 2, ws) == [2, 0, 1]
+
+    rng = np.random.default_rng(9)
+    S = rng.integers(1, 300, size=(ws, ws, 3))
+    for planes, fields in ((True, EX._CAM_FIELDS_PLANES), (False, EX._CAM_FIELDS)):
+        lay = EX.p2p_layout(S, 1, fields)
+        peer_base = np.arange(ws, dtype=np.int64) * (1 << 32) + 4096
+        field_ptr = peer_base[:, None, None] + lay["cam_base"][:, :, None] + lay["field_off"]
+        order = EX._camera_order(cut, 1, ws)
+        ids = [cut[k].gpu_ids for k in order]
+        cam = np.repeat(np.asarray(order, dtype=np.int64), [len(i) for i in ids])
+        dst = np.concatenate([np.asarray(i, dtype=np.int64) for i in ids])
+        rows = EX._destination_rows(field_ptr, lay["first_row"], cam, dst, planes)
+        at = 0
+        for k in order:                                                # the per-camera construction
+            for j in cut[k].gpu_ids:
+                want = np.zeros(10, dtype=np.uint64)
+                if planes:
+                    want[[0, 1, 2, 9, 6, 7]] = field_ptr[j, k, :]
+                else:
+                    want[:8] = field_ptr[j, k, :]
+                want[8] = lay["first_row"][j, k]
+                assert np.array_equal(rows[at], want)
+                at += 1
+        assert at == rows.shape[0] == 4
