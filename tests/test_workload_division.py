@@ -129,3 +129,40 @@ def test_distribution_config_table():
     assert len(cfg.local_running_time_mode) == 4
     with pytest.raises(ValueError):
         init_image_distribution_config(SimpleNamespace(image_distribution_mode="final"))
+
+
+def test_balancer_follows_the_reference_step_by_step():
+    """tests/golden/division_golden.json holds what the reference's own start_strategy_final / finish_strategy_final
+    did over a few steps of four scenarios (cuts moving with measured times, decay, images too small to update,
+    local sampling), made by tests/golden/make_division_golden.py.  The same time tables through this module must
+    give the same ranks, cuts and task lists at every step, the same log, and the same heuristics to float rounding."""
+    import json
+    from pathlib import Path
+    from types import SimpleNamespace as NS
+
+    golden = json.loads((Path(__file__).resolve().parent / "golden" / "division_golden.json").read_text())
+    assert len(golden) == 4
+    moved = False
+    for g in golden:
+        sc = g["scenario"]
+        ctx = WD.DivisionContext(image_height=sc["H"], image_width=sc["W"], rank=0, world_size=sc["ws"],
+                                 bsz=sc["bsz"], local_sampling=sc["local_sampling"],
+                                 border_divpos_coeff=sc["border"], heuristic_decay=sc["decay"],
+                                 adjust_strategy_warmp_iterations=sc["warm"])
+        cams = [NS(uid=100 + k) for k in range(sc["n_cams"])]
+        history = WD.DivisionStrategyHistoryFinal(cams, sc["ws"], 0, ctx=ctx)
+        for step in g["steps"]:
+            ctx.iteration = step["iteration"]
+            strategies, tasks = WD.start_strategy_final(cams, history, ctx=ctx)
+            assert [list(s.gpu_ids) for s in strategies] == step["gpu_ids"], (sc["name"], step["iteration"])
+            assert [list(map(int, s.division_pos)) for s in strategies] == step["division_pos"], (sc["name"], step["iteration"])
+            assert [[list(map(int, t)) for t in ts] for ts in tasks] == step["tasks"]
+            WD.finish_strategy_final(cams, history, strategies, None, ctx=ctx, gathered_times=step["table"])
+            for cam, want in zip(cams, step["heuristic"]):
+                got = history.accum_heuristic[cam.uid]
+                assert torch.allclose(got, torch.tensor(want), rtol=1e-6, atol=1e-9), (sc["name"], step["iteration"])
+            assert history.history[-1]["all_gpu_running_time"] == pytest.approx(step["log"], rel=1e-12)
+            assert history.history[-1]["iteration"] == step["iteration"]
+        if g["steps"][0]["division_pos"] != g["steps"][-1]["division_pos"]:
+            moved = True
+    assert moved, "no scenario of the golden file ever moved a cut"
