@@ -78,6 +78,9 @@ def _worker(rank, ws, port, out_dir):
         m2r, rgbr, cor, radr, depr, m3r, scr, rotr, sizes, sent, send_index, stats = out
 
         result = {"sizes": sizes, "strategies": [(s.gpu_ids, s.division_pos) for s in strategies], "renders": {}}
+        # every received tensor of every camera, as the reference returns them (for the golden comparison)
+        result["received_all"] = [[t[k].detach().clone() for t in (m2r, rgbr, cor, radr, depr, m3r, scr, rotr)]
+                                  for k in range(len(cams))]
         heads = []
         for k, cam in enumerate(cams):
             local = strategies[k].get_compute_locally()
@@ -316,3 +319,34 @@ def test_store_order_and_destination_rows_of_the_pack_launch():
                 assert np.array_equal(rows[at], want)
                 at += 1
         assert at == rows.shape[0] == 4
+
+
+def _digest(t):
+    import hashlib
+
+    t = t.detach().contiguous()
+    return [str(t.dtype), list(t.shape), hashlib.sha256(t.numpy().tobytes()).hexdigest()]
+
+
+def test_exchange_equals_the_reference_function(two_rank_run):
+    """tests/golden/exchange_golden.json: digests of what the reference's OWN all_to_all_communication_final
+    (gaussian_renderer/__init__.py:596-786, run on two gloo ranks by tests/golden/make_exchange_golden.py on this same
+    scene, strategies and loss) returned and back-propagated.  The exchange moves rows and adds gradient rows that
+    meet at their owner: every tensor must agree bit for bit."""
+    import json
+
+    golden = json.loads((ROOT / "tests" / "golden" / "exchange_golden.json").read_text())
+    assert golden["n_gaussians"] == N_GAUSS and golden["res"] == list(RES)
+    for rank, run in enumerate(two_rank_run):
+        want = golden["ranks"][rank]
+        assert run["sizes"] == want["sizes"]
+        for k, tensors in enumerate(run["received_all"]):
+            for name, t, w in zip(("means2D", "rgb", "conic_opacity", "radii", "depths", "means3D", "scales", "rotations"),
+                                  tensors, want["received"][k]):
+                assert _digest(t) == w, (rank, k, name)
+        for k, grads in enumerate(run["grads"]):
+            for name, gt, w in zip(("means2D", "rgb", "conic_opacity", "means3D", "scales", "rotations"), grads,
+                                   want["grads"][k]):
+                assert _digest(gt) == w, (rank, k, name)
+    assert sum(w[1][0] for r in golden["ranks"] for cam in r["received"] for w in cam[:1]) > 1000
+
