@@ -110,8 +110,13 @@ def _worker(rank, ws, port, out_dir):
 @pytest.fixture(scope="module")
 def two_rank_run(tmp_path_factory):
     out = tmp_path_factory.mktemp("gloo")
-    port = _free_port()
-    mp.spawn(_worker, args=(2, port, str(out)), nprocs=2, join=True)
+    for attempt in range(2):              # the rendezvous port can be taken between its choice and its use: once more
+        try:
+            mp.spawn(_worker, args=(2, _free_port(), str(out)), nprocs=2, join=True)
+            break
+        except Exception:
+            if attempt:
+                raise
     return [torch.load(out / f"rank{r}.pt", weights_only=False) for r in range(2)]
 
 

@@ -58,7 +58,13 @@ def _worker(rank, ws, port, out_dir, sizes):
 def test_two_gloo_ranks_match_the_reference_loops(tmp_path, sizes):
     from oracle.exchange_backend import redistribute_reference
 
-    mp.spawn(_worker, args=(2, _free_port(), str(tmp_path), sizes), nprocs=2, join=True)
+    for attempt in range(2):              # the rendezvous port can be taken between its choice and its use: once more
+        try:
+            mp.spawn(_worker, args=(2, _free_port(), str(tmp_path), sizes), nprocs=2, join=True)
+            break
+        except Exception:
+            if attempt:
+                raise
     parts = [torch.load(tmp_path / f"rank{r}.pt", weights_only=False) for r in range(2)]
     per_rank = [_states(r, sizes[r]) for r in range(2)]
     want = redistribute_reference([s for s, _ in per_rank], [d for _, d in per_rank])
