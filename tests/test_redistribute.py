@@ -117,3 +117,31 @@ def test_kernels_on_one_gpu(n, cuda_device):
     bad[n // 2] = ws
     counts, _ = be.count(bad, ws)
     assert int(counts[ws]) == 1
+
+
+def test_two_gloo_ranks_match_the_reference_method(tmp_path):
+    """tests/golden/redistribute_golden.json: digests of what the reference's OWN `all2all_gaussian_state`
+    (scene/gaussian_model.py:1485-1515, run on two gloo ranks by tests/golden/make_redistribute_golden.py on these
+    states and destinations) leaves on every rank.  One packed exchange here, eight list all-to-alls there: the same
+    rows in the same order, bit for bit."""
+    import hashlib
+    import json
+
+    golden = json.loads((ROOT / "tests" / "golden" / "redistribute_golden.json").read_text())
+    sizes = tuple(golden["sizes"])
+    for attempt in range(2):
+        try:
+            mp.spawn(_worker, args=(2, _free_port(), str(tmp_path), sizes), nprocs=2, join=True)
+            break
+        except Exception:
+            if attempt:
+                raise
+    for r in range(2):
+        part = torch.load(tmp_path / f"rank{r}.pt", weights_only=False)
+        want = golden["ranks"][r]
+        assert part["table"] == want["table"]
+        assert len(part["out"]) == len(want["out"]) == 8
+        for t, w in zip(part["out"], want["out"]):
+            t = t.detach().contiguous()
+            raw = t.view(torch.uint8) if t.dtype == torch.bool else t
+            assert [str(t.dtype), list(t.shape), hashlib.sha256(raw.numpy().tobytes()).hexdigest()] == w
