@@ -355,3 +355,56 @@ def test_exchange_equals_the_reference_function(two_rank_run):
                 assert _digest(gt) == w, (rank, k, name)
     assert sum(w[1][0] for r in golden["ranks"] for cam in r["received"] for w in cam[:1]) > 1000
 
+
+
+def test_prepared_pack_launch_passes_the_same_tables(monkeypatch):
+    """The pack launch prepared while the size table is in flight (static part first, destination rows of all
+    cameras at once afterwards) must hand the library the same camera table and destination rows as the launch built
+    camera by camera.  Host code only: the library call is intercepted, the tensors are CPU stand-ins."""
+    import ctypes as C
+
+    import numpy as np
+    from cgx import exchange as EX
+    from diff_gaussian_rasterization import _C
+
+    seen = []
+
+    def capture(name, fn, n, table_ptr, send_index_ptr, stream, **kw):
+        table = np.ctypeslib.as_array(C.cast(table_ptr, C.POINTER(C.c_uint64)), shape=(n, 19)).copy()
+        rows = []
+        for row in table:
+            ws = int(row[3])
+            dst = np.ctypeslib.as_array(C.cast(int(row[14]), C.POINTER(C.c_uint64)), shape=(ws, 10)).copy()
+            offs = np.ctypeslib.as_array(C.cast(int(row[15]), C.POINTER(C.c_int64)), shape=(ws,)).copy()
+            rows.append((dst, offs))
+        seen.append((name, table, rows))
+
+    monkeypatch.setattr(_C, "_call", capture)
+    monkeypatch.setattr(EX.CudaPackBackend, "_st", staticmethod(lambda: None))
+    be = EX.CudaPackBackend()
+    gen = torch.Generator().manual_seed(2)
+    P, ids = 50, [[0], [1, 2], [3]]
+    cams = []
+    for k, i in enumerate(ids):
+        params = (torch.rand(P, 2, generator=gen), torch.rand(P, 3, generator=gen), torch.rand(P, 4, generator=gen),
+                  torch.ones(P, dtype=torch.int32), torch.rand(P, generator=gen), torch.rand(P, 5, generator=gen))
+        cams.append(dict(params=params, bounds=torch.arange(len(i) + 1, dtype=torch.int32) * 10, H=160 + k, W=128,
+                         avoid=bool(k & 1), workspace=torch.zeros(64, dtype=torch.uint8)))
+    order = [1, 2, 0]
+    rng = np.random.default_rng(4)
+    dst_tables = [rng.integers(1, 1 << 40, size=(len(i), 10)).astype(np.uint64) for i in ids]
+    row_offsets = [rng.integers(0, 1000, size=(len(i),)).astype(np.int64) for i in ids]
+    send_index = torch.zeros(10, dtype=torch.int32)
+    # camera by camera
+    be.pack_p2p_batched([dict(cams[k], dst_table=dst_tables[k], row_offsets=row_offsets[k]) for k in order], send_index)
+    # prepared
+    prep = be.prepare_pack_p2p(cams, order)
+    be.pack_p2p_prepared(prep, np.concatenate([dst_tables[k] for k in order]),
+                         np.concatenate([row_offsets[k] for k in order]), send_index)
+    (name_a, table_a, rows_a), (name_b, table_b, rows_b) = seen
+    assert name_a == name_b == "cgx_local2j_pack_p2p_batched"
+    keep = [c for c in range(19) if c not in (14, 15)]           # 14 / 15 are the addresses of the two side arrays
+    assert np.array_equal(table_a[:, keep], table_b[:, keep])
+    assert [int(r[3]) for r in table_b] == [len(ids[k]) for k in order]
+    for (dst_a, offs_a), (dst_b, offs_b) in zip(rows_a, rows_b):
+        assert np.array_equal(dst_a, dst_b) and np.array_equal(offs_a, offs_b)
